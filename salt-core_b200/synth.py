@@ -1,0 +1,114 @@
+"""Seeded synthetic tensors with the shapes and value distributions of the
+benchmark configurations (no real checkpoints are involved anywhere).
+
+Affine-Q4 tensors follow the reference storage format
+(include/salt/kernels.h:117-130): eight 4-bit codes per little-endian uint32,
+low nibble first, packed along K; one bf16 scale and one bf16 bias per 64
+consecutive elements (row-major, absolute group index); w = q*scale + bias.
+
+An expert occupies one contiguous slot ``gate | up | down``, each tensor stored
+as ``values | scales | biases`` -- the slot order of the reference's expert pool
+(tools/gemma4-mlx4-source.py:180-199).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+
+GROUP = 64
+
+
+def bf16_round(x: np.ndarray) -> np.ndarray:
+    """fp32 -> bf16 bits (round to nearest even), returned as uint16."""
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    u = u + 0x7FFF + ((u >> 16) & 1)
+    return (u >> 16).astype(np.uint16)
+
+
+def bf16_to_f32(h: np.ndarray) -> np.ndarray:
+    return (h.astype(np.uint32) << 16).view(np.float32)
+
+
+def q4_tensor_bytes(R: int, C: int) -> tuple[int, int]:
+    """(value bytes, scale bytes == bias bytes) of one R x C affine-Q4 tensor."""
+    elems = R * C
+    return elems // 2, elems // GROUP * 2
+
+
+def fill_q4(rng: np.random.Generator, out: np.ndarray, R: int, C: int) -> None:
+    """Write one Q4 tensor (values|scales|biases) into the uint8 view ``out``:
+    nibbles iid uniform 0..15, scale ~ U(0.005, 0.02) rounded to bf16,
+    bias = bf16(-8*scale)."""
+    vb, gb = q4_tensor_bytes(R, C)
+    assert out.size == vb + 2 * gb
+    out[:vb] = rng.integers(0, 256, vb, dtype=np.uint8)
+    s = bf16_round(rng.uniform(0.005, 0.02, gb // 2).astype(np.float32))
+    b = bf16_round(np.float32(-8.0) * bf16_to_f32(s))
+    out[vb:vb + gb] = s.view(np.uint8)
+    out[vb + gb:] = b.view(np.uint8)
+
+
+def make_q4(rng, R, C):
+    """Stand-alone Q4 tensor: (vals uint32[R*C/8], scales uint16, biases uint16)."""
+    vb, gb = q4_tensor_bytes(R, C)
+    buf = np.empty(vb + 2 * gb, np.uint8)
+    fill_q4(rng, buf, R, C)
+    return (buf[:vb].view(np.uint32), buf[vb:vb + gb].view(np.uint16),
+            buf[vb + gb:].view(np.uint16))
+
+
+@dataclass
+class Q4MoeLayer:
+    """One MoE feed-forward layer with affine-Q4 experts, host resident."""
+    hidden: int
+    inter: int
+    n_experts: int
+    topk: int
+    eps: float
+    router_w: np.ndarray          # [E][H] fp32
+    router_scale: np.ndarray      # [H] fp32
+    per_expert_scale: np.ndarray  # [E] fp32
+    pool: np.ndarray              # uint8 [E * expert_stride]
+    expert_stride: int
+    norm_weight: np.ndarray | None = None  # [H] fp32, RMSNorm applied to this layer's output
+
+    @property
+    def tensor_bytes(self) -> int:
+        vb, gb = q4_tensor_bytes(self.inter, self.hidden)
+        return vb + 2 * gb
+
+    def tensor(self, expert: int, which: int):
+        """(vals, scales, biases) views of gate (0), up (1) or down (2)."""
+        vb, gb = q4_tensor_bytes(self.inter, self.hidden)
+        base = expert * self.expert_stride + which * (vb + 2 * gb)
+        p = self.pool
+        return (p[base:base + vb].view(np.uint32),
+                p[base + vb:base + vb + gb].view(np.uint16),
+                p[base + vb + gb:base + vb + 2 * gb].view(np.uint16))
+
+
+def make_q4_moe_layer(seed: int, hidden=2816, inter=704, n_experts=128, topk=8,
+                      eps=1e-6, router_std=0.02) -> Q4MoeLayer:
+    """Router weight fp32 N(0, router_std); router_scale = per_expert_scale = 1;
+    experts as ``fill_q4``; RMSNorm weight 1 + 0.1*N(0,1)."""
+    rng = np.random.default_rng(seed)
+    vb, gb = q4_tensor_bytes(inter, hidden)
+    tb = vb + 2 * gb
+    stride = 3 * tb
+    pool = np.empty(n_experts * stride, np.uint8)
+    for e in range(n_experts):
+        for which in range(3):
+            R, C = (inter, hidden) if which < 2 else (hidden, inter)
+            fill_q4(rng, pool[e * stride + which * tb: e * stride + (which + 1) * tb], R, C)
+    return Q4MoeLayer(
+        hidden, inter, n_experts, topk, eps,
+        router_w=(rng.standard_normal((n_experts, hidden)) * router_std).astype(np.float32),
+        router_scale=np.ones(hidden, np.float32),
+        per_expert_scale=np.ones(n_experts, np.float32),
+        pool=pool, expert_stride=stride,
+        norm_weight=(1.0 + 0.1 * rng.standard_normal(hidden)).astype(np.float32))
+
+
+def make_tokens(seed: int, B: int, hidden: int) -> np.ndarray:
+    return np.random.default_rng(seed).standard_normal((B, hidden)).astype(np.float32)

@@ -1,0 +1,149 @@
+"""Regenerate tests/golden/*.npz from the reference project's own code.
+
+Run in a container where the reference checkout is mounted and
+``make -C oracle ref`` has produced ``oracle/_ref/libsalt_ref.so`` (the
+reference sources compiled unmodified).  Every array written here is an output
+of that library; small cases also store their inputs so the fixtures do not
+depend on a PRNG implementation.
+
+    python tests/golden/make_golden.py
+"""
+import importlib
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+import oracle  # noqa: E402
+
+synth = importlib.import_module("salt-core_b200.synth")
+OUT = os.path.dirname(os.path.abspath(__file__))
+
+
+def main():
+    ref = oracle.Reference()
+    rng = np.random.default_rng(20261125)
+
+    # --- scalar math tables -------------------------------------------
+    xs = np.concatenate([np.linspace(-100, 100, 1501), np.linspace(-3, 3, 1500),
+                         [0.0, -0.0, 1.0, 88.7, -87.3, 1e-30, 3e38]]).astype(np.float32)
+    pos = np.concatenate([np.abs(xs) + np.float32(1e-6), [1.0, 1e-40, 2816.0, 704.0]]).astype(np.float32)
+    np.savez_compressed(
+        os.path.join(OUT, "bitmath.npz"), xs=xs, pos=pos,
+        expf=ref.map_f32("expf", xs), tanhf=ref.map_f32("tanhf", xs),
+        gelu_tanh=ref.map_f32("gelu_tanh", xs),
+        rsqrtf=ref.map_f32("rsqrtf", pos), sqrtf=ref.map_f32("sqrtf", pos))
+
+    # --- Q4 matvec: small cases with inputs stored ---------------------
+    q4 = {}
+    for i, (R, C, B) in enumerate([(64, 64, 1), (8, 200, 1), (3, 32, 2), (16, 2816, 3),
+                                   (40, 704, 5), (2, 8192, 1), (33, 128, 4)]):
+        n = R * C
+        vals = rng.integers(0, 2**32, (n + 7) // 8, dtype=np.uint32)
+        ng = (n + 63) // 64
+        s = synth.bf16_round(rng.uniform(0.005, 0.02, ng).astype(np.float32))
+        b = synth.bf16_round(np.float32(-8.0) * synth.bf16_to_f32(s))
+        x = rng.standard_normal((B, C)).astype(np.float32)
+        y = np.stack([ref.q4_matvec(vals, s, b, R, C, x[t]) for t in range(B)])
+        if C % 64 == 0 and R >= 16:
+            # the batch form must agree with the single-vector form bit for bit
+            # (tools/test/gemma4-bit-identity-test.c).  It is only consulted for
+            # R >= its worker count: below that the reference's x86 batch path
+            # leaves trailing rows unwritten.
+            assert (ref.q4_matvec_batch(vals, s, b, R, C, x).view(np.uint32) == y.view(np.uint32)).all()
+        q4.update({f"c{i}_shape": np.array([R, C, B]), f"c{i}_vals": vals, f"c{i}_scales": s,
+                   f"c{i}_biases": b, f"c{i}_x": x, f"c{i}_y": y})
+    q4["n_cases"] = np.array(7)
+    np.savez_compressed(os.path.join(OUT, "q4_matvec.npz"), **q4)
+
+    # --- Q4 matvec at benchmark shapes: seed + output only -------------
+    big = {}
+    for name, (R, C, seed) in {"cfg1_4096x4096": (4096, 4096, 101), "gate_704x2816": (704, 2816, 102),
+                               "down_2816x704": (2816, 704, 103), "odd_705x2816": (705, 2816, 104)}.items():
+        g = np.random.default_rng(seed)
+        vals, s, b = synth.make_q4(g, R, C)
+        x = g.standard_normal(C).astype(np.float32)
+        big[name + "_y"] = ref.q4_matvec(vals, s, b, R, C, x)
+        big[name + "_meta"] = np.array([R, C, seed])
+    np.savez_compressed(os.path.join(OUT, "q4_matvec_seeded.npz"), **big)
+
+    # --- router ----------------------------------------------------------
+    H, E, K = 96, 24, 5
+    x = rng.standard_normal((4, H)).astype(np.float32)
+    x[3] *= 37.0
+    scale = (1.0 + 0.25 * rng.standard_normal(H)).astype(np.float32)
+    W = (rng.standard_normal((E, H)) * 0.02).astype(np.float32)
+    W[7] = W[3]                                   # an exact tie: lower index must win
+    pes = (1.0 + 0.1 * rng.standard_normal(E)).astype(np.float32)
+    nw = (1.0 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+    rin, logits, sel, wts, sel_rank, wts_rank, norm = [], [], [], [], [], [], []
+    for t in range(4):
+        rc, ri = ref.router_input(x[t], scale, 1e-6); assert rc == 0
+        lg = ref.router_scores(W, None, ri)
+        rc, s_, w_ = ref.router_topk(lg, pes, K, sort_by_expert=True); assert rc == 0
+        rc, s2, w2 = ref.router_topk(lg, pes, K, sort_by_expert=False); assert rc == 0
+        rc, nm = ref.rmsnorm(x[t], nw, 1e-6, True); assert rc == 0
+        rin.append(ri); logits.append(lg); sel.append(s_); wts.append(w_)
+        sel_rank.append(s2); wts_rank.append(w2); norm.append(nm)
+    np.savez_compressed(os.path.join(OUT, "router.npz"), x=x, scale=scale, W=W, pes=pes, nw=nw,
+                        rin=np.stack(rin), logits=np.stack(logits), sel=np.stack(sel),
+                        wts=np.stack(wts), sel_rank=np.stack(sel_rank), wts_rank=np.stack(wts_rank),
+                        norm=np.stack(norm), topk=np.array(K), eps=np.float32(1e-6))
+
+    # --- grouping / reduction -----------------------------------------
+    rows, topk, ne, hid = 7, 3, 9, 5
+    selected = np.stack([rng.permutation(ne)[:topk] for _ in range(rows)]).astype(np.int32)
+    selected.sort(axis=1)
+    rin_ = rng.standard_normal((rows, hid)).astype(np.float32)
+    rc, offs, g2c, c2g, routed = ref.route_group(selected.ravel(), rows, topk, ne, rin_); assert rc == 0
+    gout = rng.standard_normal((rows * topk, hid)).astype(np.float32)
+    gw = rng.uniform(0.05, 0.5, rows * topk).astype(np.float32)
+    rc, red = ref.weighted_reduce(gw, c2g, gout, rows, topk); assert rc == 0
+    np.savez_compressed(os.path.join(OUT, "grouping.npz"), selected=selected, row_inputs=rin_, offs=offs,
+                        g2c=g2c, c2g=c2g, routed=routed, grouped_outputs=gout, weights=gw, reduced=red,
+                        n_experts=np.array(ne))
+
+    # --- NVFP4 -------------------------------------------------------------
+    R, C = 12, 96
+    wf = (rng.standard_normal((R, C)) * 0.02).astype(np.float32)
+    enc = np.array([ref.e4m3fn_encode(float(v))[1] for v in np.linspace(-500, 500, 4001).astype(np.float32)], np.uint8)
+    dec = np.array([ref.e4m3fn(c) for c in range(256)], np.float32)
+    xin = np.stack([rng.standard_normal(C), rng.standard_normal(C) * 40, np.zeros(C),
+                    rng.standard_normal(C) * 1e-3]).astype(np.float32)
+    # weights quantised with the reference's own encoders (divisor chosen so the
+    # largest block scale sits near the top of the e4m3 range)
+    amax = np.abs(wf).reshape(R, C // 16, 16).max(axis=2)
+    divisor = np.float32(448.0 * 6.0 / np.abs(wf).max())
+    wscale = np.array([[ref.e4m3fn_encode(float(np.float32(a / 6.0) * divisor))[1] for a in row] for row in amax], np.uint8)
+    codes = np.zeros((R, C), np.uint8)
+    e2 = np.array([ref.e2m1(c) for c in range(16)], np.float32)
+    for r in range(R):
+        for c in range(C):
+            sc = np.float32(ref.e4m3fn(int(wscale[r, c // 16]))) / divisor
+            t = 0.0 if sc == 0 else float(wf[r, c]) / float(sc)
+            codes[r, c] = int(np.argmin(np.abs(e2 - np.float32(np.clip(t, -6, 6)))))
+    wpacked = (codes[:, 0::2] | (codes[:, 1::2] << 4)).astype(np.uint8)
+    qp, qs, qd, ys = [], [], [], []
+    for t in range(4):
+        rc, p, s, d = ref.nvfp4_qdq(xin[t], 64.0); assert rc == 0
+        rc, y = ref.nvfp4_matvec(wpacked, wscale, float(divisor), 64.0, R, C, xin[t]); assert rc == 0
+        qp.append(p); qs.append(s); qd.append(d); ys.append(y)
+    rc, wdq = ref.nvfp4_dequant_weights(wpacked, wscale, float(divisor), R, C); assert rc == 0
+    np.savez_compressed(os.path.join(OUT, "nvfp4.npz"), enc_in=np.linspace(-500, 500, 4001).astype(np.float32),
+                        enc=enc, dec=dec, x=xin, qdq_packed=np.stack(qp), qdq_scales=np.stack(qs),
+                        qdq_dequant=np.stack(qd), wpacked=wpacked, wscale=wscale, divisor=divisor,
+                        input_global=np.float32(64.0), y=np.stack(ys), wdq=wdq)
+
+    # --- whole MoE layer, small geometry: seed + outputs -------------------
+    layer = synth.make_q4_moe_layer(7, hidden=256, inter=128, n_experts=16, topk=4)
+    xt = synth.make_tokens(8, 6, 256)
+    y, sel_, w_ = ref.moe_layer_q4(layer, xt, threads=4)
+    np.savez_compressed(os.path.join(OUT, "moe_layer_small.npz"), y=y, sel=sel_, w=w_,
+                        meta=np.array([7, 8, 6, 256, 128, 16, 4]))
+    print("golden fixtures written to", OUT)
+
+
+if __name__ == "__main__":
+    main()
