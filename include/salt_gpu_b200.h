@@ -1,0 +1,371 @@
+/* salt_gpu_b200.h -- C ABI of libsalt_gpu_b200.so, a B200 (sm_100a) physical
+ * backend for the quantized MoE feed-forward path of SALT-core.
+ *
+ * Part 1 declares the operator surface the reference engine links a GPU
+ * backend through: every symbol the reference's stub backend defines
+ * (reference src/gpu_stub.c:9-431), with the signatures of reference
+ * include/salt/gpu.h.  A reference build links this library in place of its
+ * own src/gpu_cuda.o; each declaration cites the reference line it replaces.
+ * Operations outside the MoE-FFN path are present and fail closed (-1), exactly
+ * like the stub.
+ *
+ * Part 2 is additive: device-resident entry points (salt_b200_*) so that
+ * activations need not cross PCIe between layers.  They have no counterpart
+ * in the reference.
+ *
+ * Conventions (reference include/salt/gpu.h:22-25): 0 = success, -1 =
+ * unavailable or failed, never a partial result.  Pointers in Part 1 are
+ * caller-owned HOST memory unless stated otherwise.  One calling thread at a
+ * time.  There is no CPU fallback inside this library: if no CUDA device is
+ * usable, salt_gpu_init() returns -1 and every operation fails.
+ *
+ * Deviation from the reference CUDA backend, by design: weights are COPIED into
+ * HBM when a resource is activated (the reference reads host memory zero-copy,
+ * which suits a unified-memory part and would be PCIe-bound here).  The copied
+ * bytes are reported in SaltGpuWeightResourceUsage.device_copied_weight_bytes.
+ */
+#ifndef SALT_GPU_B200_H
+#define SALT_GPU_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ====================================================================== */
+/* Part 1: the reference operator surface                                  */
+/* ====================================================================== */
+
+struct SaltTextGpuProgramOps;      /* reference include/salt/text_verify.h:746 */
+struct SaltGpuResidencyBackendOps; /* reference include/salt/gpu_residency.h:63 */
+
+/* gpu.h:102-109 */
+typedef struct SaltGpuBatchStats {
+    uint64_t arena_batches, trunk_batches, expert_layer_batches;
+    uint64_t mapped_only_misses, direct_output_batches, direct_output_jobs;
+} SaltGpuBatchStats;
+
+/* gpu.h:111-132 */
+typedef struct SaltGpuBatchStatsV2 {
+    uint64_t arena_batches, trunk_batches, expert_layer_batches;
+    uint64_t mapped_only_misses, direct_output_batches, direct_output_jobs;
+    uint64_t nvfp4_logical_packed_weight_bytes, nvfp4_logical_weight_scale_bytes;
+    uint64_t nvfp4_activation_input_bytes, nvfp4_activation_qdq_bytes;
+    uint64_t nvfp4_projection_output_bytes, nvfp4_kernel_launches;
+    uint64_t nvfp4_completion_fences;
+    uint64_t nvfp4_h2d_ns, nvfp4_qdq_ns, nvfp4_projection_ns, nvfp4_d2h_ns;
+    uint64_t q4_weight_stationary_batches;
+} SaltGpuBatchStatsV2;
+
+/* gpu.h:140-157 */
+typedef struct SaltGpuBatchDesc {
+    const uint32_t *const *vals;
+    const uint16_t *const *scales;
+    const uint16_t *const *biases;
+    const float *const *xs;
+    float *const *ys;
+    const void *const *ids;
+    const int *Rj;
+    int C, njobs;
+} SaltGpuBatchDesc;
+
+typedef struct SaltGpuDispatch {
+    const char *name;
+    int (*init)(void **state);
+    int (*replay)(void *state, const SaltGpuBatchDesc *d);
+    void (*destroy)(void *state);
+} SaltGpuDispatch;
+
+/* gpu.h:198-202: host-visible storage that is also a device buffer.
+ * contents = pinned host pointer, backend = its device alias. */
+typedef struct SaltGpuSharedBuffer {
+    void *contents;
+    size_t nbytes;
+    void *backend;
+} SaltGpuSharedBuffer;
+
+/* gpu.h:211-234 */
+typedef enum SaltGpuExactCellKind {
+    SALT_GPU_EXACT_RMSNORM = 1,
+    SALT_GPU_EXACT_TOPK = 2,
+    SALT_GPU_EXACT_RESIDUAL_POSTNORM = 3,
+    SALT_GPU_EXACT_PARALLEL_COMBINE = 4,
+    SALT_GPU_EXACT_SOFTCAP = 5,
+    SALT_GPU_EXACT_ROUTER_INPUT = 6
+} SaltGpuExactCellKind;
+
+typedef struct SaltGpuExactCell {
+    SaltGpuExactCellKind kind;
+    SaltGpuSharedBuffer *views[8];
+    size_t offsets[8];
+    uint32_t n;
+    uint32_t aux;
+    float eps;
+    float scalar;
+} SaltGpuExactCell;
+
+/* gpu.h:276-295 */
+typedef struct SaltGpuMoeExpert {
+    const uint32_t *gate_vals;
+    const uint16_t *gate_scales;
+    const uint16_t *gate_biases;
+    const void *gate_id;
+    const uint32_t *up_vals;
+    const uint16_t *up_scales;
+    const uint16_t *up_biases;
+    const void *up_id;
+    const uint32_t *down_vals;
+    const uint16_t *down_scales;
+    const uint16_t *down_biases;
+    const void *down_id;
+    int group;
+    int resource_slot;
+    uint64_t logical_resource_id;
+} SaltGpuMoeExpert;
+
+/* gpu.h:297-309 */
+typedef struct SaltGpuSelectedProjectionJob {
+    const uint32_t *vals;
+    const uint16_t *scales;
+    const uint16_t *biases;
+    const void *id;
+    const float *inputs;
+    float *outputs;
+    int rows;
+    int cols;
+    int batch;
+    int resource_slot;
+    uint64_t logical_resource_id;
+} SaltGpuSelectedProjectionJob;
+
+/* gpu.h:411-416 */
+typedef enum SaltGpuWeightAddressability {
+    SALT_GPU_WEIGHT_ADDRESS_AUTO = 0,
+    SALT_GPU_WEIGHT_ADDRESS_BOUNDED_WINDOW = 1,
+    SALT_GPU_WEIGHT_ADDRESS_REGISTERED_PERSISTENT = 2,
+    SALT_GPU_WEIGHT_ADDRESS_PAGEABLE = 3
+} SaltGpuWeightAddressability;
+
+/* gpu.h:418-429 */
+typedef struct SaltGpuWeightResourceUsage {
+    uint64_t described_bytes, registered_bytes, pageable_bytes;
+    uint64_t active_window_bytes, peak_window_bytes, device_copied_weight_bytes;
+    uint32_t described_resources, active_resources, active_windows, reserved;
+} SaltGpuWeightResourceUsage;
+
+/* gpu.h:431-440 */
+typedef struct SaltGpuStartupRequirements {
+    uint64_t fixed_device_bytes, fixed_pinned_host_bytes, descriptor_bytes;
+    uint64_t device_copied_weight_bytes;
+    uint32_t max_output_floats, max_batch_jobs, shared_buffer_slots, reserved;
+} SaltGpuStartupRequirements;
+
+/* resource kinds, reference include/salt/gpu_resource.h:10-14 */
+enum { SALT_GPU_RESOURCE_ARENA = 0, SALT_GPU_RESOURCE_TRUNK = 1, SALT_GPU_RESOURCE_EXPERT_LAYER = 2 };
+
+/* ---- lifecycle ------------------------------------------------------- */
+int salt_gpu_init(void);                                                    /* gpu.h:26 */
+int salt_gpu_free(void);                                                    /* gpu.h:27 */
+int salt_gpu_startup_requirements(SaltGpuStartupRequirements *r, size_t n); /* gpu.h:443 */
+int salt_gpu_set_defer(int on);                                             /* gpu.h:190 */
+int salt_gpu_defer(void);                                                   /* gpu.h:191 */
+int salt_gpu_sync(void);                                                    /* gpu.h:192 */
+void salt_gpu_set_mapped_only(int on);                                      /* gpu.h:99 */
+int salt_gpu_mapped_only(void);                                             /* gpu.h:100 */
+void salt_gpu_batch_stats_get(SaltGpuBatchStats *stats);                    /* gpu.h:134 */
+int salt_gpu_batch_stats_get_v2(SaltGpuBatchStatsV2 *stats, size_t n);      /* gpu.h:135 */
+const SaltGpuDispatch *salt_dispatch_get(void);                             /* gpu.h:163, NULL */
+int salt_gpu_cuda_present(void);                                            /* gpu.h:168, 1 */
+int salt_gpu_rocm_present(void);                                            /* gpu.h:170, 0 */
+int salt_gpu_pageable_mmap_active(void);                                    /* gpu.h:173, 0 */
+const struct SaltTextGpuProgramOps *salt_gpu_tensor_program_ops(void);      /* gpu.h:209, NULL */
+const struct SaltGpuResidencyBackendOps *salt_gpu_residency_backend_ops(void); /* gpu_residency.h:147, NULL */
+
+/* ---- weight resources (gpu.h:443-487, 380-409) ------------------------ */
+int salt_gpu_weight_resource_describe(uint32_t kind, uint32_t id, const void *base, size_t nbytes);
+int salt_gpu_weight_resource_activate(uint32_t kind, uint32_t id, SaltGpuWeightAddressability policy);
+int salt_gpu_weight_resource_pool_bind(uint32_t kind, uint32_t id);
+int salt_gpu_weight_resource_deactivate(uint32_t kind, uint32_t id);
+int salt_gpu_weight_resource_usage(SaltGpuWeightResourceUsage *usage, size_t n);
+int salt_gpu_weight_resource_bind(uint32_t kind, uint32_t id, const void *base, size_t nbytes);
+int salt_gpu_weight_window_bind(uint32_t kind, uint32_t id, uint64_t offset, size_t nbytes);
+int salt_gpu_weight_window_unbind(uint32_t kind, uint32_t id);
+int salt_gpu_weight_resource_slot(uint32_t kind, uint32_t id, const void *key, const uint32_t *vals,
+                                  const uint16_t *scales, const uint16_t *biases, int bits, int R, int C);
+int salt_gpu_nvfp4_resource_slot(uint32_t kind, uint32_t id, const void *key, const uint8_t *weight_packed,
+                                 const uint8_t *weight_scales, const float *weight_global_scale,
+                                 const float *input_global_scale, int R, int C);
+int salt_gpu_bf16_resource_slot(uint32_t kind, uint32_t id, const void *key, const uint16_t *weights, int R,
+                                int C);                                      /* gpu.h:60, -1 */
+int salt_gpu_weight_resource_unbind(uint32_t kind, uint32_t id);
+int salt_gpu_resident_trunk_map(const void *base, size_t nbytes);           /* gpu.h:180 */
+int salt_gpu_resident_trunk_unmap(void);                                    /* gpu.h:183 */
+int salt_gpu_resident_pool_map(const void *base, size_t nbytes);            /* gpu.h:484 */
+int salt_gpu_resident_slot(const void *key, const uint32_t *vals, const uint16_t *scales,
+                           const uint16_t *biases, int R, int C);           /* gpu.h:392 */
+int salt_gpu_expert_resource_bind(uint32_t id, const void *base, size_t nbytes);   /* gpu.h:403 */
+int salt_gpu_expert_resource_slot(uint32_t id, const void *key, const uint32_t *vals, const uint16_t *scales,
+                                  const uint16_t *biases, int R, int C);    /* gpu.h:405 */
+int salt_gpu_expert_resource_unbind(uint32_t id);                           /* gpu.h:409 */
+
+/* ---- selected-expert table (gpu.h:335-347) ---------------------------- */
+int salt_gpu_selected_resources_prepare(int capacity, int logical_capacity);
+int salt_gpu_selected_resource_bind(int slot, uint64_t logical_id, const void *base, size_t nbytes,
+                                    const void *payload);
+int salt_gpu_selected_resource_bind_resident(int slot, uint64_t logical_id, const void *payload, size_t nbytes,
+                                             uintptr_t device_address, uint64_t generation);
+int salt_gpu_selected_resources_fence(void);
+int salt_gpu_selected_resource_unbind(int slot, uint64_t logical_id);
+
+/* ---- affine-Q4 compute ------------------------------------------------ */
+int salt_gpu_q4_matvec(const uint32_t *vals, const uint16_t *scales, const uint16_t *biases, int R, int C,
+                       const float *x, float *y);                           /* gpu.h:34 */
+int salt_gpu_q4_batch(const uint32_t *const *vals, const uint16_t *const *scales, const uint16_t *const *biases,
+                      const float *const *xs, float *const *ys, const void *const *ids, const int *Rj, int C,
+                      int njobs);                                            /* gpu.h:83 */
+int salt_gpu_proj_batch(const uint32_t *vals, const uint16_t *scales, const uint16_t *biases, int R, int C, int B,
+                        const float *const *xs, float *const *ys, const void *id);   /* gpu.h:388 */
+int salt_gpu_proj_batch_indexed(const uint32_t *vals, const uint16_t *scales, const uint16_t *biases, int R,
+                                int C, int B, int first_job, int job_count, const float *xs,
+                                SaltGpuSharedBuffer *output, size_t y_float_offset, const void *id); /* gpu.h:354 */
+int salt_gpu_proj_batch_indexed_exact_views(const uint32_t *vals, const uint16_t *scales, const uint16_t *biases,
+                                            int R, int C, int B, int first_job, int job_count, const float *xs,
+                                            SaltGpuSharedBuffer *output, size_t y_float_offset,
+                                            const void *id);                /* gpu.h:363 */
+int salt_gpu_q4_selected_shared(const SaltGpuSelectedProjectionJob *jobs, int job_count,
+                                SaltGpuSharedBuffer *arena);                /* gpu.h:314 */
+int salt_gpu_q4_moe_chain(const SaltGpuMoeExpert *experts, int count, int hidden, int routed, const float *inputs,
+                          float *outputs, float *gate_scratch, float *up_scratch,
+                          size_t scratch_float_capacity);                   /* gpu.h:320 */
+int salt_gpu_q4_moe_chain_selected(const SaltGpuMoeExpert *experts, int count, int hidden, int routed,
+                                   const float *inputs, float *outputs, float *gate_scratch, float *up_scratch,
+                                   size_t scratch_float_capacity);          /* gpu.h:325 */
+
+/* ---- NVFP4 compute (gpu.h:41-59) --------------------------------------- */
+int salt_gpu_nvfp4_qdq(const float *input, int C, float input_global_scale, uint8_t *packed, uint8_t *scales,
+                       float *dequant);
+int salt_gpu_nvfp4_matvec(const void *key, int R, int C, const float *input, float *output);
+int salt_gpu_nvfp4_matvec_batch(const void *key, int R, int C, int B, const float *inputs, float *outputs);
+int salt_gpu_nvfp4_batch(const void *const *keys, const float *const *inputs, float *const *outputs,
+                         const int *batches, int R, int C, int njobs);
+int salt_gpu_nvfp4_mixed_batch(const void *const *keys, const float *const *inputs, float *const *outputs,
+                               const int *batches, const int *rows, int C, int njobs);
+
+/* ---- exact cells and shared buffers (gpu.h:198-234) -------------------- */
+int salt_gpu_shared_buffer_alloc(SaltGpuSharedBuffer *buffer, size_t nbytes);
+int salt_gpu_shared_buffer_free(SaltGpuSharedBuffer *buffer);
+int salt_gpu_exact_cells(const SaltGpuExactCell *cells, int count);
+
+/* ---- present, fail closed: outside the MoE-FFN path -------------------- */
+int salt_gpu_q8_matvec(const uint32_t *vals, const uint16_t *scales, const uint16_t *biases, int R, int C,
+                       const float *x, float *y);                           /* gpu.h:37 */
+int salt_gpu_q8_batch(const uint32_t *const *vals, const uint16_t *const *scales, const uint16_t *const *biases,
+                      const float *const *xs, float *const *ys, const void *const *ids, const int *Rj, int C,
+                      int njobs);                                            /* gpu.h:89 */
+int salt_gpu_bf16_matvec(const void *key, int R, int C, const float *input, float *output);        /* gpu.h:63 */
+int salt_gpu_bf16_matvec_batch(const void *key, int R, int C, int B, const float *inputs, float *outputs);
+int salt_gpu_attention_batch(int full_attention, int n_heads, int n_kv_heads, int head_dim, int window,
+                             const SaltGpuSharedBuffer *queries, size_t query_float_offset,
+                             const SaltGpuSharedBuffer *kv, size_t key_float_offset, size_t value_float_offset,
+                             int start_position, int batch, int query_stride, int kv_stride,
+                             SaltGpuSharedBuffer *outputs, size_t output_float_offset,
+                             SaltGpuSharedBuffer *score_workspace, size_t score_float_offset,
+                             size_t score_stride, int score_task_capacity);  /* gpu.h:239 */
+int salt_gpu_attention_prepare(const SaltGpuSharedBuffer *kv);
+int salt_gpu_attention_bind_kv(size_t key_float_offset, size_t value_float_offset, int kv_stride);
+int salt_gpu_attention_materialize(SaltGpuSharedBuffer *kv, int position, uint64_t *copied_bytes);
+int salt_gpu_attention_import(SaltGpuSharedBuffer *kv, int position, uint64_t *copied_bytes);
+int salt_gpu_attention_rewind(int position);
+int salt_gpu_attention_transform(int n_heads, int n_kv_heads, int head_dim, int rope_dim, int start_position,
+                                 int batch, int query_stride, int kv_stride, float eps,
+                                 SaltGpuSharedBuffer *queries, size_t query_float_offset,
+                                 SaltGpuSharedBuffer *keys, size_t key_float_offset, SaltGpuSharedBuffer *values,
+                                 size_t value_float_offset, const float *q_weight, const float *k_weight,
+                                 const float *cosines, const float *sines, int rope_pairs,
+                                 SaltGpuSharedBuffer *kv, size_t key_cache_float_offset,
+                                 size_t value_cache_float_offset);           /* gpu.h:262 */
+
+/* ====================================================================== */
+/* Part 2: device-resident MoE stack (no counterpart in the reference)     */
+/* ====================================================================== */
+
+/* One MoE feed-forward layer with affine-Q4 experts.  All pointers are HOST
+ * memory; salt_b200_stack_add_q4_layer copies them into HBM.  The pool holds
+ * n_experts slots of expert_stride bytes, each gate | up | down, each tensor
+ * values | scales | biases (the slot order of the reference's expert pool,
+ * tools/gemma4-mlx4-source.py:180-199).  norm_weight, when not NULL, is the
+ * RMSNorm weight applied to this layer's output before the next layer. */
+typedef struct SaltB200Q4LayerSpec {
+    int hidden, inter, n_experts, topk;
+    float eps;
+    const float *router_w;          /* [n_experts][hidden] fp32 */
+    const float *router_scale;      /* [hidden] */
+    const float *per_expert_scale;  /* [n_experts] */
+    const void *pool;
+    size_t expert_stride;
+    const float *norm_weight;       /* [hidden] or NULL */
+} SaltB200Q4LayerSpec;
+
+/* Device pointers of the per-call workspace, for callers that run their own
+ * exchange step between the expert phase and the combine phase. */
+typedef struct SaltB200Workspace {
+    float *grouped_out;             /* [max_tokens*topk][hidden], grouped order */
+    int32_t *group_offsets;         /* [n_experts+1] */
+    int32_t *selected;              /* [max_tokens*topk] sorted by expert within a token */
+    float *weights;                 /* [max_tokens*topk] */
+    int32_t *canonical_to_grouped;  /* [max_tokens*topk] */
+    int32_t *grouped_to_canonical;  /* [max_tokens*topk] */
+    float *logits;                  /* [max_tokens][n_experts] */
+    int32_t *status;                /* device error word */
+    size_t grouped_out_bytes;
+} SaltB200Workspace;
+
+/* Experts [expert_begin, expert_end) of every layer live on this device; other
+ * experts' weights are not uploaded and their selections are left untouched in
+ * grouped_out (expert-parallel sharding).  Pass 0, n_experts for one GPU. */
+int salt_b200_stack_create(int max_tokens, int hidden, int inter, int n_experts, int topk, int expert_begin,
+                           int expert_end, void **stack_out);
+int salt_b200_stack_destroy(void *stack);
+int salt_b200_stack_add_q4_layer(void *stack, const SaltB200Q4LayerSpec *spec);
+int salt_b200_stack_workspace(void *stack, SaltB200Workspace *out);
+/* Replace the grouped-output buffer by caller-owned device memory (for example
+ * a buffer registered with a communication library). */
+int salt_b200_stack_set_grouped_out(void *stack, void *device_buffer, size_t nbytes);
+
+/* Phase A of one layer on `stream` (a cudaStream_t, NULL = default stream):
+ * router input, logits, top-k, grouping, gate/up + GeGLU, down for the local
+ * experts.  d_x is [B][hidden] in device memory.  zero_remote != 0 first clears
+ * grouped_out so that rows of remote experts read as +0. */
+int salt_b200_layer_experts(void *stack, int layer, const float *d_x, int B, int zero_remote, void *stream);
+/* Phase B: ordered weighted reduce of grouped_out into d_y [B][hidden]; when
+ * apply_norm != 0 and the layer has a norm weight, d_y = RMSNorm(reduce). */
+int salt_b200_layer_combine(void *stack, int layer, int B, float *d_y, int apply_norm, void *stream);
+/* Layers [first, first+count) back to back (phase A + B each), chained through
+ * the layers' RMSNorm; d_x and d_y are device pointers and may alias. */
+int salt_b200_stack_forward_device(void *stack, int first, int count, const float *d_x, int B, float *d_y,
+                                   void *stream);
+/* Same with HOST input/output: copies in, runs, copies out, synchronises, and
+ * returns -1 if the device error word is set. */
+int salt_b200_stack_forward_host(void *stack, int first, int count, const float *h_x, int B, float *h_y);
+/* Synchronise `stream`, read and clear the device error word.  0 = clean. */
+int salt_b200_stack_status(void *stack, void *stream);
+/* Number of kernel launches issued by this library since load. */
+uint64_t salt_b200_launch_count(void);
+
+/* Debug tap: synchronise the device and copy nbytes of device memory to the host. */
+int salt_b200_read_device(void *host_dst, const void *device_src, size_t nbytes);
+
+/* Stand-alone device-pointer forms of the building blocks (tests, profiling). */
+int salt_b200_q4_matvec_device(const void *d_vals, const void *d_scales, const void *d_biases, int R, int C,
+                               const float *d_x, int B, float *d_y, void *stream);
+int salt_b200_route_group_device(const int32_t *d_selected, int rows, int topk, int n_experts,
+                                 int32_t *d_group_offsets, int32_t *d_grouped_to_canonical,
+                                 int32_t *d_canonical_to_grouped, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* SALT_GPU_B200_H */

@@ -1,0 +1,329 @@
+// Host side of libsalt_gpu_b200.so, part 2: a device-resident stack of MoE
+// feed-forward layers (salt_b200_*).  Weights are uploaded once; a forward pass
+// is a fixed sequence of kernel launches on the caller's stream with no host
+// round trip: router input -> logits -> top-k -> grouping/plan -> fused
+// gate/up + GeGLU -> down -> ordered weighted reduce [-> RMSNorm].
+//
+// Expert parallelism: a stack created with a sub-range of experts uploads only
+// those experts.  Every device computes the (replicated, deterministic)
+// routing for all tokens and writes the down-projection rows of ITS experts at
+// their positions in the global grouped order; rows of other devices' experts
+// arrive through whatever exchange the caller runs between the two phases.
+#include <cuda_runtime.h>
+#include <string.h>
+
+#include <vector>
+
+#include "../../include/salt_gpu_b200.h"
+#include "backend_state.h"
+#include "internal.h"
+#include "q4_core.cuh"
+
+namespace sb {
+
+struct Layer {
+    float* router_w = nullptr;
+    float* router_scale = nullptr;
+    float* per_expert_scale = nullptr;
+    float* norm_weight = nullptr;
+    uint8_t* pool = nullptr;   // local experts only; slot of expert e at pool + (e - expert_begin) * stride
+    size_t expert_stride = 0;
+    float eps = 0.0f;
+};
+
+struct Stack {
+    int max_tokens = 0, hidden = 0, inter = 0, n_experts = 0, topk = 0;
+    int expert_begin = 0, expert_end = 0;
+    std::vector<Layer> layers;
+    // workspace
+    float *rin = nullptr, *logits = nullptr, *weights = nullptr, *chain = nullptr, *grouped_out = nullptr;
+    float *reduced = nullptr, *act_a = nullptr, *act_b = nullptr, *io_in = nullptr, *io_out = nullptr;
+    int32_t *selected = nullptr, *group_offsets = nullptr, *g2c = nullptr, *c2g = nullptr, *counters = nullptr;
+    int32_t* status = nullptr;
+    Q4Job *gateup_jobs = nullptr, *down_jobs = nullptr;
+    bool own_grouped = true;
+    size_t grouped_bytes = 0;
+    float *h_in = nullptr, *h_out = nullptr;  // pinned staging for the host entry point
+};
+
+static void free_stack(Stack* s) {
+    for (auto& l : s->layers) {
+        cudaFree(l.router_w); cudaFree(l.router_scale); cudaFree(l.per_expert_scale);
+        cudaFree(l.norm_weight); cudaFree(l.pool);
+    }
+    cudaFree(s->rin); cudaFree(s->logits); cudaFree(s->weights); cudaFree(s->chain);
+    if (s->own_grouped) cudaFree(s->grouped_out);
+    cudaFree(s->reduced); cudaFree(s->act_a); cudaFree(s->act_b); cudaFree(s->io_in); cudaFree(s->io_out);
+    cudaFree(s->selected); cudaFree(s->group_offsets); cudaFree(s->g2c); cudaFree(s->c2g);
+    cudaFree(s->counters); cudaFree(s->status); cudaFree(s->gateup_jobs); cudaFree(s->down_jobs);
+    if (s->h_in) cudaFreeHost(s->h_in);
+    if (s->h_out) cudaFreeHost(s->h_out);
+    delete s;
+}
+
+template <typename T>
+static bool dev_alloc(T** p, size_t count) {
+    return cuda_ok(cudaMalloc((void**)p, count * sizeof(T) + 16), "stack alloc");
+}
+
+template <typename T>
+static bool upload(T** dst, const T* src, size_t count) {
+    return dev_alloc(dst, count) &&
+           cuda_ok(cudaMemcpy(*dst, src, count * sizeof(T), cudaMemcpyHostToDevice), "stack upload");
+}
+
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" {
+
+int salt_b200_stack_create(int max_tokens, int hidden, int inter, int n_experts, int topk, int expert_begin,
+                           int expert_end, void** stack_out) {
+    if (!stack_out || max_tokens < 1 || hidden < 64 || inter < 64 || (hidden % 64) || (inter % 64) ||
+        n_experts < 1 || n_experts > 1024 || topk < 1 || topk > n_experts || topk > 64 || expert_begin < 0 ||
+        expert_end > n_experts || expert_begin >= expert_end)
+        return -1;
+    int ndev = 0;
+    cudaDeviceProp prop;
+    int dev = 0;
+    if (!cuda_ok(cudaGetDeviceCount(&ndev), "device count") || ndev < 1 || !cuda_ok(cudaGetDevice(&dev), "device") ||
+        !cuda_ok(cudaGetDeviceProperties(&prop, dev), "props") || prop.major != 10)
+        return -1;  // sm_100a binary: nothing else can run it, and nothing else is tried
+    Stack* s = new Stack();
+    s->max_tokens = max_tokens; s->hidden = hidden; s->inter = inter; s->n_experts = n_experts; s->topk = topk;
+    s->expert_begin = expert_begin; s->expert_end = expert_end;
+    const size_t T = (size_t)max_tokens, J = T * (size_t)topk;
+    s->grouped_bytes = J * (size_t)hidden * sizeof(float);
+    bool ok = dev_alloc(&s->rin, T * hidden) && dev_alloc(&s->logits, T * n_experts) && dev_alloc(&s->weights, J) &&
+              dev_alloc(&s->chain, J * inter) && dev_alloc(&s->grouped_out, J * hidden) &&
+              dev_alloc(&s->reduced, T * hidden) && dev_alloc(&s->act_a, T * hidden) &&
+              dev_alloc(&s->act_b, T * hidden) && dev_alloc(&s->io_in, T * hidden) &&
+              dev_alloc(&s->io_out, T * hidden) && dev_alloc(&s->selected, J) &&
+              dev_alloc(&s->group_offsets, (size_t)n_experts + 1) && dev_alloc(&s->g2c, J) &&
+              dev_alloc(&s->c2g, J) && dev_alloc(&s->counters, 4) && dev_alloc(&s->status, 1) &&
+              dev_alloc(&s->gateup_jobs, (size_t)n_experts) && dev_alloc(&s->down_jobs, (size_t)n_experts) &&
+              cuda_ok(cudaMemset(s->status, 0, sizeof(int32_t)), "status") &&
+              cuda_ok(cudaHostAlloc((void**)&s->h_in, T * hidden * sizeof(float), cudaHostAllocDefault), "pinned") &&
+              cuda_ok(cudaHostAlloc((void**)&s->h_out, T * hidden * sizeof(float), cudaHostAllocDefault), "pinned");
+    if (!ok) {
+        free_stack(s);
+        return -1;
+    }
+    *stack_out = s;
+    return 0;
+}
+
+int salt_b200_stack_destroy(void* stack) {
+    if (!stack) return -1;
+    cudaDeviceSynchronize();
+    free_stack((Stack*)stack);
+    return 0;
+}
+
+int salt_b200_stack_add_q4_layer(void* stack, const SaltB200Q4LayerSpec* spec) {
+    Stack* s = (Stack*)stack;
+    if (!s || !spec || spec->hidden != s->hidden || spec->inter != s->inter || spec->n_experts != s->n_experts ||
+        spec->topk != s->topk || !spec->router_w || !spec->router_scale || !spec->per_expert_scale || !spec->pool)
+        return -1;
+    const size_t elems = (size_t)s->hidden * s->inter;
+    const size_t tensor_bytes = elems / 2 + 2 * (elems / 64 * 2);
+    if (spec->expert_stride < 3 * tensor_bytes || (spec->expert_stride % 16) != 0) return -1;
+    Layer l;
+    l.eps = spec->eps;
+    l.expert_stride = spec->expert_stride;
+    const size_t local = (size_t)(s->expert_end - s->expert_begin);
+    const uint8_t* src = (const uint8_t*)spec->pool + (size_t)s->expert_begin * spec->expert_stride;
+    bool ok = upload(&l.router_w, spec->router_w, (size_t)s->n_experts * s->hidden) &&
+              upload(&l.router_scale, spec->router_scale, (size_t)s->hidden) &&
+              upload(&l.per_expert_scale, spec->per_expert_scale, (size_t)s->n_experts) &&
+              upload(&l.pool, src, local * spec->expert_stride) &&
+              (!spec->norm_weight || upload(&l.norm_weight, spec->norm_weight, (size_t)s->hidden));
+    if (!ok) {
+        cudaFree(l.router_w); cudaFree(l.router_scale); cudaFree(l.per_expert_scale); cudaFree(l.pool);
+        cudaFree(l.norm_weight);
+        return -1;
+    }
+    s->layers.push_back(l);
+    return (int)s->layers.size() - 1;
+}
+
+int salt_b200_stack_workspace(void* stack, SaltB200Workspace* out) {
+    Stack* s = (Stack*)stack;
+    if (!s || !out) return -1;
+    out->grouped_out = s->grouped_out;
+    out->group_offsets = s->group_offsets;
+    out->selected = s->selected;
+    out->weights = s->weights;
+    out->canonical_to_grouped = s->c2g;
+    out->grouped_to_canonical = s->g2c;
+    out->logits = s->logits;
+    out->status = s->status;
+    out->grouped_out_bytes = s->grouped_bytes;
+    return 0;
+}
+
+int salt_b200_stack_set_grouped_out(void* stack, void* device_buffer, size_t nbytes) {
+    Stack* s = (Stack*)stack;
+    if (!s || !device_buffer || nbytes < s->grouped_bytes || ((uintptr_t)device_buffer & 15)) return -1;
+    if (s->own_grouped) cudaFree(s->grouped_out);
+    s->grouped_out = (float*)device_buffer;
+    s->own_grouped = false;
+    return 0;
+}
+
+int salt_b200_layer_experts(void* stack, int layer, const float* d_x, int B, int zero_remote, void* stream_) {
+    Stack* s = (Stack*)stack;
+    cudaStream_t st = (cudaStream_t)stream_;
+    if (!s || layer < 0 || layer >= (int)s->layers.size() || !d_x || B < 1 || B > s->max_tokens) return -1;
+    const Layer& l = s->layers[(size_t)layer];
+    const int H = s->hidden, M = s->inter, E = s->n_experts, K = s->topk;
+    const int jobs = B * K;
+    if (zero_remote &&
+        !cuda_ok(cudaMemsetAsync(s->grouped_out, 0, (size_t)jobs * H * sizeof(float), st), "zero grouped"))
+        return -1;
+    if (!cuda_ok(launch_router_input(d_x, l.router_scale, s->rin, B, H, l.eps, 0.0f, s->status, st), "router in") ||
+        !cuda_ok(launch_router_logits(l.router_w, nullptr, s->rin, s->logits, B, E, H, st), "logits") ||
+        !cuda_ok(launch_router_topk(s->logits, l.per_expert_scale, s->selected, s->weights, B, E, K, 1, s->status,
+                                    st), "topk"))
+        return -1;
+    const size_t elems = (size_t)H * M;
+    MoePlanArgs a;
+    memset(&a, 0, sizeof a);
+    a.selected = s->selected; a.rows = B; a.topk = K; a.n_experts = E;
+    a.expert_begin = s->expert_begin; a.expert_end = s->expert_end;
+    a.group_offsets = s->group_offsets; a.grouped_to_canonical = s->g2c; a.canonical_to_grouped = s->c2g;
+    a.n_active = s->counters; a.max_group = s->counters + 1;
+    // the plan indexes experts globally; local slot 0 is expert_begin
+    a.pool = l.pool - (size_t)s->expert_begin * l.expert_stride;
+    a.expert_stride = l.expert_stride;
+    a.value_bytes = elems / 2; a.group_bytes = elems / 64 * 2;
+    a.tensor_bytes = a.value_bytes + 2 * a.group_bytes;
+    a.hidden = H; a.inter = M; a.x = d_x; a.chain = s->chain; a.grouped_out = s->grouped_out;
+    a.gateup_jobs = s->gateup_jobs; a.down_jobs = s->down_jobs; a.status = s->status;
+    if (!cuda_ok(launch_moe_plan(a, st), "plan")) return -1;
+    const int local = s->expert_end - s->expert_begin;
+    const int njobs_max = jobs < local ? jobs : local;
+    // tokens per expert group: at most B; the kernels loop over larger groups
+    const int tok_hint = B == 1 ? 1 : (B == 2 ? 2 : 4);
+    if (!cuda_ok(launch_q4_jobs(s->gateup_jobs, njobs_max, s->counters, M, tok_hint, H, 2, true, st), "gate/up") ||
+        !cuda_ok(launch_q4_jobs(s->down_jobs, njobs_max, s->counters, H, tok_hint, M, 1, true, st), "down"))
+        return -1;
+    count_launches(6);
+    return 0;
+}
+
+int salt_b200_layer_combine(void* stack, int layer, int B, float* d_y, int apply_norm, void* stream_) {
+    Stack* s = (Stack*)stack;
+    cudaStream_t st = (cudaStream_t)stream_;
+    if (!s || layer < 0 || layer >= (int)s->layers.size() || !d_y || B < 1 || B > s->max_tokens) return -1;
+    const Layer& l = s->layers[(size_t)layer];
+    const bool norm = apply_norm && l.norm_weight;
+    float* reduce_to = norm ? s->reduced : d_y;
+    if (!cuda_ok(launch_weighted_reduce(s->weights, s->c2g, s->grouped_out, reduce_to, B, s->topk, s->hidden,
+                                        s->status, st), "reduce"))
+        return -1;
+    count_launches(1);
+    if (norm) {
+        if (!cuda_ok(launch_rmsnorm(s->reduced, l.norm_weight, d_y, B, s->hidden, l.eps, 1, s->status, st), "norm"))
+            return -1;
+        count_launches(1);
+    }
+    return 0;
+}
+
+int salt_b200_stack_forward_device(void* stack, int first, int count, const float* d_x, int B, float* d_y,
+                                   void* stream) {
+    Stack* s = (Stack*)stack;
+    if (!s || first < 0 || count < 1 || first + count > (int)s->layers.size() || !d_x || !d_y) return -1;
+    const float* in = d_x;
+    for (int i = 0; i < count; i++) {
+        const bool last = i == count - 1;
+        float* out = last ? d_y : ((i & 1) ? s->act_b : s->act_a);
+        if (salt_b200_layer_experts(stack, first + i, in, B, 0, stream) != 0 ||
+            salt_b200_layer_combine(stack, first + i, B, out, last ? 0 : 1, stream) != 0)
+            return -1;
+        in = out;
+    }
+    return 0;
+}
+
+int salt_b200_stack_status(void* stack, void* stream) {
+    Stack* s = (Stack*)stack;
+    if (!s) return -1;
+    int32_t status = 0;
+    if (!cuda_ok(cudaStreamSynchronize((cudaStream_t)stream), "status sync") ||
+        !cuda_ok(cudaMemcpy(&status, s->status, sizeof status, cudaMemcpyDeviceToHost), "status read"))
+        return -1;
+    if (status) cudaMemset(s->status, 0, sizeof status);
+    return status;
+}
+
+int salt_b200_stack_forward_host(void* stack, int first, int count, const float* h_x, int B, float* h_y) {
+    Stack* s = (Stack*)stack;
+    if (!s || !h_x || !h_y || B < 1 || B > s->max_tokens) return -1;
+    const size_t bytes = (size_t)B * s->hidden * sizeof(float);
+    memcpy(s->h_in, h_x, bytes);
+    if (!cuda_ok(cudaMemcpyAsync(s->io_in, s->h_in, bytes, cudaMemcpyHostToDevice, 0), "x upload")) return -1;
+    if (salt_b200_stack_forward_device(stack, first, count, s->io_in, B, s->io_out, 0) != 0) return -1;
+    if (!cuda_ok(cudaMemcpyAsync(s->h_out, s->io_out, bytes, cudaMemcpyDeviceToHost, 0), "y download")) return -1;
+    if (salt_b200_stack_status(stack, 0) != 0) return -1;
+    memcpy(h_y, s->h_out, bytes);
+    return 0;
+}
+
+int salt_b200_read_device(void* host_dst, const void* device_src, size_t nbytes) {
+    if (!host_dst || !device_src) return -1;
+    return cuda_ok(cudaDeviceSynchronize(), "read sync") &&
+                   cuda_ok(cudaMemcpy(host_dst, device_src, nbytes, cudaMemcpyDeviceToHost), "read") ? 0 : -1;
+}
+
+int salt_b200_q4_matvec_device(const void* d_vals, const void* d_scales, const void* d_biases, int R, int C,
+                               const float* d_x, int B, float* d_y, void* stream) {
+    if (!d_vals || !d_scales || !d_x || !d_y || R < 1 || C < 1 || B < 1) return -1;
+    Q4Job j;
+    memset(&j, 0, sizeof j);
+    j.vals = (const uint8_t*)d_vals; j.scales = (const uint8_t*)d_scales; j.biases = (const uint8_t*)d_biases;
+    j.x = d_x; j.y = d_y; j.x_div = 1; j.R = R; j.C = C; j.ntok = B; j.x_stride = C; j.y_stride = R;
+    static Q4Job* d_job = nullptr;
+    if (!d_job && !cuda_ok(cudaMalloc((void**)&d_job, sizeof(Q4Job)), "job")) return -1;
+    const bool aligned = (C % 64) == 0 &&
+                         ((((uintptr_t)d_vals | (uintptr_t)d_scales | (uintptr_t)d_biases | (uintptr_t)d_x) & 15) == 0);
+    if (!cuda_ok(cudaMemcpyAsync(d_job, &j, sizeof j, cudaMemcpyHostToDevice, (cudaStream_t)stream), "job upload") ||
+        !cuda_ok(launch_q4_jobs(d_job, 1, nullptr, R, B, C, 1, aligned, (cudaStream_t)stream), "launch"))
+        return -1;
+    count_launches(1);
+    return 0;
+}
+
+int salt_b200_route_group_device(const int32_t* d_selected, int rows, int topk, int n_experts,
+                                 int32_t* d_group_offsets, int32_t* d_grouped_to_canonical,
+                                 int32_t* d_canonical_to_grouped, void* stream) {
+    if (!d_selected || !d_group_offsets || !d_grouped_to_canonical || !d_canonical_to_grouped || rows < 1 ||
+        topk < 1 || n_experts < 1 || n_experts > 1024 || topk > n_experts)
+        return -1;
+    static int32_t* scratch = nullptr;  // n_active, max_group, status
+    static Q4Job* jobs = nullptr;
+    if (!scratch && (!cuda_ok(cudaMalloc((void**)&scratch, 4 * sizeof(int32_t)), "scratch") ||
+                     !cuda_ok(cudaMalloc((void**)&jobs, 2 * 1024 * sizeof(Q4Job)), "scratch")))
+        return -1;
+    MoePlanArgs a;
+    memset(&a, 0, sizeof a);
+    a.selected = d_selected; a.rows = rows; a.topk = topk; a.n_experts = n_experts;
+    a.expert_begin = 0; a.expert_end = 0;  // no descriptors wanted
+    a.group_offsets = d_group_offsets; a.grouped_to_canonical = d_grouped_to_canonical;
+    a.canonical_to_grouped = d_canonical_to_grouped;
+    a.n_active = scratch; a.max_group = scratch + 1; a.status = scratch + 2;
+    a.gateup_jobs = jobs; a.down_jobs = jobs + 1024;
+    if (!cuda_ok(cudaMemsetAsync(scratch, 0, 4 * sizeof(int32_t), (cudaStream_t)stream), "scratch") ||
+        !cuda_ok(launch_moe_plan(a, (cudaStream_t)stream), "plan"))
+        return -1;
+    count_launches(1);
+    int32_t status = 0;
+    if (!cuda_ok(cudaStreamSynchronize((cudaStream_t)stream), "sync") ||
+        !cuda_ok(cudaMemcpy(&status, scratch + 2, sizeof status, cudaMemcpyDeviceToHost), "status"))
+        return -1;
+    return status ? -1 : 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,104 @@
+"""ctypes mirror of the device-resident MoE stack (salt_b200_* in
+include/salt_gpu_b200.h)."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from ._lib import load_library
+
+
+class Q4LayerSpec(C.Structure):
+    _fields_ = [("hidden", C.c_int), ("inter", C.c_int), ("n_experts", C.c_int), ("topk", C.c_int),
+                ("eps", C.c_float), ("router_w", C.c_void_p), ("router_scale", C.c_void_p),
+                ("per_expert_scale", C.c_void_p), ("pool", C.c_void_p), ("expert_stride", C.c_size_t),
+                ("norm_weight", C.c_void_p)]
+
+
+class Workspace(C.Structure):
+    _fields_ = [("grouped_out", C.c_void_p), ("group_offsets", C.c_void_p), ("selected", C.c_void_p),
+                ("weights", C.c_void_p), ("canonical_to_grouped", C.c_void_p),
+                ("grouped_to_canonical", C.c_void_p), ("logits", C.c_void_p), ("status", C.c_void_p),
+                ("grouped_out_bytes", C.c_size_t)]
+
+
+class MoeStack:
+    """A stack of affine-Q4 MoE feed-forward layers resident in HBM."""
+
+    def __init__(self, max_tokens, hidden, inter, n_experts, topk, expert_begin=0, expert_end=None):
+        self.lib = load_library()
+        self.lib.salt_b200_launch_count.restype = C.c_uint64
+        self.handle = C.c_void_p()
+        self.max_tokens, self.hidden, self.inter = max_tokens, hidden, inter
+        self.n_experts, self.topk = n_experts, topk
+        self.expert_begin = expert_begin
+        self.expert_end = n_experts if expert_end is None else expert_end
+        rc = self.lib.salt_b200_stack_create(max_tokens, hidden, inter, n_experts, topk, self.expert_begin,
+                                             self.expert_end, C.byref(self.handle))
+        if rc != 0:
+            raise RuntimeError("salt_b200_stack_create failed (no sm_100 device, or out of memory)")
+        self.n_layers = 0
+
+    def add_layer(self, layer, with_norm=True):
+        """layer: synth.Q4MoeLayer (host arrays are copied to HBM)."""
+        nw = layer.norm_weight if with_norm else None
+        spec = Q4LayerSpec(layer.hidden, layer.inter, layer.n_experts, layer.topk, layer.eps,
+                           layer.router_w.ctypes.data, layer.router_scale.ctypes.data,
+                           layer.per_expert_scale.ctypes.data, layer.pool.ctypes.data, layer.expert_stride,
+                           nw.ctypes.data if nw is not None else None)
+        idx = self.lib.salt_b200_stack_add_q4_layer(self.handle, C.byref(spec))
+        if idx < 0:
+            raise RuntimeError("salt_b200_stack_add_q4_layer failed")
+        self.n_layers = idx + 1
+        return idx
+
+    def workspace(self):
+        w = Workspace()
+        if self.lib.salt_b200_stack_workspace(self.handle, C.byref(w)) != 0:
+            raise RuntimeError("salt_b200_stack_workspace failed")
+        return w
+
+    def set_grouped_out(self, device_ptr, nbytes):
+        return self.lib.salt_b200_stack_set_grouped_out(self.handle, C.c_void_p(device_ptr), C.c_size_t(nbytes))
+
+    def forward_host(self, x, first=0, count=None):
+        """x [B][hidden] float32 numpy -> y; raises if the library reports failure."""
+        x = np.ascontiguousarray(x, np.float32).reshape(-1, self.hidden)
+        y = np.empty_like(x)
+        count = self.n_layers - first if count is None else count
+        rc = self.lib.salt_b200_stack_forward_host(self.handle, first, count, C.c_void_p(x.ctypes.data),
+                                                   x.shape[0], C.c_void_p(y.ctypes.data))
+        if rc != 0:
+            raise RuntimeError(f"salt_b200_stack_forward_host failed (rc={rc})")
+        return y
+
+    def forward_device(self, d_x, B, d_y, first=0, count=None, stream=0):
+        count = self.n_layers - first if count is None else count
+        return self.lib.salt_b200_stack_forward_device(self.handle, first, count, C.c_void_p(d_x), B,
+                                                       C.c_void_p(d_y), C.c_void_p(stream))
+
+    def layer_experts(self, layer, d_x, B, zero_remote=False, stream=0):
+        return self.lib.salt_b200_layer_experts(self.handle, layer, C.c_void_p(d_x), B, int(zero_remote),
+                                                C.c_void_p(stream))
+
+    def layer_combine(self, layer, B, d_y, apply_norm=True, stream=0):
+        return self.lib.salt_b200_layer_combine(self.handle, layer, B, C.c_void_p(d_y), int(apply_norm),
+                                                C.c_void_p(stream))
+
+    def status(self, stream=0):
+        return self.lib.salt_b200_stack_status(self.handle, C.c_void_p(stream))
+
+    def launch_count(self):
+        return int(self.lib.salt_b200_launch_count())
+
+    def close(self):
+        if self.handle:
+            self.lib.salt_b200_stack_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -1,0 +1,188 @@
+"""Router, grouping, expert chain and the device-resident MoE stack on the GPU,
+against the CPU oracle and the golden fixtures (bit exact)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from conftest import assert_bits_equal, golden
+from gpu_util import backend_mod, d2h, gpu, oracle_stack, stack_mod
+
+pytestmark = pytest.mark.gpu
+
+
+def test_exact_cells_router_chain_golden():
+    g, bm, fx = gpu(), backend_mod(), golden("router.npz")
+    H, E, K = fx["x"].shape[1], fx["W"].shape[0], int(fx["topk"])
+    rc, buf = g.shared_buffer_alloc(4 * (4 * H + 2 * E + 2 * K + 16))
+    assert rc == 0
+    f = buf.array(np.float32)
+    o_x, o_w, o_out, o_log, o_pes, o_sel, o_wts = 0, H, 2 * H, 3 * H, 3 * H + E, 3 * H + 2 * E, 3 * H + 2 * E + K
+    for t in range(fx["x"].shape[0]):
+        f[o_x:o_x + H] = fx["x"][t]
+        f[o_w:o_w + H] = fx["scale"]
+        cell = bm.exact_cell(bm.EXACT_ROUTER_INPUT, [buf] * 3, [o_x, o_w, o_out], H, eps=float(fx["eps"]))
+        assert g.exact_cells([cell]) == 0
+        assert_bits_equal(f[o_out:o_out + H].copy(), fx["rin"][t], "router input cell")
+        f[o_w:o_w + H] = fx["nw"]
+        cell = bm.exact_cell(bm.EXACT_RMSNORM, [buf] * 3, [o_x, o_w, o_out], H, aux=1, eps=float(fx["eps"]))
+        assert g.exact_cells([cell]) == 0
+        assert_bits_equal(f[o_out:o_out + H].copy(), fx["norm"][t], "rmsnorm cell")
+        f[o_log:o_log + E] = fx["logits"][t]
+        f[o_pes:o_pes + E] = fx["pes"]
+        cell = bm.exact_cell(bm.EXACT_TOPK, [buf] * 4, [o_log, o_pes, o_sel, o_wts], E, aux=K)
+        assert g.exact_cells([cell]) == 0
+        assert_bits_equal(f[o_sel:o_sel + K].view(np.int32).copy(), fx["sel"][t], "topk selected")
+        assert_bits_equal(f[o_wts:o_wts + K].copy(), fx["wts"][t], "topk weights")
+    # non-finite input is rejected, as the reference functions return -1
+    f[o_log] = np.inf
+    cell = bm.exact_cell(bm.EXACT_TOPK, [buf] * 4, [o_log, o_pes, o_sel, o_wts], E, aux=K)
+    assert g.exact_cells([cell]) == -1
+    assert g.shared_buffer_free(buf) == 0
+
+
+def test_route_group_device_golden_and_reference_kat(orc):
+    import torch
+    g = gpu()
+    cases = [(np.array([2, 0, 2, 1, 0, 2], np.int32), 3, 2, 4)]
+    fx = golden("grouping.npz")
+    cases.append((fx["selected"].ravel().astype(np.int32), fx["selected"].shape[0], fx["selected"].shape[1],
+                  int(fx["n_experts"])))
+    rng = np.random.default_rng(4)
+    for rows, topk, ne in ((512, 8, 128), (2048, 8, 128), (37, 4, 64)):
+        sel = np.stack([np.sort(rng.permutation(ne)[:topk]) for _ in range(rows)]).astype(np.int32)
+        cases.append((sel.ravel(), rows, topk, ne))
+    for sel, rows, topk, ne in cases:
+        d_sel = torch.from_numpy(sel).cuda()
+        d_off = torch.zeros(ne + 1, dtype=torch.int32, device="cuda")
+        d_g2c = torch.zeros(rows * topk, dtype=torch.int32, device="cuda")
+        d_c2g = torch.zeros(rows * topk, dtype=torch.int32, device="cuda")
+        rc = g.lib.salt_b200_route_group_device(C.c_void_p(d_sel.data_ptr()), rows, topk, ne,
+                                                C.c_void_p(d_off.data_ptr()), C.c_void_p(d_g2c.data_ptr()),
+                                                C.c_void_p(d_c2g.data_ptr()), None)
+        assert rc == 0
+        rc, offs, g2c, c2g, _ = orc.route_group(sel, rows, topk, ne)
+        assert rc == 0
+        assert_bits_equal(d_g2c.cpu().numpy(), g2c, "grouped_to_canonical")
+        assert_bits_equal(d_c2g.cpu().numpy(), c2g, "canonical_to_grouped")
+        starts = np.concatenate([[0], offs]).astype(np.int32)  # the oracle leaves END offsets
+        assert_bits_equal(d_off.cpu().numpy(), starts, "group offsets")
+    assert cases[0][0] is not None and d_g2c is not None
+    # reference tests/test_text_verify.c:1238-1239
+    sel, rows, topk, ne = cases[0]
+    rc, offs, g2c, c2g, _ = orc.route_group(sel, rows, topk, ne)
+    assert g2c.tolist() == [1, 4, 3, 0, 2, 5] and c2g.tolist() == [3, 0, 4, 2, 1, 5]
+
+
+def _expert_struct(bm, layer, e, group, key_base):
+    def addr(a):
+        return a.ctypes.data
+    gv, gs, gb = layer.tensor(e, 0)
+    uv, us, ub = layer.tensor(e, 1)
+    dv, ds, db = layer.tensor(e, 2)
+    return bm.MoeExpert(addr(gv), addr(gs), addr(gb), key_base + 3 * e, addr(uv), addr(us), addr(ub),
+                        key_base + 3 * e + 1, addr(dv), addr(ds), addr(db), key_base + 3 * e + 2, group, -1, 0)
+
+
+@pytest.mark.parametrize("groups", [[1], [1, 1, 1], [3, 1, 9, 2], [40]])
+def test_q4_moe_chain_vs_oracle(orc, synth, groups):
+    # reference call: salt_gpu_q4_moe_chain from g4_group_run_many (gemma4_text.c:9050)
+    g, bm = gpu(), backend_mod()
+    H, M = 256, 128
+    layer = synth.make_q4_moe_layer(21, hidden=H, inter=M, n_experts=8, topk=2)
+    assert g.expert_resource_bind(33, layer.pool) == 0
+    key_base = 0x77000
+    experts = []
+    for i, grp in enumerate(groups):
+        e = (i * 3 + 1) % 8
+        for which in range(3):
+            R, Cc = (M, H) if which < 2 else (H, M)
+            v, s, b = layer.tensor(e, which)
+            assert g.expert_resource_slot(33, key_base + 3 * e + which, v, s, b, R, Cc) == 0
+        experts.append(_expert_struct(bm, layer, e, grp, key_base))
+    total = sum(groups)
+    x = synth.make_tokens(5, total, H)
+    y = np.zeros((total, H), np.float32)
+    assert g.q4_moe_chain(experts, H, M, x, y) == 0
+    row = 0
+    for i, grp in enumerate(groups):
+        e = (i * 3 + 1) % 8
+        for t in range(grp):
+            gate = orc.q4_matvec(*layer.tensor(e, 0), M, H, x[row])
+            up = orc.q4_matvec(*layer.tensor(e, 1), M, H, x[row])
+            chain = orc.map_f32("gelu_tanh", gate) * up
+            want = orc.q4_matvec(*layer.tensor(e, 2), H, M, chain)
+            assert_bits_equal(y[row], want, f"expert {e} row {row}")
+            row += 1
+    assert g.expert_resource_unbind(33) == 0
+
+
+def test_stack_small_geometry_golden(synth):
+    fx = golden("moe_layer_small.npz")
+    lseed, xseed, B, H, M, E, K = (int(v) for v in fx["meta"])
+    layer = synth.make_q4_moe_layer(lseed, hidden=H, inter=M, n_experts=E, topk=K)
+    x = synth.make_tokens(xseed, B, H)
+    st = stack_mod().MoeStack(16, H, M, E, K)
+    st.add_layer(layer)
+    y = st.forward_host(x)
+    ws = st.workspace()
+    assert_bits_equal(d2h(ws.selected, B * K, np.int32).reshape(B, K), fx["sel"], "selected")
+    assert_bits_equal(d2h(ws.weights, B * K, np.float32).reshape(B, K), fx["w"], "weights")
+    assert_bits_equal(y, fx["y"], "layer output")
+    st.close()
+
+
+@pytest.mark.parametrize("B", [1, 4, 16, 64])
+def test_stack_cfg2_layer_decode_sweep_vs_oracle(orc, synth, B):
+    layer = synth.make_q4_moe_layer(2, )          # H=2816, E=128, top-8, M=704
+    x = synth.make_tokens(100 + B, B, layer.hidden)
+    st = stack_mod().MoeStack(64, layer.hidden, layer.inter, layer.n_experts, layer.topk)
+    st.add_layer(layer)
+    y = st.forward_host(x)
+    want, sel, w = orc.moe_layer_q4(layer, x, threads=8)
+    ws = st.workspace()
+    assert_bits_equal(d2h(ws.selected, B * 8, np.int32).reshape(B, 8), sel, "selected")
+    assert_bits_equal(d2h(ws.weights, B * 8, np.float32).reshape(B, 8), w, "weights")
+    assert_bits_equal(y, want, f"cfg2 layer B={B}")
+    y2 = st.forward_host(x)
+    assert_bits_equal(y2, y, "run-to-run")
+    st.close()
+
+
+def test_stack_three_layers_with_rmsnorm_vs_oracle(orc, synth):
+    H, M, E, K = 512, 128, 32, 4
+    layers = [synth.make_q4_moe_layer(40 + i, hidden=H, inter=M, n_experts=E, topk=K) for i in range(3)]
+    x = synth.make_tokens(9, 5, H)
+    st = stack_mod().MoeStack(8, H, M, E, K)
+    for layer in layers:
+        st.add_layer(layer)
+    y = st.forward_host(x)
+    want, _ = oracle_stack(orc, layers, x, threads=4)
+    assert_bits_equal(y, want, "3-layer stack")
+    st.close()
+
+
+def test_stack_expert_sharding_union_equals_single_device(orc, synth):
+    """Two half-stacks (experts 0-15 and 16-31) on the same GPU: each fills only its
+    rows of the grouped buffer; their union reproduces the unsharded result."""
+    import torch
+    H, M, E, K, B = 256, 128, 32, 4, 7
+    layer = synth.make_q4_moe_layer(61, hidden=H, inter=M, n_experts=E, topk=K)
+    x = synth.make_tokens(62, B, H)
+    want, _, _ = orc.moe_layer_q4(layer, x, threads=4)
+    sm = stack_mod()
+    d_x = torch.from_numpy(x).cuda()
+    shared = torch.zeros(B * K * H, dtype=torch.float32, device="cuda")
+    halves = []
+    for lo, hi in ((0, 16), (16, 32)):
+        st = sm.MoeStack(8, H, M, E, K, expert_begin=lo, expert_end=hi)
+        st.add_layer(layer)
+        assert st.set_grouped_out(shared.data_ptr(), shared.numel() * 4) == 0
+        assert st.layer_experts(0, d_x.data_ptr(), B) == 0
+        halves.append(st)
+    d_y = torch.zeros(B, H, dtype=torch.float32, device="cuda")
+    assert halves[0].layer_combine(0, B, d_y.data_ptr(), apply_norm=False) == 0
+    assert halves[0].status() == 0 and halves[1].status() == 0
+    assert_bits_equal(d_y.cpu().numpy(), want, "sharded union")
+    for st in halves:
+        st.close()
