@@ -1,0 +1,395 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized MoE feed-forward decode path on B200.
+
+Workload (config 2 of the baseline: one MoE-FFN layer, hidden 2816, 128 experts,
+top-8, expert GeGLU 2816->704->2816, all affine-Q4 group-64, fp32 router),
+decode batch B, run as the 30-layer stack of config 5 (independent seeds per
+layer, RMSNorm between layers) so that every step streams ~0.85 GB of distinct
+expert weights -- far more than the 126 MB L2.  The metric is tokens/s through
+one MoE-FFN layer: B * layers / time of one pass over the stack.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--layers L]
+    python bench.py --impl reference ...      # the reference's own CPU path
+
+One JSON line is printed by rank 0.  With N > 1 (under torchrun) the experts of
+every layer are sharded expert-parallel over the ranks, every rank holds N*B
+tokens' activations (replicated, deterministic routing), and the per-selection
+expert outputs are exchanged once per layer.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+H, M, E, K = 2816, 704, 128, 8
+TENSOR_BYTES = 1_115_136                      # one 704x2816 Q4 projection (values + scales + biases)
+METRIC = "q4_moe_ffn_decode_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=1, help="decode tokens per GPU")
+    ap.add_argument("--layers", type=int, default=30)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--cpu-seconds", type=float, default=10.0, help="budget of the CPU baseline sample")
+    ap.add_argument("--no-graph", action="store_true")
+    return ap.parse_args()
+
+
+def workload_config(args, world):
+    return {"workload": "cfg2 MoE-FFN layer decode (H2816 E128 top8 M704, affine-Q4 g64, fp32 router), "
+                        "run as the cfg5 30-layer stack with RMSNorm between layers",
+            "batch_per_gpu": args.batch, "global_batch": args.batch * world, "layers": args.layers,
+            "parallelism": f"ep{world}" if world > 1 else "single",
+            "l2": "inputs larger than L2 (about 0.85 GB of distinct expert weights streamed per step at B=1)"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks during the timed region (read-only query)."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.rows = []
+        self.proc = None
+        self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def generate_layers(synth, n_layers, keep_host, consume):
+    """Generate the stack's layers on a thread pool and hand each to `consume`
+    (upload) in order; returns the first `keep_host` layers for the CPU baseline."""
+    kept = []
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
+        futs = []
+        window = 6                                # bounds host memory: 6 x 428 MB in flight
+        nxt = 0
+        for i in range(n_layers):
+            while len(futs) < window and nxt < n_layers:
+                futs.append(pool.submit(synth.make_q4_moe_layer_bulk, 5000 + nxt))
+                nxt += 1
+            layer = futs.pop(0).result()
+            consume(i, layer)
+            if i < keep_host:
+                kept.append(layer)
+    return kept
+
+
+def cpu_baseline(layers, B, seconds, threads):
+    """The reference's own CPU decode path (oracle/_ref, all host cores) on a bounded
+    sample: the host-kept layers are cycled for about `seconds`."""
+    import oracle
+    synth = importlib.import_module("salt-core_b200.synth")
+    x = synth.make_tokens(77, B, H)
+    if oracle.RefDriver.available():
+        drv, kind = oracle.RefDriver(threads), "reference"
+        run = lambda layer: drv.moe_layer_q4(layer, x)
+        used = drv.threads
+    else:
+        orc, kind, used = oracle.Oracle(), "port", threads
+        run = lambda layer: orc.moe_layer_q4(layer, x, threads=threads)
+    run(layers[0])
+    t0 = time.perf_counter()
+    n = 0
+    while True:
+        run(layers[n % len(layers)])
+        n += 1
+        el = time.perf_counter() - t0
+        if el >= seconds or n >= 100000:
+            break
+    return {"value": B * n / el, "unit": UNIT, "cores": used, "kind": kind,
+            "sample": f"{n} single-layer passes at B={B} cycling {len(layers)} distinct layers "
+                      f"({el:.1f} s); reference functions on a persistent pthread pool",
+            "ms_per_layer": 1e3 * el / n}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    synth = importlib.import_module("salt-core_b200.synth")
+    threads = os.cpu_count() or 1
+    n_host = min(3, args.layers)
+    layers = [synth.make_q4_moe_layer_bulk(5000 + i) for i in range(n_host)]
+    world = max(1, args.gpus)
+    B = args.batch * world
+    import oracle
+    x = synth.make_tokens(77, B, H)
+    if oracle.RefDriver.available():
+        drv = oracle.RefDriver(threads)
+        kind, used = "reference", drv.threads
+        def step():
+            cur = x
+            for layer in layers:
+                y, _, _ = drv.moe_layer_q4(layer, cur)
+                cur = drv.rmsnorm_rows(y, layer.norm_weight, layer.eps)
+    else:
+        orc = oracle.Oracle()
+        kind, used = "port", threads
+        def step():
+            cur = x
+            for layer in layers:
+                y, _, _ = orc.moe_layer_q4(layer, cur, threads=threads)
+                cur = np.stack([orc.rmsnorm(y[t], layer.norm_weight, layer.eps, True)[1] for t in range(B)])
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    el = time.perf_counter() - t0
+    ms = 1e3 * el / args.steps
+    value = B * n_host / (ms * 1e-3)
+    sample = (f"each step = {n_host} layers of the stack (of {args.layers}) at B={B}, RMSNorm between layers; "
+              f"reference CPU functions, {used} threads")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, world),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": used, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+    pkg = importlib.import_module("salt-core_b200")
+    pkg.load_library()                        # raises when the CUDA library is missing: no fallback
+    synth = pkg.synth
+    stack_mod = importlib.import_module("salt-core_b200.stack")
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    B = args.batch * world
+    L = args.layers
+    per = E // world
+    stack = stack_mod.MoeStack(max(B, 1), H, M, E, K, expert_begin=rank * per,
+                               expert_end=E if rank == world - 1 else (rank + 1) * per)
+    host_layers = generate_layers(synth, L, 3 if rank == 0 else 0, lambda i, layer: stack.add_layer(layer))
+    x_host = synth.make_tokens(77, B, H)
+    stream = torch.cuda.Stream()
+    sp = stream.cuda_stream
+    d_x = torch.from_numpy(x_host).cuda()
+    d_y = torch.empty_like(d_x)
+    act = [torch.empty_like(d_x), torch.empty_like(d_x)]
+    grouped = torch.zeros(B * K * H, dtype=torch.float32, device="cuda")
+    assert stack.set_grouped_out(grouped.data_ptr(), grouped.numel() * 4) == 0
+
+    def forward_ep(src_ptr, dst):
+        """Expert-parallel pass: one exchange of the grouped expert outputs per layer."""
+        cur = src_ptr
+        for l in range(L):
+            last = l == L - 1
+            out = dst if last else act[l & 1]
+            if stack.layer_experts(l, cur, B, zero_remote=True, stream=sp) != 0:
+                raise RuntimeError("layer_experts failed")
+            dist.all_reduce(grouped)          # each row is written by one rank, the others add +0
+            if stack.layer_combine(l, B, out.data_ptr(), apply_norm=not last, stream=sp) != 0:
+                raise RuntimeError("layer_combine failed")
+            cur = out.data_ptr()
+
+    use_graph = world == 1 and not args.no_graph
+    with torch.cuda.stream(stream):
+        n0 = stack.launch_count()
+        if world == 1:
+            assert stack.forward_device(d_x.data_ptr(), B, d_y.data_ptr(), stream=sp) == 0
+        else:
+            forward_ep(d_x.data_ptr(), d_y)
+        launches_per_step = stack.launch_count() - n0
+        assert stack.status(sp) == 0
+        if use_graph:
+            assert stack.graph_capture(d_x.data_ptr(), B, d_y.data_ptr(), sp) == 0
+
+        def step():
+            if use_graph:
+                assert stack.graph_launch(sp) == 0
+            elif world == 1:
+                assert stack.forward_device(d_x.data_ptr(), B, d_y.data_ptr(), stream=sp) == 0
+            else:
+                forward_ep(d_x.data_ptr(), d_y)
+
+        def timed(fn, steps):
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                fn()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+            if world > 1:
+                dist.barrier()
+                dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            return float(ms.item()) / steps
+
+        for _ in range(max(3, args.warmup)):
+            step()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+            time.sleep(0.3)
+        ms_step = timed(step, args.steps)
+        clocks = sampler.stop() if rank == 0 else None
+        assert stack.status(sp) == 0
+
+        # end to end through the public host API: pinned host input -> H2D -> stack -> D2H
+        h_in = torch.from_numpy(x_host).pin_memory()
+        h_out = torch.empty_like(h_in).pin_memory()
+
+        def e2e_step():
+            if world == 1:
+                stack.forward_host(x_host)
+            else:
+                d_x.copy_(h_in, non_blocking=True)
+                forward_ep(d_x.data_ptr(), d_y)
+                h_out.copy_(d_y, non_blocking=True)
+                stream.synchronize()
+
+        for _ in range(3):
+            e2e_step()
+        if world == 1:
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(args.steps):
+                e2e_step()
+            ms_e2e = 1e3 * (time.perf_counter() - t0) / args.steps
+        else:
+            ms_e2e = timed(e2e_step, args.steps)
+
+        # per-kernel-class device time (CUDA event pairs around every launch), separate pass
+        kernels, roofline = {}, None
+        if world == 1:
+            stack.profile(True, max_launches=launches_per_step * args.steps + 16)
+            for _ in range(args.steps):
+                assert stack.forward_device(d_x.data_ptr(), B, d_y.data_ptr(), stream=sp) == 0
+            prof = stack.profile_read()
+            stack.profile(False, 0)
+            # distinct experts per layer (decides the algorithmic bytes of a launch)
+            distinct = []
+            ws = stack.workspace()
+            lib = stack.lib
+            offs = np.empty(E + 1, np.int32)
+            cur = d_x.data_ptr()
+            for l in range(L):
+                out = act[l & 1]
+                stack.layer_experts(l, cur, B, stream=sp)
+                stack.layer_combine(l, B, out.data_ptr(), apply_norm=True, stream=sp)
+                import ctypes as C
+                lib.salt_b200_read_device(C.c_void_p(offs.ctypes.data), C.c_void_p(ws.group_offsets),
+                                          C.c_size_t(offs.nbytes))
+                distinct.append(int((np.diff(offs) > 0).sum()))
+                cur = out.data_ptr()
+            mean_distinct = float(np.mean(distinct))
+            for name, (ms, n) in prof.items():
+                if n:
+                    kernels[name] = {"launches": n, "total_ms": ms, "us_per_launch": 1e3 * ms / n}
+            gu = kernels["gate_up_geglu"]
+            alg = mean_distinct * 2 * TENSOR_BYTES + B * H * 4 + B * K * M * 4
+            peaks = {}
+            try:
+                peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+            except OSError:
+                pass
+            peak = float(peaks.get("hbm_gbs", 6650.0))
+            achieved = alg / (gu["us_per_launch"] * 1e-6) / 1e9
+            dn = kernels["down"]
+            roofline = {"bound": "hbm", "kernel": "q4_tile_kernel<2,TT> (fused gate/up + GeGLU)",
+                        "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                        "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback 6650 GB/s",
+                        "algorithmic_bytes_per_launch": alg, "us_per_launch": gu["us_per_launch"],
+                        "mean_distinct_experts": mean_distinct, "traffic": None,
+                        "down_kernel": {"achieved": (mean_distinct * TENSOR_BYTES + B * K * (M + H) * 4)
+                                        / (dn["us_per_launch"] * 1e-6) / 1e9,
+                                        "us_per_launch": dn["us_per_launch"]}}
+
+    value = B * L / (ms_step * 1e-3)
+    out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+           "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+           "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(args, world),
+           "clocks": clocks,
+           "e2e": {"value": B * L / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": B * H * 4,
+                   "d2h_bytes_per_step": B * H * 4, "ms_per_step": ms_e2e,
+                   "api": "salt_b200_stack_forward_host" if world == 1 else "layer_experts/all_reduce/layer_combine"},
+           "gpu_launches": launches_per_step * args.steps,
+           "launch_mode": "cuda graph replay" if use_graph else "stream launches",
+           "us_per_layer": 1e3 * ms_step / L}
+    if roofline:
+        out["roofline"] = roofline
+        out["kernels"] = kernels
+    if rank == 0 and world == 1:
+        out["cpu_baseline"] = cpu_baseline(host_layers, B, args.cpu_seconds, os.cpu_count() or 1)
+    if rank == 0:
+        print(json.dumps(out))
+    stack.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -349,6 +349,18 @@ int salt_b200_stack_forward_device(void *stack, int first, int count, const floa
 /* Same with HOST input/output: copies in, runs, copies out, synchronises, and
  * returns -1 if the device error word is set. */
 int salt_b200_stack_forward_host(void *stack, int first, int count, const float *h_x, int B, float *h_y);
+/* Capture layers [first, first+count) into a CUDA graph on `stream` (not the
+ * legacy default stream); pointers and B are baked in.  Replay with
+ * salt_b200_stack_graph_launch. */
+int salt_b200_stack_graph_capture(void *stack, int first, int count, const float *d_x, int B, float *d_y,
+                                  void *stream);
+int salt_b200_stack_graph_launch(void *stack, void *stream);
+/* Per-kernel-class device timing: while enabled every launch of a forward pass
+ * is bracketed by CUDA events (at most max_launches launches between reads).
+ * _read returns summed milliseconds and launch counts for the 8 classes
+ * router input, logits, top-k, plan, gate/up+GeGLU, down, reduce, RMSNorm. */
+int salt_b200_stack_profile(void *stack, int enable, int max_launches);
+int salt_b200_stack_profile_read(void *stack, float *ms_by_class, int *launches_by_class, int n_classes);
 /* Synchronise `stream`, read and clear the device error word.  0 = clean. */
 int salt_b200_stack_status(void *stack, void *stream);
 /* Number of kernel launches issued by this library since load. */

@@ -414,3 +414,49 @@ class Reference:
                     y[t] = y[t] + down * w[t, j]
         self.set_expert_scope(False)
         return y, sel, w
+
+
+REF_DRIVER_SO = os.path.join(HERE, "_ref", "libref_driver.so")
+
+
+class RefDriver:
+    """_ref/libref_driver.so: the reference's own decode-path functions driven by
+    a persistent pthread pool (oracle/ref_driver.c).  Used as the timed CPU
+    baseline; only available where oracle/_ref was built."""
+
+    kind = "reference"
+
+    def __init__(self, threads: int):
+        if not os.path.exists(REF_DRIVER_SO):
+            raise FileNotFoundError(REF_DRIVER_SO)
+        self.lib = C.CDLL(REF_DRIVER_SO)
+        self.threads = int(self.lib.refdrv_pool_start(int(threads)))
+
+    @staticmethod
+    def available() -> bool:
+        return os.path.exists(REF_DRIVER_SO)
+
+    def moe_layer_q4(self, layer, x, threads=None):
+        x = _f32(x).reshape(-1, layer.hidden)
+        B = x.shape[0]
+        d = MoeLayerDesc(layer.hidden, layer.inter, layer.n_experts, layer.topk, layer.eps,
+                         layer.router_w.ctypes.data, layer.router_scale.ctypes.data,
+                         layer.per_expert_scale.ctypes.data, layer.pool.ctypes.data, layer.expert_stride)
+        y = np.empty((B, layer.hidden), np.float32)
+        sel = np.empty((B, layer.topk), np.int32)
+        w = np.empty((B, layer.topk), np.float32)
+        rc = self.lib.refdrv_moe_layer_q4(C.byref(d), _p(x), B, _p(y), _p(sel), _p(w))
+        if rc:
+            raise ValueError("refdrv_moe_layer_q4 failed")
+        return y, sel, w
+
+    def rmsnorm_rows(self, x, weight, eps):
+        x = _f32(x)
+        out = np.empty_like(x)
+        rc = self.lib.refdrv_rmsnorm_rows(_p(out), _p(x), _p(_f32(weight)), x.shape[0], x.shape[1], C.c_float(eps))
+        if rc:
+            raise ValueError("refdrv_rmsnorm_rows failed")
+        return out
+
+    def close(self):
+        self.lib.refdrv_pool_stop()

@@ -44,6 +44,29 @@ struct Stack {
     bool own_grouped = true;
     size_t grouped_bytes = 0;
     float *h_in = nullptr, *h_out = nullptr;  // pinned staging for the host entry point
+    // optional per-kernel-class timing: event pairs recorded around every launch
+    bool profile = false;
+    std::vector<cudaEvent_t> ev;          // pairs (begin, end)
+    std::vector<int> ev_class;
+    size_t ev_used = 0;
+    cudaGraphExec_t graph = nullptr;
+};
+
+enum KernelClass { KC_ROUTER_INPUT = 0, KC_LOGITS, KC_TOPK, KC_PLAN, KC_GATE_UP, KC_DOWN, KC_REDUCE, KC_NORM, KC_COUNT };
+
+struct Timed {
+    Stack* s; cudaStream_t st; bool on;
+    Timed(Stack* s_, int cls, cudaStream_t st_) : s(s_), st(st_), on(false) {
+        if (!s->profile || s->ev_used + 2 > s->ev.size()) return;
+        on = true;
+        s->ev_class[s->ev_used / 2] = cls;
+        cudaEventRecord(s->ev[s->ev_used], st);
+    }
+    ~Timed() {
+        if (!on) return;
+        cudaEventRecord(s->ev[s->ev_used + 1], st);
+        s->ev_used += 2;
+    }
 };
 
 static void free_stack(Stack* s) {
@@ -58,6 +81,8 @@ static void free_stack(Stack* s) {
     cudaFree(s->counters); cudaFree(s->status); cudaFree(s->gateup_jobs); cudaFree(s->down_jobs);
     if (s->h_in) cudaFreeHost(s->h_in);
     if (s->h_out) cudaFreeHost(s->h_out);
+    for (auto e : s->ev) cudaEventDestroy(e);
+    if (s->graph) cudaGraphExecDestroy(s->graph);
     delete s;
 }
 
@@ -182,11 +207,21 @@ int salt_b200_layer_experts(void* stack, int layer, const float* d_x, int B, int
     if (zero_remote &&
         !cuda_ok(cudaMemsetAsync(s->grouped_out, 0, (size_t)jobs * H * sizeof(float), st), "zero grouped"))
         return -1;
-    if (!cuda_ok(launch_router_input(d_x, l.router_scale, s->rin, B, H, l.eps, 0.0f, s->status, st), "router in") ||
-        !cuda_ok(launch_router_logits(l.router_w, nullptr, s->rin, s->logits, B, E, H, st), "logits") ||
-        !cuda_ok(launch_router_topk(s->logits, l.per_expert_scale, s->selected, s->weights, B, E, K, 1, s->status,
-                                    st), "topk"))
-        return -1;
+    {
+        Timed t(s, KC_ROUTER_INPUT, st);
+        if (!cuda_ok(launch_router_input(d_x, l.router_scale, s->rin, B, H, l.eps, 0.0f, s->status, st), "router in"))
+            return -1;
+    }
+    {
+        Timed t(s, KC_LOGITS, st);
+        if (!cuda_ok(launch_router_logits(l.router_w, nullptr, s->rin, s->logits, B, E, H, st), "logits")) return -1;
+    }
+    {
+        Timed t(s, KC_TOPK, st);
+        if (!cuda_ok(launch_router_topk(s->logits, l.per_expert_scale, s->selected, s->weights, B, E, K, 1,
+                                        s->status, st), "topk"))
+            return -1;
+    }
     const size_t elems = (size_t)H * M;
     MoePlanArgs a;
     memset(&a, 0, sizeof a);
@@ -201,14 +236,24 @@ int salt_b200_layer_experts(void* stack, int layer, const float* d_x, int B, int
     a.tensor_bytes = a.value_bytes + 2 * a.group_bytes;
     a.hidden = H; a.inter = M; a.x = d_x; a.chain = s->chain; a.grouped_out = s->grouped_out;
     a.gateup_jobs = s->gateup_jobs; a.down_jobs = s->down_jobs; a.status = s->status;
-    if (!cuda_ok(launch_moe_plan(a, st), "plan")) return -1;
+    {
+        Timed t(s, KC_PLAN, st);
+        if (!cuda_ok(launch_moe_plan(a, st), "plan")) return -1;
+    }
     const int local = s->expert_end - s->expert_begin;
     const int njobs_max = jobs < local ? jobs : local;
     // tokens per expert group: at most B; the kernels loop over larger groups
     const int tok_hint = B == 1 ? 1 : (B == 2 ? 2 : 4);
-    if (!cuda_ok(launch_q4_jobs(s->gateup_jobs, njobs_max, s->counters, M, tok_hint, H, 2, true, st), "gate/up") ||
-        !cuda_ok(launch_q4_jobs(s->down_jobs, njobs_max, s->counters, H, tok_hint, M, 1, true, st), "down"))
-        return -1;
+    {
+        Timed t(s, KC_GATE_UP, st);
+        if (!cuda_ok(launch_q4_jobs(s->gateup_jobs, njobs_max, s->counters, M, tok_hint, H, 2, true, st), "gate/up"))
+            return -1;
+    }
+    {
+        Timed t(s, KC_DOWN, st);
+        if (!cuda_ok(launch_q4_jobs(s->down_jobs, njobs_max, s->counters, H, tok_hint, M, 1, true, st), "down"))
+            return -1;
+    }
     count_launches(6);
     return 0;
 }
@@ -220,11 +265,15 @@ int salt_b200_layer_combine(void* stack, int layer, int B, float* d_y, int apply
     const Layer& l = s->layers[(size_t)layer];
     const bool norm = apply_norm && l.norm_weight;
     float* reduce_to = norm ? s->reduced : d_y;
-    if (!cuda_ok(launch_weighted_reduce(s->weights, s->c2g, s->grouped_out, reduce_to, B, s->topk, s->hidden,
-                                        s->status, st), "reduce"))
-        return -1;
+    {
+        Timed t(s, KC_REDUCE, st);
+        if (!cuda_ok(launch_weighted_reduce(s->weights, s->c2g, s->grouped_out, reduce_to, B, s->topk, s->hidden,
+                                            s->status, st), "reduce"))
+            return -1;
+    }
     count_launches(1);
     if (norm) {
+        Timed t(s, KC_NORM, st);
         if (!cuda_ok(launch_rmsnorm(s->reduced, l.norm_weight, d_y, B, s->hidden, l.eps, 1, s->status, st), "norm"))
             return -1;
         count_launches(1);
@@ -246,6 +295,72 @@ int salt_b200_stack_forward_device(void* stack, int first, int count, const floa
         in = out;
     }
     return 0;
+}
+
+// Per-kernel-class device timing.  While enabled, every launch of a forward pass
+// is bracketed by a pair of CUDA events on the launching stream.
+int salt_b200_stack_profile(void* stack, int enable, int max_launches) {
+    Stack* s = (Stack*)stack;
+    if (!s || max_launches < 0) return -1;
+    s->profile = enable != 0;
+    s->ev_used = 0;
+    while (s->ev.size() < (size_t)2 * max_launches) {
+        cudaEvent_t e;
+        if (!cuda_ok(cudaEventCreate(&e), "event")) return -1;
+        s->ev.push_back(e);
+    }
+    s->ev_class.assign(s->ev.size() / 2 + 1, 0);
+    return 0;
+}
+
+// Sum of elapsed milliseconds and launch count per kernel class since the last
+// call (classes: 0 router input, 1 logits, 2 top-k, 3 plan, 4 gate/up+GeGLU,
+// 5 down, 6 weighted reduce, 7 RMSNorm).  Synchronises the device.
+int salt_b200_stack_profile_read(void* stack, float* ms_by_class, int* launches_by_class, int n_classes) {
+    Stack* s = (Stack*)stack;
+    if (!s || !ms_by_class || !launches_by_class || n_classes < KC_COUNT) return -1;
+    if (!cuda_ok(cudaDeviceSynchronize(), "profile sync")) return -1;
+    for (int i = 0; i < n_classes; i++) { ms_by_class[i] = 0.0f; launches_by_class[i] = 0; }
+    for (size_t i = 0; i + 1 < s->ev_used; i += 2) {
+        float ms = 0.0f;
+        if (!cuda_ok(cudaEventElapsedTime(&ms, s->ev[i], s->ev[i + 1]), "elapsed")) return -1;
+        ms_by_class[s->ev_class[i / 2]] += ms;
+        launches_by_class[s->ev_class[i / 2]]++;
+    }
+    s->ev_used = 0;
+    return 0;
+}
+
+// Capture layers [first, first+count) as one CUDA graph on `stream` (which must
+// not be the legacy default stream), for replay with salt_b200_stack_graph_launch.
+// The pointers and B are baked into the graph.
+int salt_b200_stack_graph_capture(void* stack, int first, int count, const float* d_x, int B, float* d_y,
+                                  void* stream) {
+    Stack* s = (Stack*)stack;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!s || !st || s->profile) return -1;
+    // one uncaptured pass first: it performs the one-time function attribute setup
+    if (salt_b200_stack_forward_device(stack, first, count, d_x, B, d_y, stream) != 0 ||
+        !cuda_ok(cudaStreamSynchronize(st), "pre-capture sync"))
+        return -1;
+    if (s->graph) { cudaGraphExecDestroy(s->graph); s->graph = nullptr; }
+    cudaGraph_t graph = nullptr;
+    if (!cuda_ok(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal), "begin capture")) return -1;
+    const int rc = salt_b200_stack_forward_device(stack, first, count, d_x, B, d_y, stream);
+    const bool ended = cuda_ok(cudaStreamEndCapture(st, &graph), "end capture");
+    if (rc != 0 || !ended || !graph) {
+        if (graph) cudaGraphDestroy(graph);
+        return -1;
+    }
+    const bool ok = cuda_ok(cudaGraphInstantiate(&s->graph, graph, 0), "instantiate");
+    cudaGraphDestroy(graph);
+    return ok ? 0 : -1;
+}
+
+int salt_b200_stack_graph_launch(void* stack, void* stream) {
+    Stack* s = (Stack*)stack;
+    if (!s || !s->graph) return -1;
+    return cuda_ok(cudaGraphLaunch(s->graph, (cudaStream_t)stream), "graph launch") ? 0 : -1;
 }
 
 int salt_b200_stack_status(void* stack, void* stream) {

@@ -6,11 +6,15 @@
 //   L_j = ((((0 + acc[j]) + acc[j+4]) + ...) + acc[j+28]),  j = 0..3
 //   y   = fl(fl(L0 + L2) + fl(L1 + L3))
 //
-// Thread mapping of the tiled kernel: four lanes share a weight row; lane
-// quarter t owns accumulators 8t..8t+7, i.e. exactly the eight nibbles of packed
-// word 4i+t of every 32-column step i.  Each lane keeps two weight rows
+// Thread mapping of the tiled kernel: eight lanes share a weight row; lane
+// octant u owns accumulators 4u..4u+3, i.e. the four nibbles of half-word u of
+// every 32-column step (16 packed bytes).  Each lane keeps two weight rows
 // (gate + up of the same output row, or rows r and r+8) so the activation
 // values it loads are used twice, and TT tokens share one dequantisation.
+// Dequantisation and the products are issued as sm_100 packed pairs
+// (add/mul/fma.rn.f32x2): each half of a pair is an independent IEEE
+// round-to-nearest operation.  An add that consumes a packed product is always
+// a scalar add.rn.f32 (see mul_then_add in q4_kernels.cu for why).
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -45,52 +49,107 @@ __device__ __forceinline__ bool scale_needs_literal(uint32_t sbits16) {
     return (sbits16 & 0x7f80u) >= 0x7c00u;
 }
 
-// The eight nibbles of one packed word as exact floats 0..15.  Nibble k is
-// masked in place and OR-ed with the exponent of 2^(23-4k'), which makes the
-// float equal 2^(23-4k') + q; subtracting that power of two is exact.
-__device__ __forceinline__ void nibbles_to_float(uint32_t w, float (&q)[8]) {
-    uint32_t hi = w >> 16;
-    q[0] = __fsub_rn(__uint_as_float((w & 0x0000000fu) | 0x4b000000u), 8388608.0f);
-    q[1] = __fsub_rn(__uint_as_float((w & 0x000000f0u) | 0x49000000u), 524288.0f);
-    q[2] = __fsub_rn(__uint_as_float((w & 0x00000f00u) | 0x47000000u), 32768.0f);
-    q[3] = __fsub_rn(__uint_as_float((w & 0x0000f000u) | 0x45000000u), 2048.0f);
-    q[4] = __fsub_rn(__uint_as_float((hi & 0x0000000fu) | 0x4b000000u), 8388608.0f);
-    q[5] = __fsub_rn(__uint_as_float((hi & 0x000000f0u) | 0x49000000u), 524288.0f);
-    q[6] = __fsub_rn(__uint_as_float((hi & 0x00000f00u) | 0x47000000u), 32768.0f);
-    q[7] = __fsub_rn(__uint_as_float((hi & 0x0000f000u) | 0x45000000u), 2048.0f);
+// ---- packed fp32 pairs -------------------------------------------------
+typedef unsigned long long f32x2;
+
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ f32x2 pack2u(uint32_t lo, uint32_t hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+#ifndef SB_SCALAR_MATH
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+#else
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    float a0, a1, b0, b1;
+    unpack2(a, a0, a1); unpack2(b, b0, b1);
+    return pack2(__fadd_rn(a0, b0), __fadd_rn(a1, b1));
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    float a0, a1, b0, b1;
+    unpack2(a, a0, a1); unpack2(b, b0, b1);
+    return pack2(__fmul_rn(a0, b0), __fmul_rn(a1, b1));
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    float a0, a1, b0, b1, c0, c1;
+    unpack2(a, a0, a1); unpack2(b, b0, b1); unpack2(c, c0, c1);
+    return pack2(__fmaf_rn(a0, b0, c0), __fmaf_rn(a1, b1, c1));
+}
+#endif
+
+// The four nibbles of one packed half-word as exact floats 0..15, as two pairs.
+// Nibble k is masked in place and OR-ed with the exponent of 2^(23-4k), which
+// makes the float equal 2^(23-4k) + q; adding -2^(23-4k) is exact.
+__device__ __forceinline__ void nibbles4(uint32_t h, f32x2& q01, f32x2& q23) {
+    const f32x2 neg01 = pack2(-8388608.0f, -524288.0f);
+    const f32x2 neg23 = pack2(-32768.0f, -2048.0f);
+    q01 = add2(pack2u((h & 0x000fu) | 0x4b000000u, (h & 0x00f0u) | 0x49000000u), neg01);
+    q23 = add2(pack2u((h & 0x0f00u) | 0x47000000u, (h & 0xf000u) | 0x45000000u), neg23);
 }
 
-__device__ __forceinline__ void dequant8(uint32_t w, float s, float b, bool literal, float (&d)[8]) {
-    float q[8];
-    nibbles_to_float(w, q);
-    if (!literal) {
-#pragma unroll
-        for (int m = 0; m < 8; m++) d[m] = __fmaf_rn(q[m], s, b);
+// d = fl(fl(q*s) + b) for four elements.  LIT selects the literal two-rounding
+// form (needed only when q*s could overflow).
+template <bool LIT>
+__device__ __forceinline__ void dequant4(uint32_t h, f32x2 ss, f32x2 bb, f32x2& d01, f32x2& d23) {
+    f32x2 q01, q23;
+    nibbles4(h, q01, q23);
+    if (LIT) {
+        // two roundings; scalar adds, because ptxas contracts packed mul + packed add
+        float p0, p1, p2, p3, b0, b1;
+        unpack2(mul2(q01, ss), p0, p1);
+        unpack2(mul2(q23, ss), p2, p3);
+        unpack2(bb, b0, b1);
+        d01 = pack2(__fadd_rn(p0, b0), __fadd_rn(p1, b1));
+        d23 = pack2(__fadd_rn(p2, b0), __fadd_rn(p3, b1));
     } else {
-#pragma unroll
-        for (int m = 0; m < 8; m++) d[m] = __fadd_rn(__fmul_rn(q[m], s), b);
+        d01 = fma2(q01, ss, bb);
+        d23 = fma2(q23, ss, bb);
     }
 }
 
-// Canonical fold of one row whose 32 accumulators live 8 per lane in four
-// adjacent lanes (quarter t = lane & 3).  The result is valid in the lane with
-// t == 3.  The chain runs through the quarters in order: quarter t contributes
-// acc[8t + j] then acc[8t + 4 + j] to L_j.
-__device__ __forceinline__ float fold_row_quarters(const float (&a)[8], int t) {
+// Canonical fold of one row whose 32 accumulators live 4 per lane in eight
+// adjacent lanes (octant u = lane & 7; lane holds acc[4u + j], j = 0..3).
+// L_j runs through the octants in order.  The result is valid where u == 7.
+__device__ __forceinline__ float fold_row_octants(f32x2 a01, f32x2 a23, int u) {
+    float a0, a1, a2, a3;
+    unpack2(a01, a0, a1);
+    unpack2(a23, a2, a3);
     float L0 = 0.0f, L1 = 0.0f, L2 = 0.0f, L3 = 0.0f;
 #pragma unroll
-    for (int s = 0; s < 4; s++) {
+    for (int s = 0; s < 8; s++) {
         if (s > 0) {
-            L0 = __shfl_up_sync(0xffffffffu, L0, 1, 4);
-            L1 = __shfl_up_sync(0xffffffffu, L1, 1, 4);
-            L2 = __shfl_up_sync(0xffffffffu, L2, 1, 4);
-            L3 = __shfl_up_sync(0xffffffffu, L3, 1, 4);
+            L0 = __shfl_up_sync(0xffffffffu, L0, 1, 8);
+            L1 = __shfl_up_sync(0xffffffffu, L1, 1, 8);
+            L2 = __shfl_up_sync(0xffffffffu, L2, 1, 8);
+            L3 = __shfl_up_sync(0xffffffffu, L3, 1, 8);
         }
-        if (t == s) {
-            L0 = __fadd_rn(__fadd_rn(L0, a[0]), a[4]);
-            L1 = __fadd_rn(__fadd_rn(L1, a[1]), a[5]);
-            L2 = __fadd_rn(__fadd_rn(L2, a[2]), a[6]);
-            L3 = __fadd_rn(__fadd_rn(L3, a[3]), a[7]);
+        if (u == s) {
+            L0 = __fadd_rn(L0, a0);
+            L1 = __fadd_rn(L1, a1);
+            L2 = __fadd_rn(L2, a2);
+            L3 = __fadd_rn(L3, a3);
         }
     }
     return __fadd_rn(__fadd_rn(L0, L2), __fadd_rn(L1, L3));

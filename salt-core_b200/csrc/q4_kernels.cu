@@ -1,6 +1,6 @@
 // Grouped affine-Q4 projections (decode and exact prefill), hand-written for sm_100a.
 //
-// q4_tile_kernel  -- the hot kernel.  One warp per block of 8 output rows x 2
+// q4_tile_kernel  -- the hot kernel.  Two warps per block of 8 output rows x 2
 //   matrices (fused gate/up + GeGLU) or 16 output rows x 1 matrix.  The packed
 //   rows are pulled into shared memory with 16-byte cp.async copies, one commit
 //   group per 256-column chunk, ALL chunks requested before the first is
@@ -17,10 +17,78 @@
 
 namespace sb {
 
-static __device__ __forceinline__ int align16(int v) { return (v + 15) & ~15; }
+// Shared-memory geometry of one block (16 weight rows).
+struct TileGeom {
+    int row_bytes, w_stride, sc_row, sc_stride, sc_block, steps, chunk_steps, nch;
+    bool sc_padded;
+};
 
+static __host__ __device__ __forceinline__ TileGeom tile_geom(int C, int rows_a) {
+    TileGeom g;
+    g.row_bytes = C >> 1;
+    g.w_stride = g.row_bytes + 16;   // +16 B: rows r and r+1 start 4 banks apart
+    g.sc_row = C >> 5;               // bytes of bf16 scales per row
+    g.sc_padded = (g.sc_row & 15) == 0;
+    g.sc_stride = g.sc_padded ? g.sc_row + 16 : g.sc_row;
+    g.sc_block = (rows_a * g.sc_stride + 15) & ~15;
+    g.steps = C >> 5;                // 32-column steps (16 packed bytes per row)
+    g.chunk_steps = 8;
+    g.nch = (g.steps + 7) / 8;
+    if (g.nch > 15) {
+        g.chunk_steps = (((g.steps + 14) / 15) + 1) & ~1;
+        g.nch = (g.steps + g.chunk_steps - 1) / g.chunk_steps;
+    }
+    return g;
+}
+
+// acc = fl(acc + fl(d * x)) on a pair: packed multiply, SCALAR adds.  ptxas
+// contracts mul.rn.f32x2 followed by add.rn.f32x2 (and even fma.rn.f32x2 with a
+// multiplier of 1) into one fused multiply-add, which changes the last bit; the
+// scalar add.rn.f32 is never a contraction candidate, and measured results with
+// it are bit-identical to the reference order.
+__device__ __forceinline__ f32x2 mul_then_add(f32x2 acc, f32x2 d, f32x2 x) {
+    float p0, p1, a0, a1;
+    unpack2(mul2(d, x), p0, p1);
+    unpack2(acc, a0, a1);
+    return pack2(__fadd_rn(a0, p0), __fadd_rn(a1, p1));
+}
+
+// Accumulate steps [s_begin, s_end) (both even) of the thread's two rows for TT tokens.
+template <int TT, bool LIT>
+__device__ __forceinline__ void tile_steps(int s_begin, int s_end, const uint8_t* wA, const uint8_t* wB,
+                                           const uint16_t* sA, const uint16_t* bA, const uint16_t* sB,
+                                           const uint16_t* bB, const float* sX, int x_pitch,
+                                           f32x2 (&accA)[TT][2], f32x2 (&accB)[TT][2]) {
+#pragma unroll 4
+    for (int g = s_begin >> 1; g < (s_end >> 1); g++) {
+        const float fsA = bf16_bits_to_f32(sA[g]), fbA = bf16_bits_to_f32(bA[g]);
+        const float fsB = bf16_bits_to_f32(sB[g]), fbB = bf16_bits_to_f32(bB[g]);
+        const f32x2 ssA = pack2(fsA, fsA), bbA = pack2(fbA, fbA);
+        const f32x2 ssB = pack2(fsB, fsB), bbB = pack2(fbB, fbB);
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            const int st = 2 * g + half;
+            const uint32_t hA = *(const uint16_t*)(wA + st * 16);
+            const uint32_t hB = *(const uint16_t*)(wB + st * 16);
+            f32x2 dA01, dA23, dB01, dB23;
+            dequant4<LIT>(hA, ssA, bbA, dA01, dA23);
+            dequant4<LIT>(hB, ssB, bbB, dB01, dB23);
+#pragma unroll
+            for (int tt = 0; tt < TT; tt++) {
+                const ulonglong2 xv = *(const ulonglong2*)(sX + tt * x_pitch + st * 32);
+                accA[tt][0] = mul_then_add(accA[tt][0], dA01, xv.x);
+                accA[tt][1] = mul_then_add(accA[tt][1], dA23, xv.y);
+                accB[tt][0] = mul_then_add(accB[tt][0], dB01, xv.x);
+                accB[tt][1] = mul_then_add(accB[tt][1], dB23, xv.y);
+            }
+        }
+    }
+}
+
+// One block = 64 threads = 8 row pairs (NMAT == 2: gate row r and up row r,
+// fused GeGLU epilogue) or 16 rows (NMAT == 1: rows r and r + 8 per lane).
 template <int NMAT, int TT>
-__global__ void __launch_bounds__(32)
+__global__ void __launch_bounds__(64)
 q4_tile_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_dev, int C) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int job_id = blockIdx.y;
@@ -29,147 +97,134 @@ q4_tile_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_dev
     constexpr int ROWS_A = (NMAT == 2) ? 8 : 16;
     const int r0 = blockIdx.x * ROWS_A;
     if (r0 >= jb.R || jb.ntok < 1) return;
-    const int lane = threadIdx.x, t = lane & 3, rsub = lane >> 2;
+    const int tid = threadIdx.x;
+    const int u = tid & 7;                       // octant: accumulators 4u..4u+3
+    const int pr = tid >> 3;                     // row slot 0..7
     const int nvalid = min(ROWS_A, jb.R - r0);
+    const TileGeom G = tile_geom(C, ROWS_A);
+    uint8_t* sW = smem;                                   // [16][w_stride]
+    uint8_t* sS = sW + 16 * G.w_stride;                   // [NMAT][sc_block]
+    uint8_t* sBi = sS + NMAT * G.sc_block;                // [NMAT][sc_block]
+    float* sX = (float*)(sBi + NMAT * G.sc_block);        // [TT][C]
 
-    const int row_bytes = C >> 1;
-    const int w_stride = row_bytes + 16;
-    const int sc_row = C >> 5;  // bytes of bf16 scales per row
-    const bool sc_padded = (sc_row & 15) == 0;
-    const int sc_stride = sc_padded ? sc_row + 16 : sc_row;
-    const int sc_block = align16(ROWS_A * sc_stride);  // one matrix' scales
-    uint8_t* sW = smem;                                // [16][w_stride]
-    uint8_t* sS = sW + 16 * w_stride;                  // [NMAT][sc_block]
-    uint8_t* sB = sS + NMAT * sc_block;                // [NMAT][sc_block]
-
-    const int steps = C >> 5;
-    int chunk_steps = 8;
-    int nch = (steps + chunk_steps - 1) / chunk_steps;
-    if (nch > 15) {
-        chunk_steps = (steps + 14) / 15;
-        nch = (steps + chunk_steps - 1) / chunk_steps;
-    }
-
-    // ---- issue every copy of this block, one commit group per K chunk ----
-    {
-        // scales / biases of the block (group 0)
+    // ---- group 0: activations of the first token block, scales, biases, K chunk 0 ----
+    auto issue_x = [&](int tb) {
+        const int ppr = C >> 2;                  // 16-byte pieces per activation row
+        for (int p = tid; p < TT * ppr; p += 64) {
+            const int tt = p / ppr, pc = p - tt * ppr;
+            const int tok = min(tb + tt, jb.ntok - 1);
+            const int row = jb.x_rows ? (jb.x_rows[tok] / jb.x_div) : tok;
+            cp_async16(sX + tt * C + pc * 4, jb.x + (size_t)row * jb.x_stride + pc * 4);
+        }
+    };
+    issue_x(0);
 #pragma unroll
-        for (int m = 0; m < NMAT; m++) {
-            const uint8_t* gs = (m == 0 ? jb.scales : jb.scales2) + (size_t)r0 * sc_row;
-            const uint8_t* gb = (m == 0 ? jb.biases : jb.biases2);
-            if (gb) gb += (size_t)r0 * sc_row;
-            uint8_t* ds = sS + m * sc_block;
-            uint8_t* db = sB + m * sc_block;
-            if (sc_padded) {
-                const int ppr = sc_row >> 4;  // 16-byte pieces per row
-                for (int p = lane; p < nvalid * ppr; p += 32) {
-                    int rr = p / ppr, pc = p - rr * ppr;
-                    cp_async16(ds + rr * sc_stride + pc * 16, gs + (size_t)rr * sc_row + pc * 16);
-                    if (gb) cp_async16(db + rr * sc_stride + pc * 16, gb + (size_t)rr * sc_row + pc * 16);
-                }
-            } else {
-                const int total = nvalid * sc_row;
-                const int full = total >> 4;
-                for (int p = lane; p < full; p += 32) {
-                    cp_async16(ds + p * 16, gs + p * 16);
-                    if (gb) cp_async16(db + p * 16, gb + p * 16);
-                }
-                for (int i = (full << 4) + lane; i < total; i += 32) {
-                    ds[i] = gs[i];
-                    if (gb) db[i] = gb[i];
-                }
+    for (int m = 0; m < NMAT; m++) {
+        const uint8_t* gs = (m == 0 ? jb.scales : jb.scales2) + (size_t)r0 * G.sc_row;
+        const uint8_t* gb = (m == 0 ? jb.biases : jb.biases2);
+        if (gb) gb += (size_t)r0 * G.sc_row;
+        uint8_t* ds = sS + m * G.sc_block;
+        uint8_t* db = sBi + m * G.sc_block;
+        if (G.sc_padded) {
+            const int ppr = G.sc_row >> 4;
+            for (int p = tid; p < nvalid * ppr; p += 64) {
+                const int rr = p / ppr, pc = p - rr * ppr;
+                cp_async16(ds + rr * G.sc_stride + pc * 16, gs + (size_t)rr * G.sc_row + pc * 16);
+                if (gb) cp_async16(db + rr * G.sc_stride + pc * 16, gb + (size_t)rr * G.sc_row + pc * 16);
             }
-            if (!gb) {
-                for (int i = lane; i < (sc_block >> 2); i += 32) ((uint32_t*)db)[i] = 0u;
+        } else {
+            const int total = nvalid * G.sc_row;
+            const int full = total >> 4;
+            for (int p = tid; p < full; p += 64) {
+                cp_async16(ds + p * 16, gs + p * 16);
+                if (gb) cp_async16(db + p * 16, gb + p * 16);
+            }
+            for (int i = (full << 4) + tid; i < total; i += 64) {
+                ds[i] = gs[i];
+                if (gb) db[i] = gb[i];
             }
         }
-        for (int ch = 0; ch < nch; ch++) {
-            const int s_begin = ch * chunk_steps;
-            const int cs = min(chunk_steps, steps - s_begin);
-            for (int p = lane; p < 16 * cs; p += 32) {
-                const int rr = p / cs, pc = p - rr * cs;
-                const int m = (NMAT == 2) ? (rr >> 3) : 0;
-                int grow = r0 + ((NMAT == 2) ? (rr & 7) : rr);
-                grow = min(grow, jb.R - 1);
-                const uint8_t* g = (m == 0 ? jb.vals : jb.vals2) + (size_t)grow * row_bytes + (s_begin + pc) * 16;
-                cp_async16(sW + rr * w_stride + (s_begin + pc) * 16, g);
-            }
-            cp_async_commit();
+        if (!gb)
+            for (int i = tid; i < (G.sc_block >> 2); i += 64) ((uint32_t*)db)[i] = 0u;
+    }
+    for (int ch = 0; ch < G.nch; ch++) {
+        const int s_begin = ch * G.chunk_steps;
+        const int cs = min(G.chunk_steps, G.steps - s_begin);
+        for (int p = tid; p < 16 * cs; p += 64) {
+            const int rr = p / cs, pc = p - rr * cs;
+            const int m = (NMAT == 2) ? (rr >> 3) : 0;
+            int grow = r0 + ((NMAT == 2) ? (rr & 7) : rr);
+            grow = min(grow, jb.R - 1);
+            const uint8_t* g = (m == 0 ? jb.vals : jb.vals2) + (size_t)grow * G.row_bytes + (s_begin + pc) * 16;
+            cp_async16(sW + rr * G.w_stride + (s_begin + pc) * 16, g);
         }
+        cp_async_commit();
     }
 
-    // thread's two weight rows: shared rows rsub and rsub + 8
-    const uint32_t* w0 = (const uint32_t*)(sW + rsub * w_stride) + t;
-    const uint32_t* w1 = (const uint32_t*)(sW + (rsub + 8) * w_stride) + t;
-    const int sc_m1 = (NMAT == 2) ? sc_block : 0;
-    const int sc_r1 = (NMAT == 2) ? rsub : rsub + 8;
-    const uint16_t* s0p = (const uint16_t*)(sS + rsub * sc_stride);
-    const uint16_t* b0p = (const uint16_t*)(sB + rsub * sc_stride);
-    const uint16_t* s1p = (const uint16_t*)(sS + sc_m1 + sc_r1 * sc_stride);
-    const uint16_t* b1p = (const uint16_t*)(sB + sc_m1 + sc_r1 * sc_stride);
+    // ---- this thread's operands ----
+    const uint8_t* wA = sW + pr * G.w_stride + 2 * u;
+    const uint8_t* wB = sW + (pr + 8) * G.w_stride + 2 * u;
+    const int scB_block = (NMAT == 2) ? G.sc_block : 0;
+    const int scB_row = (NMAT == 2) ? pr : pr + 8;
+    const uint16_t* sA = (const uint16_t*)(sS + pr * G.sc_stride);
+    const uint16_t* bA = (const uint16_t*)(sBi + pr * G.sc_stride);
+    const uint16_t* sB = (const uint16_t*)(sS + scB_block + scB_row * G.sc_stride);
+    const uint16_t* bB = (const uint16_t*)(sBi + scB_block + scB_row * G.sc_stride);
+    const float* xs = sX + 4 * u;
+
+    // wait for group 0, then decide whether any scale of the block needs the
+    // literal (two-rounding) dequantisation
+    cp_async_wait_dyn(G.nch - 1);
+    __syncthreads();
+    int lit = 0;
+    {
+        const int rows_here = (NMAT == 2) ? 8 : 16;
+        const int gpr = C >> 6;                  // groups per row
+        for (int i = tid; i < NMAT * rows_here * gpr; i += 64) {
+            const int m = i / (rows_here * gpr), rem = i - m * rows_here * gpr;
+            const int rr = rem / gpr, gg = rem - rr * gpr;
+            if (rr < nvalid)
+                lit |= scale_needs_literal(((const uint16_t*)(sS + m * G.sc_block + rr * G.sc_stride))[gg]) ? 1 : 0;
+        }
+    }
+    lit = __syncthreads_or(lit);
 
     for (int tb = 0; tb < jb.ntok; tb += TT) {
-        const float* xp[TT];
+        if (tb > 0) {
+            __syncthreads();                     // everyone is done with the previous activations
+            issue_x(tb);
+            cp_async_commit();
+            cp_async_wait_dyn(0);
+            __syncthreads();
+        }
+        f32x2 accA[TT][2], accB[TT][2];
 #pragma unroll
         for (int tt = 0; tt < TT; tt++) {
-            int tok = min(tb + tt, jb.ntok - 1);
-            int row = jb.x_rows ? (jb.x_rows[tok] / jb.x_div) : tok;
-            xp[tt] = jb.x + (size_t)row * jb.x_stride + 8 * t;
+            accA[tt][0] = accA[tt][1] = accB[tt][0] = accB[tt][1] = pack2(0.0f, 0.0f);
         }
-        float acc0[TT][8], acc1[TT][8];
-#pragma unroll
-        for (int tt = 0; tt < TT; tt++)
-#pragma unroll
-            for (int m = 0; m < 8; m++) { acc0[tt][m] = 0.0f; acc1[tt][m] = 0.0f; }
-
-        for (int ch = 0; ch < nch; ch++) {
-            if (tb == 0) {
-                cp_async_wait_dyn(nch - 1 - ch);
-                __syncwarp();
+        for (int ch = 0; ch < G.nch; ch++) {
+            if (tb == 0 && ch > 0) {
+                cp_async_wait_dyn(G.nch - 1 - ch);
+                __syncthreads();
             }
-            const int s_begin = ch * chunk_steps;
-            const int s_end = min(s_begin + chunk_steps, steps);
-            float sA = 0.0f, bA = 0.0f, sB_ = 0.0f, bB_ = 0.0f;
-            bool litA = false, litB = false;
-#pragma unroll 2
-            for (int st = s_begin; st < s_end; st++) {
-                if ((st & 1) == 0 || st == s_begin) {
-                    const int g = st >> 1;
-                    uint32_t hs0 = s0p[g], hs1 = s1p[g];
-                    sA = bf16_bits_to_f32(hs0); bA = bf16_bits_to_f32(b0p[g]);
-                    sB_ = bf16_bits_to_f32(hs1); bB_ = bf16_bits_to_f32(b1p[g]);
-                    litA = scale_needs_literal(hs0); litB = scale_needs_literal(hs1);
-                }
-                float d0[8], d1[8];
-                dequant8(w0[st * 4], sA, bA, litA, d0);
-                dequant8(w1[st * 4], sB_, bB_, litB, d1);
-#pragma unroll
-                for (int tt = 0; tt < TT; tt++) {
-                    const float4 xa = __ldg((const float4*)(xp[tt] + st * 32));
-                    const float4 xb = __ldg((const float4*)(xp[tt] + st * 32 + 4));
-                    const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-#pragma unroll
-                    for (int m = 0; m < 8; m++) {
-                        acc0[tt][m] = __fadd_rn(acc0[tt][m], __fmul_rn(d0[m], xv[m]));
-                        acc1[tt][m] = __fadd_rn(acc1[tt][m], __fmul_rn(d1[m], xv[m]));
-                    }
-                }
-            }
+            const int s_begin = ch * G.chunk_steps;
+            const int s_end = min(s_begin + G.chunk_steps, G.steps);
+            if (lit) tile_steps<TT, true>(s_begin, s_end, wA, wB, sA, bA, sB, bB, xs, C, accA, accB);
+            else tile_steps<TT, false>(s_begin, s_end, wA, wB, sA, bA, sB, bB, xs, C, accA, accB);
         }
-
 #pragma unroll
         for (int tt = 0; tt < TT; tt++) {
-            const float y0 = fold_row_quarters(acc0[tt], t);
-            const float y1 = fold_row_quarters(acc1[tt], t);
+            const float y0 = fold_row_octants(accA[tt][0], accA[tt][1], u);
+            const float y1 = fold_row_octants(accB[tt][0], accB[tt][1], u);
             const int tok = tb + tt;
-            if (t == 3 && tok < jb.ntok) {
+            if (u == 7 && tok < jb.ntok) {
                 float* yrow = jb.y + (size_t)tok * jb.y_stride;
                 if (NMAT == 2) {
                     // fused GeGLU (reference gemma4.c:80-83 then gate*up)
-                    if (rsub < nvalid) yrow[r0 + rsub] = __fmul_rn(gelu_tanh_exact(y0), y1);
+                    if (pr < nvalid) yrow[r0 + pr] = __fmul_rn(gelu_tanh_exact(y0), y1);
                 } else {
-                    if (rsub < nvalid) yrow[r0 + rsub] = y0;
-                    if (rsub + 8 < nvalid) yrow[r0 + rsub + 8] = y1;
+                    if (pr < nvalid) yrow[r0 + pr] = y0;
+                    if (pr + 8 < nvalid) yrow[r0 + pr + 8] = y1;
                 }
             }
         }
@@ -222,21 +277,17 @@ q4_generic_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_
     }
 }
 
-static size_t tile_smem_bytes(int C, int nmat) {
-    int row_bytes = C / 2, w_stride = row_bytes + 16;
-    int sc_row = C / 32;
-    int sc_stride = (sc_row % 16 == 0) ? sc_row + 16 : sc_row;
-    int rows_a = nmat == 2 ? 8 : 16;
-    int sc_block = (rows_a * sc_stride + 15) & ~15;
-    return (size_t)16 * w_stride + (size_t)2 * nmat * sc_block;
+static size_t tile_smem_bytes(int C, int nmat, int tt) {
+    const TileGeom g = tile_geom(C, nmat == 2 ? 8 : 16);
+    return (size_t)16 * g.w_stride + (size_t)2 * nmat * g.sc_block + (size_t)tt * C * sizeof(float);
 }
 
-bool q4_tile_supported(int C) { return C >= 64 && (C % 64) == 0 && tile_smem_bytes(C, 2) <= 200 * 1024; }
+bool q4_tile_supported(int C) { return C >= 64 && (C % 64) == 0 && tile_smem_bytes(C, 2, 4) <= 200 * 1024; }
 
 template <int NMAT, int TT>
 static cudaError_t launch_tile(const Q4Job* jobs, int njobs_max, const int* njobs_dev, int max_rows, int C,
                                cudaStream_t stream) {
-    size_t smem = tile_smem_bytes(C, NMAT);
+    size_t smem = tile_smem_bytes(C, NMAT, TT);
     static size_t configured = 0;
     if (smem > 48 * 1024 && smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(q4_tile_kernel<NMAT, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -246,7 +297,7 @@ static cudaError_t launch_tile(const Q4Job* jobs, int njobs_max, const int* njob
     }
     constexpr int ROWS_A = NMAT == 2 ? 8 : 16;
     dim3 grid((max_rows + ROWS_A - 1) / ROWS_A, njobs_max);
-    q4_tile_kernel<NMAT, TT><<<grid, 32, smem, stream>>>(jobs, njobs_dev, C);
+    q4_tile_kernel<NMAT, TT><<<grid, 64, smem, stream>>>(jobs, njobs_dev, C);
     return cudaGetLastError();
 }
 

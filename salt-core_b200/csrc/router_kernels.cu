@@ -15,23 +15,22 @@ static __device__ __forceinline__ void flag(int* status, int bit) {
 }
 
 // Serial sum of squares of one row, in element order, as the reference does
-// (gemma4.c:46-62, src/text_verify_cpu.c:642-655).  Lanes compute the squares
-// of 32 consecutive elements in parallel; every lane then replays the same
-// 32-step add chain on shuffled values, so only the adds are serial.
-static __device__ __forceinline__ float serial_sum_squares_warp(const float* row_smem, int n, int lane) {
+// (gemma4.c:46-62, src/text_verify_cpu.c:642-655).  The squares are formed in
+// parallel beforehand; one thread then runs the add chain over them, reading
+// shared memory 16 bytes at a time so the loads run ahead of the 4-cycle adds.
+static __device__ __forceinline__ float serial_sum(const float* sq, int n) {
     float ss = 0.0f;
-    int base = 0;
-    for (; base + 32 <= n; base += 32) {
-        const float v = row_smem[base + lane];
-        const float sq = __fmul_rn(v, v);
-#pragma unroll
-        for (int j = 0; j < 32; j++) ss = __fadd_rn(ss, __shfl_sync(0xffffffffu, sq, j));
+    int i = 0;
+    if ((((uintptr_t)sq) & 15) == 0) {
+#pragma unroll 4
+        for (; i + 8 <= n; i += 8) {
+            const float4 a = *(const float4*)(sq + i);
+            const float4 b = *(const float4*)(sq + i + 4);
+            ss = __fadd_rn(ss, a.x); ss = __fadd_rn(ss, a.y); ss = __fadd_rn(ss, a.z); ss = __fadd_rn(ss, a.w);
+            ss = __fadd_rn(ss, b.x); ss = __fadd_rn(ss, b.y); ss = __fadd_rn(ss, b.z); ss = __fadd_rn(ss, b.w);
+        }
     }
-    if (base < n) {
-        const float v = (base + lane < n) ? row_smem[base + lane] : 0.0f;
-        const float sq = __fmul_rn(v, v);
-        for (int j = 0; j < n - base; j++) ss = __fadd_rn(ss, __shfl_sync(0xffffffffu, sq, j));
-    }
+    for (; i < n; i++) ss = __fadd_rn(ss, sq[i]);
     return ss;
 }
 
@@ -41,7 +40,8 @@ template <int MODE>
 __global__ void __launch_bounds__(256)
 norm_rows_kernel(const float* __restrict__ x, const float* __restrict__ weight, float* __restrict__ y, int n,
                  float eps, int with_scale, float root_in, int* status) {
-    extern __shared__ float srow[];
+    extern __shared__ __align__(16) float srow[];   // [n] row, then [n (padded to 4)] squares
+    float* ssq = srow + ((n + 3) & ~3);
     __shared__ float s_inv, s_root;
     const float* xr = x + (size_t)blockIdx.x * n;
     float* yr = y + (size_t)blockIdx.x * n;
@@ -49,13 +49,14 @@ norm_rows_kernel(const float* __restrict__ x, const float* __restrict__ weight, 
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         const float v = xr[i];
         srow[i] = v;
+        ssq[i] = __fmul_rn(v, v);
         bad |= !finite_f(v);
         if (MODE == 1 || with_scale) bad |= !finite_f(weight[i]);
     }
     __syncthreads();
-    if (threadIdx.x < 32) {
-        const float ss = serial_sum_squares_warp(srow, n, threadIdx.x);
-        if (threadIdx.x == 0) {
+    if (threadIdx.x == 0) {
+        const float ss = serial_sum(ssq, n);
+        {
             const float mean = __fadd_rn(__fdiv_rn(ss, (float)n), eps);
             const float inv = pow_neg_half(mean);
             float root = 1.0f;
@@ -84,7 +85,7 @@ norm_rows_kernel(const float* __restrict__ x, const float* __restrict__ weight, 
 cudaError_t launch_rmsnorm(const float* x, const float* weight, float* y, int rows, int n, float eps, int with_scale,
                            int* status, cudaStream_t stream) {
     if (rows < 1) return cudaSuccess;
-    norm_rows_kernel<0><<<rows, 256, (size_t)n * sizeof(float), stream>>>(x, weight, y, n, eps, with_scale, 0.0f,
+    norm_rows_kernel<0><<<rows, 256, (size_t)(2 * n + 8) * sizeof(float), stream>>>(x, weight, y, n, eps, with_scale, 0.0f,
                                                                            status);
     return cudaGetLastError();
 }
@@ -92,51 +93,34 @@ cudaError_t launch_rmsnorm(const float* x, const float* weight, float* y, int ro
 cudaError_t launch_router_input(const float* x, const float* scale, float* out, int rows, int n, float eps,
                                 float root, int* status, cudaStream_t stream) {
     if (rows < 1) return cudaSuccess;
-    norm_rows_kernel<1><<<rows, 256, (size_t)n * sizeof(float), stream>>>(x, scale, out, n, eps, 1, root, status);
+    norm_rows_kernel<1><<<rows, 256, (size_t)(2 * n + 8) * sizeof(float), stream>>>(x, scale, out, n, eps, 1, root, status);
     return cudaGetLastError();
 }
 
-// One warp per (row, expert): the reference chain acc = fl(acc + fl(W[e][c]*x[c]))
-// (src/kernels.c:98-106).  Lanes load W and x coalesced and form the products;
-// the add chain is replayed by all lanes on shuffled products.
+// Small batches: one block per (expert, block of up to LOGIT_TB rows).  All
+// threads form the products fl(W[e][c]*x[r][c]) (coalesced loads) into shared
+// memory; then one thread per row runs the reference chain
+// acc = fl(acc + p[c]) over them (src/kernels.c:98-106).
+constexpr int LOGIT_TB = 8;
+
 __global__ void __launch_bounds__(128)
-router_logits_warp_kernel(const float* __restrict__ W, const float* __restrict__ bias, const float* __restrict__ x,
-                          float* __restrict__ logits, int E, int H) {
-    const int e = blockIdx.x * 4 + (threadIdx.x >> 5);
-    const int row = blockIdx.y;
-    if (e >= E) return;
-    const int lane = threadIdx.x & 31;
+router_logits_block_kernel(const float* __restrict__ W, const float* __restrict__ bias,
+                           const float* __restrict__ x, float* __restrict__ logits, int rows, int E, int H) {
+    extern __shared__ __align__(16) float sprod[];       // [nr][pitch]
+    const int e = blockIdx.x;
+    const int r0 = blockIdx.y * LOGIT_TB;
+    const int nr = min(LOGIT_TB, rows - r0);
+    const int pitch = ((H + 3) & ~3) + 4;                // +4 floats: rows start in different banks
     const float* w = W + (size_t)e * H;
-    const float* xr = x + (size_t)row * H;
-    float acc = 0.0f;
-    constexpr int G = 8;  // 32-column blocks fetched ahead: covers L2/HBM latency behind the add chain
-    float pn[G];
-#pragma unroll
-    for (int b = 0; b < G; b++) {
-        const int c = b * 32 + lane;
-        pn[b] = (c < H) ? __fmul_rn(__ldg(w + c), __ldg(xr + c)) : 0.0f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float wv = __ldg(w + c);
+        for (int r = 0; r < nr; r++) sprod[r * pitch + c] = __fmul_rn(wv, __ldg(x + (size_t)(r0 + r) * H + c));
     }
-    for (int g0 = 0; g0 < H; g0 += 32 * G) {
-        float p[G];
-#pragma unroll
-        for (int b = 0; b < G; b++) p[b] = pn[b];
-#pragma unroll
-        for (int b = 0; b < G; b++) {
-            const int c = g0 + 32 * G + b * 32 + lane;
-            pn[b] = (c < H) ? __fmul_rn(__ldg(w + c), __ldg(xr + c)) : 0.0f;
-        }
-#pragma unroll
-        for (int b = 0; b < G; b++) {
-            const int left = H - (g0 + 32 * b);
-            if (left >= 32) {
-#pragma unroll
-                for (int j = 0; j < 32; j++) acc = __fadd_rn(acc, __shfl_sync(0xffffffffu, p[b], j));
-            } else {
-                for (int j = 0; j < left; j++) acc = __fadd_rn(acc, __shfl_sync(0xffffffffu, p[b], j));
-            }
-        }
+    __syncthreads();
+    if (threadIdx.x < nr) {
+        const float acc = serial_sum(sprod + threadIdx.x * pitch, H);
+        logits[(size_t)(r0 + threadIdx.x) * E + e] = __fadd_rn(acc, bias ? bias[e] : 0.0f);
     }
-    if (lane == 0) logits[(size_t)row * E + e] = __fadd_rn(acc, bias ? bias[e] : 0.0f);
 }
 
 // Thread per (row, expert) for large batches: 32 experts x 8 rows per block,
@@ -172,9 +156,19 @@ router_logits_tile_kernel(const float* __restrict__ W, const float* __restrict__
 cudaError_t launch_router_logits(const float* W, const float* bias, const float* x, float* logits, int rows, int E,
                                  int H, cudaStream_t stream) {
     if (rows < 1) return cudaSuccess;
-    if (rows <= 16) {
-        dim3 grid((E + 3) / 4, rows);
-        router_logits_warp_kernel<<<grid, 128, 0, stream>>>(W, bias, x, logits, E, H);
+    if (rows <= 32) {
+        const int nr = rows < LOGIT_TB ? rows : LOGIT_TB;
+        const size_t smem = (size_t)nr * (((H + 3) & ~3) + 4) * sizeof(float);
+        static bool configured = false;
+        if (smem > 48 * 1024 && !configured) {
+            cudaError_t e = cudaFuncSetAttribute(router_logits_block_kernel,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (e != cudaSuccess) return e;
+            configured = true;
+        }
+        if (smem > 200 * 1024) return cudaErrorInvalidValue;
+        dim3 grid(E, (rows + LOGIT_TB - 1) / LOGIT_TB);
+        router_logits_block_kernel<<<grid, 128, smem, stream>>>(W, bias, x, logits, rows, E, H);
     } else {
         dim3 grid((E + 31) / 32, (rows + 7) / 8);
         router_logits_tile_kernel<<<grid, 256, 0, stream>>>(W, bias, x, logits, rows, E, H);
@@ -231,8 +225,7 @@ router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ p
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        float all = 0.0f;
-        for (int e = 0; e < E; e++) all = __fadd_rn(all, se[e]);
+        const float all = serial_sum(se, E);
         s_all = all;
         if (!(all > 0.0f) || !finite_f(all)) s_bad = 1;
         float selsum = 0.0f;
@@ -307,19 +300,44 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(MoePlanArgs a) {
         offs[e] = run;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int run = 0, nact = 0, mg = 0;
-        for (int e = 0; e < E; e++) {
-            const int c = offs[e];
-            offs[e] = run;
-            run += c;
-            const bool local = e >= a.expert_begin && e < a.expert_end && c > 0;
-            act[e] = local ? nact : -1;
-            if (local) { nact++; mg = max(mg, c); }
+    // exclusive scans over experts (E <= 1024 = one expert per thread): group
+    // starts, and the compacted index of each local non-empty expert
+    {
+        __shared__ int warp_cnt[32], warp_act[32], s_max[32];
+        const int e = threadIdx.x;
+        const int c = e < E ? offs[e] : 0;
+        const int local = (e < E && e >= a.expert_begin && e < a.expert_end && c > 0) ? 1 : 0;
+        int pc = c, pa = local, mx = local ? c : 0;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int tc = __shfl_up_sync(0xffffffffu, pc, o);
+            const int ta = __shfl_up_sync(0xffffffffu, pa, o);
+            if (lane >= o) { pc += tc; pa += ta; }
+            mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
         }
-        offs[E] = run;
-        *a.n_active = nact;
-        *a.max_group = mg;
+        if (lane == 31) { warp_cnt[warp] = pc; warp_act[warp] = pa; }
+        if (lane == 0) s_max[warp] = mx;
+        __syncthreads();
+        if (warp == 0) {
+            int wc = warp_cnt[lane], wa = warp_act[lane], wm = s_max[lane];
+            const int tot_c = wc, tot_a = wa;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int tc = __shfl_up_sync(0xffffffffu, wc, o);
+                const int ta = __shfl_up_sync(0xffffffffu, wa, o);
+                if (lane >= o) { wc += tc; wa += ta; }
+                wm = max(wm, __shfl_xor_sync(0xffffffffu, wm, o));
+            }
+            warp_cnt[lane] = wc - tot_c;     // exclusive prefix of the warp totals
+            warp_act[lane] = wa - tot_a;
+            if (lane == 31) { offs[E] = wc; *a.n_active = wa; }
+            if (lane == 0) *a.max_group = wm;
+        }
+        __syncthreads();
+        if (e < E) {
+            offs[e] = warp_cnt[warp] + pc - c;
+            act[e] = local ? warp_act[warp] + pa - 1 : -1;
+        }
     }
     __syncthreads();
     for (int e = threadIdx.x; e <= E; e += blockDim.x) a.group_offsets[e] = offs[e];
@@ -389,15 +407,21 @@ weighted_reduce_kernel(const float* __restrict__ weights, const int32_t* __restr
     const int d = blockIdx.x * blockDim.x + threadIdx.x;
     if (d >= width) return;
     float acc = 0.0f;
-    for (int rank = 0; rank < topk; rank++) {
-        const int canonical = row * topk + rank;
-        const int g = c2g[canonical];
-        const float w = weights[canonical];
-        if (g < 0 || g >= jobs || !finite_f(w)) {
-            if (d == 0) flag(status, g < 0 || g >= jobs ? SB_ERR_INDEX : SB_ERR_NONFINITE);
-            continue;
+    for (int r0 = 0; r0 < topk; r0 += 8) {
+        float w[8], v[8];
+        bool ok[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int canonical = row * topk + min(r0 + i, topk - 1);
+            const int g = c2g[canonical];
+            w[i] = weights[canonical];
+            ok[i] = g >= 0 && g < jobs && finite_f(w[i]);
+            v[i] = ok[i] ? grouped[(size_t)g * width + d] : 0.0f;
+            if (!ok[i] && d == 0 && r0 + i < topk) flag(status, g < 0 || g >= jobs ? SB_ERR_INDEX : SB_ERR_NONFINITE);
         }
-        acc = __fadd_rn(acc, __fmul_rn(w, grouped[(size_t)g * width + d]));
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            if (r0 + i < topk && ok[i]) acc = __fadd_rn(acc, __fmul_rn(w[i], v[i]));
     }
     out[(size_t)row * width + d] = acc;
 }

@@ -86,6 +86,27 @@ class MoeStack:
         return self.lib.salt_b200_layer_combine(self.handle, layer, B, C.c_void_p(d_y), int(apply_norm),
                                                 C.c_void_p(stream))
 
+    KERNEL_CLASSES = ("router_input", "router_logits", "router_topk", "plan", "gate_up_geglu", "down",
+                      "weighted_reduce", "rmsnorm")
+
+    def graph_capture(self, d_x, B, d_y, stream, first=0, count=None):
+        count = self.n_layers - first if count is None else count
+        return self.lib.salt_b200_stack_graph_capture(self.handle, first, count, C.c_void_p(d_x), B,
+                                                      C.c_void_p(d_y), C.c_void_p(stream))
+
+    def graph_launch(self, stream):
+        return self.lib.salt_b200_stack_graph_launch(self.handle, C.c_void_p(stream))
+
+    def profile(self, enable, max_launches=4096):
+        return self.lib.salt_b200_stack_profile(self.handle, int(enable), max_launches)
+
+    def profile_read(self):
+        ms = (C.c_float * 8)()
+        n = (C.c_int * 8)()
+        if self.lib.salt_b200_stack_profile_read(self.handle, ms, n, 8) != 0:
+            raise RuntimeError("salt_b200_stack_profile_read failed")
+        return {k: (float(ms[i]), int(n[i])) for i, k in enumerate(self.KERNEL_CLASSES)}
+
     def status(self, stream=0):
         return self.lib.salt_b200_stack_status(self.handle, C.c_void_p(stream))
 

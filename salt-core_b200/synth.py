@@ -112,3 +112,27 @@ def make_q4_moe_layer(seed: int, hidden=2816, inter=704, n_experts=128, topk=8,
 
 def make_tokens(seed: int, B: int, hidden: int) -> np.ndarray:
     return np.random.default_rng(seed).standard_normal((B, hidden)).astype(np.float32)
+
+
+def make_q4_moe_layer_bulk(seed: int, hidden=2816, inter=704, n_experts=128, topk=8, eps=1e-6,
+                           router_std=0.02) -> Q4MoeLayer:
+    """Same distributions as ``make_q4_moe_layer`` drawn in a few vectorised
+    calls (a different value stream): used for the full-size benchmark stack,
+    where a layer holds 428 MB of expert weights."""
+    rng = np.random.default_rng(seed)
+    vb, gb = q4_tensor_bytes(inter, hidden)
+    tb = vb + 2 * gb
+    stride = 3 * tb
+    pool = rng.integers(0, 2**64, (n_experts * stride + 7) // 8, dtype=np.uint64).view(np.uint8)[:n_experts * stride]
+    view = pool.reshape(n_experts * 3, tb)
+    s = bf16_round(rng.uniform(0.005, 0.02, (n_experts * 3, gb // 2)).astype(np.float32))
+    b = bf16_round(np.float32(-8.0) * bf16_to_f32(s))
+    view[:, vb:vb + gb] = s.view(np.uint8).reshape(n_experts * 3, gb)
+    view[:, vb + gb:] = b.view(np.uint8).reshape(n_experts * 3, gb)
+    return Q4MoeLayer(
+        hidden, inter, n_experts, topk, eps,
+        router_w=(rng.standard_normal((n_experts, hidden)) * router_std).astype(np.float32),
+        router_scale=np.ones(hidden, np.float32),
+        per_expert_scale=np.ones(n_experts, np.float32),
+        pool=pool, expert_stride=stride,
+        norm_weight=(1.0 + 0.1 * rng.standard_normal(hidden)).astype(np.float32))

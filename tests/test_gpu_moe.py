@@ -172,7 +172,7 @@ def test_stack_expert_sharding_union_equals_single_device(orc, synth):
     want, _, _ = orc.moe_layer_q4(layer, x, threads=4)
     sm = stack_mod()
     d_x = torch.from_numpy(x).cuda()
-    shared = torch.zeros(B * K * H, dtype=torch.float32, device="cuda")
+    shared = torch.zeros(8 * K * H, dtype=torch.float32, device="cuda")   # max_tokens rows
     halves = []
     for lo, hi in ((0, 16), (16, 32)):
         st = sm.MoeStack(8, H, M, E, K, expert_begin=lo, expert_end=hi)
