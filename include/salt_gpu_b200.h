@@ -376,6 +376,32 @@ int salt_b200_route_group_device(const int32_t *d_selected, int rows, int topk, 
                                  int32_t *d_group_offsets, int32_t *d_grouped_to_canonical,
                                  int32_t *d_canonical_to_grouped, void *stream);
 
+/* One expert's chain y = down(gelu_tanh(gate x) * up x) for ntok activation rows,
+ * all pointers in DEVICE memory (16-byte aligned), asynchronous on `stream`.
+ * No counterpart in the reference: this entry point exists for callers that
+ * cannot allocate device memory -- an engine whose own allocator already owns
+ * the whole device, a plugin that must keep a pre-sized budget, a loop that
+ * cannot afford the synchronisation an allocation implies.  It calls no
+ * allocation routine; its
+ * intermediate rows live in a fixed 256 KiB array inside the library image
+ * that every GPU loading the library holds until the process exits.
+ *   - limit: ntok * inter <= 65536 floats (e.g. 93 rows at inter = 704); larger
+ *     calls are rejected with -1 and a message on stderr.  hidden and inter
+ *     must be positive multiples of 64.
+ *   - the first call on a device looks the array's address up; make that call
+ *     before any stream capture.
+ *   - all calls on a device share the array, which keeps the previous call's
+ *     contents (nothing in it needs clearing: each call writes what it reads);
+ *     two calls whose kernels overlap on the GPU race on it -- issue them on
+ *     one stream or order them yourself.
+ * Results are bit-identical to salt_gpu_q4_moe_chain on the same data. */
+int salt_b200_q4_expert_chain_static(const void *d_gate_vals, const void *d_gate_scales,
+                                     const void *d_gate_biases, const void *d_up_vals,
+                                     const void *d_up_scales, const void *d_up_biases,
+                                     const void *d_down_vals, const void *d_down_scales,
+                                     const void *d_down_biases, int hidden, int inter, const float *d_x,
+                                     int ntok, float *d_y, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
