@@ -237,10 +237,11 @@ def run_b200(args):
         for l in range(L):
             last = l == L - 1
             out = dst if last else act[l & 1]
-            if stack.layer_experts(l, cur, B, zero_remote=True, stream=sp) != 0:
+            if stack.layer_experts(l, cur, B, zero_remote=True, router_input_ready=l > 0, stream=sp) != 0:
                 raise RuntimeError("layer_experts failed")
             dist.all_reduce(grouped)          # each row is written by one rank, the others add +0
-            if stack.layer_combine(l, B, out.data_ptr(), apply_norm=not last, stream=sp) != 0:
+            if stack.layer_combine(l, B, out.data_ptr(), apply_norm=not last, prepare_next=not last,
+                                   stream=sp) != 0:
                 raise RuntimeError("layer_combine failed")
             cur = out.data_ptr()
 
@@ -330,8 +331,8 @@ def run_b200(args):
             cur = d_x.data_ptr()
             for l in range(L):
                 out = act[l & 1]
-                stack.layer_experts(l, cur, B, stream=sp)
-                stack.layer_combine(l, B, out.data_ptr(), apply_norm=True, stream=sp)
+                stack.layer_experts(l, cur, B, router_input_ready=l > 0, stream=sp)
+                stack.layer_combine(l, B, out.data_ptr(), apply_norm=True, prepare_next=True, stream=sp)
                 import ctypes as C
                 lib.salt_b200_read_device(C.c_void_p(offs.ctypes.data), C.c_void_p(ws.group_offsets),
                                           C.c_size_t(offs.nbytes))

@@ -336,12 +336,18 @@ int salt_b200_stack_set_grouped_out(void *stack, void *device_buffer, size_t nby
 
 /* Phase A of one layer on `stream` (a cudaStream_t, NULL = default stream):
  * router input, logits, top-k, grouping, gate/up + GeGLU, down for the local
- * experts.  d_x is [B][hidden] in device memory.  zero_remote != 0 first clears
- * grouped_out so that rows of remote experts read as +0. */
-int salt_b200_layer_experts(void *stack, int layer, const float *d_x, int B, int zero_remote, void *stream);
-/* Phase B: ordered weighted reduce of grouped_out into d_y [B][hidden]; when
- * apply_norm != 0 and the layer has a norm weight, d_y = RMSNorm(reduce). */
-int salt_b200_layer_combine(void *stack, int layer, int B, float *d_y, int apply_norm, void *stream);
+ * experts.  d_x is [B][hidden] in device memory.  flags:
+ *   SALT_B200_EXPERTS_ZERO_REMOTE         clear grouped_out first, so rows of remote experts read as +0
+ *   SALT_B200_EXPERTS_ROUTER_INPUT_READY  the previous layer's combine already prepared the router input */
+#define SALT_B200_EXPERTS_ZERO_REMOTE 1
+#define SALT_B200_EXPERTS_ROUTER_INPUT_READY 2
+int salt_b200_layer_experts(void *stack, int layer, const float *d_x, int B, int flags, void *stream);
+/* Phase B: ordered weighted reduce of grouped_out into d_y [B][hidden].  flags:
+ *   SALT_B200_COMBINE_NORM          d_y = RMSNorm(reduce) when the layer has a norm weight
+ *   SALT_B200_COMBINE_PREPARE_NEXT  also form the router input of layer + 1 from d_y (same launch) */
+#define SALT_B200_COMBINE_NORM 1
+#define SALT_B200_COMBINE_PREPARE_NEXT 2
+int salt_b200_layer_combine(void *stack, int layer, int B, float *d_y, int flags, void *stream);
 /* Layers [first, first+count) back to back (phase A + B each), chained through
  * the layers' RMSNorm; d_x and d_y are device pointers and may alias. */
 int salt_b200_stack_forward_device(void *stack, int first, int count, const float *d_x, int B, float *d_y,

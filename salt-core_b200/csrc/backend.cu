@@ -25,6 +25,7 @@
 
 namespace sb {
 
+void fp4_release();
 Backend g_backend;
 static uint64_t g_launches = 0;
 void count_launches(int n) { g_launches += (uint64_t)n; }
@@ -258,6 +259,7 @@ int salt_gpu_free(void) {
     if (B.h_y) cudaFreeHost(B.h_y);
     if (B.h_jobs) cudaFreeHost(B.h_jobs);
     if (B.stream) cudaStreamDestroy(B.stream);
+    fp4_release();
     const SaltGpuBatchStatsV2 keep = B.stats;
     const int mapped_only = B.mapped_only;
     B = Backend();

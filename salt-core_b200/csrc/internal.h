@@ -16,6 +16,22 @@ bool q4_tile_supported(int C);
 cudaError_t launch_q4_jobs(const Q4Job* jobs, int njobs_max, const int* njobs_dev, int max_rows, int max_tok, int C,
                            int nmat, bool aligned, cudaStream_t stream);
 
+// ---- nvfp4_kernels.cu ------------------------------------------------------
+// One NVFP4 projection job: ntok rows of already dequantised activations.
+struct Fp4Job {
+    const uint8_t* codes;    // [R][C/2] E2M1, low nibble = even column
+    const uint8_t* scales;   // [R][C/16] E4M3FN
+    float wg;                // 1 / stored weight divisor
+    const float* x;          // [ntok][x_stride] dequantised activations
+    float* y;                // y[t*y_stride + r]
+    int R, C, ntok, x_stride, y_stride;
+};
+// ig_rows[row] = input global scale of the row's tensor
+cudaError_t launch_nvfp4_qdq(const float* x, int rows, int C, const float* ig_rows, uint8_t* packed, uint8_t* scales,
+                             float* dequant, int* status, cudaStream_t stream);
+cudaError_t launch_nvfp4_jobs(const Fp4Job* jobs, int njobs, int max_rows, int max_tok, int C, bool aligned,
+                              cudaStream_t stream);
+
 // ---- router_kernels.cu ---------------------------------------------------
 // Device-side error word: 0 = ok; set (never cleared) by kernels that meet a
 // non-finite value or an invalid index, as the reference's CPU functions
@@ -28,6 +44,23 @@ cudaError_t launch_rmsnorm(const float* x, const float* weight, float* y, int ro
 // out = ((x * inv) * scale) * root; root <= 0 selects 1/sqrt(n)
 cudaError_t launch_router_input(const float* x, const float* scale, float* out, int rows, int n, float eps,
                                 float root, int* status, cudaStream_t stream);
+// Fused per-row glue: [ordered weighted reduce] -> [RMSNorm] -> [router input].
+struct GlueArgs {
+    const float* weights;        // reduce: [rows*topk]; grouped == null skips the reduce
+    const int32_t* c2g;
+    const float* grouped;        // [jobs][n]
+    int topk, jobs;
+    const float* x_in;           // [rows][n], used when there is no reduce
+    float* y_out;                // [rows][n] row after reduce/norm, or null
+    const float* norm_w;         // [n] or null
+    float eps_norm;
+    const float* router_scale;   // [n] or null
+    float eps_router;
+    float* rin;                  // [rows][n]
+    int n;
+    int* status;
+};
+cudaError_t launch_glue(const GlueArgs& a, int rows, cudaStream_t stream);
 // logits[t][e] = serial dot of W[e][:] with x[t][:]  (+ bias[e])
 cudaError_t launch_router_logits(const float* W, const float* bias, const float* x, float* logits, int rows, int E,
                                  int H, cudaStream_t stream);
@@ -38,6 +71,12 @@ cudaError_t launch_router_topk(const float* logits, const float* per_expert_scal
 // Grouping of rows*topk selections by expert (stable counting sort) plus the
 // job descriptors the expert kernels consume.
 struct MoePlanArgs {
+    // optional fused router top-k (rows <= 8): when logits != null the kernel first
+    // computes selected_out / weights_out from the logits, and `selected` must alias selected_out
+    const float* logits;
+    const float* per_expert_scale;
+    int32_t* selected_out;
+    float* weights_out;
     const int32_t* selected;     // [rows*topk]
     int rows, topk, n_experts;
     int expert_begin, expert_end;  // experts owned by this device (others are skipped)

@@ -197,34 +197,48 @@ int salt_b200_stack_set_grouped_out(void* stack, void* device_buffer, size_t nby
     return 0;
 }
 
-int salt_b200_layer_experts(void* stack, int layer, const float* d_x, int B, int zero_remote, void* stream_) {
+// flags for salt_b200_layer_experts / salt_b200_layer_combine
+enum { SB_EXPERTS_ZERO_REMOTE = 1, SB_EXPERTS_ROUTER_INPUT_READY = 2 };
+enum { SB_COMBINE_NORM = 1, SB_COMBINE_PREPARE_NEXT = 2 };
+
+int salt_b200_layer_experts(void* stack, int layer, const float* d_x, int B, int flags, void* stream_) {
     Stack* s = (Stack*)stack;
     cudaStream_t st = (cudaStream_t)stream_;
     if (!s || layer < 0 || layer >= (int)s->layers.size() || !d_x || B < 1 || B > s->max_tokens) return -1;
     const Layer& l = s->layers[(size_t)layer];
     const int H = s->hidden, M = s->inter, E = s->n_experts, K = s->topk;
     const int jobs = B * K;
-    if (zero_remote &&
+    if ((flags & SB_EXPERTS_ZERO_REMOTE) &&
         !cuda_ok(cudaMemsetAsync(s->grouped_out, 0, (size_t)jobs * H * sizeof(float), st), "zero grouped"))
         return -1;
-    {
+    if (!(flags & SB_EXPERTS_ROUTER_INPUT_READY)) {
         Timed t(s, KC_ROUTER_INPUT, st);
-        if (!cuda_ok(launch_router_input(d_x, l.router_scale, s->rin, B, H, l.eps, 0.0f, s->status, st), "router in"))
-            return -1;
+        GlueArgs g;
+        memset(&g, 0, sizeof g);
+        g.x_in = d_x; g.router_scale = l.router_scale; g.eps_router = l.eps; g.rin = s->rin; g.n = H;
+        g.status = s->status;
+        if (!cuda_ok(launch_glue(g, B, st), "router in")) return -1;
+        count_launches(1);
     }
     {
         Timed t(s, KC_LOGITS, st);
         if (!cuda_ok(launch_router_logits(l.router_w, nullptr, s->rin, s->logits, B, E, H, st), "logits")) return -1;
     }
-    {
+    const bool fused_topk = B <= 8;
+    if (!fused_topk) {
         Timed t(s, KC_TOPK, st);
         if (!cuda_ok(launch_router_topk(s->logits, l.per_expert_scale, s->selected, s->weights, B, E, K, 1,
                                         s->status, st), "topk"))
             return -1;
+        count_launches(1);
     }
     const size_t elems = (size_t)H * M;
     MoePlanArgs a;
     memset(&a, 0, sizeof a);
+    if (fused_topk) {
+        a.logits = s->logits; a.per_expert_scale = l.per_expert_scale;
+        a.selected_out = s->selected; a.weights_out = s->weights;
+    }
     a.selected = s->selected; a.rows = B; a.topk = K; a.n_experts = E;
     a.expert_begin = s->expert_begin; a.expert_end = s->expert_end;
     a.group_offsets = s->group_offsets; a.grouped_to_canonical = s->g2c; a.canonical_to_grouped = s->c2g;
@@ -254,30 +268,34 @@ int salt_b200_layer_experts(void* stack, int layer, const float* d_x, int B, int
         if (!cuda_ok(launch_q4_jobs(s->down_jobs, njobs_max, s->counters, H, tok_hint, M, 1, true, st), "down"))
             return -1;
     }
-    count_launches(6);
+    count_launches(4);
     return 0;
 }
 
-int salt_b200_layer_combine(void* stack, int layer, int B, float* d_y, int apply_norm, void* stream_) {
+// Ordered weighted reduce of grouped_out into d_y; SB_COMBINE_NORM applies the
+// layer's RMSNorm (if it has one) to the result; SB_COMBINE_PREPARE_NEXT also
+// forms the router input of layer + 1 from it, so that layer's
+// salt_b200_layer_experts can be called with SB_EXPERTS_ROUTER_INPUT_READY.
+int salt_b200_layer_combine(void* stack, int layer, int B, float* d_y, int flags, void* stream_) {
     Stack* s = (Stack*)stack;
     cudaStream_t st = (cudaStream_t)stream_;
     if (!s || layer < 0 || layer >= (int)s->layers.size() || !d_y || B < 1 || B > s->max_tokens) return -1;
     const Layer& l = s->layers[(size_t)layer];
-    const bool norm = apply_norm && l.norm_weight;
-    float* reduce_to = norm ? s->reduced : d_y;
+    const bool next = (flags & SB_COMBINE_PREPARE_NEXT) && layer + 1 < (int)s->layers.size();
+    GlueArgs g;
+    memset(&g, 0, sizeof g);
+    g.weights = s->weights; g.c2g = s->c2g; g.grouped = s->grouped_out; g.topk = s->topk; g.jobs = B * s->topk;
+    g.y_out = d_y; g.n = s->hidden; g.status = s->status;
+    if ((flags & SB_COMBINE_NORM) && l.norm_weight) { g.norm_w = l.norm_weight; g.eps_norm = l.eps; }
+    if (next) {
+        const Layer& nl = s->layers[(size_t)layer + 1];
+        g.router_scale = nl.router_scale; g.eps_router = nl.eps; g.rin = s->rin;
+    }
     {
         Timed t(s, KC_REDUCE, st);
-        if (!cuda_ok(launch_weighted_reduce(s->weights, s->c2g, s->grouped_out, reduce_to, B, s->topk, s->hidden,
-                                            s->status, st), "reduce"))
-            return -1;
+        if (!cuda_ok(launch_glue(g, B, st), "combine")) return -1;
     }
     count_launches(1);
-    if (norm) {
-        Timed t(s, KC_NORM, st);
-        if (!cuda_ok(launch_rmsnorm(s->reduced, l.norm_weight, d_y, B, s->hidden, l.eps, 1, s->status, st), "norm"))
-            return -1;
-        count_launches(1);
-    }
     return 0;
 }
 
@@ -289,8 +307,10 @@ int salt_b200_stack_forward_device(void* stack, int first, int count, const floa
     for (int i = 0; i < count; i++) {
         const bool last = i == count - 1;
         float* out = last ? d_y : ((i & 1) ? s->act_b : s->act_a);
-        if (salt_b200_layer_experts(stack, first + i, in, B, 0, stream) != 0 ||
-            salt_b200_layer_combine(stack, first + i, B, out, last ? 0 : 1, stream) != 0)
+        if (salt_b200_layer_experts(stack, first + i, in, B, i > 0 ? SB_EXPERTS_ROUTER_INPUT_READY : 0,
+                                    stream) != 0 ||
+            salt_b200_layer_combine(stack, first + i, B, out,
+                                    last ? 0 : (SB_COMBINE_NORM | SB_COMBINE_PREPARE_NEXT), stream) != 0)
             return -1;
         in = out;
     }

@@ -1,0 +1,307 @@
+// NVFP4 (E2M1 codes, one E4M3FN scale per 16 elements, per-tensor fp32 scalars)
+// kernels, bit-exact against the reference src/nvfp4.c:
+//
+//   nvfp4_qdq_kernel     dynamic group-16 activation quantise -> dequantise
+//                        (salt_nvfp4_quantize_input_reference, nvfp4.c:82-130)
+//   nvfp4_tile_kernel    W4A4 projection on the dequantised activations with the
+//                        canonical 32-accumulator order (nvfp4.c:173-192, 157-171)
+//   nvfp4_generic_kernel any C that is a multiple of 16
+//
+// The encoders are arithmetic instead of the reference's nearest-code searches:
+// "nearest, ties to the even code" over a monotone code table is round-to-
+// nearest-even in that format (checked against the searches in the tests).
+#include "internal.h"
+#include "q4_core.cuh"
+
+namespace sb {
+
+static __device__ __forceinline__ void flag_status(int* status, int bit) {
+    if (status) atomicOr(status, bit);
+}
+
+// E4M3FN decode (nvfp4.c:25-39) for the finite codes.
+__device__ __forceinline__ float e4m3_decode(uint32_t code) {
+    const uint32_t ex = (code >> 3) & 15u, man = code & 7u;
+    float v;
+    if (ex == 0) v = __fmul_rn((float)man, 0.001953125f);
+    else if (ex == 15 && man == 7) v = __int_as_float(0x7fc00000);
+    else v = __uint_as_float(((ex + 120u) << 23) | (man << 20));
+    return (code & 0x80u) ? -v : v;
+}
+
+// E4M3FN encode of a finite value in [0, 448] (nvfp4.c:41-63): nearest code,
+// ties to the even code.
+__device__ __forceinline__ uint32_t e4m3_encode_pos(float v) {
+    if (v < 0.015625f) return (uint32_t)__float2int_rn(__fmul_rn(v, 512.0f));  // subnormal grid 2^-9
+    uint32_t b = __float_as_uint(v);
+    b = (b + 0x7ffffu + ((b >> 20) & 1u)) >> 20;   // round to 3 mantissa bits, ties to even
+    return (((b >> 3) - 120u) << 3) | (b & 7u);
+}
+
+// E2M1 encode of a value already clamped to [-6, 6] (nvfp4.c:65-80): magnitudes
+// {0, .5, 1, 1.5, 2, 3, 4, 6}; on a tie the even code wins.
+__device__ __forceinline__ uint32_t e2m1_encode(float t) {
+    const float m = fabsf(t);
+    uint32_t c = (m > 0.25f) + (m >= 0.75f) + (m > 1.25f) + (m >= 1.75f) + (m > 2.5f) + (m >= 3.5f) + (m > 5.0f);
+    if (__float_as_uint(t) & 0x80000000u) c |= 8u;
+    return c;
+}
+
+// E2M1 decode (nvfp4.c:19-23): both zero codes give +0.
+__device__ __forceinline__ float e2m1_decode(uint32_t code) {
+    const uint32_t e = (code >> 1) & 3u, m = code & 1u;
+    float v = e == 0 ? (m ? 0.5f : 0.0f) : __uint_as_float(((e + 126u) << 23) | (m << 22));
+    if (v == 0.0f) return 0.0f;
+    return (code & 8u) ? -v : v;
+}
+
+// One thread per block of 16 activations.  ig_rows[row] is the row's input
+// global scale.  Non-finite activations set the status word (the reference
+// function returns -1).
+__global__ void __launch_bounds__(256)
+nvfp4_qdq_kernel(const float* __restrict__ x, int rows, int C, const float* __restrict__ ig_rows,
+                 uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, float* __restrict__ dequant,
+                 int* status) {
+    const int bpr = C >> 4;
+    const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= (long long)rows * bpr) return;
+    const int row = (int)(gid / bpr), blk = (int)(gid - (long long)row * bpr);
+    const float ig = ig_rows[row];
+    const float4* in4 = (const float4*)(x + (size_t)row * C + blk * 16);
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float4 t = in4[i];
+        v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
+    }
+    float amax = 0.0f;
+    bool bad = false;
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        const float m = fabsf(v[i]);
+        bad |= !finite_f(m);
+        if (m > amax) amax = m;
+    }
+    if (bad) {
+        flag_status(status, SB_ERR_NONFINITE);
+        return;
+    }
+    float raw = __fmul_rn(ig, __fmul_rn(amax, 0.16666667163372039794921875f));
+    if (raw > 448.0f) raw = 448.0f;
+    const uint32_t sc = e4m3_encode_pos(raw);
+    const float scale = e4m3_decode(sc);
+    const float out_scale = scale == 0.0f ? 0.0f : __fdiv_rn(ig, scale);
+    const float dq_scale = __fdiv_rn(scale, ig);
+    uint32_t lo = 0, hi = 0;
+    float dq[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        float t = __fmul_rn(v[i], out_scale);
+        if (t > 6.0f) t = 6.0f;
+        if (t < -6.0f) t = -6.0f;
+        const uint32_t c = e2m1_encode(t);
+        dq[i] = __fmul_rn(e2m1_decode(c), dq_scale);
+        if (i < 8) lo |= c << (4 * i);
+        else hi |= c << (4 * (i - 8));
+    }
+    scales[(size_t)row * bpr + blk] = (uint8_t)sc;
+    *(uint2*)(packed + (size_t)row * (C >> 1) + blk * 8) = make_uint2(lo, hi);
+    float4* out4 = (float4*)(dequant + (size_t)row * C + blk * 16);
+#pragma unroll
+    for (int i = 0; i < 4; i++) out4[i] = make_float4(dq[4 * i], dq[4 * i + 1], dq[4 * i + 2], dq[4 * i + 3]);
+}
+
+cudaError_t launch_nvfp4_qdq(const float* x, int rows, int C, const float* ig_rows, uint8_t* packed, uint8_t* scales,
+                             float* dequant, int* status, cudaStream_t stream) {
+    if (rows < 1) return cudaSuccess;
+    const long long blocks16 = (long long)rows * (C >> 4);
+    nvfp4_qdq_kernel<<<(unsigned)((blocks16 + 255) / 256), 256, 0, stream>>>(x, rows, C, ig_rows, packed, scales,
+                                                                           dequant, status);
+    return cudaGetLastError();
+}
+
+// Four E2M1 codes of one half-word as floats.
+__device__ __forceinline__ void e2m1x4(uint32_t h, f32x2& w01, f32x2& w23) {
+    w01 = pack2(e2m1_decode(h & 15u), e2m1_decode((h >> 4) & 15u));
+    w23 = pack2(e2m1_decode((h >> 8) & 15u), e2m1_decode((h >> 12) & 15u));
+}
+
+// Tile kernel: 64 threads, 16 weight rows (lane rows r and r+8), eight lanes per
+// row, lane octant u owns accumulators 4u..4u+3 (same mapping as the Q4 kernel).
+// Requires C % 256 == 0 and 16-byte aligned operands.
+template <int TT>
+__global__ void __launch_bounds__(64)
+nvfp4_tile_kernel(const Fp4Job* __restrict__ jobs, int C) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const Fp4Job jb = jobs[blockIdx.y];
+    const int r0 = blockIdx.x * 16;
+    if (r0 >= jb.R || jb.ntok < 1) return;
+    const int tid = threadIdx.x, u = tid & 7, pr = tid >> 3;
+    const int nvalid = min(16, jb.R - r0);
+    const int row_bytes = C >> 1, w_stride = row_bytes + 16;
+    const int sc_row = C >> 4, sc_stride = sc_row + 16;
+    const int steps = C >> 5;
+    int chunk_steps = 8, nch = (steps + 7) / 8;
+    if (nch > 15) {
+        chunk_steps = (((steps + 14) / 15) + 1) & ~1;
+        nch = (steps + chunk_steps - 1) / chunk_steps;
+    }
+    uint8_t* sW = smem;                                 // [16][w_stride]
+    uint8_t* sS = sW + 16 * w_stride;                   // [16][sc_stride]
+    float* sTbl = (float*)(sS + 16 * sc_stride);        // [256] fl(e4m3(code) * wg)
+    float* sX = sTbl + 256;                             // [TT][C]
+
+    auto issue_x = [&](int tb) {
+        const int ppr = C >> 2;
+        for (int p = tid; p < TT * ppr; p += 64) {
+            const int tt = p / ppr, pc = p - tt * ppr;
+            const int tok = min(tb + tt, jb.ntok - 1);
+            cp_async16(sX + tt * C + pc * 4, jb.x + (size_t)tok * jb.x_stride + pc * 4);
+        }
+    };
+    issue_x(0);
+    {
+        const int ppr = sc_row >> 4;
+        for (int p = tid; p < nvalid * ppr; p += 64) {
+            const int rr = p / ppr, pc = p - rr * ppr;
+            cp_async16(sS + rr * sc_stride + pc * 16, jb.scales + (size_t)(r0 + rr) * sc_row + pc * 16);
+        }
+    }
+    for (int ch = 0; ch < nch; ch++) {
+        const int s_begin = ch * chunk_steps;
+        const int cs = min(chunk_steps, steps - s_begin);
+        for (int p = tid; p < 16 * cs; p += 64) {
+            const int rr = p / cs, pc = p - rr * cs;
+            const int grow = min(r0 + rr, jb.R - 1);
+            cp_async16(sW + rr * w_stride + (s_begin + pc) * 16,
+                       jb.codes + (size_t)grow * row_bytes + (s_begin + pc) * 16);
+        }
+        cp_async_commit();
+    }
+    for (int c = tid; c < 256; c += 64) sTbl[c] = __fmul_rn(e4m3_decode((uint32_t)c), jb.wg);
+
+    const uint8_t* wA = sW + pr * w_stride + 2 * u;
+    const uint8_t* wB = sW + (pr + 8) * w_stride + 2 * u;
+    const uint8_t* scA = sS + pr * sc_stride + (u >> 2);
+    const uint8_t* scB = sS + (pr + 8) * sc_stride + (u >> 2);
+    const float* xs = sX + 4 * u;
+
+    for (int tb = 0; tb < jb.ntok; tb += TT) {
+        if (tb > 0) {
+            __syncthreads();
+            issue_x(tb);
+            cp_async_commit();
+            cp_async_wait_dyn(0);
+            __syncthreads();
+        }
+        float accA[TT][4], accB[TT][4];
+#pragma unroll
+        for (int tt = 0; tt < TT; tt++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) { accA[tt][j] = 0.0f; accB[tt][j] = 0.0f; }
+        for (int ch = 0; ch < nch; ch++) {
+            if (tb == 0) {
+                cp_async_wait_dyn(nch - 1 - ch);
+                __syncthreads();
+            }
+            const int s_begin = ch * chunk_steps;
+            const int s_end = min(s_begin + chunk_steps, steps);
+#pragma unroll 2
+            for (int st = s_begin; st < s_end; st++) {
+                const float sa = sTbl[scA[2 * st]], sb_ = sTbl[scB[2 * st]];
+                const uint32_t hA = *(const uint16_t*)(wA + st * 16);
+                const uint32_t hB = *(const uint16_t*)(wB + st * 16);
+                f32x2 a01, a23, b01, b23;
+                e2m1x4(hA, a01, a23);
+                e2m1x4(hB, b01, b23);
+                const f32x2 ssa = pack2(sa, sa), ssb = pack2(sb_, sb_);
+                a01 = mul2(a01, ssa); a23 = mul2(a23, ssa);
+                b01 = mul2(b01, ssb); b23 = mul2(b23, ssb);
+#pragma unroll
+                for (int tt = 0; tt < TT; tt++) {
+                    const ulonglong2 xv = *(const ulonglong2*)(xs + tt * C + st * 32);
+                    float p0, p1, p2, p3;
+                    unpack2(mul2(a01, xv.x), p0, p1);
+                    unpack2(mul2(a23, xv.y), p2, p3);
+                    accA[tt][0] = __fadd_rn(accA[tt][0], p0); accA[tt][1] = __fadd_rn(accA[tt][1], p1);
+                    accA[tt][2] = __fadd_rn(accA[tt][2], p2); accA[tt][3] = __fadd_rn(accA[tt][3], p3);
+                    unpack2(mul2(b01, xv.x), p0, p1);
+                    unpack2(mul2(b23, xv.y), p2, p3);
+                    accB[tt][0] = __fadd_rn(accB[tt][0], p0); accB[tt][1] = __fadd_rn(accB[tt][1], p1);
+                    accB[tt][2] = __fadd_rn(accB[tt][2], p2); accB[tt][3] = __fadd_rn(accB[tt][3], p3);
+                }
+            }
+        }
+#pragma unroll
+        for (int tt = 0; tt < TT; tt++) {
+            const float y0 = fold_row_octants(accA[tt], u);
+            const float y1 = fold_row_octants(accB[tt], u);
+            const int tok = tb + tt;
+            if (u == 7 && tok < jb.ntok) {
+                float* yrow = jb.y + (size_t)tok * jb.y_stride;
+                if (pr < nvalid) yrow[r0 + pr] = y0;
+                if (pr + 8 < nvalid) yrow[r0 + pr + 8] = y1;
+            }
+        }
+    }
+}
+
+// Any C (multiple of 16), any alignment: one warp per (row, token), lane l owns
+// accumulator l.
+__global__ void __launch_bounds__(128) nvfp4_generic_kernel(const Fp4Job* __restrict__ jobs) {
+    const Fp4Job jb = jobs[blockIdx.z];
+    const int r = blockIdx.x * 4 + (threadIdx.x >> 5), tok = blockIdx.y;
+    if (r >= jb.R || tok >= jb.ntok) return;
+    const int lane = threadIdx.x & 31;
+    const float* x = jb.x + (size_t)tok * jb.x_stride;
+    float acc = 0.0f;
+    for (int c = lane; c < jb.C; c += 32) {
+        const size_t k = (size_t)r * jb.C + c;
+        const uint8_t byte = jb.codes[k >> 1];
+        const uint32_t code = (k & 1) ? (byte >> 4) : (byte & 15u);
+        const float sc = __fmul_rn(e4m3_decode(jb.scales[(size_t)r * (jb.C >> 4) + (c >> 4)]), jb.wg);
+        const float w = __fmul_rn(e2m1_decode(code), sc);
+        acc = __fadd_rn(acc, __fmul_rn(w, x[c]));
+    }
+    float L = 0.0f;
+#pragma unroll
+    for (int a = 0; a < 8; a++) L = __fadd_rn(L, __shfl_sync(0xffffffffu, acc, (lane & 3) + 4 * a));
+    const float L2 = __shfl_sync(0xffffffffu, L, 2);
+    const float L1 = __shfl_sync(0xffffffffu, L, 1);
+    const float L3 = __shfl_sync(0xffffffffu, L, 3);
+    if (lane == 0) jb.y[(size_t)tok * jb.y_stride + r] = __fadd_rn(__fadd_rn(L, L2), __fadd_rn(L1, L3));
+}
+
+static size_t fp4_smem(int C, int tt) {
+    return (size_t)16 * (C / 2 + 16) + (size_t)16 * (C / 16 + 16) + 256 * sizeof(float) + (size_t)tt * C * sizeof(float);
+}
+
+template <int TT>
+static cudaError_t launch_fp4_tile(const Fp4Job* jobs, int njobs, int max_rows, int C, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(nvfp4_tile_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             200 * 1024);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    dim3 grid((max_rows + 15) / 16, njobs);
+    nvfp4_tile_kernel<TT><<<grid, 64, fp4_smem(C, TT), stream>>>(jobs, C);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_nvfp4_jobs(const Fp4Job* jobs, int njobs, int max_rows, int max_tok, int C, bool aligned,
+                              cudaStream_t stream) {
+    if (njobs < 1 || max_rows < 1 || max_tok < 1) return cudaSuccess;
+    if (aligned && (C % 256) == 0) {
+        if (max_tok >= 3 && fp4_smem(C, 4) <= 200 * 1024) return launch_fp4_tile<4>(jobs, njobs, max_rows, C, stream);
+        if (max_tok >= 2 && fp4_smem(C, 2) <= 200 * 1024) return launch_fp4_tile<2>(jobs, njobs, max_rows, C, stream);
+        if (fp4_smem(C, 1) <= 200 * 1024) return launch_fp4_tile<1>(jobs, njobs, max_rows, C, stream);
+    }
+    dim3 grid((max_rows + 3) / 4, max_tok, njobs);
+    if (grid.y > 65535 || grid.z > 65535) return cudaErrorInvalidValue;
+    nvfp4_generic_kernel<<<grid, 128, 0, stream>>>(jobs);
+    return cudaGetLastError();
+}
+
+}  // namespace sb

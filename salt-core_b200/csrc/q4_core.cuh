@@ -99,22 +99,43 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
 }
 #endif
 
+// Exponent patterns of 2^23, 2^19, 2^15, 2^11.  They are read from constant
+// memory into registers on purpose: with the pattern in a register and the
+// nibble mask as the immediate, "(h & mask) | pattern" is ONE three-input
+// logic operation; written with two literals the compiler emits two.
+__constant__ uint32_t c_nibble_magic[4] = {0x4b000000u, 0x49000000u, 0x47000000u, 0x45000000u};
+
+struct NibbleMagic {
+    uint32_t m0, m1, m2, m3;
+};
+__device__ __forceinline__ NibbleMagic load_nibble_magic() {
+    NibbleMagic m;
+    m.m0 = c_nibble_magic[0]; m.m1 = c_nibble_magic[1]; m.m2 = c_nibble_magic[2]; m.m3 = c_nibble_magic[3];
+    return m;
+}
+
 // The four nibbles of one packed half-word as exact floats 0..15, as two pairs.
 // Nibble k is masked in place and OR-ed with the exponent of 2^(23-4k), which
 // makes the float equal 2^(23-4k) + q; adding -2^(23-4k) is exact.
-__device__ __forceinline__ void nibbles4(uint32_t h, f32x2& q01, f32x2& q23) {
+__device__ __forceinline__ void nibbles4(uint32_t h, const NibbleMagic& mg, f32x2& q01, f32x2& q23) {
     const f32x2 neg01 = pack2(-8388608.0f, -524288.0f);
     const f32x2 neg23 = pack2(-32768.0f, -2048.0f);
-    q01 = add2(pack2u((h & 0x000fu) | 0x4b000000u, (h & 0x00f0u) | 0x49000000u), neg01);
-    q23 = add2(pack2u((h & 0x0f00u) | 0x47000000u, (h & 0xf000u) | 0x45000000u), neg23);
+    uint32_t f0, f1, f2, f3;
+    asm("lop3.b32 %0, %1, 0x000f, %2, 0xEA;" : "=r"(f0) : "r"(h), "r"(mg.m0));
+    asm("lop3.b32 %0, %1, 0x00f0, %2, 0xEA;" : "=r"(f1) : "r"(h), "r"(mg.m1));
+    asm("lop3.b32 %0, %1, 0x0f00, %2, 0xEA;" : "=r"(f2) : "r"(h), "r"(mg.m2));
+    asm("lop3.b32 %0, %1, 0xf000, %2, 0xEA;" : "=r"(f3) : "r"(h), "r"(mg.m3));
+    q01 = add2(pack2u(f0, f1), neg01);
+    q23 = add2(pack2u(f2, f3), neg23);
 }
 
 // d = fl(fl(q*s) + b) for four elements.  LIT selects the literal two-rounding
 // form (needed only when q*s could overflow).
 template <bool LIT>
-__device__ __forceinline__ void dequant4(uint32_t h, f32x2 ss, f32x2 bb, f32x2& d01, f32x2& d23) {
+__device__ __forceinline__ void dequant4(uint32_t h, const NibbleMagic& mg, f32x2 ss, f32x2 bb, f32x2& d01,
+                                         f32x2& d23) {
     f32x2 q01, q23;
-    nibbles4(h, q01, q23);
+    nibbles4(h, mg, q01, q23);
     if (LIT) {
         // two roundings; scalar adds, because ptxas contracts packed mul + packed add
         float p0, p1, p2, p3, b0, b1;
@@ -131,27 +152,28 @@ __device__ __forceinline__ void dequant4(uint32_t h, f32x2 ss, f32x2 bb, f32x2& 
 
 // Canonical fold of one row whose 32 accumulators live 4 per lane in eight
 // adjacent lanes (octant u = lane & 7; lane holds acc[4u + j], j = 0..3).
-// L_j runs through the octants in order.  The result is valid where u == 7.
-__device__ __forceinline__ float fold_row_octants(f32x2 a01, f32x2 a23, int u) {
-    float a0, a1, a2, a3;
-    unpack2(a01, a0, a1);
-    unpack2(a23, a2, a3);
-    float L0 = 0.0f, L1 = 0.0f, L2 = 0.0f, L3 = 0.0f;
+// Lane u of the octet gathers acc[4s + (u & 3)] from octant s = 0..7 in order and
+// runs the chain L_j = (((0 + acc[j]) + acc[4 + j]) + ...) for j = u & 3 (lanes
+// 4..7 repeat lanes 0..3); the four L values are then combined as
+// (L0 + L2) + (L1 + L3).  The result is valid in every lane of the octet.
+__device__ __forceinline__ float fold_row_octants(const float (&a)[4], int u) {
+    const int j = u & 3;
+    const int base = (threadIdx.x & 31) & ~7;
+    float L = 0.0f;
 #pragma unroll
     for (int s = 0; s < 8; s++) {
-        if (s > 0) {
-            L0 = __shfl_up_sync(0xffffffffu, L0, 1, 8);
-            L1 = __shfl_up_sync(0xffffffffu, L1, 1, 8);
-            L2 = __shfl_up_sync(0xffffffffu, L2, 1, 8);
-            L3 = __shfl_up_sync(0xffffffffu, L3, 1, 8);
-        }
-        if (u == s) {
-            L0 = __fadd_rn(L0, a0);
-            L1 = __fadd_rn(L1, a1);
-            L2 = __fadd_rn(L2, a2);
-            L3 = __fadd_rn(L3, a3);
-        }
+        // every lane offers all four of its accumulators; the reader picks column j of octant s
+        const float v0 = __shfl_sync(0xffffffffu, a[0], base + s);
+        const float v1 = __shfl_sync(0xffffffffu, a[1], base + s);
+        const float v2 = __shfl_sync(0xffffffffu, a[2], base + s);
+        const float v3 = __shfl_sync(0xffffffffu, a[3], base + s);
+        const float v = j == 0 ? v0 : (j == 1 ? v1 : (j == 2 ? v2 : v3));
+        L = __fadd_rn(L, v);
     }
+    const float L0 = __shfl_sync(0xffffffffu, L, base + 0);
+    const float L1 = __shfl_sync(0xffffffffu, L, base + 1);
+    const float L2 = __shfl_sync(0xffffffffu, L, base + 2);
+    const float L3 = __shfl_sync(0xffffffffu, L, base + 3);
     return __fadd_rn(__fadd_rn(L0, L2), __fadd_rn(L1, L3));
 }
 

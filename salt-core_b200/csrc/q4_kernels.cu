@@ -19,7 +19,7 @@ namespace sb {
 
 // Shared-memory geometry of one block (16 weight rows).
 struct TileGeom {
-    int row_bytes, w_stride, sc_row, sc_stride, sc_block, steps, chunk_steps, nch;
+    int row_bytes, w_stride, sc_row, sc_stride, sc_block, steps, chunk_steps, nch, tpitch;
     bool sc_padded;
 };
 
@@ -31,6 +31,9 @@ static __host__ __device__ __forceinline__ TileGeom tile_geom(int C, int rows_a)
     g.sc_padded = (g.sc_row & 15) == 0;
     g.sc_stride = g.sc_padded ? g.sc_row + 16 : g.sc_row;
     g.sc_block = (rows_a * g.sc_stride + 15) & ~15;
+    // words per row of the interleaved scale|bias table: the smallest pitch >= C/64 that is
+    // 8 mod 16, so the four rows a warp reads together start in four different banks
+    g.tpitch = (C >> 6) + ((8 - ((C >> 6) & 15)) & 15);
     g.steps = C >> 5;                // 32-column steps (16 packed bytes per row)
     g.chunk_steps = 8;
     g.nch = (g.steps + 7) / 8;
@@ -41,47 +44,73 @@ static __host__ __device__ __forceinline__ TileGeom tile_geom(int C, int rows_a)
     return g;
 }
 
-// acc = fl(acc + fl(d * x)) on a pair: packed multiply, SCALAR adds.  ptxas
-// contracts mul.rn.f32x2 followed by add.rn.f32x2 (and even fma.rn.f32x2 with a
-// multiplier of 1) into one fused multiply-add, which changes the last bit; the
-// scalar add.rn.f32 is never a contraction candidate, and measured results with
-// it are bit-identical to the reference order.
-__device__ __forceinline__ f32x2 mul_then_add(f32x2 acc, f32x2 d, f32x2 x) {
-    float p0, p1, a0, a1;
+// Why the accumulate is a scalar add: ptxas contracts mul.rn.f32x2 followed by
+// add.rn.f32x2 (and even fma.rn.f32x2 with a multiplier of 1) into one fused
+// multiply-add, which changes the last bit; the scalar add.rn.f32 is never a
+// contraction candidate, and results with it are bit-identical to the reference
+// order.  Accumulators therefore live in scalar registers; products come out of
+// the packed multiply as register pairs, which costs nothing to split.
+__device__ __forceinline__ void mul_then_add(float& a0, float& a1, f32x2 d, f32x2 x) {
+    float p0, p1;
     unpack2(mul2(d, x), p0, p1);
-    unpack2(acc, a0, a1);
-    return pack2(__fadd_rn(a0, p0), __fadd_rn(a1, p1));
+    a0 = __fadd_rn(a0, p0);
+    a1 = __fadd_rn(a1, p1);
 }
 
-// Accumulate steps [s_begin, s_end) (both even) of the thread's two rows for TT tokens.
-template <int TT, bool LIT>
-__device__ __forceinline__ void tile_steps(int s_begin, int s_end, const uint8_t* wA, const uint8_t* wB,
-                                           const uint16_t* sA, const uint16_t* bA, const uint16_t* sB,
-                                           const uint16_t* bB, const float* sX, int x_pitch,
-                                           f32x2 (&accA)[TT][2], f32x2 (&accB)[TT][2]) {
-#pragma unroll 4
-    for (int g = s_begin >> 1; g < (s_end >> 1); g++) {
-        const float fsA = bf16_bits_to_f32(sA[g]), fbA = bf16_bits_to_f32(bA[g]);
-        const float fsB = bf16_bits_to_f32(sB[g]), fbB = bf16_bits_to_f32(bB[g]);
-        const f32x2 ssA = pack2(fsA, fsA), bbA = pack2(fbA, fbA);
-        const f32x2 ssB = pack2(fsB, fsB), bbB = pack2(fbB, fbB);
+// NSTEPS consecutive 32-column steps (NSTEPS even, compile-time) of the thread's
+// two rows for TT tokens.  All operands are pre-offset to the first step, so
+// every shared-memory access below has a compile-time displacement.
+// tA / tB point at the rows' table words: bf16 scale in the high half, bf16
+// bias in the low half of one 32-bit word per quantisation group.
+template <int TT, bool LIT, int NSTEPS>
+__device__ __forceinline__ void tile_steps(const NibbleMagic& mg, const uint8_t* wA, const uint8_t* wB,
+                                           const uint32_t* tA, const uint32_t* tB, const float* const (&xs)[TT],
+                                           float (&accA)[TT][4], float (&accB)[TT][4]) {
+#pragma unroll
+    for (int g = 0; g < NSTEPS / 2; g++) {
+        const uint32_t wa = tA[g], wb = tB[g];
+        const float sa = __uint_as_float(wa & 0xffff0000u), ba = __uint_as_float(wa << 16);
+        const float sb_ = __uint_as_float(wb & 0xffff0000u), bb_ = __uint_as_float(wb << 16);
+        const f32x2 ssA = pack2(sa, sa), bbA = pack2(ba, ba), ssB = pack2(sb_, sb_), bbB = pack2(bb_, bb_);
 #pragma unroll
         for (int half = 0; half < 2; half++) {
-            const int st = 2 * g + half;
-            const uint32_t hA = *(const uint16_t*)(wA + st * 16);
-            const uint32_t hB = *(const uint16_t*)(wB + st * 16);
+            const int k = 2 * g + half;
+            const uint32_t hA = *(const uint16_t*)(wA + k * 16);
+            const uint32_t hB = *(const uint16_t*)(wB + k * 16);
             f32x2 dA01, dA23, dB01, dB23;
-            dequant4<LIT>(hA, ssA, bbA, dA01, dA23);
-            dequant4<LIT>(hB, ssB, bbB, dB01, dB23);
+            dequant4<LIT>(hA, mg, ssA, bbA, dA01, dA23);
+            dequant4<LIT>(hB, mg, ssB, bbB, dB01, dB23);
 #pragma unroll
             for (int tt = 0; tt < TT; tt++) {
-                const ulonglong2 xv = *(const ulonglong2*)(sX + tt * x_pitch + st * 32);
-                accA[tt][0] = mul_then_add(accA[tt][0], dA01, xv.x);
-                accA[tt][1] = mul_then_add(accA[tt][1], dA23, xv.y);
-                accB[tt][0] = mul_then_add(accB[tt][0], dB01, xv.x);
-                accB[tt][1] = mul_then_add(accB[tt][1], dB23, xv.y);
+                const ulonglong2 xv = *(const ulonglong2*)(xs[tt] + k * 32);
+                mul_then_add(accA[tt][0], accA[tt][1], dA01, xv.x);
+                mul_then_add(accA[tt][2], accA[tt][3], dA23, xv.y);
+                mul_then_add(accB[tt][0], accB[tt][1], dB01, xv.x);
+                mul_then_add(accB[tt][2], accB[tt][3], dB23, xv.y);
             }
         }
+    }
+}
+
+// A run of steps [s_begin, s_end): whole 8-step blocks, then 2-step blocks.
+template <int TT, bool LIT>
+__device__ __forceinline__ void tile_run(const NibbleMagic& mg, int s_begin, int s_end, const uint8_t* wA,
+                                         const uint8_t* wB, const uint32_t* tA, const uint32_t* tB,
+                                         const float* sX, int x_pitch,
+                                         float (&accA)[TT][4], float (&accB)[TT][4]) {
+    int st = s_begin;
+    constexpr int BLK = 8;
+    for (; st + BLK <= s_end; st += BLK) {
+        const float* xs[TT];
+#pragma unroll
+        for (int tt = 0; tt < TT; tt++) xs[tt] = sX + tt * x_pitch + st * 32;
+        tile_steps<TT, LIT, BLK>(mg, wA + st * 16, wB + st * 16, tA + (st >> 1), tB + (st >> 1), xs, accA, accB);
+    }
+    for (; st + 2 <= s_end; st += 2) {
+        const float* xs[TT];
+#pragma unroll
+        for (int tt = 0; tt < TT; tt++) xs[tt] = sX + tt * x_pitch + st * 32;
+        tile_steps<TT, LIT, 2>(mg, wA + st * 16, wB + st * 16, tA + (st >> 1), tB + (st >> 1), xs, accA, accB);
     }
 }
 
@@ -105,16 +134,19 @@ q4_tile_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_dev
     uint8_t* sW = smem;                                   // [16][w_stride]
     uint8_t* sS = sW + 16 * G.w_stride;                   // [NMAT][sc_block]
     uint8_t* sBi = sS + NMAT * G.sc_block;                // [NMAT][sc_block]
-    float* sX = (float*)(sBi + NMAT * G.sc_block);        // [TT][C]
+    uint32_t* sT = (uint32_t*)(sBi + NMAT * G.sc_block);  // [16][tpitch] (scale bf16 << 16) | bias bf16
+    const int tpitch = G.tpitch;
+    float* sX = (float*)(sT + 16 * tpitch);               // [TT][C]
 
     // ---- group 0: activations of the first token block, scales, biases, K chunk 0 ----
     auto issue_x = [&](int tb) {
         const int ppr = C >> 2;                  // 16-byte pieces per activation row
-        for (int p = tid; p < TT * ppr; p += 64) {
-            const int tt = p / ppr, pc = p - tt * ppr;
+#pragma unroll
+        for (int tt = 0; tt < TT; tt++) {
             const int tok = min(tb + tt, jb.ntok - 1);
             const int row = jb.x_rows ? (jb.x_rows[tok] / jb.x_div) : tok;
-            cp_async16(sX + tt * C + pc * 4, jb.x + (size_t)row * jb.x_stride + pc * 4);
+            const float* src = jb.x + (size_t)row * jb.x_stride;
+            for (int pc = tid; pc < ppr; pc += 64) cp_async16(sX + tt * C + pc * 4, src + pc * 4);
         }
     };
     issue_x(0);
@@ -147,11 +179,34 @@ q4_tile_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_dev
         if (!gb)
             for (int i = tid; i < (G.sc_block >> 2); i += 64) ((uint32_t*)db)[i] = 0u;
     }
+    if (G.chunk_steps == 8) {
+        // 8-step chunks: a chunk is 16 rows x 8 pieces of 16 bytes = 128 copies, two per
+        // thread, and the thread's (row, piece) pair is the same in every chunk
+        const int pc = tid & 7, rrA = tid >> 3, rrB = rrA + 8;
+        const int mA = (NMAT == 2) ? 0 : 0, mB = (NMAT == 2) ? 1 : 0;
+        const int growA = min(r0 + ((NMAT == 2) ? rrA : rrA), jb.R - 1);
+        const int growB = min(r0 + ((NMAT == 2) ? (rrB & 7) : rrB), jb.R - 1);
+        const uint8_t* gA = (mA == 0 ? jb.vals : jb.vals2) + (size_t)growA * G.row_bytes + pc * 16;
+        const uint8_t* gB = (mB == 0 ? jb.vals : jb.vals2) + (size_t)growB * G.row_bytes + pc * 16;
+        uint8_t* dA = sW + rrA * G.w_stride + pc * 16;
+        uint8_t* dB = sW + rrB * G.w_stride + pc * 16;
+        const int valid_pieces = G.steps;        // pieces per row
+        for (int ch = 0; ch < G.nch; ch++) {
+            if (ch * 8 + pc < valid_pieces) {
+#ifndef SB_EXP_NOLOAD
+                cp_async16(dA + ch * 128, gA + ch * 128);
+                cp_async16(dB + ch * 128, gB + ch * 128);
+#endif
+            }
+            cp_async_commit();
+        }
+    } else
     for (int ch = 0; ch < G.nch; ch++) {
         const int s_begin = ch * G.chunk_steps;
         const int cs = min(G.chunk_steps, G.steps - s_begin);
         for (int p = tid; p < 16 * cs; p += 64) {
-            const int rr = p / cs, pc = p - rr * cs;
+            const int rr = p / cs;
+            const int pc = p - rr * cs;
             const int m = (NMAT == 2) ? (rr >> 3) : 0;
             int grow = r0 + ((NMAT == 2) ? (rr & 7) : rr);
             grow = min(grow, jb.R - 1);
@@ -164,28 +219,26 @@ q4_tile_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_dev
     // ---- this thread's operands ----
     const uint8_t* wA = sW + pr * G.w_stride + 2 * u;
     const uint8_t* wB = sW + (pr + 8) * G.w_stride + 2 * u;
-    const int scB_block = (NMAT == 2) ? G.sc_block : 0;
-    const int scB_row = (NMAT == 2) ? pr : pr + 8;
-    const uint16_t* sA = (const uint16_t*)(sS + pr * G.sc_stride);
-    const uint16_t* bA = (const uint16_t*)(sBi + pr * G.sc_stride);
-    const uint16_t* sB = (const uint16_t*)(sS + scB_block + scB_row * G.sc_stride);
-    const uint16_t* bB = (const uint16_t*)(sBi + scB_block + scB_row * G.sc_stride);
+    const int gpr = C >> 6;                      // quantisation groups per row
+    const uint32_t* tA = sT + pr * tpitch;
+    const uint32_t* tB = sT + (pr + 8) * tpitch;
+    const NibbleMagic mg = load_nibble_magic();
     const float* xs = sX + 4 * u;
 
-    // wait for group 0, then decide whether any scale of the block needs the
-    // literal (two-rounding) dequantisation
+    // wait for group 0, interleave the bf16 scales/biases of the 16 rows into one
+    // word per group, and note whether any scale needs the literal
+    // (two-rounding) dequantisation
     cp_async_wait_dyn(G.nch - 1);
     __syncthreads();
     int lit = 0;
-    {
-        const int rows_here = (NMAT == 2) ? 8 : 16;
-        const int gpr = C >> 6;                  // groups per row
-        for (int i = tid; i < NMAT * rows_here * gpr; i += 64) {
-            const int m = i / (rows_here * gpr), rem = i - m * rows_here * gpr;
-            const int rr = rem / gpr, gg = rem - rr * gpr;
-            if (rr < nvalid)
-                lit |= scale_needs_literal(((const uint16_t*)(sS + m * G.sc_block + rr * G.sc_stride))[gg]) ? 1 : 0;
-        }
+    for (int gg = tid & 3; gg < gpr; gg += 4) {
+        const int rr = tid >> 2;                 // 64 threads = 16 rows x 4 column phases
+        const int m = (NMAT == 2) ? (rr >> 3) : 0;
+        const int lr = (NMAT == 2) ? (rr & 7) : rr;
+        const uint32_t hs = ((const uint16_t*)(sS + m * G.sc_block + lr * G.sc_stride))[gg];
+        const uint32_t hb = ((const uint16_t*)(sBi + m * G.sc_block + lr * G.sc_stride))[gg];
+        sT[rr * tpitch + gg] = (hs << 16) | hb;
+        if (lr < nvalid) lit |= scale_needs_literal(hs) ? 1 : 0;
     }
     lit = __syncthreads_or(lit);
 
@@ -197,11 +250,11 @@ q4_tile_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_dev
             cp_async_wait_dyn(0);
             __syncthreads();
         }
-        f32x2 accA[TT][2], accB[TT][2];
+        float accA[TT][4], accB[TT][4];
 #pragma unroll
-        for (int tt = 0; tt < TT; tt++) {
-            accA[tt][0] = accA[tt][1] = accB[tt][0] = accB[tt][1] = pack2(0.0f, 0.0f);
-        }
+        for (int tt = 0; tt < TT; tt++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) { accA[tt][j] = 0.0f; accB[tt][j] = 0.0f; }
         for (int ch = 0; ch < G.nch; ch++) {
             if (tb == 0 && ch > 0) {
                 cp_async_wait_dyn(G.nch - 1 - ch);
@@ -209,13 +262,17 @@ q4_tile_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_dev
             }
             const int s_begin = ch * G.chunk_steps;
             const int s_end = min(s_begin + G.chunk_steps, G.steps);
-            if (lit) tile_steps<TT, true>(s_begin, s_end, wA, wB, sA, bA, sB, bB, xs, C, accA, accB);
-            else tile_steps<TT, false>(s_begin, s_end, wA, wB, sA, bA, sB, bB, xs, C, accA, accB);
+#ifndef SB_EXP_NOCOMPUTE
+            if (lit) tile_run<TT, true>(mg, s_begin, s_end, wA, wB, tA, tB, xs, C, accA, accB);
+            else tile_run<TT, false>(mg, s_begin, s_end, wA, wB, tA, tB, xs, C, accA, accB);
+#else
+            accA[0][0] += *(const float*)(wA + s_begin * 16) + (float)lit;
+#endif
         }
 #pragma unroll
         for (int tt = 0; tt < TT; tt++) {
-            const float y0 = fold_row_octants(accA[tt][0], accA[tt][1], u);
-            const float y1 = fold_row_octants(accB[tt][0], accB[tt][1], u);
+            const float y0 = fold_row_octants(accA[tt], u);
+            const float y1 = fold_row_octants(accB[tt], u);
             const int tok = tb + tt;
             if (u == 7 && tok < jb.ntok) {
                 float* yrow = jb.y + (size_t)tok * jb.y_stride;
@@ -279,7 +336,8 @@ q4_generic_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_
 
 static size_t tile_smem_bytes(int C, int nmat, int tt) {
     const TileGeom g = tile_geom(C, nmat == 2 ? 8 : 16);
-    return (size_t)16 * g.w_stride + (size_t)2 * nmat * g.sc_block + (size_t)tt * C * sizeof(float);
+    return (size_t)16 * g.w_stride + (size_t)2 * nmat * g.sc_block + (size_t)16 * g.tpitch * 4 +
+           (size_t)tt * C * sizeof(float);
 }
 
 bool q4_tile_supported(int C) { return C >= 64 && (C % 64) == 0 && tile_smem_bytes(C, 2, 4) <= 200 * 1024; }

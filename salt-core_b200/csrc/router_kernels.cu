@@ -82,6 +82,112 @@ norm_rows_kernel(const float* __restrict__ x, const float* __restrict__ weight, 
     if (bad) flag(status, SB_ERR_NONFINITE);
 }
 
+// Token-wise glue between the expert phase of one layer and the router of the
+// next, in one launch per row:
+//   [reduce]  v = ordered weighted sum of the row's grouped expert outputs
+//             (src/tensorops.c:291-325), else v = x_in
+//   [norm]    v = RMSNorm(v) * norm_w                      (gemma4.c:85-101)
+//             y_out = v  (written whenever reduce or norm ran)
+//   [router]  rin = ((v * inv) * scale) * (1/sqrt(n))      (gemma4.c:103-130)
+// The two sums of squares are serial chains run by one thread over squares
+// formed in parallel.
+__global__ void __launch_bounds__(1024) glue_rows_kernel(GlueArgs a) {
+    extern __shared__ __align__(16) float gsm[];
+    const int n = a.n;
+    float* v = gsm;                        // [n]
+    float* sq = gsm + ((n + 3) & ~3);      // [n]
+    __shared__ float s_inv, s_root;
+    const int row = blockIdx.x;
+    bool bad = false;
+    if (a.grouped != nullptr) {
+        // rank -> (grouped row, weight) once per block; invalid ranks are dropped and flagged
+        __shared__ int s_g[64];
+        __shared__ float s_w[64];
+        if (threadIdx.x < a.topk) {
+            const int canonical = row * a.topk + threadIdx.x;
+            int g = a.c2g[canonical];
+            const float w = a.weights[canonical];
+            if (g < 0 || g >= a.jobs || !finite_f(w)) {
+                flag(a.status, g < 0 || g >= a.jobs ? SB_ERR_INDEX : SB_ERR_NONFINITE);
+                g = -1;
+            }
+            s_g[threadIdx.x] = g;
+            s_w[threadIdx.x] = w;
+        }
+        __syncthreads();
+        for (int d = threadIdx.x; d < n; d += blockDim.x) {
+            float acc = 0.0f;
+            for (int r0 = 0; r0 < a.topk; r0 += 8) {
+                float o[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int g = r0 + i < a.topk ? s_g[r0 + i] : -1;
+                    o[i] = g >= 0 ? __ldg(a.grouped + (size_t)g * n + d) : 0.0f;
+                }
+#pragma unroll
+                for (int i = 0; i < 8; i++)
+                    if (r0 + i < a.topk && s_g[r0 + i] >= 0) acc = __fadd_rn(acc, __fmul_rn(s_w[r0 + i], o[i]));
+            }
+            v[d] = acc;
+        }
+    } else {
+        for (int d = threadIdx.x; d < n; d += blockDim.x) v[d] = a.x_in[(size_t)row * n + d];
+    }
+    __syncthreads();
+    if (a.norm_w != nullptr) {
+        for (int d = threadIdx.x; d < n; d += blockDim.x) {
+            const float t = v[d];
+            sq[d] = __fmul_rn(t, t);
+            bad |= !finite_f(t) || !finite_f(a.norm_w[d]);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const float ss = serial_sum(sq, n);
+            s_inv = pow_neg_half(__fadd_rn(__fdiv_rn(ss, (float)n), a.eps_norm));
+            if (!finite_f(s_inv)) flag(a.status, SB_ERR_NONFINITE);
+        }
+        __syncthreads();
+        const float inv = s_inv;
+        for (int d = threadIdx.x; d < n; d += blockDim.x) {
+            const float t = __fmul_rn(__fmul_rn(v[d], inv), a.norm_w[d]);
+            bad |= !finite_f(t);
+            v[d] = t;
+        }
+        __syncthreads();
+    }
+    if (a.y_out != nullptr)
+        for (int d = threadIdx.x; d < n; d += blockDim.x) a.y_out[(size_t)row * n + d] = v[d];
+    if (a.router_scale != nullptr) {
+        for (int d = threadIdx.x; d < n; d += blockDim.x) {
+            const float t = v[d];
+            sq[d] = __fmul_rn(t, t);
+            bad |= !finite_f(t) || !finite_f(a.router_scale[d]);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const float ss = serial_sum(sq, n);
+            s_inv = pow_neg_half(__fadd_rn(__fdiv_rn(ss, (float)n), a.eps_router));
+            s_root = __fdiv_rn(1.0f, sqrtf_exact((float)n));
+            if (!finite_f(s_inv) || !finite_f(s_root)) flag(a.status, SB_ERR_NONFINITE);
+        }
+        __syncthreads();
+        const float inv = s_inv, root = s_root;
+        for (int d = threadIdx.x; d < n; d += blockDim.x) {
+            const float t = __fmul_rn(__fmul_rn(__fmul_rn(v[d], inv), a.router_scale[d]), root);
+            bad |= !finite_f(t);
+            a.rin[(size_t)row * n + d] = t;
+        }
+    }
+    if (bad) flag(a.status, SB_ERR_NONFINITE);
+}
+
+cudaError_t launch_glue(const GlueArgs& a, int rows, cudaStream_t stream) {
+    if (rows < 1) return cudaSuccess;
+    if (a.topk > 64) return cudaErrorInvalidValue;
+    glue_rows_kernel<<<rows, rows <= 16 ? 1024 : 256, (size_t)(2 * a.n + 8) * sizeof(float), stream>>>(a);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_rmsnorm(const float* x, const float* weight, float* y, int rows, int n, float eps, int with_scale,
                            int* status, cudaStream_t stream) {
     if (rows < 1) return cudaSuccess;
@@ -103,7 +209,7 @@ cudaError_t launch_router_input(const float* x, const float* scale, float* out, 
 // acc = fl(acc + p[c]) over them (src/kernels.c:98-106).
 constexpr int LOGIT_TB = 8;
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 router_logits_block_kernel(const float* __restrict__ W, const float* __restrict__ bias,
                            const float* __restrict__ x, float* __restrict__ logits, int rows, int E, int H) {
     extern __shared__ __align__(16) float sprod[];       // [nr][pitch]
@@ -112,9 +218,46 @@ router_logits_block_kernel(const float* __restrict__ W, const float* __restrict_
     const int nr = min(LOGIT_TB, rows - r0);
     const int pitch = ((H + 3) & ~3) + 4;                // +4 floats: rows start in different banks
     const float* w = W + (size_t)e * H;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) {
-        const float wv = __ldg(w + c);
-        for (int r = 0; r < nr; r++) sprod[r * pitch + c] = __fmul_rn(wv, __ldg(x + (size_t)(r0 + r) * H + c));
+    if ((H & 3) == 0) {
+        // 16-byte loads; the (up to 4) W quads of a thread are all in flight before the first product
+        const int nq = H >> 2;
+        float4 wq[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int q = threadIdx.x + i * 256;
+            wq[i] = q < nq ? __ldg((const float4*)w + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        for (int q0 = 0; q0 < nq; q0 += 1024) {
+            if (q0 > 0) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int q = q0 + threadIdx.x + i * 256;
+                    wq[i] = q < nq ? __ldg((const float4*)w + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+            for (int r = 0; r < nr; r++) {
+                const float4* xr = (const float4*)(x + (size_t)(r0 + r) * H);
+                float4 xq[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int q = q0 + threadIdx.x + i * 256;
+                    xq[i] = q < nq ? __ldg(xr + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int q = q0 + threadIdx.x + i * 256;
+                    if (q < nq)
+                        *(float4*)(sprod + r * pitch + 4 * q) =
+                            make_float4(__fmul_rn(wq[i].x, xq[i].x), __fmul_rn(wq[i].y, xq[i].y),
+                                        __fmul_rn(wq[i].z, xq[i].z), __fmul_rn(wq[i].w, xq[i].w));
+                }
+            }
+        }
+    } else {
+        for (int c = threadIdx.x; c < H; c += blockDim.x) {
+            const float wv = __ldg(w + c);
+            for (int r = 0; r < nr; r++) sprod[r * pitch + c] = __fmul_rn(wv, __ldg(x + (size_t)(r0 + r) * H + c));
+        }
     }
     __syncthreads();
     if (threadIdx.x < nr) {
@@ -168,7 +311,7 @@ cudaError_t launch_router_logits(const float* W, const float* bias, const float*
         }
         if (smem > 200 * 1024) return cudaErrorInvalidValue;
         dim3 grid(E, (rows + LOGIT_TB - 1) / LOGIT_TB);
-        router_logits_block_kernel<<<grid, 128, smem, stream>>>(W, bias, x, logits, rows, E, H);
+        router_logits_block_kernel<<<grid, 256, smem, stream>>>(W, bias, x, logits, rows, E, H);
     } else {
         dim3 grid((E + 31) / 32, (rows + 7) / 8);
         router_logits_tile_kernel<<<grid, 256, 0, stream>>>(W, bias, x, logits, rows, E, H);
@@ -180,83 +323,102 @@ cudaError_t launch_router_logits(const float* W, const float* bias, const float*
 // pairs (gemma4_text.c:8541-8550).  The insertion top-k with strict '>' equals
 // ranking by (logit descending, expert ascending); the softmax denominator and
 // the renormalisation sum are serial chains in expert / rank order.
-__global__ void __launch_bounds__(256)
-router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ per_expert_scale,
-                   int32_t* __restrict__ selected, float* __restrict__ weights, int E, int topk, int sort_by_expert,
-                   int* status) {
-    extern __shared__ float sm[];
+//
+// Executed by a group of `gsize` consecutive threads (ltid = index in group) on
+// one row; every thread of the block must call it (block-wide barriers inside),
+// groups without a row pass active = false.  sm = this group's scratch of
+// 2E + 2*topk floats (16-byte aligned), sc = 4 floats of per-group scalars.
+static __device__ __forceinline__ void topk_group(bool active, const float* lr, const float* per_expert_scale,
+                                                  int32_t* sel_out, float* w_out, int E, int topk,
+                                                  int sort_by_expert, int* status, float* sm, float* sc,
+                                                  int ltid, int gsize) {
     float* sl = sm;                  // [E] logits
     float* se = sm + E;              // [E] exp(l - max)
     int* ssel = (int*)(sm + 2 * E);  // [topk]
     float* sw = sm + 2 * E + topk;   // [topk]
-    __shared__ float s_max, s_all, s_selsum;
-    __shared__ int s_bad;
-    const float* lr = logits + (size_t)blockIdx.x * E;
-    if (threadIdx.x == 0) s_bad = 0;
+    int* s_bad = (int*)(sc + 3);
+    if (ltid == 0) *s_bad = 0;
     __syncthreads();
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
-        const float v = lr[e];
-        sl[e] = v;
-        if (!finite_f(v) || (per_expert_scale && !finite_f(per_expert_scale[e]))) s_bad = 1;
-    }
+    if (active)
+        for (int e = ltid; e < E; e += gsize) {
+            const float v = lr[e];
+            sl[e] = v;
+            if (!finite_f(v) || (per_expert_scale && !finite_f(per_expert_scale[e]))) *s_bad = 1;
+        }
     __syncthreads();
-    if (s_bad) {  // the reference rejects non-finite logits before ranking (gemma4.c:149-152)
-        if (threadIdx.x == 0) flag(status, SB_ERR_NONFINITE);
-        return;
-    }
-    if (threadIdx.x < 32) {
+    // the reference rejects non-finite logits before ranking (gemma4.c:149-152)
+    const bool go = active && !*s_bad;
+    if (go && ltid < 32) {
         float m = __int_as_float(0xff800000);
-        for (int e = threadIdx.x; e < E; e += 32) m = fmaxf(m, sl[e]);
+        for (int e = ltid; e < E; e += 32) m = fmaxf(m, sl[e]);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        if (threadIdx.x == 0) s_max = m;
+        if (ltid == 0) sc[0] = m;
     }
     __syncthreads();
-    const float mx = s_max;
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
-        const float v = sl[e];
-        se[e] = expf_exact(__fsub_rn(v, mx));
-        int rank = 0;
-        for (int o = 0; o < E; o++) {
-            const float u = sl[o];
-            rank += (u > v || (u == v && o < e)) ? 1 : 0;
+    if (go) {
+        const float mx = sc[0];
+        for (int e = ltid; e < E; e += gsize) {
+            const float v = sl[e];
+            se[e] = expf_exact(__fsub_rn(v, mx));
+            int rank = 0;
+            for (int o = 0; o < E; o++) {
+                const float u = sl[o];
+                rank += (u > v || (u == v && o < e)) ? 1 : 0;
+            }
+            if (rank < topk) ssel[rank] = e;
         }
-        if (rank < topk) ssel[rank] = e;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (go && ltid == 0) {
         const float all = serial_sum(se, E);
-        s_all = all;
-        if (!(all > 0.0f) || !finite_f(all)) s_bad = 1;
+        int bad = (!(all > 0.0f) || !finite_f(all)) ? 1 : 0;
         float selsum = 0.0f;
         for (int j = 0; j < topk; j++) {
             const float w = __fdiv_rn(se[ssel[j]], all);
             sw[j] = w;
             selsum = __fadd_rn(selsum, w);
         }
-        s_selsum = selsum;
-        if (!(selsum > 0.0f) || !finite_f(selsum)) s_bad = 1;
+        sc[1] = selsum;
+        if (!(selsum > 0.0f) || !finite_f(selsum)) bad = 1;
+        if (bad) *s_bad = 1;
     }
     __syncthreads();
-    for (int j = threadIdx.x; j < topk; j += blockDim.x) {
-        const int e = ssel[j];
-        const float nrm = __fdiv_rn(sw[j], s_selsum);
-        const float w = __fmul_rn(nrm, per_expert_scale ? per_expert_scale[e] : 1.0f);
-        int pos = j;
-        if (sort_by_expert) {
-            pos = 0;
-            for (int i = 0; i < topk; i++) pos += (ssel[i] < e) ? 1 : 0;
+    if (go)
+        for (int j = ltid; j < topk; j += gsize) {
+            const int e = ssel[j];
+            const float nrm = __fdiv_rn(sw[j], sc[1]);
+            const float w = __fmul_rn(nrm, per_expert_scale ? per_expert_scale[e] : 1.0f);
+            int pos = j;
+            if (sort_by_expert) {
+                pos = 0;
+                for (int i = 0; i < topk; i++) pos += (ssel[i] < e) ? 1 : 0;
+            }
+            sel_out[pos] = e;
+            w_out[pos] = w;
         }
-        selected[(size_t)blockIdx.x * topk + pos] = e;
-        weights[(size_t)blockIdx.x * topk + pos] = w;
-    }
-    if (threadIdx.x == 0 && s_bad) flag(status, SB_ERR_NONFINITE);
+    if (active && ltid == 0 && *s_bad) flag(status, SB_ERR_NONFINITE);
+}
+
+static __host__ __device__ __forceinline__ int topk_scratch_floats(int E, int topk) {
+    return ((2 * E + 2 * topk + 3) & ~3) + 4;
+}
+
+__global__ void __launch_bounds__(128)
+router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ per_expert_scale,
+                   int32_t* __restrict__ selected, float* __restrict__ weights, int E, int topk, int sort_by_expert,
+                   int* status) {
+    extern __shared__ __align__(16) float tk_sm[];
+    float* sc = tk_sm + topk_scratch_floats(E, topk) - 4;
+    topk_group(true, logits + (size_t)blockIdx.x * E, per_expert_scale, selected + (size_t)blockIdx.x * topk,
+               weights + (size_t)blockIdx.x * topk, E, topk, sort_by_expert, status, tk_sm, sc, threadIdx.x,
+               blockDim.x);
 }
 
 cudaError_t launch_router_topk(const float* logits, const float* per_expert_scale, int32_t* selected, float* weights,
                                int rows, int E, int topk, int sort_by_expert, int* status, cudaStream_t stream) {
     if (rows < 1) return cudaSuccess;
-    size_t smem = (size_t)(2 * E + 2 * topk) * sizeof(float);
+    size_t smem = (size_t)topk_scratch_floats(E, topk) * sizeof(float);
     router_topk_kernel<<<rows, 128, smem, stream>>>(logits, per_expert_scale, selected, weights, E, topk,
                                                     sort_by_expert, status);
     return cudaGetLastError();
@@ -272,8 +434,20 @@ cudaError_t launch_router_topk(const float* logits, const float* per_expert_scal
 // step with match_any.  Experts outside [expert_begin, expert_end) keep their
 // slots in the global order but get no job descriptor.
 __global__ void __launch_bounds__(1024) moe_plan_kernel(MoePlanArgs a) {
-    extern __shared__ int sp[];
+    extern __shared__ __align__(16) int sp[];
     const int E = a.n_experts;
+    if (a.logits != nullptr) {
+        // fused router top-k for small batches: 128 threads per row, up to 8 rows
+        float* tk = (float*)(sp + (34 * E + 4));
+        const int grp = threadIdx.x >> 7, ltid = threadIdx.x & 127;
+        const int per = topk_scratch_floats(E, a.topk);
+        float* mine = tk + grp * per;
+        const bool active = grp < a.rows;
+        const int row = active ? grp : 0;
+        topk_group(active, a.logits + (size_t)row * E, a.per_expert_scale, a.selected_out + (size_t)row * a.topk,
+                   a.weights_out + (size_t)row * a.topk, E, a.topk, 1, a.status, mine, mine + per - 4, ltid, 128);
+        __syncthreads();   // selections written by this block are read back below
+    }
     int* hist = sp;               // [32][E]
     int* offs = sp + 32 * E;      // [E+1]
     int* act = offs + (E + 1);    // [E] active prefix
@@ -385,7 +559,11 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(MoePlanArgs a) {
 }
 
 cudaError_t launch_moe_plan(const MoePlanArgs& a, cudaStream_t stream) {
-    size_t smem = (size_t)(32 * a.n_experts + 2 * a.n_experts + 1) * sizeof(int);
+    size_t smem = (size_t)(34 * a.n_experts + 4) * sizeof(int);
+    if (a.logits != nullptr) {
+        if (a.rows > 8) return cudaErrorInvalidValue;
+        smem += (size_t)8 * topk_scratch_floats(a.n_experts, a.topk) * sizeof(float);
+    }
     static bool configured = false;
     if (smem > 48 * 1024 && !configured) {
         cudaError_t e = cudaFuncSetAttribute(moe_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);

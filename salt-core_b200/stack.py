@@ -78,16 +78,19 @@ class MoeStack:
         return self.lib.salt_b200_stack_forward_device(self.handle, first, count, C.c_void_p(d_x), B,
                                                        C.c_void_p(d_y), C.c_void_p(stream))
 
-    def layer_experts(self, layer, d_x, B, zero_remote=False, stream=0):
-        return self.lib.salt_b200_layer_experts(self.handle, layer, C.c_void_p(d_x), B, int(zero_remote),
-                                                C.c_void_p(stream))
+    EXPERTS_ZERO_REMOTE, EXPERTS_ROUTER_INPUT_READY = 1, 2
+    COMBINE_NORM, COMBINE_PREPARE_NEXT = 1, 2
 
-    def layer_combine(self, layer, B, d_y, apply_norm=True, stream=0):
-        return self.lib.salt_b200_layer_combine(self.handle, layer, B, C.c_void_p(d_y), int(apply_norm),
-                                                C.c_void_p(stream))
+    def layer_experts(self, layer, d_x, B, zero_remote=False, router_input_ready=False, stream=0):
+        flags = (1 if zero_remote else 0) | (2 if router_input_ready else 0)
+        return self.lib.salt_b200_layer_experts(self.handle, layer, C.c_void_p(d_x), B, flags, C.c_void_p(stream))
 
-    KERNEL_CLASSES = ("router_input", "router_logits", "router_topk", "plan", "gate_up_geglu", "down",
-                      "weighted_reduce", "rmsnorm")
+    def layer_combine(self, layer, B, d_y, apply_norm=True, prepare_next=False, stream=0):
+        flags = (1 if apply_norm else 0) | (2 if prepare_next else 0)
+        return self.lib.salt_b200_layer_combine(self.handle, layer, B, C.c_void_p(d_y), flags, C.c_void_p(stream))
+
+    KERNEL_CLASSES = ("router_input", "router_logits", "router_topk", "plan_topk", "gate_up_geglu", "down",
+                      "reduce_norm_router_input", "rmsnorm")
 
     def graph_capture(self, d_x, B, d_y, stream, first=0, count=None):
         count = self.n_layers - first if count is None else count

@@ -136,3 +136,50 @@ def make_q4_moe_layer_bulk(seed: int, hidden=2816, inter=704, n_experts=128, top
         per_expert_scale=np.ones(n_experts, np.float32),
         pool=pool, expert_stride=stride,
         norm_weight=(1.0 + 0.1 * rng.standard_normal(hidden)).astype(np.float32))
+
+
+# ---- NVFP4 (E2M1 codes, E4M3FN block scales, per-tensor fp32 scalars) -----------
+E2M1_MAG = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], np.float32)
+
+
+def e4m3fn_encode(v: np.ndarray) -> np.ndarray:
+    """Non-negative fp32 -> E4M3FN code, round to nearest, ties to the even code,
+    saturating at 448 (the arithmetic equivalent of reference src/nvfp4.c:41-63)."""
+    v = np.minimum(np.asarray(v, np.float32), np.float32(448.0))
+    sub = np.rint(v * np.float32(512.0)).astype(np.uint32)
+    b = v.view(np.uint32).astype(np.uint64)
+    b = (b + 0x7FFFF + ((b >> 20) & 1)) >> 20
+    norm = ((((b >> 3) - 120) << 3) | (b & 7)).astype(np.uint32)
+    return np.where(v < np.float32(2.0 ** -6), sub, norm).astype(np.uint8)
+
+
+def e4m3fn_decode(code: np.ndarray) -> np.ndarray:
+    code = np.asarray(code, np.uint8).astype(np.uint32)
+    ex, man = (code >> 3) & 15, code & 7
+    sub = man.astype(np.float32) * np.float32(2.0 ** -9)
+    norm = (((ex + 120) << 23) | (man << 20)).astype(np.uint32).view(np.float32)
+    return np.where(ex == 0, sub, norm).astype(np.float32)
+
+
+def e2m1_encode(t: np.ndarray) -> np.ndarray:
+    """fp32 in [-6, 6] -> E2M1 code, nearest with ties to the even code (nvfp4.c:65-80)."""
+    m = np.abs(t)
+    c = ((m > 0.25).astype(np.uint8) + (m >= 0.75) + (m > 1.25) + (m >= 1.75) + (m > 2.5) + (m >= 3.5) + (m > 5.0))
+    return (c | (np.signbit(t).astype(np.uint8) << 3)).astype(np.uint8)
+
+
+def make_nvfp4(rng: np.random.Generator, R: int, C: int, std=0.02):
+    """Quantise an N(0, std) matrix to NVFP4.  Returns (packed uint8 [R][C/2],
+    scales uint8 [R][C/16], weight_divisor float32): the dequantised weight is
+    e2m1(code) * e4m3(scale) / divisor, as compressed-tensors stores it."""
+    w = (rng.standard_normal((R, C)) * std).astype(np.float32)
+    divisor = np.float32(448.0 * 6.0) / np.abs(w).max()
+    blocks = w.reshape(R, C // 16, 16)
+    amax = np.abs(blocks).max(axis=2)
+    sc = e4m3fn_encode((amax / np.float32(6.0)) * divisor)
+    scale_f = e4m3fn_decode(sc) / divisor
+    safe = np.where(scale_f == 0, np.float32(1.0), scale_f)
+    t = np.clip(blocks / safe[:, :, None], -6.0, 6.0).astype(np.float32)
+    codes = e2m1_encode(t).reshape(R, C)
+    packed = (codes[:, 0::2] | (codes[:, 1::2] << 4)).astype(np.uint8)
+    return np.ascontiguousarray(packed), np.ascontiguousarray(sc), np.float32(divisor)

@@ -158,3 +158,25 @@ def test_nvfp4_known_answers(orc):
     rc, y = orc.nvfp4_matvec(weights, np.array([0x38] * 4, np.uint8), 1.0, 64.0, 2, 32, x)
     assert rc == 0
     assert y.view(np.uint32).tolist() == [0xc0d00000, 0xc0f00000]
+
+
+def test_synthetic_nvfp4_encoders_agree_with_the_search_based_reference_form(orc, synth):
+    """synth's arithmetic E4M3 / E2M1 encoders (also used inside the CUDA kernels)
+    against the oracle's nearest-code searches, including every midpoint."""
+    dec = [orc.e4m3fn(c) for c in range(0x7f)]
+    vals = [np.float32(0), np.float32(448), np.float32(1000), np.float32(1e-10)]
+    for c in range(0x7e):
+        m = np.float32((np.float64(dec[c]) + np.float64(dec[c + 1])) / 2)
+        vals += [m, np.nextafter(m, np.float32(0)), np.nextafter(m, np.float32(1e9)), np.float32(dec[c])]
+    vals = np.array(vals, np.float32)
+    want = np.array([orc.e4m3fn_encode(float(v))[1] for v in vals], np.uint8)
+    assert (synth.e4m3fn_encode(vals) == want).all()
+    assert (synth.e4m3fn_decode(np.arange(0x7f, dtype=np.uint8)) == np.array(dec, np.float32)).all()
+    # E2M1: drive the oracle's encoder through the activation Q/DQ with scale exactly 1
+    t = np.array([0, 0.25, 0.26, 0.5, 0.75, 1.0, 1.25, 1.3, 1.75, 2.0, 2.5, 2.6, 3.5, 4.0, 5.0, 6.0], np.float32)
+    for sign in (1.0, -1.0):
+        x = (t * np.float32(sign)).astype(np.float32)
+        rc, packed, scales, _ = orc.nvfp4_qdq(x, 1.0)       # amax 6 -> scale code 0x38 (1.0)
+        assert rc == 0 and scales[0] == 0x38
+        codes = np.stack([packed & 15, packed >> 4], axis=1).ravel()
+        assert (synth.e2m1_encode(x) == codes).all()
