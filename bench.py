@@ -218,9 +218,8 @@ def run_b200(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     B = args.batch * world
     L = args.layers
-    per = E // world
-    stack = stack_mod.MoeStack(max(B, 1), H, M, E, K, expert_begin=rank * per,
-                               expert_end=E if rank == world - 1 else (rank + 1) * per)
+    lo, hi = importlib.import_module("salt-core_b200.ep").expert_range(rank, world, E)
+    stack = stack_mod.MoeStack(max(B, 1), H, M, E, K, expert_begin=lo, expert_end=hi)
     host_layers = generate_layers(synth, L, 3 if rank == 0 else 0, lambda i, layer: stack.add_layer(layer))
     x_host = synth.make_tokens(77, B, H)
     stream = torch.cuda.Stream()
@@ -231,19 +230,11 @@ def run_b200(args):
     grouped = torch.zeros(B * K * H, dtype=torch.float32, device="cuda")
     assert stack.set_grouped_out(grouped.data_ptr(), grouped.numel() * 4) == 0
 
-    def forward_ep(src_ptr, dst):
+    ep = importlib.import_module("salt-core_b200.ep")
+
+    def forward_ep(src, dst):
         """Expert-parallel pass: one exchange of the grouped expert outputs per layer."""
-        cur = src_ptr
-        for l in range(L):
-            last = l == L - 1
-            out = dst if last else act[l & 1]
-            if stack.layer_experts(l, cur, B, zero_remote=True, router_input_ready=l > 0, stream=sp) != 0:
-                raise RuntimeError("layer_experts failed")
-            dist.all_reduce(grouped)          # each row is written by one rank, the others add +0
-            if stack.layer_combine(l, B, out.data_ptr(), apply_norm=not last, prepare_next=not last,
-                                   stream=sp) != 0:
-                raise RuntimeError("layer_combine failed")
-            cur = out.data_ptr()
+        ep.forward(stack, grouped, src, B, dst, act, stream=sp)
 
     use_graph = world == 1 and not args.no_graph
     with torch.cuda.stream(stream):
@@ -251,7 +242,7 @@ def run_b200(args):
         if world == 1:
             assert stack.forward_device(d_x.data_ptr(), B, d_y.data_ptr(), stream=sp) == 0
         else:
-            forward_ep(d_x.data_ptr(), d_y)
+            forward_ep(d_x, d_y)
         launches_per_step = stack.launch_count() - n0
         assert stack.status(sp) == 0
         if use_graph:
@@ -263,7 +254,7 @@ def run_b200(args):
             elif world == 1:
                 assert stack.forward_device(d_x.data_ptr(), B, d_y.data_ptr(), stream=sp) == 0
             else:
-                forward_ep(d_x.data_ptr(), d_y)
+                forward_ep(d_x, d_y)
 
         def timed(fn, steps):
             if world > 1:
@@ -300,7 +291,7 @@ def run_b200(args):
                 stack.forward_host(x_host)
             else:
                 d_x.copy_(h_in, non_blocking=True)
-                forward_ep(d_x.data_ptr(), d_y)
+                forward_ep(d_x, d_y)
                 h_out.copy_(d_y, non_blocking=True)
                 stream.synchronize()
 

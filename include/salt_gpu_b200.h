@@ -341,6 +341,14 @@ int salt_b200_stack_set_grouped_out(void *stack, void *device_buffer, size_t nby
  *   SALT_B200_EXPERTS_ROUTER_INPUT_READY  the previous layer's combine already prepared the router input */
 #define SALT_B200_EXPERTS_ZERO_REMOTE 1
 #define SALT_B200_EXPERTS_ROUTER_INPUT_READY 2
+/*   SALT_B200_EXPERTS_TENSOR_CORE         run the expert projections as fp16 GEMMs on the tensor cores
+ *                                          (tcgen05/TMEM, fp32 accumulate) with every operand carried as
+ *                                          hi + lo fp16 halves: a TOLERANCE path for prefill-sized batches,
+ *                                          max |err| / max(|ref|, row rms) <= 1e-3; router and reduce stay exact
+ *   SALT_B200_EXPERTS_TENSOR_CORE_SINGLE  same with operands rounded to fp16 once (a third of the tensor work):
+ *                                          max |err| <= 1e-3 of the row maximum, about 2e-3 of the row rms */
+#define SALT_B200_EXPERTS_TENSOR_CORE 4
+#define SALT_B200_EXPERTS_TENSOR_CORE_SINGLE 8
 int salt_b200_layer_experts(void *stack, int layer, const float *d_x, int B, int flags, void *stream);
 /* Phase B: ordered weighted reduce of grouped_out into d_y [B][hidden].  flags:
  *   SALT_B200_COMBINE_NORM          d_y = RMSNorm(reduce) when the layer has a norm weight

@@ -16,6 +16,16 @@ bool q4_tile_supported(int C);
 cudaError_t launch_q4_jobs(const Q4Job* jobs, int njobs_max, const int* njobs_dev, int max_rows, int max_tok, int C,
                            int nmat, bool aligned, cudaStream_t stream);
 
+// ---- q4_gemm_tc.cu (tcgen05 / TMEM, tolerance path) --------------------------
+cudaError_t launch_gather_convert(const float* x, const int32_t* g2c, void* xh, void* xl, int jobs, int topk,
+                                  int hidden, cudaStream_t stream);
+// fused: gate/up + GeGLU -> out_h (+ out_l) [grouped rows][R] fp16; plain: -> out_f [grouped rows][R] fp32.
+// split: operands carried as hi + lo fp16 halves (xl / out_l must then be given).
+// y_base / y_cols locate each job's first grouped row from its y pointer.
+cudaError_t launch_q4_gemm_tc(bool fused, bool split, const Q4Job* jobs, int njobs_max, const int* njobs_dev,
+                              const void* xh, const void* xl, const float* y_base, int y_cols, void* out_h,
+                              void* out_l, float* out_f, int R, int* status, cudaStream_t stream);
+
 // ---- nvfp4_kernels.cu ------------------------------------------------------
 // One NVFP4 projection job: ntok rows of already dequantised activations.
 struct Fp4Job {
@@ -36,7 +46,7 @@ cudaError_t launch_nvfp4_jobs(const Fp4Job* jobs, int njobs, int max_rows, int m
 // Device-side error word: 0 = ok; set (never cleared) by kernels that meet a
 // non-finite value or an invalid index, as the reference's CPU functions
 // return -1 for them.
-enum : int { SB_ERR_NONFINITE = 1, SB_ERR_INDEX = 2, SB_ERR_CAPACITY = 4 };
+enum : int { SB_ERR_NONFINITE = 1, SB_ERR_INDEX = 2, SB_ERR_CAPACITY = 4, SB_ERR_TIMEOUT = 8 };
 
 // y = (x * rsqrt(mean(x^2) + eps)) [* weight]        (rows independent)
 cudaError_t launch_rmsnorm(const float* x, const float* weight, float* y, int rows, int n, float eps, int with_scale,

@@ -41,6 +41,7 @@ struct Stack {
     int32_t *selected = nullptr, *group_offsets = nullptr, *g2c = nullptr, *c2g = nullptr, *counters = nullptr;
     int32_t* status = nullptr;
     Q4Job *gateup_jobs = nullptr, *down_jobs = nullptr;
+    void *xh = nullptr, *xl = nullptr, *chain_h = nullptr, *chain_l = nullptr;   // fp16 operands (hi, lo) of the tensor-core path
     bool own_grouped = true;
     size_t grouped_bytes = 0;
     float *h_in = nullptr, *h_out = nullptr;  // pinned staging for the host entry point
@@ -79,6 +80,7 @@ static void free_stack(Stack* s) {
     cudaFree(s->reduced); cudaFree(s->act_a); cudaFree(s->act_b); cudaFree(s->io_in); cudaFree(s->io_out);
     cudaFree(s->selected); cudaFree(s->group_offsets); cudaFree(s->g2c); cudaFree(s->c2g);
     cudaFree(s->counters); cudaFree(s->status); cudaFree(s->gateup_jobs); cudaFree(s->down_jobs);
+    cudaFree(s->xh); cudaFree(s->xl); cudaFree(s->chain_h); cudaFree(s->chain_l);
     if (s->h_in) cudaFreeHost(s->h_in);
     if (s->h_out) cudaFreeHost(s->h_out);
     for (auto e : s->ev) cudaEventDestroy(e);
@@ -128,6 +130,8 @@ int salt_b200_stack_create(int max_tokens, int hidden, int inter, int n_experts,
               dev_alloc(&s->group_offsets, (size_t)n_experts + 1) && dev_alloc(&s->g2c, J) &&
               dev_alloc(&s->c2g, J) && dev_alloc(&s->counters, 4) && dev_alloc(&s->status, 1) &&
               dev_alloc(&s->gateup_jobs, (size_t)n_experts) && dev_alloc(&s->down_jobs, (size_t)n_experts) &&
+              dev_alloc((uint16_t**)&s->xh, J * hidden) && dev_alloc((uint16_t**)&s->chain_h, J * inter) &&
+              dev_alloc((uint16_t**)&s->xl, J * hidden) && dev_alloc((uint16_t**)&s->chain_l, J * inter) &&
               cuda_ok(cudaMemset(s->status, 0, sizeof(int32_t)), "status") &&
               cuda_ok(cudaHostAlloc((void**)&s->h_in, T * hidden * sizeof(float), cudaHostAllocDefault), "pinned") &&
               cuda_ok(cudaHostAlloc((void**)&s->h_out, T * hidden * sizeof(float), cudaHostAllocDefault), "pinned");
@@ -198,7 +202,8 @@ int salt_b200_stack_set_grouped_out(void* stack, void* device_buffer, size_t nby
 }
 
 // flags for salt_b200_layer_experts / salt_b200_layer_combine
-enum { SB_EXPERTS_ZERO_REMOTE = 1, SB_EXPERTS_ROUTER_INPUT_READY = 2 };
+enum { SB_EXPERTS_ZERO_REMOTE = 1, SB_EXPERTS_ROUTER_INPUT_READY = 2, SB_EXPERTS_TENSOR_CORE = 4,
+       SB_EXPERTS_TENSOR_CORE_SINGLE = 8 };
 enum { SB_COMBINE_NORM = 1, SB_COMBINE_PREPARE_NEXT = 2 };
 
 int salt_b200_layer_experts(void* stack, int layer, const float* d_x, int B, int flags, void* stream_) {
@@ -258,6 +263,28 @@ int salt_b200_layer_experts(void* stack, int layer, const float* d_x, int B, int
     const int njobs_max = jobs < local ? jobs : local;
     // tokens per expert group: at most B; the kernels loop over larger groups
     const int tok_hint = B == 1 ? 1 : (B == 2 ? 2 : 4);
+    if (flags & (SB_EXPERTS_TENSOR_CORE | SB_EXPERTS_TENSOR_CORE_SINGLE)) {
+        const bool split = (flags & SB_EXPERTS_TENSOR_CORE) != 0;
+        // tolerance path: fp16 operands on tcgen05, fp32 accumulation in TMEM
+        {
+            Timed t(s, KC_ROUTER_INPUT, st);
+            if (!cuda_ok(launch_gather_convert(d_x, s->g2c, s->xh, split ? s->xl : nullptr, jobs, K, H, st), "gather/convert")) return -1;
+        }
+        {
+            Timed t(s, KC_GATE_UP, st);
+            if (!cuda_ok(launch_q4_gemm_tc(true, split, s->gateup_jobs, njobs_max, s->counters, s->xh, s->xl, s->chain,
+                                           M, s->chain_h, s->chain_l, nullptr, M, s->status, st), "tc gate/up"))
+                return -1;
+        }
+        {
+            Timed t(s, KC_DOWN, st);
+            if (!cuda_ok(launch_q4_gemm_tc(false, split, s->down_jobs, njobs_max, s->counters, s->chain_h, s->chain_l,
+                                           s->grouped_out, H, nullptr, nullptr, s->grouped_out, H, s->status, st), "tc down"))
+                return -1;
+        }
+        count_launches(5);
+        return 0;
+    }
     {
         Timed t(s, KC_GATE_UP, st);
         if (!cuda_ok(launch_q4_jobs(s->gateup_jobs, njobs_max, s->counters, M, tok_hint, H, 2, true, st), "gate/up"))

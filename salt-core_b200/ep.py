@@ -1,0 +1,53 @@
+"""Expert-parallel plumbing for the MoE stack (one process per GPU, torch.distributed).
+
+Sharding rule: rank r of W owns the contiguous expert range
+[r*E//W, (r+1)*E//W) of every layer.  Activations are replicated; each rank
+fills only the rows of the grouped expert-output buffer that belong to its
+experts (global grouped order), and one exchange per layer completes the buffer
+on every rank.  Each row is written by exactly one rank and is +0 elsewhere, so a
+sum over ranks reproduces it exactly, in any order: the result is independent
+of the number of ranks.
+"""
+from __future__ import annotations
+
+
+def expert_range(rank: int, world: int, n_experts: int) -> tuple[int, int]:
+    if not 0 <= rank < world or world < 1 or n_experts < world:
+        raise ValueError("invalid expert-parallel layout")
+    return rank * n_experts // world, (rank + 1) * n_experts // world
+
+
+def owner_of(expert: int, world: int, n_experts: int) -> int:
+    for r in range(world):
+        lo, hi = expert_range(r, world, n_experts)
+        if lo <= expert < hi:
+            return r
+    raise ValueError("expert out of range")
+
+
+def exchange_grouped(grouped, group=None):
+    """Complete the zero-padded grouped buffer on every rank (in place)."""
+    import torch.distributed as dist
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(grouped, op=dist.ReduceOp.SUM, group=group)
+    return grouped
+
+
+def forward(stack, grouped, d_x, B, d_out, act, stream=0, first=0, count=None, group=None):
+    """One pass of layers [first, first+count) with one exchange per layer.
+    d_x / d_out / act[0..1] are torch tensors [B][hidden] on the device;
+    `grouped` is the stack's grouped-output buffer (set_grouped_out)."""
+    count = stack.n_layers - first if count is None else count
+    cur = d_x.data_ptr()
+    for i in range(count):
+        layer = first + i
+        last = i == count - 1
+        out = d_out if last else act[i & 1]
+        if stack.layer_experts(layer, cur, B, zero_remote=True, router_input_ready=i > 0, stream=stream) != 0:
+            raise RuntimeError("salt_b200_layer_experts failed")
+        exchange_grouped(grouped, group)
+        if stack.layer_combine(layer, B, out.data_ptr(), apply_norm=not last, prepare_next=not last,
+                               stream=stream) != 0:
+            raise RuntimeError("salt_b200_layer_combine failed")
+        cur = out.data_ptr()
+    return d_out

@@ -81,8 +81,11 @@ class MoeStack:
     EXPERTS_ZERO_REMOTE, EXPERTS_ROUTER_INPUT_READY = 1, 2
     COMBINE_NORM, COMBINE_PREPARE_NEXT = 1, 2
 
-    def layer_experts(self, layer, d_x, B, zero_remote=False, router_input_ready=False, stream=0):
-        flags = (1 if zero_remote else 0) | (2 if router_input_ready else 0)
+    def layer_experts(self, layer, d_x, B, zero_remote=False, router_input_ready=False, tensor_core=False,
+                      stream=0):
+        """tensor_core: False (exact kernels), True / "split" (hi+lo fp16 operands), "single"."""
+        tc = 0 if not tensor_core else (8 if tensor_core == "single" else 4)
+        flags = (1 if zero_remote else 0) | (2 if router_input_ready else 0) | tc
         return self.lib.salt_b200_layer_experts(self.handle, layer, C.c_void_p(d_x), B, flags, C.c_void_p(stream))
 
     def layer_combine(self, layer, B, d_y, apply_norm=True, prepare_next=False, stream=0):

@@ -1,0 +1,59 @@
+"""Prefill expert GEMMs on the tensor cores (tcgen05/TMEM), tolerance path.
+
+Stated tolerances against the fp32 CPU oracle (the router - selected experts, weights - stays
+bit-exact in both):
+  split  (hi + lo fp16 operands): max |y - y_ref| / max(|y_ref|, rms(y_ref row)) <= 1e-3
+  single (operands rounded once): max |y - y_ref| / max|y_ref row|               <= 1e-3"""
+import numpy as np
+import pytest
+
+from conftest import assert_bits_equal
+from gpu_util import d2h, stack_mod
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-3
+
+
+def _run_tc_layer(st, x, B, H, mode=True):
+    import torch
+    d_x = torch.from_numpy(x).cuda()
+    d_y = torch.zeros(B, H, dtype=torch.float32, device="cuda")
+    assert st.layer_experts(0, d_x.data_ptr(), B, tensor_core=mode) == 0
+    assert st.layer_combine(0, B, d_y.data_ptr(), apply_norm=False) == 0
+    assert st.status() == 0
+    return d_y.cpu().numpy()
+
+
+def _rel_err(y, ref):
+    rms = np.sqrt((ref.astype(np.float64) ** 2).mean(axis=1, keepdims=True))
+    return float((np.abs(y.astype(np.float64) - ref) / np.maximum(np.abs(ref), rms)).max())
+
+
+def _rel_err_rowmax(y, ref):
+    top = np.abs(ref).max(axis=1, keepdims=True).astype(np.float64)
+    return float((np.abs(y.astype(np.float64) - ref) / top).max())
+
+
+@pytest.mark.parametrize("geom", [(256, 128, 8, 2, 64), (512, 256, 16, 4, 200), (2816, 704, 128, 8, 512)])
+def test_tensor_core_prefill_within_tolerance(orc, synth, geom):
+    H, M, E, K, B = geom
+    make = synth.make_q4_moe_layer_bulk if H == 2816 else synth.make_q4_moe_layer
+    layer = make(70 + B, hidden=H, inter=M, n_experts=E, topk=K)
+    x = synth.make_tokens(71 + B, B, H)
+    st = stack_mod().MoeStack(B, H, M, E, K)
+    st.add_layer(layer)
+    y = _run_tc_layer(st, x, B, H, "split")
+    want, sel, w = orc.moe_layer_q4(layer, x, threads=16)
+    ws = st.workspace()
+    assert_bits_equal(d2h(ws.selected, B * K, np.int32).reshape(B, K), sel, "selected (exact)")
+    assert_bits_equal(d2h(ws.weights, B * K, np.float32).reshape(B, K), w, "weights (exact)")
+    err = _rel_err(y, want)
+    print(f"tensor-core prefill H={H} B={B}: max relative error {err:.3e}")
+    assert err <= TOL, err
+    y1 = _run_tc_layer(st, x, B, H, "single")
+    err1, err1_rms = _rel_err_rowmax(y1, want), _rel_err(y1, want)
+    print(f"  single-pass fp16: {err1:.3e} of the row maximum, {err1_rms:.3e} of max(|ref|, row rms)")
+    assert err1 <= TOL, err1
+    assert st.status() == 0
+    st.close()
