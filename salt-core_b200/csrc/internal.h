@@ -1,5 +1,6 @@
 // Declarations shared by the translation units of libsalt_gpu_b200.so.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stddef.h>
 #include <stdint.h>
@@ -19,12 +20,19 @@ cudaError_t launch_q4_jobs(const Q4Job* jobs, int njobs_max, const int* njobs_de
 // ---- q4_gemm_tc.cu (tcgen05 / TMEM, tolerance path) --------------------------
 cudaError_t launch_gather_convert(const float* x, const int32_t* g2c, void* xh, void* xl, int jobs, int topk,
                                   int hidden, cudaStream_t stream);
+// TMA descriptors of a [rows][cols] fp16 activation buffer and of its residual buffer:
+// boxes of 64 columns x (16 << i) rows.
+struct TcMaps {
+    CUtensorMap hi[4];
+    CUtensorMap lo[4];
+};
+cudaError_t make_tc_maps(TcMaps* out, const void* hi, const void* lo, int rows, int cols);
 // fused: gate/up + GeGLU -> out_h (+ out_l) [grouped rows][R] fp16; plain: -> out_f [grouped rows][R] fp32.
-// split: operands carried as hi + lo fp16 halves (xl / out_l must then be given).
+// split: operands carried as hi + lo fp16 halves.  bmaps describes the activations (grouped order).
 // y_base / y_cols locate each job's first grouped row from its y pointer.
 cudaError_t launch_q4_gemm_tc(bool fused, bool split, const Q4Job* jobs, int njobs_max, const int* njobs_dev,
-                              const void* xh, const void* xl, const float* y_base, int y_cols, void* out_h,
-                              void* out_l, float* out_f, int R, int* status, cudaStream_t stream);
+                              const TcMaps& bmaps, const float* y_base, int y_cols, void* out_h, void* out_l,
+                              float* out_f, int R, int* status, cudaStream_t stream);
 
 // ---- nvfp4_kernels.cu ------------------------------------------------------
 // One NVFP4 projection job: ntok rows of already dequantised activations.

@@ -10,6 +10,7 @@
 // their positions in the global grouped order; rows of other devices' experts
 // arrive through whatever exchange the caller runs between the two phases.
 #include <cuda_runtime.h>
+#include <stdio.h>
 #include <string.h>
 
 #include <vector>
@@ -42,6 +43,8 @@ struct Stack {
     int32_t* status = nullptr;
     Q4Job *gateup_jobs = nullptr, *down_jobs = nullptr;
     void *xh = nullptr, *xl = nullptr, *chain_h = nullptr, *chain_l = nullptr;   // fp16 operands (hi, lo) of the tensor-core path
+    bool tc_ready = false;                     // tensor maps built (needs hidden, inter multiples of 64)
+    TcMaps x_maps, chain_maps;                 // TMA descriptors of (xh, xl) and (chain_h, chain_l)
     bool own_grouped = true;
     size_t grouped_bytes = 0;
     float *h_in = nullptr, *h_out = nullptr;  // pinned staging for the host entry point
@@ -139,6 +142,8 @@ int salt_b200_stack_create(int max_tokens, int hidden, int inter, int n_experts,
         free_stack(s);
         return -1;
     }
+    s->tc_ready = make_tc_maps(&s->x_maps, s->xh, s->xl, (int)J, hidden) == cudaSuccess &&
+                  make_tc_maps(&s->chain_maps, s->chain_h, s->chain_l, (int)J, inter) == cudaSuccess;
     *stack_out = s;
     return 0;
 }
@@ -265,6 +270,10 @@ int salt_b200_layer_experts(void* stack, int layer, const float* d_x, int B, int
     const int tok_hint = B == 1 ? 1 : (B == 2 ? 2 : 4);
     if (flags & (SB_EXPERTS_TENSOR_CORE | SB_EXPERTS_TENSOR_CORE_SINGLE)) {
         const bool split = (flags & SB_EXPERTS_TENSOR_CORE) != 0;
+        if (!s->tc_ready) {
+            fprintf(stderr, "salt_b200: tensor-core path unavailable for this geometry\n");
+            return -1;
+        }
         // tolerance path: fp16 operands on tcgen05, fp32 accumulation in TMEM
         {
             Timed t(s, KC_ROUTER_INPUT, st);
@@ -272,13 +281,13 @@ int salt_b200_layer_experts(void* stack, int layer, const float* d_x, int B, int
         }
         {
             Timed t(s, KC_GATE_UP, st);
-            if (!cuda_ok(launch_q4_gemm_tc(true, split, s->gateup_jobs, njobs_max, s->counters, s->xh, s->xl, s->chain,
+            if (!cuda_ok(launch_q4_gemm_tc(true, split, s->gateup_jobs, njobs_max, s->counters, s->x_maps, s->chain,
                                            M, s->chain_h, s->chain_l, nullptr, M, s->status, st), "tc gate/up"))
                 return -1;
         }
         {
             Timed t(s, KC_DOWN, st);
-            if (!cuda_ok(launch_q4_gemm_tc(false, split, s->down_jobs, njobs_max, s->counters, s->chain_h, s->chain_l,
+            if (!cuda_ok(launch_q4_gemm_tc(false, split, s->down_jobs, njobs_max, s->counters, s->chain_maps,
                                            s->grouped_out, H, nullptr, nullptr, s->grouped_out, H, s->status, st), "tc down"))
                 return -1;
         }

@@ -1,30 +1,37 @@
 // Grouped affine-Q4 expert GEMMs on the 5th-generation tensor cores (tcgen05 +
 // TMEM) for prefill-sized token groups.  TOLERANCE path: operands are fp16
-// (weights dequantised in fp32 as q*s+b, then rounded to fp16; activations
-// rounded to fp16), accumulation is fp32 in TMEM.  The bit-exact kernels in
-// q4_kernels.cu remain the reference-conformant path.
+// (weights dequantised as q*s+b and rounded to fp16; activations rounded to
+// fp16), accumulation is fp32 in TMEM.  The bit-exact kernels in q4_kernels.cu
+// remain the reference-conformant path.
 //
 // Two precisions (template SPLIT):
 //   single  one MMA per k-step, operands rounded to fp16 once: measured
 //           max |err| / max(|ref|, row rms) about 2e-3 (5e-4 of the row maximum)
 //   split   every operand is carried as hi + lo fp16 halves (lo = fp16(v - hi)) and
 //           each k-step issues Ah*Bh + Al*Bh + Ah*Bl: operand error ~2^-22, three
-//           times the tensor work, which the HBM-bound prefill sizes can afford
+//           times the tensor work
 //
 // One block = one 128-row weight tile of one expert group.  Weight rows sit on
 // the MMA M dimension (always full), the group's tokens on N (16..128 per pass),
 // so small groups waste no tensor rows.  K advances in 64-column chunks = one
-// quantisation group per row:
-//   all 256 threads  : dequantise 2 x 128 row-chunks (gate, up) Q4 -> fp16 into the
-//                      K-major, unswizzled core-matrix layout (8 rows x 16 bytes),
-//                      copy the tokens' fp16 activations next to them
-//   one thread       : four tcgen05.mma.kind::f16 (M128 x N x K16) per matrix,
-//                      then tcgen05.commit on the stage's mbarrier
-//   3 stages         : conversion of chunk k+1, k+2 overlaps the MMAs of chunk k
-//   epilogue warps   : tcgen05.ld the accumulators, GeGLU (fused gate/up) or plain
-//                      store (down)
-// Every mbarrier wait is bounded: on expiry the block records an error in the
-// status word, skips its remaining work, frees its TMEM and returns.
+// quantisation group per row.  Warp-specialised:
+//   warps 0-7 (converters)  dequantise 128 row-chunks per matrix Q4 -> fp16 into the
+//                           K-major 128-byte-swizzled tile layout;
+//                           packed weights come through a 4-chunk-deep register ring;
+//                           one elected mbarrier arrive per warp marks the stage full
+//   warp 8 (issuer)         prefetches the tile's weights into L2, feeds the tokens' fp16
+//                           activations by TMA (cp.async.bulk.tensor, 128-byte swizzle)
+//                           into a ring of B tiles several chunks ahead, issues the
+//                           tcgen05.mma.kind::f16 (M128 x N x K16) of every full stage
+//                           and tcgen05.commit on the stage's "free" mbarrier
+//   warps 0-3 (epilogue)    tcgen05.ld the accumulators, GeGLU (fused gate/up) or plain
+//                           store (down)
+// Column order inside every group of 8 K columns is permuted to [0,4,1,5,2,6,3,7] in
+// BOTH operands (a contraction does not care): it is the order in which two masks
+// and one shift peel half2 pairs out of a packed 32-bit word.
+// Every mbarrier wait is bounded: on expiry the block raises a shared flag, records
+// an error in the status word, every role leaves its loop, outstanding copies and
+// MMAs are waited for (bounded), TMEM is freed and the block returns.
 #include <cuda_fp16.h>
 
 #include "internal.h"
@@ -33,11 +40,13 @@
 namespace sb {
 
 constexpr int TC_STAGES = 3;
-constexpr int TC_THREADS = 256;
+constexpr int TC_CONVERTERS = 256;
+constexpr int TC_THREADS = TC_CONVERTERS + 32;
 constexpr int TC_KC = 64;                    // K columns per chunk
 constexpr int TC_A_BYTES = 128 * TC_KC * 2;  // one matrix' 128 x 64 fp16 tile
 constexpr int TC_MAX_NT = 128;
-constexpr int TC_B_BYTES = TC_MAX_NT * TC_KC * 2;
+constexpr int TC_MAX_BSLOTS = 8;
+constexpr int TC_SMEM_BYTES = 225 * 1024;    // dynamic shared memory of every launch (one block per SM)
 constexpr uint32_t TC_SPIN_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -46,8 +55,13 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
 
-// Bounded wait for the phase with the given parity.  Returns false on expiry.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Bounded wait for the phase with the given parity.  Returns false on expiry or when
+// another thread of the block has raised the failure flag.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* fail) {
     const uint32_t addr = smem_u32(bar);
     for (uint32_t i = 0; i < TC_SPIN_LIMIT; i++) {
         uint32_t ok;
@@ -59,19 +73,70 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
             : "r"(addr), "r"(parity)
             : "memory");
         if (ok) return true;
+        if ((i & 255u) == 255u && *fail) return false;
     }
+    *fail = 1;
     return false;
 }
 
-// K-major operand without swizzle: core matrices of 8 rows x 16 bytes; LBO = byte
-// distance between the two K-adjacent core matrices of one MMA, SBO = distance
-// between 8-row groups.  Descriptor version 1 (sm_100).
-__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
-    uint64_t d = (uint64_t)((saddr & 0x3ffffu) >> 4);
-    d |= (uint64_t)(lbo >> 4) << 16;
-    d |= (uint64_t)(sbo >> 4) << 32;
-    d |= (uint64_t)1 << 46;
+__device__ __forceinline__ uint64_t make_desc(uint32_t lo, uint32_t hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
     return d;
+}
+
+// Shared-memory matrix descriptors (sm_100 version 1), split into 32-bit words so that
+// the issuing thread only adds byte offsets >> 4 to the low word.
+// Both operands are K-major with 128-byte swizzle, as a TMA copy with
+// CU_TENSOR_MAP_SWIZZLE_128B lays a tile down: rows of 64 fp16 (128 bytes), 16-byte chunk c
+// of row r stored at chunk position c ^ (r & 7), 8-row atoms of 1024 bytes; a tile starts
+// on a 1024-byte boundary and a K step of 16 elements advances the start address by 32 bytes.
+// (The unswizzled core-matrix layout gives the same results but its MMAs ran several times
+// slower here.)
+constexpr uint32_t DESC_B_LO = 1u << 16;
+constexpr uint32_t DESC_B_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+
+// 2-D tiled TMA load (no multicast) of one box at element column x, row y.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
+            "r"(dst),
+        "l"((uint64_t)map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// Hint: bring [p, p + bytes) into L2 with large sequential DRAM reads (16-byte granules,
+// rounded inward).  The tile's later 16-byte loads, scattered over 128 rows, then hit L2.
+__device__ __forceinline__ void l2_prefetch_range(const void* p, size_t bytes) {
+    uintptr_t b = ((uintptr_t)p + 15) & ~(uintptr_t)15, e = ((uintptr_t)p + bytes) & ~(uintptr_t)15;
+    while (b < e) {
+        const uint32_t n = (uint32_t)min((size_t)(e - b), (size_t)16384);
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(b), "r"(n) : "memory");
+        b += n;
+    }
+}
+
+// Ring loads as volatile asm: an ordinary read-only load is an invariant load to the
+// compiler, which is then free to sink it down to its first use, chunks later, and the
+// prefetch distance is lost.  Volatile asm statements keep their program order.
+__device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+// 16-bit load straight into a 32-bit register (zero-extended by the load itself): a
+// separate widening instruction would wait for the data right behind the load.
+__device__ __forceinline__ uint32_t ld_stream_u16(const void* p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
 }
 
 // kind::f16 instruction descriptor: D = F32, A = B = F16, both K-major.
@@ -107,73 +172,126 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
 
-__device__ __forceinline__ uint32_t pack_half2(f32x2 v) {
-    float lo, hi;
-    unpack2(v, lo, hi);
+// half2 {lo, hi} from two floats (round to nearest even)
+__device__ __forceinline__ uint32_t f16x2_from(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
 }
-
-__device__ __forceinline__ f32x2 half2_to_f32x2(uint32_t h2) {
-    float lo, hi;
-    asm("{\n\t.reg .f16 l, h;\n\tmov.b32 {l, h}, %2;\n\tcvt.f32.f16 %0, l;\n\tcvt.f32.f16 %1, h;\n\t}\n"
-        : "=f"(lo), "=f"(hi)
-        : "r"(h2));
-    return pack2(lo, hi);
+__device__ __forceinline__ float f16_lo_to_f32(uint32_t h2) {
+    float f;
+    asm("{\n\t.reg .f16 l, h;\n\tmov.b32 {l, h}, %1;\n\tcvt.f32.f16 %0, l;\n\t}\n" : "=f"(f) : "r"(h2));
+    return f;
+}
+__device__ __forceinline__ float f16_hi_to_f32(uint32_t h2) {
+    float f;
+    asm("{\n\t.reg .f16 l, h;\n\tmov.b32 {l, h}, %1;\n\tcvt.f32.f16 %0, h;\n\t}\n" : "=f"(f) : "r"(h2));
+    return f;
+}
+__device__ __forceinline__ uint32_t hsub2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t hfma2(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
 }
 
-// hi = fp16(v), lo = fp16(v - hi) for a pair
-__device__ __forceinline__ void split_half2(f32x2 v, uint32_t& hi, uint32_t& lo) {
-    hi = pack_half2(v);
-    const f32x2 neg_one = pack2(-1.0f, -1.0f);
-    lo = pack_half2(fma2(half2_to_f32x2(hi), neg_one, v));   // v - hi, exact in fp32
+// Position of original column o (0..7) inside its group of 8 in the operands' K order
+// [0,4,1,5,2,6,3,7].
+__host__ __device__ __forceinline__ int tc_kpos(int o) { return ((o & 3) << 1) | (o >> 2); }
+
+// Can q*s+b of this group be formed in fp16 arithmetic without loss?  s/16 and b must be
+// exact fp16 values (bf16 has 8 significant bits) and 15*s+b must stay finite.
+// bf16 exponent fields: s in [2^-13, 2^10), b zero or in [2^-17, 2^14).
+__device__ __forceinline__ bool fp16_path_ok(uint32_t s_bits, uint32_t b_bits) {
+    const uint32_t es = (s_bits >> 7) & 0xffu, eb = (b_bits >> 7) & 0xffu;
+    const bool s_ok = es >= 114u && es <= 136u;
+    const bool b_ok = (b_bits & 0x7fffu) == 0u || (eb >= 110u && eb <= 140u);
+    return s_ok && b_ok;
 }
 
-// 64 consecutive Q4 elements of one row (32 packed bytes) -> 64 fp16 written as
-// eight 16-byte core-matrix rows at dst + kcore*128 (and their fp16 residuals at
-// dst_lo when SPLIT).  Nibbles become floats by the mask-and-exponent trick.
+// 32 consecutive Q4 elements of one row (16 packed bytes) -> four 16-byte chunks of the
+// row's 128-byte line at dst, chunk c0 + i stored at position (c0 + i) ^ sw (128-byte
+// swizzle, sw = row & 7), fp16 arithmetic: a nibble masked in place under the exponent of
+// 2^10 reads as 1024 + q (low nibble of a byte) or 1024 + 16 q (high nibble); subtracting
+// 1024 is exact and one half2 fma with s (or s/16) forms q*s + b with a single rounding.
+__device__ __forceinline__ void dequant_half_chunk_f16(const uint4& p, uint32_t s_bits, uint32_t b_bits, uint8_t* dst,
+                                                       uint32_t c0, uint32_t sw) {
+    const float s = bf16_bits_to_f32(s_bits), b = bf16_bits_to_f32(b_bits);
+    const uint32_t s2 = f16x2_from(s, s), s2_16 = f16x2_from(s * 0.0625f, s * 0.0625f), b2 = f16x2_from(b, b);
+    const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+    const uint32_t k1024 = 0x64006400u;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {  // word i = 8 columns = one K core matrix
+        const uint32_t w0 = w[i], w1 = w[i] >> 8;
+        uint32_t a0, a1, a2, a3;
+        asm("lop3.b32 %0, %1, 0x000f000f, %2, 0xEA;" : "=r"(a0) : "r"(w0), "r"(k1024));   // cols (0,4)
+        asm("lop3.b32 %0, %1, 0x00f000f0, %2, 0xEA;" : "=r"(a1) : "r"(w0), "r"(k1024));   // cols (1,5) * 16
+        asm("lop3.b32 %0, %1, 0x000f000f, %2, 0xEA;" : "=r"(a2) : "r"(w1), "r"(k1024));   // cols (2,6)
+        asm("lop3.b32 %0, %1, 0x00f000f0, %2, 0xEA;" : "=r"(a3) : "r"(w1), "r"(k1024));   // cols (3,7) * 16
+        uint4 o;
+        o.x = hfma2(hsub2(a0, k1024), s2, b2);
+        o.y = hfma2(hsub2(a1, k1024), s2_16, b2);
+        o.z = hfma2(hsub2(a2, k1024), s2, b2);
+        o.w = hfma2(hsub2(a3, k1024), s2_16, b2);
+        *(uint4*)(dst + (((c0 + i) ^ sw) << 4)) = o;
+    }
+}
+
+// The same 32 elements through fp32 (any scale), optionally with the fp16 residuals
+// lo = fp16(v - hi) at dst_lo.
 template <bool SPLIT>
-__device__ __forceinline__ void dequant_row_chunk(const NibbleMagic& mg, const uint4& p0, const uint4& p1, float s,
-                                                  float b, uint8_t* dst, uint8_t* dst_lo) {
-    const uint32_t w[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+__device__ __forceinline__ void dequant_half_chunk_f32(const NibbleMagic& mg, const uint4& p, uint32_t s_bits,
+                                                       uint32_t b_bits, uint8_t* dst, uint8_t* dst_lo, uint32_t c0,
+                                                       uint32_t sw) {
+    const float s = bf16_bits_to_f32(s_bits), b = bf16_bits_to_f32(b_bits);
+    const uint32_t w[4] = {p.x, p.y, p.z, p.w};
     const f32x2 ss = pack2(s, s), bb = pack2(b, b);
 #pragma unroll
-    for (int i = 0; i < 8; i++) {  // word i = columns 8i .. 8i+7 = K core matrix i
+    for (int i = 0; i < 4; i++) {
         f32x2 q[4];
         nibbles4(w[i] & 0xffffu, mg, q[0], q[1]);
         nibbles4(w[i] >> 16, mg, q[2], q[3]);
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 4; k++) unpack2(fma2(q[k], ss, bb), v[2 * k], v[2 * k + 1]);
         uint32_t hi[4], lo[4];
 #pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const f32x2 d = fma2(q[k], ss, bb);
-            if (SPLIT) split_half2(d, hi[k], lo[k]);
-            else hi[k] = pack_half2(d);
+        for (int k = 0; k < 4; k++) {   // half2 k holds columns (k, k + 4)
+            hi[k] = f16x2_from(v[k], v[k + 4]);
+            if (SPLIT) lo[k] = f16x2_from(v[k] - f16_lo_to_f32(hi[k]), v[k + 4] - f16_hi_to_f32(hi[k]));
         }
-        *(uint4*)(dst + i * 128) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-        if (SPLIT) *(uint4*)(dst_lo + i * 128) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        const uint32_t off = ((c0 + i) ^ sw) << 4;
+        *(uint4*)(dst + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        if (SPLIT) *(uint4*)(dst_lo + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
     }
 }
 
 struct TcArgs {
     const Q4Job* jobs;         // per expert group: weights (A = gate or the only matrix, B = up), R, C, ntok
     const int* njobs_dev;
-    const __half* xh;          // [grouped rows][C] fp16 activations, grouped order
-    const __half* xl;          // their fp16 residuals (split precision) or null
     const float* y_base;       // base the jobs' y pointers are relative to (to recover the group's first row)
     int y_cols;                // columns of that buffer (inter for gate/up, hidden for down)
-    __half* out_h;             // fused: GeGLU output [grouped rows][R] fp16
+    __half* out_h;             // fused: GeGLU output [grouped rows][R] fp16, columns in operand K order
     __half* out_l;             // its fp16 residual (split precision) or null
     float* out_f;              // plain: projection output [grouped rows][R] fp32
     int* status;
+    int prefetch_ahead;        // blocks between a tile and the one whose weights it prefetches into L2
 };
 
 template <bool FUSED, bool SPLIT>
-__global__ void __launch_bounds__(TC_THREADS, 1) q4_gemm_tc_kernel(TcArgs a) {
-    extern __shared__ __align__(1024) uint8_t smem[];
-    __shared__ __align__(8) uint64_t bar_free[TC_STAGES];
-    __shared__ __align__(8) uint64_t bar_done;
+__global__ void __launch_bounds__(TC_THREADS, 1)
+q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_free[TC_STAGES];   // stage's MMAs complete (tcgen05.commit)
+    __shared__ __align__(8) uint64_t bar_full[TC_STAGES];   // stage converted (8 warp arrivals)
+    __shared__ __align__(8) uint64_t bar_b[TC_MAX_BSLOTS];  // B tile landed (TMA transaction bytes)
+    __shared__ __align__(8) uint64_t bar_done;              // a token pass' accumulators are final
     __shared__ uint32_t s_tmem;
+    __shared__ int s_fail;
 
     const int job_id = blockIdx.y;
     if (a.njobs_dev != nullptr && job_id >= *a.njobs_dev) return;
@@ -186,13 +304,28 @@ __global__ void __launch_bounds__(TC_THREADS, 1) q4_gemm_tc_kernel(TcArgs a) {
     constexpr int NMAT = FUSED ? 2 : 1;
     constexpr int NPART = SPLIT ? 2 : 1;                     // hi (+ lo) copies of every operand tile
     constexpr int STAGES = (FUSED && SPLIT) ? 2 : TC_STAGES;
-    constexpr int A_ALL = NMAT * NPART * TC_A_BYTES;         // A tiles of a stage: [matrix][hi, lo]
-    constexpr int STAGE_BYTES = A_ALL + NPART * TC_B_BYTES;
-    uint8_t* stage_base = smem;
+    constexpr int STAGE_BYTES = NMAT * NPART * TC_A_BYTES;   // A tiles of a stage: [matrix][hi, lo]
+    // 1024-byte aligned carve-up: A stages, then the ring of B tiles (tokens' activations)
+    uint8_t* stage_base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t* bring = stage_base + STAGES * STAGE_BYTES;
+    // B tile rows = smallest TMA box (16, 32, 64, 128 token rows) that holds a pass
+    const int ntok_cap = min(jb.ntok, TC_MAX_NT);
+    const int variant = ntok_cap <= 16 ? 0 : ntok_cap <= 32 ? 1 : ntok_cap <= 64 ? 2 : 3;
+    const uint32_t part_bytes = (16u << variant) * 128u;
+    const uint32_t slot_bytes = NPART * part_bytes;
+    const uint32_t NB = (uint32_t)min(TC_MAX_BSLOTS, (int)((TC_SMEM_BYTES - 1024 - STAGES * STAGE_BYTES) / slot_bytes));
+    const int npass = (jb.ntok + TC_MAX_NT - 1) / TC_MAX_NT;
+    const uint32_t total = (uint32_t)npass * (uint32_t)nchunks;
+    volatile int* fail = &s_fail;
 
     if (tid == 0) {
-        for (int s = 0; s < STAGES; s++) mbar_init(&bar_free[s], 1);
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&bar_free[s], 1);
+            mbar_init(&bar_full[s], TC_CONVERTERS / 32);
+        }
+        for (int s = 0; s < TC_MAX_BSLOTS; s++) mbar_init(&bar_b[s], 1);
         mbar_init(&bar_done, 1);
+        s_fail = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -206,100 +339,178 @@ __global__ void __launch_bounds__(TC_THREADS, 1) q4_gemm_tc_kernel(TcArgs a) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = s_tmem;
 
-    // converter role of this thread: (matrix, row) of the A tiles
-    const int cm = FUSED ? (tid >> 7) : 0;
-    const int crow = tid & 127;
-    const bool conv_active = FUSED || tid < 128;
+    // ---- converter set-up: one 32-element half of a 64-column chunk of one row, in every matrix.
+    // Eight consecutive lanes take eight consecutive rows; the swizzle sends their 16-byte
+    // stores to eight different bank groups.
+    constexpr int DEPTH = 4;                                  // chunks of packed weights in flight per thread
+    const int crow = ((tid & 7) | ((tid >> 4) << 3)) & 127, chalf = (tid >> 3) & 1;
     const int grow = min(r0 + crow, jb.R - 1);
-    const uint8_t* cvals = (cm == 0 ? jb.vals : jb.vals2) + (size_t)grow * (C >> 1);
-    const uint16_t* csc = (const uint16_t*)(cm == 0 ? jb.scales : jb.scales2) + (size_t)grow * nchunks;
-    const uint8_t* cbi_raw = (cm == 0 ? jb.biases : jb.biases2);
-    const uint16_t* cbi = cbi_raw ? (const uint16_t*)cbi_raw + (size_t)grow * nchunks : nullptr;
-    const uint32_t a_off = (uint32_t)cm * NPART * TC_A_BYTES + (uint32_t)(crow >> 3) * 1024 + (uint32_t)(crow & 7) * 16;
-
+    const uint8_t* cvals[NMAT];
+    const uint16_t* csc[NMAT];
+    const uint16_t* cbi[NMAT];
+#pragma unroll
+    for (int m = 0; m < NMAT; m++) {
+        cvals[m] = (m == 0 ? jb.vals : jb.vals2) + (size_t)grow * (C >> 1) + chalf * 16;
+        csc[m] = (const uint16_t*)(m == 0 ? jb.scales : jb.scales2) + (size_t)grow * nchunks;
+        const uint8_t* braw = (m == 0 ? jb.biases : jb.biases2);
+        cbi[m] = braw ? (const uint16_t*)braw + (size_t)grow * nchunks : nullptr;
+    }
+    const uint32_t a_off = (uint32_t)crow * 128;            // the row's 128-byte line in a 128 x 64 fp16 tile
+    const uint32_t a_c0 = (uint32_t)chalf * 4, a_sw = (uint32_t)crow & 7;
     const NibbleMagic mg = load_nibble_magic();
-    uint32_t it = 0;          // running chunk counter across token passes (stage / parity bookkeeping)
-    uint32_t done_phase = 0;
-    bool failed = false;
 
-    for (int tb = 0; tb < jb.ntok; tb += TC_MAX_NT) {
+    // ---- issuer set-up
+    uint32_t b_issued = 0;                                    // B tiles requested so far
+    const uint32_t a_lo0 = DESC_B_LO | ((smem_u32(stage_base) & 0x3ffffu) >> 4);
+    const uint32_t b_lo0 = DESC_B_LO | ((smem_u32(bring) & 0x3ffffu) >> 4);
+    // request the B tile of running chunk t (pass t / nchunks, chunk t % nchunks)
+    auto issue_b = [&](uint32_t t) {
+        const uint32_t slot = t % NB;
+        const int pass = (int)(t / (uint32_t)nchunks), kq = (int)(t % (uint32_t)nchunks);
+        const uint32_t dst = smem_u32(bring + slot * slot_bytes);
+        mbar_expect_tx(&bar_b[slot], slot_bytes);
+        tma_load_2d(dst, &maps.hi[variant], kq * TC_KC, g0 + pass * TC_MAX_NT, &bar_b[slot]);
+        if (SPLIT) tma_load_2d(dst + part_bytes, &maps.lo[variant], kq * TC_KC, g0 + pass * TC_MAX_NT, &bar_b[slot]);
+    };
+    if (warp == 8) {
+        if (lane == 0)
+            for (; b_issued < total && b_issued < NB; b_issued++) issue_b(b_issued);
+        // L2 prefetch of the weights of this tile and of the tile `prefetch_ahead` blocks later
+        // in launch order (whichever SM runs it, L2 is shared): large sequential DRAM reads.
+        const int njobs_live = a.njobs_dev ? *a.njobs_dev : (int)gridDim.y;
+        for (int which = 0; which < 2; which++) {
+            const uint32_t lin = blockIdx.y * gridDim.x + blockIdx.x + (which ? (uint32_t)a.prefetch_ahead : 0u);
+            const int py = (int)(lin / gridDim.x), px = (int)(lin % gridDim.x);
+            if (py >= njobs_live || (which && a.prefetch_ahead <= 0)) break;
+            const Q4Job pj = which ? a.jobs[py] : jb;
+            const int pr0 = px * 128;
+            if (pr0 >= pj.R) continue;
+            const size_t prow = (size_t)min(128, pj.R - pr0);
+            const size_t vb = (size_t)(pj.C >> 1), gb = (size_t)(pj.C / TC_KC) * 2;
+            const uint8_t* reg = nullptr;
+            size_t len = 0;
+            switch (lane) {   // one region per lane
+                case 0: reg = pj.vals + pr0 * vb; len = prow * vb; break;
+                case 1: reg = pj.scales + pr0 * gb; len = prow * gb; break;
+                case 2: if (pj.biases) { reg = pj.biases + pr0 * gb; len = prow * gb; } break;
+                case 3: if (FUSED) { reg = pj.vals2 + pr0 * vb; len = prow * vb; } break;
+                case 4: if (FUSED) { reg = pj.scales2 + pr0 * gb; len = prow * gb; } break;
+                case 5: if (FUSED && pj.biases2) { reg = pj.biases2 + pr0 * gb; len = prow * gb; } break;
+                default: break;
+            }
+            if (reg) l2_prefetch_range(reg, len);
+        }
+        __syncwarp();
+    }
+
+    uint32_t it = 0;          // running chunk counter across token passes (stage / parity bookkeeping)
+    for (int pass = 0; pass < npass; pass++) {
+        const int tb = pass * TC_MAX_NT;
         const int nt_real = min(TC_MAX_NT, jb.ntok - tb);
         const int NT = (nt_real + 15) & ~15;
-        const uint32_t idesc = umma_idesc_f16(128, NT);
 
-        uint4 p0 = make_uint4(0, 0, 0, 0), p1 = p0;
-        uint32_t hs = 0, hb = 0;
-        if (conv_active) {
-            p0 = __ldg((const uint4*)cvals);
-            p1 = __ldg((const uint4*)cvals + 1);
-            hs = csc[0];
-            hb = cbi ? cbi[0] : 0;
-        }
-        for (int kc = 0; kc < nchunks; kc++, it++) {
-            const int s = it % STAGES;
-            uint8_t* st = stage_base + s * STAGE_BYTES;
-            if (it >= STAGES && !failed) {
-                // the MMAs that last read this stage must have completed
-                if (!mbar_wait(&bar_free[s], ((it / STAGES) - 1) & 1)) failed = true;
-            }
-            // current chunk's packed data is in registers; fetch the next chunk's first
-            const uint4 c0 = p0, c1 = p1;
-            const uint32_t chs = hs, chb = hb;
-            if (conv_active && kc + 1 < nchunks) {
-                p0 = __ldg((const uint4*)(cvals + (kc + 1) * 32));
-                p1 = __ldg((const uint4*)(cvals + (kc + 1) * 32) + 1);
-                hs = csc[kc + 1];
-                hb = cbi ? cbi[kc + 1] : 0;
-            }
-            // B tile: NT token rows x 64 fp16 of this chunk -> core-matrix layout
-            {
-                uint8_t* sb_ = st + A_ALL;
-                for (int p = tid; p < NT * 8; p += TC_THREADS) {
-                    const int n = p >> 3, kcore = p & 7;
-                    const int tok = min(tb + n, jb.ntok - 1);
-                    const size_t src = (size_t)(g0 + tok) * C + kc * TC_KC;
-                    const uint32_t off = (n >> 3) * 1024 + kcore * 128 + (n & 7) * 16;
-                    *(uint4*)(sb_ + off) = __ldg((const uint4*)(a.xh + src) + kcore);
-                    if (SPLIT) *(uint4*)(sb_ + TC_B_BYTES + off) = __ldg((const uint4*)(a.xl + src) + kcore);
-                }
-            }
-            if (conv_active)
-                dequant_row_chunk<SPLIT>(mg, c0, c1, bf16_bits_to_f32(chs), bf16_bits_to_f32(chb), st + a_off,
-                                         st + a_off + TC_A_BYTES);
-            // make the generic-proxy writes visible to the tensor core (async proxy)
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncthreads();
-            if (tid == 0 && !failed) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t sa = smem_u32(st);
-                const uint32_t sbh = sa + A_ALL, sbl = sbh + TC_B_BYTES;
+        if (warp < 8) {
+            // ================= converters =================
+            uint4 ring[DEPTH][NMAT];
+            uint32_t rsc[DEPTH][NMAT], rbi[DEPTH][NMAT];   // raw loads only: no arithmetic until consumed
 #pragma unroll
-                for (int j = 0; j < TC_KC / 16; j++) {
-                    const uint64_t bh = umma_desc(sbh + j * 256, 128, 1024);
-                    const uint64_t bl = umma_desc(sbl + j * 256, 128, 1024);
-                    const uint32_t acc = (kc > 0 || j > 0) ? 1u : 0u;
+            for (int d = 0; d < DEPTH; d++)
+#pragma unroll
+                for (int m = 0; m < NMAT; m++) {
+                    const int kq = min(d, nchunks - 1);
+                    ring[d][m] = ld_stream_v4(cvals[m] + kq * 32);
+                    rsc[d][m] = ld_stream_u16(csc[m] + kq);
+                    rbi[d][m] = cbi[m] ? ld_stream_u16(cbi[m] + kq) : 0u;
+                }
+            for (int kc0 = 0; kc0 < nchunks; kc0 += DEPTH) {
+#pragma unroll
+                for (int d = 0; d < DEPTH; d++) {
+                    const int kc = kc0 + d;
+                    if (kc >= nchunks) break;
+                    const uint32_t s = it % STAGES;
+                    uint8_t* st = stage_base + s * STAGE_BYTES;
+                    // the MMAs that last read this stage must have completed
+                    const bool ok = it < (uint32_t)STAGES || mbar_wait(&bar_free[s], ((it / STAGES) - 1) & 1, fail);
+                    // take this chunk's packed data out of the ring and refill the slot DEPTH chunks ahead
+                    uint4 cur[NMAT];
+                    uint32_t cur_s[NMAT], cur_b[NMAT];
 #pragma unroll
                     for (int m = 0; m < NMAT; m++) {
-                        const uint32_t ah = sa + m * NPART * TC_A_BYTES + j * 256;
-                        const uint32_t d = tmem + m * 128;
-                        umma_f16(d, umma_desc(ah, 128, 1024), bh, idesc, acc);
-                        if (SPLIT) {
-                            umma_f16(d, umma_desc(ah + TC_A_BYTES, 128, 1024), bh, idesc, 1u);   // A_lo * B_hi
-                            umma_f16(d, umma_desc(ah, 128, 1024), bl, idesc, 1u);                // A_hi * B_lo
+                        cur[m] = ring[d][m];
+                        cur_s[m] = rsc[d][m];
+                        cur_b[m] = rbi[d][m];
+                        if (kc + DEPTH < nchunks) {
+                            ring[d][m] = ld_stream_v4(cvals[m] + (kc + DEPTH) * 32);
+                            rsc[d][m] = ld_stream_u16(csc[m] + kc + DEPTH);
+                            if (cbi[m]) rbi[d][m] = ld_stream_u16(cbi[m] + kc + DEPTH);
                         }
                     }
+                    if (ok) {
+#pragma unroll
+                        for (int m = 0; m < NMAT; m++) {
+                            uint8_t* dst = st + m * NPART * TC_A_BYTES + a_off;
+                            if (!SPLIT && fp16_path_ok(cur_s[m], cur_b[m]))
+                                dequant_half_chunk_f16(cur[m], cur_s[m], cur_b[m], dst, a_c0, a_sw);
+                            else
+                                dequant_half_chunk_f32<SPLIT>(mg, cur[m], cur_s[m], cur_b[m], dst, dst + TC_A_BYTES,
+                                                              a_c0, a_sw);
+                        }
+                    }
+                    // generic-proxy writes -> visible to the tensor core (async proxy), then one
+                    // arrival per warp (always, so the issuer never waits for a converter that gave up)
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bar_full[s]);
+                    it++;
                 }
-                umma_commit(&bar_free[s]);
-                if (kc == nchunks - 1) umma_commit(&bar_done);
+            }
+        } else {
+            // ================= issuer warp =================
+            const uint32_t idesc = umma_idesc_f16(128, NT);
+            for (int kc = 0; kc < nchunks; kc++, it++) {
+                const uint32_t s = it % STAGES, slot = it % NB;
+                bool ok = !*fail;
+                // stage s free again => so is the B slot of chunk it - STAGES: refill it
+                if (ok && it >= (uint32_t)STAGES) ok = mbar_wait(&bar_free[s], ((it / STAGES) - 1) & 1, fail);
+                if (ok && lane == 0 && it >= (uint32_t)STAGES && b_issued < total && b_issued == it - STAGES + NB) {
+                    issue_b(b_issued);
+                    b_issued++;
+                }
+                if (ok) ok = mbar_wait(&bar_full[s], (it / STAGES) & 1, fail);
+                if (ok) ok = mbar_wait(&bar_b[slot], (it / NB) & 1, fail);
+                if (ok && lane == 0) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t alo = a_lo0 + s * (STAGE_BYTES >> 4);
+                    const uint32_t blo = b_lo0 + slot * (slot_bytes >> 4);
+                    const uint32_t blo_l = blo + (part_bytes >> 4);
+#pragma unroll
+                    for (int j = 0; j < TC_KC / 16; j++) {
+                        const uint64_t bh = make_desc(blo + j * 2, DESC_B_HI);
+                        const uint32_t acc = (kc > 0 || j > 0) ? 1u : 0u;
+#pragma unroll
+                        for (int m = 0; m < NMAT; m++) {
+                            const uint32_t ah = alo + ((m * NPART * TC_A_BYTES + j * 32) >> 4);
+                            const uint32_t d = tmem + m * 128;
+                            umma_f16(d, make_desc(ah, DESC_B_HI), bh, idesc, acc);
+                            if (SPLIT) {
+                                // A_lo * B_hi, then A_hi * B_lo
+                                umma_f16(d, make_desc(ah + (TC_A_BYTES >> 4), DESC_B_HI), bh, idesc, 1u);
+                                umma_f16(d, make_desc(ah, DESC_B_HI), make_desc(blo_l + j * 2, DESC_B_HI), idesc, 1u);
+                            }
+                        }
+                    }
+                    umma_commit(&bar_free[s]);
+                    if (kc == nchunks - 1) umma_commit(&bar_done);
+                }
+                __syncwarp();
             }
         }
-        // ---- epilogue of this token pass ----
-        if (!failed && !mbar_wait(&bar_done, done_phase & 1)) failed = true;
-        done_phase++;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (warp < 4 && !failed) {
+
+        // ================= epilogue of this token pass (warps 0-3) =================
+        if (warp < 4 && mbar_wait(&bar_done, pass & 1, fail)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int m = r0 + warp * 32 + lane;
+            const int mpos = (m & ~7) | tc_kpos(m & 7);      // GeGLU output feeds the next GEMM's K
             const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
             for (int n0 = 0; n0 < NT; n0 += 32) {
                 uint32_t g[32];
@@ -316,8 +527,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) q4_gemm_tc_kernel(TcArgs a) {
                             const float act = 0.5f * gv * (1.0f + tanhf(inner));
                             const float o = act * uv;
                             const __half oh = __float2half_rn(o);
-                            a.out_h[(size_t)(g0 + tb + n) * jb.R + m] = oh;
-                            if (SPLIT) a.out_l[(size_t)(g0 + tb + n) * jb.R + m] = __float2half_rn(o - __half2float(oh));
+                            a.out_h[(size_t)(g0 + tb + n) * jb.R + mpos] = oh;
+                            if (SPLIT)
+                                a.out_l[(size_t)(g0 + tb + n) * jb.R + mpos] = __float2half_rn(o - __half2float(oh));
                         }
                     }
                 } else {
@@ -332,78 +544,126 @@ __global__ void __launch_bounds__(TC_THREADS, 1) q4_gemm_tc_kernel(TcArgs a) {
         // all accumulator reads of this pass precede the next pass' first MMA
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (*fail) break;
     }
-    if (failed && a.status) atomicOr(a.status, SB_ERR_TIMEOUT);
-    // wait (bounded) for any MMAs still in flight before releasing TMEM and shared memory
-    if (tid == 0 && it > 0) {
-        const uint32_t last = it - 1;
-        (void)mbar_wait(&bar_free[last % STAGES], (last / STAGES) & 1);
+    if (*fail) {
+        if (tid == 0 && a.status) atomicOr(a.status, SB_ERR_TIMEOUT);
+        // wait (bounded, no early exit) for MMAs and TMA copies still in flight before releasing
+        // TMEM and shared memory
+        if (tid == TC_CONVERTERS) {
+            int none = 0;
+            if (it > 0) (void)mbar_wait(&bar_free[(it - 1) % STAGES], ((it - 1) / STAGES) & 1, &none);
+            for (uint32_t t = (b_issued > NB ? b_issued - NB : 0); t < b_issued; t++)
+                (void)mbar_wait(&bar_b[t % NB], (t / NB) & 1, &none);
+        }
+        __syncthreads();
     }
-    __syncthreads();
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
     }
 }
 
 // x (fp32, token rows) -> fp16 rows in grouped order: xh[g] = fp16(x[g2c[g] / topk]),
-// and (when xl != null) the residuals xl[g] = fp16(x - xh).
+// and (when xl != null) the residuals xl[g] = fp16(x - xh).  Columns inside every group
+// of 8 are written in the operands' K order.
 __global__ void __launch_bounds__(256)
 gather_convert_kernel(const float* __restrict__ x, const int32_t* __restrict__ g2c, __half* __restrict__ xh,
                       __half* __restrict__ xl, int topk, int hidden) {
     const int g = blockIdx.y;
-    const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (d >= hidden) return;
-    const float4 v = *(const float4*)(x + (size_t)(g2c[g] / topk) * hidden + d);
-    const __half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
-    __half2* o = (__half2*)(xh + (size_t)g * hidden + d);
-    o[0] = h0;
-    o[1] = h1;
-    if (xl) {
-        const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
-        __half2* l = (__half2*)(xl + (size_t)g * hidden + d);
-        l[0] = __floats2half2_rn(v.x - f0.x, v.y - f0.y);
-        l[1] = __floats2half2_rn(v.z - f1.x, v.w - f1.y);
+    const float* src = x + (size_t)(g2c[g] / topk) * hidden + d;
+    const float4 v0 = *(const float4*)src, v1 = *(const float4*)(src + 4);
+    const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    uint32_t hi[4], lo[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) {   // half2 k holds columns (k, k + 4)
+        hi[k] = f16x2_from(v[k], v[k + 4]);
+        lo[k] = f16x2_from(v[k] - f16_lo_to_f32(hi[k]), v[k + 4] - f16_hi_to_f32(hi[k]));
     }
+    *(uint4*)(xh + (size_t)g * hidden + d) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    if (xl) *(uint4*)(xl + (size_t)g * hidden + d) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
 }
 
 cudaError_t launch_gather_convert(const float* x, const int32_t* g2c, void* xh, void* xl, int jobs, int topk,
                                   int hidden, cudaStream_t stream) {
     if (jobs < 1) return cudaSuccess;
-    dim3 grid((hidden / 4 + 255) / 256, jobs);
+    if (hidden % 8) return cudaErrorInvalidValue;
+    dim3 grid((hidden / 8 + 255) / 256, jobs);
     gather_convert_kernel<<<grid, 256, 0, stream>>>(x, g2c, (__half*)xh, (__half*)xl, topk, hidden);
     return cudaGetLastError();
 }
 
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                      const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                      CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// Tensor maps over a [rows][cols] fp16 buffer (and its residual buffer): boxes of 64
+// columns x 16 / 32 / 64 / 128 rows, 128-byte swizzle, zero fill past the last row.
+cudaError_t make_tc_maps(TcMaps* out, const void* hi, const void* lo, int rows, int cols) {
+    static TensorMapEncodeFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess) return e;
+        if (!fn || q != cudaDriverEntryPointSuccess) return cudaErrorNotSupported;
+        encode = (TensorMapEncodeFn)fn;
+    }
+    if ((cols % TC_KC) != 0 || rows < 1) return cudaErrorInvalidValue;
+    for (int v = 0; v < 4; v++)
+        for (int part = 0; part < 2; part++) {
+            const void* base = part ? lo : hi;
+            if (!base) return cudaErrorInvalidValue;
+            cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+            cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+            cuuint32_t box[2] = {(cuuint32_t)TC_KC, (cuuint32_t)(16 << v)};
+            cuuint32_t estr[2] = {1, 1};
+            CUresult r = encode(part ? &out->lo[v] : &out->hi[v], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                                const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+        }
+    return cudaSuccess;
+}
+
 template <bool FUSED, bool SPLIT>
-static cudaError_t launch_tc(const TcArgs& a, dim3 grid, cudaStream_t stream) {
-    constexpr int NMAT = FUSED ? 2 : 1, NPART = SPLIT ? 2 : 1;
-    constexpr int STAGES = (FUSED && SPLIT) ? 2 : TC_STAGES;
-    // at least 116 KB of dynamic shared memory keeps one block per SM, so a block's 256 TMEM
-    // columns can always be allocated without waiting for a neighbour
-    size_t smem = (size_t)STAGES * (NMAT * NPART * TC_A_BYTES + NPART * TC_B_BYTES) + 1024;
-    if (smem < 120 * 1024) smem = 120 * 1024;
+static cudaError_t launch_tc(const TcArgs& a, const TcMaps& maps, dim3 grid, cudaStream_t stream) {
+    // the full dynamic shared memory keeps one block per SM, so a block's 256 TMEM columns
+    // can always be allocated without waiting for a neighbour
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(q4_gemm_tc_kernel<FUSED, SPLIT>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    q4_gemm_tc_kernel<FUSED, SPLIT><<<grid, TC_THREADS, smem, stream>>>(a);
+    q4_gemm_tc_kernel<FUSED, SPLIT><<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(a, maps);
     return cudaGetLastError();
 }
 
 cudaError_t launch_q4_gemm_tc(bool fused, bool split, const Q4Job* jobs, int njobs_max, const int* njobs_dev,
-                              const void* xh, const void* xl, const float* y_base, int y_cols, void* out_h,
-                              void* out_l, float* out_f, int R, int* status, cudaStream_t stream) {
+                              const TcMaps& bmaps, const float* y_base, int y_cols, void* out_h, void* out_l,
+                              float* out_f, int R, int* status, cudaStream_t stream) {
     if (njobs_max < 1) return cudaSuccess;
     TcArgs a;
-    a.jobs = jobs; a.njobs_dev = njobs_dev; a.xh = (const __half*)xh; a.xl = (const __half*)xl;
+    a.jobs = jobs; a.njobs_dev = njobs_dev;
     a.y_base = y_base; a.y_cols = y_cols;
     a.out_h = (__half*)out_h; a.out_l = (__half*)out_l; a.out_f = out_f; a.status = status;
+    static int n_sm = 0;
+    if (!n_sm) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm < 1) n_sm = 148;
+    }
+    a.prefetch_ahead = n_sm;
     dim3 grid((R + 127) / 128, njobs_max);
-    if (fused) return split ? launch_tc<true, true>(a, grid, stream) : launch_tc<true, false>(a, grid, stream);
-    return split ? launch_tc<false, true>(a, grid, stream) : launch_tc<false, false>(a, grid, stream);
+    if (fused)
+        return split ? launch_tc<true, true>(a, bmaps, grid, stream) : launch_tc<true, false>(a, bmaps, grid, stream);
+    return split ? launch_tc<false, true>(a, bmaps, grid, stream) : launch_tc<false, false>(a, bmaps, grid, stream);
 }
 
 }  // namespace sb
+
