@@ -41,6 +41,41 @@ def test_exact_cells_router_chain_golden():
     assert g.shared_buffer_free(buf) == 0
 
 
+@pytest.mark.parametrize("kind", ["normal", "wide_range", "ties", "subnormal_squares", "sparse", "powers_of_two"])
+def test_ordered_sum_of_squares_adversarial_rows(orc, kind):
+    """RMSNorm and router-input cells on rows built to stress the in-order sum of squares:
+    half-way cases, subnormal squares, zeros and terms spread over many binades."""
+    g, bm = gpu(), backend_mod()
+    rng = np.random.default_rng(abs(hash(kind)) % (1 << 31))
+    nmax = 5000
+    rc, buf = g.shared_buffer_alloc(4 * (3 * nmax + 16))
+    assert rc == 0
+    f = buf.array(np.float32)
+    for n in (1, 2, 63, 64, 65, 257, 1024, 1025, 2816, 5000):
+        if kind == "normal":
+            x = rng.standard_normal(n)
+        elif kind == "wide_range":
+            x = rng.standard_normal(n) * 10.0 ** rng.uniform(-18, 12, n)
+        elif kind == "ties":
+            x = rng.integers(0, 64, n) * 2.0 ** -10
+        elif kind == "subnormal_squares":
+            x = rng.standard_normal(n) * 1e-20
+        elif kind == "sparse":
+            x = np.where(rng.random(n) < 0.6, 0.0, rng.standard_normal(n))
+        else:
+            x = np.sign(rng.standard_normal(n)) * 2.0 ** rng.integers(-8, 8, n)
+        x = x.astype(np.float32)
+        w = (1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+        f[0:n] = x
+        f[nmax:nmax + n] = w
+        for cell_kind, name in ((bm.EXACT_RMSNORM, "rmsnorm"), (bm.EXACT_ROUTER_INPUT, "router input")):
+            cell = bm.exact_cell(cell_kind, [buf] * 3, [0, nmax, 2 * nmax], n, aux=1, eps=1e-6)
+            assert g.exact_cells([cell]) == 0, (kind, n, name)
+            want = orc.rmsnorm(x, w, 1e-6)[1] if cell_kind == bm.EXACT_RMSNORM else orc.router_input(x, w, 1e-6)[1]
+            assert_bits_equal(f[2 * nmax:2 * nmax + n].copy(), want, f"{name} {kind} n={n}")
+    assert g.shared_buffer_free(buf) == 0
+
+
 def test_route_group_device_golden_and_reference_kat(orc):
     import torch
     g = gpu()
