@@ -50,11 +50,15 @@ def parse():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="budget of the CPU baseline sample")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--prefill", default=None, choices=["exact", "single", "split"],
+                    help="run the layers one by one with the expert projections on the exact kernels, or on the "
+                         "tensor cores with operands rounded to fp16 once (single) or carried as hi+lo halves (split)")
     return ap.parse_args()
 
 
 def workload_config(args, world):
-    return {"workload": "cfg2 MoE-FFN layer decode (H2816 E128 top8 M704, affine-Q4 g64, fp32 router), "
+    kind = "decode" if not args.prefill else f"prefill ({args.prefill} expert projections)"
+    return {"workload": f"cfg2 MoE-FFN layer {kind} (H2816 E128 top8 M704, affine-Q4 g64, fp32 router), "
                         "run as the cfg5 30-layer stack with RMSNorm between layers",
             "batch_per_gpu": args.batch, "global_batch": args.batch * world, "layers": args.layers,
             "parallelism": f"ep{world}" if world > 1 else "single",
@@ -236,13 +240,26 @@ def run_b200(args):
         """Expert-parallel pass: one exchange of the grouped expert outputs per layer."""
         ep.forward(stack, grouped, src, B, dst, act, stream=sp)
 
-    use_graph = world == 1 and not args.no_graph
+    tc_mode = {None: False, "exact": False, "single": "single", "split": "split"}[args.prefill]
+
+    def forward_layers(src, dst):
+        """Layer by layer through the two-phase entry points (the only way to pick the projection kernels)."""
+        cur = src.data_ptr()
+        for l in range(L):
+            out = dst if l == L - 1 else act[l & 1]
+            assert stack.layer_experts(l, cur, B, router_input_ready=l > 0, tensor_core=tc_mode, stream=sp) == 0
+            assert stack.layer_combine(l, B, out.data_ptr(), apply_norm=True, prepare_next=l + 1 < L, stream=sp) == 0
+            cur = out.data_ptr()
+
+    use_graph = world == 1 and not args.no_graph and not args.prefill
     with torch.cuda.stream(stream):
         n0 = stack.launch_count()
-        if world == 1:
-            assert stack.forward_device(d_x.data_ptr(), B, d_y.data_ptr(), stream=sp) == 0
-        else:
+        if world > 1:
             forward_ep(d_x, d_y)
+        elif args.prefill:
+            forward_layers(d_x, d_y)
+        else:
+            assert stack.forward_device(d_x.data_ptr(), B, d_y.data_ptr(), stream=sp) == 0
         launches_per_step = stack.launch_count() - n0
         assert stack.status(sp) == 0
         if use_graph:
@@ -251,10 +268,12 @@ def run_b200(args):
         def step():
             if use_graph:
                 assert stack.graph_launch(sp) == 0
-            elif world == 1:
-                assert stack.forward_device(d_x.data_ptr(), B, d_y.data_ptr(), stream=sp) == 0
-            else:
+            elif world > 1:
                 forward_ep(d_x, d_y)
+            elif args.prefill:
+                forward_layers(d_x, d_y)
+            else:
+                assert stack.forward_device(d_x.data_ptr(), B, d_y.data_ptr(), stream=sp) == 0
 
         def timed(fn, steps):
             if world > 1:
@@ -287,17 +306,20 @@ def run_b200(args):
         h_out = torch.empty_like(h_in).pin_memory()
 
         def e2e_step():
-            if world == 1:
+            if world == 1 and not args.prefill:
                 stack.forward_host(x_host)
             else:
                 d_x.copy_(h_in, non_blocking=True)
-                forward_ep(d_x, d_y)
+                if world > 1:
+                    forward_ep(d_x, d_y)
+                else:
+                    forward_layers(d_x, d_y)
                 h_out.copy_(d_y, non_blocking=True)
                 stream.synchronize()
 
         for _ in range(3):
             e2e_step()
-        if world == 1:
+        if world == 1 and not args.prefill:
             torch.cuda.synchronize()
             t0 = time.perf_counter()
             for _ in range(args.steps):
@@ -311,7 +333,10 @@ def run_b200(args):
         if world == 1:
             stack.profile(True, max_launches=launches_per_step * args.steps + 16)
             for _ in range(args.steps):
-                assert stack.forward_device(d_x.data_ptr(), B, d_y.data_ptr(), stream=sp) == 0
+                if args.prefill:
+                    forward_layers(d_x, d_y)
+                else:
+                    assert stack.forward_device(d_x.data_ptr(), B, d_y.data_ptr(), stream=sp) == 0
             prof = stack.profile_read()
             stack.profile(False, 0)
             # distinct experts per layer (decides the algorithmic bytes of a launch)
@@ -343,11 +368,17 @@ def run_b200(args):
             peak = float(peaks.get("hbm_gbs", 6650.0))
             achieved = alg / (gu["us_per_launch"] * 1e-6) / 1e9
             dn = kernels["down"]
-            roofline = {"bound": "hbm", "kernel": "q4_tile_kernel<2,TT> (fused gate/up + GeGLU)",
+            # DRAM bytes of one gate/up launch from the ncu capture of this kernel (read + write,
+            # 2.241 MB per distinct expert at B=1: profiles/q4_tile_kernel_decode_b1.md); scales with
+            # the distinct experts of a launch, so it is only reported for the decode kernel at B=1
+            traffic = mean_distinct * 2_240_992.0 if (B == 1 and not tc_mode) else None
+            kname = ("q4_gemm_tc_kernel<fused> (tcgen05 gate/up + GeGLU)" if tc_mode
+                     else "q4_tile_kernel<2,TT> (fused gate/up + GeGLU)")
+            roofline = {"bound": "hbm", "kernel": kname,
                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                         "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback 6650 GB/s",
                         "algorithmic_bytes_per_launch": alg, "us_per_launch": gu["us_per_launch"],
-                        "mean_distinct_experts": mean_distinct, "traffic": None,
+                        "mean_distinct_experts": mean_distinct, "traffic": traffic,
                         "down_kernel": {"achieved": (mean_distinct * TENSOR_BYTES + B * K * (M + H) * 4)
                                         / (dn["us_per_launch"] * 1e-6) / 1e9,
                                         "us_per_launch": dn["us_per_launch"]}}
@@ -359,7 +390,9 @@ def run_b200(args):
            "clocks": clocks,
            "e2e": {"value": B * L / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": B * H * 4,
                    "d2h_bytes_per_step": B * H * 4, "ms_per_step": ms_e2e,
-                   "api": "salt_b200_stack_forward_host" if world == 1 else "layer_experts/all_reduce/layer_combine"},
+                   "api": ("salt_b200_stack_forward_host" if world == 1 and not args.prefill else
+                           "salt_b200_layer_experts / salt_b200_layer_combine per layer" if world == 1 else
+                           "layer_experts/all_reduce/layer_combine")},
            "gpu_launches": launches_per_step * args.steps,
            "launch_mode": "cuda graph replay" if use_graph else "stream launches",
            "us_per_layer": 1e3 * ms_step / L}

@@ -19,8 +19,7 @@
 //                           K-major 128-byte-swizzled tile layout;
 //                           packed weights come through a 4-chunk-deep register ring;
 //                           one elected mbarrier arrive per warp marks the stage full
-//   warp 8 (issuer)         prefetches the tile's weights into L2, feeds the tokens' fp16
-//                           activations by TMA (cp.async.bulk.tensor, 128-byte swizzle)
+//   warp 8 (issuer)         feeds the tokens' fp16 activations by TMA (cp.async.bulk.tensor, 128-byte swizzle)
 //                           into a ring of B tiles several chunks ahead, issues the
 //                           tcgen05.mma.kind::f16 (M128 x N x K16) of every full stage
 //                           and tcgen05.commit on the stage's "free" mbarrier
@@ -108,17 +107,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
             "r"(dst),
         "l"((uint64_t)map), "r"(x), "r"(y), "r"(smem_u32(bar))
         : "memory");
-}
-
-// Hint: bring [p, p + bytes) into L2 with large sequential DRAM reads (16-byte granules,
-// rounded inward).  The tile's later 16-byte loads, scattered over 128 rows, then hit L2.
-__device__ __forceinline__ void l2_prefetch_range(const void* p, size_t bytes) {
-    uintptr_t b = ((uintptr_t)p + 15) & ~(uintptr_t)15, e = ((uintptr_t)p + bytes) & ~(uintptr_t)15;
-    while (b < e) {
-        const uint32_t n = (uint32_t)min((size_t)(e - b), (size_t)16384);
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(b), "r"(n) : "memory");
-        b += n;
-    }
 }
 
 // Ring loads as volatile asm: an ordinary read-only load is an invariant load to the
@@ -279,7 +267,6 @@ struct TcArgs {
     __half* out_l;             // its fp16 residual (split precision) or null
     float* out_f;              // plain: projection output [grouped rows][R] fp32
     int* status;
-    int prefetch_ahead;        // blocks between a tile and the one whose weights it prefetches into L2
 };
 
 template <bool FUSED, bool SPLIT>
@@ -375,31 +362,6 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps) {
     if (warp == 8) {
         if (lane == 0)
             for (; b_issued < total && b_issued < NB; b_issued++) issue_b(b_issued);
-        // L2 prefetch of the weights of this tile and of the tile `prefetch_ahead` blocks later
-        // in launch order (whichever SM runs it, L2 is shared): large sequential DRAM reads.
-        const int njobs_live = a.njobs_dev ? *a.njobs_dev : (int)gridDim.y;
-        for (int which = 0; which < 2; which++) {
-            const uint32_t lin = blockIdx.y * gridDim.x + blockIdx.x + (which ? (uint32_t)a.prefetch_ahead : 0u);
-            const int py = (int)(lin / gridDim.x), px = (int)(lin % gridDim.x);
-            if (py >= njobs_live || (which && a.prefetch_ahead <= 0)) break;
-            const Q4Job pj = which ? a.jobs[py] : jb;
-            const int pr0 = px * 128;
-            if (pr0 >= pj.R) continue;
-            const size_t prow = (size_t)min(128, pj.R - pr0);
-            const size_t vb = (size_t)(pj.C >> 1), gb = (size_t)(pj.C / TC_KC) * 2;
-            const uint8_t* reg = nullptr;
-            size_t len = 0;
-            switch (lane) {   // one region per lane
-                case 0: reg = pj.vals + pr0 * vb; len = prow * vb; break;
-                case 1: reg = pj.scales + pr0 * gb; len = prow * gb; break;
-                case 2: if (pj.biases) { reg = pj.biases + pr0 * gb; len = prow * gb; } break;
-                case 3: if (FUSED) { reg = pj.vals2 + pr0 * vb; len = prow * vb; } break;
-                case 4: if (FUSED) { reg = pj.scales2 + pr0 * gb; len = prow * gb; } break;
-                case 5: if (FUSED && pj.biases2) { reg = pj.biases2 + pr0 * gb; len = prow * gb; } break;
-                default: break;
-            }
-            if (reg) l2_prefetch_range(reg, len);
-        }
         __syncwarp();
     }
 
@@ -652,13 +614,6 @@ cudaError_t launch_q4_gemm_tc(bool fused, bool split, const Q4Job* jobs, int njo
     a.jobs = jobs; a.njobs_dev = njobs_dev;
     a.y_base = y_base; a.y_cols = y_cols;
     a.out_h = (__half*)out_h; a.out_l = (__half*)out_l; a.out_f = out_f; a.status = status;
-    static int n_sm = 0;
-    if (!n_sm) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm < 1) n_sm = 148;
-    }
-    a.prefetch_ahead = n_sm;
     dim3 grid((R + 127) / 128, njobs_max);
     if (fused)
         return split ? launch_tc<true, true>(a, bmaps, grid, stream) : launch_tc<true, false>(a, bmaps, grid, stream);
