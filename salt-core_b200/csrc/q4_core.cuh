@@ -105,6 +105,9 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
 // logic operation; written with two literals the compiler emits two.
 __constant__ uint32_t c_nibble_magic[4] = {0x4b000000u, 0x49000000u, 0x47000000u, 0x45000000u};
 
+// -0.0f, kept out of the compiler's sight (see product_then_add in q4_kernels.cu).
+__constant__ uint32_t c_neg_zero = 0x80000000u;
+
 struct NibbleMagic {
     uint32_t m0, m1, m2, m3;
 };

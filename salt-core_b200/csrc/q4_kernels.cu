@@ -44,17 +44,14 @@ static __host__ __device__ __forceinline__ TileGeom tile_geom(int C, int rows_a)
     return g;
 }
 
-// Why the accumulate is a scalar add: ptxas contracts mul.rn.f32x2 followed by
-// add.rn.f32x2 (and even fma.rn.f32x2 with a multiplier of 1) into one fused
-// multiply-add, which changes the last bit; the scalar add.rn.f32 is never a
-// contraction candidate, and results with it are bit-identical to the reference
-// order.  Accumulators therefore live in scalar registers; products come out of
-// the packed multiply as register pairs, which costs nothing to split.
-__device__ __forceinline__ void mul_then_add(float& a0, float& a1, f32x2 d, f32x2 x) {
-    float p0, p1;
-    unpack2(mul2(d, x), p0, p1);
-    a0 = __fadd_rn(a0, p0);
-    a1 = __fadd_rn(a1, p1);
+// acc = fl(acc + fl(d * x)) on register pairs.  ptxas contracts a packed multiply followed
+// by a packed add (and even a packed fma with a multiplier of 1) into one fused
+// multiply-add, which changes the last bit.  The product is therefore formed as
+// fma(d, x, -0): adding -0 leaves every product, signed zeros included, unchanged, a fused
+// multiply-add cannot be merged into the following add, and the -0 comes from constant
+// memory so that the compiler cannot simplify the fma back into a multiply.
+__device__ __forceinline__ void product_then_add(f32x2& acc, f32x2 d, f32x2 x, f32x2 negzero) {
+    acc = add2(acc, fma2(d, x, negzero));
 }
 
 // NSTEPS consecutive 32-column steps (NSTEPS even, compile-time) of the thread's
@@ -65,7 +62,7 @@ __device__ __forceinline__ void mul_then_add(float& a0, float& a1, f32x2 d, f32x
 template <int TT, bool LIT, int NSTEPS>
 __device__ __forceinline__ void tile_steps(const NibbleMagic& mg, const uint8_t* wA, const uint8_t* wB,
                                            const uint32_t* tA, const uint32_t* tB, const float* const (&xs)[TT],
-                                           float (&accA)[TT][4], float (&accB)[TT][4]) {
+                                           f32x2 (&accA)[TT][2], f32x2 (&accB)[TT][2], f32x2 nz) {
 #pragma unroll
     for (int g = 0; g < NSTEPS / 2; g++) {
         const uint32_t wa = tA[g], wb = tB[g];
@@ -83,10 +80,10 @@ __device__ __forceinline__ void tile_steps(const NibbleMagic& mg, const uint8_t*
 #pragma unroll
             for (int tt = 0; tt < TT; tt++) {
                 const ulonglong2 xv = *(const ulonglong2*)(xs[tt] + k * 32);
-                mul_then_add(accA[tt][0], accA[tt][1], dA01, xv.x);
-                mul_then_add(accA[tt][2], accA[tt][3], dA23, xv.y);
-                mul_then_add(accB[tt][0], accB[tt][1], dB01, xv.x);
-                mul_then_add(accB[tt][2], accB[tt][3], dB23, xv.y);
+                product_then_add(accA[tt][0], dA01, xv.x, nz);
+                product_then_add(accA[tt][1], dA23, xv.y, nz);
+                product_then_add(accB[tt][0], dB01, xv.x, nz);
+                product_then_add(accB[tt][1], dB23, xv.y, nz);
             }
         }
     }
@@ -97,20 +94,20 @@ template <int TT, bool LIT>
 __device__ __forceinline__ void tile_run(const NibbleMagic& mg, int s_begin, int s_end, const uint8_t* wA,
                                          const uint8_t* wB, const uint32_t* tA, const uint32_t* tB,
                                          const float* sX, int x_pitch,
-                                         float (&accA)[TT][4], float (&accB)[TT][4]) {
+                                         f32x2 (&accA)[TT][2], f32x2 (&accB)[TT][2], f32x2 nz) {
     int st = s_begin;
     constexpr int BLK = 8;
     for (; st + BLK <= s_end; st += BLK) {
         const float* xs[TT];
 #pragma unroll
         for (int tt = 0; tt < TT; tt++) xs[tt] = sX + tt * x_pitch + st * 32;
-        tile_steps<TT, LIT, BLK>(mg, wA + st * 16, wB + st * 16, tA + (st >> 1), tB + (st >> 1), xs, accA, accB);
+        tile_steps<TT, LIT, BLK>(mg, wA + st * 16, wB + st * 16, tA + (st >> 1), tB + (st >> 1), xs, accA, accB, nz);
     }
     for (; st + 2 <= s_end; st += 2) {
         const float* xs[TT];
 #pragma unroll
         for (int tt = 0; tt < TT; tt++) xs[tt] = sX + tt * x_pitch + st * 32;
-        tile_steps<TT, LIT, 2>(mg, wA + st * 16, wB + st * 16, tA + (st >> 1), tB + (st >> 1), xs, accA, accB);
+        tile_steps<TT, LIT, 2>(mg, wA + st * 16, wB + st * 16, tA + (st >> 1), tB + (st >> 1), xs, accA, accB, nz);
     }
 }
 
@@ -223,6 +220,7 @@ q4_tile_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_dev
     const uint32_t* tA = sT + pr * tpitch;
     const uint32_t* tB = sT + (pr + 8) * tpitch;
     const NibbleMagic mg = load_nibble_magic();
+    const f32x2 nz = pack2u(c_neg_zero, c_neg_zero);
     const float* xs = sX + 4 * u;
 
     // wait for group 0, interleave the bf16 scales/biases of the 16 rows into one
@@ -250,11 +248,11 @@ q4_tile_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_dev
             cp_async_wait_dyn(0);
             __syncthreads();
         }
-        float accA[TT][4], accB[TT][4];
+        f32x2 accA[TT][2], accB[TT][2];
 #pragma unroll
         for (int tt = 0; tt < TT; tt++)
 #pragma unroll
-            for (int j = 0; j < 4; j++) { accA[tt][j] = 0.0f; accB[tt][j] = 0.0f; }
+            for (int j = 0; j < 2; j++) { accA[tt][j] = pack2(0.0f, 0.0f); accB[tt][j] = pack2(0.0f, 0.0f); }
         for (int ch = 0; ch < G.nch; ch++) {
             if (tb == 0 && ch > 0) {
                 cp_async_wait_dyn(G.nch - 1 - ch);
@@ -263,18 +261,278 @@ q4_tile_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_dev
             const int s_begin = ch * G.chunk_steps;
             const int s_end = min(s_begin + G.chunk_steps, G.steps);
 #ifndef SB_EXP_NOCOMPUTE
-            if (lit) tile_run<TT, true>(mg, s_begin, s_end, wA, wB, tA, tB, xs, C, accA, accB);
-            else tile_run<TT, false>(mg, s_begin, s_end, wA, wB, tA, tB, xs, C, accA, accB);
-#else
-            accA[0][0] += *(const float*)(wA + s_begin * 16) + (float)lit;
+            if (lit) tile_run<TT, true>(mg, s_begin, s_end, wA, wB, tA, tB, xs, C, accA, accB, nz);
+            else tile_run<TT, false>(mg, s_begin, s_end, wA, wB, tA, tB, xs, C, accA, accB, nz);
 #endif
         }
 #pragma unroll
         for (int tt = 0; tt < TT; tt++) {
-            const float y0 = fold_row_octants(accA[tt], u);
-            const float y1 = fold_row_octants(accB[tt], u);
+            float fa[4], fb[4];
+            unpack2(accA[tt][0], fa[0], fa[1]); unpack2(accA[tt][1], fa[2], fa[3]);
+            unpack2(accB[tt][0], fb[0], fb[1]); unpack2(accB[tt][1], fb[2], fb[3]);
+            const float y0 = fold_row_octants(fa, u);
+            const float y1 = fold_row_octants(fb, u);
             const int tok = tb + tt;
             if (u == 7 && tok < jb.ntok) {
+                float* yrow = jb.y + (size_t)tok * jb.y_stride;
+                if (NMAT == 2) {
+                    // fused GeGLU (reference gemma4.c:80-83 then gate*up)
+                    if (pr < nvalid) yrow[r0 + pr] = __fmul_rn(gelu_tanh_exact(y0), y1);
+                } else {
+                    if (pr < nvalid) yrow[r0 + pr] = y0;
+                    if (pr + 8 < nvalid) yrow[r0 + pr + 8] = y1;
+                }
+            }
+        }
+    }
+}
+
+// ---- 16 lanes per row ---------------------------------------------------------------
+// Same tile, same shared-memory layout and the same row DAG, but a row's 32 accumulators are
+// spread over SIXTEEN adjacent lanes (lane v = tid & 15 holds acc[2v], acc[2v + 1], i.e. one
+// packed byte per 32-column step), so a block is 128 threads = 4 warps and every SM holds
+// twice the warps of the 8-lane form: the kernel is bound by instruction latency, not by
+// bandwidth or issue slots, and more warps in flight is what hides it.
+
+// One packed byte (two nibbles) as exact floats.
+template <bool LIT>
+__device__ __forceinline__ f32x2 dequant2(uint32_t b, const NibbleMagic& mg, f32x2 ss, f32x2 bb) {
+    const f32x2 neg01 = pack2(-8388608.0f, -524288.0f);
+    uint32_t f0, f1;
+    asm("lop3.b32 %0, %1, 0x0f, %2, 0xEA;" : "=r"(f0) : "r"(b), "r"(mg.m0));
+    asm("lop3.b32 %0, %1, 0xf0, %2, 0xEA;" : "=r"(f1) : "r"(b), "r"(mg.m1));
+    const f32x2 q = add2(pack2u(f0, f1), neg01);
+    if (LIT) {
+        float p0, p1, b0, b1;
+        unpack2(mul2(q, ss), p0, p1);
+        unpack2(bb, b0, b1);
+        return pack2(__fadd_rn(p0, b0), __fadd_rn(p1, b1));
+    }
+    return fma2(q, ss, bb);
+}
+
+template <int TT, bool LIT, int NSTEPS>
+__device__ __forceinline__ void tile16_steps(const NibbleMagic& mg, const uint8_t* wA, const uint8_t* wB,
+                                             const uint32_t* tA, const uint32_t* tB, const float* const (&xs)[TT],
+                                             f32x2 (&accA)[TT], f32x2 (&accB)[TT], f32x2 nz) {
+#pragma unroll
+    for (int g = 0; g < NSTEPS / 2; g++) {
+        const uint32_t wa = tA[g], wb = tB[g];
+        const float sa = __uint_as_float(wa & 0xffff0000u), ba = __uint_as_float(wa << 16);
+        const float sb_ = __uint_as_float(wb & 0xffff0000u), bb_ = __uint_as_float(wb << 16);
+        const f32x2 ssA = pack2(sa, sa), bbA = pack2(ba, ba), ssB = pack2(sb_, sb_), bbB = pack2(bb_, bb_);
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            const int k = 2 * g + half;
+            const f32x2 dA = dequant2<LIT>(wA[k * 16], mg, ssA, bbA);
+            const f32x2 dB = dequant2<LIT>(wB[k * 16], mg, ssB, bbB);
+#pragma unroll
+            for (int tt = 0; tt < TT; tt++) {
+                const f32x2 xv = *(const f32x2*)(xs[tt] + k * 32);
+                product_then_add(accA[tt], dA, xv, nz);
+                product_then_add(accB[tt], dB, xv, nz);
+            }
+        }
+    }
+}
+
+template <int TT, bool LIT>
+__device__ __forceinline__ void tile16_run(const NibbleMagic& mg, int s_begin, int s_end, const uint8_t* wA,
+                                           const uint8_t* wB, const uint32_t* tA, const uint32_t* tB,
+                                           const float* sX, int x_pitch, f32x2 (&accA)[TT], f32x2 (&accB)[TT],
+                                           f32x2 nz) {
+    int st = s_begin;
+    constexpr int BLK = 8;
+    for (; st + BLK <= s_end; st += BLK) {
+        const float* xs[TT];
+#pragma unroll
+        for (int tt = 0; tt < TT; tt++) xs[tt] = sX + tt * x_pitch + st * 32;
+        tile16_steps<TT, LIT, BLK>(mg, wA + st * 16, wB + st * 16, tA + (st >> 1), tB + (st >> 1), xs, accA, accB, nz);
+    }
+    for (; st + 2 <= s_end; st += 2) {
+        const float* xs[TT];
+#pragma unroll
+        for (int tt = 0; tt < TT; tt++) xs[tt] = sX + tt * x_pitch + st * 32;
+        tile16_steps<TT, LIT, 2>(mg, wA + st * 16, wB + st * 16, tA + (st >> 1), tB + (st >> 1), xs, accA, accB, nz);
+    }
+}
+
+// Canonical fold (src/kernels.c:240-250) of a row whose accumulators sit two per lane in
+// sixteen adjacent lanes: L_j = sum over a = 0..7 of acc[4a + j], added in that order from
+// +0, then y = (L0 + L2) + (L1 + L3).  acc[4a + j] is component j & 1 of lane 2a + (j >> 1).
+__device__ __forceinline__ float fold_row_hexadecants(f32x2 acc, int v) {
+    float lo, hi;
+    unpack2(acc, lo, hi);
+    const int j = v & 3;
+    const int base = (threadIdx.x & 31) & ~15;
+    float L = 0.0f;
+#pragma unroll
+    for (int a = 0; a < 8; a++) {
+        const int src = base + 2 * a + (j >> 1);
+        const float vlo = __shfl_sync(0xffffffffu, lo, src);
+        const float vhi = __shfl_sync(0xffffffffu, hi, src);
+        L = __fadd_rn(L, (j & 1) ? vhi : vlo);
+    }
+    const float L0 = __shfl_sync(0xffffffffu, L, base + 0);
+    const float L1 = __shfl_sync(0xffffffffu, L, base + 1);
+    const float L2 = __shfl_sync(0xffffffffu, L, base + 2);
+    const float L3 = __shfl_sync(0xffffffffu, L, base + 3);
+    return __fadd_rn(__fadd_rn(L0, L2), __fadd_rn(L1, L3));
+}
+
+// One block = 128 threads = 8 row pairs (NMAT == 2: gate row r and up row r, fused GeGLU
+// epilogue) or 16 rows (NMAT == 1: rows r and r + 8 per lane group).
+template <int NMAT, int TT>
+__global__ void __launch_bounds__(128)
+q4_tile16_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_dev, int C) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    constexpr int NT = 128;
+    const int job_id = blockIdx.y;
+    if (njobs_dev != nullptr && job_id >= *njobs_dev) return;
+    const Q4Job jb = jobs[job_id];
+    constexpr int ROWS_A = (NMAT == 2) ? 8 : 16;
+    const int r0 = blockIdx.x * ROWS_A;
+    if (r0 >= jb.R || jb.ntok < 1) return;
+    const int tid = threadIdx.x;
+    const int v = tid & 15;                      // accumulators 2v, 2v + 1
+    const int pr = tid >> 4;                     // row slot 0..7
+    const int nvalid = min(ROWS_A, jb.R - r0);
+    const TileGeom G = tile_geom(C, ROWS_A);
+    uint8_t* sW = smem;                                   // [16][w_stride]
+    uint8_t* sS = sW + 16 * G.w_stride;                   // [NMAT][sc_block]
+    uint8_t* sBi = sS + NMAT * G.sc_block;                // [NMAT][sc_block]
+    uint32_t* sT = (uint32_t*)(sBi + NMAT * G.sc_block);  // [16][tpitch] (scale bf16 << 16) | bias bf16
+    const int tpitch = G.tpitch;
+    float* sX = (float*)(sT + 16 * tpitch);               // [TT][C]
+
+    // ---- group 0: activations of the first token block, scales, biases, K chunk 0 ----
+    auto issue_x = [&](int tb) {
+        const int ppr = C >> 2;                  // 16-byte pieces per activation row
+#pragma unroll
+        for (int tt = 0; tt < TT; tt++) {
+            const int tok = min(tb + tt, jb.ntok - 1);
+            const int row = jb.x_rows ? (jb.x_rows[tok] / jb.x_div) : tok;
+            const float* src = jb.x + (size_t)row * jb.x_stride;
+            for (int pc = tid; pc < ppr; pc += NT) cp_async16(sX + tt * C + pc * 4, src + pc * 4);
+        }
+    };
+    issue_x(0);
+#pragma unroll
+    for (int m = 0; m < NMAT; m++) {
+        const uint8_t* gs = (m == 0 ? jb.scales : jb.scales2) + (size_t)r0 * G.sc_row;
+        const uint8_t* gb = (m == 0 ? jb.biases : jb.biases2);
+        if (gb) gb += (size_t)r0 * G.sc_row;
+        uint8_t* ds = sS + m * G.sc_block;
+        uint8_t* db = sBi + m * G.sc_block;
+        if (G.sc_padded) {
+            const int ppr = G.sc_row >> 4;
+            for (int p = tid; p < nvalid * ppr; p += NT) {
+                const int rr = p / ppr, pc = p - rr * ppr;
+                cp_async16(ds + rr * G.sc_stride + pc * 16, gs + (size_t)rr * G.sc_row + pc * 16);
+                if (gb) cp_async16(db + rr * G.sc_stride + pc * 16, gb + (size_t)rr * G.sc_row + pc * 16);
+            }
+        } else {
+            const int total = nvalid * G.sc_row;
+            const int full = total >> 4;
+            for (int p = tid; p < full; p += NT) {
+                cp_async16(ds + p * 16, gs + p * 16);
+                if (gb) cp_async16(db + p * 16, gb + p * 16);
+            }
+            for (int i = (full << 4) + tid; i < total; i += NT) {
+                ds[i] = gs[i];
+                if (gb) db[i] = gb[i];
+            }
+        }
+        if (!gb)
+            for (int i = tid; i < (G.sc_block >> 2); i += NT) ((uint32_t*)db)[i] = 0u;
+    }
+    if (G.chunk_steps == 8) {
+        // 8-step chunks: a chunk is 16 rows x 8 pieces of 16 bytes = 128 copies, one per thread,
+        // and the thread's (row, piece) pair is the same in every chunk
+        const int pc = tid & 7, rr = tid >> 3;
+        const int m = (NMAT == 2) ? (rr >> 3) : 0;
+        const int grow = min(r0 + ((NMAT == 2) ? (rr & 7) : rr), jb.R - 1);
+        const uint8_t* gsrc = (m == 0 ? jb.vals : jb.vals2) + (size_t)grow * G.row_bytes + pc * 16;
+        uint8_t* dst = sW + rr * G.w_stride + pc * 16;
+        for (int ch = 0; ch < G.nch; ch++) {
+#ifndef SB_EXP_NOLOAD
+            if (ch * 8 + pc < G.steps) cp_async16(dst + ch * 128, gsrc + ch * 128);
+#endif
+            cp_async_commit();
+        }
+    } else {
+        for (int ch = 0; ch < G.nch; ch++) {
+            const int s_begin = ch * G.chunk_steps;
+            const int cs = min(G.chunk_steps, G.steps - s_begin);
+            for (int p = tid; p < 16 * cs; p += NT) {
+                const int rr = p / cs;
+                const int pc = p - rr * cs;
+                const int m = (NMAT == 2) ? (rr >> 3) : 0;
+                const int grow = min(r0 + ((NMAT == 2) ? (rr & 7) : rr), jb.R - 1);
+                const uint8_t* g = (m == 0 ? jb.vals : jb.vals2) + (size_t)grow * G.row_bytes + (s_begin + pc) * 16;
+                cp_async16(sW + rr * G.w_stride + (s_begin + pc) * 16, g);
+            }
+            cp_async_commit();
+        }
+    }
+
+    // ---- this thread's operands ----
+    const uint8_t* wA = sW + pr * G.w_stride + v;
+    const uint8_t* wB = sW + (pr + 8) * G.w_stride + v;
+    const int gpr = C >> 6;                      // quantisation groups per row
+    const uint32_t* tA = sT + pr * tpitch;
+    const uint32_t* tB = sT + (pr + 8) * tpitch;
+    const NibbleMagic mg = load_nibble_magic();
+    const f32x2 nz = pack2u(c_neg_zero, c_neg_zero);
+    const float* xs = sX + 2 * v;
+
+    // wait for group 0, interleave the bf16 scales/biases of the 16 rows into one word per
+    // group, and note whether any scale needs the literal (two-rounding) dequantisation
+    cp_async_wait_dyn(G.nch - 1);
+    __syncthreads();
+    int lit = 0;
+    for (int gg = tid & 7; gg < gpr; gg += 8) {
+        const int rr = tid >> 3;                 // 128 threads = 16 rows x 8 column phases
+        const int m = (NMAT == 2) ? (rr >> 3) : 0;
+        const int lr = (NMAT == 2) ? (rr & 7) : rr;
+        const uint32_t hs = ((const uint16_t*)(sS + m * G.sc_block + lr * G.sc_stride))[gg];
+        const uint32_t hb = ((const uint16_t*)(sBi + m * G.sc_block + lr * G.sc_stride))[gg];
+        sT[rr * tpitch + gg] = (hs << 16) | hb;
+        if (lr < nvalid) lit |= scale_needs_literal(hs) ? 1 : 0;
+    }
+    lit = __syncthreads_or(lit);
+
+    for (int tb = 0; tb < jb.ntok; tb += TT) {
+        if (tb > 0) {
+            __syncthreads();                     // everyone is done with the previous activations
+            issue_x(tb);
+            cp_async_commit();
+            cp_async_wait_dyn(0);
+            __syncthreads();
+        }
+        f32x2 accA[TT], accB[TT];
+#pragma unroll
+        for (int tt = 0; tt < TT; tt++) { accA[tt] = pack2(0.0f, 0.0f); accB[tt] = pack2(0.0f, 0.0f); }
+        for (int ch = 0; ch < G.nch; ch++) {
+            if (tb == 0 && ch > 0) {
+                cp_async_wait_dyn(G.nch - 1 - ch);
+                __syncthreads();
+            }
+            const int s_begin = ch * G.chunk_steps;
+            const int s_end = min(s_begin + G.chunk_steps, G.steps);
+#ifndef SB_EXP_NOCOMPUTE
+            if (lit) tile16_run<TT, true>(mg, s_begin, s_end, wA, wB, tA, tB, xs, C, accA, accB, nz);
+            else tile16_run<TT, false>(mg, s_begin, s_end, wA, wB, tA, tB, xs, C, accA, accB, nz);
+#else
+            accA[0] = add2(accA[0], pack2(*(const float*)(wA - v + s_begin * 16), (float)lit));
+#endif
+        }
+#pragma unroll
+        for (int tt = 0; tt < TT; tt++) {
+            const float y0 = fold_row_hexadecants(accA[tt], v);
+            const float y1 = fold_row_hexadecants(accB[tt], v);
+            const int tok = tb + tt;
+            if (v == 0 && tok < jb.ntok) {
                 float* yrow = jb.y + (size_t)tok * jb.y_stride;
                 if (NMAT == 2) {
                     // fused GeGLU (reference gemma4.c:80-83 then gate*up)
@@ -348,14 +606,14 @@ static cudaError_t launch_tile(const Q4Job* jobs, int njobs_max, const int* njob
     size_t smem = tile_smem_bytes(C, NMAT, TT);
     static size_t configured = 0;
     if (smem > 48 * 1024 && smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(q4_tile_kernel<NMAT, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(q4_tile16_kernel<NMAT, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)(200 * 1024));
         if (e != cudaSuccess) return e;
         configured = 200 * 1024;
     }
     constexpr int ROWS_A = NMAT == 2 ? 8 : 16;
     dim3 grid((max_rows + ROWS_A - 1) / ROWS_A, njobs_max);
-    q4_tile_kernel<NMAT, TT><<<grid, 64, smem, stream>>>(jobs, njobs_dev, C);
+    q4_tile16_kernel<NMAT, TT><<<grid, 128, smem, stream>>>(jobs, njobs_dev, C);
     return cudaGetLastError();
 }
 
