@@ -335,10 +335,20 @@ int salt_b200_layer_combine(void* stack, int layer, int B, float* d_y, int flags
     return 0;
 }
 
+// Keeps the stream busy for a fixed number of clock cycles (bounded loop, nothing is waited
+// for).  Used only while profiling: with the device occupied for about a millisecond the
+// host enqueues a whole pass of launches and event records ahead of it, so the event pairs
+// measure kernels that run back to back instead of kernels that wait for the host.
+__global__ void profile_head_start_kernel(long long cycles) {
+    const long long t0 = clock64();
+    for (int i = 0; i < (1 << 24) && clock64() - t0 < cycles; i++) { }
+}
+
 int salt_b200_stack_forward_device(void* stack, int first, int count, const float* d_x, int B, float* d_y,
                                    void* stream) {
     Stack* s = (Stack*)stack;
     if (!s || first < 0 || count < 1 || first + count > (int)s->layers.size() || !d_x || !d_y) return -1;
+    if (s->profile) profile_head_start_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(80000LL * count + 400000LL);
     const float* in = d_x;
     for (int i = 0; i < count; i++) {
         const bool last = i == count - 1;

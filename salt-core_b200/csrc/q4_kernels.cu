@@ -388,8 +388,10 @@ q4_tile16_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_d
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr int NT = 128;
     const int job_id = blockIdx.y;
-    if (njobs_dev != nullptr && job_id >= *njobs_dev) return;
+    // both loads are issued before the count is tested (blockIdx.y always indexes inside the job array)
+    const int njobs_live = njobs_dev != nullptr ? *njobs_dev : 0x7fffffff;
     const Q4Job jb = jobs[job_id];
+    if (job_id >= njobs_live) return;
     constexpr int ROWS_A = (NMAT == 2) ? 8 : 16;
     const int r0 = blockIdx.x * ROWS_A;
     if (r0 >= jb.R || jb.ntok < 1) return;
@@ -405,7 +407,22 @@ q4_tile16_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_d
     const int tpitch = G.tpitch;
     float* sX = (float*)(sT + 16 * tpitch);               // [TT][C]
 
-    // ---- group 0: activations of the first token block, scales, biases, K chunk 0 ----
+    // ---- group 0: K chunk 0, scales, biases, activations of the first token block (the weight
+    // copies go first: they need nothing but the job, while the activation rows may sit behind
+    // one more dependent load of the row table) ----
+    const bool fast_chunks = G.chunk_steps == 8;
+    // 8-step chunks: a chunk is 16 rows x 8 pieces of 16 bytes = 128 copies, one per thread,
+    // and the thread's (row, piece) pair is the same in every chunk
+    const int f_pc = tid & 7, f_rr = tid >> 3;
+    const int f_m = (NMAT == 2) ? (f_rr >> 3) : 0;
+    const int f_grow = min(r0 + ((NMAT == 2) ? (f_rr & 7) : f_rr), jb.R - 1);
+    const uint8_t* f_src = (f_m == 0 ? jb.vals : jb.vals2) + (size_t)f_grow * G.row_bytes + f_pc * 16;
+    uint8_t* f_dst = sW + f_rr * G.w_stride + f_pc * 16;
+    if (fast_chunks && f_pc < G.steps) {
+#ifndef SB_EXP_NOLOAD
+        cp_async16(f_dst, f_src);
+#endif
+    }
     auto issue_x = [&](int tb) {
         const int ppr = C >> 2;                  // 16-byte pieces per activation row
 #pragma unroll
@@ -416,7 +433,6 @@ q4_tile16_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_d
             for (int pc = tid; pc < ppr; pc += NT) cp_async16(sX + tt * C + pc * 4, src + pc * 4);
         }
     };
-    issue_x(0);
 #pragma unroll
     for (int m = 0; m < NMAT; m++) {
         const uint8_t* gs = (m == 0 ? jb.scales : jb.scales2) + (size_t)r0 * G.sc_row;
@@ -446,17 +462,12 @@ q4_tile16_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_d
         if (!gb)
             for (int i = tid; i < (G.sc_block >> 2); i += NT) ((uint32_t*)db)[i] = 0u;
     }
-    if (G.chunk_steps == 8) {
-        // 8-step chunks: a chunk is 16 rows x 8 pieces of 16 bytes = 128 copies, one per thread,
-        // and the thread's (row, piece) pair is the same in every chunk
-        const int pc = tid & 7, rr = tid >> 3;
-        const int m = (NMAT == 2) ? (rr >> 3) : 0;
-        const int grow = min(r0 + ((NMAT == 2) ? (rr & 7) : rr), jb.R - 1);
-        const uint8_t* gsrc = (m == 0 ? jb.vals : jb.vals2) + (size_t)grow * G.row_bytes + pc * 16;
-        uint8_t* dst = sW + rr * G.w_stride + pc * 16;
-        for (int ch = 0; ch < G.nch; ch++) {
+    issue_x(0);
+    if (fast_chunks) {
+        cp_async_commit();
+        for (int ch = 1; ch < G.nch; ch++) {
 #ifndef SB_EXP_NOLOAD
-            if (ch * 8 + pc < G.steps) cp_async16(dst + ch * 128, gsrc + ch * 128);
+            if (ch * 8 + f_pc < G.steps) cp_async16(f_dst + ch * 128, f_src + ch * 128);
 #endif
             cp_async_commit();
         }

@@ -513,6 +513,41 @@ router_logits_block_kernel(const float* __restrict__ W, const float* __restrict_
     }
 }
 
+// Decode batches of a few rows: one WARP per (expert, row).  Lane l forms the products of
+// columns [l*CH, (l+1)*CH) in registers (H == 32*CH), then the reference chain
+// acc = fl(acc + p[c]), c ascending (src/kernels.c:98-106), runs lane after lane: lane l
+// takes the running value from lane l-1 and adds its CH products from registers, so each
+// step costs one dependent-add latency and nothing else.
+template <int CH>
+__global__ void __launch_bounds__(32)
+router_logits_warp_kernel(const float* __restrict__ W, const float* __restrict__ bias, const float* __restrict__ x,
+                          float* __restrict__ logits, int E, int H) {
+    const int e = blockIdx.x, r = blockIdx.y, lane = threadIdx.x;
+    const float4* w4 = (const float4*)(W + (size_t)e * H + lane * CH);
+    const float4* x4 = (const float4*)(x + (size_t)r * H + lane * CH);
+    float p[CH];
+#pragma unroll
+    for (int i = 0; i < CH / 4; i++) {
+        const float4 wv = __ldg(w4 + i), xv = x4[i];
+        p[4 * i + 0] = __fmul_rn(wv.x, xv.x);
+        p[4 * i + 1] = __fmul_rn(wv.y, xv.y);
+        p[4 * i + 2] = __fmul_rn(wv.z, xv.z);
+        p[4 * i + 3] = __fmul_rn(wv.w, xv.w);
+    }
+    float acc = 0.0f;
+#pragma unroll 1
+    for (int l = 0; l < 32; l++) {
+        float a = __shfl_sync(0xffffffffu, acc, (l + 31) & 31);
+        if (l == 0) a = 0.0f;
+        if (lane == l) {
+#pragma unroll
+            for (int i = 0; i < CH; i++) a = __fadd_rn(a, p[i]);
+            acc = a;
+        }
+    }
+    if (lane == 31) logits[(size_t)r * E + e] = __fadd_rn(acc, bias ? bias[e] : 0.0f);
+}
+
 // Thread per (row, expert) for large batches: 32 experts x 8 rows per block,
 // W and x staged through shared memory in 64-column slabs.
 __global__ void __launch_bounds__(256)
@@ -546,6 +581,13 @@ router_logits_tile_kernel(const float* __restrict__ W, const float* __restrict__
 cudaError_t launch_router_logits(const float* W, const float* bias, const float* x, float* logits, int rows, int E,
                                  int H, cudaStream_t stream) {
     if (rows < 1) return cudaSuccess;
+    const bool aligned16 = ((((uintptr_t)W) | ((uintptr_t)x)) & 15) == 0;
+    if (rows <= 4 && aligned16 && (H == 32 * 88 || H == 32 * 160)) {
+        dim3 grid(E, rows);
+        if (H == 32 * 88) router_logits_warp_kernel<88><<<grid, 32, 0, stream>>>(W, bias, x, logits, E, H);
+        else router_logits_warp_kernel<160><<<grid, 32, 0, stream>>>(W, bias, x, logits, E, H);
+        return cudaGetLastError();
+    }
     if (rows <= 32) {
         const int nr = rows < LOGIT_TB ? rows : LOGIT_TB;
         const size_t smem = (size_t)nr * (((H + 3) & ~3) + 4) * sizeof(float);
@@ -805,7 +847,102 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(MoePlanArgs a) {
     }
 }
 
+// The same plan for at most 32 selections (decode batches of a few tokens), with the
+// router top-k always fused: 128 threads per row run the top-k, then ONE warp places the
+// selections (slot = selections with a smaller expert + earlier selections of the same
+// expert, which is the stable counting sort) and every thread derives its experts' group
+// starts and descriptors by counting over the <= 32 selections.  No histogram, no block
+// scans: a handful of barriers instead of a dozen.
+__global__ void __launch_bounds__(512) moe_plan_small_kernel(MoePlanArgs a) {
+    extern __shared__ __align__(16) int sp[];
+    const int E = a.n_experts;
+    __shared__ int s_sel[32], s_first[32];
+    {
+        float* tk = (float*)sp;
+        const int grp = threadIdx.x >> 7, ltid = threadIdx.x & 127;
+        const int per = topk_scratch_floats(E, a.topk);
+        float* mine = tk + grp * per;
+        const bool active = grp < a.rows;
+        const int row = active ? grp : 0;
+        topk_group(active, a.logits + (size_t)row * E, a.per_expert_scale, a.selected_out + (size_t)row * a.topk,
+                   a.weights_out + (size_t)row * a.topk, E, a.topk, 1, a.status, mine, mine + per - 4, ltid, 128);
+        __syncthreads();   // selections written by this block are read back below
+    }
+    const int jobs = a.rows * a.topk;
+    const int lane = threadIdx.x & 31;
+    if (threadIdx.x < 32) {
+        int e = lane < jobs ? a.selected[lane] : -1;
+        if (lane < jobs && (e < 0 || e >= E)) { flag(a.status, SB_ERR_INDEX); e = -1; }
+        int before = 0;
+        bool first = true;
+        for (int j = 0; j < jobs; j++) {
+            const int ej = __shfl_sync(0xffffffffu, e, j);
+            if (ej >= 0 && (ej < e || (ej == e && j < lane))) before++;
+            if (ej == e && j < lane) first = false;
+        }
+        if (e >= 0) {
+            a.grouped_to_canonical[before] = lane;
+            a.canonical_to_grouped[lane] = before;
+        }
+        s_sel[lane] = e;
+        s_first[lane] = (e >= 0 && first) ? 1 : 0;
+    }
+    __syncthreads();
+    int valid = 0;
+    for (int j = 0; j < jobs; j++) valid += s_sel[j] >= 0 ? 1 : 0;
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) {
+        int lt = 0, eq = 0, slot = 0;
+        for (int j = 0; j < jobs; j++) {
+            const int ej = s_sel[j];
+            if (ej < 0) continue;
+            lt += ej < e ? 1 : 0;
+            eq += ej == e ? 1 : 0;
+            slot += (s_first[j] && ej < e && ej >= a.expert_begin && ej < a.expert_end) ? 1 : 0;
+        }
+        a.group_offsets[e] = e < E ? lt : valid;
+        if (e == E || eq == 0 || e < a.expert_begin || e >= a.expert_end) continue;
+        const int g0 = lt, cnt = eq;
+        const uint8_t* base = a.pool + (size_t)e * a.expert_stride;
+        Q4Job gu;
+        gu.vals = base; gu.scales = base + a.value_bytes; gu.biases = base + a.value_bytes + a.group_bytes;
+        gu.vals2 = base + a.tensor_bytes; gu.scales2 = gu.vals2 + a.value_bytes;
+        gu.biases2 = gu.scales2 + a.group_bytes;
+        gu.x = a.x; gu.y = a.chain + (size_t)g0 * a.inter;
+        gu.x_rows = a.grouped_to_canonical + g0; gu.x_div = a.topk;
+        gu.R = a.inter; gu.C = a.hidden; gu.ntok = cnt; gu.x_stride = a.hidden; gu.y_stride = a.inter;
+        a.gateup_jobs[slot] = gu;
+        Q4Job dn;
+        dn.vals = base + 2 * a.tensor_bytes; dn.scales = dn.vals + a.value_bytes;
+        dn.biases = dn.scales + a.group_bytes;
+        dn.vals2 = nullptr; dn.scales2 = nullptr; dn.biases2 = nullptr;
+        dn.x = a.chain + (size_t)g0 * a.inter; dn.y = a.grouped_out + (size_t)g0 * a.hidden;
+        dn.x_rows = nullptr; dn.x_div = 1;
+        dn.R = a.hidden; dn.C = a.inter; dn.ntok = cnt; dn.x_stride = a.inter; dn.y_stride = a.hidden;
+        a.down_jobs[slot] = dn;
+    }
+    if (threadIdx.x == 0) {
+        int n_active = 0, max_group = 0;
+        for (int j = 0; j < jobs; j++) {
+            const int ej = s_sel[j];
+            if (!s_first[j] || ej < a.expert_begin || ej >= a.expert_end) continue;
+            n_active++;
+            int cnt = 0;
+            for (int k = 0; k < jobs; k++) cnt += s_sel[k] == ej ? 1 : 0;
+            max_group = max(max_group, cnt);
+        }
+        *a.n_active = n_active;
+        *a.max_group = max_group;
+    }
+}
+
 cudaError_t launch_moe_plan(const MoePlanArgs& a, cudaStream_t stream) {
+    if (a.logits != nullptr && a.rows >= 1 && a.rows <= 4 && a.rows * a.topk <= 32) {
+        const size_t small = (size_t)a.rows * topk_scratch_floats(a.n_experts, a.topk) * sizeof(float);
+        if (small <= 40 * 1024) {
+            moe_plan_small_kernel<<<1, 128 * a.rows, small, stream>>>(a);
+            return cudaGetLastError();
+        }
+    }
     size_t smem = (size_t)(34 * a.n_experts + 4) * sizeof(int);
     if (a.logits != nullptr) {
         if (a.rows > 8) return cudaErrorInvalidValue;
