@@ -14,8 +14,11 @@ bool q4_tile_supported(int C);
 // Runs every job (all share C and nmat).  njobs_dev (device int, may be null)
 // bounds the live jobs when the count is only known on the device; blocks past
 // it exit at once.  `aligned` promises 16-byte aligned tensors and x rows.
+// pdl: -1 ordinary launch; 0 programmatic dependent launch, the jobs come from the previous
+// kernel; 1 the same but the jobs (and njobs_dev) were written at least two launches back, so
+// the weights are prefetched while the previous kernel is still running.
 cudaError_t launch_q4_jobs(const Q4Job* jobs, int njobs_max, const int* njobs_dev, int max_rows, int max_tok, int C,
-                           int nmat, bool aligned, cudaStream_t stream);
+                           int nmat, bool aligned, cudaStream_t stream, int pdl = -1);
 
 // ---- q4_gemm_tc.cu (tcgen05 / TMEM, tolerance path) --------------------------
 cudaError_t launch_gather_convert(const float* x, const int32_t* g2c, void* xh, void* xl, int jobs, int topk,

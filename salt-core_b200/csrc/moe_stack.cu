@@ -296,12 +296,12 @@ int salt_b200_layer_experts(void* stack, int layer, const float* d_x, int B, int
     }
     {
         Timed t(s, KC_GATE_UP, st);
-        if (!cuda_ok(launch_q4_jobs(s->gateup_jobs, njobs_max, s->counters, M, tok_hint, H, 2, true, st), "gate/up"))
+        if (!cuda_ok(launch_q4_jobs(s->gateup_jobs, njobs_max, s->counters, M, tok_hint, H, 2, true, st, 0), "gate/up"))
             return -1;
     }
     {
         Timed t(s, KC_DOWN, st);
-        if (!cuda_ok(launch_q4_jobs(s->down_jobs, njobs_max, s->counters, H, tok_hint, M, 1, true, st), "down"))
+        if (!cuda_ok(launch_q4_jobs(s->down_jobs, njobs_max, s->counters, H, tok_hint, M, 1, true, st, 1), "down"))
             return -1;
     }
     count_launches(4);

@@ -13,6 +13,7 @@
 //
 // Both reproduce the reference row DAG (src/kernels.c:220-250) bit for bit.
 #include "internal.h"
+#include "pdl.cuh"
 #include "q4_core.cuh"
 
 namespace sb {
@@ -384,13 +385,28 @@ __device__ __forceinline__ float fold_row_hexadecants(f32x2 acc, int v) {
 // epilogue) or 16 rows (NMAT == 1: rows r and r + 8 per lane group).
 template <int NMAT, int TT>
 __global__ void __launch_bounds__(128)
-q4_tile16_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_dev, int C) {
+q4_tile16_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_dev, int C, int jobs_early) {
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr int NT = 128;
+    // jobs_early: the job table was written at least two launches back, so everything except the
+    // activation rows (the previous kernel's output) may be fetched before the dependency wait
+    if (!jobs_early) {
+        pdl_wait();
+        pdl_launch_dependents();
+    }
     const int job_id = blockIdx.y;
     // both loads are issued before the count is tested (blockIdx.y always indexes inside the job array)
-    const int njobs_live = njobs_dev != nullptr ? *njobs_dev : 0x7fffffff;
-    const Q4Job jb = jobs[job_id];
+    // (read through L2: with jobs_early these loads run before the dependency wait, when this
+    // SM's L1 may still hold the table of an earlier pass)
+    const int njobs_live = njobs_dev != nullptr ? __ldcg(njobs_dev) : 0x7fffffff;
+    Q4Job jb;
+    {
+        static_assert(sizeof(Q4Job) % 16 == 0, "job descriptors are copied in 16-byte pieces");
+        const uint4* src = (const uint4*)(jobs + job_id);
+        uint4* dst = (uint4*)&jb;
+#pragma unroll
+        for (int q = 0; q < (int)(sizeof(Q4Job) / 16); q++) dst[q] = __ldcg(src + q);
+    }
     if (job_id >= njobs_live) return;
     constexpr int ROWS_A = (NMAT == 2) ? 8 : 16;
     const int r0 = blockIdx.x * ROWS_A;
@@ -461,6 +477,10 @@ q4_tile16_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_d
         }
         if (!gb)
             for (int i = tid; i < (G.sc_block >> 2); i += NT) ((uint32_t*)db)[i] = 0u;
+    }
+    if (jobs_early) {
+        pdl_wait();
+        pdl_launch_dependents();
     }
     issue_x(0);
     if (fast_chunks) {
@@ -613,7 +633,7 @@ bool q4_tile_supported(int C) { return C >= 64 && (C % 64) == 0 && tile_smem_byt
 
 template <int NMAT, int TT>
 static cudaError_t launch_tile(const Q4Job* jobs, int njobs_max, const int* njobs_dev, int max_rows, int C,
-                               cudaStream_t stream) {
+                               cudaStream_t stream, int pdl) {
     size_t smem = tile_smem_bytes(C, NMAT, TT);
     static size_t configured = 0;
     if (smem > 48 * 1024 && smem > configured) {
@@ -624,23 +644,24 @@ static cudaError_t launch_tile(const Q4Job* jobs, int njobs_max, const int* njob
     }
     constexpr int ROWS_A = NMAT == 2 ? 8 : 16;
     dim3 grid((max_rows + ROWS_A - 1) / ROWS_A, njobs_max);
-    q4_tile16_kernel<NMAT, TT><<<grid, 128, smem, stream>>>(jobs, njobs_dev, C);
+    if (pdl >= 0) return launch_pdl(q4_tile16_kernel<NMAT, TT>, grid, dim3(128), smem, stream, jobs, njobs_dev, C, pdl);
+    q4_tile16_kernel<NMAT, TT><<<grid, 128, smem, stream>>>(jobs, njobs_dev, C, 0);
     return cudaGetLastError();
 }
 
 cudaError_t launch_q4_jobs(const Q4Job* jobs, int njobs_max, const int* njobs_dev, int max_rows, int max_tok, int C,
-                           int nmat, bool aligned, cudaStream_t stream) {
+                           int nmat, bool aligned, cudaStream_t stream, int pdl) {
     if (njobs_max < 1 || max_rows < 1 || max_tok < 1) return cudaSuccess;
     if (aligned && q4_tile_supported(C)) {
         const int tt = max_tok >= 3 ? 4 : (max_tok == 2 ? 2 : 1);
         if (nmat == 2) {
-            if (tt == 1) return launch_tile<2, 1>(jobs, njobs_max, njobs_dev, max_rows, C, stream);
-            if (tt == 2) return launch_tile<2, 2>(jobs, njobs_max, njobs_dev, max_rows, C, stream);
-            return launch_tile<2, 4>(jobs, njobs_max, njobs_dev, max_rows, C, stream);
+            if (tt == 1) return launch_tile<2, 1>(jobs, njobs_max, njobs_dev, max_rows, C, stream, pdl);
+            if (tt == 2) return launch_tile<2, 2>(jobs, njobs_max, njobs_dev, max_rows, C, stream, pdl);
+            return launch_tile<2, 4>(jobs, njobs_max, njobs_dev, max_rows, C, stream, pdl);
         }
-        if (tt == 1) return launch_tile<1, 1>(jobs, njobs_max, njobs_dev, max_rows, C, stream);
-        if (tt == 2) return launch_tile<1, 2>(jobs, njobs_max, njobs_dev, max_rows, C, stream);
-        return launch_tile<1, 4>(jobs, njobs_max, njobs_dev, max_rows, C, stream);
+        if (tt == 1) return launch_tile<1, 1>(jobs, njobs_max, njobs_dev, max_rows, C, stream, pdl);
+        if (tt == 2) return launch_tile<1, 2>(jobs, njobs_max, njobs_dev, max_rows, C, stream, pdl);
+        return launch_tile<1, 4>(jobs, njobs_max, njobs_dev, max_rows, C, stream, pdl);
     }
     dim3 grid((max_rows + 3) / 4, max_tok, njobs_max);
     if (grid.y > 65535 || grid.z > 65535) return cudaErrorInvalidValue;

@@ -6,6 +6,7 @@
 // serial per row/expert and parallelism comes from running many of them side
 // by side, with the independent products computed ahead by other lanes.
 #include "internal.h"
+#include "pdl.cuh"
 #include "q4_core.cuh"
 
 namespace sb {
@@ -319,12 +320,20 @@ __global__ void __launch_bounds__(GLUE_NV == 4 ? 1024 : 512) glue_rows_kernel(Gl
         rs[j] = (a.router_scale != nullptr && d < n) ? __ldg(a.router_scale + d) : 1.0f;
         v[j] = 0.0f;
     }
+    // the rank table was written by the plan kernel, at least two launches back
+    int early_g = -1;
+    float early_w = 0.0f;
+    if (a.grouped != nullptr && tid < a.topk) {
+        early_g = __ldcg(a.c2g + row * a.topk + tid);      // through L2: this SM's L1 may hold an earlier pass
+        early_w = __ldcg(a.weights + row * a.topk + tid);
+    }
+    pdl_wait();                    // the expert outputs (or x_in) come from the previous kernel
+    pdl_launch_dependents();
     if (a.grouped != nullptr) {
         // rank -> (grouped row, weight) once per block; invalid ranks are dropped and flagged
         if (tid < a.topk) {
-            const int canonical = row * a.topk + tid;
-            int g = a.c2g[canonical];
-            const float w = a.weights[canonical];
+            int g = early_g;
+            const float w = early_w;
             if (g < 0 || g >= a.jobs || !finite_f(w)) {
                 flag(a.status, g < 0 || g >= a.jobs ? SB_ERR_INDEX : SB_ERR_NONFINITE);
                 g = -1;
@@ -426,9 +435,9 @@ cudaError_t launch_glue(const GlueArgs& a, int rows, cudaStream_t stream) {
     if (a.n <= 4096) {
         // every thread owns 4 columns: wide rows and small batches get the largest block
         const int threads = (rows <= 16 || a.n > 1024) ? 1024 : 256;
-        glue_rows_kernel<4, 8><<<rows, threads, smem, stream>>>(a);
+        return launch_pdl(glue_rows_kernel<4, 8>, dim3(rows), dim3(threads), smem, stream, a);
     } else if (a.n <= 8192) {
-        glue_rows_kernel<16, 2><<<rows, 512, smem, stream>>>(a);
+        return launch_pdl(glue_rows_kernel<16, 2>, dim3(rows), dim3(512), smem, stream, a);
     } else {
         return cudaErrorInvalidValue;
     }
@@ -527,12 +536,19 @@ router_logits_warp_kernel(const float* __restrict__ W, const float* __restrict__
     const float4* x4 = (const float4*)(x + (size_t)r * H + lane * CH);
     float p[CH];
 #pragma unroll
+    for (int i = 0; i < CH / 4; i++) {       // the router weights do not depend on the previous kernel
+        const float4 wv = __ldg(w4 + i);
+        p[4 * i + 0] = wv.x; p[4 * i + 1] = wv.y; p[4 * i + 2] = wv.z; p[4 * i + 3] = wv.w;
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+#pragma unroll
     for (int i = 0; i < CH / 4; i++) {
-        const float4 wv = __ldg(w4 + i), xv = x4[i];
-        p[4 * i + 0] = __fmul_rn(wv.x, xv.x);
-        p[4 * i + 1] = __fmul_rn(wv.y, xv.y);
-        p[4 * i + 2] = __fmul_rn(wv.z, xv.z);
-        p[4 * i + 3] = __fmul_rn(wv.w, xv.w);
+        const float4 xv = x4[i];
+        p[4 * i + 0] = __fmul_rn(p[4 * i + 0], xv.x);
+        p[4 * i + 1] = __fmul_rn(p[4 * i + 1], xv.y);
+        p[4 * i + 2] = __fmul_rn(p[4 * i + 2], xv.z);
+        p[4 * i + 3] = __fmul_rn(p[4 * i + 3], xv.w);
     }
     float acc = 0.0f;
 #pragma unroll 1
@@ -584,9 +600,8 @@ cudaError_t launch_router_logits(const float* W, const float* bias, const float*
     const bool aligned16 = ((((uintptr_t)W) | ((uintptr_t)x)) & 15) == 0;
     if (rows <= 4 && aligned16 && (H == 32 * 88 || H == 32 * 160)) {
         dim3 grid(E, rows);
-        if (H == 32 * 88) router_logits_warp_kernel<88><<<grid, 32, 0, stream>>>(W, bias, x, logits, E, H);
-        else router_logits_warp_kernel<160><<<grid, 32, 0, stream>>>(W, bias, x, logits, E, H);
-        return cudaGetLastError();
+        if (H == 32 * 88) return launch_pdl(router_logits_warp_kernel<88>, grid, dim3(32), 0, stream, W, bias, x, logits, E, H);
+        return launch_pdl(router_logits_warp_kernel<160>, grid, dim3(32), 0, stream, W, bias, x, logits, E, H);
     }
     if (rows <= 32) {
         const int nr = rows < LOGIT_TB ? rows : LOGIT_TB;
@@ -856,6 +871,8 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(MoePlanArgs a) {
 __global__ void __launch_bounds__(512) moe_plan_small_kernel(MoePlanArgs a) {
     extern __shared__ __align__(16) int sp[];
     const int E = a.n_experts;
+    pdl_wait();                    // the logits come from the previous kernel
+    pdl_launch_dependents();
     __shared__ int s_sel[32], s_first[32];
     {
         float* tk = (float*)sp;
@@ -939,8 +956,7 @@ cudaError_t launch_moe_plan(const MoePlanArgs& a, cudaStream_t stream) {
     if (a.logits != nullptr && a.rows >= 1 && a.rows <= 4 && a.rows * a.topk <= 32) {
         const size_t small = (size_t)a.rows * topk_scratch_floats(a.n_experts, a.topk) * sizeof(float);
         if (small <= 40 * 1024) {
-            moe_plan_small_kernel<<<1, 128 * a.rows, small, stream>>>(a);
-            return cudaGetLastError();
+            return launch_pdl(moe_plan_small_kernel, dim3(1), dim3(128 * a.rows), small, stream, a);
         }
     }
     size_t smem = (size_t)(34 * a.n_experts + 4) * sizeof(int);
