@@ -350,18 +350,23 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps) {
     uint32_t b_issued = 0;                                    // B tiles requested so far
     const uint32_t a_lo0 = DESC_B_LO | ((smem_u32(stage_base) & 0x3ffffu) >> 4);
     const uint32_t b_lo0 = DESC_B_LO | ((smem_u32(bring) & 0x3ffffu) >> 4);
-    // request the B tile of running chunk t (pass t / nchunks, chunk t % nchunks)
-    auto issue_b = [&](uint32_t t) {
-        const uint32_t slot = t % NB;
-        const int pass = (int)(t / (uint32_t)nchunks), kq = (int)(t % (uint32_t)nchunks);
+    // request the B tile of chunk kq of token pass `pass` into ring slot `slot`
+    auto issue_b_at = [&](uint32_t slot, int kq, int pass) {
         const uint32_t dst = smem_u32(bring + slot * slot_bytes);
         mbar_expect_tx(&bar_b[slot], slot_bytes);
         tma_load_2d(dst, &maps.hi[variant], kq * TC_KC, g0 + pass * TC_MAX_NT, &bar_b[slot]);
         if (SPLIT) tma_load_2d(dst + part_bytes, &maps.lo[variant], kq * TC_KC, g0 + pass * TC_MAX_NT, &bar_b[slot]);
     };
+    uint32_t b_slot = 0;                                      // next B request: ring slot, chunk, pass
+    int b_kq = 0, b_pass = 0;
+    uint32_t iss_s = 0, iss_ph = 0, iss_slot = 0, iss_bph = 0;   // issuer: stage / slot and their phase parities
     if (warp == 8) {
         if (lane == 0)
-            for (; b_issued < total && b_issued < NB; b_issued++) issue_b(b_issued);
+            for (; b_issued < total && b_issued < NB; b_issued++) {
+                issue_b_at(b_slot, b_kq, b_pass);
+                if (++b_slot == NB) b_slot = 0;
+                if (++b_kq == nchunks) { b_kq = 0; b_pass++; }
+            }
         __syncwarp();
     }
 
@@ -428,22 +433,26 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps) {
             }
         } else {
             // ================= issuer warp =================
+            // All ring positions and phase parities are carried incrementally (iss_*): the loop
+            // is one thread's dependent instruction stream, so every division removed shortens
+            // the per-chunk critical path.
             const uint32_t idesc = umma_idesc_f16(128, NT);
             for (int kc = 0; kc < nchunks; kc++, it++) {
-                const uint32_t s = it % STAGES, slot = it % NB;
-                bool ok = !*fail;
-                // stage s free again => so is the B slot of chunk it - STAGES: refill it
-                if (ok && it >= (uint32_t)STAGES) ok = mbar_wait(&bar_free[s], ((it / STAGES) - 1) & 1, fail);
-                if (ok && lane == 0 && it >= (uint32_t)STAGES && b_issued < total && b_issued == it - STAGES + NB) {
-                    issue_b(b_issued);
+                bool ok = true;
+                // stage free again => so is the B slot of chunk it - STAGES: refill it
+                if (it >= (uint32_t)STAGES) ok = mbar_wait(&bar_free[iss_s], iss_ph ^ 1u, fail);
+                if (ok && lane == 0 && it >= (uint32_t)STAGES && b_issued < total) {
+                    issue_b_at(b_slot, b_kq, b_pass);
                     b_issued++;
+                    if (++b_slot == NB) b_slot = 0;
+                    if (++b_kq == nchunks) { b_kq = 0; b_pass++; }
                 }
-                if (ok) ok = mbar_wait(&bar_full[s], (it / STAGES) & 1, fail);
-                if (ok) ok = mbar_wait(&bar_b[slot], (it / NB) & 1, fail);
+                if (ok) ok = mbar_wait(&bar_full[iss_s], iss_ph, fail);
+                if (ok) ok = mbar_wait(&bar_b[iss_slot], iss_bph, fail);
                 if (ok && lane == 0) {
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t alo = a_lo0 + s * (STAGE_BYTES >> 4);
-                    const uint32_t blo = b_lo0 + slot * (slot_bytes >> 4);
+                    const uint32_t alo = a_lo0 + iss_s * (STAGE_BYTES >> 4);
+                    const uint32_t blo = b_lo0 + iss_slot * (slot_bytes >> 4);
                     const uint32_t blo_l = blo + (part_bytes >> 4);
 #pragma unroll
                     for (int j = 0; j < TC_KC / 16; j++) {
@@ -461,9 +470,11 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps) {
                             }
                         }
                     }
-                    umma_commit(&bar_free[s]);
+                    umma_commit(&bar_free[iss_s]);
                     if (kc == nchunks - 1) umma_commit(&bar_done);
                 }
+                if (++iss_s == (uint32_t)STAGES) { iss_s = 0; iss_ph ^= 1u; }
+                if (++iss_slot == NB) { iss_slot = 0; iss_bph ^= 1u; }
                 __syncwarp();
             }
         }
