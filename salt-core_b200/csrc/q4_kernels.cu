@@ -381,33 +381,11 @@ __device__ __forceinline__ float fold_row_hexadecants(f32x2 acc, int v) {
     return __fadd_rn(__fadd_rn(L0, L2), __fadd_rn(L1, L3));
 }
 
-// One block = 128 threads = 8 row pairs (NMAT == 2: gate row r and up row r, fused GeGLU
-// epilogue) or 16 rows (NMAT == 1: rows r and r + 8 per lane group).
+// The work of one block once its job is known: TT tokens of the group per pass.
 template <int NMAT, int TT>
-__global__ void __launch_bounds__(128)
-q4_tile16_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_dev, int C, int jobs_early) {
+__device__ void tile16_block(const Q4Job& jb, int C, int jobs_early) {
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr int NT = 128;
-    // jobs_early: the job table was written at least two launches back, so everything except the
-    // activation rows (the previous kernel's output) may be fetched before the dependency wait
-    if (!jobs_early) {
-        pdl_wait();
-        pdl_launch_dependents();
-    }
-    const int job_id = blockIdx.y;
-    // both loads are issued before the count is tested (blockIdx.y always indexes inside the job array)
-    // (read through L2: with jobs_early these loads run before the dependency wait, when this
-    // SM's L1 may still hold the table of an earlier pass)
-    const int njobs_live = njobs_dev != nullptr ? __ldcg(njobs_dev) : 0x7fffffff;
-    Q4Job jb;
-    {
-        static_assert(sizeof(Q4Job) % 16 == 0, "job descriptors are copied in 16-byte pieces");
-        const uint4* src = (const uint4*)(jobs + job_id);
-        uint4* dst = (uint4*)&jb;
-#pragma unroll
-        for (int q = 0; q < (int)(sizeof(Q4Job) / 16); q++) dst[q] = __ldcg(src + q);
-    }
-    if (job_id >= njobs_live) return;
     constexpr int ROWS_A = (NMAT == 2) ? 8 : 16;
     const int r0 = blockIdx.x * ROWS_A;
     if (r0 >= jb.R || jb.ntok < 1) return;
@@ -575,6 +553,39 @@ q4_tile16_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_d
             }
         }
     }
+}
+
+// One block = 128 threads = 8 row pairs (NMAT == 2: gate row r and up row r, fused GeGLU
+// epilogue) or 16 rows (NMAT == 1: rows r and r + 8 per lane group).  TTMAX = most tokens of a
+// group handled per pass (and what the shared activation area is sized for); a block whose
+// group is smaller runs the code specialised for 1 or 2 tokens, so decode batches whose
+// expert groups hold one or two tokens do not pay for four.
+template <int NMAT, int TTMAX>
+__global__ void __launch_bounds__(128)
+q4_tile16_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_dev, int C, int jobs_early) {
+    // jobs_early: the job table was written at least two launches back, so everything except the
+    // activation rows (the previous kernel's output) may be fetched before the dependency wait
+    if (!jobs_early) {
+        pdl_wait();
+        pdl_launch_dependents();
+    }
+    const int job_id = blockIdx.y;
+    // both loads are issued before the count is tested (blockIdx.y always indexes inside the job array)
+    // (read through L2: with jobs_early these loads run before the dependency wait, when this
+    // SM's L1 may still hold the table of an earlier pass)
+    const int njobs_live = njobs_dev != nullptr ? __ldcg(njobs_dev) : 0x7fffffff;
+    Q4Job jb;
+    {
+        static_assert(sizeof(Q4Job) % 16 == 0, "job descriptors are copied in 16-byte pieces");
+        const uint4* src = (const uint4*)(jobs + job_id);
+        uint4* dst = (uint4*)&jb;
+#pragma unroll
+        for (int q = 0; q < (int)(sizeof(Q4Job) / 16); q++) dst[q] = __ldcg(src + q);
+    }
+    if (job_id >= njobs_live) return;
+    if (TTMAX >= 4 && jb.ntok >= 3) tile16_block<NMAT, (TTMAX >= 4 ? 4 : TTMAX)>(jb, C, jobs_early);
+    else if (TTMAX >= 2 && jb.ntok == 2) tile16_block<NMAT, (TTMAX >= 2 ? 2 : TTMAX)>(jb, C, jobs_early);
+    else tile16_block<NMAT, 1>(jb, C, jobs_early);
 }
 
 // Any shape, any alignment.  Lane l owns accumulator l (columns c == l mod 32).
