@@ -564,11 +564,65 @@ router_logits_warp_kernel(const float* __restrict__ W, const float* __restrict__
     if (lane == 31) logits[(size_t)r * E + e] = __fadd_rn(acc, bias ? bias[e] : 0.0f);
 }
 
-// Thread per (row, expert) for large batches: 32 experts x 8 rows per block,
-// W and x staged through shared memory in 64-column slabs.
-__global__ void __launch_bounds__(256)
+// Thread per (row, expert) for large batches: 8 experts x 8 rows per block of 64 threads
+// (many small blocks: 64 rows x 128 experts already fill the GPU).  W and x stream through
+// shared memory in 256-column slabs, four slabs deep with 16-byte cp.async copies, so the
+// only thing a thread ever waits for is its own dependent-add chain.
+constexpr int LT_SLAB = 256, LT_PITCH = LT_SLAB + 4, LT_STAGES = 4;
+
+__global__ void __launch_bounds__(64)
 router_logits_tile_kernel(const float* __restrict__ W, const float* __restrict__ bias, const float* __restrict__ x,
                           float* __restrict__ logits, int rows, int E, int H) {
+    extern __shared__ __align__(16) float lt_sm[];      // [LT_STAGES][16][LT_PITCH]: 8 W rows, then 8 x rows
+    const int tid = threadIdx.x;
+    const int el = tid & 7, rl = tid >> 3;
+    const int e0 = blockIdx.x * 8, row0 = blockIdx.y * 8;
+    const int nslab = (H + LT_SLAB - 1) / LT_SLAB;
+    auto issue = [&](int sl) {
+        float* st = lt_sm + (size_t)(sl % LT_STAGES) * 16 * LT_PITCH;
+        const int c0 = sl * LT_SLAB;
+        const int pieces = (min(LT_SLAB, H - c0) + 3) >> 2;          // 16-byte pieces per row (H % 4 == 0)
+        for (int p = tid; p < 16 * pieces; p += 64) {
+            const int r = p / pieces, pc = p - r * pieces;
+            const float* src;
+            if (r < 8) src = W + (size_t)min(e0 + r, E - 1) * H + c0 + pc * 4;
+            else src = x + (size_t)min(row0 + r - 8, rows - 1) * H + c0 + pc * 4;
+            cp_async16(st + r * LT_PITCH + pc * 4, src);
+        }
+    };
+    for (int sl = 0; sl < LT_STAGES - 1; sl++) {
+        if (sl < nslab) issue(sl);
+        cp_async_commit();
+    }
+    float acc = 0.0f;
+    for (int sl = 0; sl < nslab; sl++) {
+        cp_async_wait_dyn(LT_STAGES - 2);      // slab sl has landed (one group per slab, empty ones included)
+        __syncthreads();                       // ... for every thread, and slab sl - 1 is no longer read
+        if (sl + LT_STAGES - 1 < nslab) issue(sl + LT_STAGES - 1);
+        cp_async_commit();
+        const float* st = lt_sm + (size_t)(sl % LT_STAGES) * 16 * LT_PITCH;
+        const float4* w4 = (const float4*)(st + el * LT_PITCH);
+        const float4* x4 = (const float4*)(st + (8 + rl) * LT_PITCH);
+        const int kc = min(LT_SLAB, H - sl * LT_SLAB);
+        int c = 0;
+#pragma unroll 4
+        for (; c + 4 <= kc; c += 4) {
+            const float4 wv = w4[c >> 2], xv = x4[c >> 2];
+            acc = __fadd_rn(acc, __fmul_rn(wv.x, xv.x));
+            acc = __fadd_rn(acc, __fmul_rn(wv.y, xv.y));
+            acc = __fadd_rn(acc, __fmul_rn(wv.z, xv.z));
+            acc = __fadd_rn(acc, __fmul_rn(wv.w, xv.w));
+        }
+    }
+    const int e = e0 + el, row = row0 + rl;
+    if (e < E && row < rows) logits[(size_t)row * E + e] = __fadd_rn(acc, bias ? bias[e] : 0.0f);
+}
+
+// The same without alignment requirements (H not a multiple of 4, or unaligned operands):
+// plain loads, 32 experts x 8 rows per block, 64-column slabs.
+__global__ void __launch_bounds__(256)
+router_logits_tile_plain_kernel(const float* __restrict__ W, const float* __restrict__ bias,
+                                const float* __restrict__ x, float* __restrict__ logits, int rows, int E, int H) {
     __shared__ float sW[32][65];
     __shared__ float sX[8][64];
     const int el = threadIdx.x & 31, rl = threadIdx.x >> 5;
@@ -616,9 +670,20 @@ cudaError_t launch_router_logits(const float* W, const float* bias, const float*
         if (smem > 200 * 1024) return cudaErrorInvalidValue;
         dim3 grid(E, (rows + LOGIT_TB - 1) / LOGIT_TB);
         router_logits_block_kernel<<<grid, 256, smem, stream>>>(W, bias, x, logits, rows, E, H);
+    } else if (aligned16 && (H & 3) == 0) {
+        const size_t smem = (size_t)LT_STAGES * 16 * LT_PITCH * sizeof(float);
+        static bool configured = false;
+        if (!configured) {
+            cudaError_t e = cudaFuncSetAttribute(router_logits_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)smem);
+            if (e != cudaSuccess) return e;
+            configured = true;
+        }
+        dim3 grid((E + 7) / 8, (rows + 7) / 8);
+        router_logits_tile_kernel<<<grid, 64, smem, stream>>>(W, bias, x, logits, rows, E, H);
     } else {
         dim3 grid((E + 31) / 32, (rows + 7) / 8);
-        router_logits_tile_kernel<<<grid, 256, 0, stream>>>(W, bias, x, logits, rows, E, H);
+        router_logits_tile_plain_kernel<<<grid, 256, 0, stream>>>(W, bias, x, logits, rows, E, H);
     }
     return cudaGetLastError();
 }
