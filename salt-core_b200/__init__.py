@@ -7,4 +7,4 @@ surface (``backend.SaltGpu``) and of the device-resident stack (``stack.MoeStack
 and the seeded synthetic tensors of the benchmark configurations (``synth``).
 """
 from . import synth  # noqa: F401
-from ._lib import LIB_PATH, load_library  # noqa: F401
+from ._lib import LIB_PATH, library_path, load_library  # noqa: F401

@@ -10,6 +10,13 @@ LIB_PATH = os.path.join(HERE, "libsalt_gpu_b200.so")
 _lib = None
 
 
+def library_path() -> str:
+    """Absolute path of the built shared library (for hosts that link it directly)."""
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(f"{LIB_PATH} is missing: build it with `python salt-core_b200/build.py`")
+    return LIB_PATH
+
+
 def load_library() -> C.CDLL:
     global _lib
     if _lib is None:
