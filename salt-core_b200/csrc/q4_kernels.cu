@@ -55,245 +55,11 @@ __device__ __forceinline__ void product_then_add(f32x2& acc, f32x2 d, f32x2 x, f
     acc = add2(acc, fma2(d, x, negzero));
 }
 
-// NSTEPS consecutive 32-column steps (NSTEPS even, compile-time) of the thread's
-// two rows for TT tokens.  All operands are pre-offset to the first step, so
-// every shared-memory access below has a compile-time displacement.
-// tA / tB point at the rows' table words: bf16 scale in the high half, bf16
-// bias in the low half of one 32-bit word per quantisation group.
-template <int TT, bool LIT, int NSTEPS>
-__device__ __forceinline__ void tile_steps(const NibbleMagic& mg, const uint8_t* wA, const uint8_t* wB,
-                                           const uint32_t* tA, const uint32_t* tB, const float* const (&xs)[TT],
-                                           f32x2 (&accA)[TT][2], f32x2 (&accB)[TT][2], f32x2 nz) {
-#pragma unroll
-    for (int g = 0; g < NSTEPS / 2; g++) {
-        const uint32_t wa = tA[g], wb = tB[g];
-        const float sa = __uint_as_float(wa & 0xffff0000u), ba = __uint_as_float(wa << 16);
-        const float sb_ = __uint_as_float(wb & 0xffff0000u), bb_ = __uint_as_float(wb << 16);
-        const f32x2 ssA = pack2(sa, sa), bbA = pack2(ba, ba), ssB = pack2(sb_, sb_), bbB = pack2(bb_, bb_);
-#pragma unroll
-        for (int half = 0; half < 2; half++) {
-            const int k = 2 * g + half;
-            const uint32_t hA = *(const uint16_t*)(wA + k * 16);
-            const uint32_t hB = *(const uint16_t*)(wB + k * 16);
-            f32x2 dA01, dA23, dB01, dB23;
-            dequant4<LIT>(hA, mg, ssA, bbA, dA01, dA23);
-            dequant4<LIT>(hB, mg, ssB, bbB, dB01, dB23);
-#pragma unroll
-            for (int tt = 0; tt < TT; tt++) {
-                const ulonglong2 xv = *(const ulonglong2*)(xs[tt] + k * 32);
-                product_then_add(accA[tt][0], dA01, xv.x, nz);
-                product_then_add(accA[tt][1], dA23, xv.y, nz);
-                product_then_add(accB[tt][0], dB01, xv.x, nz);
-                product_then_add(accB[tt][1], dB23, xv.y, nz);
-            }
-        }
-    }
-}
-
-// A run of steps [s_begin, s_end): whole 8-step blocks, then 2-step blocks.
-template <int TT, bool LIT>
-__device__ __forceinline__ void tile_run(const NibbleMagic& mg, int s_begin, int s_end, const uint8_t* wA,
-                                         const uint8_t* wB, const uint32_t* tA, const uint32_t* tB,
-                                         const float* sX, int x_pitch,
-                                         f32x2 (&accA)[TT][2], f32x2 (&accB)[TT][2], f32x2 nz) {
-    int st = s_begin;
-    constexpr int BLK = 8;
-    for (; st + BLK <= s_end; st += BLK) {
-        const float* xs[TT];
-#pragma unroll
-        for (int tt = 0; tt < TT; tt++) xs[tt] = sX + tt * x_pitch + st * 32;
-        tile_steps<TT, LIT, BLK>(mg, wA + st * 16, wB + st * 16, tA + (st >> 1), tB + (st >> 1), xs, accA, accB, nz);
-    }
-    for (; st + 2 <= s_end; st += 2) {
-        const float* xs[TT];
-#pragma unroll
-        for (int tt = 0; tt < TT; tt++) xs[tt] = sX + tt * x_pitch + st * 32;
-        tile_steps<TT, LIT, 2>(mg, wA + st * 16, wB + st * 16, tA + (st >> 1), tB + (st >> 1), xs, accA, accB, nz);
-    }
-}
-
-// One block = 64 threads = 8 row pairs (NMAT == 2: gate row r and up row r,
-// fused GeGLU epilogue) or 16 rows (NMAT == 1: rows r and r + 8 per lane).
-template <int NMAT, int TT>
-__global__ void __launch_bounds__(64)
-q4_tile_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_dev, int C) {
-    extern __shared__ __align__(16) uint8_t smem[];
-    const int job_id = blockIdx.y;
-    if (njobs_dev != nullptr && job_id >= *njobs_dev) return;
-    const Q4Job jb = jobs[job_id];
-    constexpr int ROWS_A = (NMAT == 2) ? 8 : 16;
-    const int r0 = blockIdx.x * ROWS_A;
-    if (r0 >= jb.R || jb.ntok < 1) return;
-    const int tid = threadIdx.x;
-    const int u = tid & 7;                       // octant: accumulators 4u..4u+3
-    const int pr = tid >> 3;                     // row slot 0..7
-    const int nvalid = min(ROWS_A, jb.R - r0);
-    const TileGeom G = tile_geom(C, ROWS_A);
-    uint8_t* sW = smem;                                   // [16][w_stride]
-    uint8_t* sS = sW + 16 * G.w_stride;                   // [NMAT][sc_block]
-    uint8_t* sBi = sS + NMAT * G.sc_block;                // [NMAT][sc_block]
-    uint32_t* sT = (uint32_t*)(sBi + NMAT * G.sc_block);  // [16][tpitch] (scale bf16 << 16) | bias bf16
-    const int tpitch = G.tpitch;
-    float* sX = (float*)(sT + 16 * tpitch);               // [TT][C]
-
-    // ---- group 0: activations of the first token block, scales, biases, K chunk 0 ----
-    auto issue_x = [&](int tb) {
-        const int ppr = C >> 2;                  // 16-byte pieces per activation row
-#pragma unroll
-        for (int tt = 0; tt < TT; tt++) {
-            const int tok = min(tb + tt, jb.ntok - 1);
-            const int row = jb.x_rows ? (jb.x_rows[tok] / jb.x_div) : tok;
-            const float* src = jb.x + (size_t)row * jb.x_stride;
-            for (int pc = tid; pc < ppr; pc += 64) cp_async16(sX + tt * C + pc * 4, src + pc * 4);
-        }
-    };
-    issue_x(0);
-#pragma unroll
-    for (int m = 0; m < NMAT; m++) {
-        const uint8_t* gs = (m == 0 ? jb.scales : jb.scales2) + (size_t)r0 * G.sc_row;
-        const uint8_t* gb = (m == 0 ? jb.biases : jb.biases2);
-        if (gb) gb += (size_t)r0 * G.sc_row;
-        uint8_t* ds = sS + m * G.sc_block;
-        uint8_t* db = sBi + m * G.sc_block;
-        if (G.sc_padded) {
-            const int ppr = G.sc_row >> 4;
-            for (int p = tid; p < nvalid * ppr; p += 64) {
-                const int rr = p / ppr, pc = p - rr * ppr;
-                cp_async16(ds + rr * G.sc_stride + pc * 16, gs + (size_t)rr * G.sc_row + pc * 16);
-                if (gb) cp_async16(db + rr * G.sc_stride + pc * 16, gb + (size_t)rr * G.sc_row + pc * 16);
-            }
-        } else {
-            const int total = nvalid * G.sc_row;
-            const int full = total >> 4;
-            for (int p = tid; p < full; p += 64) {
-                cp_async16(ds + p * 16, gs + p * 16);
-                if (gb) cp_async16(db + p * 16, gb + p * 16);
-            }
-            for (int i = (full << 4) + tid; i < total; i += 64) {
-                ds[i] = gs[i];
-                if (gb) db[i] = gb[i];
-            }
-        }
-        if (!gb)
-            for (int i = tid; i < (G.sc_block >> 2); i += 64) ((uint32_t*)db)[i] = 0u;
-    }
-    if (G.chunk_steps == 8) {
-        // 8-step chunks: a chunk is 16 rows x 8 pieces of 16 bytes = 128 copies, two per
-        // thread, and the thread's (row, piece) pair is the same in every chunk
-        const int pc = tid & 7, rrA = tid >> 3, rrB = rrA + 8;
-        const int mA = (NMAT == 2) ? 0 : 0, mB = (NMAT == 2) ? 1 : 0;
-        const int growA = min(r0 + ((NMAT == 2) ? rrA : rrA), jb.R - 1);
-        const int growB = min(r0 + ((NMAT == 2) ? (rrB & 7) : rrB), jb.R - 1);
-        const uint8_t* gA = (mA == 0 ? jb.vals : jb.vals2) + (size_t)growA * G.row_bytes + pc * 16;
-        const uint8_t* gB = (mB == 0 ? jb.vals : jb.vals2) + (size_t)growB * G.row_bytes + pc * 16;
-        uint8_t* dA = sW + rrA * G.w_stride + pc * 16;
-        uint8_t* dB = sW + rrB * G.w_stride + pc * 16;
-        const int valid_pieces = G.steps;        // pieces per row
-        for (int ch = 0; ch < G.nch; ch++) {
-            if (ch * 8 + pc < valid_pieces) {
-#ifndef SB_EXP_NOLOAD
-                cp_async16(dA + ch * 128, gA + ch * 128);
-                cp_async16(dB + ch * 128, gB + ch * 128);
-#endif
-            }
-            cp_async_commit();
-        }
-    } else
-    for (int ch = 0; ch < G.nch; ch++) {
-        const int s_begin = ch * G.chunk_steps;
-        const int cs = min(G.chunk_steps, G.steps - s_begin);
-        for (int p = tid; p < 16 * cs; p += 64) {
-            const int rr = p / cs;
-            const int pc = p - rr * cs;
-            const int m = (NMAT == 2) ? (rr >> 3) : 0;
-            int grow = r0 + ((NMAT == 2) ? (rr & 7) : rr);
-            grow = min(grow, jb.R - 1);
-            const uint8_t* g = (m == 0 ? jb.vals : jb.vals2) + (size_t)grow * G.row_bytes + (s_begin + pc) * 16;
-            cp_async16(sW + rr * G.w_stride + (s_begin + pc) * 16, g);
-        }
-        cp_async_commit();
-    }
-
-    // ---- this thread's operands ----
-    const uint8_t* wA = sW + pr * G.w_stride + 2 * u;
-    const uint8_t* wB = sW + (pr + 8) * G.w_stride + 2 * u;
-    const int gpr = C >> 6;                      // quantisation groups per row
-    const uint32_t* tA = sT + pr * tpitch;
-    const uint32_t* tB = sT + (pr + 8) * tpitch;
-    const NibbleMagic mg = load_nibble_magic();
-    const f32x2 nz = pack2u(c_neg_zero, c_neg_zero);
-    const float* xs = sX + 4 * u;
-
-    // wait for group 0, interleave the bf16 scales/biases of the 16 rows into one
-    // word per group, and note whether any scale needs the literal
-    // (two-rounding) dequantisation
-    cp_async_wait_dyn(G.nch - 1);
-    __syncthreads();
-    int lit = 0;
-    for (int gg = tid & 3; gg < gpr; gg += 4) {
-        const int rr = tid >> 2;                 // 64 threads = 16 rows x 4 column phases
-        const int m = (NMAT == 2) ? (rr >> 3) : 0;
-        const int lr = (NMAT == 2) ? (rr & 7) : rr;
-        const uint32_t hs = ((const uint16_t*)(sS + m * G.sc_block + lr * G.sc_stride))[gg];
-        const uint32_t hb = ((const uint16_t*)(sBi + m * G.sc_block + lr * G.sc_stride))[gg];
-        sT[rr * tpitch + gg] = (hs << 16) | hb;
-        if (lr < nvalid) lit |= scale_needs_literal(hs) ? 1 : 0;
-    }
-    lit = __syncthreads_or(lit);
-
-    for (int tb = 0; tb < jb.ntok; tb += TT) {
-        if (tb > 0) {
-            __syncthreads();                     // everyone is done with the previous activations
-            issue_x(tb);
-            cp_async_commit();
-            cp_async_wait_dyn(0);
-            __syncthreads();
-        }
-        f32x2 accA[TT][2], accB[TT][2];
-#pragma unroll
-        for (int tt = 0; tt < TT; tt++)
-#pragma unroll
-            for (int j = 0; j < 2; j++) { accA[tt][j] = pack2(0.0f, 0.0f); accB[tt][j] = pack2(0.0f, 0.0f); }
-        for (int ch = 0; ch < G.nch; ch++) {
-            if (tb == 0 && ch > 0) {
-                cp_async_wait_dyn(G.nch - 1 - ch);
-                __syncthreads();
-            }
-            const int s_begin = ch * G.chunk_steps;
-            const int s_end = min(s_begin + G.chunk_steps, G.steps);
-#ifndef SB_EXP_NOCOMPUTE
-            if (lit) tile_run<TT, true>(mg, s_begin, s_end, wA, wB, tA, tB, xs, C, accA, accB, nz);
-            else tile_run<TT, false>(mg, s_begin, s_end, wA, wB, tA, tB, xs, C, accA, accB, nz);
-#endif
-        }
-#pragma unroll
-        for (int tt = 0; tt < TT; tt++) {
-            float fa[4], fb[4];
-            unpack2(accA[tt][0], fa[0], fa[1]); unpack2(accA[tt][1], fa[2], fa[3]);
-            unpack2(accB[tt][0], fb[0], fb[1]); unpack2(accB[tt][1], fb[2], fb[3]);
-            const float y0 = fold_row_octants(fa, u);
-            const float y1 = fold_row_octants(fb, u);
-            const int tok = tb + tt;
-            if (u == 7 && tok < jb.ntok) {
-                float* yrow = jb.y + (size_t)tok * jb.y_stride;
-                if (NMAT == 2) {
-                    // fused GeGLU (reference gemma4.c:80-83 then gate*up)
-                    if (pr < nvalid) yrow[r0 + pr] = __fmul_rn(gelu_tanh_exact(y0), y1);
-                } else {
-                    if (pr < nvalid) yrow[r0 + pr] = y0;
-                    if (pr + 8 < nvalid) yrow[r0 + pr + 8] = y1;
-                }
-            }
-        }
-    }
-}
-
-// ---- 16 lanes per row ---------------------------------------------------------------
-// Same tile, same shared-memory layout and the same row DAG, but a row's 32 accumulators are
-// spread over SIXTEEN adjacent lanes (lane v = tid & 15 holds acc[2v], acc[2v + 1], i.e. one
-// packed byte per 32-column step), so a block is 128 threads = 4 warps and every SM holds
-// twice the warps of the 8-lane form: the kernel is bound by instruction latency, not by
-// bandwidth or issue slots, and more warps in flight is what hides it.
+// ---- the tile kernel: 16 lanes per row ----------------------------------------------
+// A row's 32 accumulators are spread over sixteen adjacent lanes (lane v = tid & 15 holds
+// acc[2v], acc[2v + 1], i.e. one packed byte per 32-column step).  An earlier form with eight
+// lanes per row (four accumulators each, half the warps) ran decode at the same speed and
+// batches of 64 tokens 1.4x slower.
 
 // One packed byte (two nibbles) as exact floats.
 template <bool LIT>
@@ -382,34 +148,39 @@ __device__ __forceinline__ float fold_row_hexadecants(f32x2 acc, int v) {
 }
 
 // The work of one block once its job is known: TT tokens of the group per pass.
-template <int NMAT, int TT>
+// HALF = row slots of a block (8 or 16): 16 * HALF threads, 2 * HALF weight rows in shared
+// memory (NMAT == 2: HALF gate rows then HALF up rows; NMAT == 1: slot pr owns rows pr and
+// pr + HALF).  Larger blocks halve the activation copies per weight byte, which matters once a
+// group has several tokens.
+template <int NMAT, int TT, int HALF>
 __device__ void tile16_block(const Q4Job& jb, int C, int jobs_early) {
     extern __shared__ __align__(16) uint8_t smem[];
-    constexpr int NT = 128;
-    constexpr int ROWS_A = (NMAT == 2) ? 8 : 16;
+    constexpr int NT = 16 * HALF;
+    constexpr int RT = 2 * HALF;                 // weight rows held in shared memory
+    constexpr int ROWS_A = (NMAT == 2) ? HALF : RT;
     const int r0 = blockIdx.x * ROWS_A;
     if (r0 >= jb.R || jb.ntok < 1) return;
     const int tid = threadIdx.x;
     const int v = tid & 15;                      // accumulators 2v, 2v + 1
-    const int pr = tid >> 4;                     // row slot 0..7
+    const int pr = tid >> 4;                     // row slot 0..HALF-1
     const int nvalid = min(ROWS_A, jb.R - r0);
     const TileGeom G = tile_geom(C, ROWS_A);
-    uint8_t* sW = smem;                                   // [16][w_stride]
-    uint8_t* sS = sW + 16 * G.w_stride;                   // [NMAT][sc_block]
+    uint8_t* sW = smem;                                   // [RT][w_stride]
+    uint8_t* sS = sW + RT * G.w_stride;                   // [NMAT][sc_block]
     uint8_t* sBi = sS + NMAT * G.sc_block;                // [NMAT][sc_block]
-    uint32_t* sT = (uint32_t*)(sBi + NMAT * G.sc_block);  // [16][tpitch] (scale bf16 << 16) | bias bf16
+    uint32_t* sT = (uint32_t*)(sBi + NMAT * G.sc_block);  // [RT][tpitch] (scale bf16 << 16) | bias bf16
     const int tpitch = G.tpitch;
-    float* sX = (float*)(sT + 16 * tpitch);               // [TT][C]
+    float* sX = (float*)(sT + RT * tpitch);               // [TT][C]
 
     // ---- group 0: K chunk 0, scales, biases, activations of the first token block (the weight
     // copies go first: they need nothing but the job, while the activation rows may sit behind
     // one more dependent load of the row table) ----
     const bool fast_chunks = G.chunk_steps == 8;
-    // 8-step chunks: a chunk is 16 rows x 8 pieces of 16 bytes = 128 copies, one per thread,
-    // and the thread's (row, piece) pair is the same in every chunk
+    // 8-step chunks: a chunk is RT rows x 8 pieces of 16 bytes = one copy per thread, and the
+    // thread's (row, piece) pair is the same in every chunk
     const int f_pc = tid & 7, f_rr = tid >> 3;
-    const int f_m = (NMAT == 2) ? (f_rr >> 3) : 0;
-    const int f_grow = min(r0 + ((NMAT == 2) ? (f_rr & 7) : f_rr), jb.R - 1);
+    const int f_m = (NMAT == 2) ? (f_rr / HALF) : 0;
+    const int f_grow = min(r0 + ((NMAT == 2) ? (f_rr & (HALF - 1)) : f_rr), jb.R - 1);
     const uint8_t* f_src = (f_m == 0 ? jb.vals : jb.vals2) + (size_t)f_grow * G.row_bytes + f_pc * 16;
     uint8_t* f_dst = sW + f_rr * G.w_stride + f_pc * 16;
     if (fast_chunks && f_pc < G.steps) {
@@ -473,11 +244,11 @@ __device__ void tile16_block(const Q4Job& jb, int C, int jobs_early) {
         for (int ch = 0; ch < G.nch; ch++) {
             const int s_begin = ch * G.chunk_steps;
             const int cs = min(G.chunk_steps, G.steps - s_begin);
-            for (int p = tid; p < 16 * cs; p += NT) {
+            for (int p = tid; p < RT * cs; p += NT) {
                 const int rr = p / cs;
                 const int pc = p - rr * cs;
-                const int m = (NMAT == 2) ? (rr >> 3) : 0;
-                const int grow = min(r0 + ((NMAT == 2) ? (rr & 7) : rr), jb.R - 1);
+                const int m = (NMAT == 2) ? (rr / HALF) : 0;
+                const int grow = min(r0 + ((NMAT == 2) ? (rr & (HALF - 1)) : rr), jb.R - 1);
                 const uint8_t* g = (m == 0 ? jb.vals : jb.vals2) + (size_t)grow * G.row_bytes + (s_begin + pc) * 16;
                 cp_async16(sW + rr * G.w_stride + (s_begin + pc) * 16, g);
             }
@@ -487,10 +258,10 @@ __device__ void tile16_block(const Q4Job& jb, int C, int jobs_early) {
 
     // ---- this thread's operands ----
     const uint8_t* wA = sW + pr * G.w_stride + v;
-    const uint8_t* wB = sW + (pr + 8) * G.w_stride + v;
+    const uint8_t* wB = sW + (pr + HALF) * G.w_stride + v;
     const int gpr = C >> 6;                      // quantisation groups per row
     const uint32_t* tA = sT + pr * tpitch;
-    const uint32_t* tB = sT + (pr + 8) * tpitch;
+    const uint32_t* tB = sT + (pr + HALF) * tpitch;
     const NibbleMagic mg = load_nibble_magic();
     const f32x2 nz = pack2u(c_neg_zero, c_neg_zero);
     const float* xs = sX + 2 * v;
@@ -501,9 +272,9 @@ __device__ void tile16_block(const Q4Job& jb, int C, int jobs_early) {
     __syncthreads();
     int lit = 0;
     for (int gg = tid & 7; gg < gpr; gg += 8) {
-        const int rr = tid >> 3;                 // 128 threads = 16 rows x 8 column phases
-        const int m = (NMAT == 2) ? (rr >> 3) : 0;
-        const int lr = (NMAT == 2) ? (rr & 7) : rr;
+        const int rr = tid >> 3;                 // NT threads = RT rows x 8 column phases
+        const int m = (NMAT == 2) ? (rr / HALF) : 0;
+        const int lr = (NMAT == 2) ? (rr & (HALF - 1)) : rr;
         const uint32_t hs = ((const uint16_t*)(sS + m * G.sc_block + lr * G.sc_stride))[gg];
         const uint32_t hb = ((const uint16_t*)(sBi + m * G.sc_block + lr * G.sc_stride))[gg];
         sT[rr * tpitch + gg] = (hs << 16) | hb;
@@ -548,7 +319,7 @@ __device__ void tile16_block(const Q4Job& jb, int C, int jobs_early) {
                     if (pr < nvalid) yrow[r0 + pr] = __fmul_rn(gelu_tanh_exact(y0), y1);
                 } else {
                     if (pr < nvalid) yrow[r0 + pr] = y0;
-                    if (pr + 8 < nvalid) yrow[r0 + pr + 8] = y1;
+                    if (pr + HALF < nvalid) yrow[r0 + pr + HALF] = y1;
                 }
             }
         }
@@ -560,8 +331,8 @@ __device__ void tile16_block(const Q4Job& jb, int C, int jobs_early) {
 // group handled per pass (and what the shared activation area is sized for); a block whose
 // group is smaller runs the code specialised for 1 or 2 tokens, so decode batches whose
 // expert groups hold one or two tokens do not pay for four.
-template <int NMAT, int TTMAX>
-__global__ void __launch_bounds__(128)
+template <int NMAT, int TTMAX, int HALF>
+__global__ void __launch_bounds__(16 * HALF)
 q4_tile16_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_dev, int C, int jobs_early) {
     // jobs_early: the job table was written at least two launches back, so everything except the
     // activation rows (the previous kernel's output) may be fetched before the dependency wait
@@ -583,9 +354,9 @@ q4_tile16_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_d
         for (int q = 0; q < (int)(sizeof(Q4Job) / 16); q++) dst[q] = __ldcg(src + q);
     }
     if (job_id >= njobs_live) return;
-    if (TTMAX >= 4 && jb.ntok >= 3) tile16_block<NMAT, (TTMAX >= 4 ? 4 : TTMAX)>(jb, C, jobs_early);
-    else if (TTMAX >= 2 && jb.ntok == 2) tile16_block<NMAT, (TTMAX >= 2 ? 2 : TTMAX)>(jb, C, jobs_early);
-    else tile16_block<NMAT, 1>(jb, C, jobs_early);
+    if (TTMAX >= 4 && jb.ntok >= 3) tile16_block<NMAT, (TTMAX >= 4 ? 4 : TTMAX), HALF>(jb, C, jobs_early);
+    else if (TTMAX >= 2 && jb.ntok == 2) tile16_block<NMAT, (TTMAX >= 2 ? 2 : TTMAX), HALF>(jb, C, jobs_early);
+    else tile16_block<NMAT, 1, HALF>(jb, C, jobs_early);
 }
 
 // Any shape, any alignment.  Lane l owns accumulator l (columns c == l mod 32).
@@ -634,29 +405,33 @@ q4_generic_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_
     }
 }
 
-static size_t tile_smem_bytes(int C, int nmat, int tt) {
-    const TileGeom g = tile_geom(C, nmat == 2 ? 8 : 16);
-    return (size_t)16 * g.w_stride + (size_t)2 * nmat * g.sc_block + (size_t)16 * g.tpitch * 4 +
+static size_t tile_smem_bytes(int C, int nmat, int tt, int half) {
+    const TileGeom g = tile_geom(C, nmat == 2 ? half : 2 * half);
+    return (size_t)(2 * half) * g.w_stride + (size_t)2 * nmat * g.sc_block + (size_t)(2 * half) * g.tpitch * 4 +
            (size_t)tt * C * sizeof(float);
 }
 
-bool q4_tile_supported(int C) { return C >= 64 && (C % 64) == 0 && tile_smem_bytes(C, 2, 4) <= 200 * 1024; }
+bool q4_tile_supported(int C) { return C >= 64 && (C % 64) == 0 && tile_smem_bytes(C, 2, 4, 16) <= 200 * 1024; }
 
 template <int NMAT, int TT>
 static cudaError_t launch_tile(const Q4Job* jobs, int njobs_max, const int* njobs_dev, int max_rows, int C,
                                cudaStream_t stream, int pdl) {
-    size_t smem = tile_smem_bytes(C, NMAT, TT);
+    // single-token groups: 8 row slots per block (more, smaller blocks: lowest latency);
+    // several tokens per group: 16 row slots (half the activation copies per weight byte)
+    constexpr int HALF = TT == 1 ? 8 : 16;
+    size_t smem = tile_smem_bytes(C, NMAT, TT, HALF);
     static size_t configured = 0;
     if (smem > 48 * 1024 && smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(q4_tile16_kernel<NMAT, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)(200 * 1024));
+        cudaError_t e = cudaFuncSetAttribute(q4_tile16_kernel<NMAT, TT, HALF>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024));
         if (e != cudaSuccess) return e;
         configured = 200 * 1024;
     }
-    constexpr int ROWS_A = NMAT == 2 ? 8 : 16;
+    constexpr int ROWS_A = NMAT == 2 ? HALF : 2 * HALF;
     dim3 grid((max_rows + ROWS_A - 1) / ROWS_A, njobs_max);
-    if (pdl >= 0) return launch_pdl(q4_tile16_kernel<NMAT, TT>, grid, dim3(128), smem, stream, jobs, njobs_dev, C, pdl);
-    q4_tile16_kernel<NMAT, TT><<<grid, 128, smem, stream>>>(jobs, njobs_dev, C, 0);
+    if (pdl >= 0)
+        return launch_pdl(q4_tile16_kernel<NMAT, TT, HALF>, grid, dim3(16 * HALF), smem, stream, jobs, njobs_dev, C, pdl);
+    q4_tile16_kernel<NMAT, TT, HALF><<<grid, 16 * HALF, smem, stream>>>(jobs, njobs_dev, C, 0);
     return cudaGetLastError();
 }
 

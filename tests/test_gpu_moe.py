@@ -197,6 +197,45 @@ def test_stack_three_layers_with_rmsnorm_vs_oracle(orc, synth):
     st.close()
 
 
+@pytest.mark.parametrize("B", [1, 3, 12])
+def test_stack_graph_replay_equals_stream_launches_and_oracle(orc, synth, B):
+    """The captured CUDA graph (programmatic dependent launches become graph edges) must give
+    the same bits as the stream launches and as the oracle, on every replay and after the
+    input buffer changes."""
+    import torch
+    H, M, E, K = 2816, 704, 128, 8
+    layers = [synth.make_q4_moe_layer_bulk(60 + i) for i in range(3)]
+    st = stack_mod().MoeStack(16, H, M, E, K)
+    for layer in layers:
+        st.add_layer(layer)
+    stream = torch.cuda.Stream()
+    sp = stream.cuda_stream
+    x0, x1 = synth.make_tokens(70 + B, B, H), synth.make_tokens(170 + B, B, H)
+    d_x = torch.from_numpy(x0).cuda()
+    d_y = torch.zeros_like(d_x)
+    with torch.cuda.stream(stream):
+        assert st.forward_device(d_x.data_ptr(), B, d_y.data_ptr(), stream=sp) == 0
+        stream.synchronize()
+        y_stream = d_y.cpu().numpy()
+        assert st.graph_capture(d_x.data_ptr(), B, d_y.data_ptr(), sp) == 0
+        for rep in range(3):
+            d_y.zero_()
+            assert st.graph_launch(sp) == 0
+            stream.synchronize()
+            assert_bits_equal(d_y.cpu().numpy(), y_stream, f"graph replay {rep}")
+        d_x.copy_(torch.from_numpy(x1))
+        for rep in range(2):
+            assert st.graph_launch(sp) == 0
+        stream.synchronize()
+        y1 = d_y.cpu().numpy()
+    assert st.status(sp) == 0
+    want0, _ = oracle_stack(orc, layers, x0, threads=16)
+    want1, _ = oracle_stack(orc, layers, x1, threads=16)
+    assert_bits_equal(y_stream, want0, "stream launches vs oracle")
+    assert_bits_equal(y1, want1, "graph replay on new input vs oracle")
+    st.close()
+
+
 def test_stack_expert_sharding_union_equals_single_device(orc, synth):
     """Two half-stacks (experts 0-15 and 16-31) on the same GPU: each fills only its
     rows of the grouped buffer; their union reproduces the unsharded result."""
