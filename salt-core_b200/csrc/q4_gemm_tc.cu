@@ -413,14 +413,23 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps) {
                         }
                     }
                     if (ok) {
+                        // one decision for all matrices of the chunk: the conversions of gate and up then sit
+                        // in one basic block and interleave
+                        bool half_math = !SPLIT;
 #pragma unroll
-                        for (int m = 0; m < NMAT; m++) {
-                            uint8_t* dst = st + m * NPART * TC_A_BYTES + a_off;
-                            if (!SPLIT && fp16_path_ok(cur_s[m], cur_b[m]))
-                                dequant_half_chunk_f16(cur[m], cur_s[m], cur_b[m], dst, a_c0, a_sw);
-                            else
+                        for (int m = 0; m < NMAT; m++) half_math = half_math && fp16_path_ok(cur_s[m], cur_b[m]);
+                        if (half_math) {
+#pragma unroll
+                            for (int m = 0; m < NMAT; m++)
+                                dequant_half_chunk_f16(cur[m], cur_s[m], cur_b[m], st + m * NPART * TC_A_BYTES + a_off,
+                                                       a_c0, a_sw);
+                        } else {
+#pragma unroll
+                            for (int m = 0; m < NMAT; m++) {
+                                uint8_t* dst = st + m * NPART * TC_A_BYTES + a_off;
                                 dequant_half_chunk_f32<SPLIT>(mg, cur[m], cur_s[m], cur_b[m], dst, dst + TC_A_BYTES,
                                                               a_c0, a_sw);
+                            }
                         }
                     }
                     // generic-proxy writes -> visible to the tensor core (async proxy), then one
