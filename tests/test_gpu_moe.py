@@ -167,7 +167,7 @@ def test_stack_small_geometry_golden(synth):
     st.close()
 
 
-@pytest.mark.parametrize("B", [1, 4, 16, 64])
+@pytest.mark.parametrize("B", [1, 2, 4, 8, 9, 16, 33, 64])
 def test_stack_cfg2_layer_decode_sweep_vs_oracle(orc, synth, B):
     layer = synth.make_q4_moe_layer(2, )          # H=2816, E=128, top-8, M=704
     x = synth.make_tokens(100 + B, B, layer.hidden)
@@ -260,3 +260,30 @@ def test_stack_expert_sharding_union_equals_single_device(orc, synth):
     assert_bits_equal(d_y.cpu().numpy(), want, "sharded union")
     for st in halves:
         st.close()
+
+
+def test_stack_eight_way_sharding_bench_geometry(orc, synth):
+    """The bench layer (128 experts, top-8) cut into eight expert ranges, 8 tokens: what every rank of
+    an 8-GPU run computes, here one range after the other over one shared grouped buffer."""
+    import torch
+    H, M, E, K, B = 2816, 704, 128, 8, 8
+    layer = synth.make_q4_moe_layer_bulk(64)
+    x = synth.make_tokens(65, B, H)
+    want, _, _ = orc.moe_layer_q4(layer, x, threads=16)
+    sm = stack_mod()
+    d_x = torch.from_numpy(x).cuda()
+    shared = torch.zeros(B * K * H, dtype=torch.float32, device="cuda")
+    parts = []
+    for r in range(8):
+        st = sm.MoeStack(B, H, M, E, K, expert_begin=r * 16, expert_end=(r + 1) * 16)
+        st.add_layer(layer)
+        assert st.set_grouped_out(shared.data_ptr(), shared.numel() * 4) == 0
+        assert st.layer_experts(0, d_x.data_ptr(), B) == 0
+        parts.append(st)
+    d_y = torch.zeros(B, H, dtype=torch.float32, device="cuda")
+    assert parts[3].layer_combine(0, B, d_y.data_ptr(), apply_norm=False) == 0
+    assert all(st.status() == 0 for st in parts)
+    assert_bits_equal(d_y.cpu().numpy(), want, "eight-way sharded union")
+    for st in parts:
+        st.close()
+
