@@ -112,6 +112,27 @@ class Oracle:
                                   1 if with_scale else 0)
         return rc, out
 
+    def residual_postnorm(self, residual, branch, weight, eps):
+        residual = _f32(residual)
+        out = np.empty_like(residual)
+        rc = self.lib.orc_residual_postnorm(_p(out), _p(residual), _p(_f32(branch)), _p(_f32(weight)),
+                                            residual.size, C.c_float(eps))
+        return rc, out
+
+    def parallel_ffn_combine(self, residual, dense, routed, dense_w, routed_w, final_w, scalar, eps):
+        residual = _f32(residual)
+        out = np.empty_like(residual)
+        scratch = np.empty(2 * residual.size, np.float32)
+        rc = self.lib.orc_parallel_ffn_combine(_p(out), _p(residual), _p(_f32(dense)), _p(_f32(routed)),
+                                               _p(_f32(dense_w)), _p(_f32(routed_w)), _p(_f32(final_w)),
+                                               C.c_float(scalar), residual.size, C.c_float(eps), _p(scratch))
+        return rc, out, scratch
+
+    def softcap(self, logits, cap):
+        out = _f32(logits).copy()
+        rc = self.lib.orc_softcap(_p(out), out.size, C.c_float(cap))
+        return rc, out
+
     def router_input(self, x, scale, eps):
         x = _f32(x)
         out = np.empty_like(x)
@@ -286,6 +307,27 @@ class Reference:
         w = _f32(weight) if weight is not None else None
         rc = self.lib.salt_gemma4_rmsnorm(_p(out), _p(x), _p(w), x.size, C.c_float(eps),
                                           1 if with_scale else 0)
+        return rc, out
+
+    def residual_postnorm(self, residual, branch, weight, eps):
+        residual = _f32(residual)
+        out = np.empty_like(residual)
+        rc = self.lib.salt_gemma4_residual_postnorm(_p(out), _p(residual), _p(_f32(branch)), _p(_f32(weight)),
+                                            residual.size, C.c_float(eps))
+        return rc, out
+
+    def parallel_ffn_combine(self, residual, dense, routed, dense_w, routed_w, final_w, scalar, eps):
+        residual = _f32(residual)
+        out = np.empty_like(residual)
+        scratch = np.empty(2 * residual.size, np.float32)
+        rc = self.lib.salt_gemma4_parallel_ffn_combine(_p(out), _p(residual), _p(_f32(dense)), _p(_f32(routed)),
+                                               _p(_f32(dense_w)), _p(_f32(routed_w)), _p(_f32(final_w)),
+                                               C.c_float(scalar), residual.size, C.c_float(eps), _p(scratch))
+        return rc, out, scratch
+
+    def softcap(self, logits, cap):
+        out = _f32(logits).copy()
+        rc = self.lib.salt_gemma4_softcap(_p(out), out.size, C.c_float(cap))
         return rc, out
 
     def router_input(self, x, scale, eps):

@@ -368,6 +368,89 @@ int orc_router_input(float *out, const float *x, const float *scale, int H,
     return 0;
 }
 
+/* gemma4.c:188-213 (salt_gemma4_residual_postnorm): the branch is RMS-normalised with its
+ * post-norm weight, then added to the residual: out = residual + (branch*inv)*w.
+ * Non-finite inputs or outputs reject the whole call. */
+int orc_residual_postnorm(float *out, const float *residual, const float *branch,
+                          const float *weight, int n, float eps) {
+    float ss = 0.0f, inv, mean;
+    if (!out || !residual || !branch || !weight || n < 1) return -1;
+    for (int i = 0; i < n; i++)
+        if (!isfinite(residual[i])) return -1;
+    for (int i = 0; i < n; i++) {
+        float sq;
+        if (!isfinite(branch[i]) || !isfinite(weight[i])) return -1;
+        sq = branch[i] * branch[i];
+        ss = ss + sq;
+    }
+    mean = ss / (float)n;
+    mean = mean + eps;
+    inv = orc_pow_neg_half(mean);
+    if (!isfinite(inv)) return -1;
+    for (int i = 0; i < n; i++) {
+        float y = branch[i] * inv;
+        y = y * weight[i];
+        if (!isfinite(y)) return -1;
+        y = residual[i] + y;
+        if (!isfinite(y)) return -1;
+    }
+    for (int i = 0; i < n; i++) {
+        float y = branch[i] * inv;
+        y = y * weight[i];
+        out[i] = residual[i] + y;
+    }
+    return 0;
+}
+
+/* gemma4.c:215-276 (salt_gemma4_parallel_ffn_combine): the consumer of the routed-expert
+ * output.  sum = RMSNorm(dense, wd) + RMSNorm(routed, wr); final = RMSNorm(sum, wf);
+ * out = (residual + final) * layer_scalar.  scratch_2n receives sum | final as the reference
+ * leaves them. */
+int orc_parallel_ffn_combine(float *out, const float *residual, const float *dense,
+                             const float *routed, const float *dense_w, const float *routed_w,
+                             const float *final_w, float layer_scalar, int n, float eps,
+                             float *scratch_2n) {
+    float *sum, *fin;
+    if (!out || !residual || !dense || !routed || !dense_w || !routed_w || !final_w ||
+        !scratch_2n || n < 1 || !isfinite(layer_scalar))
+        return -1;
+    for (int i = 0; i < n; i++)
+        if (!isfinite(residual[i])) return -1;
+    sum = scratch_2n;
+    fin = scratch_2n + n;
+    if (orc_rmsnorm(sum, dense, dense_w, n, eps, 1) != 0 ||
+        orc_rmsnorm(fin, routed, routed_w, n, eps, 1) != 0)
+        return -1;
+    for (int i = 0; i < n; i++) {
+        float c = sum[i] + fin[i];
+        if (!isfinite(c)) return -1;
+        sum[i] = c;
+    }
+    if (orc_rmsnorm(fin, sum, final_w, n, eps, 1) != 0) return -1;
+    for (int i = 0; i < n; i++) {
+        float y = residual[i] + fin[i];
+        y = y * layer_scalar;
+        if (!isfinite(y)) return -1;
+    }
+    for (int i = 0; i < n; i++) {
+        float y = residual[i] + fin[i];
+        out[i] = y * layer_scalar;
+    }
+    return 0;
+}
+
+/* gemma4.c:278-286 (salt_gemma4_softcap): logits = cap * tanh(logits / cap), in place. */
+int orc_softcap(float *logits, int n, float cap) {
+    if (!logits || n < 1 || !(cap > 0.0f) || !isfinite(cap)) return -1;
+    for (int i = 0; i < n; i++)
+        if (!isfinite(logits[i])) return -1;
+    for (int i = 0; i < n; i++) {
+        float q = logits[i] / cap;
+        logits[i] = cap * orc_tanhf(q);
+    }
+    return 0;
+}
+
 /* src/kernels.c:98-106 (salt_router_scores): one serial chain per expert,
  * acc = fl(acc + fl(W[e][c]*x[c])), then + bias[e] (0 when absent). */
 void orc_router_scores(const float *W, const float *bias, int E, int H,

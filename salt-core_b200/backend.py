@@ -13,6 +13,7 @@ from ._lib import load_library
 
 RESOURCE_ARENA, RESOURCE_TRUNK, RESOURCE_EXPERT_LAYER = 0, 1, 2
 EXACT_RMSNORM, EXACT_TOPK, EXACT_ROUTER_INPUT = 1, 2, 6
+EXACT_RESIDUAL_POSTNORM, EXACT_PARALLEL_COMBINE, EXACT_SOFTCAP = 3, 4, 5
 ADDRESS_REGISTERED_PERSISTENT = 2
 
 

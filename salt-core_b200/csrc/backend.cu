@@ -10,6 +10,7 @@
 // CPU execution path in this file: a call that cannot run on the device
 // returns -1.
 #include <cuda_runtime.h>
+#include <cmath>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -947,7 +948,7 @@ int salt_gpu_exact_cells(const SaltGpuExactCell* cells, int count) {
         return -1;
     for (int i = 0; i < count; i++) {
         const SaltGpuExactCell& c = cells[i];
-        void* v[4] = {nullptr, nullptr, nullptr, nullptr};
+        void* v[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
         if (c.n == 0) return -1;
         switch (c.kind) {
             case SALT_GPU_EXACT_RMSNORM:
@@ -978,8 +979,36 @@ int salt_gpu_exact_cells(const SaltGpuExactCell* cells, int count) {
                                                  c.eps, c.scalar, B.d_status, B.stream), "router-input cell"))
                     return -1;
                 break;
+            case SALT_GPU_EXACT_RESIDUAL_POSTNORM:
+                for (int k = 0; k < 4; k++)
+                    if (!cell_view(c.views[k], c.offsets[k], c.n, &v[k])) return -1;
+                if (!(c.eps >= 0.0f) || !std::isfinite(c.eps) ||
+                    !cuda_ok(launch_residual_postnorm((const float*)v[0], (const float*)v[1], (const float*)v[2],
+                                                      (float*)v[3], 1, (int)c.n, c.eps, B.d_status, B.stream),
+                             "residual cell"))
+                    return -1;
+                break;
+            case SALT_GPU_EXACT_PARALLEL_COMBINE:
+                for (int k = 0; k < 8; k++) {
+                    const size_t elements = k == 6 ? (size_t)c.n * 2u : c.n;
+                    if (!cell_view(c.views[k], c.offsets[k], elements, &v[k])) return -1;
+                }
+                if (!(c.eps >= 0.0f) || !std::isfinite(c.eps) || !std::isfinite(c.scalar) ||
+                    !cuda_ok(launch_parallel_combine((const float*)v[0], (const float*)v[1], (const float*)v[2],
+                                                     (const float*)v[3], (const float*)v[4], (const float*)v[5],
+                                                     (float*)v[6], (float*)v[6] + c.n, (float*)v[7], 1, (int)c.n,
+                                                     c.eps, c.scalar, B.d_status, B.stream),
+                             "combine cell"))
+                    return -1;
+                break;
+            case SALT_GPU_EXACT_SOFTCAP:
+                if (!(c.scalar > 0.0f) || !std::isfinite(c.scalar) ||
+                    !cell_view(c.views[0], c.offsets[0], c.n, &v[0]) ||
+                    !cuda_ok(launch_softcap((float*)v[0], (int)c.n, c.scalar, B.d_status, B.stream), "softcap cell"))
+                    return -1;
+                break;
             default:
-                return -1;  // residual/post-norm, combine and softcap cells are outside the MoE-FFN path
+                return -1;
         }
         count_launches(1);
     }

@@ -65,6 +65,16 @@ cudaError_t launch_rmsnorm(const float* x, const float* weight, float* y, int ro
 // out = ((x * inv) * scale) * root; root <= 0 selects 1/sqrt(n)
 cudaError_t launch_router_input(const float* x, const float* scale, float* out, int rows, int n, float eps,
                                 float root, int* status, cudaStream_t stream);
+// Consumers of the routed-expert output (reference gemma4.c:188-286), rows independent:
+// out = residual + RMSNorm(branch)*weight
+cudaError_t launch_residual_postnorm(const float* residual, const float* branch, const float* weight, float* out,
+                                     int rows, int n, float eps, int* status, cudaStream_t stream);
+// out = (residual + RMSNorm(RMSNorm(dense)*wd + RMSNorm(routed)*wr)*wf) * scalar; scratch_a/b = [rows][n] each
+cudaError_t launch_parallel_combine(const float* residual, const float* dense, const float* routed, const float* wd,
+                                    const float* wr, const float* wf, float* scratch_a, float* scratch_b, float* out,
+                                    int rows, int n, float eps, float scalar, int* status, cudaStream_t stream);
+// logits = cap * tanh(logits / cap), in place
+cudaError_t launch_softcap(float* logits, int n, float cap, int* status, cudaStream_t stream);
 // Fused per-row glue: [ordered weighted reduce] -> [RMSNorm] -> [router input].
 struct GlueArgs {
     const float* weights;        // reduce: [rows*topk]; grouped == null skips the reduce

@@ -296,6 +296,136 @@ norm_rows_kernel(const float* __restrict__ x, const float* __restrict__ weight, 
 //   [router]  rin = ((v * inv) * scale) * (1/sqrt(n))      (gemma4.c:103-130)
 // The two sums of squares are formed in element order by block_sum_nonneg over
 // squares computed in parallel.
+// ---- consumers of the routed-expert output (exact cells) -------------------------------------
+// y = (x * inv) * w with inv = (mean(x^2) + eps)^-1/2, one row per block; sq = n floats of shared
+// memory.  Returns with y complete and visible to the whole block.
+static __device__ void norm_row_block(const float* x, const float* w, float* y, int n, float eps, float* sq,
+                                      uint32_t* scan, float* s_inv, bool& bad, int* status) {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = x[i];
+        sq[i] = __fmul_rn(v, v);
+        bad |= !finite_f(v) || !finite_f(w[i]);
+    }
+    const float ss = ordered_sum_of_squares(sq, n, bad, scan);
+    if (threadIdx.x == 0) {
+        *s_inv = pow_neg_half(__fadd_rn(__fdiv_rn(ss, (float)n), eps));
+        if (!finite_f(*s_inv)) flag(status, SB_ERR_NONFINITE);
+    }
+    __syncthreads();
+    const float inv = *s_inv;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float t = __fmul_rn(__fmul_rn(x[i], inv), w[i]);
+        bad |= !finite_f(t);
+        y[i] = t;
+    }
+    __syncthreads();
+}
+
+// out = residual + RMSNorm(branch) * weight   (models/gemma4-26b-a4b/src/gemma4.c:188-213)
+__global__ void __launch_bounds__(1024)
+residual_postnorm_rows_kernel(const float* __restrict__ residual, const float* __restrict__ branch,
+                              const float* __restrict__ weight, float* __restrict__ out, int n, float eps,
+                              int* status) {
+    extern __shared__ __align__(16) float cell_sm[];     // [n] squares, [n] normalised branch
+    __shared__ float s_inv;
+    __shared__ __align__(8) uint32_t s_scan[POSSUM_SCRATCH];
+    const size_t row = blockIdx.x;
+    float* normed = cell_sm + ((n + 3) & ~3);
+    bool bad = false;
+    norm_row_block(branch + row * n, weight, normed, n, eps, cell_sm, s_scan, &s_inv, bad, status);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float r = residual[row * n + i];
+        const float y = __fadd_rn(r, normed[i]);
+        bad |= !finite_f(r) || !finite_f(y);
+        out[row * n + i] = y;
+    }
+    if (bad) flag(status, SB_ERR_NONFINITE);
+}
+
+// sum = RMSNorm(dense)*wd + RMSNorm(routed)*wr; fin = RMSNorm(sum)*wf; out = (residual + fin) * scalar
+// (gemma4.c:215-276).  scratch_a / scratch_b receive sum / fin as the reference leaves them.
+__global__ void __launch_bounds__(1024)
+parallel_combine_rows_kernel(const float* __restrict__ residual, const float* __restrict__ dense,
+                             const float* __restrict__ routed, const float* __restrict__ wd,
+                             const float* __restrict__ wr, const float* __restrict__ wf, float* scratch_a,
+                             float* scratch_b, float* __restrict__ out, int n, float eps, float scalar, int* status) {
+    extern __shared__ __align__(16) float cell_sm[];     // [n] squares
+    __shared__ float s_inv;
+    __shared__ __align__(8) uint32_t s_scan[POSSUM_SCRATCH];
+    const size_t row = blockIdx.x;
+    float* sum = scratch_a + row * n;
+    float* fin = scratch_b + row * n;
+    bool bad = !finite_f(scalar);
+    norm_row_block(dense + row * n, wd, sum, n, eps, cell_sm, s_scan, &s_inv, bad, status);
+    norm_row_block(routed + row * n, wr, fin, n, eps, cell_sm, s_scan, &s_inv, bad, status);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float c = __fadd_rn(sum[i], fin[i]);
+        bad |= !finite_f(c);
+        sum[i] = c;
+    }
+    __syncthreads();
+    norm_row_block(sum, wf, fin, n, eps, cell_sm, s_scan, &s_inv, bad, status);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float r = residual[row * n + i];
+        const float y = __fmul_rn(__fadd_rn(r, fin[i]), scalar);
+        bad |= !finite_f(r) || !finite_f(y);
+        out[row * n + i] = y;
+    }
+    if (bad) flag(status, SB_ERR_NONFINITE);
+}
+
+// logits = cap * tanh(logits / cap), in place   (gemma4.c:278-286)
+__global__ void __launch_bounds__(256) softcap_kernel(float* __restrict__ logits, int n, float cap, int* status) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = logits[i];
+    if (!finite_f(v)) {
+        flag(status, SB_ERR_NONFINITE);
+        return;
+    }
+    logits[i] = __fmul_rn(cap, tanhf_exact(__fdiv_rn(v, cap)));
+}
+
+cudaError_t launch_residual_postnorm(const float* residual, const float* branch, const float* weight, float* out,
+                                     int rows, int n, float eps, int* status, cudaStream_t stream) {
+    if (rows < 1) return cudaSuccess;
+    const size_t smem = (size_t)(2 * ((n + 3) & ~3) + 8) * sizeof(float);
+    if (smem > 200 * 1024) return cudaErrorInvalidValue;
+    static bool configured = false;
+    if (smem > 48 * 1024 && !configured) {
+        cudaError_t e = cudaFuncSetAttribute(residual_postnorm_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             200 * 1024);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    residual_postnorm_rows_kernel<<<rows, 1024, smem, stream>>>(residual, branch, weight, out, n, eps, status);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_parallel_combine(const float* residual, const float* dense, const float* routed, const float* wd,
+                                    const float* wr, const float* wf, float* scratch_a, float* scratch_b, float* out,
+                                    int rows, int n, float eps, float scalar, int* status, cudaStream_t stream) {
+    if (rows < 1) return cudaSuccess;
+    const size_t smem = (size_t)(n + 8) * sizeof(float);
+    if (smem > 200 * 1024) return cudaErrorInvalidValue;
+    static bool configured = false;
+    if (smem > 48 * 1024 && !configured) {
+        cudaError_t e = cudaFuncSetAttribute(parallel_combine_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             200 * 1024);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    parallel_combine_rows_kernel<<<rows, 1024, smem, stream>>>(residual, dense, routed, wd, wr, wf, scratch_a, scratch_b,
+                                                               out, n, eps, scalar, status);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_softcap(float* logits, int n, float cap, int* status, cudaStream_t stream) {
+    if (n < 1) return cudaSuccess;
+    softcap_kernel<<<(n + 255) / 256, 256, 0, stream>>>(logits, n, cap, status);
+    return cudaGetLastError();
+}
+
 // Each thread owns the columns d = threadIdx.x + j * blockDim.x (j < GLUE_NV, compile
 // time) so that every global load of a phase is issued before the first use: the norm
 // weights and router scales right at the start, the rows of the expert outputs as soon as

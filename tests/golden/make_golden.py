@@ -6,7 +6,8 @@ reference sources compiled unmodified).  Every array written here is an output
 of that library; small cases also store their inputs so the fixtures do not
 depend on a PRNG implementation.
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py            # everything
+    python tests/golden/make_golden.py cells      # only the residual / combine / softcap cells
 """
 import importlib
 import os
@@ -22,8 +23,38 @@ synth = importlib.import_module("salt-core_b200.synth")
 OUT = os.path.dirname(os.path.abspath(__file__))
 
 
+def gen_cells(ref):
+    """Consumers of the routed-expert output (reference gemma4.c:188-286): residual + post-norm,
+    parallel FFN combine, logit soft-cap.  Inputs are stored next to the outputs."""
+    rng = np.random.default_rng(20261126)
+    out = {}
+    sizes = (1, 5, 64, 257, 2816)
+    out["sizes"] = np.array(sizes)
+    for n in sizes:
+        res, dense, routed = (rng.standard_normal(n).astype(np.float32) * np.float32(sc) for sc in (1.0, 3.0, 0.4))
+        wd, wr, wf = ((1.0 + 0.2 * rng.standard_normal(n)).astype(np.float32) for _ in range(3))
+        rc, y, scratch = ref.parallel_ffn_combine(res, dense, routed, wd, wr, wf, 0.8125, 1e-6)
+        assert rc == 0
+        rc2, r2 = ref.residual_postnorm(res, dense, wd, 1e-6)
+        assert rc2 == 0
+        out.update({f"n{n}_res": res, f"n{n}_dense": dense, f"n{n}_routed": routed, f"n{n}_wd": wd,
+                    f"n{n}_wr": wr, f"n{n}_wf": wf, f"n{n}_combine": y, f"n{n}_scratch": scratch,
+                    f"n{n}_residual": r2})
+    logits = np.concatenate([rng.standard_normal(3000) * 25.0, np.linspace(-400, 400, 801),
+                             [0.0, -0.0, 1e-30, -1e-30, 29.999, 30.0, 300.0, -300.0]]).astype(np.float32)
+    rc, capped = ref.softcap(logits, 30.0)
+    assert rc == 0
+    out.update(softcap_in=logits, softcap_out=capped, softcap_cap=np.float32(30.0),
+               scalar=np.float32(0.8125), eps=np.float32(1e-6))
+    np.savez_compressed(os.path.join(OUT, "cells.npz"), **out)
+
+
 def main():
     ref = oracle.Reference()
+    if len(sys.argv) > 1 and sys.argv[1] == "cells":
+        gen_cells(ref)
+        print("cells.npz written to", OUT)
+        return
     rng = np.random.default_rng(20261125)
 
     # --- scalar math tables -------------------------------------------
@@ -142,6 +173,7 @@ def main():
     y, sel_, w_ = ref.moe_layer_q4(layer, xt, threads=4)
     np.savez_compressed(os.path.join(OUT, "moe_layer_small.npz"), y=y, sel=sel_, w=w_,
                         meta=np.array([7, 8, 6, 256, 128, 16, 4]))
+    gen_cells(ref)
     print("golden fixtures written to", OUT)
 
 

@@ -76,6 +76,57 @@ def test_ordered_sum_of_squares_adversarial_rows(orc, kind):
     assert g.shared_buffer_free(buf) == 0
 
 
+def test_exact_cells_residual_combine_softcap_golden(orc):
+    """The consumers of the routed-expert output (reference gemma4.c:188-286) through
+    salt_gpu_exact_cells, against the golden vectors and, at larger sizes, the oracle."""
+    g, bm, fx = gpu(), backend_mod(), golden("cells.npz")
+    eps, scalar = float(fx["eps"]), float(fx["scalar"])
+    nmax = 5120
+    rc, buf = g.shared_buffer_alloc(4 * (9 * nmax + 16))
+    assert rc == 0
+    f = buf.array(np.float32)
+    o = [k * nmax for k in range(9)]          # residual, dense, routed, wd, wr, wf, scratch (2n), out
+
+    def run(n, res, dense, routed, wd, wr, wf):
+        for off, arr in zip(o[:6], (res, dense, routed, wd, wr, wf)):
+            f[off:off + n] = arr
+        cell = bm.exact_cell(bm.EXACT_PARALLEL_COMBINE, [buf] * 8, [o[0], o[1], o[2], o[3], o[4], o[5], o[6], o[8]],
+                             n, eps=eps, scalar=scalar)
+        assert g.exact_cells([cell]) == 0
+        combine, scratch = f[o[8]:o[8] + n].copy(), f[o[6]:o[6] + 2 * n].copy()
+        cell = bm.exact_cell(bm.EXACT_RESIDUAL_POSTNORM, [buf] * 4, [o[0], o[1], o[3], o[8]], n, eps=eps)
+        assert g.exact_cells([cell]) == 0
+        return combine, scratch, f[o[8]:o[8] + n].copy()
+
+    for n in (int(v) for v in fx["sizes"]):
+        a = [fx[f"n{n}_{k}"] for k in ("res", "dense", "routed", "wd", "wr", "wf")]
+        combine, scratch, residual = run(n, *a)
+        assert_bits_equal(combine, fx[f"n{n}_combine"], f"combine cell n={n}")
+        assert_bits_equal(scratch, fx[f"n{n}_scratch"], f"combine scratch n={n}")
+        assert_bits_equal(residual, fx[f"n{n}_residual"], f"residual cell n={n}")
+    rng = np.random.default_rng(11)
+    for n in (1000, 4096, 4097, 5120):       # beyond the fixtures: block-parallel and serial sum paths
+        a = [rng.standard_normal(n).astype(np.float32) for _ in range(3)] + \
+            [(1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32) for _ in range(3)]
+        combine, scratch, residual = run(n, *a)
+        rc, want, want_scratch = orc.parallel_ffn_combine(*a, scalar, eps)
+        assert rc == 0
+        assert_bits_equal(combine, want, f"combine cell vs oracle n={n}")
+        assert_bits_equal(scratch, want_scratch, f"combine scratch vs oracle n={n}")
+        assert_bits_equal(residual, orc.residual_postnorm(a[0], a[1], a[3], eps)[1], f"residual cell vs oracle n={n}")
+    logits = fx["softcap_in"]
+    f[0:logits.size] = logits
+    cell = bm.exact_cell(bm.EXACT_SOFTCAP, [buf], [0], logits.size, scalar=float(fx["softcap_cap"]))
+    assert g.exact_cells([cell]) == 0
+    assert_bits_equal(f[0:logits.size].copy(), fx["softcap_out"], "softcap cell")
+    # rejections: non-finite input, non-positive cap
+    f[5] = np.nan
+    assert g.exact_cells([cell]) == -1
+    cell = bm.exact_cell(bm.EXACT_SOFTCAP, [buf], [0], 16, scalar=0.0)
+    assert g.exact_cells([cell]) == -1
+    assert g.shared_buffer_free(buf) == 0
+
+
 def test_route_group_device_golden_and_reference_kat(orc):
     import torch
     g = gpu()

@@ -57,6 +57,30 @@ def test_router_chain(orc):
     assert (g["logits"][:, 3] == g["logits"][:, 7]).all()
 
 
+def test_residual_combine_softcap_cells(orc):
+    g = golden("cells.npz")
+    eps, scalar = float(g["eps"]), float(g["scalar"])
+    for n in (int(v) for v in g["sizes"]):
+        a = {k: g[f"n{n}_{k}"] for k in ("res", "dense", "routed", "wd", "wr", "wf")}
+        rc, y, scratch = orc.parallel_ffn_combine(a["res"], a["dense"], a["routed"], a["wd"], a["wr"], a["wf"],
+                                                  scalar, eps)
+        assert rc == 0
+        assert_bits_equal(y, g[f"n{n}_combine"], f"parallel combine n={n}")
+        assert_bits_equal(scratch, g[f"n{n}_scratch"], f"parallel combine scratch n={n}")
+        rc, r = orc.residual_postnorm(a["res"], a["dense"], a["wd"], eps)
+        assert rc == 0
+        assert_bits_equal(r, g[f"n{n}_residual"], f"residual post-norm n={n}")
+    rc, capped = orc.softcap(g["softcap_in"], float(g["softcap_cap"]))
+    assert rc == 0
+    assert_bits_equal(capped, g["softcap_out"], "softcap")
+    # rejections, as the reference functions return -1
+    bad = g["n64_res"].copy()
+    bad[3] = np.inf
+    assert orc.residual_postnorm(bad, g["n64_dense"], g["n64_wd"], eps)[0] == -1
+    assert orc.softcap(bad, 30.0)[0] == -1
+    assert orc.softcap(g["n64_res"], 0.0)[0] == -1
+
+
 def test_grouping_and_reduce(orc):
     g = golden("grouping.npz")
     rows, topk = g["selected"].shape
