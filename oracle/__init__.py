@@ -112,6 +112,12 @@ class Oracle:
                                   1 if with_scale else 0)
         return rc, out
 
+    def q8_matvec(self, vals, scales, biases, R, Ccols, x):
+        y = np.empty(R, np.float32)
+        self.lib.orc_q8_matvec(_p(vals), _p(scales), _p(biases) if biases is not None else None, R, Ccols,
+                               _p(_f32(x)), _p(y))
+        return y
+
     def residual_postnorm(self, residual, branch, weight, eps):
         residual = _f32(residual)
         out = np.empty_like(residual)
@@ -308,6 +314,12 @@ class Reference:
         rc = self.lib.salt_gemma4_rmsnorm(_p(out), _p(x), _p(w), x.size, C.c_float(eps),
                                           1 if with_scale else 0)
         return rc, out
+
+    def q8_matvec(self, vals, scales, biases, R, Ccols, x):
+        y = np.empty(R, np.float32)
+        self.lib.salt_q8_matvec(_p(vals), _p(scales), _p(biases) if biases is not None else None, R, Ccols,
+                               _p(_f32(x)), _p(y))
+        return y
 
     def residual_postnorm(self, residual, branch, weight, eps):
         residual = _f32(residual)

@@ -368,6 +368,29 @@ int orc_router_input(float *out, const float *x, const float *scale, int H,
     return 0;
 }
 
+/* src/kernels.c:343-369 (salt_q8_matvec): affine 8-bit, one byte per element, bf16 scale and
+ * bias per 64 consecutive elements of the flattened matrix (a row may straddle groups).
+ * One serial chain per row: acc = fl(acc + fl(d * x[c])), d = fl(fl(q*s) + b), q = 0..255. */
+void orc_q8_matvec(const void *vals, const void *scales, const void *biases, int R, int C,
+                   const float *x, float *y) {
+    const unsigned char *b8 = (const unsigned char *)vals;
+    for (int r = 0; r < R; r++) {
+        float acc = 0.0f;
+        for (int c = 0; c < C; c++) {
+            size_t k = (size_t)r * (size_t)C + (size_t)c;
+            size_t g = k >> 6;
+            float s = orc_bf16(scales, g);
+            float b = biases ? orc_bf16(biases, g) : 0.0f;
+            float d = (float)b8[k] * s;
+            float p;
+            d = d + b;
+            p = d * x[c];
+            acc = acc + p;
+        }
+        y[r] = acc;
+    }
+}
+
 /* gemma4.c:188-213 (salt_gemma4_residual_postnorm): the branch is RMS-normalised with its
  * post-norm weight, then added to the residual: out = residual + (branch*inv)*w.
  * Non-finite inputs or outputs reject the whole call. */

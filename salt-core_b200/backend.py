@@ -144,6 +144,15 @@ class SaltGpu:
         return self.lib.salt_gpu_q4_batch(_ptr_array(vals), _ptr_array(scales), _ptr_array(biases),
                                           _ptr_array(xs), _ptr_array(ys), (C.c_void_p * n)(*ids), rj, Ccols, n)
 
+    def q8_matvec(self, vals, scales, biases, R, Ccols, x, y):
+        return self.lib.salt_gpu_q8_matvec(ptr(vals), ptr(scales), ptr(biases), R, Ccols, ptr(x), ptr(y))
+
+    def q8_batch(self, vals, scales, biases, xs, ys, ids, Rj, Ccols):
+        n = len(vals)
+        rj = (C.c_int * n)(*Rj)
+        return self.lib.salt_gpu_q8_batch(_ptr_array(vals), _ptr_array(scales), _ptr_array(biases),
+                                          _ptr_array(xs), _ptr_array(ys), (C.c_void_p * n)(*ids), rj, Ccols, n)
+
     def proj_batch(self, vals, scales, biases, R, Ccols, xs, ys, key):
         """xs [B][C], ys [B][R] numpy arrays (row pointers are passed, as the reference does)."""
         B = xs.shape[0]

@@ -57,9 +57,9 @@ static bool in_range(const Resource& r, const void* p, size_t nbytes, uint64_t* 
 }
 
 static bool q4_sizes(int bits, int R, int C, size_t* vbytes, size_t* gbytes) {
-    if (bits != 4 || R < 1 || C < 1) return false;
+    if ((bits != 4 && bits != 8) || R < 1 || C < 1) return false;
     uint64_t elems = (uint64_t)(uint32_t)R * (uint64_t)(uint32_t)C;
-    *vbytes = (size_t)(((elems + 7) / 8) * 4);
+    *vbytes = bits == 4 ? (size_t)(((elems + 7) / 8) * 4) : (size_t)(((elems + 3) / 4) * 4);
     *gbytes = (size_t)(((elems + 63) / 64) * 2);
     return true;
 }
@@ -96,15 +96,15 @@ static bool materialize(Tensor& t, const Resource& r) {
 // first sight of a tensor lying inside an active resource (registers it); in
 // non-mapped-only mode, a private device copy keyed by id ("arena").
 static Tensor* resolve_q4(const void* key, const void* vals, const void* scales, const void* biases, int R, int C,
-                          int* kind_out) {
+                          int* kind_out, int bits = 4) {
     Backend& B = g_backend;
     size_t vb, gb;
-    if (!key || !vals || !scales || !q4_sizes(4, R, C, &vb, &gb)) return nullptr;
+    if (!key || !vals || !scales || !q4_sizes(bits, R, C, &vb, &gb)) return nullptr;
     auto it = B.tensors.find(key);
     if (it != B.tensors.end()) {
         Tensor& t = it->second;
         Resource* r = live_resource(t.kind, t.id);
-        if (!r || t.bits != 4 || t.R != R || t.C != C || r->host + t.voff != (const uint8_t*)vals ||
+        if (!r || t.bits != bits || t.R != R || t.C != C || r->host + t.voff != (const uint8_t*)vals ||
             r->host + t.soff != (const uint8_t*)scales || (biases && r->host + t.boff != (const uint8_t*)biases))
             return nullptr;
         if (!materialize(t, *r)) return nullptr;
@@ -117,7 +117,7 @@ static Tensor* resolve_q4(const void* key, const void* vals, const void* scales,
             !biases || !in_range(r, biases, gb, &bo))
             continue;
         Tensor t;
-        t.kind = r.kind; t.id = r.id; t.bits = 4; t.R = R; t.C = C;
+        t.kind = r.kind; t.id = r.id; t.bits = bits; t.R = R; t.C = C;
         t.voff = vo; t.soff = so; t.boff = bo; t.vbytes = vb; t.gbytes = gb;
         Tensor& slot = B.tensors[key] = t;
         if (!materialize(slot, r)) { B.tensors.erase(key); return nullptr; }
@@ -126,9 +126,9 @@ static Tensor* resolve_q4(const void* key, const void* vals, const void* scales,
     }
     if (B.mapped_only || !biases) return nullptr;
     auto at = B.arena.find(key);
-    if (at == B.arena.end() || at->second.R != R || at->second.C != C) {
+    if (at == B.arena.end() || at->second.R != R || at->second.C != C || at->second.bits != bits) {
         Tensor t;
-        t.kind = SALT_GPU_RESOURCE_ARENA; t.bits = 4; t.R = R; t.C = C; t.vbytes = vb; t.gbytes = gb;
+        t.kind = SALT_GPU_RESOURCE_ARENA; t.bits = bits; t.R = R; t.C = C; t.vbytes = vb; t.gbytes = gb;
         void* dv = nullptr; void* ds = nullptr; void* db = nullptr;
         if (!cuda_ok(cudaMalloc(&dv, vb + 16), "arena") || !cuda_ok(cudaMalloc(&ds, gb + 16), "arena") ||
             !cuda_ok(cudaMalloc(&db, gb + 16), "arena") ||
@@ -163,13 +163,15 @@ bool stage_reserve(size_t x_floats, size_t y_floats, size_t mid_floats, size_t j
 }
 
 // Run descriptor jobs (already in B.h_jobs[0..n)) and wait.
-static bool run_jobs(int njobs, int max_rows, int max_tok, int C, int nmat, bool aligned) {
+static bool run_jobs(int njobs, int max_rows, int max_tok, int C, int nmat, bool aligned, int bits = 4) {
     Backend& B = g_backend;
     if (!cuda_ok(cudaMemcpyAsync(B.d_jobs, B.h_jobs, (size_t)njobs * sizeof(Q4Job), cudaMemcpyHostToDevice,
                                  B.stream), "job upload"))
         return false;
-    if (!cuda_ok(launch_q4_jobs(B.d_jobs, njobs, nullptr, max_rows, max_tok, C, nmat, aligned, B.stream),
-                 "q4 launch"))
+    if (bits == 8) {
+        if (!cuda_ok(launch_q8_jobs(B.d_jobs, njobs, max_rows, max_tok, C, B.stream), "q8 launch")) return false;
+    } else if (!cuda_ok(launch_q4_jobs(B.d_jobs, njobs, nullptr, max_rows, max_tok, C, nmat, aligned, B.stream),
+                        "q4 launch"))
         return false;
     count_launches(1);
     return true;
@@ -571,11 +573,11 @@ int salt_gpu_selected_resource_unbind(int slot, uint64_t logical_id) {
 // affine-Q4 compute with host pointers
 // ------------------------------------------------------------------------
 static int q4_same_weight(const void* key, const uint32_t* vals, const uint16_t* scales, const uint16_t* biases,
-                          int R, int C, int Bt, const float* const* xs, float* const* ys) {
+                          int R, int C, int Bt, const float* const* xs, float* const* ys, int bits = 4) {
     Backend& B = g_backend;
     int kind = 0;
     if (!B.ready || R < 1 || C < 1 || Bt < 1 || !xs || !ys) return -1;
-    Tensor* t = resolve_q4(key, vals, scales, biases, R, C, &kind);
+    Tensor* t = resolve_q4(key, vals, scales, biases, R, C, &kind, bits);
     if (!t) {
         if (B.mapped_only) B.stats.mapped_only_misses++;
         return -1;
@@ -591,7 +593,7 @@ static int q4_same_weight(const void* key, const uint32_t* vals, const uint16_t*
         return -1;
     fill_job(B.h_jobs[0], *t, B.d_x, B.d_y, Bt, C, R);
     const bool aligned = (C % 64) == 0;
-    if (!run_jobs(1, R, Bt, C, 1, aligned) ||
+    if (!run_jobs(1, R, Bt, C, 1, aligned, bits) ||
         !cuda_ok(cudaMemcpyAsync(B.h_y, B.d_y, (size_t)Bt * R * sizeof(float), cudaMemcpyDeviceToHost, B.stream),
                  "y download") ||
         !cuda_ok(cudaStreamSynchronize(B.stream), "sync"))
@@ -617,9 +619,9 @@ int salt_gpu_proj_batch(const uint32_t* vals, const uint16_t* scales, const uint
     return q4_same_weight(id ? id : vals, vals, scales, biases, R, C, Bt, xs, ys);
 }
 
-int salt_gpu_q4_batch(const uint32_t* const* vals, const uint16_t* const* scales, const uint16_t* const* biases,
-                      const float* const* xs, float* const* ys, const void* const* ids, const int* Rj, int C,
-                      int njobs) {
+static int q_batch(int bits, const uint32_t* const* vals, const uint16_t* const* scales,
+                   const uint16_t* const* biases, const float* const* xs, float* const* ys, const void* const* ids,
+                   const int* Rj, int C, int njobs) {
     Backend& B = g_backend;
     if (!B.ready || !vals || !scales || !biases || !xs || !ys || !ids || !Rj || C < 1 || njobs < 1 ||
         (size_t)njobs > B.job_cap)
@@ -635,7 +637,7 @@ int salt_gpu_q4_batch(const uint32_t* const* vals, const uint16_t* const* scales
     for (int j = 0; j < njobs;) {
         if (!vals[j] || !scales[j] || !biases[j] || !xs[j] || !ys[j] || Rj[j] < 1) return -1;
         int kind = 0;
-        Tensor* t = resolve_q4(ids[j], vals[j], scales[j], biases[j], Rj[j], C, &kind);
+        Tensor* t = resolve_q4(ids[j], vals[j], scales[j], biases[j], Rj[j], C, &kind, bits);
         if (!t) {
             if (B.mapped_only) B.stats.mapped_only_misses++;
             return -1;
@@ -667,7 +669,7 @@ int salt_gpu_q4_batch(const uint32_t* const* vals, const uint16_t* const* scales
     }
     if (!cuda_ok(cudaMemcpyAsync(B.d_x, B.h_x, x_floats * sizeof(float), cudaMemcpyHostToDevice, B.stream),
                  "x upload") ||
-        !run_jobs(ndesc, max_rows, max_tok, C, 1, (C % 64) == 0) ||
+        !run_jobs(ndesc, max_rows, max_tok, C, 1, (C % 64) == 0, bits) ||
         !cuda_ok(cudaMemcpyAsync(B.h_y, B.d_y, y_floats * sizeof(float), cudaMemcpyDeviceToHost, B.stream),
                  "y download") ||
         !cuda_ok(cudaStreamSynchronize(B.stream), "sync"))
@@ -677,6 +679,28 @@ int salt_gpu_q4_batch(const uint32_t* const* vals, const uint16_t* const* scales
     B.stats.direct_output_batches++;
     B.stats.direct_output_jobs += (uint64_t)njobs;
     return 0;
+}
+
+int salt_gpu_q4_batch(const uint32_t* const* vals, const uint16_t* const* scales, const uint16_t* const* biases,
+                      const float* const* xs, float* const* ys, const void* const* ids, const int* Rj, int C,
+                      int njobs) {
+    return q_batch(4, vals, scales, biases, xs, ys, ids, Rj, C, njobs);
+}
+
+// Affine 8-bit (reference src/kernels.c:343-369): same registry, staging and statistics as the
+// 4-bit entry points; the values are one byte per element.
+int salt_gpu_q8_matvec(const uint32_t* vals, const uint16_t* scales, const uint16_t* biases, int R, int C,
+                       const float* x, float* y) {
+    if (!x || !y) return -1;
+    const float* xs[1] = {x};
+    float* ys[1] = {y};
+    return q4_same_weight(vals, vals, scales, biases, R, C, 1, xs, ys, 8);
+}
+
+int salt_gpu_q8_batch(const uint32_t* const* vals, const uint16_t* const* scales, const uint16_t* const* biases,
+                      const float* const* xs, float* const* ys, const void* const* ids, const int* Rj, int C,
+                      int njobs) {
+    return q_batch(8, vals, scales, biases, xs, ys, ids, Rj, C, njobs);
 }
 
 // Jobs [first_job, first_job+job_count) of a [B][C] batch, written straight into

@@ -20,6 +20,9 @@ bool q4_tile_supported(int C);
 cudaError_t launch_q4_jobs(const Q4Job* jobs, int njobs_max, const int* njobs_dev, int max_rows, int max_tok, int C,
                            int nmat, bool aligned, cudaStream_t stream, int pdl = -1);
 
+// Affine 8-bit jobs (same descriptor; vals = one byte per element): one block per (row, token, job).
+cudaError_t launch_q8_jobs(const Q4Job* jobs, int njobs, int max_rows, int max_tok, int C, cudaStream_t stream);
+
 // ---- q4_gemm_tc.cu (tcgen05 / TMEM, tolerance path) --------------------------
 cudaError_t launch_gather_convert(const float* x, const int32_t* g2c, void* xh, void* xl, int jobs, int topk,
                                   int hidden, cudaStream_t stream);

@@ -296,6 +296,43 @@ norm_rows_kernel(const float* __restrict__ x, const float* __restrict__ weight, 
 //   [router]  rin = ((v * inv) * scale) * (1/sqrt(n))      (gemma4.c:103-130)
 // The two sums of squares are formed in element order by block_sum_nonneg over
 // squares computed in parallel.
+// ---- affine 8-bit matvec (router projections of packages that quantise the router) -----------
+// src/kernels.c:343-369: one byte per element, bf16 scale / bias per 64 consecutive elements of
+// the flattened matrix (rows may straddle groups), ONE serial chain per row:
+// acc = fl(acc + fl(d * x[c])), d = fl(fl(q*s) + b).  One block per (row, token, job): the
+// products are formed in parallel, one thread runs the chain.
+__global__ void __launch_bounds__(128) q8_rows_kernel(const Q4Job* __restrict__ jobs) {
+    extern __shared__ __align__(16) float q8_sm[];
+    const Q4Job jb = jobs[blockIdx.z];
+    const int r = blockIdx.x, tok = blockIdx.y;
+    if (r >= jb.R || tok >= jb.ntok) return;
+    const float* x = jb.x + (size_t)tok * jb.x_stride;
+    const size_t k0 = (size_t)r * (size_t)jb.C;
+    for (int c = threadIdx.x; c < jb.C; c += blockDim.x) {
+        const size_t k = k0 + (size_t)c, g = k >> 6;
+        const float s = bf16_bits_to_f32(((const uint16_t*)jb.scales)[g]);
+        const float b = jb.biases ? bf16_bits_to_f32(((const uint16_t*)jb.biases)[g]) : 0.0f;
+        const float d = __fadd_rn(__fmul_rn((float)jb.vals[k], s), b);
+        q8_sm[c] = __fmul_rn(d, x[c]);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) jb.y[(size_t)tok * jb.y_stride + r] = serial_sum(q8_sm, jb.C);
+}
+
+cudaError_t launch_q8_jobs(const Q4Job* jobs, int njobs, int max_rows, int max_tok, int C, cudaStream_t stream) {
+    if (njobs < 1 || max_rows < 1 || max_tok < 1) return cudaSuccess;
+    const size_t smem = (size_t)((C + 3) & ~3) * sizeof(float);
+    if (smem > 200 * 1024 || max_tok > 65535 || njobs > 65535) return cudaErrorInvalidValue;
+    static bool configured = false;
+    if (smem > 48 * 1024 && !configured) {
+        cudaError_t e = cudaFuncSetAttribute(q8_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    q8_rows_kernel<<<dim3(max_rows, max_tok, njobs), 128, smem, stream>>>(jobs);
+    return cudaGetLastError();
+}
+
 // ---- consumers of the routed-expert output (exact cells) -------------------------------------
 // y = (x * inv) * w with inv = (mean(x^2) + eps)^-1/2, one row per block; sq = n floats of shared
 // memory.  Returns with y complete and visible to the whole block.

@@ -5,9 +5,6 @@
 
 extern "C" {
 
-int salt_gpu_q8_matvec(const uint32_t*, const uint16_t*, const uint16_t*, int, int, const float*, float*) { return -1; }
-int salt_gpu_q8_batch(const uint32_t* const*, const uint16_t* const*, const uint16_t* const*, const float* const*,
-                      float* const*, const void* const*, const int*, int, int) { return -1; }
 int salt_gpu_bf16_matvec(const void*, int, int, const float*, float*) { return -1; }
 int salt_gpu_bf16_matvec_batch(const void*, int, int, int, const float*, float*) { return -1; }
 int salt_gpu_attention_batch(int, int, int, int, int, const SaltGpuSharedBuffer*, size_t, const SaltGpuSharedBuffer*,

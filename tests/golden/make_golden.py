@@ -48,6 +48,19 @@ def gen_cells(ref):
                scalar=np.float32(0.8125), eps=np.float32(1e-6))
     np.savez_compressed(os.path.join(OUT, "cells.npz"), **out)
 
+    # affine 8-bit matvec (reference src/kernels.c:343-369): router-sized, ragged, tiny
+    q8 = {"shapes": np.array([[128, 2816], [5, 200], [3, 64], [7, 72]])}
+    for i, (R, Cc) in enumerate(q8["shapes"]):
+        n = int(R) * int(Cc)
+        vals = rng.integers(0, 256, (n + 3) // 4 * 4, dtype=np.uint8)
+        groups = (n + 63) // 64
+        sc = (rng.uniform(0.001, 0.02, groups).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+        bi = ((-128.0 * rng.uniform(0.001, 0.02, groups)).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+        x = rng.standard_normal(int(Cc)).astype(np.float32)
+        q8.update({f"c{i}_vals": vals, f"c{i}_scales": sc, f"c{i}_biases": bi, f"c{i}_x": x,
+                   f"c{i}_y": ref.q8_matvec(vals, sc, bi, int(R), int(Cc), x)})
+    np.savez_compressed(os.path.join(OUT, "q8_matvec.npz"), **q8)
+
 
 def main():
     ref = oracle.Reference()

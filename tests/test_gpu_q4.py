@@ -137,3 +137,26 @@ def test_q4_results_are_bit_identical_run_to_run(synth):
         if first is None:
             first = ys.copy()
         assert_bits_equal(ys, first, "repeat")
+
+
+def test_q8_matvec_golden_and_batch(orc):
+    """Affine 8-bit router projections (reference src/kernels.c:343-369) through salt_gpu_q8_matvec and
+    salt_gpu_q8_batch: golden vectors, then a two-token batch on one weight against the oracle."""
+    g, fx = gpu(), golden("q8_matvec.npz")
+    g.set_mapped_only(0)
+    for i, (R, Cc) in enumerate(fx["shapes"]):
+        R, Cc = int(R), int(Cc)
+        vals, s, b, x = (np.ascontiguousarray(fx[f"c{i}_{k}"]) for k in ("vals", "scales", "biases", "x"))
+        y = np.zeros(R, np.float32)
+        assert g.q8_matvec(vals, s, b, R, Cc, x, y) == 0
+        assert_bits_equal(y, fx[f"c{i}_y"], f"q8 matvec {R}x{Cc}")
+    R, Cc = (int(v) for v in fx["shapes"][0])
+    vals, s, b = (np.ascontiguousarray(fx[f"c0_{k}"]) for k in ("vals", "scales", "biases"))
+    rng = np.random.default_rng(5)
+    xs = [rng.standard_normal(Cc).astype(np.float32) for _ in range(2)]
+    ys = [np.zeros(R, np.float32) for _ in range(2)]
+    key = vals.ctypes.data
+    assert g.q8_batch([vals, vals], [s, s], [b, b], xs, ys, [key, key], [R, R], Cc) == 0
+    for t in range(2):
+        assert_bits_equal(ys[t], orc.q8_matvec(vals, s, b, R, Cc, xs[t]), f"q8 batch token {t}")
+

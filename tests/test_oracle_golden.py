@@ -57,6 +57,13 @@ def test_router_chain(orc):
     assert (g["logits"][:, 3] == g["logits"][:, 7]).all()
 
 
+def test_q8_matvec(orc):
+    g = golden("q8_matvec.npz")
+    for i, (R, Cc) in enumerate(g["shapes"]):
+        y = orc.q8_matvec(g[f"c{i}_vals"], g[f"c{i}_scales"], g[f"c{i}_biases"], int(R), int(Cc), g[f"c{i}_x"])
+        assert_bits_equal(y, g[f"c{i}_y"], f"q8 matvec {R}x{Cc}")
+
+
 def test_residual_combine_softcap_cells(orc):
     g = golden("cells.npz")
     eps, scalar = float(g["eps"]), float(g["scalar"])
