@@ -1,13 +1,13 @@
 // Grouped affine-Q4 projections (decode and exact prefill), hand-written for sm_100a.
 //
-// q4_tile_kernel  -- the hot kernel.  Two warps per block of 8 output rows x 2
-//   matrices (fused gate/up + GeGLU) or 16 output rows x 1 matrix.  The packed
-//   rows are pulled into shared memory with 16-byte cp.async copies, one commit
-//   group per 256-column chunk, ALL chunks requested before the first is
-//   consumed, so every SM has its whole share of the weight stream in flight
-//   from the first cycle and arithmetic starts as soon as chunk 0 lands.
-//   Shared rows are padded by 16 bytes so the eight rows a warp reads at the
-//   same word index fall in eight different bank groups.
+// q4_tile16_kernel -- the hot kernel.  A block holds 8 or 16 row slots of 16 lanes each: 8 or
+//   16 output row pairs x 2 matrices (fused gate/up + GeGLU), or twice as many rows x 1 matrix.
+//   The packed rows are pulled into shared memory with 16-byte cp.async copies, one commit
+//   group per 256-column chunk, ALL chunks requested before the first is consumed, so every
+//   SM has its whole share of the weight stream in flight from the first cycle and arithmetic
+//   starts as soon as chunk 0 lands.  Shared rows are padded by 16 bytes so the rows a warp
+//   reads at the same byte index fall in different bank groups.  Launched as a programmatic
+//   dependent launch where the caller asks for it (pdl.cuh).
 // q4_generic_kernel -- any C, any byte alignment, absolute group indices
 //   (rows may straddle quantisation groups); one warp per (row, token).
 //
@@ -18,7 +18,7 @@
 
 namespace sb {
 
-// Shared-memory geometry of one block (16 weight rows).
+// Shared-memory geometry of one block (rows_a = rows of the first matrix held by a block).
 struct TileGeom {
     int row_bytes, w_stride, sc_row, sc_stride, sc_block, steps, chunk_steps, nch, tpitch;
     bool sc_padded;
