@@ -1,10 +1,11 @@
 // Router, grouping and reduction kernels of the MoE feed-forward path.
 //
-// Everything here is bit-exact against the reference CPU functions; the
-// reference arithmetic contains several chains that are serial by definition
-// (sum of squares, router logits, softmax denominators).  Those chains are kept
-// serial per row/expert and parallelism comes from running many of them side
-// by side, with the independent products computed ahead by other lanes.
+// Everything here is bit-exact against the reference CPU functions; the reference arithmetic
+// contains several chains that are serial by definition (sums of squares, router logits,
+// softmax denominators).  Signed chains (logits, denominators) are kept serial per row / expert,
+// with the independent products formed ahead by other lanes and many chains running side by
+// side; the sums of squares are reproduced by a predict-and-verify scheme (block_sum_nonneg)
+// that does most of the additions as order-free integer increments.
 #include "internal.h"
 #include "pdl.cuh"
 #include "q4_core.cuh"
