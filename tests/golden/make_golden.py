@@ -49,7 +49,7 @@ def gen_cells(ref):
     np.savez_compressed(os.path.join(OUT, "cells.npz"), **out)
 
     # affine 8-bit matvec (reference src/kernels.c:343-369): router-sized, ragged, tiny
-    q8 = {"shapes": np.array([[128, 2816], [5, 200], [3, 64], [7, 72]])}
+    q8 = {"shapes": np.array([[16, 2816], [5, 200], [3, 64], [7, 72]])}
     for i, (R, Cc) in enumerate(q8["shapes"]):
         n = int(R) * int(Cc)
         vals = rng.integers(0, 256, (n + 3) // 4 * 4, dtype=np.uint8)

@@ -159,4 +159,14 @@ def test_q8_matvec_golden_and_batch(orc):
     assert g.q8_batch([vals, vals], [s, s], [b, b], xs, ys, [key, key], [R, R], Cc) == 0
     for t in range(2):
         assert_bits_equal(ys[t], orc.q8_matvec(vals, s, b, R, Cc, xs[t]), f"q8 batch token {t}")
+    # router-sized (128 experts x 2816) seeded case against the oracle
+    R, Cc = 128, 2816
+    vals = rng.integers(0, 256, R * Cc, dtype=np.uint8)
+    groups = R * Cc // 64
+    s = (rng.uniform(0.001, 0.02, groups).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    b = ((-128.0 * rng.uniform(0.001, 0.02, groups)).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    x = rng.standard_normal(Cc).astype(np.float32)
+    y = np.zeros(R, np.float32)
+    assert g.q8_matvec(vals, s, b, R, Cc, x, y) == 0
+    assert_bits_equal(y, orc.q8_matvec(vals, s, b, R, Cc, x), "q8 router-sized")
 
