@@ -334,6 +334,27 @@ int salt_b200_stack_workspace(void *stack, SaltB200Workspace *out);
  * a buffer registered with a communication library). */
 int salt_b200_stack_set_grouped_out(void *stack, void *device_buffer, size_t nbytes);
 
+/* The dense branch and the norms that make a MoE layer the reference model's whole feed-forward
+ * block (models/gemma4-26b-a4b/src/gemma4_text.c:8293-8385; combine: src/gemma4.c:215-276):
+ *   norm_a  = RMSNorm(residual) * pre_ffn_norm;   dense  = down(GeGLU(gate(norm_a), up(norm_a)))
+ *   router input, logits, top-k from the residual
+ *   norm_b  = RMSNorm(residual) * pre_ffn_norm_2; routed = ordered reduce of the experts on norm_b
+ *   out     = (residual + RMSNorm(RMSNorm(dense)*post_ffn_norm_1 + RMSNorm(routed)*post_ffn_norm_2)
+ *                         * post_ffn_norm) * layer_scalar
+ * dense_gate / dense_up are affine-Q4 tensors [dense_inter][hidden], dense_down is
+ * [hidden][dense_inter], each laid out values | scales | biases.  Attach once per layer after
+ * salt_b200_stack_add_q4_layer; no reference counterpart as ONE call (the reference runs these
+ * steps from the host, with exact cells and projection batches in between). */
+typedef struct SaltB200FfnBlockSpec {
+    int dense_inter;
+    const void *dense_gate, *dense_up, *dense_down;
+    const float *pre_ffn_norm, *pre_ffn_norm_2, *post_ffn_norm_1, *post_ffn_norm_2, *post_ffn_norm;
+    float layer_scalar;
+} SaltB200FfnBlockSpec;
+int salt_b200_stack_attach_ffn_block(void *stack, int layer, const SaltB200FfnBlockSpec *spec);
+/* d_residual, d_out: [B][hidden] device memory (distinct buffers); every launch goes to `stream`. */
+int salt_b200_ffn_block_forward(void *stack, int layer, const float *d_residual, int B, float *d_out, void *stream);
+
 /* Phase A of one layer on `stream` (a cudaStream_t, NULL = default stream):
  * router input, logits, top-k, grouping, gate/up + GeGLU, down for the local
  * experts.  d_x is [B][hidden] in device memory.  flags:

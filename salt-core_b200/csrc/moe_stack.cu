@@ -10,6 +10,7 @@
 // their positions in the global grouped order; rows of other devices' experts
 // arrive through whatever exchange the caller runs between the two phases.
 #include <cuda_runtime.h>
+#include <cmath>
 #include <stdio.h>
 #include <string.h>
 
@@ -30,6 +31,14 @@ struct Layer {
     uint8_t* pool = nullptr;   // local experts only; slot of expert e at pool + (e - expert_begin) * stride
     size_t expert_stride = 0;
     float eps = 0.0f;
+    // optional dense branch and norms of the whole feed-forward block
+    bool ffn = false;
+    int dense_inter = 0;
+    float layer_scalar = 1.0f;
+    float *pre_ffn_norm = nullptr, *pre_ffn_norm_2 = nullptr;
+    float *post_ffn_norm_1 = nullptr, *post_ffn_norm_2 = nullptr, *post_ffn_norm = nullptr;
+    uint8_t* dense = nullptr;          // gate | up | down affine-Q4 tensors
+    Q4Job* dense_jobs = nullptr;       // [2] device: fused gate/up job, down job
 };
 
 struct Stack {
@@ -45,6 +54,10 @@ struct Stack {
     void *xh = nullptr, *xl = nullptr, *chain_h = nullptr, *chain_l = nullptr;   // fp16 operands (hi, lo) of the tensor-core path
     bool tc_ready = false;                     // tensor maps built (needs hidden, inter multiples of 64)
     TcMaps x_maps, chain_maps;                 // TMA descriptors of (xh, xl) and (chain_h, chain_l)
+    // workspace of the whole feed-forward block (allocated by the first attach)
+    float *norm_a = nullptr, *norm_b = nullptr, *dense_chain = nullptr, *dense_out = nullptr;
+    float *routed_out = nullptr, *combine_scratch = nullptr;
+    int dense_cap = 0;
     bool own_grouped = true;
     size_t grouped_bytes = 0;
     float *h_in = nullptr, *h_out = nullptr;  // pinned staging for the host entry point
@@ -77,7 +90,11 @@ static void free_stack(Stack* s) {
     for (auto& l : s->layers) {
         cudaFree(l.router_w); cudaFree(l.router_scale); cudaFree(l.per_expert_scale);
         cudaFree(l.norm_weight); cudaFree(l.pool);
+        cudaFree(l.pre_ffn_norm); cudaFree(l.pre_ffn_norm_2); cudaFree(l.post_ffn_norm_1);
+        cudaFree(l.post_ffn_norm_2); cudaFree(l.post_ffn_norm); cudaFree(l.dense); cudaFree(l.dense_jobs);
     }
+    cudaFree(s->norm_a); cudaFree(s->norm_b); cudaFree(s->dense_chain); cudaFree(s->dense_out);
+    cudaFree(s->routed_out); cudaFree(s->combine_scratch);
     cudaFree(s->rin); cudaFree(s->logits); cudaFree(s->weights); cudaFree(s->chain);
     if (s->own_grouped) cudaFree(s->grouped_out);
     cudaFree(s->reduced); cudaFree(s->act_a); cudaFree(s->act_b); cudaFree(s->io_in); cudaFree(s->io_out);
@@ -211,10 +228,11 @@ enum { SB_EXPERTS_ZERO_REMOTE = 1, SB_EXPERTS_ROUTER_INPUT_READY = 2, SB_EXPERTS
        SB_EXPERTS_TENSOR_CORE_SINGLE = 8 };
 enum { SB_COMBINE_NORM = 1, SB_COMBINE_PREPARE_NEXT = 2 };
 
-int salt_b200_layer_experts(void* stack, int layer, const float* d_x, int B, int flags, void* stream_) {
-    Stack* s = (Stack*)stack;
-    cudaStream_t st = (cudaStream_t)stream_;
-    if (!s || layer < 0 || layer >= (int)s->layers.size() || !d_x || B < 1 || B > s->max_tokens) return -1;
+// d_router_src feeds the router input (unless it is already prepared), d_x the expert projections.
+static int layer_experts_impl(Stack* s, int layer, const float* d_router_src, const float* d_x, int B, int flags,
+                              cudaStream_t st) {
+    if (!s || layer < 0 || layer >= (int)s->layers.size() || !d_x || !d_router_src || B < 1 || B > s->max_tokens)
+        return -1;
     const Layer& l = s->layers[(size_t)layer];
     const int H = s->hidden, M = s->inter, E = s->n_experts, K = s->topk;
     const int jobs = B * K;
@@ -225,7 +243,7 @@ int salt_b200_layer_experts(void* stack, int layer, const float* d_x, int B, int
         Timed t(s, KC_ROUTER_INPUT, st);
         GlueArgs g;
         memset(&g, 0, sizeof g);
-        g.x_in = d_x; g.router_scale = l.router_scale; g.eps_router = l.eps; g.rin = s->rin; g.n = H;
+        g.x_in = d_router_src; g.router_scale = l.router_scale; g.eps_router = l.eps; g.rin = s->rin; g.n = H;
         g.status = s->status;
         if (!cuda_ok(launch_glue(g, B, st), "router in")) return -1;
         count_launches(1);
@@ -308,6 +326,10 @@ int salt_b200_layer_experts(void* stack, int layer, const float* d_x, int B, int
     return 0;
 }
 
+int salt_b200_layer_experts(void* stack, int layer, const float* d_x, int B, int flags, void* stream_) {
+    return layer_experts_impl((Stack*)stack, layer, d_x, d_x, B, flags, (cudaStream_t)stream_);
+}
+
 // Ordered weighted reduce of grouped_out into d_y; SB_COMBINE_NORM applies the
 // layer's RMSNorm (if it has one) to the result; SB_COMBINE_PREPARE_NEXT also
 // forms the router input of layer + 1 from it, so that layer's
@@ -332,6 +354,109 @@ int salt_b200_layer_combine(void* stack, int layer, int B, float* d_y, int flags
         if (!cuda_ok(launch_glue(g, B, st), "combine")) return -1;
     }
     count_launches(1);
+    return 0;
+}
+
+// ---- the whole feed-forward block ------------------------------------------------------------
+__global__ void patch_job_tokens_kernel(Q4Job* jobs, int n, int ntok) {
+    if ((int)threadIdx.x < n) jobs[threadIdx.x].ntok = ntok;
+}
+
+static size_t q4_blob_bytes(int R, int C) {
+    const size_t elems = (size_t)R * C;
+    return elems / 2 + 2 * (elems / 64 * 2);
+}
+
+int salt_b200_stack_attach_ffn_block(void* stack, int layer, const SaltB200FfnBlockSpec* spec) {
+    Stack* s = (Stack*)stack;
+    if (!s || !spec || layer < 0 || layer >= (int)s->layers.size() || spec->dense_inter < 64 ||
+        (spec->dense_inter % 64) != 0 || (s->hidden % 64) != 0 || !spec->dense_gate || !spec->dense_up ||
+        !spec->dense_down || !spec->pre_ffn_norm || !spec->pre_ffn_norm_2 || !spec->post_ffn_norm_1 ||
+        !spec->post_ffn_norm_2 || !spec->post_ffn_norm || !std::isfinite(spec->layer_scalar))
+        return -1;
+    Layer& l = s->layers[(size_t)layer];
+    if (l.ffn) return -1;
+    const int H = s->hidden, D = spec->dense_inter;
+    const size_t T = (size_t)s->max_tokens;
+    if (D > s->dense_cap) {
+        cudaFree(s->dense_chain);
+        s->dense_chain = nullptr;
+        if (!dev_alloc(&s->dense_chain, T * D)) return -1;
+        s->dense_cap = D;
+    }
+    if (!s->norm_a &&
+        !(dev_alloc(&s->norm_a, T * H) && dev_alloc(&s->norm_b, T * H) && dev_alloc(&s->dense_out, T * H) &&
+          dev_alloc(&s->routed_out, T * H) && dev_alloc(&s->combine_scratch, 2 * T * H)))
+        return -1;
+    const size_t gu = q4_blob_bytes(D, H), dn = q4_blob_bytes(H, D);      // equal, kept apart for clarity
+    bool ok = dev_alloc(&l.dense, 2 * gu + dn) &&
+              cuda_ok(cudaMemcpy(l.dense, spec->dense_gate, gu, cudaMemcpyHostToDevice), "dense gate") &&
+              cuda_ok(cudaMemcpy(l.dense + gu, spec->dense_up, gu, cudaMemcpyHostToDevice), "dense up") &&
+              cuda_ok(cudaMemcpy(l.dense + 2 * gu, spec->dense_down, dn, cudaMemcpyHostToDevice), "dense down") &&
+              upload(&l.pre_ffn_norm, spec->pre_ffn_norm, (size_t)H) &&
+              upload(&l.pre_ffn_norm_2, spec->pre_ffn_norm_2, (size_t)H) &&
+              upload(&l.post_ffn_norm_1, spec->post_ffn_norm_1, (size_t)H) &&
+              upload(&l.post_ffn_norm_2, spec->post_ffn_norm_2, (size_t)H) &&
+              upload(&l.post_ffn_norm, spec->post_ffn_norm, (size_t)H);
+    if (!ok) return -1;
+    const size_t vb = (size_t)D * H / 2, gb = (size_t)D * H / 64 * 2;
+    Q4Job jobs[2];
+    memset(jobs, 0, sizeof jobs);
+    Q4Job& a = jobs[0];
+    a.vals = l.dense; a.scales = l.dense + vb; a.biases = l.dense + vb + gb;
+    a.vals2 = l.dense + gu; a.scales2 = a.vals2 + vb; a.biases2 = a.scales2 + gb;
+    a.x = s->norm_a; a.y = s->dense_chain; a.x_rows = nullptr; a.x_div = 1;
+    a.R = D; a.C = H; a.ntok = 1; a.x_stride = H; a.y_stride = D;
+    Q4Job& b = jobs[1];
+    b.vals = l.dense + 2 * gu; b.scales = b.vals + vb; b.biases = b.scales + gb;
+    b.x = s->dense_chain; b.y = s->dense_out; b.x_rows = nullptr; b.x_div = 1;
+    b.R = H; b.C = D; b.ntok = 1; b.x_stride = D; b.y_stride = H;
+    if (!upload(&l.dense_jobs, jobs, (size_t)2)) return -1;
+    l.dense_inter = D;
+    l.layer_scalar = spec->layer_scalar;
+    l.ffn = true;
+    return 0;
+}
+
+int salt_b200_ffn_block_forward(void* stack, int layer, const float* d_residual, int B, float* d_out,
+                                void* stream_) {
+    Stack* s = (Stack*)stack;
+    cudaStream_t st = (cudaStream_t)stream_;
+    if (!s || layer < 0 || layer >= (int)s->layers.size() || !d_residual || !d_out || B < 1 || B > s->max_tokens)
+        return -1;
+    const Layer& l = s->layers[(size_t)layer];
+    if (!l.ffn) return -1;
+    const int H = s->hidden, D = l.dense_inter;
+    const int tok_hint = B == 1 ? 1 : (B == 2 ? 2 : 4);
+    auto norm = [&](const float* w, float* y) {
+        GlueArgs g;
+        memset(&g, 0, sizeof g);
+        g.x_in = d_residual; g.norm_w = w; g.eps_norm = l.eps; g.y_out = y; g.n = H; g.status = s->status;
+        return cuda_ok(launch_glue(g, B, st), "ffn pre-norm");
+    };
+    // dense branch: norm_a -> gate/up + GeGLU -> down
+    patch_job_tokens_kernel<<<1, 32, 0, st>>>(l.dense_jobs, 2, B);
+    if (!norm(l.pre_ffn_norm, s->norm_a) ||
+        !cuda_ok(launch_q4_jobs(l.dense_jobs, 1, nullptr, D, tok_hint, H, 2, true, st), "dense gate/up") ||
+        !cuda_ok(launch_q4_jobs(l.dense_jobs + 1, 1, nullptr, H, tok_hint, D, 1, true, st), "dense down"))
+        return -1;
+    // routed branch: router on the residual, experts on norm_b
+    if (!norm(l.pre_ffn_norm_2, s->norm_b)) return -1;
+    count_launches(5);
+    if (layer_experts_impl(s, layer, d_residual, s->norm_b, B, 0, st) != 0) return -1;
+    {
+        GlueArgs g;
+        memset(&g, 0, sizeof g);
+        g.weights = s->weights; g.c2g = s->c2g; g.grouped = s->grouped_out; g.topk = s->topk; g.jobs = B * s->topk;
+        g.y_out = s->routed_out; g.n = H; g.status = s->status;
+        if (!cuda_ok(launch_glue(g, B, st), "routed reduce")) return -1;
+    }
+    if (!cuda_ok(launch_parallel_combine(d_residual, s->dense_out, s->routed_out, l.post_ffn_norm_1,
+                                         l.post_ffn_norm_2, l.post_ffn_norm, s->combine_scratch,
+                                         s->combine_scratch + (size_t)s->max_tokens * H, d_out, B, H, l.eps,
+                                         l.layer_scalar, s->status, st), "parallel combine"))
+        return -1;
+    count_launches(2);
     return 0;
 }
 

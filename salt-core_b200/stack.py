@@ -16,6 +16,13 @@ class Q4LayerSpec(C.Structure):
                 ("norm_weight", C.c_void_p)]
 
 
+class FfnBlockSpec(C.Structure):
+    _fields_ = [("dense_inter", C.c_int), ("dense_gate", C.c_void_p), ("dense_up", C.c_void_p),
+                ("dense_down", C.c_void_p), ("pre_ffn_norm", C.c_void_p), ("pre_ffn_norm_2", C.c_void_p),
+                ("post_ffn_norm_1", C.c_void_p), ("post_ffn_norm_2", C.c_void_p), ("post_ffn_norm", C.c_void_p),
+                ("layer_scalar", C.c_float)]
+
+
 class Workspace(C.Structure):
     _fields_ = [("grouped_out", C.c_void_p), ("group_offsets", C.c_void_p), ("selected", C.c_void_p),
                 ("weights", C.c_void_p), ("canonical_to_grouped", C.c_void_p),
@@ -52,6 +59,19 @@ class MoeStack:
             raise RuntimeError("salt_b200_stack_add_q4_layer failed")
         self.n_layers = idx + 1
         return idx
+
+    def attach_ffn_block(self, layer, block):
+        """block: synth.FfnBlock; completes MoE layer `layer` to the whole feed-forward block."""
+        spec = FfnBlockSpec(block.dense_inter, block.dense_gate.ctypes.data, block.dense_up.ctypes.data,
+                            block.dense_down.ctypes.data, block.pre_ffn_norm.ctypes.data,
+                            block.pre_ffn_norm_2.ctypes.data, block.post_ffn_norm_1.ctypes.data,
+                            block.post_ffn_norm_2.ctypes.data, block.post_ffn_norm.ctypes.data,
+                            block.layer_scalar)
+        return self.lib.salt_b200_stack_attach_ffn_block(self.handle, layer, C.byref(spec))
+
+    def ffn_block_forward(self, layer, d_residual, B, d_out, stream=0):
+        return self.lib.salt_b200_ffn_block_forward(self.handle, layer, C.c_void_p(d_residual), B,
+                                                    C.c_void_p(d_out), C.c_void_p(stream))
 
     def workspace(self):
         w = Workspace()

@@ -110,6 +110,41 @@ def make_q4_moe_layer(seed: int, hidden=2816, inter=704, n_experts=128, topk=8,
         norm_weight=(1.0 + 0.1 * rng.standard_normal(hidden)).astype(np.float32))
 
 
+@dataclass
+class FfnBlock:
+    """Dense branch and norms that complete a MoE layer to the whole feed-forward block."""
+    dense_inter: int
+    dense_gate: np.ndarray          # uint8 blobs: values | scales | biases
+    dense_up: np.ndarray
+    dense_down: np.ndarray
+    pre_ffn_norm: np.ndarray
+    pre_ffn_norm_2: np.ndarray
+    post_ffn_norm_1: np.ndarray
+    post_ffn_norm_2: np.ndarray
+    post_ffn_norm: np.ndarray
+    layer_scalar: float
+
+    def tensor(self, which: str, hidden: int):
+        """(vals uint32, scales uint16, biases uint16, R, C) of dense_gate / dense_up / dense_down."""
+        R, C = (hidden, self.dense_inter) if which == "dense_down" else (self.dense_inter, hidden)
+        vb, gb = q4_tensor_bytes(R, C)
+        buf = getattr(self, which)
+        return buf[:vb].view(np.uint32), buf[vb:vb + gb].view(np.uint16), buf[vb + gb:].view(np.uint16), R, C
+
+
+def make_ffn_block(seed: int, hidden=2816, dense_inter=2112) -> FfnBlock:
+    """Dense GeGLU MLP (affine-Q4 as ``fill_q4``) and five RMSNorm weights 1 + 0.1*N(0,1)."""
+    rng = np.random.default_rng(seed)
+    blobs = []
+    for R, C in ((dense_inter, hidden), (dense_inter, hidden), (hidden, dense_inter)):
+        vb, gb = q4_tensor_bytes(R, C)
+        buf = np.empty(vb + 2 * gb, np.uint8)
+        fill_q4(rng, buf, R, C)
+        blobs.append(buf)
+    norms = [(1.0 + 0.1 * rng.standard_normal(hidden)).astype(np.float32) for _ in range(5)]
+    return FfnBlock(dense_inter, *blobs, *norms, layer_scalar=0.8125)
+
+
 def make_tokens(seed: int, B: int, hidden: int) -> np.ndarray:
     return np.random.default_rng(seed).standard_normal((B, hidden)).astype(np.float32)
 

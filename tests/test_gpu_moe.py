@@ -338,3 +338,69 @@ def test_stack_eight_way_sharding_bench_geometry(orc, synth):
     for st in parts:
         st.close()
 
+
+def _oracle_ffn_block(orc, layer, block, residual):
+    """CPU statement of the whole feed-forward block (reference gemma4_text.c:8293-8385, gemma4.c:215-276)
+    from the oracle's functions: dense GeGLU MLP on RMSNorm(residual), router on the residual, experts on
+    the second RMSNorm, parallel combine."""
+    B, H = residual.shape
+    out = np.empty_like(residual)
+    gate, up, down = (block.tensor(k, H) for k in ("dense_gate", "dense_up", "dense_down"))
+    vb = layer.hidden * layer.inter // 2
+    gb = layer.hidden * layer.inter // 64 * 2
+    tb = vb + 2 * gb
+
+    def expert_tensor(e, which):
+        base = e * layer.expert_stride + which * tb
+        buf = layer.pool[base:base + tb]
+        return buf[:vb].view(np.uint32), buf[vb:vb + gb].view(np.uint16), buf[vb + gb:].view(np.uint16)
+
+    gelu = np.vectorize(orc.gelu_tanh, otypes=[np.float32])
+    for t in range(B):
+        res = residual[t]
+        rc, norm_a = orc.rmsnorm(res, block.pre_ffn_norm, layer.eps, True)
+        assert rc == 0
+        g = orc.q4_matvec(*gate[:3], gate[3], gate[4], norm_a, threads=8)
+        u = orc.q4_matvec(*up[:3], up[3], up[4], norm_a, threads=8)
+        dense = orc.q4_matvec(*down[:3], down[3], down[4], (gelu(g) * u).astype(np.float32), threads=8)
+        rc, rin = orc.router_input(res, layer.router_scale, layer.eps)
+        assert rc == 0
+        logits = orc.router_scores(layer.router_w, None, rin)
+        rc, sel, w = orc.router_topk(logits, layer.per_expert_scale, layer.topk, True)
+        assert rc == 0
+        rc, norm_b = orc.rmsnorm(res, block.pre_ffn_norm_2, layer.eps, True)
+        assert rc == 0
+        routed = np.zeros(H, np.float32)
+        for rank in range(layer.topk):
+            e = int(sel[rank])
+            eg = orc.q4_matvec(*expert_tensor(e, 0), layer.inter, H, norm_b, threads=8)
+            eu = orc.q4_matvec(*expert_tensor(e, 1), layer.inter, H, norm_b, threads=8)
+            ed = orc.q4_matvec(*expert_tensor(e, 2), H, layer.inter, (gelu(eg) * eu).astype(np.float32), threads=8)
+            routed = (routed + (np.float32(w[rank]) * ed).astype(np.float32)).astype(np.float32)
+        rc, y, _ = orc.parallel_ffn_combine(res, dense, routed, block.post_ffn_norm_1, block.post_ffn_norm_2,
+                                            block.post_ffn_norm, block.layer_scalar, layer.eps)
+        assert rc == 0
+        out[t] = y
+    return out
+
+
+@pytest.mark.parametrize("geom", [(256, 128, 192, 16, 4, 5), (2816, 704, 2112, 128, 8, 2)])
+def test_whole_ffn_block_vs_oracle(orc, synth, geom):
+    import torch
+    H, M, D, E, K, B = geom
+    make = synth.make_q4_moe_layer_bulk if H == 2816 else synth.make_q4_moe_layer
+    layer = make(81, hidden=H, inter=M, n_experts=E, topk=K)
+    block = synth.make_ffn_block(82, hidden=H, dense_inter=D)
+    st = stack_mod().MoeStack(8, H, M, E, K)
+    st.add_layer(layer)
+    assert st.attach_ffn_block(0, block) == 0
+    residual = synth.make_tokens(83, B, H)
+    d_res = torch.from_numpy(residual).cuda()
+    d_out = torch.zeros_like(d_res)
+    for rep in range(2):
+        assert st.ffn_block_forward(0, d_res.data_ptr(), B, d_out.data_ptr()) == 0
+    assert st.status() == 0
+    want = _oracle_ffn_block(orc, layer, block, residual)
+    assert_bits_equal(d_out.cpu().numpy(), want, f"whole FFN block H={H}")
+    st.close()
+
