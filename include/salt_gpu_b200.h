@@ -377,6 +377,33 @@ int salt_b200_layer_experts(void *stack, int layer, const float *d_x, int B, int
 #define SALT_B200_COMBINE_NORM 1
 #define SALT_B200_COMBINE_PREPARE_NEXT 2
 int salt_b200_layer_combine(void *stack, int layer, int B, float *d_y, int flags, void *stream);
+/* Expert-parallel exchange over peer memory (no reference counterpart: the reference is
+ * single-device; the sharding rule follows from its expert independence,
+ * models/gemma4-26b-a4b/src/gemma4.c:154-186 reduces per-selection outputs in rank order).
+ * Each rank (one process per GPU, or several stacks of one process) owns experts
+ * [expert_begin, expert_end) and runs the same tokens through a replicated router.
+ *   _ep_region   allocates this stack's landing region and returns its CUDA IPC handle
+ *                (64 bytes) and its device address
+ *   _ep_connect  takes the handles of all `world` ranks in rank order (entry `rank` is ignored),
+ *                or, with ipc_handles == NULL, `regions`: the device addresses themselves when
+ *                the ranks live in one process.  world <= 8.
+ *   _ep_exchange after salt_b200_layer_experts: pushes this rank's rows of grouped_out into every
+ *                peer's region, waits (bounded, about a second; a timeout sets the device error
+ *                word) for the peers' rows and copies them into grouped_out.  After it,
+ *                salt_b200_layer_combine sees the complete buffer.  phase = PUSH | PULL; the two
+ *                halves may be launched separately only when all ranks share one device and
+ *                every rank's PUSH is enqueued before any PULL.
+ * Once connected, salt_b200_stack_forward_device (and a graph captured from it) runs the
+ * exchange between the two phases of every layer.  All ranks must run the same sequence of
+ * exchanges; start the first one only after every rank has connected (host barrier). */
+#define SALT_B200_EP_PUSH 1
+#define SALT_B200_EP_PULL 2
+int salt_b200_stack_ep_region(void *stack, void *ipc_handle_out, void **region_out);
+int salt_b200_stack_ep_connect(void *stack, int rank, int world, const void *ipc_handles, void *const *regions);
+int salt_b200_stack_ep_exchange(void *stack, int B, int phase, void *stream);
+/* Back to the unconnected state (peer mappings closed); call only between exchanges, after a host barrier. */
+int salt_b200_stack_ep_disconnect(void *stack);
+
 /* Layers [first, first+count) back to back (phase A + B each), chained through
  * the layers' RMSNorm; d_x and d_y are device pointers and may alias. */
 int salt_b200_stack_forward_device(void *stack, int first, int count, const float *d_x, int B, float *d_y,

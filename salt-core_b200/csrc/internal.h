@@ -141,4 +141,23 @@ cudaError_t launch_weighted_reduce(const float* weights, const int32_t* canonica
 cudaError_t launch_routed_gather(const float* x, const int32_t* grouped_to_canonical, float* routed, int jobs,
                                  int topk, int hidden, cudaStream_t stream);
 
+// ---- ep_exchange.cu ---------------------------------------------------------
+// Exchange of grouped expert outputs between expert-parallel ranks over peer memory.
+// A region = header (epoch, flags) + two landing buffers of [rows_cap][width] floats.
+enum : int { EP_MAX_WORLD = 8, EP_BLOCKS = 32, EP_THREADS = 256, EP_HEADER_BYTES = 4096 };
+enum : int { EP_PHASE_PUSH = 1, EP_PHASE_PULL = 2 };
+struct EpExchangeArgs {
+    uint8_t* region[EP_MAX_WORLD];   // region[rank] is this device's own, the others are peer mappings
+    int rank, world;
+    const int32_t* group_offsets;    // [n_experts + 1], identical on every rank
+    int expert_begin, expert_end, n_experts;
+    float* grouped;                  // [rows][width]: own rows are read, the others written
+    int width, rows_cap;
+    int phase;                       // EP_PHASE_PUSH | EP_PHASE_PULL; one at a time only when all
+                                     // ranks share a device and their launches are serialised
+    int* status;
+};
+size_t ep_region_bytes(int rows_cap, int width);
+cudaError_t launch_ep_exchange(const EpExchangeArgs& a, cudaStream_t stream);
+
 }  // namespace sb

@@ -67,6 +67,11 @@ struct Stack {
     std::vector<int> ev_class;
     size_t ev_used = 0;
     cudaGraphExec_t graph = nullptr;
+    // expert-parallel exchange over peer memory
+    uint8_t* ep_region = nullptr;              // this stack's landing region
+    uint8_t* ep_peer[EP_MAX_WORLD] = {};       // all ranks' regions (own included) once connected
+    bool ep_opened[EP_MAX_WORLD] = {};         // mapped through a CUDA IPC handle
+    int ep_rank = 0, ep_world = 0;
 };
 
 enum KernelClass { KC_ROUTER_INPUT = 0, KC_LOGITS, KC_TOPK, KC_PLAN, KC_GATE_UP, KC_DOWN, KC_REDUCE, KC_NORM, KC_COUNT };
@@ -105,6 +110,9 @@ static void free_stack(Stack* s) {
     if (s->h_out) cudaFreeHost(s->h_out);
     for (auto e : s->ev) cudaEventDestroy(e);
     if (s->graph) cudaGraphExecDestroy(s->graph);
+    for (int p = 0; p < EP_MAX_WORLD; p++)
+        if (s->ep_opened[p]) cudaIpcCloseMemHandle(s->ep_peer[p]);
+    cudaFree(s->ep_region);
     delete s;
 }
 
@@ -357,6 +365,86 @@ int salt_b200_layer_combine(void* stack, int layer, int B, float* d_y, int flags
     return 0;
 }
 
+// ---- expert-parallel exchange over peer memory ------------------------------------------------
+int salt_b200_stack_ep_region(void* stack, void* ipc_handle_out, void** region_out) {
+    Stack* s = (Stack*)stack;
+    if (!s || !ipc_handle_out) return -1;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size is part of the ABI");
+    if (!s->ep_region) {
+        const size_t bytes = ep_region_bytes(s->max_tokens * s->topk, s->hidden);
+        if (!cuda_ok(cudaMalloc((void**)&s->ep_region, bytes), "ep region") ||
+            !cuda_ok(cudaMemset(s->ep_region, 0, bytes), "ep region clear") ||
+            !cuda_ok(cudaDeviceSynchronize(), "ep region sync"))
+            return -1;
+    }
+    cudaIpcMemHandle_t h;
+    if (!cuda_ok(cudaIpcGetMemHandle(&h, s->ep_region), "ipc handle")) return -1;
+    memcpy(ipc_handle_out, &h, sizeof h);
+    if (region_out) *region_out = s->ep_region;
+    return 0;
+}
+
+int salt_b200_stack_ep_connect(void* stack, int rank, int world, const void* ipc_handles, void* const* regions) {
+    Stack* s = (Stack*)stack;
+    if (!s || !s->ep_region || s->ep_world || world < 2 || world > EP_MAX_WORLD || rank < 0 || rank >= world ||
+        (!ipc_handles && !regions))
+        return -1;
+    for (int p = 0; p < world; p++) {
+        if (p == rank) {
+            s->ep_peer[p] = s->ep_region;
+            continue;
+        }
+        if (ipc_handles) {
+            cudaIpcMemHandle_t h;
+            memcpy(&h, (const uint8_t*)ipc_handles + (size_t)p * sizeof h, sizeof h);
+            void* ptr = nullptr;
+            if (!cuda_ok(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess), "ipc open")) {
+                for (int q = 0; q < p; q++)
+                    if (s->ep_opened[q]) { cudaIpcCloseMemHandle(s->ep_peer[q]); s->ep_opened[q] = false; }
+                return -1;
+            }
+            s->ep_peer[p] = (uint8_t*)ptr;
+            s->ep_opened[p] = true;
+        } else {
+            if (!regions[p]) return -1;
+            s->ep_peer[p] = (uint8_t*)regions[p];
+        }
+    }
+    s->ep_rank = rank;
+    s->ep_world = world;
+    return 0;
+}
+
+int salt_b200_stack_ep_disconnect(void* stack) {
+    Stack* s = (Stack*)stack;
+    if (!s) return -1;
+    cudaDeviceSynchronize();
+    for (int p = 0; p < EP_MAX_WORLD; p++) {
+        if (s->ep_opened[p]) cudaIpcCloseMemHandle(s->ep_peer[p]);
+        s->ep_opened[p] = false;
+        s->ep_peer[p] = nullptr;
+    }
+    s->ep_world = 0;
+    return 0;
+}
+
+int salt_b200_stack_ep_exchange(void* stack, int B, int phase, void* stream) {
+    Stack* s = (Stack*)stack;
+    if (!s || s->ep_world < 2 || B < 1 || B > s->max_tokens) return -1;
+    EpExchangeArgs a;
+    memset(&a, 0, sizeof a);
+    for (int p = 0; p < s->ep_world; p++) a.region[p] = s->ep_peer[p];
+    a.rank = s->ep_rank; a.world = s->ep_world;
+    a.group_offsets = s->group_offsets;
+    a.expert_begin = s->expert_begin; a.expert_end = s->expert_end; a.n_experts = s->n_experts;
+    a.grouped = s->grouped_out; a.width = s->hidden; a.rows_cap = s->max_tokens * s->topk;
+    a.phase = phase; a.status = s->status;
+    Timed t(s, KC_NORM, (cudaStream_t)stream);
+    if (!cuda_ok(launch_ep_exchange(a, (cudaStream_t)stream), "ep exchange")) return -1;
+    count_launches(1);
+    return 0;
+}
+
 // ---- the whole feed-forward block ------------------------------------------------------------
 __global__ void patch_job_tokens_kernel(Q4Job* jobs, int n, int ntok) {
     if ((int)threadIdx.x < n) jobs[threadIdx.x].ntok = ntok;
@@ -444,6 +532,7 @@ int salt_b200_ffn_block_forward(void* stack, int layer, const float* d_residual,
     if (!norm(l.pre_ffn_norm_2, s->norm_b)) return -1;
     count_launches(5);
     if (layer_experts_impl(s, layer, d_residual, s->norm_b, B, 0, st) != 0) return -1;
+    if (s->ep_world > 1 && salt_b200_stack_ep_exchange(stack, B, EP_PHASE_PUSH | EP_PHASE_PULL, stream_) != 0) return -1;
     {
         GlueArgs g;
         memset(&g, 0, sizeof g);
@@ -480,6 +569,7 @@ int salt_b200_stack_forward_device(void* stack, int first, int count, const floa
         float* out = last ? d_y : ((i & 1) ? s->act_b : s->act_a);
         if (salt_b200_layer_experts(stack, first + i, in, B, i > 0 ? SB_EXPERTS_ROUTER_INPUT_READY : 0,
                                     stream) != 0 ||
+            (s->ep_world > 1 && salt_b200_stack_ep_exchange(stack, B, EP_PHASE_PUSH | EP_PHASE_PULL, stream) != 0) ||
             salt_b200_layer_combine(stack, first + i, B, out,
                                     last ? 0 : (SB_COMBINE_NORM | SB_COMBINE_PREPARE_NEXT), stream) != 0)
             return -1;

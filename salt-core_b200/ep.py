@@ -33,6 +33,29 @@ def exchange_grouped(grouped, group=None):
     return grouped
 
 
+def connect_peer_memory(stack, group=None) -> bool:
+    """Map every rank's landing region into this process (CUDA IPC) so that the stack exchanges
+    the grouped outputs itself, inside salt_b200_stack_forward_device, instead of through
+    exchange_grouped.  Returns False on every rank when any rank could not map its peers; the
+    caller then stays on forward().  Ends with a barrier: no rank starts an exchange before all
+    are connected."""
+    import torch
+    import torch.distributed as dist
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    handle, _ = stack.ep_region()
+    mine = torch.tensor(list(handle), dtype=torch.uint8, device="cuda")
+    gathered = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(gathered, mine, group=group)
+    handles = [bytes(t.cpu().tolist()) for t in gathered]
+    ok = torch.tensor([1 if stack.ep_connect(rank, world, ipc_handles=handles) == 0 else 0], device="cuda")
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+    good = bool(ok.item())
+    if not good:
+        stack.ep_disconnect()
+    dist.barrier(group)
+    return good
+
+
 def forward(stack, grouped, d_x, B, d_out, act, stream=0, first=0, count=None, group=None):
     """One pass of layers [first, first+count) with one exchange per layer.
     d_x / d_out / act[0..1] are torch tensors [B][hidden] on the device;

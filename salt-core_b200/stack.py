@@ -112,6 +112,32 @@ class MoeStack:
         flags = (1 if apply_norm else 0) | (2 if prepare_next else 0)
         return self.lib.salt_b200_layer_combine(self.handle, layer, B, C.c_void_p(d_y), flags, C.c_void_p(stream))
 
+    EP_PUSH, EP_PULL = 1, 2
+
+    def ep_region(self):
+        """(64-byte CUDA IPC handle, device address) of this stack's landing region."""
+        handle = (C.c_ubyte * 64)()
+        region = C.c_void_p()
+        if self.lib.salt_b200_stack_ep_region(self.handle, handle, C.byref(region)) != 0:
+            raise RuntimeError("salt_b200_stack_ep_region failed")
+        return bytes(handle), int(region.value)
+
+    def ep_connect(self, rank, world, ipc_handles=None, regions=None):
+        """ipc_handles: list of `world` 64-byte handles (ranks in other processes), or regions: list of
+        `world` device addresses (ranks in this process)."""
+        if ipc_handles is not None:
+            blob = b"".join(ipc_handles)
+            assert len(blob) == 64 * world
+            return self.lib.salt_b200_stack_ep_connect(self.handle, rank, world, blob, None)
+        arr = (C.c_void_p * world)(*[C.c_void_p(r) for r in regions])
+        return self.lib.salt_b200_stack_ep_connect(self.handle, rank, world, None, arr)
+
+    def ep_disconnect(self):
+        return self.lib.salt_b200_stack_ep_disconnect(self.handle)
+
+    def ep_exchange(self, B, phase=3, stream=0):
+        return self.lib.salt_b200_stack_ep_exchange(self.handle, B, phase, C.c_void_p(stream))
+
     KERNEL_CLASSES = ("router_input", "router_logits", "router_topk", "plan_topk", "gate_up_geglu", "down",
                       "reduce_norm_router_input", "rmsnorm")
 
