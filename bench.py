@@ -50,6 +50,9 @@ def parse():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="budget of the CPU baseline sample")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--ep-exchange", choices=["peer", "nccl"], default="peer",
+                    help="N>1: exchange of the grouped expert outputs by the stack's own kernel over peer "
+                         "memory (falls back to nccl when the regions cannot be mapped) or by an NCCL all-reduce")
     ap.add_argument("--prefill", default=None, choices=["exact", "single", "split"],
                     help="run the layers one by one with the expert projections on the exact kernels, or on the "
                          "tensor cores with operands rounded to fp16 once (single) or carried as hi+lo halves (split)")
@@ -254,10 +257,11 @@ def run_b200(args):
             assert stack.layer_combine(l, B, out.data_ptr(), apply_norm=True, prepare_next=l + 1 < L, stream=sp) == 0
             cur = out.data_ptr()
 
-    use_graph = world == 1 and not args.no_graph and not args.prefill
+    peer = world > 1 and args.ep_exchange == "peer" and not args.prefill and ep.connect_peer_memory(stack)
+    use_graph = (world == 1 or peer) and not args.no_graph and not args.prefill
     with torch.cuda.stream(stream):
         n0 = stack.launch_count()
-        if world > 1:
+        if world > 1 and not peer:
             forward_ep(d_x, d_y)
         elif args.prefill:
             forward_layers(d_x, d_y)
@@ -267,11 +271,13 @@ def run_b200(args):
         assert stack.status(sp) == 0
         if use_graph:
             assert stack.graph_capture(d_x.data_ptr(), B, d_y.data_ptr(), sp) == 0
+        if peer:
+            dist.barrier()                    # ranks start their exchanges together
 
         def step():
             if use_graph:
                 assert stack.graph_launch(sp) == 0
-            elif world > 1:
+            elif world > 1 and not peer:
                 forward_ep(d_x, d_y)
             elif args.prefill:
                 forward_layers(d_x, d_y)
@@ -313,13 +319,19 @@ def run_b200(args):
                 stack.forward_host(x_host)
             else:
                 d_x.copy_(h_in, non_blocking=True)
-                if world > 1:
+                if use_graph:
+                    assert stack.graph_launch(sp) == 0
+                elif peer:
+                    assert stack.forward_device(d_x.data_ptr(), B, d_y.data_ptr(), stream=sp) == 0
+                elif world > 1:
                     forward_ep(d_x, d_y)
                 else:
                     forward_layers(d_x, d_y)
                 h_out.copy_(d_y, non_blocking=True)
                 stream.synchronize()
 
+        if peer:
+            dist.barrier()
         for _ in range(3):
             e2e_step()
         if world == 1 and not args.prefill:
@@ -395,10 +407,13 @@ def run_b200(args):
                    "d2h_bytes_per_step": B * H * 4, "ms_per_step": ms_e2e,
                    "api": ("salt_b200_stack_forward_host" if world == 1 and not args.prefill else
                            "salt_b200_layer_experts / salt_b200_layer_combine per layer" if world == 1 else
+                           "salt_b200_stack_forward_device with the peer-memory exchange" if peer else
                            "layer_experts/all_reduce/layer_combine")},
            "gpu_launches": launches_per_step * args.steps,
            "launch_mode": "cuda graph replay" if use_graph else "stream launches",
            "us_per_layer": 1e3 * ms_step / L}
+    if world > 1:
+        out["ep_exchange"] = "peer memory (own kernel over NVLink)" if peer else "nccl all_reduce"
     if roofline:
         out["roofline"] = roofline
         out["kernels"] = kernels
@@ -406,6 +421,8 @@ def run_b200(args):
         out["cpu_baseline"] = cpu_baseline(host_layers, B, args.cpu_seconds, os.cpu_count() or 1)
     if rank == 0:
         print(json.dumps(out))
+    if world > 1:
+        dist.barrier()                        # no rank unmaps a peer's region while it is still in use
     stack.close()
     if world > 1:
         dist.destroy_process_group()

@@ -3,121 +3,111 @@
 //
 // Every rank owns a contiguous expert range and therefore a contiguous range of rows of the
 // grouped output (the grouping is computed from a replicated router, so all ranks agree on
-// it).  The kernel PUSHES its own rows into a landing buffer in every peer's memory, raises
-// one flag per (source rank, block) there, waits for the peers' flags on its own landing
-// buffer, and copies the rows it does not own into its grouped buffer.  Each row is produced
-// by exactly one rank and copied unchanged, so the result does not depend on the number of
-// ranks.  Remote data is only ever written into the consumer's memory and then read locally.
+// it).  The kernel PUSHES its own rows into a landing buffer in every peer's memory, then
+// PULLS the rows it does not own out of its own landing buffer into its grouped buffer.  Each
+// row is produced by exactly one rank and copied unchanged, so the result does not depend on
+// the number of ranks.  Remote data is only ever written into the consumer's memory and read
+// locally.
+//
+// Data and arrival flag travel together: a 16-byte slot holds two floats, each followed by
+// the 32-bit sequence number of the exchange {d0, seq, d1, seq}, written with one store.  The
+// reader polls the slot until both sequence numbers match; 8-byte halves of an aligned store
+// are never torn, so a matching number vouches for the float next to it.  No fence and no
+// separate flag round trip sit between the producer's store and the consumer's load.
 //
 // Landing buffers alternate with the parity of an epoch counter that lives on the device and
-// advances once per exchange, so a replayed CUDA graph needs no host-side state.  A peer may
-// be one epoch ahead (it pushes epoch e + 1 into the other buffer while this rank still reads
-// epoch e); it cannot be two ahead, because passing epoch e + 1 needs this rank's push of
-// e + 1, which this rank issues after it has finished reading epoch e.
+// advances once per exchange (seq = epoch + 1), so a replayed CUDA graph needs no host-side
+// state.  A peer may be one epoch ahead (it pushes epoch e + 1 into the other buffer while this
+// rank still reads epoch e); it cannot be two ahead, because completing epoch e + 1 needs this
+// rank's push of e + 1, which this rank issues after it has finished reading epoch e.
 //
-// Every wait is bounded: when a flag does not arrive within about a second the kernel sets
-// SB_ERR_TIMEOUT in the status word, skips the copy and still advances the epoch.
+// Every wait is bounded: when a slot does not arrive within about a second the block gives
+// up, the kernel sets SB_ERR_TIMEOUT in the status word and still advances the epoch.
 #include "internal.h"
+#include "pdl.cuh"
 
 namespace sb {
 
 struct EpHeader {
     int epoch;
     int done;
-    int pad[62];
-    int flags[EP_MAX_WORLD][EP_BLOCKS];
 };
 static_assert(sizeof(EpHeader) <= EP_HEADER_BYTES, "header area too small");
 
 size_t ep_region_bytes(int rows_cap, int width) {
-    return (size_t)EP_HEADER_BYTES + 2 * (size_t)rows_cap * width * sizeof(float);
+    return (size_t)EP_HEADER_BYTES + 2 * (size_t)rows_cap * (width / 2) * 16;
 }
 
-__device__ __forceinline__ int ld_acquire_sys(const int* p) {
-    int v;
-    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint4 ld_slot(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_slot(uint4* p, uint4 v) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};"
+                 ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-constexpr int EP_SPIN_LIMIT = 1 << 21;   // polls of >= 0.3 us each
-constexpr int EP_ROW_PIECES = 4;         // a row is moved by up to four blocks
+constexpr int EP_SPIN_LIMIT = 1 << 21;   // polls of about half a microsecond
 
 __global__ void __launch_bounds__(EP_THREADS) ep_exchange_kernel(EpExchangeArgs a) {
     __shared__ int s_timed_out;
+    pdl_wait();
+    pdl_launch_dependents();
     EpHeader* own = (EpHeader*)a.region[a.rank];
     const int e = *(volatile const int*)&own->epoch;
+    const uint32_t seq = (uint32_t)e + 1u;
     int lo = a.group_offsets[a.expert_begin], hi = a.group_offsets[a.expert_end];
     int total = a.group_offsets[a.n_experts];
     if (lo < 0 || lo > hi || hi > total || total > a.rows_cap) {
-        // still raise the flags, so that no peer waits for this rank in vain
         if (blockIdx.x == 0 && threadIdx.x == 0) atomicOr(a.status, SB_ERR_CAPACITY);
         lo = hi = total = 0;
     }
-    const int w4 = a.width >> 2;
-    const int piece = (w4 + EP_ROW_PIECES - 1) / EP_ROW_PIECES;
-    const size_t buf_off = (size_t)EP_HEADER_BYTES + (size_t)(e & 1) * a.rows_cap * a.width * sizeof(float);
-    const int peers = a.world - 1;
+    const int slots = a.width >> 1;              // 16-byte slots per row
+    const size_t buf_off = (size_t)EP_HEADER_BYTES + (size_t)(e & 1) * a.rows_cap * slots * 16;
+    const int stride = gridDim.x * blockDim.x;
+    const int first = blockIdx.x * blockDim.x + threadIdx.x;
 
     if (a.phase & EP_PHASE_PUSH) {
-        const int items = (hi - lo) * peers * EP_ROW_PIECES;
-        for (int it = blockIdx.x; it < items; it += gridDim.x) {
-            const int pc = it % EP_ROW_PIECES;
-            const int rp = it / EP_ROW_PIECES;
-            const int pi = rp % peers;
-            const int r = lo + rp / peers;
-            const int p = pi + (pi >= a.rank ? 1 : 0);
-            const float4* src = (const float4*)(a.grouped + (size_t)r * a.width);
-            float4* dst = (float4*)(a.region[p] + buf_off) + (size_t)r * w4;
-            const int end = min((pc + 1) * piece, w4);
-            for (int i = pc * piece + threadIdx.x; i < end; i += blockDim.x) dst[i] = src[i];
+        const int n = (hi - lo) * slots;
+        for (int i = first; i < n; i += stride) {
+            const int rr = i / slots, c = i - rr * slots;
+            const int r = lo + rr;
+            const float2 v = *(const float2*)(a.grouped + (size_t)r * a.width + 2 * c);
+            const uint4 w = make_uint4(__float_as_uint(v.x), seq, __float_as_uint(v.y), seq);
+            const size_t at = buf_off + ((size_t)r * slots + c) * 16;
+            for (int p = 0; p < a.world; p++)
+                if (p != a.rank) st_slot((uint4*)(a.region[p] + at), w);
         }
-        __threadfence_system();
-        __syncthreads();
-        if ((int)threadIdx.x < a.world && (int)threadIdx.x != a.rank)
-            st_release_sys(&((EpHeader*)a.region[threadIdx.x])->flags[a.rank][blockIdx.x], e + 1);
     }
 
     if (a.phase & EP_PHASE_PULL) {
         if (threadIdx.x == 0) s_timed_out = 0;
         __syncthreads();
-        for (int f = threadIdx.x; f < peers * (int)gridDim.x; f += blockDim.x) {
-            const int pi = f / (int)gridDim.x, b = f - pi * (int)gridDim.x;
-            const int p = pi + (pi >= a.rank ? 1 : 0);
-            const int* flag = &own->flags[p][b];
+        const int nown = hi - lo;
+        const int n = (total - nown) * slots;
+        for (int i = first; i < n; i += stride) {
+            const int q = i / slots, c = i - q * slots;
+            const int r = q < lo ? q : q + nown;
+            const uint4* src = (const uint4*)(a.region[a.rank] + buf_off) + (size_t)r * slots + c;
+            uint4 w = ld_slot(src);
             int spins = 0;
-            while (ld_acquire_sys(flag) - (e + 1) < 0) {
-                if (++spins > EP_SPIN_LIMIT) {
+            while (w.y != seq || w.w != seq) {
+                if (++spins > EP_SPIN_LIMIT || *(volatile int*)&s_timed_out) {
                     s_timed_out = 1;
                     break;
                 }
-                __nanosleep(200);
+                if (spins > 8) __nanosleep(100);
+                w = ld_slot(src);
             }
+            if (w.y == seq && w.w == seq)
+                *(float2*)(a.grouped + (size_t)r * a.width + 2 * c) = make_float2(__uint_as_float(w.x), __uint_as_float(w.z));
         }
-        __threadfence_system();
-        __syncthreads();
-        if (s_timed_out) {
-            if (threadIdx.x == 0) atomicOr(a.status, SB_ERR_TIMEOUT);
-        } else {
-            // rows below lo and from hi on came from the peers; the landing buffer was written by
-            // another device, so it is read past the L1 cache
-            const int nown = hi - lo;
-            const int items = (total - nown) * EP_ROW_PIECES;
-            for (int it = blockIdx.x; it < items; it += gridDim.x) {
-                const int pc = it % EP_ROW_PIECES;
-                const int q = it / EP_ROW_PIECES;
-                const int r = q < lo ? q : q + nown;
-                const float4* src = (const float4*)(a.region[a.rank] + buf_off) + (size_t)r * w4;
-                float4* dst = (float4*)(a.grouped + (size_t)r * a.width);
-                const int end = min((pc + 1) * piece, w4);
-                for (int i = pc * piece + threadIdx.x; i < end; i += blockDim.x) dst[i] = __ldcg(src + i);
-            }
-        }
-        // the last block to get here has seen every block read the epoch: advance it
         __syncthreads();
         if (threadIdx.x == 0) {
+            if (s_timed_out) atomicOr(a.status, SB_ERR_TIMEOUT);
+            // the last block to get here has seen every block read the epoch: advance it
             __threadfence();
             const int prev = atomicAdd(&own->done, 1);
             if (prev == (int)gridDim.x - 1) {
@@ -129,14 +119,17 @@ __global__ void __launch_bounds__(EP_THREADS) ep_exchange_kernel(EpExchangeArgs 
     }
 }
 
-cudaError_t launch_ep_exchange(const EpExchangeArgs& a, cudaStream_t stream) {
-    if (a.world < 2 || a.world > EP_MAX_WORLD || a.rank < 0 || a.rank >= a.world || (a.width & 3) || !a.grouped ||
-        !(a.phase & (EP_PHASE_PUSH | EP_PHASE_PULL)))
+cudaError_t launch_ep_exchange(const EpExchangeArgs& a, int rows, cudaStream_t stream) {
+    if (a.world < 2 || a.world > EP_MAX_WORLD || a.rank < 0 || a.rank >= a.world || (a.width & 1) || !a.grouped ||
+        !(a.phase & (EP_PHASE_PUSH | EP_PHASE_PULL)) || rows < 1)
         return cudaErrorInvalidValue;
     for (int p = 0; p < a.world; p++)
         if (!a.region[p]) return cudaErrorInvalidValue;
-    ep_exchange_kernel<<<EP_BLOCKS, EP_THREADS, 0, stream>>>(a);
-    return cudaGetLastError();
+    // two slots per thread when the whole batch fits one wave, never more than one block per SM
+    const long long work = (long long)rows * (a.width >> 1);
+    long long blocks = (work + 2 * EP_THREADS - 1) / (2 * EP_THREADS);
+    blocks = blocks < 8 ? 8 : (blocks > 148 ? 148 : blocks);
+    return launch_pdl(ep_exchange_kernel, dim3((unsigned)blocks), dim3(EP_THREADS), 0, stream, a);
 }
 
 }  // namespace sb

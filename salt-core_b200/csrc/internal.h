@@ -143,8 +143,8 @@ cudaError_t launch_routed_gather(const float* x, const int32_t* grouped_to_canon
 
 // ---- ep_exchange.cu ---------------------------------------------------------
 // Exchange of grouped expert outputs between expert-parallel ranks over peer memory.
-// A region = header (epoch, flags) + two landing buffers of [rows_cap][width] floats.
-enum : int { EP_MAX_WORLD = 8, EP_BLOCKS = 32, EP_THREADS = 256, EP_HEADER_BYTES = 4096 };
+// A region = header (epoch) + two landing buffers of [rows_cap][width / 2] 16-byte slots.
+enum : int { EP_MAX_WORLD = 8, EP_THREADS = 256, EP_HEADER_BYTES = 4096 };
 enum : int { EP_PHASE_PUSH = 1, EP_PHASE_PULL = 2 };
 struct EpExchangeArgs {
     uint8_t* region[EP_MAX_WORLD];   // region[rank] is this device's own, the others are peer mappings
@@ -158,6 +158,7 @@ struct EpExchangeArgs {
     int* status;
 };
 size_t ep_region_bytes(int rows_cap, int width);
-cudaError_t launch_ep_exchange(const EpExchangeArgs& a, cudaStream_t stream);
+// rows = grouped rows of this call (all ranks'), sizes the grid
+cudaError_t launch_ep_exchange(const EpExchangeArgs& a, int rows, cudaStream_t stream);
 
 }  // namespace sb

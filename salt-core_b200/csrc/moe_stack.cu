@@ -440,7 +440,7 @@ int salt_b200_stack_ep_exchange(void* stack, int B, int phase, void* stream) {
     a.grouped = s->grouped_out; a.width = s->hidden; a.rows_cap = s->max_tokens * s->topk;
     a.phase = phase; a.status = s->status;
     Timed t(s, KC_NORM, (cudaStream_t)stream);
-    if (!cuda_ok(launch_ep_exchange(a, (cudaStream_t)stream), "ep exchange")) return -1;
+    if (!cuda_ok(launch_ep_exchange(a, B * s->topk, (cudaStream_t)stream), "ep exchange")) return -1;
     count_launches(1);
     return 0;
 }
