@@ -786,6 +786,102 @@ router_logits_tile_kernel(const float* __restrict__ W, const float* __restrict__
     if (e < E && row < rows) logits[(size_t)row * E + e] = __fadd_rn(acc, bias ? bias[e] : 0.0f);
 }
 
+// Prefill-sized batches: 256 threads as 16 experts x 16 rows, each thread EPT x RPT outputs
+// (independent dependent-add chains, so a warp always has an add to issue), tiles of
+// 16*EPT experts x 16*RPT rows.  The 8 x 8 tiles above re-read W and x from L2 sixteen times
+// more often per output than a 32 x 32 tile; past a few hundred rows that traffic, not the
+// chains, set their time.
+template <int EPT, int RPT>
+struct LogitsBig {
+    static constexpr int TE = 16 * EPT, TR = 16 * RPT, ROWS = TE + TR;
+    static constexpr int SLAB = 128, PITCH = SLAB + 4, STAGES = 3;   // two blocks per SM
+    static constexpr size_t SMEM = (size_t)STAGES * ROWS * PITCH * sizeof(float);
+};
+
+template <int EPT, int RPT>
+__global__ void __launch_bounds__(256, 2)
+router_logits_big_kernel(const float* __restrict__ W, const float* __restrict__ bias, const float* __restrict__ x,
+                         float* __restrict__ logits, int rows, int E, int H) {
+    using G = LogitsBig<EPT, RPT>;
+    extern __shared__ __align__(16) float lt_sm[];      // [STAGES][TE W rows, then TR x rows][PITCH]
+    const int tid = threadIdx.x;
+    const int el = tid & 15, rl = tid >> 4;
+    const int e0 = blockIdx.x * G::TE, row0 = blockIdx.y * G::TR;
+    const int nslab = (H + G::SLAB - 1) / G::SLAB;
+    // a slab row is 32 pieces of 16 bytes: thread tid copies piece tid & 31 of rows tid >> 5, + 8, ...
+    const int pc = tid & 31;
+    auto issue = [&](int sl) {
+        float* st = lt_sm + (size_t)(sl % G::STAGES) * G::ROWS * G::PITCH;
+        const int c = sl * G::SLAB + pc * 4;
+        if (c >= H) return;
+#pragma unroll
+        for (int r = tid >> 5; r < G::ROWS; r += 8) {
+            const float* src = r < G::TE ? W + (size_t)min(e0 + r, E - 1) * H + c
+                                         : x + (size_t)min(row0 + r - G::TE, rows - 1) * H + c;
+            cp_async16(st + r * G::PITCH + pc * 4, src);
+        }
+    };
+    for (int sl = 0; sl < G::STAGES - 1; sl++) {
+        if (sl < nslab) issue(sl);
+        cp_async_commit();
+    }
+    float acc[EPT][RPT];
+#pragma unroll
+    for (int i = 0; i < EPT; i++)
+#pragma unroll
+        for (int j = 0; j < RPT; j++) acc[i][j] = 0.0f;
+    for (int sl = 0; sl < nslab; sl++) {
+        cp_async_wait_dyn(G::STAGES - 2);
+        __syncthreads();
+        if (sl + G::STAGES - 1 < nslab) issue(sl + G::STAGES - 1);
+        cp_async_commit();
+        const float* st = lt_sm + (size_t)(sl % G::STAGES) * G::ROWS * G::PITCH;
+        const int kc = min(G::SLAB, H - sl * G::SLAB);
+#pragma unroll 2
+        for (int c = 0; c + 4 <= kc; c += 4) {
+            float4 wv[EPT], xv[RPT];
+#pragma unroll
+            for (int i = 0; i < EPT; i++) wv[i] = *(const float4*)(st + (el + 16 * i) * G::PITCH + c);
+#pragma unroll
+            for (int j = 0; j < RPT; j++) xv[j] = *(const float4*)(st + (G::TE + rl + 16 * j) * G::PITCH + c);
+#pragma unroll
+            for (int i = 0; i < EPT; i++)
+#pragma unroll
+                for (int j = 0; j < RPT; j++) {
+                    float a = acc[i][j];
+                    a = __fadd_rn(a, __fmul_rn(wv[i].x, xv[j].x));
+                    a = __fadd_rn(a, __fmul_rn(wv[i].y, xv[j].y));
+                    a = __fadd_rn(a, __fmul_rn(wv[i].z, xv[j].z));
+                    a = __fadd_rn(a, __fmul_rn(wv[i].w, xv[j].w));
+                    acc[i][j] = a;
+                }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < EPT; i++)
+#pragma unroll
+        for (int j = 0; j < RPT; j++) {
+            const int e = e0 + el + 16 * i, row = row0 + rl + 16 * j;
+            if (e < E && row < rows) logits[(size_t)row * E + e] = __fadd_rn(acc[i][j], bias ? bias[e] : 0.0f);
+        }
+}
+
+template <int EPT, int RPT>
+static cudaError_t launch_logits_big(const float* W, const float* bias, const float* x, float* logits, int rows, int E,
+                                     int H, cudaStream_t stream) {
+    using G = LogitsBig<EPT, RPT>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(router_logits_big_kernel<EPT, RPT>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G::SMEM);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    dim3 grid((E + G::TE - 1) / G::TE, (rows + G::TR - 1) / G::TR);
+    router_logits_big_kernel<EPT, RPT><<<grid, 256, G::SMEM, stream>>>(W, bias, x, logits, rows, E, H);
+    return cudaGetLastError();
+}
+
 // The same without alignment requirements (H not a multiple of 4, or unaligned operands):
 // plain loads, 32 experts x 8 rows per block, 64-column slabs.
 __global__ void __launch_bounds__(256)
@@ -838,6 +934,10 @@ cudaError_t launch_router_logits(const float* W, const float* bias, const float*
         if (smem > 200 * 1024) return cudaErrorInvalidValue;
         dim3 grid(E, (rows + LOGIT_TB - 1) / LOGIT_TB);
         router_logits_block_kernel<<<grid, 256, smem, stream>>>(W, bias, x, logits, rows, E, H);
+    } else if (aligned16 && (H & 3) == 0 && rows >= 1024) {
+        return launch_logits_big<2, 2>(W, bias, x, logits, rows, E, H, stream);
+    } else if (aligned16 && (H & 3) == 0 && rows >= 256) {
+        return launch_logits_big<2, 1>(W, bias, x, logits, rows, E, H, stream);
     } else if (aligned16 && (H & 3) == 0) {
         const size_t smem = (size_t)LT_STAGES * 16 * LT_PITCH * sizeof(float);
         static bool configured = false;

@@ -404,3 +404,27 @@ def test_whole_ffn_block_vs_oracle(orc, synth, geom):
     assert_bits_equal(d_out.cpu().numpy(), want, f"whole FFN block H={H}")
     st.close()
 
+
+
+@pytest.mark.parametrize("geom", [(320, 64, 24, 2, 300), (320, 64, 24, 2, 1030), (2816, 704, 128, 8, 1030)])
+def test_router_logits_prefill_sized_batches_vs_oracle(orc, synth, geom):
+    """Batches of several hundred rows take the large-tile logits kernels (32 experts x 16 or 32 rows
+    per block); ragged tiles in both directions, a last column slab shorter than the others."""
+    import torch
+    H, M, E, K, B = geom
+    make = synth.make_q4_moe_layer_bulk if H == 2816 else synth.make_q4_moe_layer
+    layer = make(91, hidden=H, inter=M, n_experts=E, topk=K)
+    st = stack_mod().MoeStack(B, H, M, E, K)
+    st.add_layer(layer)
+    x = synth.make_tokens(92, B, H)
+    d_x = torch.from_numpy(x).cuda()
+    assert st.layer_experts(0, d_x.data_ptr(), B) == 0
+    assert st.status() == 0
+    got = d2h(st.workspace().logits, B * E, np.float32).reshape(B, E)
+    want = np.empty_like(got)
+    for t in range(B):
+        rc, rin = orc.router_input(x[t], layer.router_scale, layer.eps)
+        assert rc == 0
+        want[t] = orc.router_scores(layer.router_w, None, rin)
+    assert_bits_equal(got, want, f"router logits B={B} H={H}")
+    st.close()
