@@ -596,10 +596,120 @@ __global__ void __launch_bounds__(GLUE_NV == 4 ? 1024 : 512) glue_rows_kernel(Gl
     if (bad) flag(a.status, SB_ERR_NONFINITE);
 }
 
+// The same glue for batches of several hundred rows: one WARP per row, lane l holds the CH
+// consecutive columns [l*CH, (l+1)*CH) in registers, and each in-order sum is the plain
+// dependent-add chain handed from lane to lane (the reference's order: columns ascending from
+// +0).  A chain costs about 6.5 us, but thousands of rows run side by side (16 warps per SM),
+// where the block-per-row form above keeps a whole SM busy for 13 us per pair of rows.
+template <int CH>
+static __device__ __forceinline__ float warp_chain_sum_of_squares(const float (&v)[CH], int lane) {
+    float acc = 0.0f;
+#pragma unroll 1
+    for (int l = 0; l < 32; l++) {
+        float a = __shfl_sync(0xffffffffu, acc, (l + 31) & 31);
+        if (l == 0) a = 0.0f;
+        if (lane == l) {
+#pragma unroll
+            for (int i = 0; i < CH; i++) a = __fadd_rn(a, __fmul_rn(v[i], v[i]));
+            acc = a;
+        }
+    }
+    return __shfl_sync(0xffffffffu, acc, 31);
+}
+
+template <int CH>
+__global__ void __launch_bounds__(128, 4) glue_rows_warp_kernel(GlueArgs a, int rows) {
+    static_assert(CH % 4 == 0, "rows are moved in 16-byte pieces");
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int n = a.n;                         // == 32 * CH
+    const int c0 = lane * CH;
+    bool bad = false;
+    float v[CH];
+#pragma unroll
+    for (int i = 0; i < CH; i++) v[i] = 0.0f;
+    if (a.grouped != nullptr) {
+        for (int r = 0; r < a.topk; r++) {
+            const int g = a.c2g[row * a.topk + r];
+            const float w = a.weights[row * a.topk + r];
+            if (g < 0 || g >= a.jobs || !finite_f(w)) {
+                if (lane == 0) flag(a.status, g < 0 || g >= a.jobs ? SB_ERR_INDEX : SB_ERR_NONFINITE);
+                continue;
+            }
+            const float4* src = (const float4*)(a.grouped + (size_t)g * n + c0);
+#pragma unroll
+            for (int i = 0; i < CH / 4; i++) {
+                const float4 o = __ldg(src + i);
+                v[4 * i + 0] = __fadd_rn(v[4 * i + 0], __fmul_rn(w, o.x));
+                v[4 * i + 1] = __fadd_rn(v[4 * i + 1], __fmul_rn(w, o.y));
+                v[4 * i + 2] = __fadd_rn(v[4 * i + 2], __fmul_rn(w, o.z));
+                v[4 * i + 3] = __fadd_rn(v[4 * i + 3], __fmul_rn(w, o.w));
+            }
+        }
+    } else {
+        const float4* src = (const float4*)(a.x_in + (size_t)row * n + c0);
+#pragma unroll
+        for (int i = 0; i < CH / 4; i++) {
+            const float4 o = src[i];
+            v[4 * i + 0] = o.x; v[4 * i + 1] = o.y; v[4 * i + 2] = o.z; v[4 * i + 3] = o.w;
+        }
+    }
+    if (a.norm_w != nullptr) {
+        const float ss = warp_chain_sum_of_squares<CH>(v, lane);
+        const float inv = pow_neg_half(__fadd_rn(__fdiv_rn(ss, (float)n), a.eps_norm));
+        if (!finite_f(inv) && lane == 0) flag(a.status, SB_ERR_NONFINITE);
+        const float4* nw4 = (const float4*)(a.norm_w + c0);
+#pragma unroll
+        for (int i = 0; i < CH / 4; i++) {
+            const float4 w = __ldg(nw4 + i);
+            bad |= !finite_f(v[4 * i]) || !finite_f(v[4 * i + 1]) || !finite_f(v[4 * i + 2]) || !finite_f(v[4 * i + 3]);
+            bad |= !finite_f(w.x) || !finite_f(w.y) || !finite_f(w.z) || !finite_f(w.w);
+            v[4 * i + 0] = __fmul_rn(__fmul_rn(v[4 * i + 0], inv), w.x);
+            v[4 * i + 1] = __fmul_rn(__fmul_rn(v[4 * i + 1], inv), w.y);
+            v[4 * i + 2] = __fmul_rn(__fmul_rn(v[4 * i + 2], inv), w.z);
+            v[4 * i + 3] = __fmul_rn(__fmul_rn(v[4 * i + 3], inv), w.w);
+        }
+    }
+    if (a.y_out != nullptr) {
+        float4* dst = (float4*)(a.y_out + (size_t)row * n + c0);
+#pragma unroll
+        for (int i = 0; i < CH / 4; i++) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    }
+    if (a.router_scale != nullptr) {
+        const float ss = warp_chain_sum_of_squares<CH>(v, lane);
+        const float inv = pow_neg_half(__fadd_rn(__fdiv_rn(ss, (float)n), a.eps_router));
+        const float root = __fdiv_rn(1.0f, sqrtf_exact((float)n));
+        if ((!finite_f(inv) || !finite_f(root)) && lane == 0) flag(a.status, SB_ERR_NONFINITE);
+        const float4* rs4 = (const float4*)(a.router_scale + c0);
+        float4* dst = (float4*)(a.rin + (size_t)row * n + c0);
+#pragma unroll
+        for (int i = 0; i < CH / 4; i++) {
+            const float4 w = __ldg(rs4 + i);
+            float4 t;
+            t.x = __fmul_rn(__fmul_rn(__fmul_rn(v[4 * i + 0], inv), w.x), root);
+            t.y = __fmul_rn(__fmul_rn(__fmul_rn(v[4 * i + 1], inv), w.y), root);
+            t.z = __fmul_rn(__fmul_rn(__fmul_rn(v[4 * i + 2], inv), w.z), root);
+            t.w = __fmul_rn(__fmul_rn(__fmul_rn(v[4 * i + 3], inv), w.w), root);
+            bad |= !finite_f(v[4 * i]) || !finite_f(v[4 * i + 1]) || !finite_f(v[4 * i + 2]) || !finite_f(v[4 * i + 3]);
+            bad |= !finite_f(w.x) || !finite_f(w.y) || !finite_f(w.z) || !finite_f(w.w);
+            bad |= !finite_f(t.x) || !finite_f(t.y) || !finite_f(t.z) || !finite_f(t.w);
+            dst[i] = t;
+        }
+    }
+    if (bad) flag(a.status, SB_ERR_NONFINITE);
+}
+
 cudaError_t launch_glue(const GlueArgs& a, int rows, cudaStream_t stream) {
     if (rows < 1) return cudaSuccess;
     if (a.topk > 64) return cudaErrorInvalidValue;
     const size_t smem = (size_t)(a.n + 8) * sizeof(float);
+    const auto al16 = [](const void* p) { return (((uintptr_t)p) & 15) == 0; };
+    if (rows >= 256 && a.n == 32 * 88 && al16(a.grouped) && al16(a.x_in) && al16(a.y_out) && al16(a.norm_w) &&
+        al16(a.router_scale) && al16(a.rin)) {
+        glue_rows_warp_kernel<88><<<(rows + 3) / 4, 128, 0, stream>>>(a, rows);
+        return cudaGetLastError();
+    }
     if (a.n <= 4096) {
         // every thread owns 4 columns: wide rows and small batches get the largest block
         const int threads = (rows <= 16 || a.n > 1024) ? 1024 : 256;

@@ -428,3 +428,19 @@ def test_router_logits_prefill_sized_batches_vs_oracle(orc, synth, geom):
         want[t] = orc.router_scores(layer.router_w, None, rin)
     assert_bits_equal(got, want, f"router logits B={B} H={H}")
     st.close()
+
+
+def test_stack_two_layers_prefill_sized_batch_vs_oracle(orc, synth):
+    """300 rows at the bench geometry: the reduce + RMSNorm + router-input glue runs one warp per row
+    (dependent-add chains handed from lane to lane), the logits take the large tiles; the second layer's
+    output depends on both."""
+    B = 300
+    layers = [synth.make_q4_moe_layer_bulk(95 + i) for i in range(2)]
+    x = synth.make_tokens(97, B, 2816)
+    st = stack_mod().MoeStack(B, 2816, 704, 128, 8)
+    for layer in layers:
+        st.add_layer(layer)
+    y = st.forward_host(x)
+    want, _ = oracle_stack(orc, layers, x, threads=16)
+    assert_bits_equal(y, want, "2-layer stack, 300 rows")
+    st.close()
