@@ -384,11 +384,11 @@ def run_b200(args):
             achieved = alg / (gu["us_per_launch"] * 1e-6) / 1e9
             dn = kernels["down"]
             # DRAM bytes of one gate/up launch from the ncu capture of this kernel (read + write,
-            # 2.241 MB per distinct expert at B=1: profiles/q4_tile_kernel_decode_b1.md); scales with
+            # 2.241 MB per distinct expert at B=1: profiles/q4_tile16_kernel_decode_b1.md); scales with
             # the distinct experts of a launch, so it is only reported for the decode kernel at B=1
             traffic = mean_distinct * 2_240_992.0 if (B == 1 and not tc_mode) else None
             kname = ("q4_gemm_tc_kernel<fused> (tcgen05 gate/up + GeGLU)" if tc_mode
-                     else "q4_tile_kernel<2,TT> (fused gate/up + GeGLU)")
+                     else "q4_tile16_kernel<2,TT> (fused gate/up + GeGLU)")
             roofline = {"bound": "hbm", "kernel": kname,
                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                         "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback 6650 GB/s",
