@@ -268,6 +268,17 @@ def run_b200(args):
         else:
             assert stack.forward_device(d_x.data_ptr(), B, d_y.data_ptr(), stream=sp) == 0
         launches_per_step = stack.launch_count() - n0
+        if peer:
+            # a rank that never saw a peer's rows (bounded wait ran out) sends every rank back to NCCL
+            failed = torch.tensor([stack.status(sp)], dtype=torch.int32, device="cuda")
+            dist.all_reduce(failed, op=dist.ReduceOp.MAX)
+            if int(failed.item()) != 0:
+                dist.barrier()
+                stack.ep_disconnect()
+                peer, use_graph = False, False
+                n0 = stack.launch_count()
+                forward_ep(d_x, d_y)
+                launches_per_step = stack.launch_count() - n0
         assert stack.status(sp) == 0
         if use_graph:
             assert stack.graph_capture(d_x.data_ptr(), B, d_y.data_ptr(), sp) == 0

@@ -388,7 +388,7 @@ int salt_b200_layer_combine(void *stack, int layer, int B, float *d_y, int flags
  *                or, with ipc_handles == NULL, `regions`: the device addresses themselves when
  *                the ranks live in one process.  world <= 8.
  *   _ep_exchange after salt_b200_layer_experts: pushes this rank's rows of grouped_out into every
- *                peer's region, waits (bounded, about a second; a timeout sets the device error
+ *                peer's region, waits (bounded, a few seconds; a timeout sets the device error
  *                word) for the peers' rows and copies them into grouped_out.  After it,
  *                salt_b200_layer_combine sees the complete buffer.  phase = PUSH | PULL; the two
  *                halves may be launched separately only when all ranks share one device and

@@ -21,7 +21,7 @@
 // rank still reads epoch e); it cannot be two ahead, because completing epoch e + 1 needs this
 // rank's push of e + 1, which this rank issues after it has finished reading epoch e.
 //
-// Every wait is bounded: when a slot does not arrive within about a second the block gives
+// Every wait is bounded: when a slot does not arrive within a few seconds the block gives
 // up, the kernel sets SB_ERR_TIMEOUT in the status word and still advances the epoch.
 #include "internal.h"
 #include "pdl.cuh"
@@ -49,7 +49,7 @@ __device__ __forceinline__ void st_slot(uint4* p, uint4 v) {
                  ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-constexpr int EP_SPIN_LIMIT = 1 << 21;   // polls of about half a microsecond
+constexpr int EP_SPIN_LIMIT = 1 << 23;   // polls of about half a microsecond: a few seconds
 
 __global__ void __launch_bounds__(EP_THREADS) ep_exchange_kernel(EpExchangeArgs a) {
     __shared__ int s_timed_out;
