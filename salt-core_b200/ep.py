@@ -42,12 +42,15 @@ def connect_peer_memory(stack, group=None) -> bool:
     import torch
     import torch.distributed as dist
     world, rank = dist.get_world_size(group), dist.get_rank(group)
+    # the handles travel through whatever the process group moves: device tensors for NCCL, host tensors otherwise
+    dev = "cuda" if dist.get_backend(group) == "nccl" else "cpu"
     handle, _ = stack.ep_region()
-    mine = torch.tensor(list(handle), dtype=torch.uint8, device="cuda")
+    mine = torch.tensor(list(handle), dtype=torch.uint8, device=dev)
     gathered = [torch.empty_like(mine) for _ in range(world)]
     dist.all_gather(gathered, mine, group=group)
     handles = [bytes(t.cpu().tolist()) for t in gathered]
-    ok = torch.tensor([1 if stack.ep_connect(rank, world, ipc_handles=handles) == 0 else 0], device="cuda")
+    ok = torch.tensor([1 if stack.ep_connect(rank, world, ipc_handles=handles) == 0 else 0], dtype=torch.int32,
+                      device=dev)
     dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
     good = bool(ok.item())
     if not good:

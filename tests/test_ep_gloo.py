@@ -68,3 +68,56 @@ def test_expert_ranges_partition_the_experts():
             lo, hi = ep.expert_range(r, world, 128)
             covered += list(range(lo, hi))
         assert covered == list(range(128))
+
+
+class _FakeStack:
+    """Stands in for MoeStack in the handle exchange: records what connect_peer_memory does."""
+
+    def __init__(self, rank, fail):
+        self.rank, self.fail, self.connected, self.disconnected, self.seen = rank, fail, False, False, None
+
+    def ep_region(self):
+        return bytes([self.rank + 1]) * 64, 0x1000 * (self.rank + 1)
+
+    def ep_connect(self, rank, world, ipc_handles=None, regions=None):
+        self.seen = (rank, world, [h[0] for h in ipc_handles], [len(h) for h in ipc_handles])
+        if self.fail:
+            return -1
+        self.connected = True
+        return 0
+
+    def ep_disconnect(self):
+        self.disconnected = True
+        self.connected = False
+        return 0
+
+
+def _connect_worker(rank, world, port, out_path, failing_rank):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ep = importlib.import_module("salt-core_b200.ep")
+    st = _FakeStack(rank, fail=rank == failing_rank)
+    good = ep.connect_peer_memory(st)
+    ordered = st.seen == (rank, world, [r + 1 for r in range(world)], [64] * world)
+    flags = torch.tensor([int(good), int(st.connected), int(st.disconnected), int(ordered)])
+    gathered = [torch.zeros(4, dtype=torch.int64) for _ in range(world)]
+    dist.all_gather(gathered, flags)
+    if rank == 0:
+        np.save(out_path, torch.stack(gathered).numpy())
+    dist.destroy_process_group()
+
+
+def test_peer_memory_handles_are_gathered_in_rank_order(tmp_path):
+    out = str(tmp_path / "connect.npy")
+    mp.spawn(_connect_worker, args=(2, 31500 + os.getpid() % 2000, out, -1), nprocs=2, join=True)
+    flags = np.load(out)
+    assert flags.tolist() == [[1, 1, 0, 1], [1, 1, 0, 1]]      # connected everywhere, handles in rank order
+
+
+def test_peer_memory_connect_failure_on_one_rank_disconnects_all(tmp_path):
+    out = str(tmp_path / "connect_fail.npy")
+    mp.spawn(_connect_worker, args=(2, 33500 + os.getpid() % 2000, out, 1), nprocs=2, join=True)
+    flags = np.load(out)
+    assert flags[:, 0].tolist() == [0, 0]                      # every rank reports failure ...
+    assert flags[:, 1].tolist() == [0, 0] and flags[:, 2].tolist() == [1, 1]   # ... and none stays connected
