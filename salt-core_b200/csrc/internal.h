@@ -35,10 +35,11 @@ struct TcMaps {
 cudaError_t make_tc_maps(TcMaps* out, const void* hi, const void* lo, int rows, int cols);
 // fused: gate/up + GeGLU -> out_h (+ out_l) [grouped rows][R] fp16; plain: -> out_f [grouped rows][R] fp32.
 // split: operands carried as hi + lo fp16 halves.  bmaps describes the activations (grouped order).
-// y_base / y_cols locate each job's first grouped row from its y pointer.
+// y_base / y_cols locate each job's first grouped row from its y pointer.  rows_total = grouped rows of the
+// call (tokens x top-k): with njobs_max it gives the mean group size that picks the token split of the grid.
 cudaError_t launch_q4_gemm_tc(bool fused, bool split, const Q4Job* jobs, int njobs_max, const int* njobs_dev,
                               const TcMaps& bmaps, const float* y_base, int y_cols, void* out_h, void* out_l,
-                              float* out_f, int R, int* status, cudaStream_t stream);
+                              float* out_f, int R, int rows_total, int* status, cudaStream_t stream);
 
 // ---- nvfp4_kernels.cu ------------------------------------------------------
 // One NVFP4 projection job: ntok rows of already dequantised activations.

@@ -308,13 +308,13 @@ static int layer_experts_impl(Stack* s, int layer, const float* d_router_src, co
         {
             Timed t(s, KC_GATE_UP, st);
             if (!cuda_ok(launch_q4_gemm_tc(true, split, s->gateup_jobs, njobs_max, s->counters, s->x_maps, s->chain,
-                                           M, s->chain_h, s->chain_l, nullptr, M, s->status, st), "tc gate/up"))
+                                           M, s->chain_h, s->chain_l, nullptr, M, jobs, s->status, st), "tc gate/up"))
                 return -1;
         }
         {
             Timed t(s, KC_DOWN, st);
             if (!cuda_ok(launch_q4_gemm_tc(false, split, s->down_jobs, njobs_max, s->counters, s->chain_maps,
-                                           s->grouped_out, H, nullptr, nullptr, s->grouped_out, H, s->status, st), "tc down"))
+                                           s->grouped_out, H, nullptr, nullptr, s->grouped_out, H, jobs, s->status, st), "tc down"))
                 return -1;
         }
         count_launches(5);
