@@ -330,6 +330,12 @@ int salt_b200_stack_create(int max_tokens, int hidden, int inter, int n_experts,
 int salt_b200_stack_destroy(void *stack);
 int salt_b200_stack_add_q4_layer(void *stack, const SaltB200Q4LayerSpec *spec);
 int salt_b200_stack_workspace(void *stack, SaltB200Workspace *out);
+/* Batches of up to 4 tokens run gate/up, GeGLU and down of all selected experts in ONE launch
+ * (one persistent block per SM, weights of both phases in flight from the start; the reference
+ * runs the three projections as separate calls, models/gemma4-26b-a4b/src/gemma4_text.c:7971-7997).
+ * enable = 0 makes every later forward pass of this stack use the two-launch form instead;
+ * both produce the same bits.  Default: enabled. */
+int salt_b200_stack_set_fused_decode(void *stack, int enable);
 /* Replace the grouped-output buffer by caller-owned device memory (for example
  * a buffer registered with a communication library). */
 int salt_b200_stack_set_grouped_out(void *stack, void *device_buffer, size_t nbytes);
@@ -370,6 +376,9 @@ int salt_b200_ffn_block_forward(void *stack, int layer, const float *d_residual,
  *                                          max |err| <= 1e-3 of the row maximum, about 2e-3 of the row rms */
 #define SALT_B200_EXPERTS_TENSOR_CORE 4
 #define SALT_B200_EXPERTS_TENSOR_CORE_SINGLE 8
+/*   SALT_B200_EXPERTS_TWO_LAUNCHES        run gate/up + GeGLU and down as two launches even where the
+ *                                          one-launch decode kernel applies (same bits; for comparison) */
+#define SALT_B200_EXPERTS_TWO_LAUNCHES 16
 int salt_b200_layer_experts(void *stack, int layer, const float *d_x, int B, int flags, void *stream);
 /* Phase B: ordered weighted reduce of grouped_out into d_y [B][hidden].  flags:
  *   SALT_B200_COMBINE_NORM          d_y = RMSNorm(reduce) when the layer has a norm weight

@@ -41,9 +41,6 @@ def build(force: bool = False, verbose: bool = False) -> str:
     for src in sources():
         obj = os.path.join(HERE, "build", os.path.basename(src) + ".o")
         cmd = [nvcc, *[f for f in NVCC_FLAGS if f != "--shared"], "-c", src, "-o", obj]
-        for macro in ("SB_SCALAR_MATH", "SB_EXP_NOCOMPUTE", "SB_EXP_NOLOAD"):   # A/B switches for kernel experiments
-            if os.environ.get(macro):
-                cmd.insert(1, "-D" + macro)
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

@@ -20,6 +20,37 @@ bool q4_tile_supported(int C);
 cudaError_t launch_q4_jobs(const Q4Job* jobs, int njobs_max, const int* njobs_dev, int max_rows, int max_tok, int C,
                            int nmat, bool aligned, cudaStream_t stream, int pdl = -1);
 
+// ---- q4_fused_decode.cu ------------------------------------------------------
+// Decode-sized expert execution in one launch (gate | up -> GeGLU -> down).
+constexpr int FUSED_MAX_JOBS = 32;       // expert groups per launch
+constexpr int FUSED_MAX_TOKENS = 4;      // activation rows per launch (and tokens per group)
+struct FusedJob {
+    const uint8_t *gate_v, *gate_s, *gate_b;   // packed values, bf16 scales, bf16 biases (null: bias 0)
+    const uint8_t *up_v, *up_s, *up_b;
+    const uint8_t *down_v, *down_s, *down_b;
+    int32_t x_row[FUSED_MAX_TOKENS];           // activation row of each token of the group
+    int32_t g0;                                // first grouped row (GeGLU rows and output rows g0, g0 + 1, ...)
+    int32_t ntok;
+};
+struct FusedArgs {
+    const FusedJob* jobs;        // [n_jobs_max]
+    const int* n_jobs_dev;       // live jobs (device)
+    int n_jobs_max;
+    int* done;                   // [n_jobs_max] arrival counters, zero at launch
+    const float* x;              // [n_x][x_stride] activation rows
+    int x_stride, n_x;
+    float* chain;                // [grouped rows][M]
+    float* out;                  // [grouped rows][H]
+    int H, M;
+    int jobs_per_round;          // filled in by the launcher
+    int* status;
+};
+struct FusedLaunch { int grid, jobs_per_round, tt; size_t smem; };
+// Whether the fused kernel serves this geometry on the current device (and how it would be launched).
+bool q4_fused_plan(int H, int M, int n_x, int n_jobs_max, FusedLaunch* out);
+// Launched as a programmatic dependent launch; jobs, counters and x come from the previous kernel.
+cudaError_t launch_q4_fused(const FusedArgs& args, cudaStream_t stream);
+
 // Affine 8-bit jobs (same descriptor; vals = one byte per element): one block per (row, token, job).
 cudaError_t launch_q8_jobs(const Q4Job* jobs, int njobs, int max_rows, int max_tok, int C, cudaStream_t stream);
 
@@ -131,6 +162,10 @@ struct MoePlanArgs {
     float* grouped_out;          // [jobs][hidden] grouped down output
     Q4Job* gateup_jobs;          // [E]
     Q4Job* down_jobs;            // [E]
+    // optional: descriptors and zeroed arrival counters of the fused decode kernel
+    // (the first FUSED_MAX_JOBS local groups; the caller only uses them when there can be no more)
+    FusedJob* fused_jobs;        // [FUSED_MAX_JOBS] or null
+    int* fused_done;             // [FUSED_MAX_JOBS] or null
     int* status;
 };
 cudaError_t launch_moe_plan(const MoePlanArgs& a, cudaStream_t stream);

@@ -51,6 +51,9 @@ struct Stack {
     int32_t *selected = nullptr, *group_offsets = nullptr, *g2c = nullptr, *c2g = nullptr, *counters = nullptr;
     int32_t* status = nullptr;
     Q4Job *gateup_jobs = nullptr, *down_jobs = nullptr;
+    FusedJob* fused_jobs = nullptr;            // descriptors and arrival counters of the fused decode kernel
+    int32_t* fused_done = nullptr;
+    bool fused_decode = true;                  // batches of up to FUSED_MAX_TOKENS tokens take the one-launch expert kernel
     void *xh = nullptr, *xl = nullptr, *chain_h = nullptr, *chain_l = nullptr;   // fp16 operands (hi, lo) of the tensor-core path
     bool tc_ready = false;                     // tensor maps built (needs hidden, inter multiples of 64)
     TcMaps x_maps, chain_maps;                 // TMA descriptors of (xh, xl) and (chain_h, chain_l)
@@ -105,6 +108,7 @@ static void free_stack(Stack* s) {
     cudaFree(s->reduced); cudaFree(s->act_a); cudaFree(s->act_b); cudaFree(s->io_in); cudaFree(s->io_out);
     cudaFree(s->selected); cudaFree(s->group_offsets); cudaFree(s->g2c); cudaFree(s->c2g);
     cudaFree(s->counters); cudaFree(s->status); cudaFree(s->gateup_jobs); cudaFree(s->down_jobs);
+    cudaFree(s->fused_jobs); cudaFree(s->fused_done);
     cudaFree(s->xh); cudaFree(s->xl); cudaFree(s->chain_h); cudaFree(s->chain_l);
     if (s->h_in) cudaFreeHost(s->h_in);
     if (s->h_out) cudaFreeHost(s->h_out);
@@ -158,6 +162,7 @@ int salt_b200_stack_create(int max_tokens, int hidden, int inter, int n_experts,
               dev_alloc(&s->group_offsets, (size_t)n_experts + 1) && dev_alloc(&s->g2c, J) &&
               dev_alloc(&s->c2g, J) && dev_alloc(&s->counters, 4) && dev_alloc(&s->status, 1) &&
               dev_alloc(&s->gateup_jobs, (size_t)n_experts) && dev_alloc(&s->down_jobs, (size_t)n_experts) &&
+              dev_alloc(&s->fused_jobs, (size_t)FUSED_MAX_JOBS) && dev_alloc(&s->fused_done, (size_t)FUSED_MAX_JOBS) &&
               dev_alloc((uint16_t**)&s->xh, J * hidden) && dev_alloc((uint16_t**)&s->chain_h, J * inter) &&
               dev_alloc((uint16_t**)&s->xl, J * hidden) && dev_alloc((uint16_t**)&s->chain_l, J * inter) &&
               cuda_ok(cudaMemset(s->status, 0, sizeof(int32_t)), "status") &&
@@ -207,6 +212,13 @@ int salt_b200_stack_add_q4_layer(void* stack, const SaltB200Q4LayerSpec* spec) {
     return (int)s->layers.size() - 1;
 }
 
+int salt_b200_stack_set_fused_decode(void* stack, int enable) {
+    Stack* s = (Stack*)stack;
+    if (!s) return -1;
+    s->fused_decode = enable != 0;
+    return 0;
+}
+
 int salt_b200_stack_workspace(void* stack, SaltB200Workspace* out) {
     Stack* s = (Stack*)stack;
     if (!s || !out) return -1;
@@ -233,7 +245,7 @@ int salt_b200_stack_set_grouped_out(void* stack, void* device_buffer, size_t nby
 
 // flags for salt_b200_layer_experts / salt_b200_layer_combine
 enum { SB_EXPERTS_ZERO_REMOTE = 1, SB_EXPERTS_ROUTER_INPUT_READY = 2, SB_EXPERTS_TENSOR_CORE = 4,
-       SB_EXPERTS_TENSOR_CORE_SINGLE = 8 };
+       SB_EXPERTS_TENSOR_CORE_SINGLE = 8, SB_EXPERTS_TWO_LAUNCHES = 16 };
 enum { SB_COMBINE_NORM = 1, SB_COMBINE_PREPARE_NEXT = 2 };
 
 // d_router_src feeds the router input (unless it is already prepared), d_x the expert projections.
@@ -286,12 +298,30 @@ static int layer_experts_impl(Stack* s, int layer, const float* d_router_src, co
     a.tensor_bytes = a.value_bytes + 2 * a.group_bytes;
     a.hidden = H; a.inter = M; a.x = d_x; a.chain = s->chain; a.grouped_out = s->grouped_out;
     a.gateup_jobs = s->gateup_jobs; a.down_jobs = s->down_jobs; a.status = s->status;
+    const int local = s->expert_end - s->expert_begin;
+    const int njobs_max = jobs < local ? jobs : local;
+    // decode batches: gate/up, GeGLU and down of all selected experts in one launch
+    const bool fused = s->fused_decode && !(flags & (SB_EXPERTS_TENSOR_CORE | SB_EXPERTS_TENSOR_CORE_SINGLE |
+                                                     SB_EXPERTS_TWO_LAUNCHES)) &&
+                       B <= FUSED_MAX_TOKENS && njobs_max <= FUSED_MAX_JOBS &&
+                       ((((uintptr_t)d_x) | ((uintptr_t)l.pool) | l.expert_stride) & 15) == 0 &&
+                       q4_fused_plan(H, M, B, njobs_max, nullptr);
+    if (fused) { a.fused_jobs = s->fused_jobs; a.fused_done = s->fused_done; }
     {
         Timed t(s, KC_PLAN, st);
         if (!cuda_ok(launch_moe_plan(a, st), "plan")) return -1;
     }
-    const int local = s->expert_end - s->expert_begin;
-    const int njobs_max = jobs < local ? jobs : local;
+    if (fused) {
+        FusedArgs f;
+        memset(&f, 0, sizeof f);
+        f.jobs = s->fused_jobs; f.n_jobs_dev = s->counters; f.n_jobs_max = njobs_max; f.done = s->fused_done;
+        f.x = d_x; f.x_stride = H; f.n_x = B; f.chain = s->chain; f.out = s->grouped_out; f.H = H; f.M = M;
+        f.status = s->status;
+        Timed t(s, KC_GATE_UP, st);
+        if (!cuda_ok(launch_q4_fused(f, st), "fused experts")) return -1;
+        count_launches(3);
+        return 0;
+    }
     // tokens per expert group: at most B; the kernels loop over larger groups
     const int tok_hint = B == 1 ? 1 : (B == 2 ? 2 : 4);
     if (flags & (SB_EXPERTS_TENSOR_CORE | SB_EXPERTS_TENSOR_CORE_SINGLE)) {

@@ -1,20 +1,19 @@
-// Affine-Q4 (group 64, bf16 scale + bias) projection kernels, bit-exact against
-// the reference row DAG (reference src/kernels.c:220-250):
+// Affine-Q4 (group 64, bf16 scale + bias) arithmetic shared by the projection kernels, bit-exact
+// against the reference row DAG (reference src/kernels.c:220-250):
 //
 //   for c ascending:  d = fl(fl(q*s) + b);  p = fl(d * x[c]);
 //                     acc[c & 31] = fl(acc[c & 31] + p)
 //   L_j = ((((0 + acc[j]) + acc[j+4]) + ...) + acc[j+28]),  j = 0..3
 //   y   = fl(fl(L0 + L2) + fl(L1 + L3))
 //
-// Thread mapping of the tiled kernel: eight lanes share a weight row; lane
-// octant u owns accumulators 4u..4u+3, i.e. the four nibbles of half-word u of
-// every 32-column step (16 packed bytes).  Each lane keeps two weight rows
-// (gate + up of the same output row, or rows r and r+8) so the activation
-// values it loads are used twice, and TT tokens share one dequantisation.
-// Dequantisation and the products are issued as sm_100 packed pairs
-// (add/mul/fma.rn.f32x2): each half of a pair is an independent IEEE
-// round-to-nearest operation.  An add that consumes a packed product is always
-// a scalar add.rn.f32 (see mul_then_add in q4_kernels.cu for why).
+// Thread mapping: sixteen adjacent lanes share a weight row; lane v = tid & 15 owns the
+// accumulators 2v and 2v + 1, i.e. the two nibbles of byte v of every 32-column step (16 packed
+// bytes), so "accumulator c mod 32, columns ascending" is a sequential loop per lane and the
+// canonical fold is a chain through the sixteen lanes.  Each lane keeps two weight rows (gate +
+// up of the same output row, or two rows of one matrix) so the activation values it loads are
+// used twice, and TT tokens share one dequantisation.  Dequantisation and the products are
+// issued as sm_100 packed pairs (add/mul/fma.rn.f32x2): each half of a pair is an independent
+// IEEE round-to-nearest operation.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -65,7 +64,6 @@ __device__ __forceinline__ f32x2 pack2u(uint32_t lo, uint32_t hi) {
 __device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) {
     asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
 }
-#ifndef SB_SCALAR_MATH
 __device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
     f32x2 r;
     asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
@@ -81,23 +79,6 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
     return r;
 }
-#else
-__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
-    float a0, a1, b0, b1;
-    unpack2(a, a0, a1); unpack2(b, b0, b1);
-    return pack2(__fadd_rn(a0, b0), __fadd_rn(a1, b1));
-}
-__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
-    float a0, a1, b0, b1;
-    unpack2(a, a0, a1); unpack2(b, b0, b1);
-    return pack2(__fmul_rn(a0, b0), __fmul_rn(a1, b1));
-}
-__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
-    float a0, a1, b0, b1, c0, c1;
-    unpack2(a, a0, a1); unpack2(b, b0, b1); unpack2(c, c0, c1);
-    return pack2(__fmaf_rn(a0, b0, c0), __fmaf_rn(a1, b1, c1));
-}
-#endif
 
 // Exponent patterns of 2^23, 2^19, 2^15, 2^11.  They are read from constant
 // memory into registers on purpose: with the pattern in a register and the
@@ -105,7 +86,7 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
 // logic operation; written with two literals the compiler emits two.
 __constant__ uint32_t c_nibble_magic[4] = {0x4b000000u, 0x49000000u, 0x47000000u, 0x45000000u};
 
-// -0.0f, kept out of the compiler's sight (see product_then_add in q4_kernels.cu).
+// -0.0f, kept out of the compiler's sight (see product_then_add).
 __constant__ uint32_t c_neg_zero = 0x80000000u;
 
 struct NibbleMagic {
@@ -115,6 +96,110 @@ __device__ __forceinline__ NibbleMagic load_nibble_magic() {
     NibbleMagic m;
     m.m0 = c_nibble_magic[0]; m.m1 = c_nibble_magic[1]; m.m2 = c_nibble_magic[2]; m.m3 = c_nibble_magic[3];
     return m;
+}
+
+// acc = fl(acc + fl(d * x)) on register pairs.  ptxas contracts a packed multiply followed
+// by a packed add (and even a packed fma with a multiplier of 1) into one fused
+// multiply-add, which changes the last bit.  The product is therefore formed as
+// fma(d, x, -0): adding -0 leaves every product, signed zeros included, unchanged, a fused
+// multiply-add cannot be merged into the following add, and the -0 comes from constant
+// memory so that the compiler cannot simplify the fma back into a multiply.
+__device__ __forceinline__ void product_then_add(f32x2& acc, f32x2 d, f32x2 x, f32x2 negzero) {
+    acc = add2(acc, fma2(d, x, negzero));
+}
+
+// ---- the tile kernel: 16 lanes per row ----------------------------------------------
+// A row's 32 accumulators are spread over sixteen adjacent lanes (lane v = tid & 15 holds
+// acc[2v], acc[2v + 1], i.e. one packed byte per 32-column step).  An earlier form with eight
+// lanes per row (four accumulators each, half the warps) ran decode at the same speed and
+// batches of 64 tokens 1.4x slower.
+
+// One packed byte (two nibbles) as exact floats.
+template <bool LIT>
+__device__ __forceinline__ f32x2 dequant2(uint32_t b, const NibbleMagic& mg, f32x2 ss, f32x2 bb) {
+    const f32x2 neg01 = pack2(-8388608.0f, -524288.0f);
+    uint32_t f0, f1;
+    asm("lop3.b32 %0, %1, 0x0f, %2, 0xEA;" : "=r"(f0) : "r"(b), "r"(mg.m0));
+    asm("lop3.b32 %0, %1, 0xf0, %2, 0xEA;" : "=r"(f1) : "r"(b), "r"(mg.m1));
+    const f32x2 q = add2(pack2u(f0, f1), neg01);
+    if (LIT) {
+        float p0, p1, b0, b1;
+        unpack2(mul2(q, ss), p0, p1);
+        unpack2(bb, b0, b1);
+        return pack2(__fadd_rn(p0, b0), __fadd_rn(p1, b1));
+    }
+    return fma2(q, ss, bb);
+}
+
+template <int TT, bool LIT, int NSTEPS>
+__device__ __forceinline__ void tile16_steps(const NibbleMagic& mg, const uint8_t* wA, const uint8_t* wB,
+                                             const uint32_t* tA, const uint32_t* tB, const float* const (&xs)[TT],
+                                             f32x2 (&accA)[TT], f32x2 (&accB)[TT], f32x2 nz) {
+#pragma unroll
+    for (int g = 0; g < NSTEPS / 2; g++) {
+        const uint32_t wa = tA[g], wb = tB[g];
+        const float sa = __uint_as_float(wa & 0xffff0000u), ba = __uint_as_float(wa << 16);
+        const float sb_ = __uint_as_float(wb & 0xffff0000u), bb_ = __uint_as_float(wb << 16);
+        const f32x2 ssA = pack2(sa, sa), bbA = pack2(ba, ba), ssB = pack2(sb_, sb_), bbB = pack2(bb_, bb_);
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            const int k = 2 * g + half;
+            const f32x2 dA = dequant2<LIT>(wA[k * 16], mg, ssA, bbA);
+            const f32x2 dB = dequant2<LIT>(wB[k * 16], mg, ssB, bbB);
+#pragma unroll
+            for (int tt = 0; tt < TT; tt++) {
+                const f32x2 xv = *(const f32x2*)(xs[tt] + k * 32);
+                product_then_add(accA[tt], dA, xv, nz);
+                product_then_add(accB[tt], dB, xv, nz);
+            }
+        }
+    }
+}
+
+template <int TT, bool LIT>
+__device__ __forceinline__ void tile16_run(const NibbleMagic& mg, int s_begin, int s_end, const uint8_t* wA,
+                                           const uint8_t* wB, const uint32_t* tA, const uint32_t* tB,
+                                           const float* sX, int x_pitch, f32x2 (&accA)[TT], f32x2 (&accB)[TT],
+                                           f32x2 nz) {
+    int st = s_begin;
+    constexpr int BLK = 8;
+    for (; st + BLK <= s_end; st += BLK) {
+        const float* xs[TT];
+#pragma unroll
+        for (int tt = 0; tt < TT; tt++) xs[tt] = sX + tt * x_pitch + st * 32;
+        tile16_steps<TT, LIT, BLK>(mg, wA + st * 16, wB + st * 16, tA + (st >> 1), tB + (st >> 1), xs, accA, accB, nz);
+    }
+    for (; st + 2 <= s_end; st += 2) {
+        const float* xs[TT];
+#pragma unroll
+        for (int tt = 0; tt < TT; tt++) xs[tt] = sX + tt * x_pitch + st * 32;
+        tile16_steps<TT, LIT, 2>(mg, wA + st * 16, wB + st * 16, tA + (st >> 1), tB + (st >> 1), xs, accA, accB, nz);
+    }
+}
+
+// Canonical fold (src/kernels.c:240-250) of a row whose accumulators sit two per lane in
+// sixteen adjacent lanes: L_j = sum over a = 0..7 of acc[4a + j], added in that order from
+// +0, then y = (L0 + L2) + (L1 + L3).  acc[4a + j] is component j & 1 of lane 2a + (j >> 1).
+// mask: the lanes that take part (the whole warp, or the row's own sixteen lanes when the two
+// halves of a warp may run different code).
+__device__ __forceinline__ float fold_row_hexadecants(f32x2 acc, int v, uint32_t mask = 0xffffffffu) {
+    float lo, hi;
+    unpack2(acc, lo, hi);
+    const int j = v & 3;
+    const int base = (threadIdx.x & 31) & ~15;
+    float L = 0.0f;
+#pragma unroll
+    for (int a = 0; a < 8; a++) {
+        const int src = base + 2 * a + (j >> 1);
+        const float vlo = __shfl_sync(mask, lo, src);
+        const float vhi = __shfl_sync(mask, hi, src);
+        L = __fadd_rn(L, (j & 1) ? vhi : vlo);
+    }
+    const float L0 = __shfl_sync(mask, L, base + 0);
+    const float L1 = __shfl_sync(mask, L, base + 1);
+    const float L2 = __shfl_sync(mask, L, base + 2);
+    const float L3 = __shfl_sync(mask, L, base + 3);
+    return __fadd_rn(__fadd_rn(L0, L2), __fadd_rn(L1, L3));
 }
 
 // The four nibbles of one packed half-word as exact floats 0..15, as two pairs.
@@ -130,27 +215,6 @@ __device__ __forceinline__ void nibbles4(uint32_t h, const NibbleMagic& mg, f32x
     asm("lop3.b32 %0, %1, 0xf000, %2, 0xEA;" : "=r"(f3) : "r"(h), "r"(mg.m3));
     q01 = add2(pack2u(f0, f1), neg01);
     q23 = add2(pack2u(f2, f3), neg23);
-}
-
-// d = fl(fl(q*s) + b) for four elements.  LIT selects the literal two-rounding
-// form (needed only when q*s could overflow).
-template <bool LIT>
-__device__ __forceinline__ void dequant4(uint32_t h, const NibbleMagic& mg, f32x2 ss, f32x2 bb, f32x2& d01,
-                                         f32x2& d23) {
-    f32x2 q01, q23;
-    nibbles4(h, mg, q01, q23);
-    if (LIT) {
-        // two roundings; scalar adds, because ptxas contracts packed mul + packed add
-        float p0, p1, p2, p3, b0, b1;
-        unpack2(mul2(q01, ss), p0, p1);
-        unpack2(mul2(q23, ss), p2, p3);
-        unpack2(bb, b0, b1);
-        d01 = pack2(__fadd_rn(p0, b0), __fadd_rn(p1, b1));
-        d23 = pack2(__fadd_rn(p2, b0), __fadd_rn(p3, b1));
-    } else {
-        d01 = fma2(q01, ss, bb);
-        d23 = fma2(q23, ss, bb);
-    }
 }
 
 // Canonical fold of one row whose 32 accumulators live 4 per lane in eight

@@ -35,6 +35,7 @@
 
 #include <stdlib.h>
 #include "internal.h"
+#include "mbar.cuh"
 #include "q4_core.cuh"
 
 namespace sb {
@@ -48,16 +49,6 @@ constexpr int TC_MAX_NT = 128;
 constexpr int TC_MAX_BSLOTS = 8;
 constexpr int TC_SMEM_BYTES = 225 * 1024;    // dynamic shared memory of every launch (one block per SM)
 constexpr uint32_t TC_SPIN_LIMIT = 1u << 22;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 
 // Bounded wait for the phase with the given parity.  Returns false on expiry or when
 // another thread of the block has raised the failure flag.
@@ -95,11 +86,6 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t lo, uint32_t hi) {
 // slower here.)
 constexpr uint32_t DESC_B_LO = 1u << 16;
 constexpr uint32_t DESC_B_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
-
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-                 : "memory");
-}
 
 // 2-D tiled TMA load of one box at element column x, row y, into this block's own shared memory.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {

@@ -45,108 +45,6 @@ static __host__ __device__ __forceinline__ TileGeom tile_geom(int C, int rows_a)
     return g;
 }
 
-// acc = fl(acc + fl(d * x)) on register pairs.  ptxas contracts a packed multiply followed
-// by a packed add (and even a packed fma with a multiplier of 1) into one fused
-// multiply-add, which changes the last bit.  The product is therefore formed as
-// fma(d, x, -0): adding -0 leaves every product, signed zeros included, unchanged, a fused
-// multiply-add cannot be merged into the following add, and the -0 comes from constant
-// memory so that the compiler cannot simplify the fma back into a multiply.
-__device__ __forceinline__ void product_then_add(f32x2& acc, f32x2 d, f32x2 x, f32x2 negzero) {
-    acc = add2(acc, fma2(d, x, negzero));
-}
-
-// ---- the tile kernel: 16 lanes per row ----------------------------------------------
-// A row's 32 accumulators are spread over sixteen adjacent lanes (lane v = tid & 15 holds
-// acc[2v], acc[2v + 1], i.e. one packed byte per 32-column step).  An earlier form with eight
-// lanes per row (four accumulators each, half the warps) ran decode at the same speed and
-// batches of 64 tokens 1.4x slower.
-
-// One packed byte (two nibbles) as exact floats.
-template <bool LIT>
-__device__ __forceinline__ f32x2 dequant2(uint32_t b, const NibbleMagic& mg, f32x2 ss, f32x2 bb) {
-    const f32x2 neg01 = pack2(-8388608.0f, -524288.0f);
-    uint32_t f0, f1;
-    asm("lop3.b32 %0, %1, 0x0f, %2, 0xEA;" : "=r"(f0) : "r"(b), "r"(mg.m0));
-    asm("lop3.b32 %0, %1, 0xf0, %2, 0xEA;" : "=r"(f1) : "r"(b), "r"(mg.m1));
-    const f32x2 q = add2(pack2u(f0, f1), neg01);
-    if (LIT) {
-        float p0, p1, b0, b1;
-        unpack2(mul2(q, ss), p0, p1);
-        unpack2(bb, b0, b1);
-        return pack2(__fadd_rn(p0, b0), __fadd_rn(p1, b1));
-    }
-    return fma2(q, ss, bb);
-}
-
-template <int TT, bool LIT, int NSTEPS>
-__device__ __forceinline__ void tile16_steps(const NibbleMagic& mg, const uint8_t* wA, const uint8_t* wB,
-                                             const uint32_t* tA, const uint32_t* tB, const float* const (&xs)[TT],
-                                             f32x2 (&accA)[TT], f32x2 (&accB)[TT], f32x2 nz) {
-#pragma unroll
-    for (int g = 0; g < NSTEPS / 2; g++) {
-        const uint32_t wa = tA[g], wb = tB[g];
-        const float sa = __uint_as_float(wa & 0xffff0000u), ba = __uint_as_float(wa << 16);
-        const float sb_ = __uint_as_float(wb & 0xffff0000u), bb_ = __uint_as_float(wb << 16);
-        const f32x2 ssA = pack2(sa, sa), bbA = pack2(ba, ba), ssB = pack2(sb_, sb_), bbB = pack2(bb_, bb_);
-#pragma unroll
-        for (int half = 0; half < 2; half++) {
-            const int k = 2 * g + half;
-            const f32x2 dA = dequant2<LIT>(wA[k * 16], mg, ssA, bbA);
-            const f32x2 dB = dequant2<LIT>(wB[k * 16], mg, ssB, bbB);
-#pragma unroll
-            for (int tt = 0; tt < TT; tt++) {
-                const f32x2 xv = *(const f32x2*)(xs[tt] + k * 32);
-                product_then_add(accA[tt], dA, xv, nz);
-                product_then_add(accB[tt], dB, xv, nz);
-            }
-        }
-    }
-}
-
-template <int TT, bool LIT>
-__device__ __forceinline__ void tile16_run(const NibbleMagic& mg, int s_begin, int s_end, const uint8_t* wA,
-                                           const uint8_t* wB, const uint32_t* tA, const uint32_t* tB,
-                                           const float* sX, int x_pitch, f32x2 (&accA)[TT], f32x2 (&accB)[TT],
-                                           f32x2 nz) {
-    int st = s_begin;
-    constexpr int BLK = 8;
-    for (; st + BLK <= s_end; st += BLK) {
-        const float* xs[TT];
-#pragma unroll
-        for (int tt = 0; tt < TT; tt++) xs[tt] = sX + tt * x_pitch + st * 32;
-        tile16_steps<TT, LIT, BLK>(mg, wA + st * 16, wB + st * 16, tA + (st >> 1), tB + (st >> 1), xs, accA, accB, nz);
-    }
-    for (; st + 2 <= s_end; st += 2) {
-        const float* xs[TT];
-#pragma unroll
-        for (int tt = 0; tt < TT; tt++) xs[tt] = sX + tt * x_pitch + st * 32;
-        tile16_steps<TT, LIT, 2>(mg, wA + st * 16, wB + st * 16, tA + (st >> 1), tB + (st >> 1), xs, accA, accB, nz);
-    }
-}
-
-// Canonical fold (src/kernels.c:240-250) of a row whose accumulators sit two per lane in
-// sixteen adjacent lanes: L_j = sum over a = 0..7 of acc[4a + j], added in that order from
-// +0, then y = (L0 + L2) + (L1 + L3).  acc[4a + j] is component j & 1 of lane 2a + (j >> 1).
-__device__ __forceinline__ float fold_row_hexadecants(f32x2 acc, int v) {
-    float lo, hi;
-    unpack2(acc, lo, hi);
-    const int j = v & 3;
-    const int base = (threadIdx.x & 31) & ~15;
-    float L = 0.0f;
-#pragma unroll
-    for (int a = 0; a < 8; a++) {
-        const int src = base + 2 * a + (j >> 1);
-        const float vlo = __shfl_sync(0xffffffffu, lo, src);
-        const float vhi = __shfl_sync(0xffffffffu, hi, src);
-        L = __fadd_rn(L, (j & 1) ? vhi : vlo);
-    }
-    const float L0 = __shfl_sync(0xffffffffu, L, base + 0);
-    const float L1 = __shfl_sync(0xffffffffu, L, base + 1);
-    const float L2 = __shfl_sync(0xffffffffu, L, base + 2);
-    const float L3 = __shfl_sync(0xffffffffu, L, base + 3);
-    return __fadd_rn(__fadd_rn(L0, L2), __fadd_rn(L1, L3));
-}
-
 // The work of one block once its job is known: TT tokens of the group per pass.
 // HALF = row slots of a block (8 or 16): 16 * HALF threads, 2 * HALF weight rows in shared
 // memory (NMAT == 2: HALF gate rows then HALF up rows; NMAT == 1: slot pr owns rows pr and
@@ -184,9 +82,7 @@ __device__ void tile16_block(const Q4Job& jb, int C, int jobs_early) {
     const uint8_t* f_src = (f_m == 0 ? jb.vals : jb.vals2) + (size_t)f_grow * G.row_bytes + f_pc * 16;
     uint8_t* f_dst = sW + f_rr * G.w_stride + f_pc * 16;
     if (fast_chunks && f_pc < G.steps) {
-#ifndef SB_EXP_NOLOAD
         cp_async16(f_dst, f_src);
-#endif
     }
     auto issue_x = [&](int tb) {
         const int ppr = C >> 2;                  // 16-byte pieces per activation row
@@ -235,9 +131,7 @@ __device__ void tile16_block(const Q4Job& jb, int C, int jobs_early) {
     if (fast_chunks) {
         cp_async_commit();
         for (int ch = 1; ch < G.nch; ch++) {
-#ifndef SB_EXP_NOLOAD
             if (ch * 8 + f_pc < G.steps) cp_async16(f_dst + ch * 128, f_src + ch * 128);
-#endif
             cp_async_commit();
         }
     } else {
@@ -300,12 +194,8 @@ __device__ void tile16_block(const Q4Job& jb, int C, int jobs_early) {
             }
             const int s_begin = ch * G.chunk_steps;
             const int s_end = min(s_begin + G.chunk_steps, G.steps);
-#ifndef SB_EXP_NOCOMPUTE
             if (lit) tile16_run<TT, true>(mg, s_begin, s_end, wA, wB, tA, tB, xs, C, accA, accB, nz);
             else tile16_run<TT, false>(mg, s_begin, s_end, wA, wB, tA, tB, xs, C, accA, accB, nz);
-#else
-            accA[0] = add2(accA[0], pack2(*(const float*)(wA - v + s_begin * 16), (float)lit));
-#endif
         }
 #pragma unroll
         for (int tt = 0; tt < TT; tt++) {

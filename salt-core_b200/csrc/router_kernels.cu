@@ -1280,6 +1280,8 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(MoePlanArgs a) {
             hist[warp * E + e] += __popc(peers);
         __syncwarp();
     }
+    if (a.fused_done != nullptr && threadIdx.x < FUSED_MAX_JOBS) a.fused_done[threadIdx.x] = 0;
+    __syncthreads();               // the placement is complete: the descriptors below read it back
     // job descriptors for the local, non-empty experts (ascending expert order)
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
         const int slot = act[e];
@@ -1302,6 +1304,16 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(MoePlanArgs a) {
         dn.x_rows = nullptr; dn.x_div = 1;
         dn.R = a.hidden; dn.C = a.inter; dn.ntok = cnt; dn.x_stride = a.inter; dn.y_stride = a.hidden;
         a.down_jobs[slot] = dn;
+        if (a.fused_jobs != nullptr && slot < FUSED_MAX_JOBS) {
+            FusedJob fj;
+            fj.gate_v = gu.vals; fj.gate_s = gu.scales; fj.gate_b = gu.biases;
+            fj.up_v = gu.vals2; fj.up_s = gu.scales2; fj.up_b = gu.biases2;
+            fj.down_v = dn.vals; fj.down_s = dn.scales; fj.down_b = dn.biases;
+            for (int t = 0; t < FUSED_MAX_TOKENS; t++)
+                fj.x_row[t] = a.grouped_to_canonical[g0 + min(t, cnt - 1)] / a.topk;
+            fj.g0 = g0; fj.ntok = cnt;
+            a.fused_jobs[slot] = fj;
+        }
     }
 }
 
@@ -1316,7 +1328,8 @@ __global__ void __launch_bounds__(512) moe_plan_small_kernel(MoePlanArgs a) {
     const int E = a.n_experts;
     pdl_wait();                    // the logits come from the previous kernel
     pdl_launch_dependents();
-    __shared__ int s_sel[32], s_first[32];
+    __shared__ int s_sel[32], s_first[32], s_g2c[32];
+    if (a.fused_done != nullptr && threadIdx.x < FUSED_MAX_JOBS) a.fused_done[threadIdx.x] = 0;
     {
         float* tk = (float*)sp;
         const int grp = threadIdx.x >> 7, ltid = threadIdx.x & 127;
@@ -1343,6 +1356,7 @@ __global__ void __launch_bounds__(512) moe_plan_small_kernel(MoePlanArgs a) {
         if (e >= 0) {
             a.grouped_to_canonical[before] = lane;
             a.canonical_to_grouped[lane] = before;
+            s_g2c[before] = lane;
         }
         s_sel[lane] = e;
         s_first[lane] = (e >= 0 && first) ? 1 : 0;
@@ -1379,6 +1393,16 @@ __global__ void __launch_bounds__(512) moe_plan_small_kernel(MoePlanArgs a) {
         dn.x_rows = nullptr; dn.x_div = 1;
         dn.R = a.hidden; dn.C = a.inter; dn.ntok = cnt; dn.x_stride = a.inter; dn.y_stride = a.hidden;
         a.down_jobs[slot] = dn;
+        if (a.fused_jobs != nullptr && slot < FUSED_MAX_JOBS) {
+            FusedJob fj;
+            fj.gate_v = gu.vals; fj.gate_s = gu.scales; fj.gate_b = gu.biases;
+            fj.up_v = gu.vals2; fj.up_s = gu.scales2; fj.up_b = gu.biases2;
+            fj.down_v = dn.vals; fj.down_s = dn.scales; fj.down_b = dn.biases;
+            for (int t = 0; t < FUSED_MAX_TOKENS; t++)
+                fj.x_row[t] = s_g2c[g0 + min(t, cnt - 1)] / a.topk;
+            fj.g0 = g0; fj.ntok = cnt;
+            a.fused_jobs[slot] = fj;
+        }
     }
     if (threadIdx.x == 0) {
         int n_active = 0, max_group = 0;

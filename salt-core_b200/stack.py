@@ -79,6 +79,10 @@ class MoeStack:
             raise RuntimeError("salt_b200_stack_workspace failed")
         return w
 
+    def set_fused_decode(self, enable):
+        """Batches of up to 4 tokens: one-launch expert kernel (default) or the two-launch form."""
+        return self.lib.salt_b200_stack_set_fused_decode(self.handle, int(bool(enable)))
+
     def set_grouped_out(self, device_ptr, nbytes):
         return self.lib.salt_b200_stack_set_grouped_out(self.handle, C.c_void_p(device_ptr), C.c_size_t(nbytes))
 
@@ -102,10 +106,10 @@ class MoeStack:
     COMBINE_NORM, COMBINE_PREPARE_NEXT = 1, 2
 
     def layer_experts(self, layer, d_x, B, zero_remote=False, router_input_ready=False, tensor_core=False,
-                      stream=0):
+                      two_launches=False, stream=0):
         """tensor_core: False (exact kernels), True / "split" (hi+lo fp16 operands), "single"."""
         tc = 0 if not tensor_core else (8 if tensor_core == "single" else 4)
-        flags = (1 if zero_remote else 0) | (2 if router_input_ready else 0) | tc
+        flags = (1 if zero_remote else 0) | (2 if router_input_ready else 0) | tc | (16 if two_launches else 0)
         return self.lib.salt_b200_layer_experts(self.handle, layer, C.c_void_p(d_x), B, flags, C.c_void_p(stream))
 
     def layer_combine(self, layer, B, d_y, apply_norm=True, prepare_next=False, stream=0):
