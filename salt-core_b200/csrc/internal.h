@@ -25,7 +25,7 @@ cudaError_t launch_q4_jobs(const Q4Job* jobs, int njobs_max, const int* njobs_de
 constexpr int FUSED_MAX_JOBS = 32;       // expert groups per launch
 constexpr int FUSED_MAX_TOKENS = 4;      // activation rows per launch (and tokens per group)
 struct FusedJob {
-    const uint8_t *gate_v, *gate_s, *gate_b;   // packed values, bf16 scales, bf16 biases (null: bias 0)
+    const uint8_t *gate_v, *gate_s, *gate_b;   // packed values, bf16 scales, bf16 biases (all present, 16-byte aligned)
     const uint8_t *up_v, *up_s, *up_b;
     const uint8_t *down_v, *down_s, *down_b;
     int32_t x_row[FUSED_MAX_TOKENS];           // activation row of each token of the group

@@ -223,24 +223,25 @@ __device__ __forceinline__ void nibbles4(uint32_t h, const NibbleMagic& mg, f32x
 // runs the chain L_j = (((0 + acc[j]) + acc[4 + j]) + ...) for j = u & 3 (lanes
 // 4..7 repeat lanes 0..3); the four L values are then combined as
 // (L0 + L2) + (L1 + L3).  The result is valid in every lane of the octet.
-__device__ __forceinline__ float fold_row_octants(const float (&a)[4], int u) {
+// mask: the lanes that take part (the whole warp, or the row's own eight lanes).
+__device__ __forceinline__ float fold_row_octants(const float (&a)[4], int u, uint32_t mask = 0xffffffffu) {
     const int j = u & 3;
     const int base = (threadIdx.x & 31) & ~7;
     float L = 0.0f;
 #pragma unroll
     for (int s = 0; s < 8; s++) {
         // every lane offers all four of its accumulators; the reader picks column j of octant s
-        const float v0 = __shfl_sync(0xffffffffu, a[0], base + s);
-        const float v1 = __shfl_sync(0xffffffffu, a[1], base + s);
-        const float v2 = __shfl_sync(0xffffffffu, a[2], base + s);
-        const float v3 = __shfl_sync(0xffffffffu, a[3], base + s);
+        const float v0 = __shfl_sync(mask, a[0], base + s);
+        const float v1 = __shfl_sync(mask, a[1], base + s);
+        const float v2 = __shfl_sync(mask, a[2], base + s);
+        const float v3 = __shfl_sync(mask, a[3], base + s);
         const float v = j == 0 ? v0 : (j == 1 ? v1 : (j == 2 ? v2 : v3));
         L = __fadd_rn(L, v);
     }
-    const float L0 = __shfl_sync(0xffffffffu, L, base + 0);
-    const float L1 = __shfl_sync(0xffffffffu, L, base + 1);
-    const float L2 = __shfl_sync(0xffffffffu, L, base + 2);
-    const float L3 = __shfl_sync(0xffffffffu, L, base + 3);
+    const float L0 = __shfl_sync(mask, L, base + 0);
+    const float L1 = __shfl_sync(mask, L, base + 1);
+    const float L2 = __shfl_sync(mask, L, base + 2);
+    const float L3 = __shfl_sync(mask, L, base + 3);
     return __fadd_rn(__fadd_rn(L0, L2), __fadd_rn(L1, L3));
 }
 

@@ -2,18 +2,21 @@
 // expert of a layer, bit-exact against the reference row DAG (src/kernels.c:220-250, GeGLU
 // models/gemma4-26b-a4b/src/gemma4.c:80-83).
 //
-// One persistent block per SM, SLOTS row slots of 16 lanes each.  The selected experts are
+// One persistent block per SM, SLOTS row slots of 16 lanes each (a slot = a gate row and its up
+// row, or two adjacent down rows).  The selected experts are
 // processed in rounds of up to `jobs_per_round` jobs.  Inside a round the jobs' gate/up row
 // pairs form one index space [0, J*M) and their down rows another [0, J*H); block i owns the
 // contiguous share [i*P, (i+1)*P) of the first and [i*Q, (i+1)*Q) of the second, so every SM
 // streams the same number of bytes whatever the number of experts.
 //
-//   * every packed weight row is one cp.async.bulk copy (global -> shared, tracked by an
-//     mbarrier with a transaction count) into a padded row of shared memory; a warp issues
-//     the copies of its own rows, and the copies of BOTH phases are issued before the first
-//     product is formed: the down rows are in flight while gate/up computes;
-//   * the bf16 scales and biases of a warp's rows are fetched with plain loads and interleaved
-//     into one word per quantisation group;
+//   * every packed gate/up row is one cp.async.bulk copy (global -> shared, tracked by an
+//     mbarrier with a transaction count) into a padded row of shared memory, issued by the warp
+//     that owns the row; the block's down rows are contiguous and go in one copy; the copies of
+//     BOTH phases are issued before the first product is formed, so the down rows are in flight
+//     while gate/up computes;
+//   * the bf16 scales and biases of a block's share are contiguous in memory: each tensor's
+//     range (widened to 16-byte boundaries) is one more bulk copy; the warps then interleave them
+//     in place into one word per quantisation group;
 //   * the GeGLU values go through global memory (a few KB that stay in L2): a block adds the
 //     number of row pairs it finished to a per-job arrival counter (release), and a block
 //     whose down rows need that job polls the counter (acquire, bounded), then reads the
@@ -22,6 +25,9 @@
 //     a block never waits before its own gate/up share is done, so residency is the only
 //     condition for progress.  Every wait is bounded; on expiry the block records
 //     SB_ERR_TIMEOUT in the status word and carries on, so the launch always ends.
+// The kernel runs once per layer between other kernels, so its instructions are fetched cold
+// every time: set-up code is written as short per-lane code instead of unrolled per-row code,
+// and the rarely needed two-rounding dequantisation lives in a function that is not inlined.
 #include "internal.h"
 #include "mbar.cuh"
 #include "pdl.cuh"
@@ -31,12 +37,11 @@ namespace sb {
 
 constexpr uint32_t FUSED_SPIN_LIMIT = 1u << 21;   // polls of a counter or of an mbarrier (a fraction of a second)
 
-// Stride of a packed row in shared memory: the smallest multiple of 16 bytes for which the two
-// rows a warp reads at the same byte index (`apart` rows from each other: adjacent slots hold
-// adjacent gate or up rows, but every second down row) start at least four banks apart.
-static __host__ __device__ __forceinline__ int fused_row_stride(int row_bytes, int apart) {
+// Stride of a packed gate/up row in shared memory: the smallest multiple of 16 bytes for which the
+// rows of two adjacent slots, read by one warp at the same byte index, start at least four banks apart.
+static __host__ __device__ __forceinline__ int fused_row_stride(int row_bytes) {
     int s = row_bytes;
-    while (((s * apart) & 127) < 16 || ((s * apart) & 127) > 112) s += 16;
+    while ((s & 127) < 16 || (s & 127) > 112) s += 16;
     return s;
 }
 
@@ -44,23 +49,26 @@ struct FusedGeom {
     int gu_rb, gu_stride, gu_gpr;     // gate/up: row bytes, padded stride, groups per row
     int dn_rb, dn_stride, dn_gpr;
     int dn_cap;                       // down rows held per block
-    size_t off_dn, off_tgu, off_tdn, off_x, off_chain, off_jobs, off_bars, total;
+    int gu_sc_cap, dn_sc_cap;         // bytes of one staged scale (or bias) range
+    size_t off_dn, off_sgu, off_sdn, off_x, off_chain, off_jobs, off_bars, total;
 };
 
 static __host__ __device__ __forceinline__ FusedGeom fused_geom(int H, int M, int tt, int slots) {
     FusedGeom g;
-    g.gu_rb = H >> 1; g.gu_stride = fused_row_stride(g.gu_rb, 1); g.gu_gpr = H >> 6;
-    g.dn_rb = M >> 1; g.dn_stride = fused_row_stride(g.dn_rb, 2); g.dn_gpr = M >> 6;
+    g.gu_rb = H >> 1; g.gu_stride = fused_row_stride(g.gu_rb); g.gu_gpr = H >> 6;
+    g.dn_rb = M >> 1; g.dn_stride = g.dn_rb; g.dn_gpr = M >> 6;      // dense: the block's down rows arrive as one copy
     g.dn_cap = 4 * slots;
+    // a block's share may touch two jobs: two ranges, each widened to 16-byte boundaries
+    g.gu_sc_cap = ((slots * g.gu_gpr * 2 + 15) & ~15) + 64;
+    g.dn_sc_cap = ((g.dn_cap * g.dn_gpr * 2 + 15) & ~15) + 64;
     size_t o = (size_t)2 * slots * g.gu_stride;
     g.off_dn = o;    o += (size_t)g.dn_cap * g.dn_stride;
-    g.off_tgu = o;   o += (size_t)2 * slots * g.gu_gpr * 4;
-    g.off_tdn = o;   o += (size_t)g.dn_cap * g.dn_gpr * 4;
-    o = (o + 15) & ~(size_t)15;
+    g.off_sgu = o;   o += (size_t)4 * g.gu_sc_cap;       // gate scales, gate biases, up scales, up biases
+    g.off_sdn = o;   o += (size_t)2 * g.dn_sc_cap;       // down scales, down biases
     g.off_x = o;     o += (size_t)tt * H * 4;
     g.off_chain = o; o += (size_t)2 * tt * M * 4;
     g.off_jobs = o;  o += (size_t)FUSED_MAX_JOBS * sizeof(FusedJob);
-    g.off_bars = o;  o += (size_t)(slots + 2) * 8;       // slots/2 gate/up + slots/2 down barriers, one for x
+    g.off_bars = o;  o += (size_t)(slots / 2 + 4) * 8;   // one gate/up barrier per warp, x, gate/up scales, down
     g.total = o;
     return g;
 }
@@ -75,6 +83,7 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 // Bounded wait for the phase with the given parity; false on expiry.
 __device__ __forceinline__ bool fused_mbar_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = smem_u32(bar);
+#pragma unroll 1
     for (uint32_t i = 0; i < FUSED_SPIN_LIMIT; i++) {
         uint32_t ok;
         asm volatile(
@@ -95,48 +104,10 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
     return v;
 }
 
-// (scale bf16 << 16) | bias bf16 for the groups of `nrows` rows owned by one warp.
-// row r of the warp: packed scales at srcs[r], biases at srcb[r] (null: bias 0), table row at dst[r].
-// Returns (in every lane) whether any scale needs the literal two-rounding dequantisation.
-template <int NROWS>
-__device__ __forceinline__ bool fused_build_table(const uint8_t* const (&srcs)[NROWS], const uint8_t* const (&srcb)[NROWS],
-                                                  uint32_t* const (&dst)[NROWS], int gpr, int lane) {
-    int lit = 0;
-#pragma unroll
-    for (int r = 0; r < NROWS; r++) {
-        if (srcs[r] == nullptr) continue;
-        for (int g = lane; g < gpr; g += 32) {
-            const uint32_t hs = __ldg((const uint16_t*)srcs[r] + g);
-            const uint32_t hb = srcb[r] ? (uint32_t)__ldg((const uint16_t*)srcb[r] + g) : 0u;
-            dst[r][g] = (hs << 16) | hb;
-            lit |= scale_needs_literal(hs) ? 1 : 0;
-        }
-    }
-    return __any_sync(0xffffffffu, lit) != 0;
-}
-
-// All 32-column steps of one lane's two rows against TT activation rows.
-template <int TT, bool LIT>
-__device__ __forceinline__ void fused_rows(const NibbleMagic& mg, int steps, const uint8_t* wA, const uint8_t* wB,
-                                           const uint32_t* tA, const uint32_t* tB, const float* const (&xrow)[TT],
-                                           f32x2 (&accA)[TT], f32x2 (&accB)[TT], f32x2 nz) {
-    int st = 0;
-    for (; st + 8 <= steps; st += 8) {
-        const float* xs[TT];
-#pragma unroll
-        for (int tt = 0; tt < TT; tt++) xs[tt] = xrow[tt] + st * 32;
-        tile16_steps<TT, LIT, 8>(mg, wA + st * 16, wB + st * 16, tA + (st >> 1), tB + (st >> 1), xs, accA, accB, nz);
-    }
-    for (; st + 2 <= steps; st += 2) {
-        const float* xs[TT];
-#pragma unroll
-        for (int tt = 0; tt < TT; tt++) xs[tt] = xrow[tt] + st * 32;
-        tile16_steps<TT, LIT, 2>(mg, wA + st * 16, wB + st * 16, tA + (st >> 1), tB + (st >> 1), xs, accA, accB, nz);
-    }
-}
-
-// One lane's two rows for the NT tokens of its job (NT <= TT is the job's token count rounded
-// up to 1, 2 or 4; surplus tokens repeat the last row and are not stored).
+// One lane's two rows for the NT tokens of its job: the dot products in the reference order
+// (tile16_steps: sixteen lanes per row, lane v owns accumulators 2v and 2v + 1) and the canonical
+// fold.  The rarely needed two-rounding form (a scale so large that q*s could overflow) is
+// rolled up, so that it adds little to the code the SM has to fetch.
 template <int NT>
 __device__ __forceinline__ void fused_slot(const NibbleMagic& mg, bool lit, int steps, const uint8_t* wA,
                                            const uint8_t* wB, const uint32_t* tA, const uint32_t* tB,
@@ -148,8 +119,31 @@ __device__ __forceinline__ void fused_slot(const NibbleMagic& mg, bool lit, int 
     f32x2 accA[NT], accB[NT];
 #pragma unroll
     for (int tt = 0; tt < NT; tt++) { accA[tt] = pack2(0.0f, 0.0f); accB[tt] = pack2(0.0f, 0.0f); }
-    if (lit) fused_rows<NT, true>(mg, steps, wA, wB, tA, tB, xrow, accA, accB, nz);
-    else fused_rows<NT, false>(mg, steps, wA, wB, tA, tB, xrow, accA, accB, nz);
+    int st = 0;
+    if (lit) {
+#pragma unroll 1
+        for (; st + 2 <= steps; st += 2) {
+            const float* xs[NT];
+#pragma unroll
+            for (int tt = 0; tt < NT; tt++) xs[tt] = xrow[tt] + st * 32;
+            tile16_steps<NT, true, 2>(mg, wA + st * 16, wB + st * 16, tA + (st >> 1), tB + (st >> 1), xs, accA, accB, nz);
+        }
+    } else {
+#pragma unroll 1
+        for (; st + 8 <= steps; st += 8) {
+            const float* xs[NT];
+#pragma unroll
+            for (int tt = 0; tt < NT; tt++) xs[tt] = xrow[tt] + st * 32;
+            tile16_steps<NT, false, 8>(mg, wA + st * 16, wB + st * 16, tA + (st >> 1), tB + (st >> 1), xs, accA, accB, nz);
+        }
+#pragma unroll 1
+        for (; st + 2 <= steps; st += 2) {
+            const float* xs[NT];
+#pragma unroll
+            for (int tt = 0; tt < NT; tt++) xs[tt] = xrow[tt] + st * 32;
+            tile16_steps<NT, false, 2>(mg, wA + st * 16, wB + st * 16, tA + (st >> 1), tB + (st >> 1), xs, accA, accB, nz);
+        }
+    }
 #pragma unroll
     for (int tt = 0; tt < NT; tt++) {
         yA[tt] = fold_row_hexadecants(accA[tt], v, half_mask);
@@ -157,30 +151,47 @@ __device__ __forceinline__ void fused_slot(const NibbleMagic& mg, bool lit, int 
     }
 }
 
+// A contiguous range of bf16 scales (or biases) staged in shared memory: rows [r0, r1) of one
+// tensor, widened to 16-byte boundaries.  row_ptr(r) = stage + (r * row_bytes - byte0).
+struct ScaleRange {
+    int r0, r1;        // rows
+    int byte0;         // first staged byte (multiple of 16) within the tensor's scale array
+    int stage_off;     // offset of the staged range in its staging area
+};
+
+// Scale / bias words of up to NROWS rows of a warp held in registers between the read of the
+// staged bf16 arrays and the write of the interleaved table that replaces them in place.
+template <int NROWS, int IT>
+struct TableRegs { uint32_t w[NROWS][IT]; };
+
 template <int TT, int SLOTS>
 __global__ void __launch_bounds__(16 * SLOTS, 1) q4_fused_expert_kernel(FusedArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int NT = 16 * SLOTS, NW = SLOTS / 2;
     const int H = a.H, M = a.M;
     const FusedGeom G = fused_geom(H, M, TT, SLOTS);
-    uint8_t* sGU = smem;                                   // gate rows [0, SLOTS), up rows [SLOTS, 2*SLOTS)
-    uint8_t* sDN = smem + G.off_dn;                        // [dn_cap] down rows
-    uint32_t* tGU = (uint32_t*)(smem + G.off_tgu);
-    uint32_t* tDN = (uint32_t*)(smem + G.off_tdn);
+    uint8_t* sGU = smem;                                   // gate rows [0, SLOTS), up rows [SLOTS, 2*SLOTS), padded
+    uint8_t* sDN = smem + G.off_dn;                        // [dn_cap] down rows, dense
+    uint8_t* sSG = smem + G.off_sgu;                       // [4][gu_sc_cap] staged scales / biases of gate, up; then
+    uint32_t* tGU = (uint32_t*)sSG;                        //   in place: [2*SLOTS][gu_gpr] (scale << 16) | bias
+    uint8_t* sSD = smem + G.off_sdn;                       // [2][dn_sc_cap] staged scales / biases of down; then
+    uint32_t* tDN = (uint32_t*)sSD;                        //   in place: [dn_cap][dn_gpr]
     float* sX = (float*)(smem + G.off_x);                  // [TT][H] the call's activation rows
     float* sC = (float*)(smem + G.off_chain);              // [2 jobs][TT][M] GeGLU rows of the down phase
     FusedJob* sJ = (FusedJob*)(smem + G.off_jobs);
-    uint64_t* bar_gu = (uint64_t*)(smem + G.off_bars);     // [NW]
-    uint64_t* bar_dn = bar_gu + NW;                        // [NW]
-    uint64_t* bar_x = bar_dn + NW;
+    uint64_t* bar_gu = (uint64_t*)(smem + G.off_bars);     // [NW] packed gate/up rows of a warp
+    uint64_t* bar_x = bar_gu + NW;                         // activations
+    uint64_t* bar_sc = bar_x + 1;                          // scales and biases of the block (both phases)
+    uint64_t* bar_dn = bar_x + 2;                          // packed down rows of the block
     __shared__ int s_njobs;
+    __shared__ ScaleRange s_rg[2], s_rd[2];                // the (up to two) job segments of the block's shares
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int v = tid & 15, pr = tid >> 4;
     const int cta = blockIdx.x, ncta = gridDim.x;
 
     if (tid == 0) {
-        for (int i = 0; i < 2 * NW + 1; i++) mbar_init(bar_gu + i, 1);
+        for (int i = 0; i < NW + 3; i++) mbar_init(bar_gu + i, bar_gu + i == bar_sc ? 2 : 1);   // bar_sc: gate/up arrays + down arrays
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     pdl_wait();                    // the jobs, the counters and the activations come from the previous kernel
@@ -197,15 +208,11 @@ __global__ void __launch_bounds__(16 * SLOTS, 1) q4_fused_expert_kernel(FusedArg
     __syncthreads();               // barriers initialised, jobs and count in shared memory
     const int n_jobs = s_njobs;
     if (n_jobs == 0) return;
-    if (tid == 0) {
-        mbar_expect_tx(bar_x, (uint32_t)(a.n_x * H * 4));
-        for (int t = 0; t < a.n_x; t++) bulk_g2s(sX + (size_t)t * H, a.x + (size_t)t * a.x_stride, (uint32_t)(H * 4), bar_x);
-    }
     const int jpr = a.jobs_per_round;
     const int rounds = (n_jobs + jpr - 1) / jpr;
     const NibbleMagic mg = load_nibble_magic();
     const f32x2 nz = pack2u(c_neg_zero, c_neg_zero);
-    uint32_t ph_gu = 0, ph_dn = 0;     // phases of this warp's two barriers
+    uint32_t ph_gu = 0;            // phase of this warp's gate/up barrier
     bool timeout = false;
 
     // ---- geometry of a round -------------------------------------------------------------
@@ -221,10 +228,9 @@ __global__ void __launch_bounds__(16 * SLOTS, 1) q4_fused_expert_kernel(FusedArg
         R.dn_lo = min(cta * Q, R.J * H); R.dn_hi = min(R.dn_lo + Q, R.J * H);
         return R;
     };
-    // slots 2*warp and 2*warp + 1 belong to this warp; lanes 0..3 issue the four gate/up rows
-    // (slot, matrix), the table is built by the whole warp
-    bool lit_gu = false, lit_dn = false;
-    int gu_rows_w = 0, dn_rows_w = 0;                 // rows of this warp in flight / landed
+    // Packed gate/up rows: slots 2*warp and 2*warp + 1 belong to this warp; lane q < 4 issues the copy
+    // of (slot q & 1, matrix q >> 1) into a padded row.
+    int gu_rows_w = 0;                                // rows of this warp in flight / landed
     auto issue_gu = [&](const Round& R) {
         const int s0 = 2 * warp;
         const int nsl = max(0, min(2, R.gu_hi - R.gu_lo - s0));      // valid slots of this warp
@@ -233,62 +239,146 @@ __global__ void __launch_bounds__(16 * SLOTS, 1) q4_fused_expert_kernel(FusedArg
         if (lane == 0) mbar_expect_tx(bar_gu + warp, (uint32_t)(2 * nsl * G.gu_rb));
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier reads of these rows precede the copies
         __syncwarp();
-        const uint8_t* srcs[4]; const uint8_t* srcb[4]; uint32_t* dst[4];
-#pragma unroll
-        for (int q = 0; q < 4; q++) {
-            const int sl = q & 1, mat = q >> 1;
-            srcs[q] = nullptr; srcb[q] = nullptr; dst[q] = nullptr;
-            if (sl >= nsl) continue;
+        const int sl = lane & 1, mat = (lane >> 1) & 1;
+        if (lane < 4 && sl < nsl) {
             const int p = R.gu_lo + s0 + sl;
             const FusedJob& jb = sJ[R.j0 + p / M];
-            const int row = p % M;
             const uint8_t* vals = mat ? jb.up_v : jb.gate_v;
-            const uint8_t* sc = mat ? jb.up_s : jb.gate_s;
-            const uint8_t* bi = mat ? jb.up_b : jb.gate_b;
-            const int srow = mat * SLOTS + s0 + sl;
-            if (lane == q) bulk_g2s(sGU + (size_t)srow * G.gu_stride, vals + (size_t)row * G.gu_rb, (uint32_t)G.gu_rb, bar_gu + warp);
-            srcs[q] = sc + (size_t)row * G.gu_gpr * 2;
-            srcb[q] = bi ? bi + (size_t)row * G.gu_gpr * 2 : nullptr;
-            dst[q] = tGU + (size_t)srow * G.gu_gpr;
+            bulk_g2s(sGU + (size_t)(mat * SLOTS + s0 + sl) * G.gu_stride, vals + (size_t)(p % M) * G.gu_rb,
+                     (uint32_t)G.gu_rb, bar_gu + warp);
         }
-        lit_gu = fused_build_table<4>(srcs, srcb, dst, G.gu_gpr, lane);
-        __syncwarp();
     };
-    // down: slot s owns rows 2s, 2s + 1 of pass 0 and 2*SLOTS + 2s, + 1 of pass 1 (local indices)
-    auto issue_dn = [&](const Round& R) {
-        const int n = R.dn_hi - R.dn_lo;
-        int cnt = 0;
+    // Ranges of the block's share [lo, hi) of an index space of `rows`-row jobs: up to two job segments.
+    // Scales and biases are one copy per array and segment (widened to 16-byte boundaries); the job's
+    // pointers are read as an array: tensor k (0 gate, 1 up, 2 down) has its values at index 3k, its
+    // scales at 3k + 1 and its biases at 3k + 2.  vals_stage != null also copies the segments' packed
+    // rows (dense, `row_bytes_v` each) under vals_bar.  Executed by one thread.
+    auto issue_ranges = [&](int j0, int lo, int hi, int rows, int gpr, ScaleRange* rg, uint8_t* stage, int cap,
+                            int first_tensor, int ntens, uint64_t* bar, uint8_t* vals_stage, int row_bytes_v,
+                            uint64_t* vals_bar) {
+        const int row_bytes = gpr * 2;
+        uint32_t total = 0, total_v = 0;
+        int stage_off = 0, nbytes[2];
+        for (int seg = 0; seg < 2; seg++) {
+            ScaleRange sr;
+            sr.r0 = 0; sr.r1 = 0; sr.byte0 = 0; sr.stage_off = stage_off;
+            nbytes[seg] = 0;
+            const int ja = lo / rows + seg;
+            const int slo = max(lo, ja * rows), shi = min(hi, (ja + 1) * rows);
+            if (hi > lo && shi > slo) {
+                sr.r0 = slo - ja * rows; sr.r1 = shi - ja * rows;
+                sr.byte0 = (sr.r0 * row_bytes) & ~15;
+                nbytes[seg] = ((sr.r1 * row_bytes + 15) & ~15) - sr.byte0;    // the array's size is a multiple of 16
+                stage_off += nbytes[seg];
+                total += (uint32_t)(2 * ntens * nbytes[seg]);
+                total_v += (uint32_t)((sr.r1 - sr.r0) * row_bytes_v);
+            }
+            rg[seg] = sr;
+        }
+        mbar_expect_tx(bar, total);
+        if (vals_stage) mbar_expect_tx(vals_bar, total_v);
+        int row_off = 0;
+        for (int seg = 0; seg < 2; seg++) {
+            if (nbytes[seg] == 0) continue;
+            const uint8_t* const* ptrs = (const uint8_t* const*)&sJ[j0 + lo / rows + seg];
+            for (int t = 0; t < 2 * ntens; t++)
+                bulk_g2s(stage + (size_t)t * cap + rg[seg].stage_off,
+                         ptrs[3 * (first_tensor + (t >> 1)) + 1 + (t & 1)] + rg[seg].byte0, (uint32_t)nbytes[seg], bar);
+            if (vals_stage) {
+                const int n = rg[seg].r1 - rg[seg].r0;
+                bulk_g2s(vals_stage + (size_t)row_off * row_bytes_v, ptrs[3 * first_tensor] + (size_t)rg[seg].r0 * row_bytes_v,
+                         (uint32_t)(n * row_bytes_v), vals_bar);
+                row_off += n;
+            }
+        }
+    };
+    // bar_sc counts two arrivals per round: the gate/up arrays and the down arrays.  The block's down
+    // rows are contiguous in memory and need no padding (the dense rows a warp reads together already
+    // fall in different banks): one copy per job segment.
+    auto issue_block = [&](const Round& R) {
+        issue_ranges(R.j0, R.gu_lo, R.gu_hi, M, G.gu_gpr, s_rg, sSG, G.gu_sc_cap, 0, 2, bar_sc, nullptr, 0, nullptr);
+        issue_ranges(R.j0, R.dn_lo, R.dn_hi, H, G.dn_gpr, s_rd, sSD, G.dn_sc_cap, 2, 1, bar_sc, sDN, G.dn_rb, bar_dn);
+    };
+    // staged bf16 value: group g of row r (job-local, in segment seg) of staged array t
+    auto staged = [&](const ScaleRange* rg, const uint8_t* stage, int cap, int t, int seg, int r, int gpr, int g) {
+        return (uint32_t) * (const uint16_t*)(stage + (size_t)t * cap + rg[seg].stage_off + ((r * gpr + g) * 2 - rg[seg].byte0));
+    };
+    // The interleaved tables replace the staged arrays in place: every warp reads the words of its own
+    // rows into registers, the block synchronises, every warp writes its table rows.
+    // gate/up: row q of the warp = (slot 2*warp + (q & 1), matrix q >> 1); down: local row
+    // (q >> 2) * 2 * SLOTS + 4 * warp + (q & 3).
+    bool lit_gu = false, lit_dn = false;
+    auto tables = [&](const Round& R) {
+        TableRegs<4, 2> rg4;
+        TableRegs<8, 1> rd8;
+        int lit_g = 0, lit_d = 0;
+        const int gu_n = R.gu_hi - R.gu_lo, dn_n = R.dn_hi - R.dn_lo;
+        const int gu_j0 = R.gu_lo / M, dn_j0 = R.dn_lo / H;
 #pragma unroll
-        for (int ps = 0; ps < 2; ps++) cnt += max(0, min(4, n - (ps * 2 * SLOTS + 4 * warp)));
-        dn_rows_w = cnt;
-        if (cnt == 0) return;
-        if (lane == 0) mbar_expect_tx(bar_dn + warp, (uint32_t)(cnt * G.dn_rb));
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        const uint8_t* srcs[8]; const uint8_t* srcb[8]; uint32_t* dst[8];
+        for (int q = 0; q < 4; q++) {
+            const int sl = 2 * warp + (q & 1);
+            const int p = R.gu_lo + sl;
+            const int jl = p / M, row = p - jl * M;
+#pragma unroll
+            for (int it = 0; it < 2; it++) {
+                const int g = lane + 32 * it;
+                uint32_t wv = 0;
+                if (sl < gu_n && g < G.gu_gpr) {
+                    const uint32_t hs = staged(s_rg, sSG, G.gu_sc_cap, 2 * (q >> 1), jl - gu_j0, row, G.gu_gpr, g);
+                    const uint32_t hb = staged(s_rg, sSG, G.gu_sc_cap, 2 * (q >> 1) + 1, jl - gu_j0, row, G.gu_gpr, g);
+                    wv = (hs << 16) | hb;
+                    lit_g |= scale_needs_literal(hs) ? 1 : 0;
+                }
+                rg4.w[q][it] = wv;
+            }
+        }
 #pragma unroll
         for (int q = 0; q < 8; q++) {
-            const int li = (q >> 2) * 2 * SLOTS + 4 * warp + (q & 3);     // local row index
-            srcs[q] = nullptr; srcb[q] = nullptr; dst[q] = nullptr;
-            if (li >= n) continue;
+            const int li = (q >> 2) * 2 * SLOTS + 4 * warp + (q & 3);
             const int qg = R.dn_lo + li;
-            const FusedJob& jb = sJ[R.j0 + qg / H];
-            const int row = qg % H;
-            if (lane == q) bulk_g2s(sDN + (size_t)li * G.dn_stride, jb.down_v + (size_t)row * G.dn_rb, (uint32_t)G.dn_rb, bar_dn + warp);
-            srcs[q] = jb.down_s + (size_t)row * G.dn_gpr * 2;
-            srcb[q] = jb.down_b ? jb.down_b + (size_t)row * G.dn_gpr * 2 : nullptr;
-            dst[q] = tDN + (size_t)li * G.dn_gpr;
+            const int jl = qg / H, row = qg - jl * H;
+            uint32_t wv = 0;
+            if (li < dn_n && lane < G.dn_gpr) {
+                const uint32_t hs = staged(s_rd, sSD, G.dn_sc_cap, 0, jl - dn_j0, row, G.dn_gpr, lane);
+                const uint32_t hb = staged(s_rd, sSD, G.dn_sc_cap, 1, jl - dn_j0, row, G.dn_gpr, lane);
+                wv = (hs << 16) | hb;
+                lit_d |= scale_needs_literal(hs) ? 1 : 0;
+            }
+            rd8.w[q][0] = wv;
         }
-        lit_dn = fused_build_table<8>(srcs, srcb, dst, G.dn_gpr, lane);
+        __syncthreads();           // every staged value has been read
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const int srow = (q >> 1) * SLOTS + 2 * warp + (q & 1);
+#pragma unroll
+            for (int it = 0; it < 2; it++) {
+                const int g = lane + 32 * it;
+                if (g < G.gu_gpr) tGU[(size_t)srow * G.gu_gpr + g] = rg4.w[q][it];
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+            const int li = (q >> 2) * 2 * SLOTS + 4 * warp + (q & 3);
+            if (lane < G.dn_gpr) tDN[(size_t)li * G.dn_gpr + lane] = rd8.w[q][0];
+        }
+        lit_gu = __any_sync(0xffffffffu, lit_g) != 0;
+        lit_dn = __any_sync(0xffffffffu, lit_d) != 0;
         __syncwarp();
     };
 
     Round R = round_of(0);
     issue_gu(R);
-    issue_dn(R);
+    if (tid == 0) {
+        mbar_expect_tx(bar_x, (uint32_t)(a.n_x * H * 4));
+        for (int t = 0; t < a.n_x; t++) bulk_g2s(sX + (size_t)t * H, a.x + (size_t)t * a.x_stride, (uint32_t)(H * 4), bar_x);
+        issue_block(R);
+    }
+    __syncthreads();               // s_rg / s_rd are published
     if (!fused_mbar_wait(bar_x, 0)) timeout = true;
 
     for (int r = 0; r < rounds; r++) {
+        if (!fused_mbar_wait(bar_sc, r & 1)) timeout = true;
+        tables(R);
         // ================= gate | up + GeGLU =================
         if (gu_rows_w > 0) {
             if (!fused_mbar_wait(bar_gu + warp, ph_gu & 1)) timeout = true;
@@ -296,8 +386,8 @@ __global__ void __launch_bounds__(16 * SLOTS, 1) q4_fused_expert_kernel(FusedArg
         }
         const int p = R.gu_lo + pr;
         if (p < R.gu_hi) {
-            const FusedJob& jb = sJ[R.j0 + p / M];
-            const int row = p % M;
+            const int jl = p / M, row = p - jl * M;
+            const FusedJob& jb = sJ[R.j0 + jl];
             const uint8_t* wA = sGU + (size_t)pr * G.gu_stride + v;
             const uint8_t* wB = sGU + (size_t)(SLOTS + pr) * G.gu_stride + v;
             const uint32_t* tA = tGU + (size_t)pr * G.gu_gpr;
@@ -339,12 +429,14 @@ __global__ void __launch_bounds__(16 * SLOTS, 1) q4_fused_expert_kernel(FusedArg
             issue_gu(Rn);
         }
         __syncthreads();               // every GeGLU value of this block has been written
-        if (tid == 0 && R.gu_hi > R.gu_lo) {
-            __threadfence();
-            const int ja = R.gu_lo / M, jb2 = (R.gu_hi - 1) / M;
-            for (int j = ja; j <= jb2; j++) {
-                const int lo = max(R.gu_lo, j * M), hi = min(R.gu_hi, (j + 1) * M);
-                atomicAdd(a.done + R.j0 + j, hi - lo);
+        if (tid == 0) {
+            if (R.gu_hi > R.gu_lo) {
+                __threadfence();
+                const int ja = R.gu_lo / M, jb2 = (R.gu_hi - 1) / M;
+                for (int j = ja; j <= jb2; j++) {
+                    const int lo = max(R.gu_lo, j * M), hi = min(R.gu_hi, (j + 1) * M);
+                    atomicAdd(a.done + R.j0 + j, hi - lo);
+                }
             }
         }
         // ================= down =================
@@ -365,17 +457,14 @@ __global__ void __launch_bounds__(16 * SLOTS, 1) q4_fused_expert_kernel(FusedArg
             float* dstc = sC + (size_t)(j - dja) * TT * M;
             for (int i = tid * 4; i < n; i += NT * 4) *(float4*)(dstc + i) = __ldcg((const float4*)(src + i));
         }
+        if (!fused_mbar_wait(bar_dn, r & 1)) timeout = true;
         __syncthreads();
-        if (dn_rows_w > 0) {
-            if (!fused_mbar_wait(bar_dn + warp, ph_dn & 1)) timeout = true;
-            ph_dn++;
-        }
 #pragma unroll 1
         for (int ps = 0; ps < 2; ps++) {
             const int li = ps * 2 * SLOTS + 2 * pr;
             if (li >= dn_n) continue;
             const int qg = R.dn_lo + li;
-            const int jl = qg / H, row = qg % H;
+            const int jl = qg / H, row = qg - jl * H;
             const FusedJob& jb = sJ[R.j0 + jl];
             const uint8_t* wA = sDN + (size_t)li * G.dn_stride + v;
             const uint8_t* wB = wA + G.dn_stride;
@@ -412,8 +501,12 @@ __global__ void __launch_bounds__(16 * SLOTS, 1) q4_fused_expert_kernel(FusedArg
                 if (v == 0) *(float2*)orow = make_float2(yA[0], yB[0]);
             }
         }
-        __syncwarp();
-        if (r + 1 < rounds) issue_dn(Rn);
+        __syncthreads();               // the block is done with this round's down rows and tables
+        if (r + 1 < rounds && tid == 0) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            issue_block(Rn);
+        }
+        __syncthreads();               // next round's s_rg / s_rd are published
         R = Rn;
     }
     if (timeout && a.status) atomicOr(a.status, SB_ERR_TIMEOUT);
@@ -421,7 +514,7 @@ __global__ void __launch_bounds__(16 * SLOTS, 1) q4_fused_expert_kernel(FusedArg
 
 // ---- host side ---------------------------------------------------------------------------
 namespace {
-struct DeviceInfo { int sms = 0; bool configured[3] = {false, false, false}; };
+struct DeviceInfo { int sms = 0; size_t configured[3] = {0, 0, 0}; };
 DeviceInfo g_dev[64];
 
 DeviceInfo* device_info() {
@@ -431,7 +524,7 @@ DeviceInfo* device_info() {
     if (d->sms == 0 && cudaDeviceGetAttribute(&d->sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return nullptr;
     return d;
 }
-constexpr size_t FUSED_SMEM_LIMIT = 227 * 1024;
+constexpr size_t FUSED_SMEM_LIMIT = 227 * 1024 - 1024;   // dynamic part: the opt-in maximum less the kernel's static variables
 int fused_tt(int n_x) { return n_x <= 1 ? 1 : (n_x == 2 ? 2 : 4); }
 int fused_slots(int tt) { return tt == 1 ? 40 : 32; }
 }  // namespace
@@ -443,9 +536,10 @@ bool q4_fused_plan(int H, int M, int n_x, int n_jobs_max, FusedLaunch* out) {
         return false;
     const int tt = fused_tt(n_x), slots = fused_slots(tt);
     const FusedGeom g = fused_geom(H, M, tt, slots);
-    if (g.total + 64 > FUSED_SMEM_LIMIT) return false;
+    // the table registers of a warp cover 64 groups per gate/up row and 32 per down row
+    if (g.total > FUSED_SMEM_LIMIT || g.gu_gpr > 64 || g.dn_gpr > 32) return false;
     const int grid = d->sms;
-    // most jobs per round whose shares fit the block: ceil(J*M/grid) <= slots, even ceil(J*H/grid) <= dn_cap
+    // most jobs per round whose shares fit the block: ceil(J*M/grid) <= slots, ceil(J*H/grid) <= dn_cap
     int jmax = 0;
     for (int J = 1; J <= grid && J <= FUSED_MAX_JOBS; J++) {
         const int P = (J * M + grid - 1) / grid;
@@ -461,11 +555,11 @@ bool q4_fused_plan(int H, int M, int n_x, int n_jobs_max, FusedLaunch* out) {
 
 template <int TT, int SLOTS>
 static cudaError_t launch_fused_t(FusedArgs& a, const FusedLaunch& L, DeviceInfo* d, int cfg_slot, cudaStream_t stream) {
-    if (!d->configured[cfg_slot]) {
+    if (d->configured[cfg_slot] < L.smem) {
         cudaError_t e = cudaFuncSetAttribute(q4_fused_expert_kernel<TT, SLOTS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)FUSED_SMEM_LIMIT);
         if (e != cudaSuccess) return e;
-        d->configured[cfg_slot] = true;
+        d->configured[cfg_slot] = FUSED_SMEM_LIMIT;
     }
     return launch_pdl(q4_fused_expert_kernel<TT, SLOTS>, dim3(L.grid), dim3(16 * SLOTS), L.smem, stream, a);
 }
