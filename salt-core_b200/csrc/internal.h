@@ -51,6 +51,32 @@ bool q4_fused_plan(int H, int M, int n_x, int n_jobs_max, FusedLaunch* out);
 // Launched as a programmatic dependent launch; jobs, counters and x come from the previous kernel.
 cudaError_t launch_q4_fused(const FusedArgs& args, cudaStream_t stream);
 
+// One decode layer (one token) in one launch: [reduce + RMSNorm of the previous layer] -> router
+// input -> logits -> top-k -> experts.
+struct LayerDecodeArgs {
+    FusedArgs f;                   // H, M, chain, out (this layer's grouped rows), done (this layer's counters), status
+    const float* x_in;             // [H] the stack input, used when prev_grouped is null
+    const float* prev_grouped;     // [topk][H] grouped outputs of the previous layer (rank order) or null
+    const float* prev_weights;     // [topk]
+    const float* norm_w;           // [H] RMSNorm weight applied to the reduced row, or null
+    float eps_norm;
+    float* y_out;                  // optional [H]: the layer's input row (block 0 writes it)
+    const float* router_scale;     // [H]
+    float eps_router;
+    const float* router_w;         // [E][H]
+    const float* per_expert_scale; // [E]
+    float* logits;                 // [E]
+    int* logits_count;             // arrival counter of this layer, zero at launch
+    int E, topk, expert_begin, expert_end;
+    int32_t* selected;             // [topk] outputs of block 0 ...
+    float* weights_out;            // [topk] (a different buffer than prev_weights)
+    int32_t *c2g, *g2c, *group_offsets;
+    const uint8_t* pool;           // slot of expert e at pool + (e - expert_begin) * expert_stride
+    size_t expert_stride, tensor_bytes, value_bytes, group_bytes;
+};
+bool q4_layer_decode_plan(int H, int M, int E, int topk, int n_jobs_max, FusedLaunch* out);
+cudaError_t launch_q4_layer_decode(const LayerDecodeArgs& args, int n_jobs_max, cudaStream_t stream);
+
 // Affine 8-bit jobs (same descriptor; vals = one byte per element): one block per (row, token, job).
 cudaError_t launch_q8_jobs(const Q4Job* jobs, int njobs, int max_rows, int max_tok, int C, cudaStream_t stream);
 
@@ -124,6 +150,7 @@ struct GlueArgs {
     float eps_router;
     float* rin;                  // [rows][n]
     int n;
+    int tables_late;             // weights / c2g are written by the kernel launched just before this one
     int* status;
 };
 cudaError_t launch_glue(const GlueArgs& a, int rows, cudaStream_t stream);

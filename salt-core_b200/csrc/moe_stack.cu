@@ -53,6 +53,10 @@ struct Stack {
     Q4Job *gateup_jobs = nullptr, *down_jobs = nullptr;
     FusedJob* fused_jobs = nullptr;            // descriptors and arrival counters of the fused decode kernel
     int32_t* fused_done = nullptr;
+    // one-launch decode layers (one token): buffers of the other parity and per-layer arrival counters
+    float *grouped_alt = nullptr, *weights_alt = nullptr;
+    int32_t* layer_counters = nullptr;         // [layers_cap][FUSED_MAX_JOBS + 1]
+    int layers_cap = 0;
     bool fused_decode = true;                  // batches of up to FUSED_MAX_TOKENS tokens take the one-launch expert kernel
     void *xh = nullptr, *xl = nullptr, *chain_h = nullptr, *chain_l = nullptr;   // fp16 operands (hi, lo) of the tensor-core path
     bool tc_ready = false;                     // tensor maps built (needs hidden, inter multiples of 64)
@@ -109,6 +113,7 @@ static void free_stack(Stack* s) {
     cudaFree(s->selected); cudaFree(s->group_offsets); cudaFree(s->g2c); cudaFree(s->c2g);
     cudaFree(s->counters); cudaFree(s->status); cudaFree(s->gateup_jobs); cudaFree(s->down_jobs);
     cudaFree(s->fused_jobs); cudaFree(s->fused_done);
+    cudaFree(s->grouped_alt); cudaFree(s->weights_alt); cudaFree(s->layer_counters);
     cudaFree(s->xh); cudaFree(s->xl); cudaFree(s->chain_h); cudaFree(s->chain_l);
     if (s->h_in) cudaFreeHost(s->h_in);
     if (s->h_out) cudaFreeHost(s->h_out);
@@ -163,6 +168,7 @@ int salt_b200_stack_create(int max_tokens, int hidden, int inter, int n_experts,
               dev_alloc(&s->c2g, J) && dev_alloc(&s->counters, 4) && dev_alloc(&s->status, 1) &&
               dev_alloc(&s->gateup_jobs, (size_t)n_experts) && dev_alloc(&s->down_jobs, (size_t)n_experts) &&
               dev_alloc(&s->fused_jobs, (size_t)FUSED_MAX_JOBS) && dev_alloc(&s->fused_done, (size_t)FUSED_MAX_JOBS) &&
+              dev_alloc(&s->grouped_alt, (size_t)topk * hidden) && dev_alloc(&s->weights_alt, (size_t)topk) &&
               dev_alloc((uint16_t**)&s->xh, J * hidden) && dev_alloc((uint16_t**)&s->chain_h, J * inter) &&
               dev_alloc((uint16_t**)&s->xl, J * hidden) && dev_alloc((uint16_t**)&s->chain_l, J * inter) &&
               cuda_ok(cudaMemset(s->status, 0, sizeof(int32_t)), "status") &&
@@ -588,11 +594,73 @@ __global__ void profile_head_start_kernel(long long cycles) {
     for (int i = 0; i < (1 << 24) && clock64() - t0 < cycles; i++) { }
 }
 
+// One token, one device: every layer is ONE launch (reduce + norm of the previous layer, router,
+// top-k, experts), then one launch for the last reduce.
+static bool decode_layers_apply(Stack* s, int B) {
+    const int local = s->expert_end - s->expert_begin;
+    return s->fused_decode && B == 1 && s->ep_world == 0 && s->topk <= FUSED_MAX_JOBS &&
+           q4_layer_decode_plan(s->hidden, s->inter, s->n_experts, s->topk, s->topk < local ? s->topk : local, nullptr);
+}
+
+static int forward_decode_layers(Stack* s, int first, int count, const float* d_x, float* d_y, cudaStream_t st) {
+    const int H = s->hidden, M = s->inter, K = s->topk;
+    const int stride = FUSED_MAX_JOBS + 1;
+    if (count > s->layers_cap) {       // set-up, not part of a captured pass: forward passes are not captured before one has run
+        cudaFree(s->layer_counters);
+        s->layer_counters = nullptr;
+        if (!dev_alloc(&s->layer_counters, (size_t)count * stride)) return -1;
+        s->layers_cap = count;
+    }
+    if (!cuda_ok(cudaMemsetAsync(s->layer_counters, 0, (size_t)count * stride * sizeof(int32_t), st), "layer counters"))
+        return -1;
+    const size_t elems = (size_t)H * M;
+    const int local = s->expert_end - s->expert_begin;
+    float* gbuf[2] = {s->grouped_out, s->grouped_alt};
+    float* wbuf[2] = {s->weights, s->weights_alt};
+    for (int i = 0; i < count; i++) {
+        const Layer& l = s->layers[(size_t)first + i];
+        LayerDecodeArgs a;
+        memset(&a, 0, sizeof a);
+        a.f.H = H; a.f.M = M; a.f.chain = s->chain; a.f.out = gbuf[i & 1];
+        a.f.done = s->layer_counters + (size_t)i * stride + 1; a.f.status = s->status;
+        a.f.n_jobs_max = K < local ? K : local;
+        a.logits_count = s->layer_counters + (size_t)i * stride;
+        if (i == 0) {
+            a.x_in = d_x;
+        } else {
+            const Layer& pl = s->layers[(size_t)first + i - 1];
+            a.prev_grouped = gbuf[(i - 1) & 1]; a.prev_weights = wbuf[(i - 1) & 1];
+            a.norm_w = pl.norm_weight; a.eps_norm = pl.eps;
+        }
+        a.router_scale = l.router_scale; a.eps_router = l.eps; a.router_w = l.router_w;
+        a.per_expert_scale = l.per_expert_scale; a.logits = s->logits;
+        a.E = s->n_experts; a.topk = K; a.expert_begin = s->expert_begin; a.expert_end = s->expert_end;
+        a.selected = s->selected; a.weights_out = wbuf[i & 1]; a.c2g = s->c2g; a.g2c = s->g2c;
+        a.group_offsets = s->group_offsets;
+        a.pool = l.pool; a.expert_stride = l.expert_stride;
+        a.value_bytes = elems / 2; a.group_bytes = elems / 64 * 2; a.tensor_bytes = a.value_bytes + 2 * a.group_bytes;
+        Timed t(s, KC_GATE_UP, st);
+        if (!cuda_ok(launch_q4_layer_decode(a, a.f.n_jobs_max, st), "decode layer")) return -1;
+    }
+    const int last = count - 1;
+    GlueArgs g;
+    memset(&g, 0, sizeof g);
+    g.weights = wbuf[last & 1]; g.c2g = s->c2g; g.grouped = gbuf[last & 1]; g.topk = K; g.jobs = K;
+    g.y_out = d_y; g.n = H; g.status = s->status; g.tables_late = 1;
+    {
+        Timed t(s, KC_REDUCE, st);
+        if (!cuda_ok(launch_glue(g, 1, st), "last reduce")) return -1;
+    }
+    count_launches(count + 1);
+    return 0;
+}
+
 int salt_b200_stack_forward_device(void* stack, int first, int count, const float* d_x, int B, float* d_y,
                                    void* stream) {
     Stack* s = (Stack*)stack;
     if (!s || first < 0 || count < 1 || first + count > (int)s->layers.size() || !d_x || !d_y) return -1;
     if (s->profile) profile_head_start_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(80000LL * count + 400000LL);
+    if (decode_layers_apply(s, B)) return forward_decode_layers(s, first, count, d_x, d_y, (cudaStream_t)stream);
     const float* in = d_x;
     for (int i = 0; i < count; i++) {
         const bool last = i == count - 1;

@@ -32,6 +32,7 @@
 #include "mbar.cuh"
 #include "pdl.cuh"
 #include "q4_core.cuh"
+#include "router_core.cuh"
 
 namespace sb {
 
@@ -164,50 +165,53 @@ struct ScaleRange {
 template <int NROWS, int IT>
 struct TableRegs { uint32_t w[NROWS][IT]; };
 
+// Shared-memory views of a block (see fused_geom).
 template <int TT, int SLOTS>
-__global__ void __launch_bounds__(16 * SLOTS, 1) q4_fused_expert_kernel(FusedArgs a) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    constexpr int NT = 16 * SLOTS, NW = SLOTS / 2;
-    const int H = a.H, M = a.M;
-    const FusedGeom G = fused_geom(H, M, TT, SLOTS);
-    uint8_t* sGU = smem;                                   // gate rows [0, SLOTS), up rows [SLOTS, 2*SLOTS), padded
-    uint8_t* sDN = smem + G.off_dn;                        // [dn_cap] down rows, dense
-    uint8_t* sSG = smem + G.off_sgu;                       // [4][gu_sc_cap] staged scales / biases of gate, up; then
-    uint32_t* tGU = (uint32_t*)sSG;                        //   in place: [2*SLOTS][gu_gpr] (scale << 16) | bias
-    uint8_t* sSD = smem + G.off_sdn;                       // [2][dn_sc_cap] staged scales / biases of down; then
-    uint32_t* tDN = (uint32_t*)sSD;                        //   in place: [dn_cap][dn_gpr]
-    float* sX = (float*)(smem + G.off_x);                  // [TT][H] the call's activation rows
-    float* sC = (float*)(smem + G.off_chain);              // [2 jobs][TT][M] GeGLU rows of the down phase
-    FusedJob* sJ = (FusedJob*)(smem + G.off_jobs);
-    uint64_t* bar_gu = (uint64_t*)(smem + G.off_bars);     // [NW] packed gate/up rows of a warp
-    uint64_t* bar_x = bar_gu + NW;                         // activations
-    uint64_t* bar_sc = bar_x + 1;                          // scales and biases of the block (both phases)
-    uint64_t* bar_dn = bar_x + 2;                          // packed down rows of the block
-    __shared__ int s_njobs;
-    __shared__ ScaleRange s_rg[2], s_rd[2];                // the (up to two) job segments of the block's shares
-
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int v = tid & 15, pr = tid >> 4;
-    const int cta = blockIdx.x, ncta = gridDim.x;
-
-    if (tid == 0) {
+struct FusedSmem {
+    static constexpr int NT = 16 * SLOTS, NW = SLOTS / 2;
+    uint8_t *sGU, *sDN, *sSG, *sSD;
+    uint32_t *tGU, *tDN;
+    float *sX, *sC;
+    FusedJob* sJ;
+    uint64_t *bar_gu, *bar_x, *bar_sc, *bar_dn;
+    __device__ __forceinline__ FusedSmem(uint8_t* smem, const FusedGeom& G) {
+        sGU = smem;                                   // gate rows [0, SLOTS), up rows [SLOTS, 2*SLOTS), padded
+        sDN = smem + G.off_dn;                        // [dn_cap] down rows, dense
+        sSG = smem + G.off_sgu;                       // [4][gu_sc_cap] staged scales / biases of gate, up; then
+        tGU = (uint32_t*)sSG;                         //   in place: [2*SLOTS][gu_gpr] (scale << 16) | bias
+        sSD = smem + G.off_sdn;                       // [2][dn_sc_cap] staged scales / biases of down; then
+        tDN = (uint32_t*)sSD;                         //   in place: [dn_cap][dn_gpr]
+        sX = (float*)(smem + G.off_x);                // [TT][H] the call's activation rows
+        sC = (float*)(smem + G.off_chain);            // [2 jobs][TT][M] GeGLU rows of the down phase
+        sJ = (FusedJob*)(smem + G.off_jobs);
+        bar_gu = (uint64_t*)(smem + G.off_bars);      // [NW] packed gate/up rows of a warp
+        bar_x = bar_gu + NW;                          // activations
+        bar_sc = bar_x + 1;                           // scales and biases of the block (both phases)
+        bar_dn = bar_x + 2;                           // packed down rows of the block
+    }
+    // by one thread, before the block's first barrier
+    __device__ __forceinline__ void init_barriers() {
         for (int i = 0; i < NW + 3; i++) mbar_init(bar_gu + i, bar_gu + i == bar_sc ? 2 : 1);   // bar_sc: gate/up arrays + down arrays
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    pdl_wait();                    // the jobs, the counters and the activations come from the previous kernel
-    pdl_launch_dependents();
-    {
-        // the live count and the whole job table in one round trip (read through L2: another
-        // layer's table may still sit in this SM's L1)
-        const int n_live = __ldcg(a.n_jobs_dev);
-        static_assert(sizeof(FusedJob) % 16 == 0, "job descriptors are copied in 16-byte pieces");
-        const int pieces = a.n_jobs_max * (int)(sizeof(FusedJob) / 16);
-        for (int i = tid; i < pieces; i += NT) ((uint4*)sJ)[i] = __ldcg((const uint4*)a.jobs + i);
-        if (tid == 0) s_njobs = min(max(n_live, 0), a.n_jobs_max);
-    }
-    __syncthreads();               // barriers initialised, jobs and count in shared memory
-    const int n_jobs = s_njobs;
-    if (n_jobs == 0) return;
+};
+
+// The expert phases of a block for the n_jobs descriptors in S.sJ (barriers initialised, the block
+// synchronised).  x_resident: S.sX already holds the activation rows; otherwise they are copied from
+// a.x.  Returns true when a bounded wait ran out.  Every thread of the block must call.
+template <int TT, int SLOTS>
+__device__ __forceinline__ bool fused_expert_rounds(const FusedArgs& a, const FusedGeom& G, const FusedSmem<TT, SLOTS>& S,
+                                                    int n_jobs, bool x_resident, ScaleRange* s_rg, ScaleRange* s_rd) {
+    constexpr int NT = 16 * SLOTS;
+    const int H = a.H, M = a.M;
+    uint8_t* const sGU = S.sGU; uint8_t* const sDN = S.sDN; uint8_t* const sSG = S.sSG; uint8_t* const sSD = S.sSD;
+    uint32_t* const tGU = S.tGU; uint32_t* const tDN = S.tDN;
+    float* const sX = S.sX; float* const sC = S.sC;
+    FusedJob* const sJ = S.sJ;
+    uint64_t* const bar_gu = S.bar_gu; uint64_t* const bar_x = S.bar_x; uint64_t* const bar_sc = S.bar_sc; uint64_t* const bar_dn = S.bar_dn;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int v = tid & 15, pr = tid >> 4;
+    const int cta = blockIdx.x, ncta = gridDim.x;
     const int jpr = a.jobs_per_round;
     const int rounds = (n_jobs + jpr - 1) / jpr;
     const NibbleMagic mg = load_nibble_magic();
@@ -369,12 +373,14 @@ __global__ void __launch_bounds__(16 * SLOTS, 1) q4_fused_expert_kernel(FusedArg
     Round R = round_of(0);
     issue_gu(R);
     if (tid == 0) {
-        mbar_expect_tx(bar_x, (uint32_t)(a.n_x * H * 4));
-        for (int t = 0; t < a.n_x; t++) bulk_g2s(sX + (size_t)t * H, a.x + (size_t)t * a.x_stride, (uint32_t)(H * 4), bar_x);
+        if (!x_resident) {
+            mbar_expect_tx(bar_x, (uint32_t)(a.n_x * H * 4));
+            for (int t = 0; t < a.n_x; t++) bulk_g2s(sX + (size_t)t * H, a.x + (size_t)t * a.x_stride, (uint32_t)(H * 4), bar_x);
+        }
         issue_block(R);
     }
     __syncthreads();               // s_rg / s_rd are published
-    if (!fused_mbar_wait(bar_x, 0)) timeout = true;
+    if (!x_resident && !fused_mbar_wait(bar_x, 0)) timeout = true;
 
     for (int r = 0; r < rounds; r++) {
         if (!fused_mbar_wait(bar_sc, r & 1)) timeout = true;
@@ -509,12 +515,307 @@ __global__ void __launch_bounds__(16 * SLOTS, 1) q4_fused_expert_kernel(FusedArg
         __syncthreads();               // next round's s_rg / s_rd are published
         R = Rn;
     }
+    return timeout;
+}
+
+template <int TT, int SLOTS>
+__global__ void __launch_bounds__(16 * SLOTS, 1) q4_fused_expert_kernel(FusedArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int NT = 16 * SLOTS;
+    const FusedGeom G = fused_geom(a.H, a.M, TT, SLOTS);
+    FusedSmem<TT, SLOTS> S(smem, G);
+    __shared__ int s_njobs;
+    __shared__ ScaleRange s_rg[2], s_rd[2];                // the (up to two) job segments of the block's shares
+    const int tid = threadIdx.x;
+    if (tid == 0) S.init_barriers();
+    pdl_wait();                    // the jobs, the counters and the activations come from the previous kernel
+    pdl_launch_dependents();
+    {
+        // the live count and the whole job table in one round trip (read through L2: another
+        // layer's table may still sit in this SM's L1)
+        const int n_live = __ldcg(a.n_jobs_dev);
+        static_assert(sizeof(FusedJob) % 16 == 0, "job descriptors are copied in 16-byte pieces");
+        const int pieces = a.n_jobs_max * (int)(sizeof(FusedJob) / 16);
+        for (int i = tid; i < pieces; i += NT) ((uint4*)S.sJ)[i] = __ldcg((const uint4*)a.jobs + i);
+        if (tid == 0) s_njobs = min(max(n_live, 0), a.n_jobs_max);
+    }
+    __syncthreads();               // barriers initialised, jobs and count in shared memory
+    const int n_jobs = s_njobs;
+    if (n_jobs == 0) return;
+    const bool timeout = fused_expert_rounds<TT, SLOTS>(a, G, S, n_jobs, false, s_rg, s_rd);
     if (timeout && a.status) atomicOr(a.status, SB_ERR_TIMEOUT);
+}
+
+// ---- one launch per decode layer (one token) -------------------------------------------------
+// [ordered reduce + RMSNorm of the previous layer] -> router input -> router logits -> softmax
+// top-k -> job list -> the expert phases above, in ONE launch of one block per SM.
+//   * the row-wise glue (reference src/tensorops.c:291-325, gemma4.c:85-130) is computed by EVERY
+//     block for itself: its results (the experts' activation row, the router input) stay in the
+//     block's shared memory and nothing is waited for;
+//   * block e forms the logit of expert e (reference src/kernels.c:98-106: one dependent-add chain
+//     over the hidden size, handed from lane to lane of one warp), stores it and bumps an arrival
+//     counter; every block polls the counter (bounded), reads the logits and repeats the top-k
+//     (gemma4.c:132-186) and the job list for itself;
+//   * block 0 also leaves selections, weights and the (trivial, one token) grouping in global
+//     memory for the next layer's reduce and for the caller.
+// The scratch of these phases overlays the weight rows, which are not requested before the job
+// list exists.  The previous layer's grouped outputs and weights are read from the buffers of the
+// OTHER parity, so a block that is late in its glue never sees rows of this layer.
+constexpr int LAYER_NV = 5;                 // columns per thread of the row-wise glue
+constexpr int LAYER_SLOTS = 40;
+
+struct LayerScratch {                        // offsets in floats from the start of shared memory
+    int sq, rin, wrow, logits, topk, scan, end;
+};
+static __host__ __device__ __forceinline__ LayerScratch layer_scratch(int H, int E, int topk) {
+    LayerScratch L;
+    const int h4 = (H + 3) & ~3;
+    L.sq = 0; L.rin = h4; L.wrow = 2 * h4; L.logits = 3 * h4;
+    L.topk = L.logits + ((E + 3) & ~3);
+    L.scan = L.topk + topk_scratch_floats(E, topk);
+    L.end = L.scan + POSSUM_SCRATCH;
+    return L;
+}
+
+// one copy of the in-order sum for both of its uses (less code for the SM to fetch)
+static __device__ __noinline__ float layer_ordered_sum(const float* sq, int n, bool bad, uint32_t* scan) {
+    return ordered_sum_of_squares<LAYER_NV>(sq, n, bad, scan);
+}
+
+__global__ void __launch_bounds__(16 * LAYER_SLOTS, 1) q4_layer_decode_kernel(LayerDecodeArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int SLOTS = LAYER_SLOTS, NT = 16 * SLOTS, NV = LAYER_NV;
+    const int H = a.f.H, M = a.f.M, E = a.E, K = a.topk;
+    const FusedGeom G = fused_geom(H, M, 1, SLOTS);
+    FusedSmem<1, SLOTS> S(smem, G);
+    const LayerScratch L = layer_scratch(H, E, K);
+    float* const fsm = (float*)smem;
+    float* const sq = fsm + L.sq;                 // squares / products for the in-order chains
+    float* const rin = fsm + L.rin;               // router input
+    float* const wrow = fsm + L.wrow;             // router weights of this block's expert
+    float* const s_logits = fsm + L.logits;
+    float* const tk = fsm + L.topk;
+    uint32_t* const scan = (uint32_t*)(fsm + L.scan);
+    __shared__ float s_inv, s_root, s_w[64], s_wts[64];
+    __shared__ int s_sel[64], s_njobs;
+    __shared__ ScaleRange s_rg[2], s_rd[2];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int cta = blockIdx.x, ncta = gridDim.x;
+    bool bad = false, timeout = false;
+
+    // ---- before the dependency: barriers, this block's router row, the norm weights ----
+    if (tid == 0) {
+        S.init_barriers();
+        if (cta < E) {
+            mbar_expect_tx(S.bar_x, (uint32_t)(H * 4));
+            bulk_g2s(wrow, a.router_w + (size_t)cta * H, (uint32_t)(H * 4), S.bar_x);
+        }
+    }
+    float v[NV], nw[NV], rs[NV];
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+        const int d = tid + j * NT;
+        nw[j] = (a.norm_w != nullptr && d < H) ? __ldg(a.norm_w + d) : 1.0f;
+        rs[j] = d < H ? __ldg(a.router_scale + d) : 1.0f;
+        v[j] = 0.0f;
+    }
+    pdl_wait();                    // the previous layer's outputs
+    pdl_launch_dependents();
+
+    // ---- the layer's input row: ordered weighted reduce of the previous layer, or the stack input ----
+    if (a.prev_grouped != nullptr) {
+        if (tid < K) {
+            const float w = __ldcg(a.prev_weights + tid);
+            if (!finite_f(w)) flag(a.f.status, SB_ERR_NONFINITE);
+            s_w[tid] = w;
+        }
+        __syncthreads();
+        for (int r0 = 0; r0 < K; r0 += 8) {
+            float o[NV][8];
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+#pragma unroll
+                for (int j = 0; j < NV; j++) {
+                    const int d = tid + j * NT;
+                    o[j][i] = (r0 + i < K && d < H) ? __ldcg(a.prev_grouped + (size_t)(r0 + i) * H + d) : 0.0f;
+                }
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                if (r0 + i < K && finite_f(s_w[r0 + i])) {
+                    const float w = s_w[r0 + i];
+#pragma unroll
+                    for (int j = 0; j < NV; j++) v[j] = __fadd_rn(v[j], __fmul_rn(w, o[j][i]));
+                }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < NV; j++) {
+            const int d = tid + j * NT;
+            if (d < H) v[j] = __ldcg(a.x_in + d);
+        }
+    }
+    if (a.norm_w != nullptr) {      // RMSNorm of the previous layer (gemma4.c:85-101)
+#pragma unroll
+        for (int j = 0; j < NV; j++) {
+            const int d = tid + j * NT;
+            if (d < H) {
+                sq[d] = __fmul_rn(v[j], v[j]);
+                bad |= !finite_f(v[j]) || !finite_f(nw[j]);
+            }
+        }
+        const float ss = layer_ordered_sum(sq, H, bad, scan);
+        if (tid == 0) {
+            s_inv = pow_neg_half(__fadd_rn(__fdiv_rn(ss, (float)H), a.eps_norm));
+            if (!finite_f(s_inv)) flag(a.f.status, SB_ERR_NONFINITE);
+        }
+        __syncthreads();
+        const float inv = s_inv;
+#pragma unroll
+        for (int j = 0; j < NV; j++) {
+            v[j] = __fmul_rn(__fmul_rn(v[j], inv), nw[j]);
+            if (tid + j * NT < H) bad |= !finite_f(v[j]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+        const int d = tid + j * NT;
+        if (d < H) {
+            S.sX[d] = v[j];           // the experts' activation row
+            if (cta == 0 && a.y_out != nullptr) a.y_out[d] = v[j];
+        }
+    }
+    // ---- router input (gemma4.c:103-130) ----
+    __syncthreads();                // the previous in-order sum has been read by everyone
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+        const int d = tid + j * NT;
+        if (d < H) {
+            sq[d] = __fmul_rn(v[j], v[j]);
+            bad |= !finite_f(v[j]) || !finite_f(rs[j]);
+        }
+    }
+    {
+        const float ss = layer_ordered_sum(sq, H, bad, scan);
+        if (tid == 0) {
+            s_inv = pow_neg_half(__fadd_rn(__fdiv_rn(ss, (float)H), a.eps_router));
+            s_root = __fdiv_rn(1.0f, sqrtf_exact((float)H));
+            if (!finite_f(s_inv) || !finite_f(s_root)) flag(a.f.status, SB_ERR_NONFINITE);
+        }
+        __syncthreads();
+        const float inv = s_inv, root = s_root;
+#pragma unroll
+        for (int j = 0; j < NV; j++) {
+            const int d = tid + j * NT;
+            if (d < H) {
+                const float t = __fmul_rn(__fmul_rn(__fmul_rn(v[j], inv), rs[j]), root);
+                bad |= !finite_f(t);
+                rin[d] = t;
+            }
+        }
+    }
+    if (bad) flag(a.f.status, SB_ERR_NONFINITE);
+    __syncthreads();                // the router input is complete
+    // ---- router logits: expert e = cta, cta + grid, ... ----
+    uint32_t ph_w = 0;
+    for (int e = cta; e < E; e += ncta) {
+        if (e != cta && tid == 0) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_expect_tx(S.bar_x, (uint32_t)(H * 4));
+            bulk_g2s(wrow, a.router_w + (size_t)e * H, (uint32_t)(H * 4), S.bar_x);
+        }
+        if (!fused_mbar_wait(S.bar_x, ph_w & 1)) timeout = true;
+        ph_w++;
+        for (int c = tid; c < H; c += NT) sq[c] = __fmul_rn(wrow[c], rin[c]);
+        __syncthreads();
+        if (warp == 0) {
+            // acc = fl(acc + p[c]), c ascending, handed from lane to lane.  The row is cut into passes of
+            // 32 * CHP columns; in a pass lane l holds the products of columns [l*CHP, (l+1)*CHP) in
+            // registers, so a step of the chain costs one dependent-add latency and nothing else.
+            constexpr int CHP = 44;
+            float acc = 0.0f;
+            float cur[CHP];
+            const int npass = (H + 32 * CHP - 1) / (32 * CHP);
+#pragma unroll 1
+            for (int ps = 0; ps < npass; ps++) {
+                const int cbase = ps * 32 * CHP;
+#pragma unroll
+                for (int i = 0; i < CHP; i += 4) *(float4*)(cur + i) = *(const float4*)(sq + cbase + lane * CHP + i);
+                const int mine = min(CHP, max(0, H - (cbase + lane * CHP)));     // valid columns of this lane in this pass
+#pragma unroll 1
+                for (int l = 0; l < 32; l++) {
+                    float s = __shfl_sync(0xffffffffu, acc, (l + 31) & 31);
+                    if (l == 0 && ps == 0) s = 0.0f;
+                    if (lane == l) {
+                        if (mine == CHP) {
+#pragma unroll
+                            for (int i = 0; i < CHP; i++) s = __fadd_rn(s, cur[i]);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < CHP; i++)
+                                if (i < mine) s = __fadd_rn(s, cur[i]);
+                        }
+                        acc = s;
+                    }
+                }
+            }
+            if (lane == 31) {
+                a.logits[e] = acc;
+                __threadfence();
+                atomicAdd(a.logits_count, 1);
+            }
+        }
+        __syncthreads();            // products and the router row are free again
+    }
+    // ---- all logits, then top-k and the job list, by every block for itself ----
+    if (tid == 0) {
+        uint32_t i = 0;
+        while (ld_acquire_gpu(a.logits_count) < E && i < FUSED_SPIN_LIMIT) i++;
+        if (i >= FUSED_SPIN_LIMIT) timeout = true;
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += NT) s_logits[e] = __ldcg(a.logits + e);
+    __syncthreads();
+    topk_group(tid < 128, s_logits, a.per_expert_scale, s_sel, s_wts, E, K, 1, cta == 0 ? a.f.status : nullptr, tk,
+               tk + topk_scratch_floats(E, K) - 4, tid & 127, 128);
+    __syncthreads();
+    if (tid == 0) {
+        int n = 0;
+        for (int j = 0; j < K; j++) {
+            const int e = s_sel[j];
+            if (e < a.expert_begin || e >= a.expert_end || n >= FUSED_MAX_JOBS) continue;
+            const uint8_t* base = a.pool + (size_t)(e - a.expert_begin) * a.expert_stride;
+            FusedJob fj;
+            fj.gate_v = base; fj.gate_s = base + a.value_bytes; fj.gate_b = fj.gate_s + a.group_bytes;
+            fj.up_v = base + a.tensor_bytes; fj.up_s = fj.up_v + a.value_bytes; fj.up_b = fj.up_s + a.group_bytes;
+            fj.down_v = base + 2 * a.tensor_bytes; fj.down_s = fj.down_v + a.value_bytes; fj.down_b = fj.down_s + a.group_bytes;
+            for (int t = 0; t < FUSED_MAX_TOKENS; t++) fj.x_row[t] = 0;
+            fj.g0 = j; fj.ntok = 1;              // one token: grouped order = rank order (experts ascending)
+            S.sJ[n++] = fj;
+        }
+        s_njobs = n;
+    }
+    if (cta == 0) {                 // what the next layer's reduce and the caller read
+        if (tid < K) {
+            a.selected[tid] = s_sel[tid];
+            a.weights_out[tid] = s_wts[tid];
+            a.c2g[tid] = tid;
+            a.g2c[tid] = tid;
+        }
+        for (int e = tid; e <= E; e += NT) {
+            int lt = 0;
+            for (int j = 0; j < K; j++) lt += s_sel[j] < e ? 1 : 0;
+            a.group_offsets[e] = lt;
+        }
+    }
+    __syncthreads();                // jobs published; the scratch is dead: the weight rows may land on it
+    const int n_jobs = s_njobs;
+    if (n_jobs > 0) timeout |= fused_expert_rounds<1, SLOTS>(a.f, G, S, n_jobs, true, s_rg, s_rd);
+    if (timeout && a.f.status) atomicOr(a.f.status, SB_ERR_TIMEOUT);
 }
 
 // ---- host side ---------------------------------------------------------------------------
 namespace {
-struct DeviceInfo { int sms = 0; size_t configured[3] = {0, 0, 0}; };
+struct DeviceInfo { int sms = 0; size_t configured[3] = {0, 0, 0}; bool layer_configured = false; };
 DeviceInfo g_dev[64];
 
 DeviceInfo* device_info() {
@@ -574,6 +875,33 @@ cudaError_t launch_q4_fused(const FusedArgs& args, cudaStream_t stream) {
     if (L.tt == 1) return launch_fused_t<1, 40>(a, L, d, 0, stream);
     if (L.tt == 2) return launch_fused_t<2, 32>(a, L, d, 1, stream);
     return launch_fused_t<4, 32>(a, L, d, 2, stream);
+}
+
+bool q4_layer_decode_plan(int H, int M, int E, int topk, int n_jobs_max, FusedLaunch* out) {
+    FusedLaunch L;
+    if (!q4_fused_plan(H, M, 1, n_jobs_max, &L) || L.tt != 1 || H > 16 * LAYER_SLOTS * LAYER_NV || (H & 3) || E < 1 ||
+        E > 1024 || topk < 1 || topk > 64 || topk > E)
+        return false;
+    const FusedGeom g = fused_geom(H, M, 1, LAYER_SLOTS);
+    if ((size_t)layer_scratch(H, E, topk).end * 4 > g.off_sgu) return false;    // the scratch overlays the weight rows only
+    if (out) *out = L;
+    return true;
+}
+
+cudaError_t launch_q4_layer_decode(const LayerDecodeArgs& args, int n_jobs_max, cudaStream_t stream) {
+    FusedLaunch L;
+    if (!q4_layer_decode_plan(args.f.H, args.f.M, args.E, args.topk, n_jobs_max, &L)) return cudaErrorInvalidValue;
+    DeviceInfo* d = device_info();
+    if (!d->layer_configured) {
+        cudaError_t e = cudaFuncSetAttribute(q4_layer_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)FUSED_SMEM_LIMIT);
+        if (e != cudaSuccess) return e;
+        d->layer_configured = true;
+    }
+    LayerDecodeArgs a = args;
+    a.f.jobs_per_round = L.jobs_per_round;
+    a.f.n_x = 1;
+    return launch_pdl(q4_layer_decode_kernel, dim3(L.grid), dim3(16 * LAYER_SLOTS), L.smem, stream, a);
 }
 
 }  // namespace sb
