@@ -25,13 +25,17 @@ cudaError_t launch_q4_jobs(const Q4Job* jobs, int njobs_max, const int* njobs_de
 constexpr int FUSED_MAX_JOBS = 32;       // expert groups per launch
 constexpr int FUSED_MAX_TOKENS = 4;      // activation rows per launch (and tokens per group)
 struct FusedJob {
-    const uint8_t *gate_v, *gate_s, *gate_b;   // packed values, bf16 scales, bf16 biases (all present, 16-byte aligned)
-    const uint8_t *up_v, *up_s, *up_b;
-    const uint8_t *down_v, *down_s, *down_b;
+    const uint8_t* v[3];                       // packed values of gate, up, down (16-byte aligned)
+    const uint32_t* t[3];                      // their derived tables: (scale bf16 << 16) | bias bf16 per group, [rows][C / 64]
     int32_t x_row[FUSED_MAX_TOKENS];           // activation row of each token of the group
     int32_t g0;                                // first grouped row (GeGLU rows and output rows g0, g0 + 1, ...)
     int32_t ntok;
+    int32_t lit, pad;                          // lit bit k: tensor k has a scale that needs the two-rounding dequantisation
 };
+// Builds the derived tables of n_experts expert slots (gate | up | down, each values | scales | biases).
+// words: [n_experts][3][groups] (groups = R * C / 64 of one tensor); flags: [n_experts].
+cudaError_t launch_q4_interleave_tables(const uint8_t* pool, size_t expert_stride, size_t tensor_bytes, size_t value_bytes,
+                                        size_t groups, int n_experts, uint32_t* words, int* flags, cudaStream_t stream);
 struct FusedArgs {
     const FusedJob* jobs;        // [n_jobs_max]
     const int* n_jobs_dev;       // live jobs (device)
@@ -72,6 +76,8 @@ struct LayerDecodeArgs {
     float* weights_out;            // [topk] (a different buffer than prev_weights)
     int32_t *c2g, *g2c, *group_offsets;
     const uint8_t* pool;           // slot of expert e at pool + (e - expert_begin) * expert_stride
+    const uint8_t* tables;         // derived scale | bias tables of the local experts
+    const int* lit_flags;          // [local experts]
     size_t expert_stride, tensor_bytes, value_bytes, group_bytes;
 };
 bool q4_layer_decode_plan(int H, int M, int E, int topk, int n_jobs_max, FusedLaunch* out);
@@ -193,6 +199,8 @@ struct MoePlanArgs {
     // (the first FUSED_MAX_JOBS local groups; the caller only uses them when there can be no more)
     FusedJob* fused_jobs;        // [FUSED_MAX_JOBS] or null
     int* fused_done;             // [FUSED_MAX_JOBS] or null
+    const uint8_t* fused_tables; // derived scale | bias tables, expert e at fused_tables + e * 6 * group_bytes
+    const int* fused_lit;        // [experts] indexed like the pool (globally; local slot 0 = expert_begin)
     int* status;
 };
 cudaError_t launch_moe_plan(const MoePlanArgs& a, cudaStream_t stream);

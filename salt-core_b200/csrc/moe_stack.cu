@@ -29,6 +29,8 @@ struct Layer {
     float* per_expert_scale = nullptr;
     float* norm_weight = nullptr;
     uint8_t* pool = nullptr;   // local experts only; slot of expert e at pool + (e - expert_begin) * stride
+    uint8_t* sb_tables = nullptr;   // derived copy for the fused decode kernels: (scale << 16) | bias words, [local][3][groups]
+    int* lit_flags = nullptr;       // [local] bit k: tensor k of the expert has a scale that needs the two-rounding form
     size_t expert_stride = 0;
     float eps = 0.0f;
     // optional dense branch and norms of the whole feed-forward block
@@ -101,7 +103,7 @@ struct Timed {
 static void free_stack(Stack* s) {
     for (auto& l : s->layers) {
         cudaFree(l.router_w); cudaFree(l.router_scale); cudaFree(l.per_expert_scale);
-        cudaFree(l.norm_weight); cudaFree(l.pool);
+        cudaFree(l.norm_weight); cudaFree(l.pool); cudaFree(l.sb_tables); cudaFree(l.lit_flags);
         cudaFree(l.pre_ffn_norm); cudaFree(l.pre_ffn_norm_2); cudaFree(l.post_ffn_norm_1);
         cudaFree(l.post_ffn_norm_2); cudaFree(l.post_ffn_norm); cudaFree(l.dense); cudaFree(l.dense_jobs);
     }
@@ -209,9 +211,14 @@ int salt_b200_stack_add_q4_layer(void* stack, const SaltB200Q4LayerSpec* spec) {
               upload(&l.per_expert_scale, spec->per_expert_scale, (size_t)s->n_experts) &&
               upload(&l.pool, src, local * spec->expert_stride) &&
               (!spec->norm_weight || upload(&l.norm_weight, spec->norm_weight, (size_t)s->hidden));
+    const size_t groups = elems / 64;
+    ok = ok && dev_alloc(&l.sb_tables, local * 3 * groups * 4) && dev_alloc(&l.lit_flags, local) &&
+         cuda_ok(launch_q4_interleave_tables(l.pool, l.expert_stride, tensor_bytes, elems / 2, groups, (int)local,
+                                             (uint32_t*)l.sb_tables, l.lit_flags, 0), "scale tables") &&
+         cuda_ok(cudaDeviceSynchronize(), "scale tables");
     if (!ok) {
         cudaFree(l.router_w); cudaFree(l.router_scale); cudaFree(l.per_expert_scale); cudaFree(l.pool);
-        cudaFree(l.norm_weight);
+        cudaFree(l.norm_weight); cudaFree(l.sb_tables); cudaFree(l.lit_flags);
         return -1;
     }
     s->layers.push_back(l);
@@ -312,7 +319,11 @@ static int layer_experts_impl(Stack* s, int layer, const float* d_router_src, co
                        B <= FUSED_MAX_TOKENS && njobs_max <= FUSED_MAX_JOBS &&
                        ((((uintptr_t)d_x) | ((uintptr_t)l.pool) | l.expert_stride) & 15) == 0 &&
                        q4_fused_plan(H, M, B, njobs_max, nullptr);
-    if (fused) { a.fused_jobs = s->fused_jobs; a.fused_done = s->fused_done; }
+    if (fused) {
+        a.fused_jobs = s->fused_jobs; a.fused_done = s->fused_done;
+        a.fused_tables = l.sb_tables - (size_t)s->expert_begin * 6 * a.group_bytes;
+        a.fused_lit = l.lit_flags - s->expert_begin;
+    }
     {
         Timed t(s, KC_PLAN, st);
         if (!cuda_ok(launch_moe_plan(a, st), "plan")) return -1;
@@ -637,7 +648,7 @@ static int forward_decode_layers(Stack* s, int first, int count, const float* d_
         a.E = s->n_experts; a.topk = K; a.expert_begin = s->expert_begin; a.expert_end = s->expert_end;
         a.selected = s->selected; a.weights_out = wbuf[i & 1]; a.c2g = s->c2g; a.g2c = s->g2c;
         a.group_offsets = s->group_offsets;
-        a.pool = l.pool; a.expert_stride = l.expert_stride;
+        a.pool = l.pool; a.tables = l.sb_tables; a.lit_flags = l.lit_flags; a.expert_stride = l.expert_stride;
         a.value_bytes = elems / 2; a.group_bytes = elems / 64 * 2; a.tensor_bytes = a.value_bytes + 2 * a.group_bytes;
         Timed t(s, KC_GATE_UP, st);
         if (!cuda_ok(launch_q4_layer_decode(a, a.f.n_jobs_max, st), "decode layer")) return -1;

@@ -998,12 +998,12 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(MoePlanArgs a) {
         a.down_jobs[slot] = dn;
         if (a.fused_jobs != nullptr && slot < FUSED_MAX_JOBS) {
             FusedJob fj;
-            fj.gate_v = gu.vals; fj.gate_s = gu.scales; fj.gate_b = gu.biases;
-            fj.up_v = gu.vals2; fj.up_s = gu.scales2; fj.up_b = gu.biases2;
-            fj.down_v = dn.vals; fj.down_s = dn.scales; fj.down_b = dn.biases;
+            fj.v[0] = gu.vals; fj.v[1] = gu.vals2; fj.v[2] = dn.vals;
+            for (int k = 0; k < 3; k++)
+                fj.t[k] = (const uint32_t*)(a.fused_tables + ((size_t)e * 6 + 2 * k) * a.group_bytes);
             for (int t = 0; t < FUSED_MAX_TOKENS; t++)
                 fj.x_row[t] = a.grouped_to_canonical[g0 + min(t, cnt - 1)] / a.topk;
-            fj.g0 = g0; fj.ntok = cnt;
+            fj.g0 = g0; fj.ntok = cnt; fj.lit = a.fused_lit[e]; fj.pad = 0;
             a.fused_jobs[slot] = fj;
         }
     }
@@ -1087,12 +1087,12 @@ __global__ void __launch_bounds__(512) moe_plan_small_kernel(MoePlanArgs a) {
         a.down_jobs[slot] = dn;
         if (a.fused_jobs != nullptr && slot < FUSED_MAX_JOBS) {
             FusedJob fj;
-            fj.gate_v = gu.vals; fj.gate_s = gu.scales; fj.gate_b = gu.biases;
-            fj.up_v = gu.vals2; fj.up_s = gu.scales2; fj.up_b = gu.biases2;
-            fj.down_v = dn.vals; fj.down_s = dn.scales; fj.down_b = dn.biases;
+            fj.v[0] = gu.vals; fj.v[1] = gu.vals2; fj.v[2] = dn.vals;
+            for (int k = 0; k < 3; k++)
+                fj.t[k] = (const uint32_t*)(a.fused_tables + ((size_t)e * 6 + 2 * k) * a.group_bytes);
             for (int t = 0; t < FUSED_MAX_TOKENS; t++)
                 fj.x_row[t] = s_g2c[g0 + min(t, cnt - 1)] / a.topk;
-            fj.g0 = g0; fj.ntok = cnt;
+            fj.g0 = g0; fj.ntok = cnt; fj.lit = a.fused_lit[e]; fj.pad = 0;
             a.fused_jobs[slot] = fj;
         }
     }
