@@ -36,7 +36,7 @@
 
 namespace sb {
 
-constexpr int FUSED_GU_CHUNKS = 4;                // pieces in which a packed gate/up row is requested
+constexpr int FUSED_GU_CHUNKS = 2;                // pieces in which a packed gate/up row is requested
 constexpr uint32_t FUSED_SPIN_LIMIT = 1u << 21;   // polls of a counter or of an mbarrier (a fraction of a second)
 
 // Stride of a packed gate/up row in shared memory: the smallest multiple of 16 bytes for which the
@@ -197,7 +197,7 @@ struct FusedSmem {
     }
     // by one thread, before the block's first barrier
     __device__ __forceinline__ void init_barriers() {
-        for (int i = 0; i < NW * FUSED_GU_CHUNKS + 3; i++) mbar_init(bar_gu + i, bar_gu + i == bar_sc ? 2 : 1);   // bar_sc: gate/up arrays + down arrays
+        for (int i = 0; i < NW * FUSED_GU_CHUNKS + 3; i++) mbar_init(bar_gu + i, bar_gu + i == bar_sc ? 6 : 1);   // bar_sc: one arrival per table and job segment
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
 };
@@ -264,40 +264,35 @@ __device__ __forceinline__ bool fused_expert_rounds(const FusedArgs& a, const Fu
     };
     // Ranges of the block's share [lo, hi) of an index space of `rows`-row jobs: up to two job segments.
     // The (scale << 16) | bias words of a segment's rows are contiguous: one copy per tensor and segment,
-    // widened to 16-byte boundaries.  Executed by one thread.
-    auto issue_ranges = [&](int j0, int lo, int hi, int rows, int gpr, ScaleRange* rg, uint8_t* stage, int cap,
-                            int first_tensor, int ntens, uint64_t* bar) {
-        const int row_bytes = gpr * 4;
-        uint32_t total = 0;
-        int stage_off = 0, nbytes[2];
-        for (int seg = 0; seg < 2; seg++) {
-            ScaleRange sr;
-            sr.r0 = 0; sr.r1 = 0; sr.byte0 = 0; sr.stage_off = stage_off;
-            nbytes[seg] = 0;
-            const int ja = lo / rows + seg;
-            const int slo = max(lo, ja * rows), shi = min(hi, (ja + 1) * rows);
-            if (hi > lo && shi > slo) {
-                sr.r0 = slo - ja * rows; sr.r1 = shi - ja * rows;
-                sr.byte0 = (sr.r0 * row_bytes) & ~15;
-                nbytes[seg] = ((sr.r1 * row_bytes + 15) & ~15) - sr.byte0;    // the table's size is a multiple of 16
-                stage_off += nbytes[seg];
-                total += (uint32_t)(ntens * nbytes[seg]);
-            }
-            rg[seg] = sr;
-        }
-        mbar_expect_tx(bar, total);
-        for (int seg = 0; seg < 2; seg++) {
-            if (nbytes[seg] == 0) continue;
-            const FusedJob& jb = sJ[j0 + lo / rows + seg];
-            for (int t = 0; t < ntens; t++)
-                bulk_g2s(stage + (size_t)t * cap + rg[seg].stage_off, (const uint8_t*)jb.t[first_tensor + t] + rg[seg].byte0,
-                         (uint32_t)nbytes[seg], bar);
-        }
-    };
-    // bar_sc counts two arrivals per round: the gate/up tables and the down table
+    // widened to 16-byte boundaries.  Lanes 0..5 of warp 0 each own one (tensor, segment) pair: lane =
+    // 2 * tensor + segment, tensor 0 gate, 1 up, 2 down; bar_sc counts their six arrivals per round.
     auto issue_scales = [&](const Round& R) {
-        issue_ranges(R.j0, R.gu_lo, R.gu_hi, M, G.gu_gpr, s_rg, sSG, G.gu_sc_cap, 0, 2, bar_sc);
-        issue_ranges(R.j0, R.dn_lo, R.dn_hi, H, G.dn_gpr, s_rd, sSD, G.dn_sc_cap, 2, 1, bar_sc);
+        if (lane >= 6) return;
+        const int t = lane >> 1, seg = lane & 1;
+        const bool dn = t == 2;
+        const int lo = dn ? R.dn_lo : R.gu_lo, hi = dn ? R.dn_hi : R.gu_hi, rows = dn ? H : M;
+        const int row_bytes = (dn ? G.dn_gpr : G.gu_gpr) * 4;
+        const int j_first = lo / rows;
+        ScaleRange sr;
+        sr.r0 = 0; sr.r1 = 0; sr.byte0 = 0; sr.stage_off = 0;
+        int nbytes = 0;
+        for (int sg = 0; sg <= seg; sg++) {          // segment 1 starts where segment 0 ends in the staging area
+            sr.stage_off += nbytes;
+            const int slo = max(lo, (j_first + sg) * rows), shi = min(hi, (j_first + sg + 1) * rows);
+            sr.r0 = 0; sr.r1 = 0; sr.byte0 = 0; nbytes = 0;
+            if (hi > lo && shi > slo) {
+                sr.r0 = slo - (j_first + sg) * rows; sr.r1 = shi - (j_first + sg) * rows;
+                sr.byte0 = (sr.r0 * row_bytes) & ~15;
+                nbytes = ((sr.r1 * row_bytes + 15) & ~15) - sr.byte0;        // the table's size is a multiple of 16
+            }
+        }
+        if (t == 0) s_rg[seg] = sr;
+        if (dn) s_rd[seg] = sr;
+        mbar_expect_tx(bar_sc, (uint32_t)nbytes);
+        if (nbytes > 0) {
+            uint8_t* stage = dn ? sSD : sSG + (size_t)t * G.gu_sc_cap;
+            bulk_g2s(stage + sr.stage_off, (const uint8_t*)sJ[R.j0 + j_first + seg].t[t] + sr.byte0, (uint32_t)nbytes, bar_sc);
+        }
     };
     // The block's down rows are contiguous in memory and need no padding (the dense rows a warp reads
     // together already fall in different banks): one copy per job segment (s_rd).  One thread.
@@ -322,8 +317,8 @@ __device__ __forceinline__ bool fused_expert_rounds(const FusedArgs& a, const Fu
     // order of the requests: the small ones first (scales, biases, activations: the tables are built
     // from them while the weights stream in), then every warp's gate/up rows, then the down rows
     Round R = round_of(0);
+    if (warp == 0) issue_scales(R);
     if (tid == 0) {
-        issue_scales(R);
         if (!x_resident) {
             mbar_expect_tx(bar_x, (uint32_t)(a.n_x * H * 4));
             for (int t = 0; t < a.n_x; t++) bulk_g2s(sX + (size_t)t * H, a.x + (size_t)t * a.x_stride, (uint32_t)(H * 4), bar_x);
@@ -458,10 +453,11 @@ __device__ __forceinline__ bool fused_expert_rounds(const FusedArgs& a, const Fu
             }
         }
         __syncthreads();               // the block is done with this round's down rows and tables
-        if (r + 1 < rounds && tid == 0) {
+        if (r + 1 < rounds && warp == 0) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             issue_scales(Rn);
-            issue_dn(Rn);
+            __syncwarp();              // s_rd is read by the thread that requests the down rows
+            if (tid == 0) issue_dn(Rn);
         }
         __syncthreads();               // next round's s_rg / s_rd are published
         R = Rn;
@@ -674,48 +670,53 @@ __global__ void __launch_bounds__(16 * LAYER_SLOTS, 1) q4_layer_decode_kernel(La
             mbar_expect_tx(S.bar_x, (uint32_t)(H * 4));
             bulk_g2s(wrow, a.router_w + (size_t)e * H, (uint32_t)(H * 4), S.bar_x);
         }
-        if (!fused_mbar_wait(S.bar_x, ph_w & 1)) timeout = true;
-        ph_w++;
-        for (int c = tid; c < H; c += NT) sq[c] = __fmul_rn(wrow[c], rin[c]);
-        __syncthreads();
         if (warp == 0) {
-            // acc = fl(acc + p[c]), c ascending, handed from lane to lane.  The row is cut into passes of
-            // 32 * CHP columns; in a pass lane l holds the products of columns [l*CHP, (l+1)*CHP) in
-            // registers, so a step of the chain costs one dependent-add latency and nothing else.
+            if (!fused_mbar_wait(S.bar_x, ph_w & 1)) timeout = true;
+            // acc = fl(acc + fl(W[c] * rin[c])), c ascending (reference src/kernels.c:98-106), handed from
+            // lane to lane.  The row is cut into passes of 32 * CHP columns; in a pass lane l holds the
+            // products of columns [l*CHP, (l+1)*CHP) in registers, so a step of the chain costs one
+            // dependent-add latency and nothing else.  Every lane runs the adds of every turn on its own
+            // products (no divergence); only the lane whose turn it is keeps the result.
             constexpr int CHP = 44;
             float acc = 0.0f;
             float cur[CHP];
             const int npass = (H + 32 * CHP - 1) / (32 * CHP);
 #pragma unroll 1
             for (int ps = 0; ps < npass; ps++) {
-                const int cbase = ps * 32 * CHP;
+                const int c0 = ps * 32 * CHP + lane * CHP;
 #pragma unroll
-                for (int i = 0; i < CHP; i += 4) *(float4*)(cur + i) = *(const float4*)(sq + cbase + lane * CHP + i);
-                const int mine = min(CHP, max(0, H - (cbase + lane * CHP)));     // valid columns of this lane in this pass
+                for (int i = 0; i < CHP; i += 4) {
+                    // columns past H read scratch that is never added
+                    const float4 wv = *(const float4*)(wrow + c0 + i), xv = *(const float4*)(rin + c0 + i);
+                    cur[i] = __fmul_rn(wv.x, xv.x); cur[i + 1] = __fmul_rn(wv.y, xv.y);
+                    cur[i + 2] = __fmul_rn(wv.z, xv.z); cur[i + 3] = __fmul_rn(wv.w, xv.w);
+                }
+                const bool full = (ps + 1) * 32 * CHP <= H;                 // every lane has CHP valid columns
+                const int mine = min(CHP, max(0, H - c0));
 #pragma unroll 1
                 for (int l = 0; l < 32; l++) {
                     float s = __shfl_sync(0xffffffffu, acc, (l + 31) & 31);
                     if (l == 0 && ps == 0) s = 0.0f;
-                    if (lane == l) {
-                        if (mine == CHP) {
+                    if (full) {
 #pragma unroll
-                            for (int i = 0; i < CHP; i++) s = __fadd_rn(s, cur[i]);
-                        } else {
+                        for (int i = 0; i < CHP; i++) s = __fadd_rn(s, cur[i]);
+                    } else {
 #pragma unroll
-                            for (int i = 0; i < CHP; i++)
-                                if (i < mine) s = __fadd_rn(s, cur[i]);
+                        for (int i = 0; i < CHP; i++) {
+                            const float t = __fadd_rn(s, cur[i]);
+                            s = i < mine ? t : s;
                         }
-                        acc = s;
                     }
+                    acc = lane == l ? s : acc;
                 }
             }
             if (lane == 31) {
                 a.logits[e] = acc;
-                __threadfence();
-                atomicAdd(a.logits_count, 1);
+                asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(a.logits_count) : "memory");
             }
         }
-        __syncthreads();            // products and the router row are free again
+        ph_w++;
+        if (e + ncta < E) __syncthreads();     // the router row is free for the next expert's copy
     }
     // ---- all logits, then top-k and the job list, by every block for itself ----
     if (tid == 0) {
