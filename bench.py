@@ -50,6 +50,8 @@ def parse():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="budget of the CPU baseline sample")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="skip the untimed extras of the default run (batch sweep, expert-phase roofline, parity check)")
     ap.add_argument("--ep-exchange", choices=["peer", "nccl"], default="peer",
                     help="N>1: exchange of the grouped expert outputs by the stack's own kernel over peer "
                          "memory (falls back to nccl when the regions cannot be mapped) or by an NCCL all-reduce")
@@ -162,6 +164,27 @@ def cpu_baseline(layers, B, seconds, threads):
             "ms_per_layer": 1e3 * el / n}
 
 
+def cpu_parity(layers, x, y_gpu, threads):
+    """Part of the CPU-baseline leg: the same layers on the CPU checker (the compiled reference where it
+    was built, else the port), compared with the GPU result bit for bit.  Not timed."""
+    import oracle
+    cur = np.ascontiguousarray(x, np.float32)
+    if oracle.RefDriver.available():
+        drv, kind = oracle.RefDriver(threads), "reference functions (oracle/_ref)"
+        for i, layer in enumerate(layers):
+            cur, _, _ = drv.moe_layer_q4(layer, cur)
+            if i + 1 < len(layers):
+                cur = drv.rmsnorm_rows(cur, layer.norm_weight, layer.eps)
+    else:
+        orc, kind = oracle.Oracle(), "CPU port (oracle/salt_oracle.c)"
+        for i, layer in enumerate(layers):
+            cur, _, _ = orc.moe_layer_q4(layer, cur, threads=threads)
+            if i + 1 < len(layers):
+                cur = np.stack([orc.rmsnorm(cur[t], layer.norm_weight, layer.eps, True)[1] for t in range(cur.shape[0])])
+    same = bool((np.ascontiguousarray(cur).view(np.uint32) == np.ascontiguousarray(y_gpu).view(np.uint32)).all())
+    return {"vs": f"{kind}, first {len(layers)} layers of the stack at B={x.shape[0]}", "bit_identical": same}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -229,7 +252,8 @@ def run_b200(args):
     B = args.batch * world
     L = args.layers
     lo, hi = importlib.import_module("salt-core_b200.ep").expert_range(rank, world, E)
-    stack = stack_mod.MoeStack(max(B, 1), H, M, E, K, expert_begin=lo, expert_end=hi)
+    extras = world == 1 and not args.prefill and not args.no_extra and B == 1
+    stack = stack_mod.MoeStack(max(B, 512 if extras else 1), H, M, E, K, expert_begin=lo, expert_end=hi)
     host_layers = generate_layers(synth, L, 3 if rank == 0 else 0, lambda i, layer: stack.add_layer(layer))
     x_host = synth.make_tokens(77, B, H)
     stream = torch.cuda.Stream()
@@ -237,8 +261,10 @@ def run_b200(args):
     d_x = torch.from_numpy(x_host).cuda()
     d_y = torch.empty_like(d_x)
     act = [torch.empty_like(d_x), torch.empty_like(d_x)]
-    grouped = torch.zeros(B * K * H, dtype=torch.float32, device="cuda")
-    assert stack.set_grouped_out(grouped.data_ptr(), grouped.numel() * 4) == 0
+    grouped = None
+    if world > 1:                             # the NCCL exchange works on a buffer this process owns
+        grouped = torch.zeros(B * K * H, dtype=torch.float32, device="cuda")
+        assert stack.set_grouped_out(grouped.data_ptr(), grouped.numel() * 4) == 0
 
     ep = importlib.import_module("salt-core_b200.ep")
 
@@ -355,59 +381,148 @@ def run_b200(args):
             ms_e2e = timed(e2e_step, args.steps)
 
         # per-kernel-class device time (CUDA event pairs around every launch), separate pass
-        kernels, roofline = {}, None
+        kernels, roofline, roofline_layer, extra = {}, None, None, {}
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except OSError:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        peak_tf = float(peaks.get("bf16_tflops", 1590.0))
+        peak_source = "measured (MEASURED_PEAKS.json)" if peaks else "fallback 6650 GB/s / 1590 TFLOP/s"
         if world == 1:
-            stack.profile(True, max_launches=launches_per_step * args.steps + 16)
-            for _ in range(args.steps):
-                if args.prefill:
-                    forward_layers(d_x, d_y)
-                else:
-                    assert stack.forward_device(d_x.data_ptr(), B, d_y.data_ptr(), stream=sp) == 0
-            prof = stack.profile_read()
-            stack.profile(False, 0)
-            # distinct experts per layer (decides the algorithmic bytes of a launch)
-            distinct = []
-            ws = stack.workspace()
-            lib = stack.lib
-            offs = np.empty(E + 1, np.int32)
-            cur = d_x.data_ptr()
-            for l in range(L):
-                out = act[l & 1]
-                stack.layer_experts(l, cur, B, router_input_ready=l > 0, stream=sp)
-                stack.layer_combine(l, B, out.data_ptr(), apply_norm=True, prepare_next=True, stream=sp)
-                import ctypes as C
-                lib.salt_b200_read_device(C.c_void_p(offs.ctypes.data), C.c_void_p(ws.group_offsets),
-                                          C.c_size_t(offs.nbytes))
-                distinct.append(int((np.diff(offs) > 0).sum()))
-                cur = out.data_ptr()
-            mean_distinct = float(np.mean(distinct))
-            for name, (ms, n) in prof.items():
-                if n:
-                    kernels[name] = {"launches": n, "total_ms": ms, "us_per_launch": 1e3 * ms / n}
+            import ctypes as C
+
+            def profiled(run, steps):
+                stack.profile(True, max_launches=8 * L * steps + 16)
+                for _ in range(steps):
+                    run()
+                prof = stack.profile_read()
+                stack.profile(False, 0)
+                return {name: {"launches": n, "total_ms": ms, "us_per_launch": 1e3 * ms / n}
+                        for name, (ms, n) in prof.items() if n}
+
+            def distinct_experts(batch, src, bufs):
+                """Mean number of distinct experts a layer selects (decides its algorithmic bytes)."""
+                out, offs, cur = [], np.empty(E + 1, np.int32), src.data_ptr()
+                ws = stack.workspace()
+                for l in range(L):
+                    nxt = bufs[l & 1]
+                    stack.layer_experts(l, cur, batch, router_input_ready=l > 0, stream=sp)
+                    stack.layer_combine(l, batch, nxt.data_ptr(), apply_norm=True, prepare_next=True, stream=sp)
+                    stack.lib.salt_b200_read_device(C.c_void_p(offs.ctypes.data), C.c_void_p(ws.group_offsets),
+                                                    C.c_size_t(offs.nbytes))
+                    out.append(int((np.diff(offs) > 0).sum()))
+                    cur = nxt.data_ptr()
+                return float(np.mean(out))
+
+            def layer_bytes(distinct, batch):
+                """Algorithmic bytes of one layer: the selected experts' three tensors, the router
+                weights, and the activation rows read and written along the way."""
+                act_bytes = batch * H * 4 * 3 + batch * K * (2 * M + 2 * H) * 4
+                return distinct * 3 * TENSOR_BYTES + E * H * 4 + act_bytes
+
+            # events are recorded around direct launches (a graph replay has no host-side launch to bracket)
+            direct = (lambda: forward_layers(d_x, d_y)) if args.prefill else \
+                     (lambda: stack.forward_device(d_x.data_ptr(), B, d_y.data_ptr(), stream=sp))
+            kernels = profiled(direct, args.steps)
+            mean_distinct = distinct_experts(B, d_x, act)
             gu = kernels["gate_up_geglu"]
-            alg = mean_distinct * 2 * TENSOR_BYTES + B * H * 4 + B * K * M * 4
-            peaks = {}
-            try:
-                peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-            except OSError:
-                pass
-            peak = float(peaks.get("hbm_gbs", 6650.0))
+            one_launch = B == 1 and not args.prefill and "down" not in kernels
+            if one_launch:
+                # one launch per layer: the kernel holds the router phases too, so its bytes are the layer's
+                alg = layer_bytes(mean_distinct, B)
+                kname = "q4_layer_decode_kernel (reduce + norm + router + top-k + gate/up + GeGLU + down of one layer)"
+            else:
+                alg = mean_distinct * 2 * TENSOR_BYTES + B * H * 4 + B * K * M * 4
+                kname = ("q4_gemm_tc_kernel<fused> (tcgen05 gate/up + GeGLU)" if tc_mode
+                         else "q4_tile16_kernel<2,TT> / q4_fused_expert_kernel (gate/up + GeGLU)")
             achieved = alg / (gu["us_per_launch"] * 1e-6) / 1e9
-            dn = kernels["down"]
-            # DRAM bytes of one gate/up launch from the ncu capture of this kernel (read + write,
-            # 2.241 MB per distinct expert at B=1: profiles/q4_tile16_kernel_decode_b1.md); scales with
-            # the distinct experts of a launch, so it is only reported for the decode kernel at B=1
-            traffic = mean_distinct * 2_240_992.0 if (B == 1 and not tc_mode) else None
-            kname = ("q4_gemm_tc_kernel<fused> (tcgen05 gate/up + GeGLU)" if tc_mode
-                     else "q4_tile16_kernel<2,TT> (fused gate/up + GeGLU)")
-            roofline = {"bound": "hbm", "kernel": kname,
-                        "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                        "peak_source": "measured (MEASURED_PEAKS.json)" if peaks else "fallback 6650 GB/s",
-                        "algorithmic_bytes_per_launch": alg, "us_per_launch": gu["us_per_launch"],
-                        "mean_distinct_experts": mean_distinct, "traffic": traffic,
-                        "down_kernel": {"achieved": (mean_distinct * TENSOR_BYTES + B * K * (M + H) * 4)
-                                        / (dn["us_per_launch"] * 1e-6) / 1e9,
-                                        "us_per_launch": dn["us_per_launch"]}}
+            roofline = {"bound": "hbm", "kernel": kname, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                        "frac": achieved / peak, "peak_source": peak_source, "algorithmic_bytes_per_launch": alg,
+                        "us_per_launch": gu["us_per_launch"], "mean_distinct_experts": mean_distinct,
+                        "traffic": None,
+                        "traffic_note": "not measured by this run; DRAM bytes per launch are in the ncu summaries under profiles/"}
+            if tc_mode and B * K / E >= 96:
+                # rows per expert beyond the ridge: the expert GEMMs are bound by the tensor pipe
+                flops = 2.0 * B * K * 2 * H * M
+                tf = flops / (gu["us_per_launch"] * 1e-6) / 1e12
+                roofline.update({"bound": "tensor", "achieved": tf, "peak": peak_tf, "unit": "TFLOP/s",
+                                 "frac": tf / peak_tf, "flops_per_launch": flops})
+            lb = layer_bytes(mean_distinct, B)
+            us_layer = 1e3 * ms_step / L
+            roofline_layer = {"bound": "hbm", "what": "one whole layer (all its kernels), graph replay",
+                              "algorithmic_bytes": lb, "us_per_layer": us_layer,
+                              "achieved": lb / (us_layer * 1e-6) / 1e9, "peak": peak, "unit": "GB/s",
+                              "frac": lb / (us_layer * 1e-6) / 1e9 / peak}
+            if extras:
+                # (a) the expert phases alone (gate/up + GeGLU + down of the selected experts in one launch)
+                def two_phase():
+                    cur = d_x.data_ptr()
+                    for l in range(L):
+                        nxt = act[l & 1]
+                        stack.layer_experts(l, cur, B, router_input_ready=l > 0, stream=sp)
+                        stack.layer_combine(l, B, nxt.data_ptr(), apply_norm=True, prepare_next=True, stream=sp)
+                        cur = nxt.data_ptr()
+                kx = profiled(two_phase, max(3, args.steps // 4))["gate_up_geglu"]
+                xb = mean_distinct * 3 * TENSOR_BYTES + B * H * 4 + B * K * (2 * M + H) * 4
+                extra["expert_phases_kernel"] = {
+                    "kernel": "q4_fused_expert_kernel (gate/up + GeGLU + down, one launch)", "us_per_launch": kx["us_per_launch"],
+                    "algorithmic_bytes_per_launch": xb, "achieved_gbs": xb / (kx["us_per_launch"] * 1e-6) / 1e9,
+                    "frac": xb / (kx["us_per_launch"] * 1e-6) / 1e9 / peak}
+                # (b) batch sweep of the same stack (device-resident, graph replay; outside the headline)
+                sweep = {}
+                for bb, mode in ((4, None), (16, None), (64, None), (512, "split")):
+                    xs = torch.from_numpy(synth.make_tokens(77, bb, H)).cuda()
+                    ys = torch.empty_like(xs)
+                    acts = [torch.empty_like(xs), torch.empty_like(xs)]
+                    if mode is None:
+                        assert stack.graph_capture(xs.data_ptr(), bb, ys.data_ptr(), sp) == 0
+                        run = lambda: stack.graph_launch(sp)
+                    else:
+                        def run(xs=xs, ys=ys, acts=acts, bb=bb):
+                            cur = xs.data_ptr()
+                            for l in range(L):
+                                o = ys if l == L - 1 else acts[l & 1]
+                                stack.layer_experts(l, cur, bb, router_input_ready=l > 0, tensor_core="split", stream=sp)
+                                stack.layer_combine(l, bb, o.data_ptr(), apply_norm=True, prepare_next=l + 1 < L, stream=sp)
+                                cur = o.data_ptr()
+                    for _ in range(3):
+                        run()
+                    n_it = 5
+                    torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(stream)
+                    for _ in range(n_it):
+                        run()
+                    e1.record(stream)
+                    torch.cuda.synchronize()
+                    ms = e0.elapsed_time(e1) / n_it
+                    dist = distinct_experts(bb, xs, acts)
+                    by = layer_bytes(dist, bb)
+                    sweep[f"B{bb}"] = {"tokens_per_s": bb * L / (ms * 1e-3), "us_per_layer": 1e3 * ms / L,
+                                       "expert_projections": "exact (bit-exact vs CPU)" if mode is None else
+                                       "tcgen05, hi+lo fp16 operands (max rel. error <= 1e-3)",
+                                       "mean_distinct_experts": dist, "algorithmic_bytes_per_layer": by,
+                                       "hbm_frac": by / (1e3 * ms / L * 1e-6) / 1e9 / peak}
+                    assert stack.status(sp) == 0
+                extra["batch_sweep"] = sweep
+                if use_graph:                 # leave the headline graph in place
+                    assert stack.graph_capture(d_x.data_ptr(), B, d_y.data_ptr(), sp) == 0
+
+        # token 0's final output row: the same bits at every GPU count when the path is bit-identical
+        # across expert-parallel shardings (token 0 of the seeded batch is the same row for every batch size)
+        import zlib
+        step()
+        stream.synchronize()
+        y_token0_crc32 = zlib.crc32(d_y[0].cpu().numpy().tobytes()) & 0xffffffff
+        parity = None
+        if rank == 0 and world == 1 and not args.prefill and not args.no_extra:
+            n_chk = min(len(host_layers), L)
+            y_chk = torch.empty_like(d_x)
+            assert stack.forward_device(d_x.data_ptr(), B, y_chk.data_ptr(), first=0, count=n_chk, stream=sp) == 0
+            stream.synchronize()
+            parity = (host_layers[:n_chk], y_chk.cpu().numpy())
 
     value = B * L / (ms_step * 1e-3)
     out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -427,9 +542,15 @@ def run_b200(args):
         out["ep_exchange"] = "peer memory (own kernel over NVLink)" if peer else "nccl all_reduce"
     if roofline:
         out["roofline"] = roofline
+        out["roofline_layer"] = roofline_layer
         out["kernels"] = kernels
+    if extra:
+        out["extra"] = extra
+    out["y_token0_crc32"] = y_token0_crc32
     if rank == 0 and world == 1:
         out["cpu_baseline"] = cpu_baseline(host_layers, B, args.cpu_seconds, os.cpu_count() or 1)
+        if parity is not None:
+            out["parity"] = cpu_parity(parity[0], x_host, parity[1], os.cpu_count() or 1)
     if rank == 0:
         print(json.dumps(out))
     if world > 1:
