@@ -410,6 +410,14 @@ int salt_b200_layer_combine(void *stack, int layer, int B, float *d_y, int flags
 int salt_b200_stack_ep_region(void *stack, void *ipc_handle_out, void **region_out);
 int salt_b200_stack_ep_connect(void *stack, int rank, int world, const void *ipc_handles, void *const *regions);
 int salt_b200_stack_ep_exchange(void *stack, int B, int phase, void *stream);
+/* Bounded waits of the exchange: a slot that has not arrived after `polls` polls (about half a
+ * microsecond each; default 2^23, a few seconds) makes the kernel give up, set the timeout bit of the
+ * device error word (salt_b200_stack_status returns it) and return; the device stays usable.  After a
+ * timeout the ranks' exchange counters may differ: call salt_b200_stack_ep_reset on EVERY rank while no
+ * exchange is in flight anywhere (it clears the landing region, its counter and the error word), then
+ * exchange again.  No reference counterpart (the reference is single-device). */
+int salt_b200_stack_ep_set_poll_limit(void *stack, int polls);
+int salt_b200_stack_ep_reset(void *stack);
 /* Back to the unconnected state (peer mappings closed); call only between exchanges, after a host barrier. */
 int salt_b200_stack_ep_disconnect(void *stack);
 

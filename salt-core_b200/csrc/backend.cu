@@ -10,6 +10,9 @@
 // CPU execution path in this file: a call that cannot run on the device
 // returns -1.
 #include <cuda_runtime.h>
+#include <map>
+#include <mutex>
+#include <utility>
 #include <cmath>
 #include <stdio.h>
 #include <stdlib.h>
@@ -30,6 +33,20 @@ void fp4_release();
 Backend g_backend;
 static uint64_t g_launches = 0;
 void count_launches(int n) { g_launches += (uint64_t)n; }
+
+cudaError_t ensure_dynamic_smem(const void* kernel, size_t bytes) {
+    static std::mutex mu;
+    static std::map<std::pair<int, const void*>, size_t> done;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    std::lock_guard<std::mutex> lock(mu);
+    size_t& have = done[std::make_pair(dev, kernel)];
+    if (have >= bytes) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess) have = bytes;
+    return e;
+}
 uint64_t launch_count() { return g_launches; }
 
 bool cuda_ok(cudaError_t e, const char* what) {

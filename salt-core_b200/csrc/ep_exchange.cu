@@ -11,8 +11,8 @@
 //
 // Data and arrival flag travel together: a 16-byte slot holds two floats, each followed by
 // the 32-bit sequence number of the exchange {d0, seq, d1, seq}, written with one store.  The
-// reader polls the slot until both sequence numbers match; 8-byte halves of an aligned store
-// are never torn, so a matching number vouches for the float next to it.  No fence and no
+// reader polls the slot until both sequence numbers match; each {float, seq} pair is one naturally
+// aligned 64-bit element of the store, so a matching number vouches for the float next to it.  No fence and no
 // separate flag round trip sit between the producer's store and the consumer's load.
 //
 // Landing buffers alternate with the parity of an epoch counter that lives on the device and
@@ -21,8 +21,9 @@
 // rank still reads epoch e); it cannot be two ahead, because completing epoch e + 1 needs this
 // rank's push of e + 1, which this rank issues after it has finished reading epoch e.
 //
-// Every wait is bounded: when a slot does not arrive within a few seconds the block gives
-// up, the kernel sets SB_ERR_TIMEOUT in the status word and still advances the epoch.
+// Every wait is bounded (spin_limit polls of about half a microsecond): when a slot does not arrive
+// the block gives up, the kernel sets SB_ERR_TIMEOUT in the status word and still advances the epoch.
+// After a timeout the ranks' epochs may differ; ep_region_reset on every rank (all idle) starts over.
 #include "internal.h"
 #include "pdl.cuh"
 
@@ -38,18 +39,18 @@ size_t ep_region_bytes(int rows_cap, int width) {
     return (size_t)EP_HEADER_BYTES + 2 * (size_t)rows_cap * (width / 2) * 16;
 }
 
+// A slot is two 64-bit elements {float, seq}: the vector access is made of 64-bit element accesses, and
+// a naturally aligned 64-bit element is written and read as a whole, which is all the protocol needs.
 __device__ __forceinline__ uint4 ld_slot(const uint4* p) {
-    uint4 v;
-    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-    return v;
+    unsigned long long a, b;
+    asm volatile("ld.volatile.global.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+    return make_uint4((uint32_t)a, (uint32_t)(a >> 32), (uint32_t)b, (uint32_t)(b >> 32));
 }
 __device__ __forceinline__ void st_slot(uint4* p, uint4 v) {
-    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};"
-                 ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+    const unsigned long long a = (unsigned long long)v.x | ((unsigned long long)v.y << 32);
+    const unsigned long long b = (unsigned long long)v.z | ((unsigned long long)v.w << 32);
+    asm volatile("st.volatile.global.v2.b64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
 }
-
-constexpr int EP_SPIN_LIMIT = 1 << 23;   // polls of about half a microsecond: a few seconds
 
 __global__ void __launch_bounds__(EP_THREADS) ep_exchange_kernel(EpExchangeArgs a) {
     __shared__ int s_timed_out;
@@ -94,7 +95,7 @@ __global__ void __launch_bounds__(EP_THREADS) ep_exchange_kernel(EpExchangeArgs 
             uint4 w = ld_slot(src);
             int spins = 0;
             while (w.y != seq || w.w != seq) {
-                if (++spins > EP_SPIN_LIMIT || *(volatile int*)&s_timed_out) {
+                if (++spins > a.spin_limit || *(volatile int*)&s_timed_out) {
                     s_timed_out = 1;
                     break;
                 }
@@ -120,7 +121,7 @@ __global__ void __launch_bounds__(EP_THREADS) ep_exchange_kernel(EpExchangeArgs 
 }
 
 cudaError_t launch_ep_exchange(const EpExchangeArgs& a, int rows, cudaStream_t stream) {
-    if (a.world < 2 || a.world > EP_MAX_WORLD || a.rank < 0 || a.rank >= a.world || (a.width & 1) || !a.grouped ||
+    if (a.spin_limit < 1 || a.world < 2 || a.world > EP_MAX_WORLD || a.rank < 0 || a.rank >= a.world || (a.width & 1) || !a.grouped ||
         !(a.phase & (EP_PHASE_PUSH | EP_PHASE_PULL)) || rows < 1)
         return cudaErrorInvalidValue;
     for (int p = 0; p < a.world; p++)

@@ -9,6 +9,11 @@ namespace sb {
 
 struct Q4Job;
 
+// ---- backend.cu ------------------------------------------------------------
+// Raises a kernel's dynamic shared memory limit to at least `bytes` on the CURRENT device (the limit
+// is a per-device attribute of the function; remembered per device and kernel, safe from any thread).
+cudaError_t ensure_dynamic_smem(const void* kernel, size_t bytes);
+
 // ---- q4_kernels.cu -------------------------------------------------------
 bool q4_tile_supported(int C);
 // Runs every job (all share C and nmat).  njobs_dev (device int, may be null)
@@ -217,6 +222,7 @@ cudaError_t launch_routed_gather(const float* x, const int32_t* grouped_to_canon
 // A region = header (epoch) + two landing buffers of [rows_cap][width / 2] 16-byte slots.
 enum : int { EP_MAX_WORLD = 8, EP_THREADS = 256, EP_HEADER_BYTES = 4096 };
 enum : int { EP_PHASE_PUSH = 1, EP_PHASE_PULL = 2 };
+enum : int { EP_DEFAULT_SPIN_LIMIT = 1 << 23 };
 struct EpExchangeArgs {
     uint8_t* region[EP_MAX_WORLD];   // region[rank] is this device's own, the others are peer mappings
     int rank, world;
@@ -224,6 +230,7 @@ struct EpExchangeArgs {
     int expert_begin, expert_end, n_experts;
     float* grouped;                  // [rows][width]: own rows are read, the others written
     int width, rows_cap;
+    int spin_limit;                  // polls of a slot before the wait gives up (EP_DEFAULT_SPIN_LIMIT: a few seconds)
     int phase;                       // EP_PHASE_PUSH | EP_PHASE_PULL; one at a time only when all
                                      // ranks share a device and their launches are serialised
     int* status;

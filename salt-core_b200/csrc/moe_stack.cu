@@ -14,6 +14,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <mutex>
 #include <vector>
 
 #include "../../include/salt_gpu_b200.h"
@@ -81,6 +82,7 @@ struct Stack {
     uint8_t* ep_peer[EP_MAX_WORLD] = {};       // all ranks' regions (own included) once connected
     bool ep_opened[EP_MAX_WORLD] = {};         // mapped through a CUDA IPC handle
     int ep_rank = 0, ep_world = 0;
+    int ep_spin_limit = EP_DEFAULT_SPIN_LIMIT;
 };
 
 enum KernelClass { KC_ROUTER_INPUT = 0, KC_LOGITS, KC_TOPK, KC_PLAN, KC_GATE_UP, KC_DOWN, KC_REDUCE, KC_NORM, KC_COUNT };
@@ -339,8 +341,9 @@ static int layer_experts_impl(Stack* s, int layer, const float* d_router_src, co
         count_launches(3);
         return 0;
     }
-    // tokens per expert group: at most B; the kernels loop over larger groups
-    const int tok_hint = B == 1 ? 1 : (B == 2 ? 2 : 4);
+    // tokens per expert group: at most B (the tile kernels loop over a group's tokens and use the bound
+    // only to pick their token block; the any-shape kernel takes one grid row per token)
+    const int tok_hint = B;
     if (flags & (SB_EXPERTS_TENSOR_CORE | SB_EXPERTS_TENSOR_CORE_SINGLE)) {
         const bool split = (flags & SB_EXPERTS_TENSOR_CORE) != 0;
         if (!s->tc_ready) {
@@ -475,6 +478,24 @@ int salt_b200_stack_ep_disconnect(void* stack) {
     return 0;
 }
 
+int salt_b200_stack_ep_set_poll_limit(void* stack, int polls) {
+    Stack* s = (Stack*)stack;
+    if (!s || polls < 1) return -1;
+    s->ep_spin_limit = polls;
+    return 0;
+}
+
+// Clears this stack's landing region (epoch and both buffers) and its error word.  To be called on
+// every rank, with no exchange in flight anywhere, before the ranks exchange again.
+int salt_b200_stack_ep_reset(void* stack) {
+    Stack* s = (Stack*)stack;
+    if (!s || !s->ep_region) return -1;
+    const size_t bytes = ep_region_bytes(s->max_tokens * s->topk, s->hidden);
+    return cuda_ok(cudaDeviceSynchronize(), "ep reset sync") && cuda_ok(cudaMemset(s->ep_region, 0, bytes), "ep reset") &&
+                   cuda_ok(cudaMemset(s->status, 0, sizeof(int32_t)), "ep reset status") &&
+                   cuda_ok(cudaDeviceSynchronize(), "ep reset sync") ? 0 : -1;
+}
+
 int salt_b200_stack_ep_exchange(void* stack, int B, int phase, void* stream) {
     Stack* s = (Stack*)stack;
     if (!s || s->ep_world < 2 || B < 1 || B > s->max_tokens) return -1;
@@ -485,7 +506,7 @@ int salt_b200_stack_ep_exchange(void* stack, int B, int phase, void* stream) {
     a.group_offsets = s->group_offsets;
     a.expert_begin = s->expert_begin; a.expert_end = s->expert_end; a.n_experts = s->n_experts;
     a.grouped = s->grouped_out; a.width = s->hidden; a.rows_cap = s->max_tokens * s->topk;
-    a.phase = phase; a.status = s->status;
+    a.phase = phase; a.status = s->status; a.spin_limit = s->ep_spin_limit;
     Timed t(s, KC_NORM, (cudaStream_t)stream);
     if (!cuda_ok(launch_ep_exchange(a, B * s->topk, (cudaStream_t)stream), "ep exchange")) return -1;
     count_launches(1);
@@ -562,7 +583,7 @@ int salt_b200_ffn_block_forward(void* stack, int layer, const float* d_residual,
     const Layer& l = s->layers[(size_t)layer];
     if (!l.ffn) return -1;
     const int H = s->hidden, D = l.dense_inter;
-    const int tok_hint = B == 1 ? 1 : (B == 2 ? 2 : 4);
+    const int tok_hint = B;            // see layer_experts_impl
     auto norm = [&](const float* w, float* y) {
         GlueArgs g;
         memset(&g, 0, sizeof g);
@@ -790,8 +811,19 @@ int salt_b200_q4_matvec_device(const void* d_vals, const void* d_scales, const v
     memset(&j, 0, sizeof j);
     j.vals = (const uint8_t*)d_vals; j.scales = (const uint8_t*)d_scales; j.biases = (const uint8_t*)d_biases;
     j.x = d_x; j.y = d_y; j.x_div = 1; j.R = R; j.C = C; j.ntok = B; j.x_stride = C; j.y_stride = R;
-    static Q4Job* d_job = nullptr;
-    if (!d_job && !cuda_ok(cudaMalloc((void**)&d_job, sizeof(Q4Job)), "job")) return -1;
+    // a ring of descriptor slots per device: calls in flight on different streams do not share one
+    constexpr int RING = 64, MAXDEV = 64;
+    static Q4Job* rings[MAXDEV] = {};
+    static unsigned cursor[MAXDEV] = {};
+    static std::mutex mu;
+    int dev = 0;
+    if (!cuda_ok(cudaGetDevice(&dev), "device") || dev < 0 || dev >= MAXDEV) return -1;
+    Q4Job* d_job;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!rings[dev] && !cuda_ok(cudaMalloc((void**)&rings[dev], RING * sizeof(Q4Job)), "job ring")) return -1;
+        d_job = rings[dev] + (cursor[dev]++ % RING);
+    }
     const bool aligned = (C % 64) == 0 &&
                          ((((uintptr_t)d_vals | (uintptr_t)d_scales | (uintptr_t)d_biases | (uintptr_t)d_x) & 15) == 0);
     if (!cuda_ok(cudaMemcpyAsync(d_job, &j, sizeof j, cudaMemcpyHostToDevice, (cudaStream_t)stream), "job upload") ||
@@ -807,11 +839,18 @@ int salt_b200_route_group_device(const int32_t* d_selected, int rows, int topk, 
     if (!d_selected || !d_group_offsets || !d_grouped_to_canonical || !d_canonical_to_grouped || rows < 1 ||
         topk < 1 || n_experts < 1 || n_experts > 1024 || topk > n_experts)
         return -1;
-    static int32_t* scratch = nullptr;  // n_active, max_group, status
-    static Q4Job* jobs = nullptr;
-    if (!scratch && (!cuda_ok(cudaMalloc((void**)&scratch, 4 * sizeof(int32_t)), "scratch") ||
-                     !cuda_ok(cudaMalloc((void**)&jobs, 2 * 1024 * sizeof(Q4Job)), "scratch")))
+    // scratch per device (n_active, max_group, status, unused descriptors); the call synchronises the
+    // stream before it returns, and callers serialise (one calling thread at a time)
+    constexpr int MAXDEV = 64;
+    static int32_t* scratch_dev[MAXDEV] = {};
+    static Q4Job* jobs_dev[MAXDEV] = {};
+    int dev = 0;
+    if (!cuda_ok(cudaGetDevice(&dev), "device") || dev < 0 || dev >= MAXDEV) return -1;
+    if (!scratch_dev[dev] && (!cuda_ok(cudaMalloc((void**)&scratch_dev[dev], 4 * sizeof(int32_t)), "scratch") ||
+                              !cuda_ok(cudaMalloc((void**)&jobs_dev[dev], 2 * 1024 * sizeof(Q4Job)), "scratch")))
         return -1;
+    int32_t* scratch = scratch_dev[dev];
+    Q4Job* jobs = jobs_dev[dev];
     MoePlanArgs a;
     memset(&a, 0, sizeof a);
     a.selected = d_selected; a.rows = rows; a.topk = topk; a.n_experts = n_experts;

@@ -278,12 +278,9 @@ static size_t fp4_smem(int C, int tt) {
 
 template <int TT>
 static cudaError_t launch_fp4_tile(const Fp4Job* jobs, int njobs, int max_rows, int C, cudaStream_t stream) {
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(nvfp4_tile_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             200 * 1024);
+    {
+        cudaError_t e = ensure_dynamic_smem((const void*)nvfp4_tile_kernel<TT>, (size_t)(200 * 1024));
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     dim3 grid((max_rows + 15) / 16, njobs);
     nvfp4_tile_kernel<TT><<<grid, 64, fp4_smem(C, TT), stream>>>(jobs, C);

@@ -800,7 +800,7 @@ cudaError_t launch_q4_interleave_tables(const uint8_t* pool, size_t expert_strid
 
 // ---- host side ---------------------------------------------------------------------------
 namespace {
-struct DeviceInfo { int sms = 0; size_t configured[3] = {0, 0, 0}; bool layer_configured = false; };
+struct DeviceInfo { int sms = 0; };
 DeviceInfo g_dev[64];
 
 DeviceInfo* device_info() {
@@ -839,13 +839,9 @@ bool q4_fused_plan(int H, int M, int n_x, int n_jobs_max, FusedLaunch* out) {
 }
 
 template <int TT, int SLOTS>
-static cudaError_t launch_fused_t(FusedArgs& a, const FusedLaunch& L, DeviceInfo* d, int cfg_slot, cudaStream_t stream) {
-    if (d->configured[cfg_slot] < L.smem) {
-        cudaError_t e = cudaFuncSetAttribute(q4_fused_expert_kernel<TT, SLOTS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)FUSED_SMEM_LIMIT);
-        if (e != cudaSuccess) return e;
-        d->configured[cfg_slot] = FUSED_SMEM_LIMIT;
-    }
+static cudaError_t launch_fused_t(FusedArgs& a, const FusedLaunch& L, cudaStream_t stream) {
+    cudaError_t e = ensure_dynamic_smem((const void*)q4_fused_expert_kernel<TT, SLOTS>, FUSED_SMEM_LIMIT);
+    if (e != cudaSuccess) return e;
     return launch_pdl(q4_fused_expert_kernel<TT, SLOTS>, dim3(L.grid), dim3(16 * SLOTS), L.smem, stream, a);
 }
 
@@ -853,12 +849,11 @@ cudaError_t launch_q4_fused(const FusedArgs& args, cudaStream_t stream) {
     FusedLaunch L;
     if (!q4_fused_plan(args.H, args.M, args.n_x, args.n_jobs_max, &L)) return cudaErrorInvalidValue;
     if ((((uintptr_t)args.x) & 15) || ((args.x_stride * 4) & 15)) return cudaErrorInvalidValue;
-    DeviceInfo* d = device_info();
     FusedArgs a = args;
     a.jobs_per_round = L.jobs_per_round;
-    if (L.tt == 1) return launch_fused_t<1, 40>(a, L, d, 0, stream);
-    if (L.tt == 2) return launch_fused_t<2, 32>(a, L, d, 1, stream);
-    return launch_fused_t<4, 32>(a, L, d, 2, stream);
+    if (L.tt == 1) return launch_fused_t<1, 40>(a, L, stream);
+    if (L.tt == 2) return launch_fused_t<2, 32>(a, L, stream);
+    return launch_fused_t<4, 32>(a, L, stream);
 }
 
 bool q4_layer_decode_plan(int H, int M, int E, int topk, int n_jobs_max, FusedLaunch* out) {
@@ -875,13 +870,8 @@ bool q4_layer_decode_plan(int H, int M, int E, int topk, int n_jobs_max, FusedLa
 cudaError_t launch_q4_layer_decode(const LayerDecodeArgs& args, int n_jobs_max, cudaStream_t stream) {
     FusedLaunch L;
     if (!q4_layer_decode_plan(args.f.H, args.f.M, args.E, args.topk, n_jobs_max, &L)) return cudaErrorInvalidValue;
-    DeviceInfo* d = device_info();
-    if (!d->layer_configured) {
-        cudaError_t e = cudaFuncSetAttribute(q4_layer_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)FUSED_SMEM_LIMIT);
-        if (e != cudaSuccess) return e;
-        d->layer_configured = true;
-    }
+    cudaError_t e = ensure_dynamic_smem((const void*)q4_layer_decode_kernel, FUSED_SMEM_LIMIT);
+    if (e != cudaSuccess) return e;
     LayerDecodeArgs a = args;
     a.f.jobs_per_round = L.jobs_per_round;
     a.f.n_x = 1;

@@ -612,12 +612,9 @@ template <bool FUSED, bool SPLIT>
 static cudaError_t launch_tc(const TcArgs& a, const TcMaps& maps, dim3 grid, cudaStream_t stream) {
     // the full dynamic shared memory keeps one block per SM, so a block's 256 TMEM columns
     // can always be allocated without waiting for a neighbour
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(q4_gemm_tc_kernel<FUSED, SPLIT>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
+    {
+        cudaError_t e = ensure_dynamic_smem((const void*)q4_gemm_tc_kernel<FUSED, SPLIT>, (size_t)TC_SMEM_BYTES);
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     q4_gemm_tc_kernel<FUSED, SPLIT><<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(a, maps);
     return cudaGetLastError();

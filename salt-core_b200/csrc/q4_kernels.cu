@@ -310,12 +310,9 @@ static cudaError_t launch_tile(const Q4Job* jobs, int njobs_max, const int* njob
     // several tokens per group: 16 row slots (half the activation copies per weight byte)
     constexpr int HALF = TT == 1 ? 8 : 16;
     size_t smem = tile_smem_bytes(C, NMAT, TT, HALF);
-    static size_t configured = 0;
-    if (smem > 48 * 1024 && smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(q4_tile16_kernel<NMAT, TT, HALF>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024));
+    if (smem > 48 * 1024) {
+        cudaError_t e = ensure_dynamic_smem((const void*)q4_tile16_kernel<NMAT, TT, HALF>, (size_t)(200 * 1024));
         if (e != cudaSuccess) return e;
-        configured = 200 * 1024;
     }
     constexpr int ROWS_A = NMAT == 2 ? HALF : 2 * HALF;
     dim3 grid((max_rows + ROWS_A - 1) / ROWS_A, njobs_max);

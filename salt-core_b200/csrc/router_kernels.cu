@@ -97,11 +97,9 @@ cudaError_t launch_q8_jobs(const Q4Job* jobs, int njobs, int max_rows, int max_t
     if (njobs < 1 || max_rows < 1 || max_tok < 1) return cudaSuccess;
     const size_t smem = (size_t)((C + 3) & ~3) * sizeof(float);
     if (smem > 200 * 1024 || max_tok > 65535 || njobs > 65535) return cudaErrorInvalidValue;
-    static bool configured = false;
-    if (smem > 48 * 1024 && !configured) {
-        cudaError_t e = cudaFuncSetAttribute(q8_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (smem > 48 * 1024) {
+        cudaError_t e = ensure_dynamic_smem((const void*)q8_rows_kernel, (size_t)(200 * 1024));
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     q8_rows_kernel<<<dim3(max_rows, max_tok, njobs), 128, smem, stream>>>(jobs);
     return cudaGetLastError();
@@ -202,12 +200,9 @@ cudaError_t launch_residual_postnorm(const float* residual, const float* branch,
     if (rows < 1) return cudaSuccess;
     const size_t smem = (size_t)(2 * ((n + 3) & ~3) + 8) * sizeof(float);
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
-    static bool configured = false;
-    if (smem > 48 * 1024 && !configured) {
-        cudaError_t e = cudaFuncSetAttribute(residual_postnorm_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             200 * 1024);
+    if (smem > 48 * 1024) {
+        cudaError_t e = ensure_dynamic_smem((const void*)residual_postnorm_rows_kernel, (size_t)(200 * 1024));
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     residual_postnorm_rows_kernel<<<rows, 1024, smem, stream>>>(residual, branch, weight, out, n, eps, status);
     return cudaGetLastError();
@@ -219,12 +214,9 @@ cudaError_t launch_parallel_combine(const float* residual, const float* dense, c
     if (rows < 1) return cudaSuccess;
     const size_t smem = (size_t)(n + 8) * sizeof(float);
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
-    static bool configured = false;
-    if (smem > 48 * 1024 && !configured) {
-        cudaError_t e = cudaFuncSetAttribute(parallel_combine_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             200 * 1024);
+    if (smem > 48 * 1024) {
+        cudaError_t e = ensure_dynamic_smem((const void*)parallel_combine_rows_kernel, (size_t)(200 * 1024));
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     parallel_combine_rows_kernel<<<rows, 1024, smem, stream>>>(residual, dense, routed, wd, wr, wf, scratch_a, scratch_b,
                                                                out, n, eps, scalar, status);
@@ -811,12 +803,9 @@ cudaError_t launch_router_logits(const float* W, const float* bias, const float*
     if (rows <= 32) {
         const int nr = rows < LOGIT_TB ? rows : LOGIT_TB;
         const size_t smem = (size_t)nr * (((H + 3) & ~3) + 4) * sizeof(float);
-        static bool configured = false;
-        if (smem > 48 * 1024 && !configured) {
-            cudaError_t e = cudaFuncSetAttribute(router_logits_block_kernel,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (smem > 48 * 1024) {
+            cudaError_t e = ensure_dynamic_smem((const void*)router_logits_block_kernel, (size_t)(200 * 1024));
             if (e != cudaSuccess) return e;
-            configured = true;
         }
         if (smem > 200 * 1024) return cudaErrorInvalidValue;
         dim3 grid(E, (rows + LOGIT_TB - 1) / LOGIT_TB);
@@ -827,12 +816,9 @@ cudaError_t launch_router_logits(const float* W, const float* bias, const float*
         return launch_logits_big<2, 1>(W, bias, x, logits, rows, E, H, stream);
     } else if (aligned16 && (H & 3) == 0) {
         const size_t smem = (size_t)LT_STAGES * 16 * LT_PITCH * sizeof(float);
-        static bool configured = false;
-        if (!configured) {
-            cudaError_t e = cudaFuncSetAttribute(router_logits_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 (int)smem);
+        {
+            cudaError_t e = ensure_dynamic_smem((const void*)router_logits_tile_kernel, (size_t)((int)smem));
             if (e != cudaSuccess) return e;
-            configured = true;
         }
         dim3 grid((E + 7) / 8, (rows + 7) / 8);
         router_logits_tile_kernel<<<grid, 64, smem, stream>>>(W, bias, x, logits, rows, E, H);
@@ -1123,11 +1109,9 @@ cudaError_t launch_moe_plan(const MoePlanArgs& a, cudaStream_t stream) {
         if (a.rows > 8) return cudaErrorInvalidValue;
         smem += (size_t)8 * topk_scratch_floats(a.n_experts, a.topk) * sizeof(float);
     }
-    static bool configured = false;
-    if (smem > 48 * 1024 && !configured) {
-        cudaError_t e = cudaFuncSetAttribute(moe_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    if (smem > 48 * 1024) {
+        cudaError_t e = ensure_dynamic_smem((const void*)moe_plan_kernel, (size_t)(160 * 1024));
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     if (smem > 160 * 1024) return cudaErrorInvalidValue;
     moe_plan_kernel<<<1, 1024, smem, stream>>>(a);

@@ -139,6 +139,12 @@ class MoeStack:
     def ep_disconnect(self):
         return self.lib.salt_b200_stack_ep_disconnect(self.handle)
 
+    def ep_set_poll_limit(self, polls):
+        return self.lib.salt_b200_stack_ep_set_poll_limit(self.handle, int(polls))
+
+    def ep_reset(self):
+        return self.lib.salt_b200_stack_ep_reset(self.handle)
+
     def ep_exchange(self, B, phase=3, stream=0):
         return self.lib.salt_b200_stack_ep_exchange(self.handle, B, phase, C.c_void_p(stream))
 

@@ -90,3 +90,51 @@ def test_ranks_on_separate_gpus(world):
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     assert r.stdout.count("EP_PEER_OK") == world, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_exchange_wait_runs_out_then_reset_recovers(synth):
+    """A rank pulls rows that nobody pushed: with a short poll limit the kernel gives up, reports the
+    timeout in the error word and returns (nothing hangs, the device stays usable).  After every rank
+    resets its landing region a normal push + pull is bit-exact again."""
+    import torch
+    H, M, E, K, B, world = 256, 128, 32, 4, 5, 2
+    layer = synth.make_q4_moe_layer(730, hidden=H, inter=M, n_experts=E, topk=K)
+    sm = stack_mod()
+    full = sm.MoeStack(8, H, M, E, K)
+    full.add_layer(layer)
+    ranks = []
+    for r in range(world):
+        st = sm.MoeStack(8, H, M, E, K, expert_begin=r * E // world, expert_end=(r + 1) * E // world)
+        st.add_layer(layer)
+        ranks.append(st)
+    regions = [st.ep_region()[1] for st in ranks]
+    for r, st in enumerate(ranks):
+        assert st.ep_connect(r, world, regions=regions) == 0
+        assert st.ep_set_poll_limit(2000) == 0          # about a millisecond
+    x = synth.make_tokens(731, B, H)
+    want = full.forward_host(x)
+    d_x = torch.from_numpy(x).cuda()
+    for st in ranks:
+        assert st.layer_experts(0, d_x.data_ptr(), B) == 0
+    # rank 0 waits for rank 1's rows, which were never pushed
+    assert ranks[0].ep_exchange(B, phase=ranks[0].EP_PULL) == 0
+    assert ranks[0].status() == 8                       # SB_ERR_TIMEOUT, and the call returned
+    for st in ranks:
+        assert st.ep_reset() == 0
+        assert st.ep_set_poll_limit(1 << 23) == 0
+    outs = []
+    for st in ranks:
+        assert st.layer_experts(0, d_x.data_ptr(), B) == 0
+    for st in ranks:
+        assert st.ep_exchange(B, phase=st.EP_PUSH) == 0
+    for st in ranks:
+        assert st.ep_exchange(B, phase=st.EP_PULL) == 0
+    for st in ranks:
+        out = torch.empty(B, H, dtype=torch.float32, device="cuda")
+        assert st.layer_combine(0, B, out.data_ptr(), apply_norm=False) == 0
+        outs.append(out)
+    for r, st in enumerate(ranks):
+        assert st.status() == 0
+        assert (outs[r].cpu().numpy().view(np.uint32) == want.view(np.uint32)).all(), f"rank {r} after reset"
+    for st in ranks + [full]:
+        st.close()

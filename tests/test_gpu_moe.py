@@ -444,3 +444,19 @@ def test_stack_two_layers_prefill_sized_batch_vs_oracle(orc, synth):
     want, _ = oracle_stack(orc, layers, x, threads=16)
     assert_bits_equal(y, want, "2-layer stack, 300 rows")
     st.close()
+
+
+def test_stack_wide_hidden_takes_any_shape_kernels_vs_oracle(orc, synth):
+    """hidden = 5696 is beyond what the tiled projection kernels hold in shared memory: the stack runs the
+    any-shape kernels, one grid row per token of a group.  Groups of more than four tokens must all be
+    computed (6 tokens over 4 experts, top-2: every group holds several tokens)."""
+    H, M, E, K, B = 5696, 128, 4, 2, 6
+    layers = [synth.make_q4_moe_layer(97 + i, hidden=H, inter=M, n_experts=E, topk=K) for i in range(2)]
+    x = synth.make_tokens(99, B, H)
+    st = stack_mod().MoeStack(8, H, M, E, K)
+    for layer in layers:
+        st.add_layer(layer)
+    y = st.forward_host(x)
+    want, _ = oracle_stack(orc, layers, x, threads=8)
+    assert_bits_equal(y, want, "wide hidden, any-shape kernels")
+    st.close()
