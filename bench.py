@@ -442,7 +442,7 @@ def run_b200(args):
                         "frac": achieved / peak, "peak_source": peak_source, "algorithmic_bytes_per_launch": alg,
                         "us_per_launch": gu["us_per_launch"], "mean_distinct_experts": mean_distinct,
                         "traffic": None,
-                        "traffic_note": "not measured by this run; DRAM bytes per launch are in the ncu summaries under profiles/"}
+                        "traffic_note": "not measured by this run (an ncu capture of this kernel gives the DRAM bytes per launch)"}
             if tc_mode and B * K / E >= 96:
                 # rows per expert beyond the ridge: the expert GEMMs are bound by the tensor pipe
                 flops = 2.0 * B * K * 2 * H * M

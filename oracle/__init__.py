@@ -112,6 +112,17 @@ class Oracle:
                                   1 if with_scale else 0)
         return rc, out
 
+    def bf16_matvec(self, W, R, Ccols, x, bias=None):
+        y = np.empty(R, np.float32)
+        self.lib.orc_bf16_matvec(_p(W), R, Ccols, _p(_f32(x)), _p(_f32(bias)) if bias is not None else None, _p(y))
+        return y
+
+    def bf16_matvec_serial(self, W, R, Ccols, xs):
+        xs = _f32(xs).reshape(-1, Ccols)
+        ys = np.empty((xs.shape[0], R), np.float32)
+        self.lib.orc_bf16_matvec_serial(_p(W), R, Ccols, xs.shape[0], _p(xs), _p(ys))
+        return ys
+
     def q8_matvec(self, vals, scales, biases, R, Ccols, x):
         y = np.empty(R, np.float32)
         self.lib.orc_q8_matvec(_p(vals), _p(scales), _p(biases) if biases is not None else None, R, Ccols,
@@ -314,6 +325,17 @@ class Reference:
         rc = self.lib.salt_gemma4_rmsnorm(_p(out), _p(x), _p(w), x.size, C.c_float(eps),
                                           1 if with_scale else 0)
         return rc, out
+
+    def bf16_matvec(self, W, R, Ccols, x, bias=None):
+        y = np.empty(R, np.float32)
+        self.lib.salt_bf16_matvec(_p(W), R, Ccols, _p(_f32(x)), _p(_f32(bias)) if bias is not None else None, _p(y))
+        return y
+
+    def f32_matvec(self, W, R, Ccols, x):
+        """salt_f32_matvec (src/kernels.c:98-116): the serial column chain."""
+        y = np.empty(R, np.float32)
+        self.lib.salt_f32_matvec(_p(_f32(W)), R, Ccols, _p(_f32(x)), _p(y))
+        return y
 
     def q8_matvec(self, vals, scales, biases, R, Ccols, x):
         y = np.empty(R, np.float32)

@@ -391,6 +391,47 @@ void orc_q8_matvec(const void *vals, const void *scales, const void *biases, int
     }
 }
 
+/* src/kernels.c:139-174 (salt_bf16_matvec): eight accumulators, a_j takes the columns c with c % 8 == j
+ * (product rounded, then added); y = ((a0+a2)+(a4+a6)) + ((a1+a3)+(a5+a7)), then the columns past the
+ * last multiple of 8 one by one, then the optional bias. */
+void orc_bf16_matvec(const void *W, int R, int C, const float *x, const float *bias, float *y) {
+    for (int r = 0; r < R; r++) {
+        float a[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+        size_t base = (size_t)r * (size_t)C;
+        int c = 0;
+        float s, e, o;
+        for (; c + 7 < C; c += 8)
+            for (int j = 0; j < 8; j++) {
+                float t = orc_bf16(W, base + (size_t)(c + j)) * x[c + j];
+                a[j] = a[j] + t;
+            }
+        e = (a[0] + a[2]) + (a[4] + a[6]);
+        o = (a[1] + a[3]) + (a[5] + a[7]);
+        s = e + o;
+        for (; c < C; c++) {
+            float t = orc_bf16(W, base + (size_t)c) * x[c];
+            s = s + t;
+        }
+        y[r] = s + (bias ? bias[r] : 0.0f);
+    }
+}
+
+/* models/gemma4-26b-a4b/src/gemma4_vision.c:700-717 (the portable loop behind salt_gpu_bf16_matvec_batch,
+ * the same chain as salt_f32_matvec, src/kernels.c:98-116, on the widened weights): per (token, row)
+ * sum = fl(sum + fl(w * x[c])), c ascending. */
+void orc_bf16_matvec_serial(const void *W, int R, int C, int B, const float *xs, float *ys) {
+    for (int t = 0; t < B; t++)
+        for (int r = 0; r < R; r++) {
+            float sum = 0.0f;
+            size_t base = (size_t)r * (size_t)C;
+            for (int c = 0; c < C; c++) {
+                float p = orc_bf16(W, base + (size_t)c) * xs[(size_t)t * C + c];
+                sum = sum + p;
+            }
+            ys[(size_t)t * R + r] = sum;
+        }
+}
+
 /* gemma4.c:188-213 (salt_gemma4_residual_postnorm): the branch is RMS-normalised with its
  * post-norm weight, then added to the residual: out = residual + (branch*inv)*w.
  * Non-finite inputs or outputs reject the whole call. */

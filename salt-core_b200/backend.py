@@ -144,6 +144,15 @@ class SaltGpu:
         return self.lib.salt_gpu_q4_batch(_ptr_array(vals), _ptr_array(scales), _ptr_array(biases),
                                           _ptr_array(xs), _ptr_array(ys), (C.c_void_p * n)(*ids), rj, Ccols, n)
 
+    def bf16_resource_slot(self, kind, rid, key, weights, R, Ccols):
+        return self.lib.salt_gpu_bf16_resource_slot(kind, rid, C.c_void_p(key), ptr(weights), R, Ccols)
+
+    def bf16_matvec(self, key, R, Ccols, x, y):
+        return self.lib.salt_gpu_bf16_matvec(C.c_void_p(key), R, Ccols, ptr(x), ptr(y))
+
+    def bf16_matvec_batch(self, key, R, Ccols, B, xs, ys):
+        return self.lib.salt_gpu_bf16_matvec_batch(C.c_void_p(key), R, Ccols, B, ptr(xs), ptr(ys))
+
     def q8_matvec(self, vals, scales, biases, R, Ccols, x, y):
         return self.lib.salt_gpu_q8_matvec(ptr(vals), ptr(scales), ptr(biases), R, Ccols, ptr(x), ptr(y))
 

@@ -467,7 +467,68 @@ int salt_gpu_weight_resource_slot(uint32_t kind, uint32_t id, const void* key, c
     return 0;
 }
 
-int salt_gpu_bf16_resource_slot(uint32_t, uint32_t, const void*, const uint16_t*, int, int) { return -1; }
+// BF16 matrices (router / head projections of packages that keep them in bf16; reference
+// include/salt/gpu.h:60-66, src/gpu_cuda.cu:3267-3300): registered inside a described, active resource.
+int salt_gpu_bf16_resource_slot(uint32_t kind, uint32_t id, const void* key, const uint16_t* weights, int R, int C) {
+    Backend& B = g_backend;
+    Resource* r = live_resource(kind, id);
+    uint64_t vo;
+    if (!r || !key || !weights || R < 1 || C < 8 || (C & 7) != 0) return -1;
+    const uint64_t elems = (uint64_t)(uint32_t)R * (uint64_t)(uint32_t)C;
+    if (elems > SIZE_MAX / 2u || !in_range(*r, weights, (size_t)(elems * 2u), &vo)) return -1;
+    auto it = B.tensors.find(key);
+    if (it != B.tensors.end()) {
+        const Tensor& t = it->second;
+        return (t.kind == kind && t.id == id && t.bits == 16 && t.R == R && t.C == C && t.voff == vo) ? 0 : -1;
+    }
+    Tensor t;
+    t.kind = kind; t.id = id; t.bits = 16; t.R = R; t.C = C; t.voff = vo; t.vbytes = (size_t)(elems * 2u);
+    B.tensors[key] = t;
+    return 0;
+}
+
+// Device view of a registered bf16 matrix (2-byte alignment is all its kernels need).
+static const uint16_t* bf16_view(const void* key, int R, int C) {
+    Backend& B = g_backend;
+    if (!B.ready || !key) return nullptr;
+    auto it = B.tensors.find(key);
+    if (it == B.tensors.end()) return nullptr;
+    const Tensor& t = it->second;
+    Resource* r = live_resource(t.kind, t.id);
+    if (!r || t.bits != 16 || t.R != R || t.C != C) return nullptr;
+    return (const uint16_t*)(r->dev + t.voff);
+}
+
+static int bf16_run(const void* key, int R, int C, int Bt, const float* in, float* out, bool serial) {
+    Backend& B = g_backend;
+    const uint16_t* W = bf16_view(key, R, C);
+    if (!W) {
+        if (B.ready && B.mapped_only) B.stats.mapped_only_misses++;
+        return -1;
+    }
+    const size_t nin = (size_t)Bt * C, nout = (size_t)Bt * R;
+    if (!in || !out || nin > B.stage_floats || nout > B.stage_floats) return -1;
+    if (!cuda_ok(cudaMemcpyAsync(B.d_x, in, nin * sizeof(float), cudaMemcpyHostToDevice, B.stream), "bf16 x upload"))
+        return -1;
+    const cudaError_t e = serial ? launch_bf16_batch(W, B.d_x, B.d_y, R, C, Bt, B.stream)
+                                 : launch_bf16_matvec(W, B.d_x, B.d_y, R, C, B.stream);
+    if (!cuda_ok(e, "bf16 launch")) return -1;
+    count_launches(1);
+    if (!cuda_ok(cudaMemcpyAsync(out, B.d_y, nout * sizeof(float), cudaMemcpyDeviceToHost, B.stream), "bf16 y download") ||
+        !cuda_ok(cudaStreamSynchronize(B.stream), "bf16 sync"))
+        return -1;
+    return 0;
+}
+
+int salt_gpu_bf16_matvec(const void* key, int R, int C, const float* input, float* output) {
+    return bf16_run(key, R, C, 1, input, output, false);
+}
+
+// every (token, row) keeps the serial column order of the reference's portable loop
+int salt_gpu_bf16_matvec_batch(const void* key, int R, int C, int Bt, const float* inputs, float* outputs) {
+    if (Bt < 1) return -1;
+    return bf16_run(key, R, C, Bt, inputs, outputs, true);
+}
 
 int salt_gpu_weight_resource_unbind(uint32_t kind, uint32_t id) {
     Backend& B = g_backend;

@@ -109,6 +109,11 @@ cudaError_t launch_q4_gemm_tc(bool fused, bool split, const Q4Job* jobs, int njo
                               const TcMaps& bmaps, const float* y_base, int y_cols, void* out_h, void* out_l,
                               float* out_f, int R, int rows_total, int* status, cudaStream_t stream);
 
+// ---- bf16_kernels.cu ---------------------------------------------------------
+// y[r] = W[r][:] . x in the reference's eight-accumulator order; ys[t][r] in the serial column order
+cudaError_t launch_bf16_matvec(const uint16_t* W, const float* x, float* y, int R, int C, cudaStream_t stream);
+cudaError_t launch_bf16_batch(const uint16_t* W, const float* xs, float* ys, int R, int C, int B, cudaStream_t stream);
+
 // ---- nvfp4_kernels.cu ------------------------------------------------------
 // One NVFP4 projection job: ntok rows of already dequantised activations.
 struct Fp4Job {
@@ -209,13 +214,6 @@ struct MoePlanArgs {
     int* status;
 };
 cudaError_t launch_moe_plan(const MoePlanArgs& a, cudaStream_t stream);
-
-// out[row] = sum over rank of fl(w * grouped[c2g[row*topk+rank]]) in rank order from 0
-cudaError_t launch_weighted_reduce(const float* weights, const int32_t* canonical_to_grouped, const float* grouped,
-                                   float* out, int rows, int topk, int width, int* status, cudaStream_t stream);
-// routed[g] = x[grouped_to_canonical[g] / topk]
-cudaError_t launch_routed_gather(const float* x, const int32_t* grouped_to_canonical, float* routed, int jobs,
-                                 int topk, int hidden, cudaStream_t stream);
 
 // ---- ep_exchange.cu ---------------------------------------------------------
 // Exchange of grouped expert outputs between expert-parallel ranks over peer memory.

@@ -633,15 +633,9 @@ cudaError_t launch_q4_gemm_tc(bool fused, bool split, const Q4Job* jobs, int njo
         // Blocks per (row tile, expert) along the token passes.  Measured at B = 512 / 2048 (32 / 128 tokens
         // per expert on average): the fused gate/up kernel gains 5 % / 20 % from 2 / 4 blocks (skewed routing
         // leaves experts with several hundred tokens), the down kernel loses 3-10 % to the blocks that find
-        // nothing to do.  SALT_B200_TC_SPLIT_Z overrides the rule for both.
-        static int forced = -1;
-        if (forced < 0) {
-            const char* e = getenv("SALT_B200_TC_SPLIT_Z");
-            forced = e ? atoi(e) : 0;
-            if (forced < 0 || forced > 8) forced = 0;
-        }
+        // nothing to do.
         const int avg = rows_total / njobs_max;
-        grid.z = forced ? (unsigned)forced : (fused ? (avg >= 96 ? 4u : (avg >= 24 ? 2u : 1u)) : 1u);
+        grid.z = fused ? (avg >= 96 ? 4u : (avg >= 24 ? 2u : 1u)) : 1u;
     }
     if (fused)
         return split ? launch_tc<true, true>(a, bmaps, grid, stream) : launch_tc<true, false>(a, bmaps, grid, stream);

@@ -1118,58 +1118,4 @@ cudaError_t launch_moe_plan(const MoePlanArgs& a, cudaStream_t stream) {
     return cudaGetLastError();
 }
 
-// src/tensorops.c:291-325 / src/moe_group.c:211-224: per output element a
-// serial chain over the ranks, starting from +0.
-__global__ void __launch_bounds__(256)
-weighted_reduce_kernel(const float* __restrict__ weights, const int32_t* __restrict__ c2g,
-                       const float* __restrict__ grouped, float* __restrict__ out, int topk, int width, int jobs,
-                       int* status) {
-    const int row = blockIdx.y;
-    const int d = blockIdx.x * blockDim.x + threadIdx.x;
-    if (d >= width) return;
-    float acc = 0.0f;
-    for (int r0 = 0; r0 < topk; r0 += 8) {
-        float w[8], v[8];
-        bool ok[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int canonical = row * topk + min(r0 + i, topk - 1);
-            const int g = c2g[canonical];
-            w[i] = weights[canonical];
-            ok[i] = g >= 0 && g < jobs && finite_f(w[i]);
-            v[i] = ok[i] ? grouped[(size_t)g * width + d] : 0.0f;
-            if (!ok[i] && d == 0 && r0 + i < topk) flag(status, g < 0 || g >= jobs ? SB_ERR_INDEX : SB_ERR_NONFINITE);
-        }
-#pragma unroll
-        for (int i = 0; i < 8; i++)
-            if (r0 + i < topk && ok[i]) acc = __fadd_rn(acc, __fmul_rn(w[i], v[i]));
-    }
-    out[(size_t)row * width + d] = acc;
-}
-
-cudaError_t launch_weighted_reduce(const float* weights, const int32_t* canonical_to_grouped, const float* grouped,
-                                   float* out, int rows, int topk, int width, int* status, cudaStream_t stream) {
-    if (rows < 1) return cudaSuccess;
-    dim3 grid((width + 255) / 256, rows);
-    weighted_reduce_kernel<<<grid, 256, 0, stream>>>(weights, canonical_to_grouped, grouped, out, topk, width,
-                                                     rows * topk, status);
-    return cudaGetLastError();
-}
-
-__global__ void __launch_bounds__(256)
-routed_gather_kernel(const float* __restrict__ x, const int32_t* __restrict__ g2c, float* __restrict__ routed,
-                     int topk, int hidden) {
-    const int g = blockIdx.y;
-    const int d = blockIdx.x * blockDim.x + threadIdx.x;
-    if (d < hidden) routed[(size_t)g * hidden + d] = x[(size_t)(g2c[g] / topk) * hidden + d];
-}
-
-cudaError_t launch_routed_gather(const float* x, const int32_t* grouped_to_canonical, float* routed, int jobs,
-                                 int topk, int hidden, cudaStream_t stream) {
-    if (jobs < 1) return cudaSuccess;
-    dim3 grid((hidden + 255) / 256, jobs);
-    routed_gather_kernel<<<grid, 256, 0, stream>>>(x, grouped_to_canonical, routed, topk, hidden);
-    return cudaGetLastError();
-}
-
 }  // namespace sb

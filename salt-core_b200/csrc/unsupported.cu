@@ -5,8 +5,6 @@
 
 extern "C" {
 
-int salt_gpu_bf16_matvec(const void*, int, int, const float*, float*) { return -1; }
-int salt_gpu_bf16_matvec_batch(const void*, int, int, int, const float*, float*) { return -1; }
 int salt_gpu_attention_batch(int, int, int, int, int, const SaltGpuSharedBuffer*, size_t, const SaltGpuSharedBuffer*,
                              size_t, size_t, int, int, int, int, SaltGpuSharedBuffer*, size_t, SaltGpuSharedBuffer*,
                              size_t, size_t, int) { return -1; }

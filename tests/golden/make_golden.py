@@ -62,11 +62,33 @@ def gen_cells(ref):
     np.savez_compressed(os.path.join(OUT, "q8_matvec.npz"), **q8)
 
 
+def gen_bf16(ref):
+    """BF16 matrices (reference src/kernels.c:139-174 salt_bf16_matvec; the serial batch form of
+    models/gemma4-26b-a4b/src/gemma4_vision.c:700-717 is pinned through salt_f32_matvec, the same
+    chain on the widened weights): router-sized, head-like, ragged and tiny shapes."""
+    rng = np.random.default_rng(20261126)
+    out = {"shapes": np.array([[128, 2816, 3], [16, 704, 2], [5, 200, 1], [3, 8, 2], [7, 75, 1]])}
+    for i, (R, Cc, B) in enumerate(out["shapes"]):
+        W = (rng.normal(0.0, 0.02, (int(R), int(Cc))).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+        W32 = (W.astype(np.uint32) << 16).view(np.float32)
+        bias = rng.standard_normal(int(R)).astype(np.float32)
+        xs = rng.standard_normal((int(B), int(Cc))).astype(np.float32)
+        out.update({f"c{i}_W": W, f"c{i}_bias": bias, f"c{i}_xs": xs,
+                    f"c{i}_y": np.stack([ref.bf16_matvec(W, int(R), int(Cc), xs[t]) for t in range(int(B))]),
+                    f"c{i}_y_bias": ref.bf16_matvec(W, int(R), int(Cc), xs[0], bias),
+                    f"c{i}_y_serial": np.stack([ref.f32_matvec(W32, int(R), int(Cc), xs[t]) for t in range(int(B))])})
+    np.savez_compressed(os.path.join(OUT, "bf16_matvec.npz"), **out)
+
+
 def main():
     ref = oracle.Reference()
     if len(sys.argv) > 1 and sys.argv[1] == "cells":
         gen_cells(ref)
         print("cells.npz written to", OUT)
+        return
+    if len(sys.argv) > 1 and sys.argv[1] == "bf16":
+        gen_bf16(ref)
+        print("bf16_matvec.npz written to", OUT)
         return
     rng = np.random.default_rng(20261125)
 

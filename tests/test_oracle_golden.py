@@ -64,6 +64,16 @@ def test_q8_matvec(orc):
         assert_bits_equal(y, g[f"c{i}_y"], f"q8 matvec {R}x{Cc}")
 
 
+def test_bf16_matvec(orc):
+    g = golden("bf16_matvec.npz")
+    for i, (R, Cc, B) in enumerate(g["shapes"]):
+        W, xs = g[f"c{i}_W"], g[f"c{i}_xs"]
+        for t in range(int(B)):
+            assert_bits_equal(orc.bf16_matvec(W, int(R), int(Cc), xs[t]), g[f"c{i}_y"][t], f"bf16 matvec {R}x{Cc}")
+        assert_bits_equal(orc.bf16_matvec(W, int(R), int(Cc), xs[0], g[f"c{i}_bias"]), g[f"c{i}_y_bias"], "bf16 matvec + bias")
+        assert_bits_equal(orc.bf16_matvec_serial(W, int(R), int(Cc), xs), g[f"c{i}_y_serial"], f"bf16 serial {R}x{Cc}")
+
+
 def test_residual_combine_softcap_cells(orc):
     g = golden("cells.npz")
     eps, scalar = float(g["eps"]), float(g["scalar"])
