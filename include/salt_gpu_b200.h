@@ -329,6 +329,24 @@ int salt_b200_stack_create(int max_tokens, int hidden, int inter, int n_experts,
                            int expert_end, void **stack_out);
 int salt_b200_stack_destroy(void *stack);
 int salt_b200_stack_add_q4_layer(void *stack, const SaltB200Q4LayerSpec *spec);
+/* A layer whose experts are NVFP4 (W4A4: E2M1 codes two per byte, one E4M3FN scale per 16 elements, a
+ * stored per-tensor weight divisor and an input global scale; reference src/nvfp4.c:82-130, 228-256).  The
+ * device sequence is what models/gemma4-26b-a4b/src/gemma4_text.c:8912-8945 runs from the host: quantise-
+ * dequantise the routed rows with each tensor's input global scale, gate and up projections, GeGLU,
+ * quantise-dequantise again, down projection; router, grouping and the ordered reduce are those of the
+ * affine-Q4 layers.  Expert slot in `pool`: gate codes [inter][hidden/2] | gate scales [inter][hidden/16] |
+ * up codes | up scales | down codes [hidden][inter/2] | down scales [hidden][inter/16].
+ * weight_divisors, input_globals: [n_experts][3] (gate, up, down).  hidden and inter must be multiples of 256. */
+typedef struct SaltB200Nvfp4LayerSpec {
+    int hidden, inter, n_experts, topk;
+    float eps;
+    const float *router_w, *router_scale, *per_expert_scale;
+    const void *pool;
+    size_t expert_stride;
+    const float *weight_divisors, *input_globals;
+    const float *norm_weight;       /* [hidden] or NULL */
+} SaltB200Nvfp4LayerSpec;
+int salt_b200_stack_add_nvfp4_layer(void *stack, const SaltB200Nvfp4LayerSpec *spec);
 int salt_b200_stack_workspace(void *stack, SaltB200Workspace *out);
 /* Batches of up to 4 tokens run gate/up, GeGLU and down of all selected experts in ONE launch
  * (one persistent block per SM, weights of both phases in flight from the start; the reference

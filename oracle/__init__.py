@@ -253,6 +253,41 @@ class Oracle:
         return rc, y
 
 
+def moe_layer_nvfp4(impl, layer, x, threads=1):
+    """One MoE layer with NVFP4 experts composed from `impl`'s functions (an Oracle or a Reference):
+    router input -> logits -> softmax top-k sorted by expert (models/gemma4-26b-a4b/src/gemma4.c:103-186,
+    gemma4_text.c:8541-8550); per selection the W4A4 gate and up projections, GeGLU, the W4A4 down
+    projection (src/nvfp4.c:228-256; caller gemma4_text.c:8912-8945); ordered weighted reduce in rank order
+    from +0 (src/moe_group.c:211-224).  Returns (y, selected, weights)."""
+    x = _f32(x).reshape(-1, layer.hidden)
+    B, H, M, K = x.shape[0], layer.hidden, layer.inter, layer.topk
+    y = np.zeros((B, H), np.float32)
+    sel_all = np.empty((B, K), np.int32)
+    w_all = np.empty((B, K), np.float32)
+    for t in range(B):
+        rc, rin = impl.router_input(x[t], layer.router_scale, layer.eps)
+        assert rc == 0
+        rc, sel, w = impl.router_topk(impl.router_scores(layer.router_w, None, rin), layer.per_expert_scale, K, True)
+        assert rc == 0
+        sel_all[t], w_all[t] = sel, w
+        acc = np.zeros(H, np.float32)
+        for rank in range(K):
+            e = int(sel[rank])
+            outs = []
+            for which in (0, 1):
+                codes, sc, dv, ig, R, Cc = layer.tensor(e, which)
+                rc, o = impl.nvfp4_matvec(codes, sc, dv, ig, R, Cc, x[t], threads=threads)
+                assert rc == 0
+                outs.append(o)
+            chain = (impl.map_f32("gelu_tanh", outs[0]) * outs[1]).astype(np.float32)
+            codes, sc, dv, ig, R, Cc = layer.tensor(e, 2)
+            rc, o = impl.nvfp4_matvec(codes, sc, dv, ig, R, Cc, chain, threads=threads)
+            assert rc == 0
+            acc = (acc + (np.float32(w[rank]) * o).astype(np.float32)).astype(np.float32)
+        y[t] = acc
+    return y, sel_all, w_all
+
+
 class Reference:
     """_ref/libsalt_ref.so: the reference project's own functions."""
 

@@ -124,9 +124,24 @@ struct Fp4Job {
     float* y;                // y[t*y_stride + r]
     int R, C, ntok, x_stride, y_stride;
 };
-// ig_rows[row] = input global scale of the row's tensor
+// ig_rows[row] = input global scale of the row's tensor; src_rows (optional): row r reads activation row
+// src_rows[r % src_mod] / src_div
 cudaError_t launch_nvfp4_qdq(const float* x, int rows, int C, const float* ig_rows, uint8_t* packed, uint8_t* scales,
-                             float* dequant, int* status, cudaStream_t stream);
+                             float* dequant, int* status, cudaStream_t stream, const int* src_rows = nullptr,
+                             int src_mod = 1, int src_div = 1);
+// An NVFP4 expert: gate, up, down codes / block scales, 1 / weight divisor and input global scale of each.
+struct Fp4ExpertDesc {
+    const uint8_t* codes[3];
+    const uint8_t* scales[3];
+    float wg[3], ig[3];
+};
+// Jobs of a grouped NVFP4 MoE layer (gu_jobs: [2E] gate then up; dn_jobs: [E]; groups of remote experts get
+// ntok = 0) and the per-row input global scales (ig_gu: [2J], ig_dn: [J]).
+cudaError_t launch_nvfp4_moe_plan(const int* group_offsets, int E, int expert_begin, int expert_end, int J,
+                                  const Fp4ExpertDesc* experts, int H, int M, const float* dq_gu, float* gate_out,
+                                  float* up_out, const float* dq_dn, float* grouped_out, Fp4Job* gu_jobs, Fp4Job* dn_jobs,
+                                  float* ig_gu, float* ig_dn, cudaStream_t stream);
+cudaError_t launch_geglu_rows(const float* gate, const float* up, float* chain, size_t n, cudaStream_t stream);
 cudaError_t launch_nvfp4_jobs(const Fp4Job* jobs, int njobs, int max_rows, int max_tok, int C, bool aligned,
                               cudaStream_t stream);
 

@@ -34,6 +34,9 @@ struct Layer {
     int* lit_flags = nullptr;       // [local] bit k: tensor k of the expert has a scale that needs the two-rounding form
     size_t expert_stride = 0;
     float eps = 0.0f;
+    // NVFP4 experts (W4A4: E2M1 codes + E4M3 block scales; reference src/nvfp4.c) instead of affine-Q4 ones
+    bool nvfp4 = false;
+    Fp4ExpertDesc* fp4_experts = nullptr;      // [local experts] device
     // optional dense branch and norms of the whole feed-forward block
     bool ffn = false;
     int dense_inter = 0;
@@ -60,6 +63,14 @@ struct Stack {
     float *grouped_alt = nullptr, *weights_alt = nullptr;
     int32_t* layer_counters = nullptr;         // [layers_cap][FUSED_MAX_JOBS + 1]
     int layers_cap = 0;
+    bool any_nvfp4 = false;
+    // workspace of NVFP4 layers (allocated with the first one): quantise-dequantised activations of the
+    // gate / up inputs [2J][H] and of the down inputs [J][M], the codes and block scales the quantisation
+    // also produces, gate / up outputs [J][M], per-row input global scales, projection jobs
+    float *fp4_dq_gu = nullptr, *fp4_dq_dn = nullptr, *fp4_gate = nullptr, *fp4_up = nullptr;
+    float *fp4_ig_gu = nullptr, *fp4_ig_dn = nullptr;
+    uint8_t *fp4_packed = nullptr, *fp4_scales = nullptr;
+    Fp4Job *fp4_gu_jobs = nullptr, *fp4_dn_jobs = nullptr;
     bool fused_decode = true;                  // batches of up to FUSED_MAX_TOKENS tokens take the one-launch expert kernel
     void *xh = nullptr, *xl = nullptr, *chain_h = nullptr, *chain_l = nullptr;   // fp16 operands (hi, lo) of the tensor-core path
     bool tc_ready = false;                     // tensor maps built (needs hidden, inter multiples of 64)
@@ -105,7 +116,7 @@ struct Timed {
 static void free_stack(Stack* s) {
     for (auto& l : s->layers) {
         cudaFree(l.router_w); cudaFree(l.router_scale); cudaFree(l.per_expert_scale);
-        cudaFree(l.norm_weight); cudaFree(l.pool); cudaFree(l.sb_tables); cudaFree(l.lit_flags);
+        cudaFree(l.norm_weight); cudaFree(l.pool); cudaFree(l.sb_tables); cudaFree(l.lit_flags); cudaFree(l.fp4_experts);
         cudaFree(l.pre_ffn_norm); cudaFree(l.pre_ffn_norm_2); cudaFree(l.post_ffn_norm_1);
         cudaFree(l.post_ffn_norm_2); cudaFree(l.post_ffn_norm); cudaFree(l.dense); cudaFree(l.dense_jobs);
     }
@@ -118,6 +129,8 @@ static void free_stack(Stack* s) {
     cudaFree(s->counters); cudaFree(s->status); cudaFree(s->gateup_jobs); cudaFree(s->down_jobs);
     cudaFree(s->fused_jobs); cudaFree(s->fused_done);
     cudaFree(s->grouped_alt); cudaFree(s->weights_alt); cudaFree(s->layer_counters);
+    cudaFree(s->fp4_dq_gu); cudaFree(s->fp4_dq_dn); cudaFree(s->fp4_gate); cudaFree(s->fp4_up); cudaFree(s->fp4_ig_gu);
+    cudaFree(s->fp4_ig_dn); cudaFree(s->fp4_packed); cudaFree(s->fp4_scales); cudaFree(s->fp4_gu_jobs); cudaFree(s->fp4_dn_jobs);
     cudaFree(s->xh); cudaFree(s->xl); cudaFree(s->chain_h); cudaFree(s->chain_l);
     if (s->h_in) cudaFreeHost(s->h_in);
     if (s->h_out) cudaFreeHost(s->h_out);
@@ -227,6 +240,58 @@ int salt_b200_stack_add_q4_layer(void* stack, const SaltB200Q4LayerSpec* spec) {
     return (int)s->layers.size() - 1;
 }
 
+int salt_b200_stack_add_nvfp4_layer(void* stack, const SaltB200Nvfp4LayerSpec* spec) {
+    Stack* s = (Stack*)stack;
+    if (!s || !spec || spec->hidden != s->hidden || spec->inter != s->inter || spec->n_experts != s->n_experts ||
+        spec->topk != s->topk || !spec->router_w || !spec->router_scale || !spec->per_expert_scale || !spec->pool ||
+        !spec->weight_divisors || !spec->input_globals || (s->hidden % 256) || (s->inter % 256))
+        return -1;
+    const size_t elems = (size_t)s->hidden * s->inter;
+    const size_t code_bytes = elems / 2, scale_bytes = elems / 16, tensor_bytes = code_bytes + scale_bytes;
+    if (spec->expert_stride < 3 * tensor_bytes || (spec->expert_stride % 16) != 0) return -1;
+    const size_t T = (size_t)s->max_tokens, J = T * (size_t)s->topk;
+    const int E = s->n_experts;
+    if (!s->fp4_dq_gu &&
+        !(dev_alloc(&s->fp4_dq_gu, 2 * J * s->hidden) && dev_alloc(&s->fp4_dq_dn, J * s->inter) &&
+          dev_alloc(&s->fp4_gate, J * s->inter) && dev_alloc(&s->fp4_up, J * s->inter) && dev_alloc(&s->fp4_ig_gu, 2 * J) &&
+          dev_alloc(&s->fp4_ig_dn, J) && dev_alloc(&s->fp4_packed, 2 * J * (size_t)s->hidden / 2) &&
+          dev_alloc(&s->fp4_scales, 2 * J * (size_t)s->hidden / 16) && dev_alloc(&s->fp4_gu_jobs, (size_t)2 * E) &&
+          dev_alloc(&s->fp4_dn_jobs, (size_t)E)))
+        return -1;
+    Layer l;
+    l.eps = spec->eps;
+    l.expert_stride = spec->expert_stride;
+    l.nvfp4 = true;
+    const size_t local = (size_t)(s->expert_end - s->expert_begin);
+    const uint8_t* src = (const uint8_t*)spec->pool + (size_t)s->expert_begin * spec->expert_stride;
+    bool ok = upload(&l.router_w, spec->router_w, (size_t)E * s->hidden) &&
+              upload(&l.router_scale, spec->router_scale, (size_t)s->hidden) &&
+              upload(&l.per_expert_scale, spec->per_expert_scale, (size_t)E) &&
+              upload(&l.pool, src, local * spec->expert_stride) &&
+              (!spec->norm_weight || upload(&l.norm_weight, spec->norm_weight, (size_t)s->hidden));
+    std::vector<Fp4ExpertDesc> desc(local);
+    for (size_t i = 0; ok && i < local; i++) {
+        const size_t e = (size_t)s->expert_begin + i;
+        for (int k = 0; k < 3; k++) {
+            const float div = spec->weight_divisors[e * 3 + k], ig = spec->input_globals[e * 3 + k];
+            if (!std::isfinite(div) || div == 0.0f || !std::isfinite(ig) || !(ig > 0.0f)) ok = false;
+            desc[i].codes[k] = l.pool + i * spec->expert_stride + (size_t)k * tensor_bytes;
+            desc[i].scales[k] = desc[i].codes[k] + code_bytes;
+            desc[i].wg[k] = 1.0f / div;              // fl(1 / stored divisor), as reference src/nvfp4.c:228-256 forms it
+            desc[i].ig[k] = ig;
+        }
+    }
+    ok = ok && upload(&l.fp4_experts, desc.data(), local);
+    if (!ok) {
+        cudaFree(l.router_w); cudaFree(l.router_scale); cudaFree(l.per_expert_scale); cudaFree(l.pool);
+        cudaFree(l.norm_weight); cudaFree(l.fp4_experts);
+        return -1;
+    }
+    s->any_nvfp4 = true;
+    s->layers.push_back(l);
+    return (int)s->layers.size() - 1;
+}
+
 int salt_b200_stack_set_fused_decode(void* stack, int enable) {
     Stack* s = (Stack*)stack;
     if (!s) return -1;
@@ -316,7 +381,7 @@ static int layer_experts_impl(Stack* s, int layer, const float* d_router_src, co
     const int local = s->expert_end - s->expert_begin;
     const int njobs_max = jobs < local ? jobs : local;
     // decode batches: gate/up, GeGLU and down of all selected experts in one launch
-    const bool fused = s->fused_decode && !(flags & (SB_EXPERTS_TENSOR_CORE | SB_EXPERTS_TENSOR_CORE_SINGLE |
+    const bool fused = !l.nvfp4 && s->fused_decode && !(flags & (SB_EXPERTS_TENSOR_CORE | SB_EXPERTS_TENSOR_CORE_SINGLE |
                                                      SB_EXPERTS_TWO_LAUNCHES)) &&
                        B <= FUSED_MAX_TOKENS && njobs_max <= FUSED_MAX_JOBS &&
                        ((((uintptr_t)d_x) | ((uintptr_t)l.pool) | l.expert_stride) & 15) == 0 &&
@@ -329,6 +394,23 @@ static int layer_experts_impl(Stack* s, int layer, const float* d_router_src, co
     {
         Timed t(s, KC_PLAN, st);
         if (!cuda_ok(launch_moe_plan(a, st), "plan")) return -1;
+    }
+    if (l.nvfp4) {
+        if (flags & (SB_EXPERTS_TENSOR_CORE | SB_EXPERTS_TENSOR_CORE_SINGLE)) return -1;
+        Timed t(s, KC_GATE_UP, st);
+        if (!cuda_ok(launch_nvfp4_moe_plan(s->group_offsets, E, s->expert_begin, s->expert_end, jobs, l.fp4_experts, H, M,
+                                           s->fp4_dq_gu, s->fp4_gate, s->fp4_up, s->fp4_dq_dn, s->grouped_out,
+                                           s->fp4_gu_jobs, s->fp4_dn_jobs, s->fp4_ig_gu, s->fp4_ig_dn, st), "nvfp4 plan") ||
+            !cuda_ok(launch_nvfp4_qdq(d_x, 2 * jobs, H, s->fp4_ig_gu, s->fp4_packed, s->fp4_scales, s->fp4_dq_gu,
+                                      s->status, st, s->g2c, jobs, K), "nvfp4 qdq x") ||
+            !cuda_ok(launch_nvfp4_jobs(s->fp4_gu_jobs, 2 * E, M, B, H, true, st), "nvfp4 gate/up") ||
+            !cuda_ok(launch_geglu_rows(s->fp4_gate, s->fp4_up, s->chain, (size_t)jobs * M, st), "geglu") ||
+            !cuda_ok(launch_nvfp4_qdq(s->chain, jobs, M, s->fp4_ig_dn, s->fp4_packed, s->fp4_scales, s->fp4_dq_dn,
+                                      s->status, st), "nvfp4 qdq chain") ||
+            !cuda_ok(launch_nvfp4_jobs(s->fp4_dn_jobs, E, H, B, M, true, st), "nvfp4 down"))
+            return -1;
+        count_launches(7);
+        return 0;
     }
     if (fused) {
         FusedArgs f;
@@ -531,7 +613,7 @@ int salt_b200_stack_attach_ffn_block(void* stack, int layer, const SaltB200FfnBl
         !spec->post_ffn_norm_2 || !spec->post_ffn_norm || !std::isfinite(spec->layer_scalar))
         return -1;
     Layer& l = s->layers[(size_t)layer];
-    if (l.ffn) return -1;
+    if (l.ffn || l.nvfp4) return -1;
     const int H = s->hidden, D = spec->dense_inter;
     const size_t T = (size_t)s->max_tokens;
     if (D > s->dense_cap) {
@@ -630,7 +712,7 @@ __global__ void profile_head_start_kernel(long long cycles) {
 // top-k, experts), then one launch for the last reduce.
 static bool decode_layers_apply(Stack* s, int B) {
     const int local = s->expert_end - s->expert_begin;
-    return s->fused_decode && B == 1 && s->ep_world == 0 && s->topk <= FUSED_MAX_JOBS &&
+    return s->fused_decode && !s->any_nvfp4 && B == 1 && s->ep_world == 0 && s->topk <= FUSED_MAX_JOBS &&
            q4_layer_decode_plan(s->hidden, s->inter, s->n_experts, s->topk, s->topk < local ? s->topk : local, nullptr);
 }
 

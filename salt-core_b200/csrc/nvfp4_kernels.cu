@@ -58,16 +58,19 @@ __device__ __forceinline__ float e2m1_decode(uint32_t code) {
 // One thread per block of 16 activations.  ig_rows[row] is the row's input
 // global scale.  Non-finite activations set the status word (the reference
 // function returns -1).
+// src_rows != null: row r of the call reads activation row src_rows[r % src_mod] / src_div (the grouped
+// order of a MoE layer: several quantisations of the same token row with different global scales).
 __global__ void __launch_bounds__(256)
 nvfp4_qdq_kernel(const float* __restrict__ x, int rows, int C, const float* __restrict__ ig_rows,
                  uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, float* __restrict__ dequant,
-                 int* status) {
+                 int* status, const int* __restrict__ src_rows, int src_mod, int src_div) {
     const int bpr = C >> 4;
     const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (gid >= (long long)rows * bpr) return;
     const int row = (int)(gid / bpr), blk = (int)(gid - (long long)row * bpr);
     const float ig = ig_rows[row];
-    const float4* in4 = (const float4*)(x + (size_t)row * C + blk * 16);
+    const int in_row = src_rows ? src_rows[row % src_mod] / src_div : row;
+    const float4* in4 = (const float4*)(x + (size_t)in_row * C + blk * 16);
     float v[16];
 #pragma unroll
     for (int i = 0; i < 4; i++) {
@@ -112,11 +115,13 @@ nvfp4_qdq_kernel(const float* __restrict__ x, int rows, int C, const float* __re
 }
 
 cudaError_t launch_nvfp4_qdq(const float* x, int rows, int C, const float* ig_rows, uint8_t* packed, uint8_t* scales,
-                             float* dequant, int* status, cudaStream_t stream) {
+                             float* dequant, int* status, cudaStream_t stream, const int* src_rows, int src_mod,
+                             int src_div) {
     if (rows < 1) return cudaSuccess;
+    if (src_rows && (src_mod < 1 || src_div < 1)) return cudaErrorInvalidValue;
     const long long blocks16 = (long long)rows * (C >> 4);
     nvfp4_qdq_kernel<<<(unsigned)((blocks16 + 255) / 256), 256, 0, stream>>>(x, rows, C, ig_rows, packed, scales,
-                                                                           dequant, status);
+                                                                           dequant, status, src_rows, src_mod, src_div);
     return cudaGetLastError();
 }
 
@@ -270,6 +275,63 @@ __global__ void __launch_bounds__(128) nvfp4_generic_kernel(const Fp4Job* __rest
     const float L1 = __shfl_sync(0xffffffffu, L, 1);
     const float L3 = __shfl_sync(0xffffffffu, L, 3);
     if (lane == 0) jb.y[(size_t)tok * jb.y_stride + r] = __fadd_rn(__fadd_rn(L, L2), __fadd_rn(L1, L3));
+}
+
+// ---- a MoE layer of NVFP4 experts (reference caller: models/gemma4-26b-a4b/src/gemma4_text.c:8912-8945,
+// two projection batches with the GeGLU between them) ------------------------------------------------
+// One thread per expert: the projection jobs of its token group and the input global scale of every
+// grouped row (gate rows [0, J), up rows [J, 2J) of the gathered activations; down rows [0, J)).
+__global__ void __launch_bounds__(128)
+nvfp4_moe_plan_kernel(const int* __restrict__ group_offsets, int E, int expert_begin, int expert_end, int J,
+                      const Fp4ExpertDesc* __restrict__ experts, int H, int M, const float* dq_gu, float* gate_out,
+                      float* up_out, const float* dq_dn, float* grouped_out, Fp4Job* gu_jobs, Fp4Job* dn_jobs,
+                      float* ig_gu, float* ig_dn) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= E) return;
+    const int g0 = group_offsets[e], cnt = group_offsets[e + 1] - g0;
+    const bool local = e >= expert_begin && e < expert_end;
+    Fp4ExpertDesc d;
+    if (local) d = experts[e - expert_begin];
+    Fp4Job j;
+    j.R = M; j.C = H; j.ntok = local ? cnt : 0; j.x_stride = H; j.y_stride = M;
+    j.codes = local ? d.codes[0] : nullptr; j.scales = local ? d.scales[0] : nullptr; j.wg = local ? d.wg[0] : 0.0f;
+    j.x = dq_gu + (size_t)g0 * H; j.y = gate_out + (size_t)g0 * M;
+    gu_jobs[e] = j;
+    j.codes = local ? d.codes[1] : nullptr; j.scales = local ? d.scales[1] : nullptr; j.wg = local ? d.wg[1] : 0.0f;
+    j.x = dq_gu + (size_t)(J + g0) * H; j.y = up_out + (size_t)g0 * M;
+    gu_jobs[E + e] = j;
+    j.R = H; j.C = M; j.x_stride = M; j.y_stride = H;
+    j.codes = local ? d.codes[2] : nullptr; j.scales = local ? d.scales[2] : nullptr; j.wg = local ? d.wg[2] : 0.0f;
+    j.x = dq_dn + (size_t)g0 * M; j.y = grouped_out + (size_t)g0 * H;
+    dn_jobs[e] = j;
+    for (int t = 0; t < cnt; t++) {                   // rows of remote experts are quantised with a neutral scale and unused
+        ig_gu[g0 + t] = local ? d.ig[0] : 1.0f;
+        ig_gu[J + g0 + t] = local ? d.ig[1] : 1.0f;
+        ig_dn[g0 + t] = local ? d.ig[2] : 1.0f;
+    }
+}
+
+// chain = gelu_tanh(gate) * up (reference gemma4.c:80-83 and the product of gemma4_text.c:8927-8930)
+__global__ void __launch_bounds__(256)
+geglu_rows_kernel(const float* __restrict__ gate, const float* __restrict__ up, float* __restrict__ chain, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) chain[i] = __fmul_rn(gelu_tanh_exact(gate[i]), up[i]);
+}
+
+cudaError_t launch_nvfp4_moe_plan(const int* group_offsets, int E, int expert_begin, int expert_end, int J,
+                                  const Fp4ExpertDesc* experts, int H, int M, const float* dq_gu, float* gate_out,
+                                  float* up_out, const float* dq_dn, float* grouped_out, Fp4Job* gu_jobs, Fp4Job* dn_jobs,
+                                  float* ig_gu, float* ig_dn, cudaStream_t stream) {
+    nvfp4_moe_plan_kernel<<<(E + 127) / 128, 128, 0, stream>>>(group_offsets, E, expert_begin, expert_end, J, experts, H, M,
+                                                              dq_gu, gate_out, up_out, dq_dn, grouped_out, gu_jobs, dn_jobs,
+                                                              ig_gu, ig_dn);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_geglu_rows(const float* gate, const float* up, float* chain, size_t n, cudaStream_t stream) {
+    if (n == 0) return cudaSuccess;
+    geglu_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(gate, up, chain, n);
+    return cudaGetLastError();
 }
 
 static size_t fp4_smem(int C, int tt) {

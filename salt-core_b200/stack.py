@@ -16,6 +16,13 @@ class Q4LayerSpec(C.Structure):
                 ("norm_weight", C.c_void_p)]
 
 
+class Nvfp4LayerSpec(C.Structure):
+    _fields_ = [("hidden", C.c_int), ("inter", C.c_int), ("n_experts", C.c_int), ("topk", C.c_int),
+                ("eps", C.c_float), ("router_w", C.c_void_p), ("router_scale", C.c_void_p),
+                ("per_expert_scale", C.c_void_p), ("pool", C.c_void_p), ("expert_stride", C.c_size_t),
+                ("weight_divisors", C.c_void_p), ("input_globals", C.c_void_p), ("norm_weight", C.c_void_p)]
+
+
 class FfnBlockSpec(C.Structure):
     _fields_ = [("dense_inter", C.c_int), ("dense_gate", C.c_void_p), ("dense_up", C.c_void_p),
                 ("dense_down", C.c_void_p), ("pre_ffn_norm", C.c_void_p), ("pre_ffn_norm_2", C.c_void_p),
@@ -57,6 +64,20 @@ class MoeStack:
         idx = self.lib.salt_b200_stack_add_q4_layer(self.handle, C.byref(spec))
         if idx < 0:
             raise RuntimeError("salt_b200_stack_add_q4_layer failed")
+        self.n_layers = idx + 1
+        return idx
+
+    def add_nvfp4_layer(self, layer, with_norm=True):
+        """layer: synth.Nvfp4MoeLayer (host arrays are copied to HBM)."""
+        nw = layer.norm_weight if with_norm else None
+        spec = Nvfp4LayerSpec(layer.hidden, layer.inter, layer.n_experts, layer.topk, layer.eps,
+                              layer.router_w.ctypes.data, layer.router_scale.ctypes.data,
+                              layer.per_expert_scale.ctypes.data, layer.pool.ctypes.data, layer.expert_stride,
+                              layer.weight_divisors.ctypes.data, layer.input_globals.ctypes.data,
+                              nw.ctypes.data if nw is not None else None)
+        idx = self.lib.salt_b200_stack_add_nvfp4_layer(self.handle, C.byref(spec))
+        if idx < 0:
+            raise RuntimeError("salt_b200_stack_add_nvfp4_layer failed")
         self.n_layers = idx + 1
         return idx
 

@@ -218,3 +218,67 @@ def make_nvfp4(rng: np.random.Generator, R: int, C: int, std=0.02):
     codes = e2m1_encode(t).reshape(R, C)
     packed = (codes[:, 0::2] | (codes[:, 1::2] << 4)).astype(np.uint8)
     return np.ascontiguousarray(packed), np.ascontiguousarray(sc), np.float32(divisor)
+
+
+@dataclass
+class Nvfp4MoeLayer:
+    """A MoE layer whose experts are NVFP4 (reference src/nvfp4.c).  Expert slot in ``pool``: gate codes |
+    gate scales | up codes | up scales | down codes | down scales."""
+    hidden: int
+    inter: int
+    n_experts: int
+    topk: int
+    eps: float
+    router_w: np.ndarray
+    router_scale: np.ndarray
+    per_expert_scale: np.ndarray
+    pool: np.ndarray                # uint8
+    expert_stride: int
+    weight_divisors: np.ndarray     # float32 [n_experts][3] (gate, up, down)
+    input_globals: np.ndarray       # float32 [n_experts][3]
+    norm_weight: np.ndarray
+
+    def tensor(self, e: int, which: int):
+        """(codes uint8 [R][C/2], scales uint8 [R][C/16], divisor, input_global, R, C) of expert e's tensor."""
+        R, C = (self.inter, self.hidden) if which < 2 else (self.hidden, self.inter)
+        cb, sb = R * C // 2, R * C // 16
+        base = e * self.expert_stride + which * (cb + sb)
+        return (self.pool[base:base + cb].reshape(R, C // 2), self.pool[base + cb:base + cb + sb].reshape(R, C // 16),
+                float(self.weight_divisors[e, which]), float(self.input_globals[e, which]), R, C)
+
+
+def make_nvfp4_moe_layer(seed: int, hidden=5120, inter=1536, n_experts=64, topk=4, eps=1e-6, router_std=0.02,
+                         input_global=64.0, distinct=None) -> Nvfp4MoeLayer:
+    """NVFP4 experts whose dequantised weights are ~N(0, 0.02): ``distinct`` experts (default: all, at most 4
+    for layers of more than 16 experts) are quantised from their own N(0, 0.02) matrices with the reference's
+    encoders; the others repeat them with the rows rotated by the expert index, which keeps the distribution
+    and makes every expert a different matrix at a fraction of the generation time."""
+    rng = np.random.default_rng(seed)
+    if distinct is None:
+        distinct = n_experts if n_experts <= 16 else 4
+    elems = hidden * inter
+    tb = elems // 2 + elems // 16
+    stride = 3 * tb
+    pool = np.empty(n_experts * stride, np.uint8)
+    div = np.empty((n_experts, 3), np.float32)
+    ig = np.full((n_experts, 3), input_global, np.float32)
+    base = []
+    for e in range(n_experts):
+        for which in range(3):
+            R, C = (inter, hidden) if which < 2 else (hidden, inter)
+            if e < distinct:
+                packed, sc, d = make_nvfp4(rng, R, C)
+                base.append((packed, sc, d))
+            else:
+                packed, sc, d = base[(e % distinct) * 3 + which]
+                packed, sc = np.roll(packed, e, axis=0), np.roll(sc, e, axis=0)
+            off = e * stride + which * tb
+            pool[off:off + R * C // 2] = packed.reshape(-1)
+            pool[off + R * C // 2:off + tb] = sc.reshape(-1)
+            div[e, which] = d
+    return Nvfp4MoeLayer(
+        hidden, inter, n_experts, topk, eps,
+        router_w=(rng.standard_normal((n_experts, hidden)) * router_std).astype(np.float32),
+        router_scale=np.ones(hidden, np.float32), per_expert_scale=np.ones(n_experts, np.float32),
+        pool=pool, expert_stride=stride, weight_divisors=div, input_globals=ig,
+        norm_weight=(1.0 + 0.1 * rng.standard_normal(hidden)).astype(np.float32))

@@ -80,8 +80,22 @@ def gen_bf16(ref):
     np.savez_compressed(os.path.join(OUT, "bf16_matvec.npz"), **out)
 
 
+def gen_nvfp4_layer(ref):
+    """A small MoE layer with NVFP4 experts through the reference's own functions."""
+    lseed, xseed, B, H, M, E, K = 4401, 4402, 3, 512, 256, 8, 2
+    layer = synth.make_nvfp4_moe_layer(lseed, hidden=H, inter=M, n_experts=E, topk=K)
+    x = synth.make_tokens(xseed, B, H)
+    y, sel, w = oracle.moe_layer_nvfp4(ref, layer, x)
+    np.savez_compressed(os.path.join(OUT, "moe_layer_nvfp4_small.npz"), meta=np.array([lseed, xseed, B, H, M, E, K]),
+                        y=y, sel=sel, w=w)
+
+
 def main():
     ref = oracle.Reference()
+    if len(sys.argv) > 1 and sys.argv[1] == "nvfp4_layer":
+        gen_nvfp4_layer(ref)
+        print("moe_layer_nvfp4_small.npz written to", OUT)
+        return
     if len(sys.argv) > 1 and sys.argv[1] == "cells":
         gen_cells(ref)
         print("cells.npz written to", OUT)

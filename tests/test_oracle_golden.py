@@ -64,6 +64,17 @@ def test_q8_matvec(orc):
         assert_bits_equal(y, g[f"c{i}_y"], f"q8 matvec {R}x{Cc}")
 
 
+def test_moe_layer_nvfp4_small(orc, synth):
+    import oracle
+    g = golden("moe_layer_nvfp4_small.npz")
+    lseed, xseed, B, H, M, E, K = (int(v) for v in g["meta"])
+    layer = synth.make_nvfp4_moe_layer(lseed, hidden=H, inter=M, n_experts=E, topk=K)
+    y, sel, w = oracle.moe_layer_nvfp4(orc, layer, synth.make_tokens(xseed, B, H))
+    assert_bits_equal(sel, g["sel"], "nvfp4 layer selected")
+    assert_bits_equal(w, g["w"], "nvfp4 layer weights")
+    assert_bits_equal(y, g["y"], "nvfp4 layer output")
+
+
 def test_bf16_matvec(orc):
     g = golden("bf16_matvec.npz")
     for i, (R, Cc, B) in enumerate(g["shapes"]):
