@@ -46,8 +46,11 @@ def parse():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=1, help="decode tokens per GPU")
-    ap.add_argument("--layers", type=int, default=30)
+    ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--format", default="q4", choices=["q4", "nvfp4"],
+                    help="q4: the headline workload (cfg 2 layers); nvfp4: cfg 4 layers (64 NVFP4 experts, hidden 5120, "
+                         "intermediate 1536, top-4), 8 layers unless --layers is given")
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="budget of the CPU baseline sample")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-extra", action="store_true",
@@ -58,11 +61,25 @@ def parse():
     ap.add_argument("--prefill", default=None, choices=["exact", "single", "split"],
                     help="run the layers one by one with the expert projections on the exact kernels, or on the "
                          "tensor cores with operands rounded to fp16 once (single) or carried as hi+lo halves (split)")
-    return ap.parse_args()
+    args = ap.parse_args()
+    if args.layers is None:
+        args.layers = 30 if args.format == "q4" else 8
+    if args.format == "nvfp4":
+        # cfg 4 geometry; one NVFP4 tensor = codes + E4M3 block scales (+ two fp32 scalars)
+        globals().update(H=5120, M=1536, E=64, K=4, TENSOR_BYTES=5120 * 1536 // 2 + 5120 * 1536 // 16 + 8,
+                         METRIC="nvfp4_moe_ffn_decode_tokens_per_s")
+    return args
 
 
 def workload_config(args, world):
     kind = "decode" if not args.prefill else f"prefill ({args.prefill} expert projections)"
+    if args.format == "nvfp4":
+        return {"workload": f"cfg4 MoE-FFN layer {kind} (H5120 E64 top4 M1536, NVFP4 W4A4 experts: E2M1 codes, E4M3 "
+                            f"block scales, fp32 router), run as a {args.layers}-layer stack with RMSNorm between layers",
+                "batch_per_gpu": args.batch, "global_batch": args.batch * world, "layers": args.layers,
+                "parallelism": f"ep{world}" if world > 1 else "single",
+                "l2": f"inputs larger than L2 ({args.layers} x 849 MB of expert weights, 53 MB of them selected per "
+                      "layer at B=1)"}
     return {"workload": f"cfg2 MoE-FFN layer {kind} (H2816 E128 top8 M704, affine-Q4 g64, fp32 router), "
                         "run as the cfg5 30-layer stack with RMSNorm between layers",
             "batch_per_gpu": args.batch, "global_batch": args.batch * world, "layers": args.layers,
@@ -117,7 +134,22 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def generate_layers(synth, n_layers, keep_host, consume):
+def make_layer(synth, fmt, seed):
+    return synth.make_q4_moe_layer_bulk(seed) if fmt == "q4" else synth.make_nvfp4_moe_layer(seed)
+
+
+def cpu_layer(drv, orc, fmt, layer, x, threads):
+    """One layer on the CPU checker: the compiled reference functions when they were built, else the port."""
+    import oracle
+    if fmt == "nvfp4":
+        impl = oracle.Reference() if oracle.Reference.available() else orc
+        return oracle.moe_layer_nvfp4(impl, layer, x, threads=threads)[0]
+    if drv is not None:
+        return drv.moe_layer_q4(layer, x)[0]
+    return orc.moe_layer_q4(layer, x, threads=threads)[0]
+
+
+def generate_layers(synth, n_layers, keep_host, consume, fmt="q4"):
     """Generate the stack's layers on a thread pool and hand each to `consume`
     (upload) in order; returns the first `keep_host` layers for the CPU baseline."""
     kept = []
@@ -127,7 +159,7 @@ def generate_layers(synth, n_layers, keep_host, consume):
         nxt = 0
         for i in range(n_layers):
             while len(futs) < window and nxt < n_layers:
-                futs.append(pool.submit(synth.make_q4_moe_layer_bulk, 5000 + nxt))
+                futs.append(pool.submit(make_layer, synth, fmt, 5000 + nxt))
                 nxt += 1
             layer = futs.pop(0).result()
             consume(i, layer)
@@ -136,13 +168,20 @@ def generate_layers(synth, n_layers, keep_host, consume):
     return kept
 
 
-def cpu_baseline(layers, B, seconds, threads):
+def cpu_baseline(layers, B, seconds, threads, fmt="q4"):
     """The reference's own CPU decode path (oracle/_ref, all host cores) on a bounded
     sample: the host-kept layers are cycled for about `seconds`."""
     import oracle
     synth = importlib.import_module("salt-core_b200.synth")
     x = synth.make_tokens(77, B, H)
-    if oracle.RefDriver.available():
+    if fmt == "nvfp4":
+        # the reference's NVFP4 CPU path takes about a second per token and layer: a bounded sample of tokens
+        kind = "reference" if oracle.Reference.available() else "port"
+        orc, used = oracle.Oracle(), threads
+        x = x[:max(1, min(B, int(seconds / 4)))]
+        B = x.shape[0]
+        run = lambda layer: cpu_layer(None, orc, fmt, layer, x, threads)
+    elif oracle.RefDriver.available():
         drv, kind = oracle.RefDriver(threads), "reference"
         run = lambda layer: drv.moe_layer_q4(layer, x)
         used = drv.threads
@@ -160,16 +199,26 @@ def cpu_baseline(layers, B, seconds, threads):
             break
     return {"value": B * n / el, "unit": UNIT, "cores": used, "kind": kind,
             "sample": f"{n} single-layer passes at B={B} cycling {len(layers)} distinct layers "
-                      f"({el:.1f} s); reference functions on a persistent pthread pool",
+                      f"({el:.1f} s); reference functions on " +
+                      ("a persistent pthread pool" if fmt == "q4" else "the reference's own row threads, one projection at a time"),
             "ms_per_layer": 1e3 * el / n}
 
 
-def cpu_parity(layers, x, y_gpu, threads):
+def cpu_parity(layers, x, y_gpu, threads, fmt="q4"):
     """Part of the CPU-baseline leg: the same layers on the CPU checker (the compiled reference where it
     was built, else the port), compared with the GPU result bit for bit.  Not timed."""
     import oracle
     cur = np.ascontiguousarray(x, np.float32)
-    if oracle.RefDriver.available():
+    if fmt == "nvfp4":
+        # tokens are independent: the first two of the batch bound the CPU time
+        cur, y_gpu = cur[:2], y_gpu[:2]
+        orc = oracle.Oracle()
+        kind = "reference functions (oracle/_ref)" if oracle.Reference.available() else "CPU port (oracle/salt_oracle.c)"
+        for i, layer in enumerate(layers):
+            cur = cpu_layer(None, orc, fmt, layer, cur, threads)
+            if i + 1 < len(layers):
+                cur = np.stack([orc.rmsnorm(cur[t], layer.norm_weight, layer.eps, True)[1] for t in range(cur.shape[0])])
+    elif oracle.RefDriver.available():
         drv, kind = oracle.RefDriver(threads), "reference functions (oracle/_ref)"
         for i, layer in enumerate(layers):
             cur, _, _ = drv.moe_layer_q4(layer, cur)
@@ -182,7 +231,8 @@ def cpu_parity(layers, x, y_gpu, threads):
             if i + 1 < len(layers):
                 cur = np.stack([orc.rmsnorm(cur[t], layer.norm_weight, layer.eps, True)[1] for t in range(cur.shape[0])])
     same = bool((np.ascontiguousarray(cur).view(np.uint32) == np.ascontiguousarray(y_gpu).view(np.uint32)).all())
-    return {"vs": f"{kind}, first {len(layers)} layers of the stack at B={x.shape[0]}", "bit_identical": same}
+    return {"vs": f"{kind}, first {len(layers)} layers of the stack, {cur.shape[0]} of the {x.shape[0]} tokens",
+            "bit_identical": same}
 
 
 def run_reference(args):
@@ -192,12 +242,22 @@ def run_reference(args):
     synth = importlib.import_module("salt-core_b200.synth")
     threads = os.cpu_count() or 1
     n_host = min(3, args.layers)
-    layers = [synth.make_q4_moe_layer_bulk(5000 + i) for i in range(n_host)]
+    layers = [make_layer(synth, args.format, 5000 + i) for i in range(n_host)]
     world = max(1, args.gpus)
     B = args.batch * world
     import oracle
     x = synth.make_tokens(77, B, H)
-    if oracle.RefDriver.available():
+    if args.format == "nvfp4":
+        orc = oracle.Oracle()
+        kind, used = ("reference" if oracle.Reference.available() else "port"), threads
+        x = x[:max(1, min(B, 2))]             # about a second per token and layer on the host
+        B = x.shape[0]
+        def step():
+            cur = x
+            for layer in layers:
+                y = cpu_layer(None, orc, "nvfp4", layer, cur, threads)
+                cur = np.stack([orc.rmsnorm(y[t], layer.norm_weight, layer.eps, True)[1] for t in range(B)])
+    elif oracle.RefDriver.available():
         drv = oracle.RefDriver(threads)
         kind, used = "reference", drv.threads
         def step():
@@ -252,9 +312,13 @@ def run_b200(args):
     B = args.batch * world
     L = args.layers
     lo, hi = importlib.import_module("salt-core_b200.ep").expert_range(rank, world, E)
-    extras = world == 1 and not args.prefill and not args.no_extra and B == 1
+    fmt = args.format
+    if fmt == "nvfp4" and args.prefill:
+        raise SystemExit("--prefill selects affine-Q4 tensor-core kernels; there is no NVFP4 tensor-core path")
+    extras = world == 1 and not args.prefill and not args.no_extra and B == 1 and fmt == "q4"
     stack = stack_mod.MoeStack(max(B, 512 if extras else 1), H, M, E, K, expert_begin=lo, expert_end=hi)
-    host_layers = generate_layers(synth, L, 3 if rank == 0 else 0, lambda i, layer: stack.add_layer(layer))
+    upload = stack.add_layer if fmt == "q4" else stack.add_nvfp4_layer
+    host_layers = generate_layers(synth, L, (3 if fmt == "q4" else 2) if rank == 0 else 0, lambda i, layer: upload(layer), fmt)
     x_host = synth.make_tokens(77, B, H)
     stream = torch.cuda.Stream()
     sp = stream.cuda_stream
@@ -428,7 +492,7 @@ def run_b200(args):
             kernels = profiled(direct, args.steps)
             mean_distinct = distinct_experts(B, d_x, act)
             gu = kernels["gate_up_geglu"]
-            one_launch = B == 1 and not args.prefill and "down" not in kernels
+            one_launch = fmt == "q4" and B == 1 and not args.prefill and "down" not in kernels
             if one_launch:
                 # one launch per layer: the kernel holds the router phases too, so its bytes are the layer's
                 alg = layer_bytes(mean_distinct, B)
@@ -437,6 +501,11 @@ def run_b200(args):
                 alg = mean_distinct * 2 * TENSOR_BYTES + B * H * 4 + B * K * M * 4
                 kname = ("q4_gemm_tc_kernel<fused> (tcgen05 gate/up + GeGLU)" if tc_mode
                          else "q4_tile16_kernel<2,TT> / q4_fused_expert_kernel (gate/up + GeGLU)")
+                if fmt == "nvfp4":
+                    # the class brackets the whole NVFP4 expert phase of a layer (six launches)
+                    alg = mean_distinct * 3 * TENSOR_BYTES + B * H * 4 + B * K * (2 * H + 4 * M) * 4
+                    kname = ("NVFP4 expert phase of a layer: plan, activation quantise-dequantise, nvfp4_tile_kernel "
+                             "gate + up, GeGLU, quantise-dequantise, nvfp4_tile_kernel down (six launches)")
             achieved = alg / (gu["us_per_launch"] * 1e-6) / 1e9
             roofline = {"bound": "hbm", "kernel": kname, "achieved": achieved, "peak": peak, "unit": "GB/s",
                         "frac": achieved / peak, "peak_source": peak_source, "algorithmic_bytes_per_launch": alg,
@@ -548,9 +617,9 @@ def run_b200(args):
         out["extra"] = extra
     out["y_token0_crc32"] = y_token0_crc32
     if rank == 0 and world == 1:
-        out["cpu_baseline"] = cpu_baseline(host_layers, B, args.cpu_seconds, os.cpu_count() or 1)
+        out["cpu_baseline"] = cpu_baseline(host_layers, B, args.cpu_seconds, os.cpu_count() or 1, args.format)
         if parity is not None:
-            out["parity"] = cpu_parity(parity[0], x_host, parity[1], os.cpu_count() or 1)
+            out["parity"] = cpu_parity(parity[0], x_host, parity[1], os.cpu_count() or 1, args.format)
     if rank == 0:
         print(json.dumps(out))
     if world > 1:
