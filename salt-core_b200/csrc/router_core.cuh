@@ -183,39 +183,53 @@ static __device__ float block_sum_nonneg(const float* sq, int n, uint32_t* scrat
         }
     __syncthreads();
 
-    // ---- 4. the exact walk
-    if (tid == 0) {
+    // ---- 4. the exact walk, by warp 0: lane j fetches serial point j of a chunk of 32 (its index, integer
+    // prefix, predicted exponent and the term itself), so that the chain below only waits for shuffles and
+    // its own arithmetic; every lane runs the same chain on the same values
+    if (warp == 0) {
         float S;
         if (ns > (uint32_t)POSSUM_NS || n <= POSSUM_HEAD) {
-            S = serial_sum(sq, n);
+            S = lane == 0 ? serial_sum(sq, n) : 0.0f;
         } else {
-            S = serial_sum(sq, POSSUM_HEAD);
+            S = lane == 0 ? serial_sum(sq, POSSUM_HEAD) : 0.0f;
+            S = __shfl_sync(0xffffffffu, S, 0);
             int prev = POSSUM_HEAD - 1;
             unsigned long long iprev = 0;
             uint32_t E = scratch[2];
-            for (uint32_t jx = 0; jx <= ns; jx++) {
-                const int idx = jx < ns ? (int)sp_k[jx] : n;
-                const unsigned long long inow = jx < ns ? sp_i[jx] : itotal;
-                if (idx - 1 > prev) {
-                    const unsigned long long tot = inow - iprev;
-                    const uint32_t sb = __float_as_uint(S);
-                    const uint32_t M = (sb & 0x7fffffu) | 0x800000u;
-                    if ((sb >> 23) == E && tot < (unsigned long long)(ONE24 - M)) {
-                        const uint32_t M2 = M + (uint32_t)tot;
-                        S = __uint_as_float((E << 23) | (M2 & 0x7fffffu));
-                    } else {
-                        for (int i = prev + 1; i < idx; i++) S = __fadd_rn(S, sq[i]);   // prediction missed
+            for (uint32_t base0 = 0; base0 <= ns; base0 += 32) {
+                const uint32_t mine = base0 + (uint32_t)lane;
+                const int my_idx = mine < ns ? (int)sp_k[mine] : n;
+                const unsigned long long my_i = mine < ns ? sp_i[mine] : itotal;
+                const uint32_t my_e = mine < ns ? sp_e[mine] : 0u;
+                const float my_v = mine < ns ? sq[my_idx] : 0.0f;
+                const int cnt = (int)min(32u, ns + 1u - base0);
+                for (int j = 0; j < cnt; j++) {
+                    const uint32_t jx = base0 + (uint32_t)j;
+                    const int idx = __shfl_sync(0xffffffffu, my_idx, j);
+                    const unsigned long long inow = __shfl_sync(0xffffffffu, my_i, j);
+                    const uint32_t e_after = __shfl_sync(0xffffffffu, my_e, j);
+                    const float term = __shfl_sync(0xffffffffu, my_v, j);
+                    if (idx - 1 > prev) {
+                        const unsigned long long tot = inow - iprev;
+                        const uint32_t sb = __float_as_uint(S);
+                        const uint32_t M = (sb & 0x7fffffu) | 0x800000u;
+                        if ((sb >> 23) == E && tot < (unsigned long long)(ONE24 - M)) {
+                            const uint32_t M2 = M + (uint32_t)tot;
+                            S = __uint_as_float((E << 23) | (M2 & 0x7fffffu));
+                        } else {
+                            for (int i = prev + 1; i < idx; i++) S = __fadd_rn(S, sq[i]);   // prediction missed
+                        }
                     }
-                }
-                if (jx < ns) {
-                    S = __fadd_rn(S, sq[idx]);
-                    prev = idx;
-                    iprev = inow;
-                    E = sp_e[jx];
+                    if (jx < ns) {
+                        S = __fadd_rn(S, term);
+                        prev = idx;
+                        iprev = inow;
+                        E = e_after;
+                    }
                 }
             }
         }
-        scratch[0] = __float_as_uint(S);
+        if (lane == 0) scratch[0] = __float_as_uint(S);
     }
     __syncthreads();
     return __uint_as_float(scratch[0]);
