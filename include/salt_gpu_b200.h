@@ -39,7 +39,40 @@ extern "C" {
 /* ====================================================================== */
 
 struct SaltTextGpuProgramOps;      /* reference include/salt/text_verify.h:746 */
-struct SaltGpuResidencyBackendOps; /* reference include/salt/gpu_residency.h:63 */
+
+/* Device-local residency (reference include/salt/gpu_residency.h:13, 26-36, 63-89).  The reference's state
+ * machine (src/gpu_residency.c) owns seats, tickets, generations and leases; the backend supplies the
+ * physical half: one HBM arena, pinned staging buffers, asynchronous staging->seat copies. */
+#define SALT_GPU_RESIDENCY_ABI_VERSION 1u
+typedef struct SaltGpuResidencyPlan {
+    uint64_t device_budget_bytes; /* whole arena */
+    uint64_t permanent_bytes;     /* leading part that is never evicted */
+    uint64_t slot_base_offset;    /* first seat, a multiple of device_alignment */
+    uint64_t slot_bytes;          /* seat stride */
+    uint64_t staging_bytes;       /* one pinned staging buffer, >= the largest payload */
+    uint32_t slot_count, staging_count;
+    uint32_t device_alignment, flags;
+} SaltGpuResidencyPlan;
+struct SaltGpuResidencyPermanentLayout; /* gpu_residency.h:51 (permanent population: not provided) */
+struct SaltGpuResidencyPermanentSpan;   /* gpu_residency.h:58 */
+typedef struct SaltGpuResidencyBackendOps {
+    uint32_t abi_version;
+    size_t ops_size;
+    int (*create)(void *context, const SaltGpuResidencyPlan *plan);
+    int (*staging)(void *context, uint32_t staging_slot, void **address, size_t *capacity);
+    int (*populate)(void *context, uint32_t physical_slot, uint64_t device_offset, uint32_t staging_slot,
+                    size_t nbytes, uint64_t ticket);
+    int (*poll)(void *context, uint32_t physical_slot, uint64_t ticket, int *complete);
+    int (*resolve)(void *context, uint64_t device_offset, size_t nbytes, uintptr_t *address);
+    int (*retire)(void *context, uint32_t physical_slot, uint64_t generation);
+    int (*destroy)(void *context);
+    int (*permanent_layout)(void *context, struct SaltGpuResidencyPermanentLayout *layout, size_t layout_size);
+    int (*permanent_span)(void *context, uint32_t span_index, struct SaltGpuResidencyPermanentSpan *span,
+                          size_t span_size);
+    int (*permanent_copy)(void *context, uint32_t span_index, uint64_t device_offset, uint32_t staging_slot,
+                          size_t nbytes, uint64_t ticket);
+    int (*permanent_publish)(void *context);
+} SaltGpuResidencyBackendOps;
 
 /* gpu.h:102-109 */
 typedef struct SaltGpuBatchStats {
@@ -181,7 +214,7 @@ int salt_gpu_cuda_present(void);                                            /* g
 int salt_gpu_rocm_present(void);                                            /* gpu.h:170, 0 */
 int salt_gpu_pageable_mmap_active(void);                                    /* gpu.h:173, 0 */
 const struct SaltTextGpuProgramOps *salt_gpu_tensor_program_ops(void);      /* gpu.h:209, NULL */
-const struct SaltGpuResidencyBackendOps *salt_gpu_residency_backend_ops(void); /* gpu_residency.h:147, NULL */
+const struct SaltGpuResidencyBackendOps *salt_gpu_residency_backend_ops(void); /* gpu_residency.h:147 */
 
 /* ---- weight resources (gpu.h:443-487, 380-409) ------------------------ */
 int salt_gpu_weight_resource_describe(uint32_t kind, uint32_t id, const void *base, size_t nbytes);

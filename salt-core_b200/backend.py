@@ -52,6 +52,30 @@ class MoeExpert(C.Structure):
                 ("group", C.c_int), ("resource_slot", C.c_int), ("logical_resource_id", C.c_uint64)]
 
 
+class ResidencyPlan(C.Structure):
+    """``SaltGpuResidencyPlan`` (reference include/salt/gpu_residency.h:26-36)."""
+    _fields_ = [("device_budget_bytes", C.c_uint64), ("permanent_bytes", C.c_uint64),
+                ("slot_base_offset", C.c_uint64), ("slot_bytes", C.c_uint64), ("staging_bytes", C.c_uint64),
+                ("slot_count", C.c_uint32), ("staging_count", C.c_uint32), ("device_alignment", C.c_uint32),
+                ("flags", C.c_uint32)]
+
+
+class ResidencyBackendOps(C.Structure):
+    """``SaltGpuResidencyBackendOps`` (reference include/salt/gpu_residency.h:63-89)."""
+    _fields_ = [("abi_version", C.c_uint32), ("ops_size", C.c_size_t),
+                ("create", C.CFUNCTYPE(C.c_int, C.c_void_p, C.POINTER(ResidencyPlan))),
+                ("staging", C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_uint32, C.POINTER(C.c_void_p),
+                                        C.POINTER(C.c_size_t))),
+                ("populate", C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_uint32, C.c_uint64, C.c_uint32, C.c_size_t,
+                                         C.c_uint64)),
+                ("poll", C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_uint32, C.c_uint64, C.POINTER(C.c_int))),
+                ("resolve", C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_uint64, C.c_size_t, C.POINTER(C.c_size_t))),
+                ("retire", C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_uint32, C.c_uint64)),
+                ("destroy", C.CFUNCTYPE(C.c_int, C.c_void_p)),
+                ("permanent_layout", C.c_void_p), ("permanent_span", C.c_void_p),
+                ("permanent_copy", C.c_void_p), ("permanent_publish", C.c_void_p)]
+
+
 class SelectedProjectionJob(C.Structure):
     _fields_ = [("vals", C.c_void_p), ("scales", C.c_void_p), ("biases", C.c_void_p), ("id", C.c_void_p),
                 ("inputs", C.c_void_p), ("outputs", C.c_void_p), ("rows", C.c_int), ("cols", C.c_int),
@@ -128,6 +152,17 @@ class SaltGpu:
         return self.lib.salt_gpu_selected_resource_bind(slot, C.c_uint64(logical_id), ptr(base),
                                                         C.c_size_t(base.nbytes),
                                                         C.c_void_p(base.ctypes.data + payload_offset))
+
+    def selected_resource_bind_resident(self, slot, logical_id, payload, device_address, generation):
+        """Publish a payload the residency engine already populated into seat ``slot`` (no copy)."""
+        return self.lib.salt_gpu_selected_resource_bind_resident(
+            slot, C.c_uint64(logical_id), ptr(payload), C.c_size_t(payload.nbytes),
+            C.c_size_t(device_address), C.c_uint64(generation))
+
+    def residency_backend_ops(self):
+        """The physical residency operations (``ResidencyBackendOps``) for the reference's state machine."""
+        self.lib.salt_gpu_residency_backend_ops.restype = C.POINTER(ResidencyBackendOps)
+        return self.lib.salt_gpu_residency_backend_ops()
 
     def selected_resource_unbind(self, slot, logical_id):
         return self.lib.salt_gpu_selected_resource_unbind(slot, C.c_uint64(logical_id))

@@ -271,7 +271,8 @@ int salt_gpu_free(void) {
         if (r.dev) cudaFree(r.dev);
     B.resources.clear();
     for (auto& s : B.selected)
-        if (s.dev) cudaFree(s.dev);
+        if (s.own) cudaFree(s.own);
+    residency_shutdown();
     B.selected.clear();
     B.logical_to_slot.clear();
     cudaFree(B.d_x); cudaFree(B.d_y); cudaFree(B.d_mid); cudaFree(B.d_jobs); cudaFree(B.d_status);
@@ -336,7 +337,6 @@ int salt_gpu_cuda_present(void) { return 1; }
 int salt_gpu_rocm_present(void) { return 0; }
 int salt_gpu_pageable_mmap_active(void) { return 0; }
 const struct SaltTextGpuProgramOps* salt_gpu_tensor_program_ops(void) { return nullptr; }
-const struct SaltGpuResidencyBackendOps* salt_gpu_residency_backend_ops(void) { return nullptr; }
 
 // ------------------------------------------------------------------------
 // weight resources
@@ -605,17 +605,20 @@ int salt_gpu_selected_resource_bind(int slot, uint64_t logical_id, const void* b
                 B.logical_to_slot[logical_id] == slot) ? 0 : -1;
     if (B.logical_to_slot[logical_id] != -1) return -1;
     const size_t payload_bytes = nbytes - (size_t)(p - b);
-    if (s.dev_cap < payload_bytes) {
-        if (s.dev) cudaFree(s.dev);
-        s.dev = nullptr;
-        s.dev_cap = 0;
+    if (s.own_cap < payload_bytes) {
+        if (s.own) cudaFree(s.own);
+        s.own = nullptr;
+        s.own_cap = 0;
         void* d = nullptr;
         if (!cuda_ok(cudaMalloc(&d, payload_bytes + 16), "selected slot")) return -1;
-        s.dev = (uint8_t*)d;
-        s.dev_cap = payload_bytes;
+        s.own = (uint8_t*)d;
+        s.own_cap = payload_bytes;
     }
-    if (!cuda_ok(cudaMemcpy(s.dev, payload, payload_bytes, cudaMemcpyHostToDevice), "selected copy")) return -1;
+    if (!cuda_ok(cudaMemcpy(s.own, payload, payload_bytes, cudaMemcpyHostToDevice), "selected copy")) return -1;
     B.copied_bytes += payload_bytes;
+    s.dev = s.own;
+    s.resident = false;
+    s.generation = 0;
     s.active = true;
     s.logical_id = logical_id;
     s.base = base; s.payload = payload; s.nbytes = nbytes;
@@ -624,7 +627,32 @@ int salt_gpu_selected_resource_bind(int slot, uint64_t logical_id, const void* b
     return 0;
 }
 
-int salt_gpu_selected_resource_bind_resident(int, uint64_t, const void*, size_t, uintptr_t, uint64_t) { return -1; }
+// Publish a payload that the residency engine has already populated into seat `slot` of its arena
+// (reference gpu.h:339-342; caller models/gemma4-26b-a4b/src/gemma4_text.c:1886-1940): no copy, the slot
+// views the seat.  `payload` is only the host identity that later tensor pointers are measured from.
+int salt_gpu_selected_resource_bind_resident(int slot, uint64_t logical_id, const void* payload, size_t nbytes,
+                                             uintptr_t device_address, uint64_t generation) {
+    Backend& B = g_backend;
+    if (!B.ready || B.selected.empty() || slot < 0 || slot >= (int)B.selected.size() ||
+        logical_id >= B.logical_to_slot.size() || !payload || nbytes < 1 || !device_address || generation == 0)
+        return -1;
+    if (residency_seat_address(slot, nbytes) != device_address) return -1;
+    Selected& s = B.selected[(size_t)slot];
+    if (s.active)
+        return (s.resident && s.logical_id == logical_id && s.generation == generation && s.payload == payload &&
+                s.nbytes == nbytes && s.dev == (uint8_t*)device_address && B.logical_to_slot[logical_id] == slot)
+                   ? 0 : -1;
+    if (B.logical_to_slot[logical_id] != -1) return -1;
+    s.active = true;
+    s.resident = true;
+    s.generation = generation;
+    s.logical_id = logical_id;
+    s.base = payload; s.payload = payload; s.nbytes = nbytes;
+    s.dev = (uint8_t*)device_address;
+    B.logical_to_slot[logical_id] = slot;
+    B.selected_fenced = false;
+    return 0;
+}
 
 int salt_gpu_selected_resources_fence(void) {
     Backend& B = g_backend;

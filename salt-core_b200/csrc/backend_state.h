@@ -45,8 +45,11 @@ struct Selected {
     const void* base = nullptr;
     const void* payload = nullptr;
     size_t nbytes = 0;
-    uint8_t* dev = nullptr;
-    size_t dev_cap = 0;
+    uint8_t* dev = nullptr;          // where the payload lives in HBM: `own`, or a residency seat
+    uint8_t* own = nullptr;          // allocation of the copying bind, kept for the slot's next occupant
+    size_t own_cap = 0;
+    bool resident = false;           // bound by salt_gpu_selected_resource_bind_resident
+    uint64_t generation = 0;
 };
 
 struct Backend {
@@ -72,5 +75,7 @@ extern Backend g_backend;
 bool cuda_ok(cudaError_t e, const char* what);
 void count_launches(int n);
 uint64_t launch_count();
+uintptr_t residency_seat_address(int seat, size_t nbytes);
+void residency_shutdown();
 
 }  // namespace sb

@@ -58,5 +58,25 @@ def test_fail_closed_without_initialisation():
     assert lib.salt_gpu_q8_matvec(None, None, None, 1, 64, None, None) == -1
     assert lib.salt_gpu_attention_rewind(0) == -1
     assert lib.salt_gpu_tensor_program_ops() in (0, None)
+
+
+def test_residency_operations_table():
+    """The seven required residency operations are present (reference src/gpu_residency.c:70-76 rejects a
+    table without them or with another size); creating a residency before salt_gpu_init fails closed."""
+    import importlib
+    bm = importlib.import_module("salt-core_b200.backend")
+    lib = load_package().load_library()
+    lib.salt_gpu_residency_backend_ops.restype = C.POINTER(bm.ResidencyBackendOps)
+    ops = lib.salt_gpu_residency_backend_ops().contents
+    assert ops.abi_version == 1 and ops.ops_size == C.sizeof(bm.ResidencyBackendOps) == 104
+    for name in ("create", "staging", "populate", "poll", "resolve", "retire", "destroy"):
+        assert getattr(ops, name)
+    for name in ("permanent_layout", "permanent_span", "permanent_copy", "permanent_publish"):
+        assert getattr(ops, name) is None
+    plan = bm.ResidencyPlan(4096, 0, 0, 1024, 1024, 2, 1, 256, 0)
+    assert ops.create(None, C.byref(plan)) == -1
+    assert ops.destroy(None) == -1
+    assert lib.salt_gpu_selected_resource_bind_resident(0, C.c_uint64(0), None, C.c_size_t(0), C.c_size_t(0),
+                                                        C.c_uint64(0)) == -1
     lib.salt_gpu_cuda_present.restype = C.c_int
     assert lib.salt_gpu_cuda_present() == 1 and lib.salt_gpu_rocm_present() == 0
