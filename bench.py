@@ -58,9 +58,10 @@ def parse():
     ap.add_argument("--ep-exchange", choices=["peer", "nccl"], default="peer",
                     help="N>1: exchange of the grouped expert outputs by the stack's own kernel over peer "
                          "memory (falls back to nccl when the regions cannot be mapped) or by an NCCL all-reduce")
-    ap.add_argument("--prefill", default=None, choices=["exact", "single", "split"],
+    ap.add_argument("--prefill", default=None, choices=["exact", "single", "split", "blockscaled"],
                     help="run the layers one by one with the expert projections on the exact kernels, or on the "
-                         "tensor cores with operands rounded to fp16 once (single) or carried as hi+lo halves (split)")
+                         "tensor cores: affine-Q4 with operands rounded to fp16 once (single) or carried as hi+lo "
+                         "halves (split); NVFP4 as block-scaled mxf4nvf4 GEMMs (blockscaled)")
     args = ap.parse_args()
     if args.layers is None:
         args.layers = 30 if args.format == "q4" else 8
@@ -313,8 +314,8 @@ def run_b200(args):
     L = args.layers
     lo, hi = importlib.import_module("salt-core_b200.ep").expert_range(rank, world, E)
     fmt = args.format
-    if fmt == "nvfp4" and args.prefill:
-        raise SystemExit("--prefill selects affine-Q4 tensor-core kernels; there is no NVFP4 tensor-core path")
+    if (fmt == "nvfp4") != (args.prefill in (None, "exact", "blockscaled")) and args.prefill not in (None, "exact"):
+        raise SystemExit("--prefill single/split are the affine-Q4 tensor-core kernels, blockscaled the NVFP4 one")
     extras = world == 1 and not args.prefill and not args.no_extra and B == 1 and fmt == "q4"
     stack = stack_mod.MoeStack(max(B, 512 if extras else 1), H, M, E, K, expert_begin=lo, expert_end=hi)
     upload = stack.add_layer if fmt == "q4" else stack.add_nvfp4_layer
@@ -336,7 +337,7 @@ def run_b200(args):
         """Expert-parallel pass: one exchange of the grouped expert outputs per layer."""
         ep.forward(stack, grouped, src, B, dst, act, stream=sp)
 
-    tc_mode = {None: False, "exact": False, "single": "single", "split": "split"}[args.prefill]
+    tc_mode = {None: False, "exact": False, "single": "single", "split": "split", "blockscaled": True}[args.prefill]
 
     def forward_layers(src, dst):
         """Layer by layer through the two-phase entry points (the only way to pick the projection kernels)."""
@@ -506,13 +507,17 @@ def run_b200(args):
                     alg = mean_distinct * 3 * TENSOR_BYTES + B * H * 4 + B * K * (2 * H + 4 * M) * 4
                     kname = ("NVFP4 expert phase of a layer: plan, activation quantise-dequantise, nvfp4_tile_kernel "
                              "gate + up, GeGLU, quantise-dequantise, nvfp4_tile_kernel down (six launches)")
+                    if tc_mode:
+                        kname = ("NVFP4 expert phase of a layer: plan, activation quantise, nvfp4_gemm_tc_kernel "
+                                 "(tcgen05.mma.kind::mxf4nvf4 block-scaled) gate + up, GeGLU, quantise, "
+                                 "nvfp4_gemm_tc_kernel down (six launches)")
             achieved = alg / (gu["us_per_launch"] * 1e-6) / 1e9
             roofline = {"bound": "hbm", "kernel": kname, "achieved": achieved, "peak": peak, "unit": "GB/s",
                         "frac": achieved / peak, "peak_source": peak_source, "algorithmic_bytes_per_launch": alg,
                         "us_per_launch": gu["us_per_launch"], "mean_distinct_experts": mean_distinct,
                         "traffic": None,
                         "traffic_note": "not measured by this run (an ncu capture of this kernel gives the DRAM bytes per launch)"}
-            if tc_mode and B * K / E >= 96:
+            if tc_mode and fmt == "q4" and B * K / E >= 96:
                 # rows per expert beyond the ridge: the expert GEMMs are bound by the tensor pipe
                 flops = 2.0 * B * K * 2 * H * M
                 tf = flops / (gu["us_per_launch"] * 1e-6) / 1e12

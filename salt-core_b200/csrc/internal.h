@@ -94,6 +94,11 @@ cudaError_t launch_q8_jobs(const Q4Job* jobs, int njobs, int max_rows, int max_t
 // ---- q4_gemm_tc.cu (tcgen05 / TMEM, tolerance path) --------------------------
 cudaError_t launch_gather_convert(const float* x, const int32_t* g2c, void* xh, void* xl, int jobs, int topk,
                                   int hidden, cudaStream_t stream);
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda)
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                      const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                      CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+cudaError_t tensor_map_encoder(TensorMapEncodeFn* out);
 // TMA descriptors of a [rows][cols] fp16 activation buffer and of its residual buffer:
 // boxes of 64 columns x (16 << i) rows.
 struct TcMaps {
@@ -140,7 +145,26 @@ struct Fp4ExpertDesc {
 cudaError_t launch_nvfp4_moe_plan(const int* group_offsets, int E, int expert_begin, int expert_end, int J,
                                   const Fp4ExpertDesc* experts, int H, int M, const float* dq_gu, float* gate_out,
                                   float* up_out, const float* dq_dn, float* grouped_out, Fp4Job* gu_jobs, Fp4Job* dn_jobs,
-                                  float* ig_gu, float* ig_dn, cudaStream_t stream);
+                                  float* ig_gu, float* ig_dn, cudaStream_t stream, struct Fp4TcJob* tc_gu = nullptr,
+                                  struct Fp4TcJob* tc_dn = nullptr, const uint8_t* x_scales = nullptr);
+// ---- nvfp4_gemm_tc.cu: block-scaled tensor-core form of a grouped NVFP4 projection (tolerance path) ----
+struct Fp4TcJob {
+    const uint8_t* w_scales;   // [R][C/16] E4M3 block scales of the weight matrix (row-major, as stored)
+    const uint8_t* x_scales;   // [ntok][C/16] block scales of the job's quantised activations
+    float* y;                  // y[n * y_stride + m]
+    float wg, ig;              // 1 / weight divisor, input global scale: y = acc * wg / ig
+    int w_row0, w_slice;       // the matrix' first row and expert slice in the layer's weight map
+    int x_row0;                // the job's first row in the packed-activation map
+    int ntok, R, y_stride;
+};
+struct Fp4TcMaps {
+    CUtensorMap w;             // weights: bytes x rows x experts
+    CUtensorMap x[3];          // packed activations: boxes of 16 / 32 / 64 rows
+};
+cudaError_t make_fp4_weight_map(CUtensorMap* out, const void* base, int C, int rows, int slices, size_t slice_stride);
+cudaError_t make_fp4_act_maps(CUtensorMap* out3, const void* base, int C, int rows);
+cudaError_t launch_nvfp4_gemm_tc(const Fp4TcJob* jobs, int njobs, int R, int C, const Fp4TcMaps& maps, int* status,
+                                 cudaStream_t stream);
 cudaError_t launch_geglu_rows(const float* gate, const float* up, float* chain, size_t n, cudaStream_t stream);
 cudaError_t launch_nvfp4_jobs(const Fp4Job* jobs, int njobs, int max_rows, int max_tok, int C, bool aligned,
                               cudaStream_t stream);

@@ -37,6 +37,8 @@ struct Layer {
     // NVFP4 experts (W4A4: E2M1 codes + E4M3 block scales; reference src/nvfp4.c) instead of affine-Q4 ones
     bool nvfp4 = false;
     Fp4ExpertDesc* fp4_experts = nullptr;      // [local experts] device
+    bool fp4_tc_ok = false;                    // every block scale is an unsigned finite E4M3 code: the tensor core can take it
+    CUtensorMap fp4_w_gu, fp4_w_dn;            // weight maps of the tensor-core form (gate | up rows; down rows)
     // optional dense branch and norms of the whole feed-forward block
     bool ffn = false;
     int dense_inter = 0;
@@ -71,6 +73,9 @@ struct Stack {
     float *fp4_ig_gu = nullptr, *fp4_ig_dn = nullptr;
     uint8_t *fp4_packed = nullptr, *fp4_scales = nullptr;
     Fp4Job *fp4_gu_jobs = nullptr, *fp4_dn_jobs = nullptr;
+    Fp4TcJob *fp4_tc_gu = nullptr, *fp4_tc_dn = nullptr;
+    CUtensorMap fp4_x_gu[3], fp4_x_dn[3];      // packed activations as [2J][H/2] and as [J][M/2]
+    bool fp4_maps_ok = false;
     bool fused_decode = true;                  // batches of up to FUSED_MAX_TOKENS tokens take the one-launch expert kernel
     void *xh = nullptr, *xl = nullptr, *chain_h = nullptr, *chain_l = nullptr;   // fp16 operands (hi, lo) of the tensor-core path
     bool tc_ready = false;                     // tensor maps built (needs hidden, inter multiples of 64)
@@ -131,6 +136,7 @@ static void free_stack(Stack* s) {
     cudaFree(s->grouped_alt); cudaFree(s->weights_alt); cudaFree(s->layer_counters);
     cudaFree(s->fp4_dq_gu); cudaFree(s->fp4_dq_dn); cudaFree(s->fp4_gate); cudaFree(s->fp4_up); cudaFree(s->fp4_ig_gu);
     cudaFree(s->fp4_ig_dn); cudaFree(s->fp4_packed); cudaFree(s->fp4_scales); cudaFree(s->fp4_gu_jobs); cudaFree(s->fp4_dn_jobs);
+    cudaFree(s->fp4_tc_gu); cudaFree(s->fp4_tc_dn);
     cudaFree(s->xh); cudaFree(s->xl); cudaFree(s->chain_h); cudaFree(s->chain_l);
     if (s->h_in) cudaFreeHost(s->h_in);
     if (s->h_out) cudaFreeHost(s->h_out);
@@ -256,8 +262,12 @@ int salt_b200_stack_add_nvfp4_layer(void* stack, const SaltB200Nvfp4LayerSpec* s
           dev_alloc(&s->fp4_gate, J * s->inter) && dev_alloc(&s->fp4_up, J * s->inter) && dev_alloc(&s->fp4_ig_gu, 2 * J) &&
           dev_alloc(&s->fp4_ig_dn, J) && dev_alloc(&s->fp4_packed, 2 * J * (size_t)s->hidden / 2) &&
           dev_alloc(&s->fp4_scales, 2 * J * (size_t)s->hidden / 16) && dev_alloc(&s->fp4_gu_jobs, (size_t)2 * E) &&
-          dev_alloc(&s->fp4_dn_jobs, (size_t)E)))
+          dev_alloc(&s->fp4_dn_jobs, (size_t)E) && dev_alloc(&s->fp4_tc_gu, (size_t)2 * E) &&
+          dev_alloc(&s->fp4_tc_dn, (size_t)E)))
         return -1;
+    if (!s->fp4_maps_ok)
+        s->fp4_maps_ok = make_fp4_act_maps(s->fp4_x_gu, s->fp4_packed, s->hidden, (int)(2 * J)) == cudaSuccess &&
+                         make_fp4_act_maps(s->fp4_x_dn, s->fp4_packed, s->inter, (int)J) == cudaSuccess;
     Layer l;
     l.eps = spec->eps;
     l.expert_stride = spec->expert_stride;
@@ -282,6 +292,21 @@ int salt_b200_stack_add_nvfp4_layer(void* stack, const SaltB200Nvfp4LayerSpec* s
         }
     }
     ok = ok && upload(&l.fp4_experts, desc.data(), local);
+    if (ok) {
+        // the tensor-core form reads the block scales as UNSIGNED E4M3: a negative or NaN scale code (legal in
+        // the stored format, never produced by a quantiser) keeps the layer on the exact kernels
+        bool plain = s->fp4_maps_ok && (s->inter % 8) == 0;
+        for (size_t i = 0; plain && i < local; i++)
+            for (int k = 0; plain && k < 3; k++) {
+                const uint8_t* sc = src + i * spec->expert_stride + (size_t)k * tensor_bytes + code_bytes;
+                for (size_t b = 0; b < scale_bytes; b++)
+                    if (sc[b] >= 0x7f) { plain = false; break; }
+            }
+        const int M = s->inter, H = s->hidden;
+        l.fp4_tc_ok = plain &&
+                      make_fp4_weight_map(&l.fp4_w_gu, l.pool, H, 2 * M + M / 8, (int)local, spec->expert_stride) == cudaSuccess &&
+                      make_fp4_weight_map(&l.fp4_w_dn, l.pool + 2 * tensor_bytes, M, H, (int)local, spec->expert_stride) == cudaSuccess;
+    }
     if (!ok) {
         cudaFree(l.router_w); cudaFree(l.router_scale); cudaFree(l.per_expert_scale); cudaFree(l.pool);
         cudaFree(l.norm_weight); cudaFree(l.fp4_experts);
@@ -395,8 +420,31 @@ static int layer_experts_impl(Stack* s, int layer, const float* d_router_src, co
         Timed t(s, KC_PLAN, st);
         if (!cuda_ok(launch_moe_plan(a, st), "plan")) return -1;
     }
+    if (l.nvfp4 && (flags & SB_EXPERTS_TENSOR_CORE)) {
+        // block-scaled tensor-core form (tolerance path): same plan, same bit-exact quantiser, the two
+        // projection batches as tcgen05.mma.kind::mxf4nvf4 GEMMs
+        if (!l.fp4_tc_ok) return -1;
+        Timed t(s, KC_GATE_UP, st);
+        Fp4TcMaps mg, md;
+        mg.w = l.fp4_w_gu; md.w = l.fp4_w_dn;
+        for (int v = 0; v < 3; v++) { mg.x[v] = s->fp4_x_gu[v]; md.x[v] = s->fp4_x_dn[v]; }
+        if (!cuda_ok(launch_nvfp4_moe_plan(s->group_offsets, E, s->expert_begin, s->expert_end, jobs, l.fp4_experts, H, M,
+                                           s->fp4_dq_gu, s->fp4_gate, s->fp4_up, s->fp4_dq_dn, s->grouped_out,
+                                           s->fp4_gu_jobs, s->fp4_dn_jobs, s->fp4_ig_gu, s->fp4_ig_dn, st, s->fp4_tc_gu,
+                                           s->fp4_tc_dn, s->fp4_scales), "nvfp4 plan") ||
+            !cuda_ok(launch_nvfp4_qdq(d_x, 2 * jobs, H, s->fp4_ig_gu, s->fp4_packed, s->fp4_scales, nullptr,
+                                      s->status, st, s->g2c, jobs, K), "nvfp4 qdq x") ||
+            !cuda_ok(launch_nvfp4_gemm_tc(s->fp4_tc_gu, 2 * E, M, H, mg, s->status, st), "nvfp4 tc gate/up") ||
+            !cuda_ok(launch_geglu_rows(s->fp4_gate, s->fp4_up, s->chain, (size_t)jobs * M, st), "geglu") ||
+            !cuda_ok(launch_nvfp4_qdq(s->chain, jobs, M, s->fp4_ig_dn, s->fp4_packed, s->fp4_scales, nullptr,
+                                      s->status, st), "nvfp4 qdq chain") ||
+            !cuda_ok(launch_nvfp4_gemm_tc(s->fp4_tc_dn, E, H, M, md, s->status, st), "nvfp4 tc down"))
+            return -1;
+        count_launches(7);
+        return 0;
+    }
     if (l.nvfp4) {
-        if (flags & (SB_EXPERTS_TENSOR_CORE | SB_EXPERTS_TENSOR_CORE_SINGLE)) return -1;
+        if (flags & SB_EXPERTS_TENSOR_CORE_SINGLE) return -1;
         Timed t(s, KC_GATE_UP, st);
         if (!cuda_ok(launch_nvfp4_moe_plan(s->group_offsets, E, s->expert_begin, s->expert_end, jobs, l.fp4_experts, H, M,
                                            s->fp4_dq_gu, s->fp4_gate, s->fp4_up, s->fp4_dq_dn, s->grouped_out,

@@ -1,0 +1,339 @@
+// Grouped NVFP4 (W4A4) expert GEMMs on the 5th-generation tensor cores: block-scaled
+// tcgen05.mma.kind::mxf4nvf4 (E2M1 codes in both operands, one unsigned E4M3 scale per 16 K elements of
+// each operand, fp32 accumulation in TMEM) for batches where the bit-exact CUDA-core kernels of
+// nvfp4_kernels.cu are compute bound.  TOLERANCE path: the tensor core forms
+//     sum over 16-blocks of (sum of code products) * weight scale * activation scale
+// in its own order and the epilogue applies the two per-tensor scalars (1 / weight divisor, 1 / input global
+// scale), where the reference (src/nvfp4.c:173-192, 228-256) rounds scale * scalar first and adds in its
+// 32-accumulator order: same real number, different fp32 roundings (measured against the CPU path in the
+// tests; the bound is 1e-3 of max(|ref|, row rms)).  Activation codes and scales come from the bit-exact
+// quantiser (nvfp4_qdq_kernel), so the only difference is the order of the additions.
+//
+// One block = one 128-row tile of one weight matrix of one expert; the weight rows sit on the MMA M
+// dimension, the expert's tokens on N (16, 32 or 64 per pass), K advances in chunks of 256 columns = one
+// 128-byte row of packed codes = four MMAs of K = 64.  Two blocks fit an SM (100 KB of shared memory,
+// 256 TMEM columns each).  Warp roles:
+//   warp 5      producer: TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) of the weight tile
+//               (3-D map: byte column, row, expert) and of the tokens' packed activations (2-D map)
+//   warps 0-3   scale warps: load the 16 scale bytes of their rows for the chunk (weights: row-major
+//               [R][C/16], reference layout src/nvfp4.c:147-149; activations: the quantiser's output) and
+//               place them in TMEM with tcgen05.st in the layout the MMA reads - row r of a 128-row operand
+//               in lane r % 32 of every 32-lane quarter, 32-bit column r / 32, byte j = K block j of the
+//               MMA - so no shared-memory staging or rearranged copy of the scales is needed; later the
+//               same warps run the epilogue (tcgen05.ld, scalars, store)
+//   warp 4      issuer: waits for the stage's data and scales, issues the four MMAs, tcgen05.commit
+// Every mbarrier wait is bounded; on expiry the block raises its failure flag, sets SB_ERR_TIMEOUT, waits
+// (bounded) for copies and MMAs in flight, frees its TMEM and returns.
+#include "internal.h"
+#include "umma.cuh"
+
+namespace sb {
+
+constexpr int FT_STAGES = 4;
+constexpr int FT_THREADS = 192;
+constexpr int FT_KC_BYTES = 128;                  // packed bytes of a K chunk (256 columns)
+constexpr int FT_A_BYTES = 128 * FT_KC_BYTES;     // 128 weight rows
+constexpr int FT_MAX_NT = 64;                     // tokens per pass
+constexpr int FT_STAGE_BYTES = FT_A_BYTES + FT_MAX_NT * FT_KC_BYTES;
+constexpr int FT_SMEM_BYTES = FT_STAGES * FT_STAGE_BYTES + 1024;
+constexpr uint32_t FT_TMEM_COLS = 256;            // accumulators at 0..63, scale stages from 128
+constexpr uint32_t FT_SF_BASE = 128, FT_SF_STAGE = 32, FT_SFB_OFF = 16;
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::
+            "r"(dst),
+        "l"((uint64_t)map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// kind::mxf4nvf4 instruction descriptor: A = B = E2M1 (format 1), both K-major, scales unsigned E4M3
+// (format 0), scale ids 0 (a K = 64 MMA with 16-element blocks uses all four bytes of a scale column), K = 64.
+__device__ __forceinline__ uint32_t umma_idesc_fp4(int M, int N) {
+    return (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_fp4(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}\n" ::
+            "r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(tmem_sfa), "r"(tmem_sfb), "r"(accumulate)
+        : "memory");
+}
+
+// 16 consecutive 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
+__device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+struct Fp4TcArgs {
+    const Fp4TcJob* jobs;
+    int C;                // K of the launch (columns of the weight matrices), a multiple of 256
+    int* status;
+};
+
+__global__ void __launch_bounds__(FT_THREADS, 2)
+nvfp4_gemm_tc_kernel(const Fp4TcArgs a, const __grid_constant__ Fp4TcMaps maps) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_free[FT_STAGES];   // the stage's MMAs are complete (tcgen05.commit)
+    __shared__ __align__(8) uint64_t bar_full[FT_STAGES];   // the stage's TMA copies have landed
+    __shared__ __align__(8) uint64_t bar_sf[FT_STAGES];     // the stage's scales are in TMEM (4 warp arrivals)
+    __shared__ __align__(8) uint64_t bar_done;              // a token pass' accumulators are final
+    __shared__ __align__(8) uint64_t bar_drain;             // failure path only: everything issued has completed
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_fail;
+
+    const Fp4TcJob jb = a.jobs[blockIdx.y];
+    const int r0 = blockIdx.x * 128;
+    if (r0 >= jb.R || jb.ntok < 1) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nchunks = a.C >> 8, sc_row = a.C >> 4;
+    uint8_t* stage_base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    const int ntok_cap = min(jb.ntok, FT_MAX_NT);
+    const int variant = ntok_cap <= 16 ? 0 : ntok_cap <= 32 ? 1 : 2;
+    const uint32_t b_bytes = (16u << variant) * FT_KC_BYTES;
+    const int npass = (jb.ntok + FT_MAX_NT - 1) / FT_MAX_NT;
+    volatile int* fail = &s_fail;
+
+    if (tid == 0) {
+        for (int s = 0; s < FT_STAGES; s++) {
+            mbar_init(&bar_free[s], 1);
+            mbar_init(&bar_full[s], 1);
+            mbar_init(&bar_sf[s], 4);
+        }
+        mbar_init(&bar_done, 1);
+        mbar_init(&bar_drain, 1);
+        s_fail = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)),
+                     "r"(FT_TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+
+    uint32_t produced = 0;                                   // producer: chunks requested so far
+    uint32_t it = 0;                                         // chunk counter across token passes
+    for (int pass = 0; pass < npass; pass++) {
+        const int tb = pass * FT_MAX_NT;
+        const int nt_real = min(FT_MAX_NT, jb.ntok - tb);
+        const int NT = (nt_real + 15) & ~15;
+
+        if (warp == 5) {
+            // ================= producer =================
+            if (lane == 0) {
+                for (int kc = 0; kc < nchunks; kc++, produced++) {
+                    const uint32_t s = produced % FT_STAGES;
+                    if (produced >= (uint32_t)FT_STAGES &&
+                        !mbar_wait(&bar_free[s], ((produced / FT_STAGES) - 1) & 1, fail))
+                        break;
+                    const uint32_t dst = smem_u32(stage_base + s * FT_STAGE_BYTES);
+                    mbar_expect_tx(&bar_full[s], FT_A_BYTES + b_bytes);
+                    tma_load_3d(dst, &maps.w, kc * FT_KC_BYTES, jb.w_row0 + r0, jb.w_slice, &bar_full[s]);
+                    tma_load_2d(dst + FT_A_BYTES, &maps.x[variant], kc * FT_KC_BYTES, jb.x_row0 + tb, &bar_full[s]);
+                }
+            }
+            __syncwarp();
+        } else if (warp == 4) {
+            // ================= issuer =================
+            const uint32_t idesc = umma_idesc_fp4(128, NT);
+            const uint32_t lo0 = DESC_B_LO | ((smem_u32(stage_base) & 0x3ffffu) >> 4);
+            uint32_t my = it;
+            for (int kc = 0; kc < nchunks; kc++, my++) {
+                const uint32_t s = my % FT_STAGES, ph = (my / FT_STAGES) & 1;
+                bool ok = mbar_wait(&bar_full[s], ph, fail);
+                if (ok) ok = mbar_wait(&bar_sf[s], ph, fail);
+                if (ok && lane == 0) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t alo = lo0 + s * (FT_STAGE_BYTES >> 4);
+                    const uint32_t blo = alo + (FT_A_BYTES >> 4);
+                    const uint32_t sf = tmem + FT_SF_BASE + s * FT_SF_STAGE;
+#pragma unroll
+                    for (int j = 0; j < 4; j++)          // K = 64 per MMA: 32 bytes further along the swizzled row
+                        umma_fp4(tmem, make_desc(alo + j * 2, DESC_B_HI), make_desc(blo + j * 2, DESC_B_HI), idesc,
+                                 sf + 4 * j, sf + FT_SFB_OFF + 4 * j, (kc > 0 || j > 0) ? 1u : 0u);
+                    umma_commit(&bar_free[s]);
+                    if (kc == nchunks - 1) umma_commit(&bar_done);
+                }
+                __syncwarp();
+                if (!ok) break;
+            }
+        } else {
+            // ================= scale warps =================
+            // lane l of every warp holds, per operand, the scale words of rows l, l + 32, l + 64, l + 96
+            const uint8_t* arow[4];
+            const uint8_t* brow[2];
+#pragma unroll
+            for (int c = 0; c < 4; c++) arow[c] = jb.w_scales + (size_t)min(r0 + lane + 32 * c, jb.R - 1) * sc_row;
+#pragma unroll
+            for (int c = 0; c < 2; c++) brow[c] = jb.x_scales + (size_t)min(tb + lane + 32 * c, jb.ntok - 1) * sc_row;
+            constexpr int DEPTH = 3;
+            uint4 ra[DEPTH][4], rb[DEPTH][2];
+#pragma unroll
+            for (int d = 0; d < DEPTH; d++) {
+                const int kq = min(d, nchunks - 1);
+#pragma unroll
+                for (int c = 0; c < 4; c++) ra[d][c] = ld_nc_v4(arow[c] + kq * 16);
+#pragma unroll
+                for (int c = 0; c < 2; c++) rb[d][c] = ld_nc_v4(brow[c] + kq * 16);
+            }
+            const uint32_t tlane = tmem + ((uint32_t)(warp * 32) << 16);
+            uint32_t my = it;
+            bool ok = true;
+            for (int kc0 = 0; kc0 < nchunks && ok; kc0 += DEPTH) {
+#pragma unroll
+                for (int d = 0; d < DEPTH; d++) {
+                    const int kc = kc0 + d;
+                    if (kc >= nchunks) break;
+                    const uint32_t s = my % FT_STAGES;
+                    uint32_t wa[16], wb[16];
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {      // column 4 j + c = K block j of row l + 32 c
+                        wa[c] = ra[d][c].x; wa[4 + c] = ra[d][c].y; wa[8 + c] = ra[d][c].z; wa[12 + c] = ra[d][c].w;
+                    }
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        const uint4 v = c < 2 ? rb[d][c] : make_uint4(0u, 0u, 0u, 0u);
+                        wb[c] = v.x; wb[4 + c] = v.y; wb[8 + c] = v.z; wb[12 + c] = v.w;
+                    }
+                    if (kc + DEPTH < nchunks) {
+#pragma unroll
+                        for (int c = 0; c < 4; c++) ra[d][c] = ld_nc_v4(arow[c] + (kc + DEPTH) * 16);
+#pragma unroll
+                        for (int c = 0; c < 2; c++) rb[d][c] = ld_nc_v4(brow[c] + (kc + DEPTH) * 16);
+                    }
+                    // the MMAs that last read this stage's scale columns must be complete
+                    if (my >= (uint32_t)FT_STAGES) ok = mbar_wait(&bar_free[s], ((my / FT_STAGES) - 1) & 1, fail);
+                    if (ok) {
+                        // order the stores after the completion just observed (they overwrite what those MMAs read)
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint32_t sf = tlane + FT_SF_BASE + s * FT_SF_STAGE;
+                        tmem_st16(sf, wa);
+                        tmem_st16(sf + FT_SFB_OFF, wb);
+                        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    }
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bar_sf[s]);   // always: the issuer never waits for a warp that gave up
+                    my++;
+                    if (!ok) break;
+                }
+            }
+        }
+        it += (uint32_t)nchunks;
+
+        // ================= epilogue of this token pass (warps 0-3) =================
+        if (warp < 4 && mbar_wait(&bar_done, pass & 1, fail)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int m = r0 + warp * 32 + lane;
+            const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
+            for (int n0 = 0; n0 < NT; n0 += 32) {
+                uint32_t acc[32];
+                tmem_ld32(trow + n0, acc);
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    const int n = n0 + i;
+                    if (n < nt_real && m < jb.R)
+                        jb.y[(size_t)(tb + n) * jb.y_stride + m] = __fdiv_rn(__fmul_rn(__uint_as_float(acc[i]), jb.wg), jb.ig);
+                }
+            }
+        }
+        // all accumulator reads of this pass precede the next pass' first MMA
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (*fail) break;
+    }
+    if (*fail) {
+        if (tid == 0 && a.status) atomicOr(a.status, SB_ERR_TIMEOUT);
+        // wait (bounded, no early exit) for the copies requested and the MMAs issued before TMEM and shared
+        // memory are released: every requested stage either completes its copy (bar_full) ...
+        if (warp == 5 && lane == 0) {
+            int none = 0;
+            for (uint32_t t = (produced > (uint32_t)FT_STAGES ? produced - FT_STAGES : 0); t < produced; t++)
+                (void)mbar_wait(&bar_full[t % FT_STAGES], (t / FT_STAGES) & 1, &none);
+        }
+        __syncthreads();
+        // ... and the tensor core has drained: one more commit tracks everything issued so far
+        if (warp == 4 && lane == 0) {
+            int none = 0;
+            umma_commit(&bar_drain);
+            (void)mbar_wait(&bar_drain, 0, &none);
+        }
+        __syncthreads();
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(FT_TMEM_COLS) : "memory");
+    }
+}
+
+// Weight map of a layer's matrices: bytes [C/2] x rows x local experts (expert stride = the pool's), boxes of
+// 128 bytes x 128 rows, 128-byte swizzle, zero fill past the last row.  Activation maps: [rows][C/2] packed
+// codes, boxes of 128 bytes x 16 / 32 / 64 rows.
+cudaError_t make_fp4_weight_map(CUtensorMap* out, const void* base, int C, int rows, int slices, size_t slice_stride) {
+    TensorMapEncodeFn encode = nullptr;
+    cudaError_t e = tensor_map_encoder(&encode);
+    if (e != cudaSuccess) return e;
+    if ((C % 256) != 0 || rows < 1 || slices < 1 || (slice_stride % 16) != 0 || ((uintptr_t)base % 16) != 0)
+        return cudaErrorInvalidValue;
+    cuuint64_t dims[3] = {(cuuint64_t)(C / 2), (cuuint64_t)rows, (cuuint64_t)slices};
+    cuuint64_t strides[2] = {(cuuint64_t)(C / 2), (cuuint64_t)slice_stride};
+    cuuint32_t box[3] = {(cuuint32_t)FT_KC_BYTES, 128u, 1u};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+cudaError_t make_fp4_act_maps(CUtensorMap* out3, const void* base, int C, int rows) {
+    TensorMapEncodeFn encode = nullptr;
+    cudaError_t e = tensor_map_encoder(&encode);
+    if (e != cudaSuccess) return e;
+    if ((C % 256) != 0 || rows < 1 || ((uintptr_t)base % 16) != 0) return cudaErrorInvalidValue;
+    for (int v = 0; v < 3; v++) {
+        cuuint64_t dims[2] = {(cuuint64_t)(C / 2), (cuuint64_t)rows};
+        cuuint64_t strides[1] = {(cuuint64_t)(C / 2)};
+        cuuint32_t box[2] = {(cuuint32_t)FT_KC_BYTES, (cuuint32_t)(16 << v)};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = encode(&out3[v], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    }
+    return cudaSuccess;
+}
+
+cudaError_t launch_nvfp4_gemm_tc(const Fp4TcJob* jobs, int njobs, int R, int C, const Fp4TcMaps& maps, int* status,
+                                 cudaStream_t stream) {
+    if (njobs < 1 || R < 1) return cudaSuccess;
+    if ((C % 256) != 0) return cudaErrorInvalidValue;
+    cudaError_t e = ensure_dynamic_smem((const void*)nvfp4_gemm_tc_kernel, (size_t)FT_SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    Fp4TcArgs a;
+    a.jobs = jobs; a.C = C; a.status = status;
+    dim3 grid((R + 127) / 128, njobs);
+    nvfp4_gemm_tc_kernel<<<grid, FT_THREADS, FT_SMEM_BYTES, stream>>>(a, maps);
+    return cudaGetLastError();
+}
+
+}  // namespace sb

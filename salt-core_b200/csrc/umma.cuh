@@ -1,0 +1,77 @@
+// tcgen05 / TMA helpers shared by the tensor-core kernels (q4_gemm_tc.cu, nvfp4_gemm_tc.cu).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "mbar.cuh"
+
+namespace sb {
+
+constexpr uint32_t TC_SPIN_LIMIT = 1u << 22;
+
+// Bounded wait for the phase with the given parity.  Returns false on expiry or when
+// another thread of the block has raised the failure flag.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* fail) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < TC_SPIN_LIMIT; i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(ok)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if ((i & 255u) == 255u && *fail) return false;
+    }
+    *fail = 1;
+    return false;
+}
+
+__device__ __forceinline__ uint64_t make_desc(uint32_t lo, uint32_t hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+    return d;
+}
+
+// Shared-memory matrix descriptors (sm_100 version 1), split into 32-bit words so that
+// the issuing thread only adds byte offsets >> 4 to the low word.
+// Both operands are K-major with 128-byte swizzle, as a TMA copy with
+// CU_TENSOR_MAP_SWIZZLE_128B lays a tile down: rows of 64 fp16 (128 bytes), 16-byte chunk c
+// of row r stored at chunk position c ^ (r & 7), 8-row atoms of 1024 bytes; a tile starts
+// on a 1024-byte boundary and a K step of 16 elements advances the start address by 32 bytes.
+// (The unswizzled core-matrix layout gives the same results but its MMAs ran several times
+// slower here.)
+constexpr uint32_t DESC_B_LO = 1u << 16;
+constexpr uint32_t DESC_B_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+
+// 2-D tiled TMA load of one box at element column x, row y, into this block's own shared memory.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
+            "r"(dst),
+        "l"((uint64_t)map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+}  // namespace sb
