@@ -381,6 +381,15 @@ typedef struct SaltB200Nvfp4LayerSpec {
 } SaltB200Nvfp4LayerSpec;
 int salt_b200_stack_add_nvfp4_layer(void *stack, const SaltB200Nvfp4LayerSpec *spec);
 int salt_b200_stack_workspace(void *stack, SaltB200Workspace *out);
+/* Intermediate buffers of the NVFP4 layers after salt_b200_layer_experts (for inspection and stage-wise
+ * checks): the gate and up projection outputs [rows][inter] in grouped order, and the quantised GeGLU
+ * output that feeds the down projection, packed E2M1 codes [rows][inter/2] and E4M3 block scales
+ * [rows][inter/16].  -1 when the stack holds no NVFP4 layer. */
+typedef struct SaltB200Nvfp4Buffers {
+    const float *gate, *up;
+    const uint8_t *chain_codes, *chain_scales;
+} SaltB200Nvfp4Buffers;
+int salt_b200_stack_nvfp4_buffers(void *stack, SaltB200Nvfp4Buffers *out);
 /* Batches of up to 4 tokens run gate/up, GeGLU and down of all selected experts in ONE launch
  * (one persistent block per SM, weights of both phases in flight from the start; the reference
  * runs the three projections as separate calls, models/gemma4-26b-a4b/src/gemma4_text.c:7971-7997).

@@ -339,6 +339,16 @@ int salt_b200_stack_workspace(void* stack, SaltB200Workspace* out) {
     return 0;
 }
 
+int salt_b200_stack_nvfp4_buffers(void* stack, SaltB200Nvfp4Buffers* out) {
+    Stack* s = (Stack*)stack;
+    if (!s || !out || !s->any_nvfp4) return -1;
+    out->gate = s->fp4_gate;
+    out->up = s->fp4_up;
+    out->chain_codes = s->fp4_packed;
+    out->chain_scales = s->fp4_scales;
+    return 0;
+}
+
 int salt_b200_stack_set_grouped_out(void* stack, void* device_buffer, size_t nbytes) {
     Stack* s = (Stack*)stack;
     if (!s || !device_buffer || nbytes < s->grouped_bytes || ((uintptr_t)device_buffer & 15)) return -1;

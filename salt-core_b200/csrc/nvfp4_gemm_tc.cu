@@ -24,19 +24,22 @@
 //   warp 4      issuer: waits for the stage's data and scales, issues the four MMAs, tcgen05.commit
 // Every mbarrier wait is bounded; on expiry the block raises its failure flag, sets SB_ERR_TIMEOUT, waits
 // (bounded) for copies and MMAs in flight, frees its TMEM and returns.
+#include <algorithm>
+
 #include "internal.h"
 #include "umma.cuh"
 
 namespace sb {
 
-constexpr int FT_STAGES = 4;
-constexpr int FT_THREADS = 192;
+constexpr int FT_STAGES = 8;
+constexpr int FT_THREADS = 320;                   // warps 0-3 scales, 4-7 epilogue, 8 issuer, 9 producer
 constexpr int FT_KC_BYTES = 128;                  // packed bytes of a K chunk (256 columns)
 constexpr int FT_A_BYTES = 128 * FT_KC_BYTES;     // 128 weight rows
 constexpr int FT_MAX_NT = 64;                     // tokens per pass
 constexpr int FT_STAGE_BYTES = FT_A_BYTES + FT_MAX_NT * FT_KC_BYTES;
 constexpr int FT_SMEM_BYTES = FT_STAGES * FT_STAGE_BYTES + 1024;
-constexpr uint32_t FT_TMEM_COLS = 256;            // accumulators at 0..63, scale stages from 128
+constexpr int FT_MAX_TILES = 64;                  // tiles of one block's list
+constexpr uint32_t FT_TMEM_COLS = 512;            // accumulators at 0..63 and 64..127, scale stages from 128
 constexpr uint32_t FT_SF_BASE = 128, FT_SF_STAGE = 32, FT_SFB_OFF = 16;
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
@@ -82,31 +85,51 @@ __device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
 
 struct Fp4TcArgs {
     const Fp4TcJob* jobs;
+    int njobs, tiles_per_job;
     int C;                // K of the launch (columns of the weight matrices), a multiple of 256
     int* status;
 };
 
-__global__ void __launch_bounds__(FT_THREADS, 2)
+// One tile of a block's list: the job's fields every role needs, and the tile's first weight row.
+struct Fp4Tile {
+    const uint8_t* w_scales;
+    const uint8_t* x_scales;
+    float* y;
+    float wg, ig;
+    int w_row, w_slice, x_row0, ntok, R, y_stride, r0;
+};
+
+__global__ void __launch_bounds__(FT_THREADS, 1)
 nvfp4_gemm_tc_kernel(const Fp4TcArgs a, const __grid_constant__ Fp4TcMaps maps) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
+    __shared__ Fp4Tile s_tiles[FT_MAX_TILES];
     __shared__ __align__(8) uint64_t bar_free[FT_STAGES];   // the stage's MMAs are complete (tcgen05.commit)
     __shared__ __align__(8) uint64_t bar_full[FT_STAGES];   // the stage's TMA copies have landed
     __shared__ __align__(8) uint64_t bar_sf[FT_STAGES];     // the stage's scales are in TMEM (4 warp arrivals)
-    __shared__ __align__(8) uint64_t bar_done;              // a token pass' accumulators are final
+    __shared__ __align__(8) uint64_t bar_done[2];           // an accumulator buffer is final
+    __shared__ __align__(8) uint64_t bar_accfree[2];        // ... and has been read out (4 warp arrivals)
     __shared__ __align__(8) uint64_t bar_drain;             // failure path only: everything issued has completed
     __shared__ uint32_t s_tmem;
     __shared__ int s_fail;
 
-    const Fp4TcJob jb = a.jobs[blockIdx.y];
-    const int r0 = blockIdx.x * 128;
-    if (r0 >= jb.R || jb.ntok < 1) return;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nchunks = a.C >> 8, sc_row = a.C >> 4;
+    // this block's tiles: t = blockIdx.x, + gridDim.x, ... over (job, row tile); consecutive blocks take the
+    // row tiles of one job, so its activations stay in L2.  The launch keeps the list within FT_MAX_TILES.
+    const int total_tiles = a.njobs * a.tiles_per_job;
+    const int my_tiles = ((int)blockIdx.x < total_tiles) ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    for (int i = tid; i < my_tiles && i < FT_MAX_TILES; i += FT_THREADS) {
+        const int t = (int)blockIdx.x + i * (int)gridDim.x;
+        const int j = t / a.tiles_per_job, rt = t - j * a.tiles_per_job;
+        const Fp4TcJob jb = a.jobs[j];
+        Fp4Tile ti;
+        ti.w_scales = jb.w_scales; ti.x_scales = jb.x_scales; ti.y = jb.y; ti.wg = jb.wg; ti.ig = jb.ig;
+        ti.r0 = rt * 128; ti.w_row = jb.w_row0 + ti.r0; ti.w_slice = jb.w_slice; ti.x_row0 = jb.x_row0;
+        ti.ntok = ti.r0 < jb.R ? jb.ntok : 0; ti.R = jb.R; ti.y_stride = jb.y_stride;
+        s_tiles[i] = ti;
+    }
+    const int ntiles = min(my_tiles, FT_MAX_TILES);
     uint8_t* stage_base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    const int ntok_cap = min(jb.ntok, FT_MAX_NT);
-    const int variant = ntok_cap <= 16 ? 0 : ntok_cap <= 32 ? 1 : 2;
-    const uint32_t b_bytes = (16u << variant) * FT_KC_BYTES;
-    const int npass = (jb.ntok + FT_MAX_NT - 1) / FT_MAX_NT;
     volatile int* fail = &s_fail;
 
     if (tid == 0) {
@@ -115,7 +138,10 @@ nvfp4_gemm_tc_kernel(const Fp4TcArgs a, const __grid_constant__ Fp4TcMaps maps) 
             mbar_init(&bar_full[s], 1);
             mbar_init(&bar_sf[s], 4);
         }
-        mbar_init(&bar_done, 1);
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&bar_done[b], 1);
+            mbar_init(&bar_accfree[b], 4);
+        }
         mbar_init(&bar_drain, 1);
         s_fail = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -131,156 +157,193 @@ nvfp4_gemm_tc_kernel(const Fp4TcArgs a, const __grid_constant__ Fp4TcMaps maps) 
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = s_tmem;
 
+    // Every role walks the same sequence: tiles of the list that have tokens, their token passes ("units":
+    // one accumulator buffer each, alternating), the K chunks of a pass (one pipeline stage each).
     uint32_t produced = 0;                                   // producer: chunks requested so far
-    uint32_t it = 0;                                         // chunk counter across token passes
-    for (int pass = 0; pass < npass; pass++) {
-        const int tb = pass * FT_MAX_NT;
-        const int nt_real = min(FT_MAX_NT, jb.ntok - tb);
-        const int NT = (nt_real + 15) & ~15;
-
-        if (warp == 5) {
-            // ================= producer =================
-            if (lane == 0) {
-                for (int kc = 0; kc < nchunks; kc++, produced++) {
-                    const uint32_t s = produced % FT_STAGES;
-                    if (produced >= (uint32_t)FT_STAGES &&
-                        !mbar_wait(&bar_free[s], ((produced / FT_STAGES) - 1) & 1, fail))
-                        break;
-                    const uint32_t dst = smem_u32(stage_base + s * FT_STAGE_BYTES);
-                    mbar_expect_tx(&bar_full[s], FT_A_BYTES + b_bytes);
-                    tma_load_3d(dst, &maps.w, kc * FT_KC_BYTES, jb.w_row0 + r0, jb.w_slice, &bar_full[s]);
-                    tma_load_2d(dst + FT_A_BYTES, &maps.x[variant], kc * FT_KC_BYTES, jb.x_row0 + tb, &bar_full[s]);
-                }
-            }
-            __syncwarp();
-        } else if (warp == 4) {
-            // ================= issuer =================
-            const uint32_t idesc = umma_idesc_fp4(128, NT);
-            const uint32_t lo0 = DESC_B_LO | ((smem_u32(stage_base) & 0x3ffffu) >> 4);
-            uint32_t my = it;
-            for (int kc = 0; kc < nchunks; kc++, my++) {
-                const uint32_t s = my % FT_STAGES, ph = (my / FT_STAGES) & 1;
-                bool ok = mbar_wait(&bar_full[s], ph, fail);
-                if (ok) ok = mbar_wait(&bar_sf[s], ph, fail);
-                if (ok && lane == 0) {
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t alo = lo0 + s * (FT_STAGE_BYTES >> 4);
-                    const uint32_t blo = alo + (FT_A_BYTES >> 4);
-                    const uint32_t sf = tmem + FT_SF_BASE + s * FT_SF_STAGE;
-#pragma unroll
-                    for (int j = 0; j < 4; j++)          // K = 64 per MMA: 32 bytes further along the swizzled row
-                        umma_fp4(tmem, make_desc(alo + j * 2, DESC_B_HI), make_desc(blo + j * 2, DESC_B_HI), idesc,
-                                 sf + 4 * j, sf + FT_SFB_OFF + 4 * j, (kc > 0 || j > 0) ? 1u : 0u);
-                    umma_commit(&bar_free[s]);
-                    if (kc == nchunks - 1) umma_commit(&bar_done);
-                }
-                __syncwarp();
-                if (!ok) break;
-            }
-        } else {
-            // ================= scale warps =================
-            // lane l of every warp holds, per operand, the scale words of rows l, l + 32, l + 64, l + 96
-            const uint8_t* arow[4];
-            const uint8_t* brow[2];
-#pragma unroll
-            for (int c = 0; c < 4; c++) arow[c] = jb.w_scales + (size_t)min(r0 + lane + 32 * c, jb.R - 1) * sc_row;
-#pragma unroll
-            for (int c = 0; c < 2; c++) brow[c] = jb.x_scales + (size_t)min(tb + lane + 32 * c, jb.ntok - 1) * sc_row;
-            constexpr int DEPTH = 3;
-            uint4 ra[DEPTH][4], rb[DEPTH][2];
-#pragma unroll
-            for (int d = 0; d < DEPTH; d++) {
-                const int kq = min(d, nchunks - 1);
-#pragma unroll
-                for (int c = 0; c < 4; c++) ra[d][c] = ld_nc_v4(arow[c] + kq * 16);
-#pragma unroll
-                for (int c = 0; c < 2; c++) rb[d][c] = ld_nc_v4(brow[c] + kq * 16);
-            }
-            const uint32_t tlane = tmem + ((uint32_t)(warp * 32) << 16);
-            uint32_t my = it;
+    uint32_t issued_units = 0;                               // issuer: passes whose MMAs have been issued
+    if (warp == 9) {
+        // ================= producer =================
+        if (lane == 0) {
             bool ok = true;
-            for (int kc0 = 0; kc0 < nchunks && ok; kc0 += DEPTH) {
+            for (int i = 0; i < ntiles && ok; i++) {
+                const Fp4Tile& ti = s_tiles[i];
+                if (ti.ntok < 1) continue;
+                const int ntok_cap = min(ti.ntok, FT_MAX_NT);
+                const int variant = ntok_cap <= 16 ? 0 : ntok_cap <= 32 ? 1 : 2;
+                const uint32_t b_bytes = (16u << variant) * FT_KC_BYTES;
+                for (int tb = 0; tb < ti.ntok && ok; tb += FT_MAX_NT)
+                    for (int kc = 0; kc < nchunks; kc++, produced++) {
+                        const uint32_t s = produced % FT_STAGES;
+                        if (produced >= (uint32_t)FT_STAGES &&
+                            !mbar_wait(&bar_free[s], ((produced / FT_STAGES) - 1) & 1, fail)) {
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t dst = smem_u32(stage_base + s * FT_STAGE_BYTES);
+                        mbar_expect_tx(&bar_full[s], FT_A_BYTES + b_bytes);
+                        tma_load_3d(dst, &maps.w, kc * FT_KC_BYTES, ti.w_row, ti.w_slice, &bar_full[s]);
+                        tma_load_2d(dst + FT_A_BYTES, &maps.x[variant], kc * FT_KC_BYTES, ti.x_row0 + tb, &bar_full[s]);
+                    }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 8) {
+        // ================= issuer =================
+        const uint32_t lo0 = DESC_B_LO | ((smem_u32(stage_base) & 0x3ffffu) >> 4);
+        uint32_t my = 0;
+        bool ok = true;
+        for (int i = 0; i < ntiles && ok; i++) {
+            const Fp4Tile& ti = s_tiles[i];
+            if (ti.ntok < 1) continue;
+            for (int tb = 0; tb < ti.ntok && ok; tb += FT_MAX_NT, issued_units++) {
+                const int NT = (min(FT_MAX_NT, ti.ntok - tb) + 15) & ~15;
+                const uint32_t idesc = umma_idesc_fp4(128, NT);
+                const uint32_t buf = issued_units & 1u;
+                // the epilogue has read this buffer's previous contents
+                if (issued_units >= 2u) ok = mbar_wait(&bar_accfree[buf], ((issued_units >> 1) - 1) & 1, fail);
+                for (int kc = 0; kc < nchunks && ok; kc++, my++) {
+                    const uint32_t s = my % FT_STAGES, ph = (my / FT_STAGES) & 1;
+                    ok = mbar_wait(&bar_full[s], ph, fail);
+                    if (ok) ok = mbar_wait(&bar_sf[s], ph, fail);
+                    if (ok && lane == 0) {
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint32_t alo = lo0 + s * (FT_STAGE_BYTES >> 4);
+                        const uint32_t blo = alo + (FT_A_BYTES >> 4);
+                        const uint32_t sf = tmem + FT_SF_BASE + s * FT_SF_STAGE;
+#pragma unroll
+                        for (int j = 0; j < 4; j++)      // K = 64 per MMA: 32 bytes further along the swizzled row
+                            umma_fp4(tmem + buf * FT_MAX_NT, make_desc(alo + j * 2, DESC_B_HI),
+                                     make_desc(blo + j * 2, DESC_B_HI), idesc, sf + 4 * j, sf + FT_SFB_OFF + 4 * j,
+                                     (kc > 0 || j > 0) ? 1u : 0u);
+                        umma_commit(&bar_free[s]);
+                        if (kc == nchunks - 1) umma_commit(&bar_done[buf]);
+                    }
+                    __syncwarp();
+                }
+            }
+        }
+    } else if (warp < 4) {
+        // ================= scale warps =================
+        // lane l of every warp holds, per operand, the scale words of rows l, l + 32, l + 64, l + 96
+        const uint32_t tlane = tmem + ((uint32_t)(warp * 32) << 16);
+        uint32_t my = 0;
+        bool ok = true;
+        for (int i = 0; i < ntiles && ok; i++) {
+            const Fp4Tile& ti = s_tiles[i];
+            if (ti.ntok < 1) continue;
+            const uint8_t* arow[4];
+#pragma unroll
+            for (int c = 0; c < 4; c++) arow[c] = ti.w_scales + (size_t)min(ti.r0 + lane + 32 * c, ti.R - 1) * sc_row;
+            for (int tb = 0; tb < ti.ntok && ok; tb += FT_MAX_NT) {
+                const uint8_t* brow[2];
+#pragma unroll
+                for (int c = 0; c < 2; c++) brow[c] = ti.x_scales + (size_t)min(tb + lane + 32 * c, ti.ntok - 1) * sc_row;
+                constexpr int DEPTH = 2;
+                uint4 ra[DEPTH][4], rb[DEPTH][2];
 #pragma unroll
                 for (int d = 0; d < DEPTH; d++) {
-                    const int kc = kc0 + d;
-                    if (kc >= nchunks) break;
-                    const uint32_t s = my % FT_STAGES;
-                    uint32_t wa[16], wb[16];
+                    const int kq = min(d, nchunks - 1);
 #pragma unroll
-                    for (int c = 0; c < 4; c++) {      // column 4 j + c = K block j of row l + 32 c
-                        wa[c] = ra[d][c].x; wa[4 + c] = ra[d][c].y; wa[8 + c] = ra[d][c].z; wa[12 + c] = ra[d][c].w;
-                    }
+                    for (int c = 0; c < 4; c++) ra[d][c] = ld_nc_v4(arow[c] + kq * 16);
 #pragma unroll
-                    for (int c = 0; c < 4; c++) {
-                        const uint4 v = c < 2 ? rb[d][c] : make_uint4(0u, 0u, 0u, 0u);
-                        wb[c] = v.x; wb[4 + c] = v.y; wb[8 + c] = v.z; wb[12 + c] = v.w;
-                    }
-                    if (kc + DEPTH < nchunks) {
+                    for (int c = 0; c < 2; c++) rb[d][c] = ld_nc_v4(brow[c] + kq * 16);
+                }
+                for (int kc0 = 0; kc0 < nchunks && ok; kc0 += DEPTH) {
 #pragma unroll
-                        for (int c = 0; c < 4; c++) ra[d][c] = ld_nc_v4(arow[c] + (kc + DEPTH) * 16);
+                    for (int d = 0; d < DEPTH; d++) {
+                        const int kc = kc0 + d;
+                        if (kc >= nchunks) break;
+                        const uint32_t s = my % FT_STAGES;
+                        uint32_t wa[16], wb[16];
 #pragma unroll
-                        for (int c = 0; c < 2; c++) rb[d][c] = ld_nc_v4(brow[c] + (kc + DEPTH) * 16);
+                        for (int c = 0; c < 4; c++) {  // column 4 j + c = K block j of row l + 32 c
+                            wa[c] = ra[d][c].x; wa[4 + c] = ra[d][c].y; wa[8 + c] = ra[d][c].z; wa[12 + c] = ra[d][c].w;
+                        }
+#pragma unroll
+                        for (int c = 0; c < 4; c++) {
+                            const uint4 v = c < 2 ? rb[d][c] : make_uint4(0u, 0u, 0u, 0u);
+                            wb[c] = v.x; wb[4 + c] = v.y; wb[8 + c] = v.z; wb[12 + c] = v.w;
+                        }
+                        if (kc + DEPTH < nchunks) {
+#pragma unroll
+                            for (int c = 0; c < 4; c++) ra[d][c] = ld_nc_v4(arow[c] + (kc + DEPTH) * 16);
+#pragma unroll
+                            for (int c = 0; c < 2; c++) rb[d][c] = ld_nc_v4(brow[c] + (kc + DEPTH) * 16);
+                        }
+                        // the MMAs that last read this stage's scale columns must be complete
+                        if (my >= (uint32_t)FT_STAGES) ok = mbar_wait(&bar_free[s], ((my / FT_STAGES) - 1) & 1, fail);
+                        if (ok) {
+                            // order the stores after the completion just observed (they overwrite what those MMAs read)
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                            const uint32_t sf = tlane + FT_SF_BASE + s * FT_SF_STAGE;
+                            tmem_st16(sf, wa);
+                            tmem_st16(sf + FT_SFB_OFF, wb);
+                            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                        }
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&bar_sf[s]);   // always: the issuer never waits for a warp that gave up
+                        my++;
+                        if (!ok) break;
                     }
-                    // the MMAs that last read this stage's scale columns must be complete
-                    if (my >= (uint32_t)FT_STAGES) ok = mbar_wait(&bar_free[s], ((my / FT_STAGES) - 1) & 1, fail);
-                    if (ok) {
-                        // order the stores after the completion just observed (they overwrite what those MMAs read)
-                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        const uint32_t sf = tlane + FT_SF_BASE + s * FT_SF_STAGE;
-                        tmem_st16(sf, wa);
-                        tmem_st16(sf + FT_SFB_OFF, wb);
-                        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                    }
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&bar_sf[s]);   // always: the issuer never waits for a warp that gave up
-                    my++;
-                    if (!ok) break;
                 }
             }
         }
-        it += (uint32_t)nchunks;
-
-        // ================= epilogue of this token pass (warps 0-3) =================
-        if (warp < 4 && mbar_wait(&bar_done, pass & 1, fail)) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int m = r0 + warp * 32 + lane;
-            const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
-            for (int n0 = 0; n0 < NT; n0 += 32) {
-                uint32_t acc[32];
-                tmem_ld32(trow + n0, acc);
+    } else {
+        // ================= epilogue warps (4-7: TMEM lane quarter warp - 4) =================
+        const int q = warp - 4;
+        const uint32_t trow = tmem + ((uint32_t)(q * 32) << 16);
+        uint32_t unit = 0;
+        bool ok = true;
+        for (int i = 0; i < ntiles && ok; i++) {
+            const Fp4Tile& ti = s_tiles[i];
+            if (ti.ntok < 1) continue;
+            const int m = ti.r0 + q * 32 + lane;
+            for (int tb = 0; tb < ti.ntok && ok; tb += FT_MAX_NT, unit++) {
+                const int nt_real = min(FT_MAX_NT, ti.ntok - tb);
+                const int NT = (nt_real + 15) & ~15;
+                const uint32_t buf = unit & 1u;
+                ok = mbar_wait(&bar_done[buf], (unit >> 1) & 1, fail);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int n0 = 0; n0 < NT; n0 += 32) {
+                    uint32_t acc[32];
+                    tmem_ld32(trow + buf * FT_MAX_NT + n0, acc);
 #pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    const int n = n0 + i;
-                    if (n < nt_real && m < jb.R)
-                        jb.y[(size_t)(tb + n) * jb.y_stride + m] = __fdiv_rn(__fmul_rn(__uint_as_float(acc[i]), jb.wg), jb.ig);
+                    for (int k = 0; k < 32; k++) {
+                        const int n = n0 + k;
+                        if (n < nt_real && m < ti.R)
+                            ti.y[(size_t)(tb + n) * ti.y_stride + m] =
+                                __fdiv_rn(__fmul_rn(__uint_as_float(acc[k]), ti.wg), ti.ig);
+                    }
                 }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_accfree[buf]);
             }
         }
-        // all accumulator reads of this pass precede the next pass' first MMA
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (*fail) break;
     }
+
+    __syncthreads();
     if (*fail) {
         if (tid == 0 && a.status) atomicOr(a.status, SB_ERR_TIMEOUT);
         // wait (bounded, no early exit) for the copies requested and the MMAs issued before TMEM and shared
-        // memory are released: every requested stage either completes its copy (bar_full) ...
-        if (warp == 5 && lane == 0) {
+        // memory are released: every requested stage completes its copy (bar_full) ...
+        if (warp == 9 && lane == 0) {
             int none = 0;
             for (uint32_t t = (produced > (uint32_t)FT_STAGES ? produced - FT_STAGES : 0); t < produced; t++)
                 (void)mbar_wait(&bar_full[t % FT_STAGES], (t / FT_STAGES) & 1, &none);
         }
         __syncthreads();
         // ... and the tensor core has drained: one more commit tracks everything issued so far
-        if (warp == 4 && lane == 0) {
+        if (warp == 8 && lane == 0) {
             int none = 0;
             umma_commit(&bar_drain);
             (void)mbar_wait(&bar_drain, 0, &none);
         }
         __syncthreads();
     }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(FT_TMEM_COLS) : "memory");
     }
@@ -329,9 +392,16 @@ cudaError_t launch_nvfp4_gemm_tc(const Fp4TcJob* jobs, int njobs, int R, int C, 
     if ((C % 256) != 0) return cudaErrorInvalidValue;
     cudaError_t e = ensure_dynamic_smem((const void*)nvfp4_gemm_tc_kernel, (size_t)FT_SMEM_BYTES);
     if (e != cudaSuccess) return e;
+    int dev = 0, sms = 0;
+    if ((e = cudaGetDevice(&dev)) != cudaSuccess ||
+        (e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess)
+        return e;
     Fp4TcArgs a;
-    a.jobs = jobs; a.C = C; a.status = status;
-    dim3 grid((R + 127) / 128, njobs);
+    a.jobs = jobs; a.njobs = njobs; a.tiles_per_job = (R + 127) / 128; a.C = C; a.status = status;
+    // persistent blocks, one per SM (the whole shared memory and all of TMEM each); more only when a block's
+    // tile list would not hold its share
+    const int total = njobs * a.tiles_per_job;
+    const int grid = std::max(std::min(sms, total), (total + FT_MAX_TILES - 1) / FT_MAX_TILES);
     nvfp4_gemm_tc_kernel<<<grid, FT_THREADS, FT_SMEM_BYTES, stream>>>(a, maps);
     return cudaGetLastError();
 }

@@ -100,6 +100,14 @@ class MoeStack:
             raise RuntimeError("salt_b200_stack_workspace failed")
         return w
 
+    def nvfp4_buffers(self):
+        """Device addresses (gate, up, chain_codes, chain_scales) of the NVFP4 intermediates of the last
+        ``layer_experts`` call."""
+        b = (C.c_void_p * 4)()
+        if self.lib.salt_b200_stack_nvfp4_buffers(self.handle, b) != 0:
+            raise RuntimeError("salt_b200_stack_nvfp4_buffers failed")
+        return tuple(int(v or 0) for v in b)
+
     def set_fused_decode(self, enable):
         """Batches of up to 4 tokens: one-launch expert kernel (default) or the two-launch form."""
         return self.lib.salt_b200_stack_set_fused_decode(self.handle, int(bool(enable)))

@@ -2,8 +2,13 @@
 
 Stated tolerance against the exact path (the CPU oracle composition at the small sizes, the bit-exact GPU
 kernels - themselves pinned to the oracle - at config-4 size): max |y - y_ref| / max(|y_ref|, rms(y_ref row))
-<= 1e-3.  Router, top-k and grouping stay bit-exact; the activation codes and block scales are the
-bit-exact quantiser's, so only the order of the fp32 additions differs."""
+<= 1e-3, for the gate and up projections and for every output row whose quantised GeGLU activations are
+the same in both paths.  Router, top-k and grouping stay bit-exact; the activation codes and block scales
+come from the bit-exact quantiser, so a projection differs only by the order of its fp32 additions (about
+1e-6).  The quantiser between the two projection batches is discontinuous, though: a last-bit difference in
+one gate or up output can move a block scale or a code of that row to the neighbouring value (W4A4 does this
+to any two implementations that differ in rounding).  Such rows are counted, must be rare (<= 3 %) and stay
+within the quantisation noise (<= 0.1)."""
 import numpy as np
 import pytest
 
@@ -16,19 +21,50 @@ pytestmark = pytest.mark.gpu
 TOL = 1e-3
 
 
-def _run(st, x, B, H, tensor_core):
+def _run(st, x, B, H, tensor_core, stages=None):
+    """Layer output; with ``stages`` (a dict) also the intermediates in grouped order."""
     import torch
     d_x = torch.from_numpy(x).cuda()
     d_y = torch.zeros(B, H, dtype=torch.float32, device="cuda")
     assert st.layer_experts(0, d_x.data_ptr(), B, tensor_core=tensor_core) == 0
+    if stages is not None:
+        J, M = B * st.topk, st.inter
+        gate, up, codes, scales = st.nvfp4_buffers()
+        stages["gate"] = d2h(gate, J * M, np.float32).reshape(J, M)
+        stages["up"] = d2h(up, J * M, np.float32).reshape(J, M)
+        stages["codes"] = d2h(codes, J * M // 2, np.uint8).reshape(J, M // 2)
+        stages["scales"] = d2h(scales, J * M // 16, np.uint8).reshape(J, M // 16)
+        stages["grouped"] = d2h(st.workspace().grouped_out, J * H, np.float32).reshape(J, H)
     assert st.layer_combine(0, B, d_y.data_ptr(), apply_norm=False) == 0
     assert st.status() == 0
     return d_y.cpu().numpy()
 
 
-def _rel_err(y, ref):
+def _check_stages(tc, ex, label):
+    """Stage-wise comparison of the tensor-core run against the exact run of the same stack."""
+    for k in ("gate", "up"):
+        err = _rel_err(tc[k], ex[k])
+        assert err <= TOL, (label, k, err)
+    same = (tc["codes"] == ex["codes"]).all(axis=1) & (tc["scales"] == ex["scales"]).all(axis=1)
+    row_err = _row_err(tc["grouped"], ex["grouped"])
+    flipped = int((~same).sum())
+    print(f"{label}: gate/up within {TOL}; {flipped} of {same.size} rows with a moved quantiser decision; "
+          f"down max error {row_err[same].max():.3e} on the others, {row_err[~same].max() if flipped else 0.0:.3e} on those")
+    assert row_err[same].max() <= TOL
+    assert flipped <= max(1, int(0.03 * same.size))
+    if flipped:
+        assert row_err[~same].max() <= 0.1
+    return same
+
+
+def _row_err(y, ref):
     rms = np.sqrt((ref.astype(np.float64) ** 2).mean(axis=1, keepdims=True))
-    return float((np.abs(y.astype(np.float64) - ref) / np.maximum(np.abs(ref), rms)).max())
+    rms = np.where(rms == 0, 1.0, rms)
+    return (np.abs(y.astype(np.float64) - ref) / np.maximum(np.abs(ref), rms)).max(axis=1)
+
+
+def _rel_err(y, ref):
+    return float(_row_err(y, ref).max())
 
 
 # (hidden, inter, experts, top-k, tokens): groups of about 10, 75 (two token passes) and 1-3 tokens
@@ -39,15 +75,21 @@ def test_nvfp4_tensor_core_layer_vs_oracle(orc, synth, geom):
     x = synth.make_tokens(4501 + B, B, H)
     st = stack_mod().MoeStack(B, H, M, E, K)
     st.add_nvfp4_layer(layer)
-    y = _run(st, x, B, H, True)
+    tc, ex = {}, {}
+    y = _run(st, x, B, H, True, tc)
     want, sel, w = oracle.moe_layer_nvfp4(orc, layer, x, threads=16)
     ws = st.workspace()
     assert_bits_equal(d2h(ws.selected, B * K, np.int32).reshape(B, K), sel, "selected (exact)")
     assert_bits_equal(d2h(ws.weights, B * K, np.float32).reshape(B, K), w, "weights (exact)")
-    err = _rel_err(y, want)
-    print(f"nvfp4 tensor-core layer H={H} M={M} B={B}: max relative error {err:.3e}")
+    assert_bits_equal(_run(st, x, B, H, False, ex), want, "exact path on the same stack")
+    same = _check_stages(tc, ex, f"nvfp4 tensor-core layer H={H} M={M} B={B}")
+    # a token all of whose selections kept their quantiser decisions is within tolerance end to end
+    g2c = d2h(ws.grouped_to_canonical, B * K, np.int32)
+    clean = np.ones(B, bool)
+    clean[g2c[~same] // K] = False
+    err = _rel_err(y[clean], want[clean])
+    print(f"   layer output of the {int(clean.sum())} unaffected tokens: max relative error {err:.3e}")
     assert err <= TOL, err
-    assert_bits_equal(_run(st, x, B, H, False), want, "exact path on the same stack")
     st.close()
 
 
@@ -58,10 +100,15 @@ def test_nvfp4_tensor_core_cfg4_vs_exact_kernels(synth, B):
     x = synth.make_tokens(4600 + B, B, layer.hidden)
     st = stack_mod().MoeStack(B, layer.hidden, layer.inter, layer.n_experts, layer.topk)
     st.add_nvfp4_layer(layer)
-    y = _run(st, x, B, layer.hidden, True)
-    want = _run(st, x, B, layer.hidden, False)
-    err = _rel_err(y, want)
-    print(f"nvfp4 tensor-core cfg 4 B={B}: max relative error {err:.3e}")
+    tc, ex = {}, {}
+    y = _run(st, x, B, layer.hidden, True, tc)
+    want = _run(st, x, B, layer.hidden, False, ex)
+    same = _check_stages(tc, ex, f"nvfp4 tensor-core cfg 4 B={B}")
+    g2c = d2h(st.workspace().grouped_to_canonical, B * layer.topk, np.int32)
+    clean = np.ones(B, bool)
+    clean[g2c[~same] // layer.topk] = False
+    err = _rel_err(y[clean], want[clean])
+    print(f"   layer output of the {int(clean.sum())} unaffected tokens: max relative error {err:.3e}")
     assert err <= TOL, err
     assert_bits_equal(_run(st, x, B, layer.hidden, True), y, "run to run")
     st.close()
