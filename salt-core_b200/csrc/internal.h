@@ -146,21 +146,22 @@ cudaError_t launch_nvfp4_moe_plan(const int* group_offsets, int E, int expert_be
                                   const Fp4ExpertDesc* experts, int H, int M, const float* dq_gu, float* gate_out,
                                   float* up_out, const float* dq_dn, float* grouped_out, Fp4Job* gu_jobs, Fp4Job* dn_jobs,
                                   float* ig_gu, float* ig_dn, cudaStream_t stream, struct Fp4TcJob* tc_gu = nullptr,
-                                  struct Fp4TcJob* tc_dn = nullptr, const uint8_t* x_scales = nullptr);
+                                  struct Fp4TcJob* tc_dn = nullptr);
 // ---- nvfp4_gemm_tc.cu: block-scaled tensor-core form of a grouped NVFP4 projection (tolerance path) ----
 struct Fp4TcJob {
-    const uint8_t* w_scales;   // [R][C/16] E4M3 block scales of the weight matrix (row-major, as stored)
-    const uint8_t* x_scales;   // [ntok][C/16] block scales of the job's quantised activations
     float* y;                  // y[n * y_stride + m]
     float wg, ig;              // 1 / weight divisor, input global scale: y = acc * wg / ig
-    int w_row0, w_slice;       // the matrix' first row and expert slice in the layer's weight map
-    int x_row0;                // the job's first row in the packed-activation map
+    int w_row0, ws_row0;       // the matrix' first row in the layer's code map and in its scale map
+    int w_slice;               // the expert's slice in both
+    int x_row0;                // the job's first row in the packed-activation map and in its scale map
     int ntok, R, y_stride;
 };
 struct Fp4TcMaps {
-    CUtensorMap w;             // weights: bytes x rows x experts
-    CUtensorMap x[3];          // packed activations: boxes of 16 / 32 / 64 rows
+    CUtensorMap w, ws;         // weight codes and their block scales: bytes x rows x experts
+    CUtensorMap x[3], xs[3];   // packed activations and their block scales: boxes of 16 / 32 / 64 rows
 };
+cudaError_t make_fp4_weight_scale_map(CUtensorMap* out, const void* base, int C, int rows, int slices, size_t slice_stride);
+cudaError_t make_fp4_act_scale_maps(CUtensorMap* out3, const void* base, int C, int rows);
 cudaError_t make_fp4_weight_map(CUtensorMap* out, const void* base, int C, int rows, int slices, size_t slice_stride);
 cudaError_t make_fp4_act_maps(CUtensorMap* out3, const void* base, int C, int rows);
 cudaError_t launch_nvfp4_gemm_tc(const Fp4TcJob* jobs, int njobs, int R, int C, const Fp4TcMaps& maps, int* status,

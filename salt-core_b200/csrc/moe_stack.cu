@@ -39,6 +39,7 @@ struct Layer {
     Fp4ExpertDesc* fp4_experts = nullptr;      // [local experts] device
     bool fp4_tc_ok = false;                    // every block scale is an unsigned finite E4M3 code: the tensor core can take it
     CUtensorMap fp4_w_gu, fp4_w_dn;            // weight maps of the tensor-core form (gate | up rows; down rows)
+    CUtensorMap fp4_ws_gu, fp4_ws_dn;          // ... and of their block scales
     // optional dense branch and norms of the whole feed-forward block
     bool ffn = false;
     int dense_inter = 0;
@@ -75,6 +76,7 @@ struct Stack {
     Fp4Job *fp4_gu_jobs = nullptr, *fp4_dn_jobs = nullptr;
     Fp4TcJob *fp4_tc_gu = nullptr, *fp4_tc_dn = nullptr;
     CUtensorMap fp4_x_gu[3], fp4_x_dn[3];      // packed activations as [2J][H/2] and as [J][M/2]
+    CUtensorMap fp4_xs_gu[3], fp4_xs_dn[3];    // their block scales as [2J][H/16] and as [J][M/16]
     bool fp4_maps_ok = false;
     bool fused_decode = true;                  // batches of up to FUSED_MAX_TOKENS tokens take the one-launch expert kernel
     void *xh = nullptr, *xl = nullptr, *chain_h = nullptr, *chain_l = nullptr;   // fp16 operands (hi, lo) of the tensor-core path
@@ -267,7 +269,9 @@ int salt_b200_stack_add_nvfp4_layer(void* stack, const SaltB200Nvfp4LayerSpec* s
         return -1;
     if (!s->fp4_maps_ok)
         s->fp4_maps_ok = make_fp4_act_maps(s->fp4_x_gu, s->fp4_packed, s->hidden, (int)(2 * J)) == cudaSuccess &&
-                         make_fp4_act_maps(s->fp4_x_dn, s->fp4_packed, s->inter, (int)J) == cudaSuccess;
+                         make_fp4_act_maps(s->fp4_x_dn, s->fp4_packed, s->inter, (int)J) == cudaSuccess &&
+                         make_fp4_act_scale_maps(s->fp4_xs_gu, s->fp4_scales, s->hidden, (int)(2 * J)) == cudaSuccess &&
+                         make_fp4_act_scale_maps(s->fp4_xs_dn, s->fp4_scales, s->inter, (int)J) == cudaSuccess;
     Layer l;
     l.eps = spec->eps;
     l.expert_stride = spec->expert_stride;
@@ -305,7 +309,11 @@ int salt_b200_stack_add_nvfp4_layer(void* stack, const SaltB200Nvfp4LayerSpec* s
         const int M = s->inter, H = s->hidden;
         l.fp4_tc_ok = plain &&
                       make_fp4_weight_map(&l.fp4_w_gu, l.pool, H, 2 * M + M / 8, (int)local, spec->expert_stride) == cudaSuccess &&
-                      make_fp4_weight_map(&l.fp4_w_dn, l.pool + 2 * tensor_bytes, M, H, (int)local, spec->expert_stride) == cudaSuccess;
+                      make_fp4_weight_map(&l.fp4_w_dn, l.pool + 2 * tensor_bytes, M, H, (int)local, spec->expert_stride) == cudaSuccess &&
+                      make_fp4_weight_scale_map(&l.fp4_ws_gu, l.pool + code_bytes, H, 10 * M, (int)local,
+                                                spec->expert_stride) == cudaSuccess &&
+                      make_fp4_weight_scale_map(&l.fp4_ws_dn, l.pool + 2 * tensor_bytes + code_bytes, M, H, (int)local,
+                                                spec->expert_stride) == cudaSuccess;
     }
     if (!ok) {
         cudaFree(l.router_w); cudaFree(l.router_scale); cudaFree(l.per_expert_scale); cudaFree(l.pool);
@@ -437,11 +445,15 @@ static int layer_experts_impl(Stack* s, int layer, const float* d_router_src, co
         Timed t(s, KC_GATE_UP, st);
         Fp4TcMaps mg, md;
         mg.w = l.fp4_w_gu; md.w = l.fp4_w_dn;
-        for (int v = 0; v < 3; v++) { mg.x[v] = s->fp4_x_gu[v]; md.x[v] = s->fp4_x_dn[v]; }
+        mg.ws = l.fp4_ws_gu; md.ws = l.fp4_ws_dn;
+        for (int v = 0; v < 3; v++) {
+            mg.x[v] = s->fp4_x_gu[v]; md.x[v] = s->fp4_x_dn[v];
+            mg.xs[v] = s->fp4_xs_gu[v]; md.xs[v] = s->fp4_xs_dn[v];
+        }
         if (!cuda_ok(launch_nvfp4_moe_plan(s->group_offsets, E, s->expert_begin, s->expert_end, jobs, l.fp4_experts, H, M,
                                            s->fp4_dq_gu, s->fp4_gate, s->fp4_up, s->fp4_dq_dn, s->grouped_out,
                                            s->fp4_gu_jobs, s->fp4_dn_jobs, s->fp4_ig_gu, s->fp4_ig_dn, st, s->fp4_tc_gu,
-                                           s->fp4_tc_dn, s->fp4_scales), "nvfp4 plan") ||
+                                           s->fp4_tc_dn), "nvfp4 plan") ||
             !cuda_ok(launch_nvfp4_qdq(d_x, 2 * jobs, H, s->fp4_ig_gu, s->fp4_packed, s->fp4_scales, nullptr,
                                       s->status, st, s->g2c, jobs, K), "nvfp4 qdq x") ||
             !cuda_ok(launch_nvfp4_gemm_tc(s->fp4_tc_gu, 2 * E, M, H, mg, s->status, st), "nvfp4 tc gate/up") ||

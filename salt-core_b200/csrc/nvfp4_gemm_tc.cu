@@ -9,19 +9,19 @@
 // tests; the bound is 1e-3 of max(|ref|, row rms)).  Activation codes and scales come from the bit-exact
 // quantiser (nvfp4_qdq_kernel), so the only difference is the order of the additions.
 //
-// One block = one 128-row tile of one weight matrix of one expert; the weight rows sit on the MMA M
-// dimension, the expert's tokens on N (16, 32 or 64 per pass), K advances in chunks of 256 columns = one
-// 128-byte row of packed codes = four MMAs of K = 64.  Two blocks fit an SM (100 KB of shared memory,
-// 256 TMEM columns each).  Warp roles:
-//   warp 5      producer: TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) of the weight tile
-//               (3-D map: byte column, row, expert) and of the tokens' packed activations (2-D map)
-//   warps 0-3   scale warps: load the 16 scale bytes of their rows for the chunk (weights: row-major
-//               [R][C/16], reference layout src/nvfp4.c:147-149; activations: the quantiser's output) and
-//               place them in TMEM with tcgen05.st in the layout the MMA reads - row r of a 128-row operand
-//               in lane r % 32 of every 32-lane quarter, 32-bit column r / 32, byte j = K block j of the
-//               MMA - so no shared-memory staging or rearranged copy of the scales is needed; later the
-//               same warps run the epilogue (tcgen05.ld, scalars, store)
-//   warp 4      issuer: waits for the stage's data and scales, issues the four MMAs, tcgen05.commit
+// One tile = 128 rows of one weight matrix of one expert; the weight rows sit on the MMA M dimension, the
+// expert's tokens on N (16, 32 or 64 per pass), K advances in chunks of 256 columns = one 128-byte row of
+// packed codes = four MMAs of K = 64.  Blocks are persistent, one per SM: each walks its share of the
+// launch's tiles with the copy pipeline running across tile boundaries.  Warp roles:
+//   warp 9      producer: TMA (cp.async.bulk.tensor, no multicast) of the weight tile (3-D map: byte column,
+//               row, expert; 128-byte swizzle), of the tokens' packed activations (2-D map), and of the chunk's
+//               16 scale bytes of every weight row (row-major [R][C/16], reference layout
+//               src/nvfp4.c:147-149) and token row (the quantiser's output), eight stages ahead
+//   warps 0-3   scale warps: move the stage's scale bytes from shared memory into TMEM with tcgen05.st in the
+//               layout the MMA reads - row r of a 128-row operand in lane r % 32 of every 32-lane quarter,
+//               32-bit column r / 32, byte j = K block j of the MMA - so the scales need no rearranged copy
+//   warp 8      issuer: waits for the stage's data and scales, issues the four MMAs, tcgen05.commit
+//   warps 4-7   epilogue: tcgen05.ld of a finished accumulator buffer (two alternate), scalars, store
 // Every mbarrier wait is bounded; on expiry the block raises its failure flag, sets SB_ERR_TIMEOUT, waits
 // (bounded) for copies and MMAs in flight, frees its TMEM and returns.
 #include <algorithm>
@@ -36,9 +36,11 @@ constexpr int FT_THREADS = 320;                   // warps 0-3 scales, 4-7 epilo
 constexpr int FT_KC_BYTES = 128;                  // packed bytes of a K chunk (256 columns)
 constexpr int FT_A_BYTES = 128 * FT_KC_BYTES;     // 128 weight rows
 constexpr int FT_MAX_NT = 64;                     // tokens per pass
-constexpr int FT_STAGE_BYTES = FT_A_BYTES + FT_MAX_NT * FT_KC_BYTES;
+constexpr int FT_B_BYTES = FT_MAX_NT * FT_KC_BYTES;
+constexpr int FT_SFA_BYTES = 128 * 16, FT_SFB_BYTES = FT_MAX_NT * 16;   // 16 scale bytes per row and chunk
+constexpr int FT_STAGE_BYTES = FT_A_BYTES + FT_B_BYTES + FT_SFA_BYTES + FT_SFB_BYTES;
 constexpr int FT_SMEM_BYTES = FT_STAGES * FT_STAGE_BYTES + 1024;
-constexpr int FT_MAX_TILES = 64;                  // tiles of one block's list
+constexpr int FT_MAX_TILES = 48;                  // tiles of one block's list
 constexpr uint32_t FT_TMEM_COLS = 512;            // accumulators at 0..63 and 64..127, scale stages from 128
 constexpr uint32_t FT_SF_BASE = 128, FT_SF_STAGE = 32, FT_SFB_OFF = 16;
 
@@ -77,12 +79,6 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         : "memory");
 }
 
-__device__ __forceinline__ uint4 ld_nc_v4(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-
 struct Fp4TcArgs {
     const Fp4TcJob* jobs;
     int njobs, tiles_per_job;
@@ -92,11 +88,9 @@ struct Fp4TcArgs {
 
 // One tile of a block's list: the job's fields every role needs, and the tile's first weight row.
 struct Fp4Tile {
-    const uint8_t* w_scales;
-    const uint8_t* x_scales;
     float* y;
     float wg, ig;
-    int w_row, w_slice, x_row0, ntok, R, y_stride, r0;
+    int w_row, ws_row, w_slice, x_row0, ntok, R, y_stride, r0;
 };
 
 __global__ void __launch_bounds__(FT_THREADS, 1)
@@ -113,7 +107,7 @@ nvfp4_gemm_tc_kernel(const Fp4TcArgs a, const __grid_constant__ Fp4TcMaps maps) 
     __shared__ int s_fail;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int nchunks = a.C >> 8, sc_row = a.C >> 4;
+    const int nchunks = a.C >> 8;
     // this block's tiles: t = blockIdx.x, + gridDim.x, ... over (job, row tile); consecutive blocks take the
     // row tiles of one job, so its activations stay in L2.  The launch keeps the list within FT_MAX_TILES.
     const int total_tiles = a.njobs * a.tiles_per_job;
@@ -123,8 +117,9 @@ nvfp4_gemm_tc_kernel(const Fp4TcArgs a, const __grid_constant__ Fp4TcMaps maps) 
         const int j = t / a.tiles_per_job, rt = t - j * a.tiles_per_job;
         const Fp4TcJob jb = a.jobs[j];
         Fp4Tile ti;
-        ti.w_scales = jb.w_scales; ti.x_scales = jb.x_scales; ti.y = jb.y; ti.wg = jb.wg; ti.ig = jb.ig;
-        ti.r0 = rt * 128; ti.w_row = jb.w_row0 + ti.r0; ti.w_slice = jb.w_slice; ti.x_row0 = jb.x_row0;
+        ti.y = jb.y; ti.wg = jb.wg; ti.ig = jb.ig;
+        ti.r0 = rt * 128; ti.w_row = jb.w_row0 + ti.r0; ti.ws_row = jb.ws_row0 + ti.r0; ti.w_slice = jb.w_slice;
+        ti.x_row0 = jb.x_row0;
         ti.ntok = ti.r0 < jb.R ? jb.ntok : 0; ti.R = jb.R; ti.y_stride = jb.y_stride;
         s_tiles[i] = ti;
     }
@@ -170,7 +165,7 @@ nvfp4_gemm_tc_kernel(const Fp4TcArgs a, const __grid_constant__ Fp4TcMaps maps) 
                 if (ti.ntok < 1) continue;
                 const int ntok_cap = min(ti.ntok, FT_MAX_NT);
                 const int variant = ntok_cap <= 16 ? 0 : ntok_cap <= 32 ? 1 : 2;
-                const uint32_t b_bytes = (16u << variant) * FT_KC_BYTES;
+                const uint32_t stage_tx = FT_A_BYTES + FT_SFA_BYTES + (16u << variant) * (FT_KC_BYTES + 16u);
                 for (int tb = 0; tb < ti.ntok && ok; tb += FT_MAX_NT)
                     for (int kc = 0; kc < nchunks; kc++, produced++) {
                         const uint32_t s = produced % FT_STAGES;
@@ -180,9 +175,12 @@ nvfp4_gemm_tc_kernel(const Fp4TcArgs a, const __grid_constant__ Fp4TcMaps maps) 
                             break;
                         }
                         const uint32_t dst = smem_u32(stage_base + s * FT_STAGE_BYTES);
-                        mbar_expect_tx(&bar_full[s], FT_A_BYTES + b_bytes);
+                        mbar_expect_tx(&bar_full[s], stage_tx);
                         tma_load_3d(dst, &maps.w, kc * FT_KC_BYTES, ti.w_row, ti.w_slice, &bar_full[s]);
                         tma_load_2d(dst + FT_A_BYTES, &maps.x[variant], kc * FT_KC_BYTES, ti.x_row0 + tb, &bar_full[s]);
+                        tma_load_3d(dst + FT_A_BYTES + FT_B_BYTES, &maps.ws, kc * 16, ti.ws_row, ti.w_slice, &bar_full[s]);
+                        tma_load_2d(dst + FT_A_BYTES + FT_B_BYTES + FT_SFA_BYTES, &maps.xs[variant], kc * 16,
+                                    ti.x_row0 + tb, &bar_full[s]);
                     }
             }
         }
@@ -224,70 +222,46 @@ nvfp4_gemm_tc_kernel(const Fp4TcArgs a, const __grid_constant__ Fp4TcMaps maps) 
         }
     } else if (warp < 4) {
         // ================= scale warps =================
-        // lane l of every warp holds, per operand, the scale words of rows l, l + 32, l + 64, l + 96
+        // The producer's copies leave the chunk's 16 scale bytes of every row in the stage (weights: 128 rows,
+        // activations: the pass' token rows).  Lane l of every warp takes, per operand, the words of rows l,
+        // l + 32, l + 64, l + 96 and stores them to its TMEM lane as 16 columns: column 4 j + c = K block j
+        // (the MMA's K = 64) of row l + 32 c.
         const uint32_t tlane = tmem + ((uint32_t)(warp * 32) << 16);
         uint32_t my = 0;
         bool ok = true;
         for (int i = 0; i < ntiles && ok; i++) {
             const Fp4Tile& ti = s_tiles[i];
             if (ti.ntok < 1) continue;
-            const uint8_t* arow[4];
-#pragma unroll
-            for (int c = 0; c < 4; c++) arow[c] = ti.w_scales + (size_t)min(ti.r0 + lane + 32 * c, ti.R - 1) * sc_row;
-            for (int tb = 0; tb < ti.ntok && ok; tb += FT_MAX_NT) {
-                const uint8_t* brow[2];
-#pragma unroll
-                for (int c = 0; c < 2; c++) brow[c] = ti.x_scales + (size_t)min(tb + lane + 32 * c, ti.ntok - 1) * sc_row;
-                constexpr int DEPTH = 2;
-                uint4 ra[DEPTH][4], rb[DEPTH][2];
-#pragma unroll
-                for (int d = 0; d < DEPTH; d++) {
-                    const int kq = min(d, nchunks - 1);
-#pragma unroll
-                    for (int c = 0; c < 4; c++) ra[d][c] = ld_nc_v4(arow[c] + kq * 16);
-#pragma unroll
-                    for (int c = 0; c < 2; c++) rb[d][c] = ld_nc_v4(brow[c] + kq * 16);
-                }
-                for (int kc0 = 0; kc0 < nchunks && ok; kc0 += DEPTH) {
-#pragma unroll
-                    for (int d = 0; d < DEPTH; d++) {
-                        const int kc = kc0 + d;
-                        if (kc >= nchunks) break;
-                        const uint32_t s = my % FT_STAGES;
+            for (int tb = 0; tb < ti.ntok && ok; tb += FT_MAX_NT)
+                for (int kc = 0; kc < nchunks && ok; kc++, my++) {
+                    const uint32_t s = my % FT_STAGES;
+                    // landed copies also mean that the MMAs which last read this stage's scale columns are
+                    // complete: the producer refilled the stage only after their commit
+                    ok = mbar_wait(&bar_full[s], (my / FT_STAGES) & 1, fail);
+                    if (ok) {
+                        const uint4* sfa = (const uint4*)(stage_base + s * FT_STAGE_BYTES + FT_A_BYTES + FT_B_BYTES);
+                        const uint4* sfb = sfa + FT_SFA_BYTES / 16;
                         uint32_t wa[16], wb[16];
 #pragma unroll
-                        for (int c = 0; c < 4; c++) {  // column 4 j + c = K block j of row l + 32 c
-                            wa[c] = ra[d][c].x; wa[4 + c] = ra[d][c].y; wa[8 + c] = ra[d][c].z; wa[12 + c] = ra[d][c].w;
+                        for (int c = 0; c < 4; c++) {
+                            const uint4 v = sfa[lane + 32 * c];
+                            wa[c] = v.x; wa[4 + c] = v.y; wa[8 + c] = v.z; wa[12 + c] = v.w;
                         }
 #pragma unroll
                         for (int c = 0; c < 4; c++) {
-                            const uint4 v = c < 2 ? rb[d][c] : make_uint4(0u, 0u, 0u, 0u);
+                            const uint4 v = c < FT_MAX_NT / 32 ? sfb[lane + 32 * c] : make_uint4(0u, 0u, 0u, 0u);
                             wb[c] = v.x; wb[4 + c] = v.y; wb[8 + c] = v.z; wb[12 + c] = v.w;
                         }
-                        if (kc + DEPTH < nchunks) {
-#pragma unroll
-                            for (int c = 0; c < 4; c++) ra[d][c] = ld_nc_v4(arow[c] + (kc + DEPTH) * 16);
-#pragma unroll
-                            for (int c = 0; c < 2; c++) rb[d][c] = ld_nc_v4(brow[c] + (kc + DEPTH) * 16);
-                        }
-                        // the MMAs that last read this stage's scale columns must be complete
-                        if (my >= (uint32_t)FT_STAGES) ok = mbar_wait(&bar_free[s], ((my / FT_STAGES) - 1) & 1, fail);
-                        if (ok) {
-                            // order the stores after the completion just observed (they overwrite what those MMAs read)
-                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                            const uint32_t sf = tlane + FT_SF_BASE + s * FT_SF_STAGE;
-                            tmem_st16(sf, wa);
-                            tmem_st16(sf + FT_SFB_OFF, wb);
-                            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                        }
-                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&bar_sf[s]);   // always: the issuer never waits for a warp that gave up
-                        my++;
-                        if (!ok) break;
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint32_t sf = tlane + FT_SF_BASE + s * FT_SF_STAGE;
+                        tmem_st16(sf, wa);
+                        tmem_st16(sf + FT_SFB_OFF, wb);
+                        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                     }
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bar_sf[s]);   // always: the issuer never waits for a warp that gave up
                 }
-            }
         }
     } else {
         // ================= epilogue warps (4-7: TMEM lane quarter warp - 4) =================
@@ -366,6 +340,41 @@ cudaError_t make_fp4_weight_map(CUtensorMap* out, const void* base, int C, int r
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+// Scale maps: the same shapes with 16 bytes (one chunk's block scales) per row, unswizzled.
+cudaError_t make_fp4_weight_scale_map(CUtensorMap* out, const void* base, int C, int rows, int slices, size_t slice_stride) {
+    TensorMapEncodeFn encode = nullptr;
+    cudaError_t e = tensor_map_encoder(&encode);
+    if (e != cudaSuccess) return e;
+    if ((C % 256) != 0 || rows < 1 || slices < 1 || (slice_stride % 16) != 0 || ((uintptr_t)base % 16) != 0)
+        return cudaErrorInvalidValue;
+    cuuint64_t dims[3] = {(cuuint64_t)(C / 16), (cuuint64_t)rows, (cuuint64_t)slices};
+    cuuint64_t strides[2] = {(cuuint64_t)(C / 16), (cuuint64_t)slice_stride};
+    cuuint32_t box[3] = {16u, 128u, 1u};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+cudaError_t make_fp4_act_scale_maps(CUtensorMap* out3, const void* base, int C, int rows) {
+    TensorMapEncodeFn encode = nullptr;
+    cudaError_t e = tensor_map_encoder(&encode);
+    if (e != cudaSuccess) return e;
+    if ((C % 256) != 0 || rows < 1 || ((uintptr_t)base % 16) != 0) return cudaErrorInvalidValue;
+    for (int v = 0; v < 3; v++) {
+        cuuint64_t dims[2] = {(cuuint64_t)(C / 16), (cuuint64_t)rows};
+        cuuint64_t strides[1] = {(cuuint64_t)(C / 16)};
+        cuuint32_t box[2] = {16u, (cuuint32_t)(16 << v)};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = encode(&out3[v], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    }
+    return cudaSuccess;
 }
 
 cudaError_t make_fp4_act_maps(CUtensorMap* out3, const void* base, int C, int rows) {

@@ -286,7 +286,7 @@ __global__ void __launch_bounds__(128)
 nvfp4_moe_plan_kernel(const int* __restrict__ group_offsets, int E, int expert_begin, int expert_end, int J,
                       const Fp4ExpertDesc* __restrict__ experts, int H, int M, const float* dq_gu, float* gate_out,
                       float* up_out, const float* dq_dn, float* grouped_out, Fp4Job* gu_jobs, Fp4Job* dn_jobs,
-                      float* ig_gu, float* ig_dn, Fp4TcJob* tc_gu, Fp4TcJob* tc_dn, const uint8_t* x_scales) {
+                      float* ig_gu, float* ig_dn, Fp4TcJob* tc_gu, Fp4TcJob* tc_dn) {
     const int e = blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= E) return;
     const int g0 = group_offsets[e], cnt = group_offsets[e + 1] - g0;
@@ -308,19 +308,18 @@ nvfp4_moe_plan_kernel(const int* __restrict__ group_offsets, int E, int expert_b
     if (tc_gu) {
         // the same jobs for the tensor-core kernel: the up matrix follows the gate codes (M rows) and the gate
         // scales (M / 8 rows of H / 2 bytes) in the expert's slot; the quantised activations' block scales
-        // use the rows of the packed codes (gate [0, J), up [J, 2J); down [0, J) after the second quantisation)
+        // use the rows of the packed codes (gate [0, J), up [J, 2J); down [0, J) after the second quantisation);
+        // scale rows are C / 16 bytes long: in those units the up scales start 9 M rows (one tensor) after the
+        // gate scales
         Fp4TcJob t;
         t.ntok = local ? cnt : 0; t.w_slice = local ? e - expert_begin : 0;
-        t.R = M; t.y_stride = M; t.w_row0 = 0; t.x_row0 = g0;
-        t.w_scales = local ? d.scales[0] : nullptr; t.x_scales = x_scales + (size_t)g0 * (H >> 4);
+        t.R = M; t.y_stride = M; t.w_row0 = 0; t.ws_row0 = 0; t.x_row0 = g0;
         t.wg = local ? d.wg[0] : 0.0f; t.ig = local ? d.ig[0] : 1.0f; t.y = gate_out + (size_t)g0 * M;
         tc_gu[e] = t;
-        t.w_row0 = M + (M >> 3); t.x_row0 = J + g0;
-        t.w_scales = local ? d.scales[1] : nullptr; t.x_scales = x_scales + (size_t)(J + g0) * (H >> 4);
+        t.w_row0 = M + (M >> 3); t.ws_row0 = 9 * M; t.x_row0 = J + g0;
         t.wg = local ? d.wg[1] : 0.0f; t.ig = local ? d.ig[1] : 1.0f; t.y = up_out + (size_t)g0 * M;
         tc_gu[E + e] = t;
-        t.R = H; t.y_stride = H; t.w_row0 = 0; t.x_row0 = g0;
-        t.w_scales = local ? d.scales[2] : nullptr; t.x_scales = x_scales + (size_t)g0 * (M >> 4);
+        t.R = H; t.y_stride = H; t.w_row0 = 0; t.ws_row0 = 0; t.x_row0 = g0;
         t.wg = local ? d.wg[2] : 0.0f; t.ig = local ? d.ig[2] : 1.0f; t.y = grouped_out + (size_t)g0 * H;
         tc_dn[e] = t;
     }
@@ -341,11 +340,10 @@ geglu_rows_kernel(const float* __restrict__ gate, const float* __restrict__ up, 
 cudaError_t launch_nvfp4_moe_plan(const int* group_offsets, int E, int expert_begin, int expert_end, int J,
                                   const Fp4ExpertDesc* experts, int H, int M, const float* dq_gu, float* gate_out,
                                   float* up_out, const float* dq_dn, float* grouped_out, Fp4Job* gu_jobs, Fp4Job* dn_jobs,
-                                  float* ig_gu, float* ig_dn, cudaStream_t stream, Fp4TcJob* tc_gu, Fp4TcJob* tc_dn,
-                                  const uint8_t* x_scales) {
+                                  float* ig_gu, float* ig_dn, cudaStream_t stream, Fp4TcJob* tc_gu, Fp4TcJob* tc_dn) {
     nvfp4_moe_plan_kernel<<<(E + 127) / 128, 128, 0, stream>>>(group_offsets, E, expert_begin, expert_end, J, experts, H, M,
                                                               dq_gu, gate_out, up_out, dq_dn, grouped_out, gu_jobs, dn_jobs,
-                                                              ig_gu, ig_dn, tc_gu, tc_dn, x_scales);
+                                                              ig_gu, ig_dn, tc_gu, tc_dn);
     return cudaGetLastError();
 }
 

@@ -387,7 +387,7 @@ static __device__ __forceinline__ float warp_chain_sum_of_squares(const float (&
 }
 
 template <int CH>
-__global__ void __launch_bounds__(128, 4) glue_rows_warp_kernel(GlueArgs a, int rows) {
+__global__ void __launch_bounds__(128, CH > 96 ? 2 : 4) glue_rows_warp_kernel(GlueArgs a, int rows) {
     static_assert(CH % 4 == 0, "rows are moved in 16-byte pieces");
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -474,9 +474,10 @@ cudaError_t launch_glue(const GlueArgs& a, int rows, cudaStream_t stream) {
     if (a.topk > 64) return cudaErrorInvalidValue;
     const size_t smem = (size_t)(a.n + 8) * sizeof(float);
     const auto al16 = [](const void* p) { return (((uintptr_t)p) & 15) == 0; };
-    if (rows >= 256 && a.n == 32 * 88 && al16(a.grouped) && al16(a.x_in) && al16(a.y_out) && al16(a.norm_w) &&
-        al16(a.router_scale) && al16(a.rin)) {
-        glue_rows_warp_kernel<88><<<(rows + 3) / 4, 128, 0, stream>>>(a, rows);
+    if (rows >= 256 && (a.n == 32 * 88 || a.n == 32 * 160) && al16(a.grouped) && al16(a.x_in) && al16(a.y_out) &&
+        al16(a.norm_w) && al16(a.router_scale) && al16(a.rin)) {
+        if (a.n == 32 * 88) glue_rows_warp_kernel<88><<<(rows + 3) / 4, 128, 0, stream>>>(a, rows);
+        else glue_rows_warp_kernel<160><<<(rows + 3) / 4, 128, 0, stream>>>(a, rows);
         return cudaGetLastError();
     }
     if (a.n <= 4096) {
@@ -665,36 +666,40 @@ router_logits_tile_kernel(const float* __restrict__ W, const float* __restrict__
     if (e < E && row < rows) logits[(size_t)row * E + e] = __fadd_rn(acc, bias ? bias[e] : 0.0f);
 }
 
-// Prefill-sized batches: 256 threads as 16 experts x 16 rows, each thread EPT x RPT outputs
+// Prefill-sized batches: 16 * RL threads as 16 experts x RL rows, each thread EPT x RPT outputs
 // (independent dependent-add chains, so a warp always has an add to issue), tiles of
-// 16*EPT experts x 16*RPT rows.  The 8 x 8 tiles above re-read W and x from L2 sixteen times
+// 16*EPT experts x RL*RPT rows.  The 8 x 8 tiles above re-read W and x from L2 sixteen times
 // more often per output than a 32 x 32 tile; past a few hundred rows that traffic, not the
 // chains, set their time.
-template <int EPT, int RPT>
+template <int EPT, int RPT, int RL>
 struct LogitsBig {
-    static constexpr int TE = 16 * EPT, TR = 16 * RPT, ROWS = TE + TR;
-    static constexpr int SLAB = 128, PITCH = SLAB + 4, STAGES = 3;   // two blocks per SM
+    static constexpr int THREADS = 16 * RL;                  // 16 expert lanes x RL row lanes
+    static constexpr int TE = 16 * EPT, TR = RL * RPT, ROWS = TE + TR;
+    static constexpr int SLAB = 128, PITCH = SLAB + 4, STAGES = 3;
     static constexpr size_t SMEM = (size_t)STAGES * ROWS * PITCH * sizeof(float);
 };
 
-template <int EPT, int RPT>
-__global__ void __launch_bounds__(256, 2)
+// RL = 16 (256 threads, two blocks per SM) for a thousand rows and more; RL = 8 (128 threads: one warp per
+// scheduler, so a warp's dependent-add chains never wait for an issue slot) for a few hundred rows, where
+// the number of chains - rows x experts - is what limits the machine and the work should reach many SMs.
+template <int EPT, int RPT, int RL>
+__global__ void __launch_bounds__(16 * RL, RL == 16 ? 2 : 1)
 router_logits_big_kernel(const float* __restrict__ W, const float* __restrict__ bias, const float* __restrict__ x,
                          float* __restrict__ logits, int rows, int E, int H) {
-    using G = LogitsBig<EPT, RPT>;
+    using G = LogitsBig<EPT, RPT, RL>;
     extern __shared__ __align__(16) float lt_sm[];      // [STAGES][TE W rows, then TR x rows][PITCH]
     const int tid = threadIdx.x;
     const int el = tid & 15, rl = tid >> 4;
     const int e0 = blockIdx.x * G::TE, row0 = blockIdx.y * G::TR;
     const int nslab = (H + G::SLAB - 1) / G::SLAB;
-    // a slab row is 32 pieces of 16 bytes: thread tid copies piece tid & 31 of rows tid >> 5, + 8, ...
+    // a slab row is 32 pieces of 16 bytes: thread tid copies piece tid & 31 of rows tid >> 5, + THREADS / 32, ...
     const int pc = tid & 31;
     auto issue = [&](int sl) {
         float* st = lt_sm + (size_t)(sl % G::STAGES) * G::ROWS * G::PITCH;
         const int c = sl * G::SLAB + pc * 4;
         if (c >= H) return;
 #pragma unroll
-        for (int r = tid >> 5; r < G::ROWS; r += 8) {
+        for (int r = tid >> 5; r < G::ROWS; r += G::THREADS / 32) {
             const float* src = r < G::TE ? W + (size_t)min(e0 + r, E - 1) * H + c
                                          : x + (size_t)min(row0 + r - G::TE, rows - 1) * H + c;
             cp_async16(st + r * G::PITCH + pc * 4, src);
@@ -722,7 +727,7 @@ router_logits_big_kernel(const float* __restrict__ W, const float* __restrict__ 
 #pragma unroll
             for (int i = 0; i < EPT; i++) wv[i] = *(const float4*)(st + (el + 16 * i) * G::PITCH + c);
 #pragma unroll
-            for (int j = 0; j < RPT; j++) xv[j] = *(const float4*)(st + (G::TE + rl + 16 * j) * G::PITCH + c);
+            for (int j = 0; j < RPT; j++) xv[j] = *(const float4*)(st + (G::TE + rl + RL * j) * G::PITCH + c);
 #pragma unroll
             for (int i = 0; i < EPT; i++)
 #pragma unroll
@@ -740,24 +745,19 @@ router_logits_big_kernel(const float* __restrict__ W, const float* __restrict__ 
     for (int i = 0; i < EPT; i++)
 #pragma unroll
         for (int j = 0; j < RPT; j++) {
-            const int e = e0 + el + 16 * i, row = row0 + rl + 16 * j;
+            const int e = e0 + el + 16 * i, row = row0 + rl + RL * j;
             if (e < E && row < rows) logits[(size_t)row * E + e] = __fadd_rn(acc[i][j], bias ? bias[e] : 0.0f);
         }
 }
 
-template <int EPT, int RPT>
+template <int EPT, int RPT, int RL>
 static cudaError_t launch_logits_big(const float* W, const float* bias, const float* x, float* logits, int rows, int E,
                                      int H, cudaStream_t stream) {
-    using G = LogitsBig<EPT, RPT>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(router_logits_big_kernel<EPT, RPT>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G::SMEM);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    using G = LogitsBig<EPT, RPT, RL>;
+    cudaError_t e = ensure_dynamic_smem((const void*)router_logits_big_kernel<EPT, RPT, RL>, G::SMEM);
+    if (e != cudaSuccess) return e;
     dim3 grid((E + G::TE - 1) / G::TE, (rows + G::TR - 1) / G::TR);
-    router_logits_big_kernel<EPT, RPT><<<grid, 256, G::SMEM, stream>>>(W, bias, x, logits, rows, E, H);
+    router_logits_big_kernel<EPT, RPT, RL><<<grid, G::THREADS, G::SMEM, stream>>>(W, bias, x, logits, rows, E, H);
     return cudaGetLastError();
 }
 
@@ -811,9 +811,9 @@ cudaError_t launch_router_logits(const float* W, const float* bias, const float*
         dim3 grid(E, (rows + LOGIT_TB - 1) / LOGIT_TB);
         router_logits_block_kernel<<<grid, 256, smem, stream>>>(W, bias, x, logits, rows, E, H);
     } else if (aligned16 && (H & 3) == 0 && rows >= 1024) {
-        return launch_logits_big<2, 2>(W, bias, x, logits, rows, E, H, stream);
+        return launch_logits_big<2, 2, 16>(W, bias, x, logits, rows, E, H, stream);
     } else if (aligned16 && (H & 3) == 0 && rows >= 256) {
-        return launch_logits_big<2, 1>(W, bias, x, logits, rows, E, H, stream);
+        return launch_logits_big<2, 1, 8>(W, bias, x, logits, rows, E, H, stream);
     } else if (aligned16 && (H & 3) == 0) {
         const size_t smem = (size_t)LT_STAGES * 16 * LT_PITCH * sizeof(float);
         {

@@ -93,9 +93,24 @@ def test_nvfp4_tensor_core_layer_vs_oracle(orc, synth, geom):
     st.close()
 
 
+def _router_oracle(orc, layer, x):
+    """Router alone on the CPU (input scaling, in-order logits, softmax top-k): cheap at any batch."""
+    sel = np.empty((x.shape[0], layer.topk), np.int32)
+    w = np.empty((x.shape[0], layer.topk), np.float32)
+    logits = np.empty((x.shape[0], layer.n_experts), np.float32)
+    for t in range(x.shape[0]):
+        rc, rin = orc.router_input(x[t], layer.router_scale, layer.eps)
+        assert rc == 0
+        logits[t] = orc.router_scores(layer.router_w, None, rin)
+        rc, sel[t], w[t] = orc.router_topk(logits[t], layer.per_expert_scale, layer.topk, True)
+        assert rc == 0
+    return logits, sel, w
+
+
 @pytest.mark.parametrize("B", [64, 256])
-def test_nvfp4_tensor_core_cfg4_vs_exact_kernels(synth, B):
-    """Config 4 (64 experts, hidden 5120, intermediate 1536, top-4) against the bit-exact GPU path."""
+def test_nvfp4_tensor_core_cfg4_vs_exact_kernels(orc, synth, B):
+    """Config 4 (64 experts, hidden 5120, intermediate 1536, top-4) against the bit-exact GPU path; the
+    router of the batch (logits of 256 rows x 64 experts over 5120 columns) bit for bit against the CPU."""
     layer = synth.make_nvfp4_moe_layer(4410)
     x = synth.make_tokens(4600 + B, B, layer.hidden)
     st = stack_mod().MoeStack(B, layer.hidden, layer.inter, layer.n_experts, layer.topk)
@@ -104,7 +119,12 @@ def test_nvfp4_tensor_core_cfg4_vs_exact_kernels(synth, B):
     y = _run(st, x, B, layer.hidden, True, tc)
     want = _run(st, x, B, layer.hidden, False, ex)
     same = _check_stages(tc, ex, f"nvfp4 tensor-core cfg 4 B={B}")
-    g2c = d2h(st.workspace().grouped_to_canonical, B * layer.topk, np.int32)
+    ws = st.workspace()
+    logits, sel, w = _router_oracle(orc, layer, x)
+    assert_bits_equal(d2h(ws.logits, B * layer.n_experts, np.float32).reshape(B, -1), logits, "router logits (exact)")
+    assert_bits_equal(d2h(ws.selected, B * layer.topk, np.int32).reshape(B, -1), sel, "selected (exact)")
+    assert_bits_equal(d2h(ws.weights, B * layer.topk, np.float32).reshape(B, -1), w, "weights (exact)")
+    g2c = d2h(ws.grouped_to_canonical, B * layer.topk, np.int32)
     clean = np.ones(B, bool)
     clean[g2c[~same] // layer.topk] = False
     err = _rel_err(y[clean], want[clean])
