@@ -293,6 +293,51 @@ def run_reference(args):
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
+def nvfp4_extra(torch, stack_mod, synth, stream, peak):
+    """Configuration 4 (64 NVFP4 experts, hidden 5120, intermediate 1536, top-4) on a two-layer stack of its
+    own, device-timed, outside the headline: decode at B = 1 on the bit-exact kernels and B = 256 with the
+    expert projections as block-scaled tcgen05 GEMMs."""
+    H4, M4, E4, K4, L4 = 5120, 1536, 64, 4, 2
+    tensor_bytes = H4 * M4 // 2 + H4 * M4 // 16 + 8
+    st = stack_mod.MoeStack(256, H4, M4, E4, K4)
+    for i in range(L4):
+        st.add_nvfp4_layer(synth.make_nvfp4_moe_layer(5400 + i))
+    sp = stream.cuda_stream
+    out = {}
+    for bb, tc in ((1, False), (256, True)):
+        xs = torch.from_numpy(synth.make_tokens(77, bb, H4)).cuda()
+        acts = [torch.empty_like(xs), torch.empty_like(xs)]
+        ys = torch.empty_like(xs)
+
+        def run():
+            cur = xs.data_ptr()
+            for l in range(L4):
+                o = ys if l == L4 - 1 else acts[l & 1]
+                assert st.layer_experts(l, cur, bb, router_input_ready=l > 0, tensor_core=tc, stream=sp) == 0
+                assert st.layer_combine(l, bb, o.data_ptr(), apply_norm=True, prepare_next=l + 1 < L4, stream=sp) == 0
+                cur = o.data_ptr()
+        for _ in range(3):
+            run()
+        n_it = 10
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(n_it):
+            run()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / n_it
+        assert st.status(sp) == 0
+        distinct = min(E4, bb * K4) if bb == 1 else E4
+        by = distinct * 3 * tensor_bytes + E4 * H4 * 4 + bb * H4 * 4 * 3 + bb * K4 * (2 * M4 + 2 * H4) * 4
+        out[f"B{bb}"] = {"tokens_per_s": bb * L4 / (ms * 1e-3), "us_per_layer": 1e3 * ms / L4,
+                         "expert_projections": ("tcgen05.mma.kind::mxf4nvf4 block-scaled (each projection within 1e-3 of "
+                                                "the exact path)") if tc else "exact (bit-exact vs CPU)",
+                         "algorithmic_bytes_per_layer": by, "hbm_frac": by / (1e3 * ms / L4 * 1e-6) / 1e9 / peak}
+    st.close()
+    return out
+
+
 def run_b200(args):
     import torch
     import torch.distributed as dist
@@ -581,6 +626,7 @@ def run_b200(args):
                                        "hbm_frac": by / (1e3 * ms / L * 1e-6) / 1e9 / peak}
                     assert stack.status(sp) == 0
                 extra["batch_sweep"] = sweep
+                extra["nvfp4_cfg4"] = nvfp4_extra(torch, stack_mod, synth, stream, peak)
                 if use_graph:                 # leave the headline graph in place
                     assert stack.graph_capture(d_x.data_ptr(), B, d_y.data_ptr(), sp) == 0
 
