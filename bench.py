@@ -297,6 +297,7 @@ def nvfp4_extra(torch, stack_mod, synth, stream, peak):
     """Configuration 4 (64 NVFP4 experts, hidden 5120, intermediate 1536, top-4) on a two-layer stack of its
     own, device-timed, outside the headline: decode at B = 1 on the bit-exact kernels and B = 256 with the
     expert projections as block-scaled tcgen05 GEMMs."""
+    import ctypes as C
     H4, M4, E4, K4, L4 = 5120, 1536, 64, 4, 2
     tensor_bytes = H4 * M4 // 2 + H4 * M4 // 16 + 8
     st = stack_mod.MoeStack(256, H4, M4, E4, K4)
@@ -304,7 +305,7 @@ def nvfp4_extra(torch, stack_mod, synth, stream, peak):
         st.add_nvfp4_layer(synth.make_nvfp4_moe_layer(5400 + i))
     sp = stream.cuda_stream
     out = {}
-    for bb, tc in ((1, False), (256, True)):
+    for bb, tc in ((1, False), (1, True), (16, False), (16, True), (256, True)):
         xs = torch.from_numpy(synth.make_tokens(77, bb, H4)).cuda()
         acts = [torch.empty_like(xs), torch.empty_like(xs)]
         ys = torch.empty_like(xs)
@@ -328,9 +329,12 @@ def nvfp4_extra(torch, stack_mod, synth, stream, peak):
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / n_it
         assert st.status(sp) == 0
-        distinct = min(E4, bb * K4) if bb == 1 else E4
+        offs = np.empty(E4 + 1, np.int32)
+        st.lib.salt_b200_read_device(C.c_void_p(offs.ctypes.data), C.c_void_p(st.workspace().group_offsets),
+                                     C.c_size_t(offs.nbytes))
+        distinct = int((np.diff(offs) > 0).sum())     # of the last layer run
         by = distinct * 3 * tensor_bytes + E4 * H4 * 4 + bb * H4 * 4 * 3 + bb * K4 * (2 * M4 + 2 * H4) * 4
-        out[f"B{bb}"] = {"tokens_per_s": bb * L4 / (ms * 1e-3), "us_per_layer": 1e3 * ms / L4,
+        out[f"B{bb}" + ("_blockscaled" if tc else "_exact")] = {"tokens_per_s": bb * L4 / (ms * 1e-3), "us_per_layer": 1e3 * ms / L4,
                          "expert_projections": ("tcgen05.mma.kind::mxf4nvf4 block-scaled (each projection within 1e-3 of "
                                                 "the exact path)") if tc else "exact (bit-exact vs CPU)",
                          "algorithmic_bytes_per_layer": by, "hbm_frac": by / (1e3 * ms / L4 * 1e-6) / 1e9 / peak}

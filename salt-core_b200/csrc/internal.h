@@ -146,7 +146,7 @@ cudaError_t launch_nvfp4_moe_plan(const int* group_offsets, int E, int expert_be
                                   const Fp4ExpertDesc* experts, int H, int M, const float* dq_gu, float* gate_out,
                                   float* up_out, const float* dq_dn, float* grouped_out, Fp4Job* gu_jobs, Fp4Job* dn_jobs,
                                   float* ig_gu, float* ig_dn, cudaStream_t stream, struct Fp4TcJob* tc_gu = nullptr,
-                                  struct Fp4TcJob* tc_dn = nullptr);
+                                  struct Fp4TcJob* tc_dn = nullptr, int* live = nullptr);
 // ---- nvfp4_gemm_tc.cu: block-scaled tensor-core form of a grouped NVFP4 projection (tolerance path) ----
 struct Fp4TcJob {
     float* y;                  // y[n * y_stride + m]
@@ -167,8 +167,11 @@ cudaError_t make_fp4_act_maps(CUtensorMap* out3, const void* base, int C, int ro
 cudaError_t launch_nvfp4_gemm_tc(const Fp4TcJob* jobs, int njobs, int R, int C, const Fp4TcMaps& maps, int* status,
                                  cudaStream_t stream);
 cudaError_t launch_geglu_rows(const float* gate, const float* up, float* chain, size_t n, cudaStream_t stream);
+// live / n_live (optional, device): indices of the jobs that have tokens and their number; njobs is then the
+// largest number of such jobs the call can have, and the grid spans only that many
 cudaError_t launch_nvfp4_jobs(const Fp4Job* jobs, int njobs, int max_rows, int max_tok, int C, bool aligned,
-                              cudaStream_t stream);
+                              cudaStream_t stream, const int* live = nullptr, const int* n_live = nullptr,
+                              int typical_tok = 0);
 
 // ---- router_kernels.cu ---------------------------------------------------
 // Device-side error word: 0 = ok; set (never cleared) by kernels that meet a

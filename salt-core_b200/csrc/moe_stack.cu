@@ -75,6 +75,7 @@ struct Stack {
     uint8_t *fp4_packed = nullptr, *fp4_scales = nullptr;
     Fp4Job *fp4_gu_jobs = nullptr, *fp4_dn_jobs = nullptr;
     Fp4TcJob *fp4_tc_gu = nullptr, *fp4_tc_dn = nullptr;
+    int* fp4_live = nullptr;                   // [2 + 3E]: counts and indices of the projection jobs that have tokens
     CUtensorMap fp4_x_gu[3], fp4_x_dn[3];      // packed activations as [2J][H/2] and as [J][M/2]
     CUtensorMap fp4_xs_gu[3], fp4_xs_dn[3];    // their block scales as [2J][H/16] and as [J][M/16]
     bool fp4_maps_ok = false;
@@ -138,7 +139,7 @@ static void free_stack(Stack* s) {
     cudaFree(s->grouped_alt); cudaFree(s->weights_alt); cudaFree(s->layer_counters);
     cudaFree(s->fp4_dq_gu); cudaFree(s->fp4_dq_dn); cudaFree(s->fp4_gate); cudaFree(s->fp4_up); cudaFree(s->fp4_ig_gu);
     cudaFree(s->fp4_ig_dn); cudaFree(s->fp4_packed); cudaFree(s->fp4_scales); cudaFree(s->fp4_gu_jobs); cudaFree(s->fp4_dn_jobs);
-    cudaFree(s->fp4_tc_gu); cudaFree(s->fp4_tc_dn);
+    cudaFree(s->fp4_tc_gu); cudaFree(s->fp4_tc_dn); cudaFree(s->fp4_live);
     cudaFree(s->xh); cudaFree(s->xl); cudaFree(s->chain_h); cudaFree(s->chain_l);
     if (s->h_in) cudaFreeHost(s->h_in);
     if (s->h_out) cudaFreeHost(s->h_out);
@@ -265,7 +266,7 @@ int salt_b200_stack_add_nvfp4_layer(void* stack, const SaltB200Nvfp4LayerSpec* s
           dev_alloc(&s->fp4_ig_dn, J) && dev_alloc(&s->fp4_packed, 2 * J * (size_t)s->hidden / 2) &&
           dev_alloc(&s->fp4_scales, 2 * J * (size_t)s->hidden / 16) && dev_alloc(&s->fp4_gu_jobs, (size_t)2 * E) &&
           dev_alloc(&s->fp4_dn_jobs, (size_t)E) && dev_alloc(&s->fp4_tc_gu, (size_t)2 * E) &&
-          dev_alloc(&s->fp4_tc_dn, (size_t)E)))
+          dev_alloc(&s->fp4_tc_dn, (size_t)E) && dev_alloc(&s->fp4_live, (size_t)(2 + 3 * E))))
         return -1;
     if (!s->fp4_maps_ok)
         s->fp4_maps_ok = make_fp4_act_maps(s->fp4_x_gu, s->fp4_packed, s->hidden, (int)(2 * J)) == cudaSuccess &&
@@ -468,16 +469,21 @@ static int layer_experts_impl(Stack* s, int layer, const float* d_router_src, co
     if (l.nvfp4) {
         if (flags & SB_EXPERTS_TENSOR_CORE_SINGLE) return -1;
         Timed t(s, KC_GATE_UP, st);
+        const int live_max = std::min(s->expert_end - s->expert_begin, jobs);   // experts that can have tokens
+        const int typical = std::max(1, (jobs + E - 1) / E);                    // selections per expert, evenly routed
         if (!cuda_ok(launch_nvfp4_moe_plan(s->group_offsets, E, s->expert_begin, s->expert_end, jobs, l.fp4_experts, H, M,
                                            s->fp4_dq_gu, s->fp4_gate, s->fp4_up, s->fp4_dq_dn, s->grouped_out,
-                                           s->fp4_gu_jobs, s->fp4_dn_jobs, s->fp4_ig_gu, s->fp4_ig_dn, st), "nvfp4 plan") ||
+                                           s->fp4_gu_jobs, s->fp4_dn_jobs, s->fp4_ig_gu, s->fp4_ig_dn, st, nullptr, nullptr,
+                                           s->fp4_live), "nvfp4 plan") ||
             !cuda_ok(launch_nvfp4_qdq(d_x, 2 * jobs, H, s->fp4_ig_gu, s->fp4_packed, s->fp4_scales, s->fp4_dq_gu,
                                       s->status, st, s->g2c, jobs, K), "nvfp4 qdq x") ||
-            !cuda_ok(launch_nvfp4_jobs(s->fp4_gu_jobs, 2 * E, M, B, H, true, st), "nvfp4 gate/up") ||
+            !cuda_ok(launch_nvfp4_jobs(s->fp4_gu_jobs, 2 * live_max, M, B, H, true, st, s->fp4_live + 2, s->fp4_live,
+                                       typical), "nvfp4 gate/up") ||
             !cuda_ok(launch_geglu_rows(s->fp4_gate, s->fp4_up, s->chain, (size_t)jobs * M, st), "geglu") ||
             !cuda_ok(launch_nvfp4_qdq(s->chain, jobs, M, s->fp4_ig_dn, s->fp4_packed, s->fp4_scales, s->fp4_dq_dn,
                                       s->status, st), "nvfp4 qdq chain") ||
-            !cuda_ok(launch_nvfp4_jobs(s->fp4_dn_jobs, E, H, B, M, true, st), "nvfp4 down"))
+            !cuda_ok(launch_nvfp4_jobs(s->fp4_dn_jobs, live_max, H, B, M, true, st, s->fp4_live + 2 + 2 * E,
+                                       s->fp4_live + 1, typical), "nvfp4 down"))
             return -1;
         count_launches(7);
         return 0;

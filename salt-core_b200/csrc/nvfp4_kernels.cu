@@ -10,6 +10,8 @@
 // The encoders are arithmetic instead of the reference's nearest-code searches:
 // "nearest, ties to the even code" over a monotone code table is round-to-
 // nearest-even in that format (checked against the searches in the tests).
+#include <algorithm>
+
 #include "internal.h"
 #include "q4_core.cuh"
 
@@ -137,9 +139,11 @@ __device__ __forceinline__ void e2m1x4(uint32_t h, f32x2& w01, f32x2& w23) {
 // Requires C % 256 == 0 and 16-byte aligned operands.
 template <int TT>
 __global__ void __launch_bounds__(64)
-nvfp4_tile_kernel(const Fp4Job* __restrict__ jobs, int C) {
+nvfp4_tile_kernel(const Fp4Job* __restrict__ jobs, int C, const int* __restrict__ live, const int* __restrict__ n_live) {
     extern __shared__ __align__(16) uint8_t smem[];
-    const Fp4Job jb = jobs[blockIdx.y];
+    // with a list of the jobs that have tokens the grid only spans those (a decode step touches 4 of 64 experts)
+    if (live != nullptr && (int)blockIdx.y >= *n_live) return;
+    const Fp4Job jb = jobs[live != nullptr ? live[blockIdx.y] : blockIdx.y];
     const int r0 = blockIdx.x * 16;
     if (r0 >= jb.R || jb.ntok < 1) return;
     const int tid = threadIdx.x, u = tid & 7, pr = tid >> 3;
@@ -254,8 +258,10 @@ nvfp4_tile_kernel(const Fp4Job* __restrict__ jobs, int C) {
 
 // Any C (multiple of 16), any alignment: one warp per (row, token), lane l owns
 // accumulator l.
-__global__ void __launch_bounds__(128) nvfp4_generic_kernel(const Fp4Job* __restrict__ jobs) {
-    const Fp4Job jb = jobs[blockIdx.z];
+__global__ void __launch_bounds__(128)
+nvfp4_generic_kernel(const Fp4Job* __restrict__ jobs, const int* __restrict__ live, const int* __restrict__ n_live) {
+    if (live != nullptr && (int)blockIdx.z >= *n_live) return;
+    const Fp4Job jb = jobs[live != nullptr ? live[blockIdx.z] : blockIdx.z];
     const int r = blockIdx.x * 4 + (threadIdx.x >> 5), tok = blockIdx.y;
     if (r >= jb.R || tok >= jb.ntok) return;
     const int lane = threadIdx.x & 31;
@@ -282,13 +288,37 @@ __global__ void __launch_bounds__(128) nvfp4_generic_kernel(const Fp4Job* __rest
 // two projection batches with the GeGLU between them) ------------------------------------------------
 // One thread per expert: the projection jobs of its token group and the input global scale of every
 // grouped row (gate rows [0, J), up rows [J, 2J) of the gathered activations; down rows [0, J)).
+static __device__ __forceinline__ void
+nvfp4_plan_expert(int e, const int* __restrict__ group_offsets, int E, int expert_begin, int expert_end, int J,
+                  const Fp4ExpertDesc* __restrict__ experts, int H, int M, const float* dq_gu, float* gate_out,
+                  float* up_out, const float* dq_dn, float* grouped_out, Fp4Job* gu_jobs, Fp4Job* dn_jobs, float* ig_gu,
+                  float* ig_dn, Fp4TcJob* tc_gu, Fp4TcJob* tc_dn, int* live, int* n_gu, int* n_dn);
+
 __global__ void __launch_bounds__(128)
 nvfp4_moe_plan_kernel(const int* __restrict__ group_offsets, int E, int expert_begin, int expert_end, int J,
                       const Fp4ExpertDesc* __restrict__ experts, int H, int M, const float* dq_gu, float* gate_out,
                       float* up_out, const float* dq_dn, float* grouped_out, Fp4Job* gu_jobs, Fp4Job* dn_jobs,
-                      float* ig_gu, float* ig_dn, Fp4TcJob* tc_gu, Fp4TcJob* tc_dn) {
-    const int e = blockIdx.x * blockDim.x + threadIdx.x;
-    if (e >= E) return;
+                      float* ig_gu, float* ig_dn, Fp4TcJob* tc_gu, Fp4TcJob* tc_dn, int* live) {
+    // live (optional): [0] / [1] = number of gate|up / down jobs with tokens, then their indices ([2, 2 + 2E)
+    // into gu_jobs, [2 + 2E, 2 + 3E) into dn_jobs) so the projection launches span only those
+    __shared__ int n_gu, n_dn;
+    if (threadIdx.x == 0) n_gu = n_dn = 0;
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x)
+        nvfp4_plan_expert(e, group_offsets, E, expert_begin, expert_end, J, experts, H, M, dq_gu, gate_out, up_out, dq_dn,
+                          grouped_out, gu_jobs, dn_jobs, ig_gu, ig_dn, tc_gu, tc_dn, live, &n_gu, &n_dn);
+    __syncthreads();
+    if (threadIdx.x == 0 && live != nullptr) {
+        live[0] = n_gu;
+        live[1] = n_dn;
+    }
+}
+
+static __device__ __forceinline__ void
+nvfp4_plan_expert(int e, const int* __restrict__ group_offsets, int E, int expert_begin, int expert_end, int J,
+                  const Fp4ExpertDesc* __restrict__ experts, int H, int M, const float* dq_gu, float* gate_out,
+                  float* up_out, const float* dq_dn, float* grouped_out, Fp4Job* gu_jobs, Fp4Job* dn_jobs, float* ig_gu,
+                  float* ig_dn, Fp4TcJob* tc_gu, Fp4TcJob* tc_dn, int* live, int* n_gu, int* n_dn) {
     const int g0 = group_offsets[e], cnt = group_offsets[e + 1] - g0;
     const bool local = e >= expert_begin && e < expert_end;
     Fp4ExpertDesc d;
@@ -305,6 +335,12 @@ nvfp4_moe_plan_kernel(const int* __restrict__ group_offsets, int E, int expert_b
     j.codes = local ? d.codes[2] : nullptr; j.scales = local ? d.scales[2] : nullptr; j.wg = local ? d.wg[2] : 0.0f;
     j.x = dq_dn + (size_t)g0 * M; j.y = grouped_out + (size_t)g0 * H;
     dn_jobs[e] = j;
+    if (live != nullptr && local && cnt > 0) {
+        const int i = atomicAdd(n_gu, 2);
+        live[2 + i] = e;
+        live[3 + i] = E + e;
+        live[2 + 2 * E + atomicAdd(n_dn, 1)] = e;
+    }
     if (tc_gu) {
         // the same jobs for the tensor-core kernel: the up matrix follows the gate codes (M rows) and the gate
         // scales (M / 8 rows of H / 2 bytes) in the expert's slot; the quantised activations' block scales
@@ -340,10 +376,11 @@ geglu_rows_kernel(const float* __restrict__ gate, const float* __restrict__ up, 
 cudaError_t launch_nvfp4_moe_plan(const int* group_offsets, int E, int expert_begin, int expert_end, int J,
                                   const Fp4ExpertDesc* experts, int H, int M, const float* dq_gu, float* gate_out,
                                   float* up_out, const float* dq_dn, float* grouped_out, Fp4Job* gu_jobs, Fp4Job* dn_jobs,
-                                  float* ig_gu, float* ig_dn, cudaStream_t stream, Fp4TcJob* tc_gu, Fp4TcJob* tc_dn) {
-    nvfp4_moe_plan_kernel<<<(E + 127) / 128, 128, 0, stream>>>(group_offsets, E, expert_begin, expert_end, J, experts, H, M,
-                                                              dq_gu, gate_out, up_out, dq_dn, grouped_out, gu_jobs, dn_jobs,
-                                                              ig_gu, ig_dn, tc_gu, tc_dn);
+                                  float* ig_gu, float* ig_dn, cudaStream_t stream, Fp4TcJob* tc_gu, Fp4TcJob* tc_dn,
+                                  int* live) {
+    nvfp4_moe_plan_kernel<<<1, 128, 0, stream>>>(group_offsets, E, expert_begin, expert_end, J, experts, H, M, dq_gu,
+                                                 gate_out, up_out, dq_dn, grouped_out, gu_jobs, dn_jobs, ig_gu, ig_dn, tc_gu,
+                                                 tc_dn, live);
     return cudaGetLastError();
 }
 
@@ -358,27 +395,31 @@ static size_t fp4_smem(int C, int tt) {
 }
 
 template <int TT>
-static cudaError_t launch_fp4_tile(const Fp4Job* jobs, int njobs, int max_rows, int C, cudaStream_t stream) {
+static cudaError_t launch_fp4_tile(const Fp4Job* jobs, int njobs, int max_rows, int C, cudaStream_t stream,
+                                   const int* live, const int* n_live) {
     {
         cudaError_t e = ensure_dynamic_smem((const void*)nvfp4_tile_kernel<TT>, (size_t)(200 * 1024));
         if (e != cudaSuccess) return e;
     }
     dim3 grid((max_rows + 15) / 16, njobs);
-    nvfp4_tile_kernel<TT><<<grid, 64, fp4_smem(C, TT), stream>>>(jobs, C);
+    nvfp4_tile_kernel<TT><<<grid, 64, fp4_smem(C, TT), stream>>>(jobs, C, live, n_live);
     return cudaGetLastError();
 }
 
 cudaError_t launch_nvfp4_jobs(const Fp4Job* jobs, int njobs, int max_rows, int max_tok, int C, bool aligned,
-                              cudaStream_t stream) {
+                              cudaStream_t stream, const int* live, const int* n_live, int typical_tok) {
     if (njobs < 1 || max_rows < 1 || max_tok < 1) return cudaSuccess;
     if (aligned && (C % 256) == 0) {
-        if (max_tok >= 3 && fp4_smem(C, 4) <= 200 * 1024) return launch_fp4_tile<4>(jobs, njobs, max_rows, C, stream);
-        if (max_tok >= 2 && fp4_smem(C, 2) <= 200 * 1024) return launch_fp4_tile<2>(jobs, njobs, max_rows, C, stream);
-        if (fp4_smem(C, 1) <= 200 * 1024) return launch_fp4_tile<1>(jobs, njobs, max_rows, C, stream);
+        // tokens per pass: sized for the typical group, not the largest possible one - a wider pass stages that
+        // many activation rows in shared memory and costs resident blocks when most groups hold one token
+        const int tt = typical_tok > 0 ? std::min(typical_tok, max_tok) : max_tok;
+        if (tt >= 3 && fp4_smem(C, 4) <= 200 * 1024) return launch_fp4_tile<4>(jobs, njobs, max_rows, C, stream, live, n_live);
+        if (tt >= 2 && fp4_smem(C, 2) <= 200 * 1024) return launch_fp4_tile<2>(jobs, njobs, max_rows, C, stream, live, n_live);
+        if (fp4_smem(C, 1) <= 200 * 1024) return launch_fp4_tile<1>(jobs, njobs, max_rows, C, stream, live, n_live);
     }
     dim3 grid((max_rows + 3) / 4, max_tok, njobs);
     if (grid.y > 65535 || grid.z > 65535) return cudaErrorInvalidValue;
-    nvfp4_generic_kernel<<<grid, 128, 0, stream>>>(jobs);
+    nvfp4_generic_kernel<<<grid, 128, 0, stream>>>(jobs, live, n_live);
     return cudaGetLastError();
 }
 
