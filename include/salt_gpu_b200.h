@@ -446,6 +446,25 @@ int salt_b200_layer_experts(void *stack, int layer, const float *d_x, int B, int
 #define SALT_B200_COMBINE_NORM 1
 #define SALT_B200_COMBINE_PREPARE_NEXT 2
 int salt_b200_layer_combine(void *stack, int layer, int B, float *d_y, int flags, void *stream);
+/* Expert parallelism by token dispatch (tokens partitioned by home rank; rows travel only to the rank that
+ * owns their expert and results only back to the home rank - any all-to-all moves them, e.g. NCCL's).  A layer
+ * is three calls, no state is kept between them except the router input prepared by _combine_rows:
+ *   _layer_route           home rank: router input (unless SALT_B200_EXPERTS_ROUTER_INPUT_READY), in-order logits,
+ *                          softmax top-k of its B tokens -> d_selected [B][topk] (expert ids, ascending within a
+ *                          token), d_weights [B][topk]; both caller-owned device memory
+ *   _layer_experts_routed  owner rank: d_out[i] = expert d_experts[i] (one of THIS stack's experts) applied to
+ *                          d_rows[i] (gate | up, GeGLU, down), i < n_rows <= max_tokens * topk, any order; the
+ *                          rows are grouped by expert as reference src/moe_group.c:83-182 groups them and every
+ *                          row's result depends only on (expert weights, row), so it is the same whichever rank
+ *                          computes it and whatever else is in the call.  flags: the TENSOR_CORE flags
+ *   _layer_combine_rows    home rank: d_rows [B * topk][hidden] in canonical order (token-major, rank order)
+ *                          -> ordered weighted reduce (src/moe_group.c:211-224), then as salt_b200_layer_combine */
+int salt_b200_layer_route(void *stack, int layer, const float *d_x, int B, int32_t *d_selected, float *d_weights,
+                          int flags, void *stream);
+int salt_b200_layer_experts_routed(void *stack, int layer, const float *d_rows, const int32_t *d_experts, int n_rows,
+                                   float *d_out, int flags, void *stream);
+int salt_b200_layer_combine_rows(void *stack, int layer, const float *d_rows, const float *d_weights, int B,
+                                 float *d_y, int flags, void *stream);
 /* Expert-parallel exchange over peer memory (no reference counterpart: the reference is
  * single-device; the sharding rule follows from its expert independence,
  * models/gemma4-26b-a4b/src/gemma4.c:154-186 reduces per-selection outputs in rank order).

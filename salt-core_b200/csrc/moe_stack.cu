@@ -58,6 +58,7 @@ struct Stack {
     float *rin = nullptr, *logits = nullptr, *weights = nullptr, *chain = nullptr, *grouped_out = nullptr;
     float *reduced = nullptr, *act_a = nullptr, *act_b = nullptr, *io_in = nullptr, *io_out = nullptr;
     int32_t *selected = nullptr, *group_offsets = nullptr, *g2c = nullptr, *c2g = nullptr, *counters = nullptr;
+    int32_t* identity = nullptr;               // 0, 1, 2, ...: the rank table of rows that arrive in canonical order
     int32_t* status = nullptr;
     Q4Job *gateup_jobs = nullptr, *down_jobs = nullptr;
     FusedJob* fused_jobs = nullptr;            // descriptors and arrival counters of the fused decode kernel
@@ -133,7 +134,7 @@ static void free_stack(Stack* s) {
     cudaFree(s->rin); cudaFree(s->logits); cudaFree(s->weights); cudaFree(s->chain);
     if (s->own_grouped) cudaFree(s->grouped_out);
     cudaFree(s->reduced); cudaFree(s->act_a); cudaFree(s->act_b); cudaFree(s->io_in); cudaFree(s->io_out);
-    cudaFree(s->selected); cudaFree(s->group_offsets); cudaFree(s->g2c); cudaFree(s->c2g);
+    cudaFree(s->selected); cudaFree(s->identity); cudaFree(s->group_offsets); cudaFree(s->g2c); cudaFree(s->c2g);
     cudaFree(s->counters); cudaFree(s->status); cudaFree(s->gateup_jobs); cudaFree(s->down_jobs);
     cudaFree(s->fused_jobs); cudaFree(s->fused_done);
     cudaFree(s->grouped_alt); cudaFree(s->weights_alt); cudaFree(s->layer_counters);
@@ -372,17 +373,11 @@ enum { SB_EXPERTS_ZERO_REMOTE = 1, SB_EXPERTS_ROUTER_INPUT_READY = 2, SB_EXPERTS
        SB_EXPERTS_TENSOR_CORE_SINGLE = 8, SB_EXPERTS_TWO_LAUNCHES = 16 };
 enum { SB_COMBINE_NORM = 1, SB_COMBINE_PREPARE_NEXT = 2 };
 
-// d_router_src feeds the router input (unless it is already prepared), d_x the expert projections.
-static int layer_experts_impl(Stack* s, int layer, const float* d_router_src, const float* d_x, int B, int flags,
-                              cudaStream_t st) {
-    if (!s || layer < 0 || layer >= (int)s->layers.size() || !d_x || !d_router_src || B < 1 || B > s->max_tokens)
-        return -1;
-    const Layer& l = s->layers[(size_t)layer];
-    const int H = s->hidden, M = s->inter, E = s->n_experts, K = s->topk;
-    const int jobs = B * K;
-    if ((flags & SB_EXPERTS_ZERO_REMOTE) &&
-        !cuda_ok(cudaMemsetAsync(s->grouped_out, 0, (size_t)jobs * H * sizeof(float), st), "zero grouped"))
-        return -1;
+// Router of a layer for B tokens: router input (unless already prepared), in-order logits and, unless the plan
+// kernel will do it (fused_topk), the softmax top-k into sel_out / w_out.
+static int layer_router(Stack* s, const Layer& l, const float* d_router_src, int B, int flags, bool fused_topk,
+                        int32_t* sel_out, float* w_out, cudaStream_t st) {
+    const int H = s->hidden, E = s->n_experts, K = s->topk;
     if (!(flags & SB_EXPERTS_ROUTER_INPUT_READY)) {
         Timed t(s, KC_ROUTER_INPUT, st);
         GlueArgs g;
@@ -396,14 +391,38 @@ static int layer_experts_impl(Stack* s, int layer, const float* d_router_src, co
         Timed t(s, KC_LOGITS, st);
         if (!cuda_ok(launch_router_logits(l.router_w, nullptr, s->rin, s->logits, B, E, H, st), "logits")) return -1;
     }
-    const bool fused_topk = B <= 8;
     if (!fused_topk) {
         Timed t(s, KC_TOPK, st);
-        if (!cuda_ok(launch_router_topk(s->logits, l.per_expert_scale, s->selected, s->weights, B, E, K, 1,
-                                        s->status, st), "topk"))
+        if (!cuda_ok(launch_router_topk(s->logits, l.per_expert_scale, sel_out, w_out, B, E, K, 1, s->status, st), "topk"))
             return -1;
         count_launches(1);
     }
+    return 0;
+}
+
+static int experts_run(Stack* s, const Layer& l, const float* d_x, int B, int K, const int32_t* selected, bool fused_topk,
+                       int flags, cudaStream_t st);
+
+// d_router_src feeds the router input (unless it is already prepared), d_x the expert projections.
+static int layer_experts_impl(Stack* s, int layer, const float* d_router_src, const float* d_x, int B, int flags,
+                              cudaStream_t st) {
+    if (!s || layer < 0 || layer >= (int)s->layers.size() || !d_x || !d_router_src || B < 1 || B > s->max_tokens)
+        return -1;
+    const Layer& l = s->layers[(size_t)layer];
+    if ((flags & SB_EXPERTS_ZERO_REMOTE) &&
+        !cuda_ok(cudaMemsetAsync(s->grouped_out, 0, (size_t)B * s->topk * s->hidden * sizeof(float), st), "zero grouped"))
+        return -1;
+    const bool fused_topk = B <= 8;
+    if (layer_router(s, l, d_router_src, B, flags, fused_topk, s->selected, s->weights, st) != 0) return -1;
+    return experts_run(s, l, d_x, B, s->topk, s->selected, fused_topk, flags, st);
+}
+
+// Grouping and expert projections for `B` rows with K selections each (`selected`: [B][K] expert ids; with
+// fused_topk the plan kernel derives them from the logits first).  Results land in grouped_out in grouped order.
+static int experts_run(Stack* s, const Layer& l, const float* d_x, int B, int K, const int32_t* selected, bool fused_topk,
+                       int flags, cudaStream_t st) {
+    const int H = s->hidden, M = s->inter, E = s->n_experts;
+    const int jobs = B * K;
     const size_t elems = (size_t)H * M;
     MoePlanArgs a;
     memset(&a, 0, sizeof a);
@@ -411,7 +430,7 @@ static int layer_experts_impl(Stack* s, int layer, const float* d_router_src, co
         a.logits = s->logits; a.per_expert_scale = l.per_expert_scale;
         a.selected_out = s->selected; a.weights_out = s->weights;
     }
-    a.selected = s->selected; a.rows = B; a.topk = K; a.n_experts = E;
+    a.selected = selected; a.rows = B; a.topk = K; a.n_experts = E;
     a.expert_begin = s->expert_begin; a.expert_end = s->expert_end;
     a.group_offsets = s->group_offsets; a.grouped_to_canonical = s->g2c; a.canonical_to_grouped = s->c2g;
     a.n_active = s->counters; a.max_group = s->counters + 1;
@@ -544,6 +563,79 @@ static int layer_experts_impl(Stack* s, int layer, const float* d_router_src, co
 
 int salt_b200_layer_experts(void* stack, int layer, const float* d_x, int B, int flags, void* stream_) {
     return layer_experts_impl((Stack*)stack, layer, d_x, d_x, B, flags, (cudaStream_t)stream_);
+}
+
+// ---- expert parallelism by token dispatch: the three steps of a layer as separate calls -----------------
+// home rank: router of its own tokens -> caller-owned selected / weights
+int salt_b200_layer_route(void* stack, int layer, const float* d_x, int B, int32_t* d_selected, float* d_weights, int flags,
+                          void* stream_) {
+    Stack* s = (Stack*)stack;
+    if (!s || layer < 0 || layer >= (int)s->layers.size() || !d_x || !d_selected || !d_weights || B < 1 || B > s->max_tokens)
+        return -1;
+    return layer_router(s, s->layers[(size_t)layer], d_x, B, flags & SB_EXPERTS_ROUTER_INPUT_READY, false, d_selected,
+                        d_weights, (cudaStream_t)stream_);
+}
+
+__global__ void __launch_bounds__(256)
+ungroup_rows_kernel(const float4* __restrict__ grouped, const int* __restrict__ c2g, float4* __restrict__ out, int n4) {
+    const int row = blockIdx.y;
+    const float4* src = grouped + (size_t)c2g[row] * n4;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x)
+        out[(size_t)row * n4 + i] = src[i];
+}
+
+// owner rank: rows that other ranks (and this one) routed to ITS experts -> d_out[i] = expert d_experts[i] applied
+// to d_rows[i], in the order given.  Every id must be one of this stack's experts (others set the status word).
+int salt_b200_layer_experts_routed(void* stack, int layer, const float* d_rows, const int32_t* d_experts, int n_rows,
+                                   float* d_out, int flags, void* stream_) {
+    Stack* s = (Stack*)stack;
+    cudaStream_t st = (cudaStream_t)stream_;
+    if (!s || layer < 0 || layer >= (int)s->layers.size() || n_rows < 0 || n_rows > s->max_tokens * s->topk ||
+        (s->hidden % 4) != 0)
+        return -1;
+    if (n_rows == 0) return 0;
+    if (!d_rows || !d_experts || !d_out || ((uintptr_t)d_out & 15)) return -1;
+    const Layer& l = s->layers[(size_t)layer];
+    flags &= (SB_EXPERTS_TENSOR_CORE | SB_EXPERTS_TENSOR_CORE_SINGLE);
+    if (experts_run(s, l, d_rows, n_rows, 1, d_experts, false, flags | SB_EXPERTS_TWO_LAUNCHES, st) != 0) return -1;
+    const int n4 = s->hidden / 4;
+    ungroup_rows_kernel<<<dim3((n4 + 255) / 256, n_rows), 256, 0, st>>>((const float4*)s->grouped_out, s->c2g, (float4*)d_out, n4);
+    count_launches(1);
+    return cuda_ok(cudaGetLastError(), "ungroup") ? 0 : -1;
+}
+
+// home rank: the returned rows in canonical order (token-major, rank order) -> ordered weighted reduce, norm,
+// next router input, exactly as salt_b200_layer_combine does from the grouped buffer
+int salt_b200_layer_combine_rows(void* stack, int layer, const float* d_rows, const float* d_weights, int B, float* d_y,
+                                 int flags, void* stream_) {
+    Stack* s = (Stack*)stack;
+    cudaStream_t st = (cudaStream_t)stream_;
+    if (!s || layer < 0 || layer >= (int)s->layers.size() || !d_rows || !d_weights || !d_y || B < 1 || B > s->max_tokens)
+        return -1;
+    const int J = s->max_tokens * s->topk;
+    if (!s->identity) {
+        std::vector<int32_t> id((size_t)J);
+        for (int i = 0; i < J; i++) id[(size_t)i] = i;
+        if (!upload(&s->identity, id.data(), (size_t)J)) return -1;
+    }
+    const Layer& l = s->layers[(size_t)layer];
+    const bool next = (flags & SB_COMBINE_PREPARE_NEXT) && layer + 1 < (int)s->layers.size();
+    GlueArgs g;
+    memset(&g, 0, sizeof g);
+    g.weights = d_weights; g.c2g = s->identity; g.grouped = d_rows; g.topk = s->topk; g.jobs = B * s->topk;
+    g.y_out = d_y; g.n = s->hidden; g.status = s->status;
+    g.tables_late = 1;                  // the weights may come from the kernel right before this one
+    if ((flags & SB_COMBINE_NORM) && l.norm_weight) { g.norm_w = l.norm_weight; g.eps_norm = l.eps; }
+    if (next) {
+        const Layer& nl = s->layers[(size_t)layer + 1];
+        g.router_scale = nl.router_scale; g.eps_router = nl.eps; g.rin = s->rin;
+    }
+    {
+        Timed t(s, KC_REDUCE, st);
+        if (!cuda_ok(launch_glue(g, B, st), "combine rows")) return -1;
+    }
+    count_launches(1);
+    return 0;
 }
 
 // Ordered weighted reduce of grouped_out into d_y; SB_COMBINE_NORM applies the

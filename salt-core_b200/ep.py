@@ -1,12 +1,20 @@
 """Expert-parallel plumbing for the MoE stack (one process per GPU, torch.distributed).
 
 Sharding rule: rank r of W owns the contiguous expert range
-[r*E//W, (r+1)*E//W) of every layer.  Activations are replicated; each rank
-fills only the rows of the grouped expert-output buffer that belong to its
-experts (global grouped order), and one exchange per layer completes the buffer
-on every rank.  Each row is written by exactly one rank and is +0 elsewhere, so a
-sum over ranks reproduces it exactly, in any order: the result is independent
-of the number of ranks.
+[r*E//W, (r+1)*E//W) of every layer.  Two data planes:
+
+* replicated activations (``forward``, and the stack's own peer-memory exchange): every rank routes
+  all tokens, fills only the rows of the grouped expert-output buffer that belong to its
+  experts (global grouped order), and one exchange per layer completes the buffer
+  on every rank.  Each row is written by exactly one rank and is +0 elsewhere, so a
+  sum over ranks reproduces it exactly, in any order.
+* token dispatch (``forward_dispatch``): tokens are partitioned by home rank; a layer routes its
+  own tokens, sends each selection's activation row to the owner of its expert (all-to-all),
+  the owner applies the expert, the result returns to the home rank (all-to-all), which reduces
+  its tokens' rows in rank order.
+
+Both give results that are independent of the number of ranks: a selection's output depends only
+on (expert weights, token row) and the reduce order is fixed at the token.
 """
 from __future__ import annotations
 
@@ -77,3 +85,91 @@ def forward(stack, grouped, d_x, B, d_out, act, stream=0, first=0, count=None, g
             raise RuntimeError("salt_b200_layer_combine failed")
         cur = out.data_ptr()
     return d_out
+
+
+def dispatch_plan(selected, n_experts: int, world: int):
+    """For a home rank's selections ``selected`` ([B][K] expert ids, torch): the order in which its B*K
+    selections are sent (grouped by destination rank, canonical order inside a group), the number sent to
+    every rank, and the expert id of every sent row."""
+    import torch
+    flat = selected.reshape(-1).to(torch.int64)
+    bounds = torch.tensor([r * n_experts // world for r in range(1, world)], dtype=torch.int64, device=flat.device)
+    dest = torch.bucketize(flat, bounds, right=True)            # owner of each selection's expert
+    order = torch.argsort(dest, stable=True)
+    counts = torch.bincount(dest, minlength=world)
+    return order, counts, flat[order].to(torch.int32)
+
+
+class StackOps:
+    """The three per-layer steps of token dispatch on a MoeStack (device tensors, current CUDA stream)."""
+
+    def __init__(self, stack, tensor_core=False):
+        self.stack, self.tc = stack, tensor_core
+        self.n_experts, self.topk, self.n_layers = stack.n_experts, stack.topk, stack.n_layers
+
+    def _sp(self):
+        import torch
+        return torch.cuda.current_stream().cuda_stream
+
+    def route(self, layer, x, router_input_ready):
+        import torch
+        B = x.shape[0]
+        sel = torch.empty((B, self.topk), dtype=torch.int32, device=x.device)
+        w = torch.empty((B, self.topk), dtype=torch.float32, device=x.device)
+        if self.stack.layer_route(layer, x.data_ptr(), B, sel.data_ptr(), w.data_ptr(), router_input_ready,
+                                  stream=self._sp()) != 0:
+            raise RuntimeError("salt_b200_layer_route failed")
+        return sel, w
+
+    def experts(self, layer, rows, ids):
+        import torch
+        out = torch.empty_like(rows)
+        if rows.shape[0] and self.stack.layer_experts_routed(layer, rows.data_ptr(), ids.data_ptr(), rows.shape[0],
+                                                             out.data_ptr(), tensor_core=self.tc,
+                                                             stream=self._sp()) != 0:
+            raise RuntimeError("salt_b200_layer_experts_routed failed")
+        return out
+
+    def combine(self, layer, canon_rows, w, out, apply_norm, prepare_next):
+        if self.stack.layer_combine_rows(layer, canon_rows.data_ptr(), w.data_ptr(), w.shape[0], out.data_ptr(),
+                                         apply_norm, prepare_next, stream=self._sp()) != 0:
+            raise RuntimeError("salt_b200_layer_combine_rows failed")
+        return out
+
+
+def forward_dispatch(ops, x, out, act, first=0, count=None, group=None, norm_last=True, stats=None):
+    """Layers [first, first+count) for THIS rank's tokens ``x`` ([B_local][hidden]) with token dispatch and
+    combine over ``torch.distributed`` all-to-alls (NCCL on GPUs).  ``ops`` supplies route / experts / combine
+    (``StackOps`` on a GPU).  The stack of an owner must hold world * B_local * topk rows (every selection of
+    every rank may land on one owner).  ``stats``: a dict that receives the rows sent and received."""
+    import torch
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    count = ops.n_layers - first if count is None else count
+    K, H = ops.topk, x.shape[1]
+    cur = x
+    for i in range(count):
+        layer, last = first + i, i == count - 1
+        sel, w = ops.route(layer, cur, i > 0)
+        order, send_counts, ids = dispatch_plan(sel, ops.n_experts, world)
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=group)
+        sc, rc = send_counts.tolist(), recv_counts.tolist()          # the one host synchronisation of the layer
+        rows = cur.index_select(0, order // K)
+        n_recv = int(sum(rc))
+        recv_rows = torch.empty((n_recv, H), dtype=cur.dtype, device=cur.device)
+        recv_ids = torch.empty((n_recv,), dtype=torch.int32, device=cur.device)
+        dist.all_to_all_single(recv_rows, rows, rc, sc, group=group)
+        dist.all_to_all_single(recv_ids, ids, rc, sc, group=group)
+        done = ops.experts(layer, recv_rows, recv_ids)
+        back = torch.empty_like(rows)
+        dist.all_to_all_single(back, done, sc, rc, group=group)
+        canon = torch.empty_like(back)
+        canon.index_copy_(0, order, back)                            # back to canonical (token, rank) order
+        dst = out if last else act[i & 1]
+        ops.combine(layer, canon, w, dst, norm_last or not last, not last)
+        if stats is not None:
+            stats["rows_sent"] = stats.get("rows_sent", 0) + int(rows.shape[0])
+            stats["rows_received"] = stats.get("rows_received", 0) + n_recv
+        cur = dst
+    return out

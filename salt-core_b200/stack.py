@@ -145,6 +145,21 @@ class MoeStack:
         flags = (1 if apply_norm else 0) | (2 if prepare_next else 0)
         return self.lib.salt_b200_layer_combine(self.handle, layer, B, C.c_void_p(d_y), flags, C.c_void_p(stream))
 
+    # expert parallelism by token dispatch (see ep.forward_dispatch)
+    def layer_route(self, layer, d_x, B, d_selected, d_weights, router_input_ready=False, stream=0):
+        return self.lib.salt_b200_layer_route(self.handle, layer, C.c_void_p(d_x), B, C.c_void_p(d_selected),
+                                              C.c_void_p(d_weights), 2 if router_input_ready else 0, C.c_void_p(stream))
+
+    def layer_experts_routed(self, layer, d_rows, d_experts, n_rows, d_out, tensor_core=False, stream=0):
+        tc = 0 if not tensor_core else (8 if tensor_core == "single" else 4)
+        return self.lib.salt_b200_layer_experts_routed(self.handle, layer, C.c_void_p(d_rows), C.c_void_p(d_experts),
+                                                       n_rows, C.c_void_p(d_out), tc, C.c_void_p(stream))
+
+    def layer_combine_rows(self, layer, d_rows, d_weights, B, d_y, apply_norm=True, prepare_next=False, stream=0):
+        flags = (1 if apply_norm else 0) | (2 if prepare_next else 0)
+        return self.lib.salt_b200_layer_combine_rows(self.handle, layer, C.c_void_p(d_rows), C.c_void_p(d_weights), B,
+                                                     C.c_void_p(d_y), flags, C.c_void_p(stream))
+
     EP_PUSH, EP_PULL = 1, 2
 
     def ep_region(self):

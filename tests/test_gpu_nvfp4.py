@@ -64,6 +64,47 @@ def test_nvfp4_qdq_many_blocks_vs_oracle(orc):
     assert_bits_equal(dq, d, "dequant")
 
 
+def test_nvfp4_qdq_every_rounding_boundary_vs_oracle(orc):
+    """The device encoders are arithmetic (round to nearest even in the target format) where the reference
+    searches for the nearest code (src/nvfp4.c:41-80).  Sweep every decision boundary of both: block maxima
+    that put the scale on, just below and just above each midpoint of consecutive E4M3 codes (and on the codes
+    themselves, the sub-normal grid, the clamp at 448), and block elements on, below and above every E2M1 tie
+    point of the block's scale, both signs."""
+    g = gpu()
+    dec = np.array([orc.e4m3fn(c) for c in range(0x7f)], np.float64)          # the finite non-negative codes
+    targets = np.concatenate([(dec[:-1] + dec[1:]) / 2, dec, [448.0, 460.0, 2.0 ** -10, 2.0 ** -11, 3e-4]])
+    ties = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], np.float64)
+    blocks = []
+    for ig in (1.0, 64.0):
+        for tv in targets:
+            base = np.float32(tv * 6.0 / ig)                                  # amax that lands the scale near tv
+            for step in range(-3, 4):
+                amax = base
+                for _ in range(abs(step)):
+                    amax = np.nextafter(amax, np.float32(np.inf if step > 0 else 0), dtype=np.float32)
+                blk = np.zeros(16, np.float32)
+                blk[0] = amax
+                frac = (ties[(np.arange(15) + step) % ties.size] / 6.0) * np.float64(amax)
+                blk[1:] = frac.astype(np.float32)
+                for i in range(1, 16, 3):                                     # one ulp to either side of a tie
+                    blk[i] = np.nextafter(blk[i], np.float32(0), dtype=np.float32)
+                for i in range(2, 16, 3):
+                    blk[i] = np.nextafter(blk[i], np.float32(np.inf), dtype=np.float32)
+                blk[1::2] *= np.float32(-1.0)
+                blocks.append((ig, blk))
+    for ig in (1.0, 64.0):
+        x = np.concatenate([b for i, b in blocks if i == ig])
+        x = np.ascontiguousarray(np.concatenate([x, np.zeros((-x.size) % 256, np.float32)]))
+        packed, scales, dq = np.zeros(x.size // 2, np.uint8), np.zeros(x.size // 16, np.uint8), np.zeros(x.size, np.float32)
+        assert g.nvfp4_qdq(x, ig, packed, scales, dq) == 0
+        rc, p, sc, d = orc.nvfp4_qdq(x, ig)
+        assert rc == 0
+        assert len(set(sc.tolist())) > 120                                    # the sweep reaches (nearly) every scale code
+        assert_bits_equal(scales, sc, f"scales, input global {ig}")
+        assert_bits_equal(packed, p, f"codes, input global {ig}")
+        assert_bits_equal(dq, d, f"dequant, input global {ig}")
+
+
 def test_nvfp4_matvec_golden_and_reference_kat(orc):
     g, bm, fx = gpu(), backend_mod(), golden("nvfp4.npz")
     R, C = fx["wpacked"].shape[0], fx["wpacked"].shape[1] * 2
