@@ -576,12 +576,19 @@ int salt_b200_layer_route(void* stack, int layer, const float* d_x, int B, int32
                         d_weights, (cudaStream_t)stream_);
 }
 
+// out[row] = grouped[c2g[row]]; a row whose expert is not one of this rank's gets zeros and sets the error word
+// (its slot in the grouped buffer was never computed, or, for an id outside the table, never assigned)
 __global__ void __launch_bounds__(256)
-ungroup_rows_kernel(const float4* __restrict__ grouped, const int* __restrict__ c2g, float4* __restrict__ out, int n4) {
-    const int row = blockIdx.y;
-    const float4* src = grouped + (size_t)c2g[row] * n4;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x)
-        out[(size_t)row * n4 + i] = src[i];
+ungroup_rows_kernel(const float4* __restrict__ grouped, const int* __restrict__ c2g, const int32_t* __restrict__ experts,
+                    int expert_begin, int expert_end, int n_rows, float4* __restrict__ out, int n4, int* status) {
+    const int row = blockIdx.x;
+    const int e = experts[row];
+    const bool mine = e >= expert_begin && e < expert_end;
+    const int g = mine ? c2g[row] : -1;
+    if ((g < 0 || g >= n_rows) && blockIdx.y == 0 && threadIdx.x == 0 && status) atomicOr(status, SB_ERR_INDEX);
+    const float4* src = grouped + (size_t)(g >= 0 && g < n_rows ? g : 0) * n4;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n4; i += gridDim.y * blockDim.x)
+        out[(size_t)row * n4 + i] = (g >= 0 && g < n_rows) ? src[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 }
 
 // owner rank: rows that other ranks (and this one) routed to ITS experts -> d_out[i] = expert d_experts[i] applied
@@ -599,7 +606,9 @@ int salt_b200_layer_experts_routed(void* stack, int layer, const float* d_rows, 
     flags &= (SB_EXPERTS_TENSOR_CORE | SB_EXPERTS_TENSOR_CORE_SINGLE);
     if (experts_run(s, l, d_rows, n_rows, 1, d_experts, false, flags | SB_EXPERTS_TWO_LAUNCHES, st) != 0) return -1;
     const int n4 = s->hidden / 4;
-    ungroup_rows_kernel<<<dim3((n4 + 255) / 256, n_rows), 256, 0, st>>>((const float4*)s->grouped_out, s->c2g, (float4*)d_out, n4);
+    ungroup_rows_kernel<<<dim3(n_rows, (n4 + 255) / 256), 256, 0, st>>>((const float4*)s->grouped_out, s->c2g, d_experts,
+                                                                      s->expert_begin, s->expert_end, n_rows,
+                                                                      (float4*)d_out, n4, s->status);
     count_launches(1);
     return cuda_ok(cudaGetLastError(), "ungroup") ? 0 : -1;
 }
