@@ -55,9 +55,11 @@ def parse():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-extra", action="store_true",
                     help="skip the untimed extras of the default run (batch sweep, expert-phase roofline, parity check)")
-    ap.add_argument("--ep-exchange", choices=["peer", "nccl"], default="peer",
+    ap.add_argument("--ep-exchange", choices=["peer", "nccl", "dispatch"], default="peer",
                     help="N>1: exchange of the grouped expert outputs by the stack's own kernel over peer "
-                         "memory (falls back to nccl when the regions cannot be mapped) or by an NCCL all-reduce")
+                         "memory (falls back to nccl when the regions cannot be mapped), by an NCCL all-reduce, or "
+                         "dispatch: tokens partitioned by home rank, rows sent to the owners of their experts and "
+                         "results returned to the home rank by NCCL all-to-alls")
     ap.add_argument("--prefill", default=None, choices=["exact", "single", "split", "blockscaled"],
                     help="run the layers one by one with the expert projections on the exact kernels, or on the "
                          "tensor cores: affine-Q4 with operands rounded to fp16 once (single) or carried as hi+lo "
@@ -382,9 +384,21 @@ def run_b200(args):
 
     ep = importlib.import_module("salt-core_b200.ep")
 
+    dispatch = world > 1 and args.ep_exchange == "dispatch"
+    b_loc = args.batch
+    x_loc = d_x[rank * b_loc:(rank + 1) * b_loc]
+    y_loc = d_y[rank * b_loc:(rank + 1) * b_loc]
+    act_loc = [act[0][:b_loc], act[1][:b_loc]]
+    dispatch_stats = {}
+
     def forward_ep(src, dst):
-        """Expert-parallel pass: one exchange of the grouped expert outputs per layer."""
-        ep.forward(stack, grouped, src, B, dst, act, stream=sp)
+        """Expert-parallel pass: one exchange of the grouped expert outputs per layer, or token dispatch."""
+        if dispatch:
+            # the last layer's norm as the single-GPU path of the same mode has it (token 0's CRC then agrees)
+            ep.forward_dispatch(ep.StackOps(stack, tc_mode), x_loc, y_loc, act_loc, norm_last=bool(args.prefill),
+                                stats=dispatch_stats)
+        else:
+            ep.forward(stack, grouped, src, B, dst, act, stream=sp)
 
     tc_mode = {None: False, "exact": False, "single": "single", "split": "split", "blockscaled": True}[args.prefill]
 
@@ -398,6 +412,8 @@ def run_b200(args):
             cur = out.data_ptr()
 
     peer = world > 1 and args.ep_exchange == "peer" and not args.prefill and ep.connect_peer_memory(stack)
+    if world > 1 and args.prefill and not dispatch:
+        raise SystemExit("expert-parallel prefill runs with --ep-exchange dispatch")
     use_graph = (world == 1 or peer) and not args.no_graph and not args.prefill
     with torch.cuda.stream(stream):
         n0 = stack.launch_count()
@@ -408,6 +424,7 @@ def run_b200(args):
         else:
             assert stack.forward_device(d_x.data_ptr(), B, d_y.data_ptr(), stream=sp) == 0
         launches_per_step = stack.launch_count() - n0
+        dispatch_stats.clear()
         if peer:
             # a rank that never saw a peer's rows (bounded wait ran out) sends every rank back to NCCL
             failed = torch.tensor([stack.status(sp)], dtype=torch.int32, device="cuda")
@@ -469,7 +486,10 @@ def run_b200(args):
             if world == 1 and not args.prefill:
                 stack.forward_host(x_host)
             else:
-                d_x.copy_(h_in, non_blocking=True)
+                if dispatch:
+                    x_loc.copy_(h_in[rank * b_loc:(rank + 1) * b_loc], non_blocking=True)
+                else:
+                    d_x.copy_(h_in, non_blocking=True)
                 if use_graph:
                     assert stack.graph_launch(sp) == 0
                 elif peer:
@@ -478,7 +498,10 @@ def run_b200(args):
                     forward_ep(d_x, d_y)
                 else:
                     forward_layers(d_x, d_y)
-                h_out.copy_(d_y, non_blocking=True)
+                if dispatch:
+                    h_out[rank * b_loc:(rank + 1) * b_loc].copy_(y_loc, non_blocking=True)
+                else:
+                    h_out.copy_(d_y, non_blocking=True)
                 stream.synchronize()
 
         if peer:
@@ -663,7 +686,13 @@ def run_b200(args):
            "launch_mode": "cuda graph replay" if use_graph else "stream launches",
            "us_per_layer": 1e3 * ms_step / L}
     if world > 1:
-        out["ep_exchange"] = "peer memory (own kernel over NVLink)" if peer else "nccl all_reduce"
+        out["ep_exchange"] = ("peer memory (own kernel over NVLink)" if peer else
+                              "token dispatch and combine by NCCL all-to-alls (tokens partitioned by home rank)"
+                              if dispatch else "nccl all_reduce")
+        if dispatch:
+            out["e2e"]["h2d_bytes_per_step"] = b_loc * H * 4
+            out["e2e"]["d2h_bytes_per_step"] = b_loc * H * 4
+            out["e2e"]["api"] = "ep.forward_dispatch: salt_b200_layer_route / _experts_routed / _combine_rows + all_to_all"
     if roofline:
         out["roofline"] = roofline
         out["roofline_layer"] = roofline_layer
