@@ -23,7 +23,7 @@ from gpu_util import backend_mod, gpu
 pytestmark = pytest.mark.gpu
 
 
-def test_static_scratch_chain_matches_allocating_entry_point(synth):
+def test_static_scratch_chain_matches_allocating_entry_point(synth, orc):
     import torch
     g, bm = gpu(), backend_mod()
     H, M = 256, 128
@@ -58,6 +58,12 @@ def test_static_scratch_chain_matches_allocating_entry_point(synth):
         assert rc == 0
         torch.cuda.synchronize()
         assert_bits_equal(d_y.cpu().numpy(), want, f"call {call} (ntok={ntok})")
+        # and against the CPU oracle directly (first and last token of the call)
+        for t in (0, ntok - 1):
+            gate = orc.q4_matvec(*tensors[0], M, H, x[t])
+            up = orc.q4_matvec(*tensors[1], M, H, x[t])
+            ref = orc.q4_matvec(*tensors[2], H, M, orc.map_f32("gelu_tanh", gate) * up)
+            assert_bits_equal(d_y[t].cpu().numpy(), ref, f"call {call} token {t} vs oracle")
     # beyond the fixed capacity (ntok*inter > 65536 floats) the call is refused, nothing runs
     big = 65536 // M + 1
     d_x = torch.zeros(big, H, dtype=torch.float32, device="cuda")
