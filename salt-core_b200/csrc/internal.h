@@ -62,7 +62,7 @@ cudaError_t launch_q4_fused(const FusedArgs& args, cudaStream_t stream);
 
 // One decode layer (one token) in one launch: [reduce + RMSNorm of the previous layer] -> router
 // input -> logits -> top-k -> experts.
-struct LayerDecodeArgs {
+struct alignas(16) LayerDecodeArgs {
     FusedArgs f;                   // H, M, chain, out (this layer's grouped rows), done (this layer's counters), status
     const float* x_in;             // [H] the stack input, used when prev_grouped is null
     const float* prev_grouped;     // [topk][H] grouped outputs of the previous layer (rank order) or null
@@ -87,6 +87,11 @@ struct LayerDecodeArgs {
 };
 bool q4_layer_decode_plan(int H, int M, int E, int topk, int n_jobs_max, FusedLaunch* out);
 cudaError_t launch_q4_layer_decode(const LayerDecodeArgs& args, int n_jobs_max, cudaStream_t stream);
+// All layers in one launch: d_layers [n_layers] arguments in device memory (f.jobs_per_round = the value of
+// q4_layer_decode_jobs_per_round, f.n_x = 1), d_done [n_layers] arrival counters, zero at launch.
+cudaError_t launch_q4_stack_decode(const LayerDecodeArgs* d_layers, int n_layers, int* d_done, int H, int M, int E, int topk,
+                                   int n_jobs_max, cudaStream_t stream);
+int q4_layer_decode_jobs_per_round(int H, int M, int E, int topk, int n_jobs_max);
 
 // Affine 8-bit jobs (same descriptor; vals = one byte per element): one block per (row, token, job).
 cudaError_t launch_q8_jobs(const Q4Job* jobs, int njobs, int max_rows, int max_tok, int C, cudaStream_t stream);

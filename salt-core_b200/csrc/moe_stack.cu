@@ -65,7 +65,9 @@ struct Stack {
     int32_t* fused_done = nullptr;
     // one-launch decode layers (one token): buffers of the other parity and per-layer arrival counters
     float *grouped_alt = nullptr, *weights_alt = nullptr;
-    int32_t* layer_counters = nullptr;         // [layers_cap][FUSED_MAX_JOBS + 1]
+    int32_t* layer_counters = nullptr;         // [layers_cap][FUSED_MAX_JOBS + 1], then [layers_cap] "layer finished" counters
+    LayerDecodeArgs* d_layer_args = nullptr;   // [layers_cap] arguments of the whole-stack decode launch
+    std::vector<LayerDecodeArgs> h_layer_args;
     int layers_cap = 0;
     bool any_nvfp4 = false;
     // workspace of NVFP4 layers (allocated with the first one): quantise-dequantised activations of the
@@ -80,7 +82,7 @@ struct Stack {
     CUtensorMap fp4_x_gu[3], fp4_x_dn[3];      // packed activations as [2J][H/2] and as [J][M/2]
     CUtensorMap fp4_xs_gu[3], fp4_xs_dn[3];    // their block scales as [2J][H/16] and as [J][M/16]
     bool fp4_maps_ok = false;
-    bool fused_decode = true;                  // batches of up to FUSED_MAX_TOKENS tokens take the one-launch expert kernel
+    int fused_decode = 1;                      // 0: phase kernels; 1: one-launch expert kernel (B <= 4) and one launch per decode layer (B = 1); 2: all layers of a B = 1 pass in one launch (measured slower than 1)
     void *xh = nullptr, *xl = nullptr, *chain_h = nullptr, *chain_l = nullptr;   // fp16 operands (hi, lo) of the tensor-core path
     bool tc_ready = false;                     // tensor maps built (needs hidden, inter multiples of 64)
     TcMaps x_maps, chain_maps;                 // TMA descriptors of (xh, xl) and (chain_h, chain_l)
@@ -137,7 +139,7 @@ static void free_stack(Stack* s) {
     cudaFree(s->selected); cudaFree(s->identity); cudaFree(s->group_offsets); cudaFree(s->g2c); cudaFree(s->c2g);
     cudaFree(s->counters); cudaFree(s->status); cudaFree(s->gateup_jobs); cudaFree(s->down_jobs);
     cudaFree(s->fused_jobs); cudaFree(s->fused_done);
-    cudaFree(s->grouped_alt); cudaFree(s->weights_alt); cudaFree(s->layer_counters);
+    cudaFree(s->grouped_alt); cudaFree(s->weights_alt); cudaFree(s->layer_counters); cudaFree(s->d_layer_args);
     cudaFree(s->fp4_dq_gu); cudaFree(s->fp4_dq_dn); cudaFree(s->fp4_gate); cudaFree(s->fp4_up); cudaFree(s->fp4_ig_gu);
     cudaFree(s->fp4_ig_dn); cudaFree(s->fp4_packed); cudaFree(s->fp4_scales); cudaFree(s->fp4_gu_jobs); cudaFree(s->fp4_dn_jobs);
     cudaFree(s->fp4_tc_gu); cudaFree(s->fp4_tc_dn); cudaFree(s->fp4_live);
@@ -330,7 +332,7 @@ int salt_b200_stack_add_nvfp4_layer(void* stack, const SaltB200Nvfp4LayerSpec* s
 int salt_b200_stack_set_fused_decode(void* stack, int enable) {
     Stack* s = (Stack*)stack;
     if (!s) return -1;
-    s->fused_decode = enable != 0;
+    s->fused_decode = enable < 0 ? 0 : (enable > 2 ? 2 : enable);
     return 0;
 }
 
@@ -895,26 +897,35 @@ static bool decode_layers_apply(Stack* s, int B) {
 
 static int forward_decode_layers(Stack* s, int first, int count, const float* d_x, float* d_y, cudaStream_t st) {
     const int H = s->hidden, M = s->inter, K = s->topk;
+    // per layer: the logits arrival counter and FUSED_MAX_JOBS job counters; after all layers' blocks of those,
+    // one "layer finished" counter per layer (the whole-stack launch)
     const int stride = FUSED_MAX_JOBS + 1;
     if (count > s->layers_cap) {       // set-up, not part of a captured pass: forward passes are not captured before one has run
         cudaFree(s->layer_counters);
+        cudaFree(s->d_layer_args);
         s->layer_counters = nullptr;
-        if (!dev_alloc(&s->layer_counters, (size_t)count * stride)) return -1;
+        s->d_layer_args = nullptr;
+        if (!dev_alloc(&s->layer_counters, (size_t)count * (stride + 1)) || !dev_alloc(&s->d_layer_args, (size_t)count))
+            return -1;
+        s->h_layer_args.reserve((size_t)count);
         s->layers_cap = count;
     }
-    if (!cuda_ok(cudaMemsetAsync(s->layer_counters, 0, (size_t)count * stride * sizeof(int32_t), st), "layer counters"))
+    if (!cuda_ok(cudaMemsetAsync(s->layer_counters, 0, (size_t)count * (stride + 1) * sizeof(int32_t), st), "layer counters"))
         return -1;
     const size_t elems = (size_t)H * M;
     const int local = s->expert_end - s->expert_begin;
+    const int n_jobs_max = K < local ? K : local;
+    const bool stacked = s->fused_decode >= 2;
     float* gbuf[2] = {s->grouped_out, s->grouped_alt};
     float* wbuf[2] = {s->weights, s->weights_alt};
+    if (stacked) s->h_layer_args.resize((size_t)count);
     for (int i = 0; i < count; i++) {
         const Layer& l = s->layers[(size_t)first + i];
         LayerDecodeArgs a;
         memset(&a, 0, sizeof a);
         a.f.H = H; a.f.M = M; a.f.chain = s->chain; a.f.out = gbuf[i & 1];
         a.f.done = s->layer_counters + (size_t)i * stride + 1; a.f.status = s->status;
-        a.f.n_jobs_max = K < local ? K : local;
+        a.f.n_jobs_max = n_jobs_max;
         a.logits_count = s->layer_counters + (size_t)i * stride;
         if (i == 0) {
             a.x_in = d_x;
@@ -930,8 +941,25 @@ static int forward_decode_layers(Stack* s, int first, int count, const float* d_
         a.group_offsets = s->group_offsets;
         a.pool = l.pool; a.tables = l.sb_tables; a.lit_flags = l.lit_flags; a.expert_stride = l.expert_stride;
         a.value_bytes = elems / 2; a.group_bytes = elems / 64 * 2; a.tensor_bytes = a.value_bytes + 2 * a.group_bytes;
+        if (stacked) {
+            a.f.jobs_per_round = q4_layer_decode_jobs_per_round(H, M, s->n_experts, K, n_jobs_max);
+            a.f.n_x = 1;
+            s->h_layer_args[(size_t)i] = a;
+            continue;
+        }
         Timed t(s, KC_GATE_UP, st);
         if (!cuda_ok(launch_q4_layer_decode(a, a.f.n_jobs_max, st), "decode layer")) return -1;
+    }
+    if (stacked) {
+        // the arguments travel with every pass (a captured pass replays the copy from this host vector, whose
+        // storage stays put while the capacity holds: set-up, like the counters above)
+        if (!cuda_ok(cudaMemcpyAsync(s->d_layer_args, s->h_layer_args.data(), (size_t)count * sizeof(LayerDecodeArgs),
+                                     cudaMemcpyHostToDevice, st), "layer arguments"))
+            return -1;
+        Timed t(s, KC_GATE_UP, st);
+        if (!cuda_ok(launch_q4_stack_decode(s->d_layer_args, count, s->layer_counters + (size_t)count * stride, H, M,
+                                            s->n_experts, K, n_jobs_max, st), "decode stack"))
+            return -1;
     }
     const int last = count - 1;
     GlueArgs g;

@@ -195,6 +195,11 @@ struct FusedSmem {
         bar_sc = bar_x + 1;                           // scales and biases of the block (both phases)
         bar_dn = bar_x + 2;                           // packed down rows of the block
     }
+    // by one thread, when no thread of the block can still be waiting on them: before they are initialised again
+    __device__ __forceinline__ void inval_barriers() {
+        for (int i = 0; i < NW * FUSED_GU_CHUNKS + 3; i++)
+            asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(bar_gu + i)) : "memory");
+    }
     // by one thread, before the block's first barrier
     __device__ __forceinline__ void init_barriers() {
         for (int i = 0; i < NW * FUSED_GU_CHUNKS + 3; i++) mbar_init(bar_gu + i, bar_gu + i == bar_sc ? 6 : 1);   // bar_sc: one arrival per table and job segment
@@ -529,8 +534,13 @@ static __device__ __noinline__ float layer_ordered_sum(const float* sq, int n, b
     return ordered_sum_of_squares<LAYER_NV>(sq, n, bad, scan);
 }
 
-__global__ void __launch_bounds__(16 * LAYER_SLOTS, 1) q4_layer_decode_kernel(LayerDecodeArgs a) {
-    extern __shared__ __align__(128) uint8_t smem[];
+// One layer by the whole grid.  STACKED = false: the body of q4_layer_decode_kernel (one launch per layer; the
+// previous layer is the previous kernel).  STACKED = true: layer `li` of q4_stack_decode_kernel, whose blocks
+// stay resident over all layers: the previous layer is complete when every block has bumped its counter
+// (prev_done reaches the grid size; bounded wait), and the block's barriers are re-initialised.
+template <bool STACKED>
+__device__ __forceinline__ void layer_decode_body(const LayerDecodeArgs& a, uint8_t* smem, int li, const int* prev_done,
+                                                  int* my_done) {
     constexpr int SLOTS = LAYER_SLOTS, NT = 16 * SLOTS, NV = LAYER_NV;
     const int H = a.f.H, M = a.f.M, E = a.E, K = a.topk;
     const FusedGeom G = fused_geom(H, M, 1, SLOTS);
@@ -552,6 +562,7 @@ __global__ void __launch_bounds__(16 * LAYER_SLOTS, 1) q4_layer_decode_kernel(La
 
     // ---- before the dependency: barriers, this block's router row, the norm weights ----
     if (tid == 0) {
+        if (STACKED && li > 0) S.inval_barriers();    // every wait of the previous layer is over (block barrier at its end)
         S.init_barriers();
         if (cta < E) {
             mbar_expect_tx(S.bar_x, (uint32_t)(H * 4));
@@ -566,8 +577,20 @@ __global__ void __launch_bounds__(16 * LAYER_SLOTS, 1) q4_layer_decode_kernel(La
         rs[j] = d < H ? __ldg(a.router_scale + d) : 1.0f;
         v[j] = 0.0f;
     }
-    pdl_wait();                    // the previous layer's outputs
-    pdl_launch_dependents();
+    if (!STACKED) {
+        pdl_wait();                // the previous layer's outputs
+        pdl_launch_dependents();
+    } else if (li > 0) {
+        // the previous layer's outputs: every block of the grid has finished it
+        if (tid == 0) {
+            uint32_t i = 0;
+            while (ld_acquire_gpu(prev_done) < ncta && i < FUSED_SPIN_LIMIT) i++;
+            if (i >= FUSED_SPIN_LIMIT) timeout = true;
+        }
+        __syncthreads();
+    } else {
+        pdl_wait();
+    }
 
     // ---- the layer's input row: ordered weighted reduce of the previous layer, or the stack input ----
     if (a.prev_grouped != nullptr) {
@@ -766,6 +789,37 @@ __global__ void __launch_bounds__(16 * LAYER_SLOTS, 1) q4_layer_decode_kernel(La
     const int n_jobs = s_njobs;
     if (n_jobs > 0) timeout |= fused_expert_rounds<1, SLOTS>(a.f, G, S, n_jobs, true, s_rg, s_rd);
     if (timeout && a.f.status) atomicOr(a.f.status, SB_ERR_TIMEOUT);
+    if (STACKED) {
+        __syncthreads();            // all of this block's rows of the layer are written, its shared memory is free
+        if (tid == 0) {
+            __threadfence();
+            asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(my_done) : "memory");
+        }
+    }
+}
+
+__global__ void __launch_bounds__(16 * LAYER_SLOTS, 1) q4_layer_decode_kernel(LayerDecodeArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    layer_decode_body<false>(a, smem, 0, nullptr, nullptr);
+}
+
+// All layers of a decode step in ONE launch: the blocks (one per SM) stay resident, so the code of a layer is
+// fetched once per step instead of once per layer, and a layer ends with one arrival counter instead of a kernel
+// boundary.  layers[li] are the per-layer arguments (device memory), done[li] the arrival counters (zero at launch).
+__global__ void __launch_bounds__(16 * LAYER_SLOTS, 1)
+q4_stack_decode_kernel(const LayerDecodeArgs* __restrict__ layers, int n_layers, int* done) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ __align__(16) LayerDecodeArgs s_args;
+    static_assert(sizeof(LayerDecodeArgs) % 16 == 0, "layer arguments are copied in 16-byte pieces");
+#pragma unroll 1
+    for (int li = 0; li < n_layers; li++) {
+        __syncthreads();            // the previous layer's arguments are no longer read
+        for (int i = threadIdx.x; i < (int)(sizeof(LayerDecodeArgs) / 16); i += blockDim.x)
+            ((uint4*)&s_args)[i] = __ldg((const uint4*)(layers + li) + i);
+        __syncthreads();
+        layer_decode_body<true>(s_args, smem, li, li > 0 ? done + li - 1 : nullptr, done + li);
+    }
+    pdl_launch_dependents();
 }
 
 // ---- derived scale | bias tables ------------------------------------------------------------
@@ -865,6 +919,21 @@ bool q4_layer_decode_plan(int H, int M, int E, int topk, int n_jobs_max, FusedLa
     if ((size_t)layer_scratch(H, E, topk).end * 4 > g.off_sgu) return false;    // the scratch overlays the weight rows only
     if (out) *out = L;
     return true;
+}
+
+cudaError_t launch_q4_stack_decode(const LayerDecodeArgs* d_layers, int n_layers, int* d_done, int H, int M, int E, int topk,
+                                   int n_jobs_max, cudaStream_t stream) {
+    FusedLaunch L;
+    if (n_layers < 1 || !q4_layer_decode_plan(H, M, E, topk, n_jobs_max, &L)) return cudaErrorInvalidValue;
+    cudaError_t e = ensure_dynamic_smem((const void*)q4_stack_decode_kernel, FUSED_SMEM_LIMIT);
+    if (e != cudaSuccess) return e;
+    return launch_pdl(q4_stack_decode_kernel, dim3(L.grid), dim3(16 * LAYER_SLOTS), L.smem, stream, d_layers, n_layers, d_done);
+}
+
+// jobs_per_round of a layer's arguments (what launch_q4_layer_decode fills in for a single launch)
+int q4_layer_decode_jobs_per_round(int H, int M, int E, int topk, int n_jobs_max) {
+    FusedLaunch L;
+    return q4_layer_decode_plan(H, M, E, topk, n_jobs_max, &L) ? L.jobs_per_round : 0;
 }
 
 cudaError_t launch_q4_layer_decode(const LayerDecodeArgs& args, int n_jobs_max, cudaStream_t stream) {

@@ -110,7 +110,8 @@ class MoeStack:
 
     def set_fused_decode(self, enable):
         """Batches of up to 4 tokens: one-launch expert kernel (default) or the two-launch form."""
-        return self.lib.salt_b200_stack_set_fused_decode(self.handle, int(bool(enable)))
+        level = int(enable)                                   # 0 phase kernels, 1 one launch per layer, 2 one per pass
+        return self.lib.salt_b200_stack_set_fused_decode(self.handle, level)
 
     def set_grouped_out(self, device_ptr, nbytes):
         return self.lib.salt_b200_stack_set_grouped_out(self.handle, C.c_void_p(device_ptr), C.c_size_t(nbytes))

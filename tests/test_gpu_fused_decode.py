@@ -73,3 +73,45 @@ def test_fused_decode_sharded_expert_ranges(orc, synth):
     assert_bits_equal(d_y.cpu().numpy(), want, "eight ranges, fused kernel")
     for st in parts:
         st.close()
+
+
+@pytest.mark.parametrize("geom", [(2816, 704, 128, 8, 5), (256, 128, 32, 8, 7), (1344, 320, 16, 2, 4)])
+def test_whole_pass_in_one_launch_equals_per_layer_launches_and_oracle(orc, synth, geom):
+    """One token through several layers: all layers in one launch (level 2: resident blocks, a layer ends
+    with an arrival counter), one launch per layer (level 1), the phase kernels (level 0) and the CPU oracle
+    agree bit for bit; so do CUDA-graph replays of the one-launch pass, and sub-ranges of the layers."""
+    import torch
+    H, M, E, K, L = geom
+    make = synth.make_q4_moe_layer_bulk if H == 2816 else synth.make_q4_moe_layer
+    layers = [make(340 + i, hidden=H, inter=M, n_experts=E, topk=K) for i in range(L)]
+    x = synth.make_tokens(350, 1, H)
+    st = stack_mod().MoeStack(4, H, M, E, K)
+    for layer in layers:
+        st.add_layer(layer)
+    want, _ = oracle_stack(orc, layers, x, threads=8)
+    out = {}
+    for level in (2, 1, 0, 2):
+        assert st.set_fused_decode(level) == 0
+        out[level] = st.forward_host(x)
+        assert st.status() == 0
+        assert_bits_equal(out[level], want, f"level {level} vs oracle")
+    # graph replays of the whole-pass launch
+    stream = torch.cuda.Stream()
+    sp = stream.cuda_stream
+    d_x = torch.from_numpy(x).cuda()
+    d_y = torch.zeros_like(d_x)
+    with torch.cuda.stream(stream):
+        assert st.graph_capture(d_x.data_ptr(), 1, d_y.data_ptr(), sp) == 0
+        for rep in range(4):
+            d_y.zero_()
+            assert st.graph_launch(sp) == 0
+            stream.synchronize()
+            assert st.status(sp) == 0
+            assert_bits_equal(d_y.cpu().numpy(), want, f"graph replay {rep}")
+    # a sub-range of the layers (first = 1): the pass starts from a given row
+    mid, _ = oracle_stack(orc, layers[:1], x, threads=8)
+    rc, mid_n = orc.rmsnorm(mid[0], layers[0].norm_weight, layers[0].eps, True)
+    assert rc == 0
+    got = st.forward_host(mid_n.reshape(1, H), first=1)
+    assert_bits_equal(got, want, "layers 1.. from the normalised output of layer 0")
+    st.close()
