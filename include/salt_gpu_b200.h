@@ -462,14 +462,21 @@ int salt_b200_layer_combine(void *stack, int layer, int B, float *d_y, int flags
  *                          rows are grouped by expert as reference src/moe_group.c:83-182 groups them and every
  *                          row's result depends only on (expert weights, row), so it is the same whichever rank
  *                          computes it and whatever else is in the call.  flags: the TENSOR_CORE flags
- *   _layer_combine_rows    home rank: d_rows [B * topk][hidden] in canonical order (token-major, rank order)
+ *   _layer_combine_rows    home rank: the returned rows d_rows [B * topk][hidden]; selection (token t, rank k) is
+ *                          row d_row_index[t * topk + k], or row t * topk + k when d_row_index is NULL
  *                          -> ordered weighted reduce (src/moe_group.c:211-224), then as salt_b200_layer_combine */
 int salt_b200_layer_route(void *stack, int layer, const float *d_x, int B, int32_t *d_selected, float *d_weights,
                           int flags, void *stream);
+/* The send order of a home rank's n = B * topk selections (device arrays): rank r of `world` owns experts
+ * [r * n_experts / world, (r + 1) * n_experts / world); selections are grouped by owner, canonical order inside
+ * a group.  d_order[p] = canonical index of the p-th row sent, d_pos = its inverse (the row of selection i),
+ * d_ids[p] = that row's expert, d_counts[r] = rows for rank r.  world <= 8. */
+int salt_b200_dispatch_plan(const int32_t *d_selected, int n, int n_experts, int world, int32_t *d_order,
+                            int32_t *d_pos, int32_t *d_ids, int32_t *d_counts, void *stream);
 int salt_b200_layer_experts_routed(void *stack, int layer, const float *d_rows, const int32_t *d_experts, int n_rows,
                                    float *d_out, int flags, void *stream);
-int salt_b200_layer_combine_rows(void *stack, int layer, const float *d_rows, const float *d_weights, int B,
-                                 float *d_y, int flags, void *stream);
+int salt_b200_layer_combine_rows(void *stack, int layer, const float *d_rows, const int32_t *d_row_index,
+                                 const float *d_weights, int B, float *d_y, int flags, void *stream);
 /* Expert-parallel exchange over peer memory (no reference counterpart: the reference is
  * single-device; the sharding rule follows from its expert independence,
  * models/gemma4-26b-a4b/src/gemma4.c:154-186 reduces per-selection outputs in rank order).

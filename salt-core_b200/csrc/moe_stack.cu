@@ -568,6 +568,83 @@ int salt_b200_layer_experts(void* stack, int layer, const float* d_x, int B, int
 }
 
 // ---- expert parallelism by token dispatch: the three steps of a layer as separate calls -----------------
+// Send order of a home rank's n selections: grouped by the rank that owns each selection's expert, canonical
+// order inside a group (a stable counting sort over at most EP_MAX_WORLD destinations, one block).
+__global__ void __launch_bounds__(1024)
+dispatch_plan_kernel(const int32_t* __restrict__ sel, int n, int E, int world, int32_t* __restrict__ order,
+                     int32_t* __restrict__ pos, int32_t* __restrict__ ids, int32_t* __restrict__ counts) {
+    __shared__ int warp_tot[EP_MAX_WORLD][32];
+    __shared__ int s_start[EP_MAX_WORLD + 1];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int chunk = (n + 1023) / 1024;
+    const int i0 = min(n, tid * chunk), i1 = min(n, i0 + chunk);
+    auto owner = [&](int e) {
+        int d = 0;
+        for (int r = 1; r < world; r++) d += e >= (int)((long long)r * E / world) ? 1 : 0;
+        return d;                                     // ids outside [0, E) travel to rank 0 or the last rank, which flags them
+    };
+    int cnt[EP_MAX_WORLD], base[EP_MAX_WORLD];
+#pragma unroll
+    for (int d = 0; d < EP_MAX_WORLD; d++) cnt[d] = 0;
+    for (int i = i0; i < i1; i++) {
+        const int o = owner(sel[i]);
+#pragma unroll
+        for (int d = 0; d < EP_MAX_WORLD; d++) cnt[d] += o == d ? 1 : 0;
+    }
+#pragma unroll
+    for (int d = 0; d < EP_MAX_WORLD; d++) {
+        int inc = cnt[d];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += t;
+        }
+        base[d] = inc - cnt[d];                       // exclusive inside the warp
+        if (lane == 31) warp_tot[d][warp] = inc;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        int run = 0;
+        for (int d = 0; d < EP_MAX_WORLD; d++) {
+            int inc = warp_tot[d][lane];
+            const int own = inc;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += t;
+            }
+            warp_tot[d][lane] = inc - own;            // exclusive prefix of the warp totals
+            const int total = __shfl_sync(0xffffffffu, inc, 31);
+            if (lane == 0) {
+                s_start[d] = run;
+                if (d < world) counts[d] = total;
+            }
+            run += total;
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int d = 0; d < EP_MAX_WORLD; d++) base[d] += s_start[d] + warp_tot[d][warp];
+    for (int i = i0; i < i1; i++) {
+        const int e = sel[i], o = owner(e);
+        int p = 0;
+#pragma unroll
+        for (int d = 0; d < EP_MAX_WORLD; d++)
+            if (o == d) p = base[d]++;
+        pos[i] = p;
+        order[p] = i;
+        ids[p] = e;
+    }
+}
+
+int salt_b200_dispatch_plan(const int32_t* d_selected, int n, int n_experts, int world, int32_t* d_order, int32_t* d_pos,
+                            int32_t* d_ids, int32_t* d_counts, void* stream_) {
+    if (n < 0 || n_experts < 1 || world < 1 || world > EP_MAX_WORLD || world > n_experts || !d_counts) return -1;
+    if (n > 0 && (!d_selected || !d_order || !d_pos || !d_ids)) return -1;
+    dispatch_plan_kernel<<<1, 1024, 0, (cudaStream_t)stream_>>>(d_selected, n, n_experts, world, d_order, d_pos, d_ids, d_counts);
+    return cuda_ok(cudaGetLastError(), "dispatch plan") ? 0 : -1;
+}
+
 // home rank: router of its own tokens -> caller-owned selected / weights
 int salt_b200_layer_route(void* stack, int layer, const float* d_x, int B, int32_t* d_selected, float* d_weights, int flags,
                           void* stream_) {
@@ -617,14 +694,14 @@ int salt_b200_layer_experts_routed(void* stack, int layer, const float* d_rows, 
 
 // home rank: the returned rows in canonical order (token-major, rank order) -> ordered weighted reduce, norm,
 // next router input, exactly as salt_b200_layer_combine does from the grouped buffer
-int salt_b200_layer_combine_rows(void* stack, int layer, const float* d_rows, const float* d_weights, int B, float* d_y,
-                                 int flags, void* stream_) {
+int salt_b200_layer_combine_rows(void* stack, int layer, const float* d_rows, const int32_t* d_row_index,
+                                 const float* d_weights, int B, float* d_y, int flags, void* stream_) {
     Stack* s = (Stack*)stack;
     cudaStream_t st = (cudaStream_t)stream_;
     if (!s || layer < 0 || layer >= (int)s->layers.size() || !d_rows || !d_weights || !d_y || B < 1 || B > s->max_tokens)
         return -1;
     const int J = s->max_tokens * s->topk;
-    if (!s->identity) {
+    if (!d_row_index && !s->identity) {
         std::vector<int32_t> id((size_t)J);
         for (int i = 0; i < J; i++) id[(size_t)i] = i;
         if (!upload(&s->identity, id.data(), (size_t)J)) return -1;
@@ -633,9 +710,9 @@ int salt_b200_layer_combine_rows(void* stack, int layer, const float* d_rows, co
     const bool next = (flags & SB_COMBINE_PREPARE_NEXT) && layer + 1 < (int)s->layers.size();
     GlueArgs g;
     memset(&g, 0, sizeof g);
-    g.weights = d_weights; g.c2g = s->identity; g.grouped = d_rows; g.topk = s->topk; g.jobs = B * s->topk;
-    g.y_out = d_y; g.n = s->hidden; g.status = s->status;
-    g.tables_late = 1;                  // the weights may come from the kernel right before this one
+    g.weights = d_weights; g.c2g = d_row_index ? d_row_index : s->identity; g.grouped = d_rows; g.topk = s->topk;
+    g.jobs = B * s->topk; g.y_out = d_y; g.n = s->hidden; g.status = s->status;
+    g.tables_late = 1;                  // weights and row table may come from the kernel right before this one
     if ((flags & SB_COMBINE_NORM) && l.norm_weight) { g.norm_w = l.norm_weight; g.eps_norm = l.eps; }
     if (next) {
         const Layer& nl = s->layers[(size_t)layer + 1];

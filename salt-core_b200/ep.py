@@ -88,16 +88,36 @@ def forward(stack, grouped, d_x, B, d_out, act, stream=0, first=0, count=None, g
 
 
 def dispatch_plan(selected, n_experts: int, world: int):
-    """For a home rank's selections ``selected`` ([B][K] expert ids, torch): the order in which its B*K
+    """For a home rank's selections ``selected`` ([B][K] int32 expert ids, torch): the order in which its B*K
     selections are sent (grouped by destination rank, canonical order inside a group), the number sent to
-    every rank, and the expert id of every sent row."""
+    every rank (int64), the expert id of every sent row and the position of every selection in that order
+    (both int32).  On the GPU this is one launch of the library's counting sort; elsewhere the same thing in
+    tensor operations."""
     import torch
-    flat = selected.reshape(-1).to(torch.int64)
-    bounds = torch.tensor([r * n_experts // world for r in range(1, world)], dtype=torch.int64, device=flat.device)
-    dest = torch.bucketize(flat, bounds, right=True)            # owner of each selection's expert
+    flat = selected.reshape(-1)
+    n = flat.numel()
+    if flat.is_cuda and world <= 8:
+        import ctypes as C
+        from ._lib import load_library
+        flat = flat.to(torch.int32).contiguous()
+        order = torch.empty(n, dtype=torch.int32, device=flat.device)
+        pos, ids = torch.empty_like(order), torch.empty_like(order)
+        counts = torch.empty(world, dtype=torch.int32, device=flat.device)
+        rc = load_library().salt_b200_dispatch_plan(
+            C.c_void_p(flat.data_ptr()), n, n_experts, world, C.c_void_p(order.data_ptr()), C.c_void_p(pos.data_ptr()),
+            C.c_void_p(ids.data_ptr()), C.c_void_p(counts.data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+        if rc != 0:
+            raise RuntimeError("salt_b200_dispatch_plan failed")
+        return order.to(torch.int64), counts.to(torch.int64), ids, pos
+    flat = flat.to(torch.int64)
+    dest = torch.zeros_like(flat)
+    for r in range(1, world):                                   # owner of each selection's expert
+        dest += (flat >= r * n_experts // world).to(torch.int64)
     order = torch.argsort(dest, stable=True)
     counts = torch.bincount(dest, minlength=world)
-    return order, counts, flat[order].to(torch.int32)
+    pos = torch.empty_like(order)
+    pos[order] = torch.arange(n, device=flat.device)
+    return order, counts, flat[order].to(torch.int32), pos.to(torch.int32)
 
 
 class StackOps:
@@ -130,9 +150,10 @@ class StackOps:
             raise RuntimeError("salt_b200_layer_experts_routed failed")
         return out
 
-    def combine(self, layer, canon_rows, w, out, apply_norm, prepare_next):
-        if self.stack.layer_combine_rows(layer, canon_rows.data_ptr(), w.data_ptr(), w.shape[0], out.data_ptr(),
-                                         apply_norm, prepare_next, stream=self._sp()) != 0:
+    def combine(self, layer, rows, pos, w, out, apply_norm, prepare_next):
+        """rows in the order they were sent; pos[t*K+k] = row of selection (t, k)."""
+        if self.stack.layer_combine_rows(layer, rows.data_ptr(), w.data_ptr(), w.shape[0], out.data_ptr(),
+                                         apply_norm, prepare_next, stream=self._sp(), d_row_index=pos.data_ptr()) != 0:
             raise RuntimeError("salt_b200_layer_combine_rows failed")
         return out
 
@@ -151,7 +172,7 @@ def forward_dispatch(ops, x, out, act, first=0, count=None, group=None, norm_las
     for i in range(count):
         layer, last = first + i, i == count - 1
         sel, w = ops.route(layer, cur, i > 0)
-        order, send_counts, ids = dispatch_plan(sel, ops.n_experts, world)
+        order, send_counts, ids, pos = dispatch_plan(sel, ops.n_experts, world)
         recv_counts = torch.empty_like(send_counts)
         dist.all_to_all_single(recv_counts, send_counts, group=group)
         sc, rc = send_counts.tolist(), recv_counts.tolist()          # the one host synchronisation of the layer
@@ -164,10 +185,8 @@ def forward_dispatch(ops, x, out, act, first=0, count=None, group=None, norm_las
         done = ops.experts(layer, recv_rows, recv_ids)
         back = torch.empty_like(rows)
         dist.all_to_all_single(back, done, sc, rc, group=group)
-        canon = torch.empty_like(back)
-        canon.index_copy_(0, order, back)                            # back to canonical (token, rank) order
         dst = out if last else act[i & 1]
-        ops.combine(layer, canon, w, dst, norm_last or not last, not last)
+        ops.combine(layer, back, pos, w, dst, norm_last or not last, not last)   # pos: canonical (token, rank) -> row
         if stats is not None:
             stats["rows_sent"] = stats.get("rows_sent", 0) + int(rows.shape[0])
             stats["rows_received"] = stats.get("rows_received", 0) + n_recv

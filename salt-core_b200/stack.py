@@ -156,10 +156,12 @@ class MoeStack:
         return self.lib.salt_b200_layer_experts_routed(self.handle, layer, C.c_void_p(d_rows), C.c_void_p(d_experts),
                                                        n_rows, C.c_void_p(d_out), tc, C.c_void_p(stream))
 
-    def layer_combine_rows(self, layer, d_rows, d_weights, B, d_y, apply_norm=True, prepare_next=False, stream=0):
+    def layer_combine_rows(self, layer, d_rows, d_weights, B, d_y, apply_norm=True, prepare_next=False, stream=0,
+                           d_row_index=None):
+        """d_row_index (int32 [B*topk], device): where selection (token, rank) sits in d_rows; None = canonical order."""
         flags = (1 if apply_norm else 0) | (2 if prepare_next else 0)
-        return self.lib.salt_b200_layer_combine_rows(self.handle, layer, C.c_void_p(d_rows), C.c_void_p(d_weights), B,
-                                                     C.c_void_p(d_y), flags, C.c_void_p(stream))
+        return self.lib.salt_b200_layer_combine_rows(self.handle, layer, C.c_void_p(d_rows), C.c_void_p(d_row_index),
+                                                     C.c_void_p(d_weights), B, C.c_void_p(d_y), flags, C.c_void_p(stream))
 
     EP_PUSH, EP_PULL = 1, 2
 

@@ -159,10 +159,9 @@ class _OracleOps:
         self.rows_done += rows.shape[0]
         return torch.from_numpy(out)
 
-    def combine(self, layer, canon_rows, w, out, apply_norm, prepare_next):
+    def combine(self, layer, rows, pos, w, out, apply_norm, prepare_next):
         L, B = self.layers[layer], w.shape[0]
-        ident = np.arange(B * L.topk, dtype=np.int32)
-        rc, y = self.orc.weighted_reduce(w.numpy().ravel(), ident, canon_rows.numpy(), B, L.topk)
+        rc, y = self.orc.weighted_reduce(w.numpy().ravel(), pos.numpy().astype(np.int32), rows.numpy(), B, L.topk)
         assert rc == 0
         if apply_norm:
             y = np.stack([self.orc.rmsnorm(y[t], L.norm_weight, L.eps, True)[1] for t in range(B)])
@@ -216,9 +215,10 @@ def test_token_dispatch_and_combine_reproduce_single_process_result(tmp_path):
 def test_dispatch_plan_orders_rows_by_owner():
     ep = importlib.import_module("salt-core_b200.ep")
     sel = torch.tensor([[0, 5, 7], [1, 2, 6], [3, 4, 5]], dtype=torch.int32)
-    order, counts, ids = ep.dispatch_plan(sel, 8, 2)
+    order, counts, ids, pos = ep.dispatch_plan(sel, 8, 2)
     assert counts.tolist() == [4, 5]
     assert order.tolist() == [0, 3, 4, 6, 1, 2, 5, 7, 8]         # canonical order inside each destination
     assert ids.tolist() == [0, 1, 2, 3, 5, 7, 6, 4, 5]
-    order, counts, ids = ep.dispatch_plan(sel, 8, 4)
+    assert pos[order].tolist() == list(range(9))                 # pos is the inverse permutation
+    order, counts, ids, pos = ep.dispatch_plan(sel, 8, 4)
     assert counts.tolist() == [2, 2, 3, 2]

@@ -29,8 +29,8 @@ def _emulated_forward(ep, homes, owners, x_all, per_rank, tensor_core=False):
         plans = []
         for r in range(world):
             sel, w = ops[r].route(layer, cur[r], layer > 0)
-            order, counts, ids = ep.dispatch_plan(sel, E, world)
-            plans.append((sel, w, order, counts.tolist(), ids, cur[r].index_select(0, order // K)))
+            order, counts, ids, pos = ep.dispatch_plan(sel, E, world)
+            plans.append((sel, w, order, counts.tolist(), ids, cur[r].index_select(0, order // K), pos))
         back = [[None] * world for _ in range(world)]
         for d in range(world):
             rows, ids = [], []
@@ -47,11 +47,9 @@ def _emulated_forward(ep, homes, owners, x_all, per_rank, tensor_core=False):
                 off += n
         nxt = []
         for r in range(world):
-            sel, w, order = plans[r][0], plans[r][1], plans[r][2]
-            canon = torch.empty((per_rank * K, H), dtype=torch.float32, device="cuda")
-            canon.index_copy_(0, order, torch.cat(back[r]))
+            w, pos = plans[r][1], plans[r][6]
             out = torch.empty_like(cur[r])
-            ops[r].combine(layer, canon, w, out, True, layer + 1 < L)
+            ops[r].combine(layer, torch.cat(back[r]).contiguous(), pos, w, out, True, layer + 1 < L)
             nxt.append(out)
         cur = nxt
     torch.cuda.synchronize()
@@ -92,6 +90,21 @@ def test_token_dispatch_matches_unsharded_stack(synth, world, per_rank):
     for st in [full] + homes + owners:
         assert st.status() == 0
         st.close()
+
+
+@pytest.mark.parametrize("n,E,world", [(9, 8, 2), (4096 * 8, 128, 8), (1000, 128, 3), (1, 128, 4), (2048 * 8, 128, 2)])
+def test_dispatch_plan_kernel_equals_tensor_statement(n, E, world):
+    import torch
+    ep = importlib.import_module("salt-core_b200.ep")
+    rng = np.random.default_rng(n + world)
+    sel = torch.from_numpy(rng.integers(0, E, size=n).astype(np.int32))
+    order_c, counts_c, ids_c, pos_c = ep.dispatch_plan(sel, E, world)               # tensor operations on the CPU
+    order_g, counts_g, ids_g, pos_g = ep.dispatch_plan(sel.cuda(), E, world)        # the library's kernel
+    torch.cuda.synchronize()
+    assert counts_g.cpu().tolist() == counts_c.tolist() and int(counts_c.sum()) == n
+    assert order_g.cpu().tolist() == order_c.tolist()
+    assert ids_g.cpu().tolist() == ids_c.tolist()
+    assert pos_g.cpu().tolist() == pos_c.tolist()
 
 
 def test_routed_rows_reject_foreign_experts_and_check_arguments(synth):
