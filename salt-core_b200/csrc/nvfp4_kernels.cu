@@ -128,10 +128,34 @@ cudaError_t launch_nvfp4_qdq(const float* x, int rows, int C, const float* ig_ro
     return cudaGetLastError();
 }
 
-// Four E2M1 codes of one half-word as floats.
+// Four E2M1 codes of one half-word as floats, by the hardware conversion (two codes -> f16x2, exact: every E2M1
+// value is an f16).  It decodes the code 8 as -0 where the reference's table has +0 (src/nvfp4.c:19-23): as a
+// WEIGHT that cannot change a result - the product is a zero of either sign, and an accumulator that starts
+// at +0 never becomes -0 (x + (-0) = x, +0 + (-0) = +0) - so the dot-product kernels may use it; the
+// quantise-dequantise kernel, whose decoded values are output, keeps the table form.
 __device__ __forceinline__ void e2m1x4(uint32_t h, f32x2& w01, f32x2& w23) {
-    w01 = pack2(e2m1_decode(h & 15u), e2m1_decode((h >> 4) & 15u));
-    w23 = pack2(e2m1_decode((h >> 8) & 15u), e2m1_decode((h >> 12) & 15u));
+    uint32_t p0, p1;
+    asm("{ .reg .b8 b0, b1;\n\t"
+        "mov.b16 {b0, b1}, %2;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %1, b1; }\n"
+        : "=r"(p0), "=r"(p1)
+        : "h"((unsigned short)h));
+    float f0, f1, f2, f3;
+    asm("{ .reg .b16 l, u;\n\t"
+        "mov.b32 {l, u}, %2;\n\t"
+        "cvt.f32.f16 %0, l;\n\t"
+        "cvt.f32.f16 %1, u; }\n"
+        : "=f"(f0), "=f"(f1)
+        : "r"(p0));
+    asm("{ .reg .b16 l, u;\n\t"
+        "mov.b32 {l, u}, %2;\n\t"
+        "cvt.f32.f16 %0, l;\n\t"
+        "cvt.f32.f16 %1, u; }\n"
+        : "=f"(f2), "=f"(f3)
+        : "r"(p1));
+    w01 = pack2(f0, f1);
+    w23 = pack2(f2, f3);
 }
 
 // Tile kernel: 64 threads, 16 weight rows (lane rows r and r+8), eight lanes per
