@@ -314,7 +314,7 @@ __global__ void __launch_bounds__(GLUE_NV == 4 ? 1024 : 512) glue_rows_kernel(Gl
                 bad |= !finite_f(v[j]) || !finite_f(nw[j]);
             }
         }
-        const float ss = ordered_sum_of_squares(sq, n, bad, s_scan);
+        const float ss = ordered_sum_of_squares<GLUE_NV>(sq, n, bad, s_scan);
         if (tid == 0) {
             s_inv = pow_neg_half(__fadd_rn(__fdiv_rn(ss, (float)n), a.eps_norm));
             if (!finite_f(s_inv)) flag(a.status, SB_ERR_NONFINITE);
@@ -344,7 +344,7 @@ __global__ void __launch_bounds__(GLUE_NV == 4 ? 1024 : 512) glue_rows_kernel(Gl
                 bad |= !finite_f(v[j]) || !finite_f(rs[j]);
             }
         }
-        const float ss = ordered_sum_of_squares(sq, n, bad, s_scan);
+        const float ss = ordered_sum_of_squares<GLUE_NV>(sq, n, bad, s_scan);
         if (tid == 0) {
             s_inv = pow_neg_half(__fadd_rn(__fdiv_rn(ss, (float)n), a.eps_router));
             s_root = __fdiv_rn(1.0f, sqrtf_exact((float)n));
