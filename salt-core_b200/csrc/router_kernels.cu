@@ -675,7 +675,10 @@ template <int EPT, int RPT, int RL>
 struct LogitsBig {
     static constexpr int THREADS = 16 * RL;                  // 16 expert lanes x RL row lanes
     static constexpr int TE = 16 * EPT, TR = RL * RPT, ROWS = TE + TR;
-    static constexpr int SLAB = 128, PITCH = SLAB + 4, STAGES = 3;
+    // the smallest tiles (one chain per lane, chosen when the grid would not fill the SMs otherwise) run one block
+    // per SM: their copy ring is deep enough to cover the L2 latency of a slab that takes a third of a
+    // microsecond to consume; the larger tiles keep three stages so that several blocks share an SM
+    static constexpr int SLAB = 128, PITCH = SLAB + 4, STAGES = (RL == 8 && EPT == 1) ? 6 : 3;
     static constexpr size_t SMEM = (size_t)STAGES * ROWS * PITCH * sizeof(float);
 };
 
@@ -813,7 +816,9 @@ cudaError_t launch_router_logits(const float* W, const float* bias, const float*
     } else if (aligned16 && (H & 3) == 0 && rows >= 1024) {
         return launch_logits_big<2, 2, 16>(W, bias, x, logits, rows, E, H, stream);
     } else if (aligned16 && (H & 3) == 0 && rows >= 256) {
-        return launch_logits_big<2, 1, 8>(W, bias, x, logits, rows, E, H, stream);
+        // two chains per lane while that still gives every SM a block, else one chain per lane and twice the blocks
+        if (((E + 31) / 32) * ((rows + 7) / 8) >= 148) return launch_logits_big<2, 1, 8>(W, bias, x, logits, rows, E, H, stream);
+        return launch_logits_big<1, 1, 8>(W, bias, x, logits, rows, E, H, stream);
     } else if (aligned16 && (H & 3) == 0) {
         const size_t smem = (size_t)LT_STAGES * 16 * LT_PITCH * sizeof(float);
         {
