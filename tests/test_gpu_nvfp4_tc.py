@@ -132,3 +132,32 @@ def test_nvfp4_tensor_core_cfg4_vs_exact_kernels(orc, synth, B):
     assert err <= TOL, err
     assert_bits_equal(_run(st, x, B, layer.hidden, True), y, "run to run")
     st.close()
+
+
+def test_nvfp4_tensor_core_expert_ranges_equal_whole_layer(synth):
+    """Expert-parallel ranges on the tensor-core path: two stacks holding half of the experts each fill one shared
+    grouped buffer; the result has the bits of the unsharded tensor-core layer (a row's accumulation does not
+    depend on which other rows share its tile)."""
+    import torch
+    H, M, E, K, B = 1024, 512, 8, 2, 37
+    layer = synth.make_nvfp4_moe_layer(4700, hidden=H, inter=M, n_experts=E, topk=K)
+    x = synth.make_tokens(4701, B, H)
+    sm = stack_mod()
+    whole = sm.MoeStack(B, H, M, E, K)
+    whole.add_nvfp4_layer(layer)
+    want = _run(whole, x, B, H, True)
+    d_x = torch.from_numpy(x).cuda()
+    shared = torch.zeros(B * K * H, dtype=torch.float32, device="cuda")
+    halves = []
+    for lo, hi in ((0, 4), (4, 8)):
+        h = sm.MoeStack(B, H, M, E, K, expert_begin=lo, expert_end=hi)
+        h.add_nvfp4_layer(layer)
+        assert h.set_grouped_out(shared.data_ptr(), shared.numel() * 4) == 0
+        assert h.layer_experts(0, d_x.data_ptr(), B, tensor_core=True) == 0
+        halves.append(h)
+    d_y = torch.zeros(B, H, dtype=torch.float32, device="cuda")
+    assert halves[0].layer_combine(0, B, d_y.data_ptr(), apply_norm=False) == 0
+    assert all(h.status() == 0 for h in halves)
+    assert_bits_equal(d_y.cpu().numpy(), want, "two expert ranges, tensor-core nvfp4")
+    for h in halves + [whole]:
+        h.close()
