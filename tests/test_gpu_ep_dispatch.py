@@ -107,6 +107,39 @@ def test_dispatch_plan_kernel_equals_tensor_statement(n, E, world):
     assert pos_g.cpu().tolist() == pos_c.tolist()
 
 
+def test_token_dispatch_with_nvfp4_layers(synth):
+    """The same three entry points over NVFP4 layers (exact kernels): 2 ranks, against the unsharded stack."""
+    import torch
+    ep = importlib.import_module("salt-core_b200.ep")
+    sm = stack_mod()
+    H, M, E, K, L, world, per_rank = 512, 256, 8, 2, 2, 2, 4
+    layers = [synth.make_nvfp4_moe_layer(920 + i, hidden=H, inter=M, n_experts=E, topk=K) for i in range(L)]
+    B = world * per_rank
+    x = synth.make_tokens(925, B, H)
+    full = sm.MoeStack(B, H, M, E, K)
+    homes = [sm.MoeStack(per_rank, H, M, E, K, expert_begin=0, expert_end=1) for _ in range(world)]
+    owners = [sm.MoeStack(B, H, M, E, K, expert_begin=r * E // world, expert_end=(r + 1) * E // world)
+              for r in range(world)]
+    for layer in layers:
+        for st in [full] + homes + owners:
+            st.add_nvfp4_layer(layer)
+    d_x = torch.from_numpy(x).cuda()
+    act = [torch.empty_like(d_x), torch.empty_like(d_x)]
+    cur = d_x.data_ptr()
+    for l in range(L):
+        out = act[l & 1]
+        assert full.layer_experts(l, cur, B, router_input_ready=l > 0) == 0
+        assert full.layer_combine(l, B, out.data_ptr(), apply_norm=True, prepare_next=l + 1 < L) == 0
+        cur = out.data_ptr()
+    torch.cuda.synchronize()
+    want = act[(L - 1) & 1].cpu().numpy()
+    got = _emulated_forward(ep, homes, owners, x, per_rank)
+    assert_bits_equal(got, want, "token dispatch, nvfp4 layers")
+    for st in [full] + homes + owners:
+        assert st.status() == 0
+        st.close()
+
+
 def test_routed_rows_reject_foreign_experts_and_check_arguments(synth):
     import torch
     sm = stack_mod()
