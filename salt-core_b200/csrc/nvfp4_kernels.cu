@@ -62,59 +62,63 @@ __device__ __forceinline__ float e2m1_decode(uint32_t code) {
 // function returns -1).
 // src_rows != null: row r of the call reads activation row src_rows[r % src_mod] / src_div (the grouped
 // order of a MoE layer: several quantisations of the same token row with different global scales).
-__global__ void __launch_bounds__(256)
+template <bool WANT_DQ>
+__global__ void __launch_bounds__(512)
 nvfp4_qdq_kernel(const float* __restrict__ x, int rows, int C, const float* __restrict__ ig_rows,
                  uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, float* __restrict__ dequant,
                  int* status, const int* __restrict__ src_rows, int src_mod, int src_div) {
+    // blocks (x, y): row x, 16-element blocks y * blockDim.x + thread; the row's source and scale are found once
     const int bpr = C >> 4;
-    const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (gid >= (long long)rows * bpr) return;
-    const int row = (int)(gid / bpr), blk = (int)(gid - (long long)row * bpr);
+    const int row = blockIdx.x;
     const float ig = ig_rows[row];
+    if (!(ig > 0.0f)) return;         // a row nobody will read (its expert lives on another rank): its source may be unwritten
     const int in_row = src_rows ? src_rows[row % src_mod] / src_div : row;
-    const float4* in4 = (const float4*)(x + (size_t)in_row * C + blk * 16);
-    float v[16];
+    for (int blk = blockIdx.y * blockDim.x + threadIdx.x; blk < bpr; blk += gridDim.y * blockDim.x) {
+        const float4* in4 = (const float4*)(x + (size_t)in_row * C + blk * 16);
+        float v[16];
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const float4 t = in4[i];
-        v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
-    }
-    float amax = 0.0f;
-    bool bad = false;
+        for (int i = 0; i < 4; i++) {
+            const float4 t = in4[i];
+            v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
+        }
+        float amax = 0.0f;
+        bool bad = false;
 #pragma unroll
-    for (int i = 0; i < 16; i++) {
-        const float m = fabsf(v[i]);
-        bad |= !finite_f(m);
-        if (m > amax) amax = m;
-    }
-    if (bad) {
-        flag_status(status, SB_ERR_NONFINITE);
-        return;
-    }
-    float raw = __fmul_rn(ig, __fmul_rn(amax, 0.16666667163372039794921875f));
-    if (raw > 448.0f) raw = 448.0f;
-    const uint32_t sc = e4m3_encode_pos(raw);
-    const float scale = e4m3_decode(sc);
-    const float out_scale = scale == 0.0f ? 0.0f : __fdiv_rn(ig, scale);
-    const float dq_scale = __fdiv_rn(scale, ig);
-    uint32_t lo = 0, hi = 0;
-    float dq[16];
+        for (int i = 0; i < 16; i++) {
+            const float m = fabsf(v[i]);
+            bad |= !finite_f(m);
+            if (m > amax) amax = m;
+        }
+        if (bad) {
+            flag_status(status, SB_ERR_NONFINITE);
+            continue;
+        }
+        float raw = __fmul_rn(ig, __fmul_rn(amax, 0.16666667163372039794921875f));
+        if (raw > 448.0f) raw = 448.0f;
+        const uint32_t sc = e4m3_encode_pos(raw);
+        const float scale = e4m3_decode(sc);
+        const float out_scale = scale == 0.0f ? 0.0f : __fdiv_rn(ig, scale);
+        const float dq_scale = WANT_DQ ? __fdiv_rn(scale, ig) : 0.0f;
+        uint32_t lo = 0, hi = 0;
+        float dq[16];
 #pragma unroll
-    for (int i = 0; i < 16; i++) {
-        float t = __fmul_rn(v[i], out_scale);
-        if (t > 6.0f) t = 6.0f;
-        if (t < -6.0f) t = -6.0f;
-        const uint32_t c = e2m1_encode(t);
-        dq[i] = __fmul_rn(e2m1_decode(c), dq_scale);
-        if (i < 8) lo |= c << (4 * i);
-        else hi |= c << (4 * (i - 8));
-    }
-    scales[(size_t)row * bpr + blk] = (uint8_t)sc;
-    *(uint2*)(packed + (size_t)row * (C >> 1) + blk * 8) = make_uint2(lo, hi);
-    if (dequant == nullptr) return;     // the tensor-core consumer reads codes and scales only
-    float4* out4 = (float4*)(dequant + (size_t)row * C + blk * 16);
+        for (int i = 0; i < 16; i++) {
+            float t = __fmul_rn(v[i], out_scale);
+            if (t > 6.0f) t = 6.0f;
+            if (t < -6.0f) t = -6.0f;
+            const uint32_t c = e2m1_encode(t);
+            if (WANT_DQ) dq[i] = __fmul_rn(e2m1_decode(c), dq_scale);
+            if (i < 8) lo |= c << (4 * i);
+            else hi |= c << (4 * (i - 8));
+        }
+        scales[(size_t)row * bpr + blk] = (uint8_t)sc;
+        *(uint2*)(packed + (size_t)row * (C >> 1) + blk * 8) = make_uint2(lo, hi);
+        if (WANT_DQ) {
+            float4* out4 = (float4*)(dequant + (size_t)row * C + blk * 16);
 #pragma unroll
-    for (int i = 0; i < 4; i++) out4[i] = make_float4(dq[4 * i], dq[4 * i + 1], dq[4 * i + 2], dq[4 * i + 3]);
+            for (int i = 0; i < 4; i++) out4[i] = make_float4(dq[4 * i], dq[4 * i + 1], dq[4 * i + 2], dq[4 * i + 3]);
+        }
+    }
 }
 
 cudaError_t launch_nvfp4_qdq(const float* x, int rows, int C, const float* ig_rows, uint8_t* packed, uint8_t* scales,
@@ -122,9 +126,15 @@ cudaError_t launch_nvfp4_qdq(const float* x, int rows, int C, const float* ig_ro
                              int src_div) {
     if (rows < 1) return cudaSuccess;
     if (src_rows && (src_mod < 1 || src_div < 1)) return cudaErrorInvalidValue;
-    const long long blocks16 = (long long)rows * (C >> 4);
-    nvfp4_qdq_kernel<<<(unsigned)((blocks16 + 255) / 256), 256, 0, stream>>>(x, rows, C, ig_rows, packed, scales,
-                                                                           dequant, status, src_rows, src_mod, src_div);
+    const int bpr = C >> 4;
+    const int threads = bpr >= 512 ? 512 : ((bpr + 31) & ~31);
+    const dim3 grid((unsigned)rows, (unsigned)std::min(65535, (bpr + threads - 1) / threads));
+    if (dequant)
+        nvfp4_qdq_kernel<true><<<grid, threads, 0, stream>>>(x, rows, C, ig_rows, packed, scales, dequant, status, src_rows,
+                                                            src_mod, src_div);
+    else            // the tensor-core consumer reads codes and scales only
+        nvfp4_qdq_kernel<false><<<grid, threads, 0, stream>>>(x, rows, C, ig_rows, packed, scales, dequant, status,
+                                                             src_rows, src_mod, src_div);
     return cudaGetLastError();
 }
 
@@ -383,10 +393,10 @@ nvfp4_plan_expert(int e, const int* __restrict__ group_offsets, int E, int exper
         t.wg = local ? d.wg[2] : 0.0f; t.ig = local ? d.ig[2] : 1.0f; t.y = grouped_out + (size_t)g0 * H;
         tc_dn[e] = t;
     }
-    for (int t = 0; t < cnt; t++) {                   // rows of remote experts are quantised with a neutral scale and unused
-        ig_gu[g0 + t] = local ? d.ig[0] : 1.0f;
-        ig_gu[J + g0 + t] = local ? d.ig[1] : 1.0f;
-        ig_dn[g0 + t] = local ? d.ig[2] : 1.0f;
+    for (int t = 0; t < cnt; t++) {                   // rows of remote experts are marked (scale 0) and skipped by the quantiser
+        ig_gu[g0 + t] = local ? d.ig[0] : 0.0f;
+        ig_gu[J + g0 + t] = local ? d.ig[1] : 0.0f;
+        ig_dn[g0 + t] = local ? d.ig[2] : 0.0f;
     }
 }
 
