@@ -168,12 +168,15 @@ __device__ __forceinline__ void e2m1x4(uint32_t h, f32x2& w01, f32x2& w23) {
     w23 = pack2(f2, f3);
 }
 
-// Tile kernel: 64 threads, 16 weight rows (lane rows r and r+8), eight lanes per
-// row, lane octant u owns accumulators 4u..4u+3 (same mapping as the Q4 kernel).
+// Tile kernel: 16 weight rows per block, eight lanes per row, lane octant u owns accumulators
+// 4u..4u+3 (same mapping as the Q4 kernel).  RPL = rows per lane group: 2 (64 threads, lane rows r and r + 8:
+// one activation load serves two rows - batches) or 1 (128 threads: twice the warps on the same shared
+// memory, which is what a one-token pass, bound by latency, wants).
 // Requires C % 256 == 0 and 16-byte aligned operands.
-template <int TT>
-__global__ void __launch_bounds__(64)
+template <int TT, int RPL>
+__global__ void __launch_bounds__(128 / RPL)
 nvfp4_tile_kernel(const Fp4Job* __restrict__ jobs, int C, const int* __restrict__ live, const int* __restrict__ n_live) {
+    constexpr int NTH = 128 / RPL;
     extern __shared__ __align__(16) uint8_t smem[];
     // with a list of the jobs that have tokens the grid only spans those (a decode step touches 4 of 64 experts)
     if (live != nullptr && (int)blockIdx.y >= *n_live) return;
@@ -197,7 +200,7 @@ nvfp4_tile_kernel(const Fp4Job* __restrict__ jobs, int C, const int* __restrict_
 
     auto issue_x = [&](int tb) {
         const int ppr = C >> 2;
-        for (int p = tid; p < TT * ppr; p += 64) {
+        for (int p = tid; p < TT * ppr; p += NTH) {
             const int tt = p / ppr, pc = p - tt * ppr;
             const int tok = min(tb + tt, jb.ntok - 1);
             cp_async16(sX + tt * C + pc * 4, jb.x + (size_t)tok * jb.x_stride + pc * 4);
@@ -206,7 +209,7 @@ nvfp4_tile_kernel(const Fp4Job* __restrict__ jobs, int C, const int* __restrict_
     issue_x(0);
     {
         const int ppr = sc_row >> 4;
-        for (int p = tid; p < nvalid * ppr; p += 64) {
+        for (int p = tid; p < nvalid * ppr; p += NTH) {
             const int rr = p / ppr, pc = p - rr * ppr;
             cp_async16(sS + rr * sc_stride + pc * 16, jb.scales + (size_t)(r0 + rr) * sc_row + pc * 16);
         }
@@ -214,7 +217,7 @@ nvfp4_tile_kernel(const Fp4Job* __restrict__ jobs, int C, const int* __restrict_
     for (int ch = 0; ch < nch; ch++) {
         const int s_begin = ch * chunk_steps;
         const int cs = min(chunk_steps, steps - s_begin);
-        for (int p = tid; p < 16 * cs; p += 64) {
+        for (int p = tid; p < 16 * cs; p += NTH) {
             const int rr = p / cs, pc = p - rr * cs;
             const int grow = min(r0 + rr, jb.R - 1);
             cp_async16(sW + rr * w_stride + (s_begin + pc) * 16,
@@ -222,13 +225,14 @@ nvfp4_tile_kernel(const Fp4Job* __restrict__ jobs, int C, const int* __restrict_
         }
         cp_async_commit();
     }
-    for (int c = tid; c < 256; c += 64) sTbl[c] = __fmul_rn(e4m3_decode((uint32_t)c), jb.wg);
+    for (int c = tid; c < 256; c += NTH) sTbl[c] = __fmul_rn(e4m3_decode((uint32_t)c), jb.wg);
 
     const uint8_t* wA = sW + pr * w_stride + 2 * u;
-    const uint8_t* wB = sW + (pr + 8) * w_stride + 2 * u;
+    const uint8_t* wB = sW + (RPL == 2 ? pr + 8 : pr) * w_stride + 2 * u;
     const uint8_t* scA = sS + pr * sc_stride + (u >> 2);
-    const uint8_t* scB = sS + (pr + 8) * sc_stride + (u >> 2);
+    const uint8_t* scB = sS + (RPL == 2 ? pr + 8 : pr) * sc_stride + (u >> 2);
     const float* xs = sX + 4 * u;
+    const f32x2 nz = pack2u(c_neg_zero, c_neg_zero);
 
     for (int tb = 0; tb < jb.ntok; tb += TT) {
         if (tb > 0) {
@@ -238,11 +242,12 @@ nvfp4_tile_kernel(const Fp4Job* __restrict__ jobs, int C, const int* __restrict_
             cp_async_wait_dyn(0);
             __syncthreads();
         }
-        float accA[TT][4], accB[TT][4];
+        // accumulators 4u .. 4u + 3 of each row as two packed pairs (add.rn.f32x2 = two independent roundings)
+        f32x2 accA[TT][2], accB[TT][2];
 #pragma unroll
         for (int tt = 0; tt < TT; tt++)
 #pragma unroll
-            for (int j = 0; j < 4; j++) { accA[tt][j] = 0.0f; accB[tt][j] = 0.0f; }
+            for (int j = 0; j < 2; j++) { accA[tt][j] = pack2(0.0f, 0.0f); accB[tt][j] = pack2(0.0f, 0.0f); }
         for (int ch = 0; ch < nch; ch++) {
             if (tb == 0) {
                 cp_async_wait_dyn(nch - 1 - ch);
@@ -252,39 +257,45 @@ nvfp4_tile_kernel(const Fp4Job* __restrict__ jobs, int C, const int* __restrict_
             const int s_end = min(s_begin + chunk_steps, steps);
 #pragma unroll 2
             for (int st = s_begin; st < s_end; st++) {
-                const float sa = sTbl[scA[2 * st]], sb_ = sTbl[scB[2 * st]];
+                const float sa = sTbl[scA[2 * st]];
                 const uint32_t hA = *(const uint16_t*)(wA + st * 16);
-                const uint32_t hB = *(const uint16_t*)(wB + st * 16);
                 f32x2 a01, a23, b01, b23;
                 e2m1x4(hA, a01, a23);
-                e2m1x4(hB, b01, b23);
-                const f32x2 ssa = pack2(sa, sa), ssb = pack2(sb_, sb_);
+                const f32x2 ssa = pack2(sa, sa);
                 a01 = mul2(a01, ssa); a23 = mul2(a23, ssa);
-                b01 = mul2(b01, ssb); b23 = mul2(b23, ssb);
+                if (RPL == 2) {
+                    const float sb_ = sTbl[scB[2 * st]];
+                    const uint32_t hB = *(const uint16_t*)(wB + st * 16);
+                    e2m1x4(hB, b01, b23);
+                    const f32x2 ssb = pack2(sb_, sb_);
+                    b01 = mul2(b01, ssb); b23 = mul2(b23, ssb);
+                }
 #pragma unroll
                 for (int tt = 0; tt < TT; tt++) {
                     const ulonglong2 xv = *(const ulonglong2*)(xs + tt * C + st * 32);
-                    float p0, p1, p2, p3;
-                    unpack2(mul2(a01, xv.x), p0, p1);
-                    unpack2(mul2(a23, xv.y), p2, p3);
-                    accA[tt][0] = __fadd_rn(accA[tt][0], p0); accA[tt][1] = __fadd_rn(accA[tt][1], p1);
-                    accA[tt][2] = __fadd_rn(accA[tt][2], p2); accA[tt][3] = __fadd_rn(accA[tt][3], p3);
-                    unpack2(mul2(b01, xv.x), p0, p1);
-                    unpack2(mul2(b23, xv.y), p2, p3);
-                    accB[tt][0] = __fadd_rn(accB[tt][0], p0); accB[tt][1] = __fadd_rn(accB[tt][1], p1);
-                    accB[tt][2] = __fadd_rn(accB[tt][2], p2); accB[tt][3] = __fadd_rn(accB[tt][3], p3);
+                    // the product as fma(w, x, -0): exactly fl(w * x), and an add that the assembler cannot
+                    // contract with it into one fused multiply-add (it would with a plain mul.f32x2)
+                    accA[tt][0] = add2(accA[tt][0], fma2(a01, xv.x, nz));
+                    accA[tt][1] = add2(accA[tt][1], fma2(a23, xv.y, nz));
+                    if (RPL == 2) {
+                        accB[tt][0] = add2(accB[tt][0], fma2(b01, xv.x, nz));
+                        accB[tt][1] = add2(accB[tt][1], fma2(b23, xv.y, nz));
+                    }
                 }
             }
         }
 #pragma unroll
         for (int tt = 0; tt < TT; tt++) {
-            const float y0 = fold_row_octants(accA[tt], u);
-            const float y1 = fold_row_octants(accB[tt], u);
+            float fa[4], fb[4];
+            unpack2(accA[tt][0], fa[0], fa[1]); unpack2(accA[tt][1], fa[2], fa[3]);
+            unpack2(accB[tt][0], fb[0], fb[1]); unpack2(accB[tt][1], fb[2], fb[3]);
+            const float y0 = fold_row_octants(fa, u);
+            const float y1 = RPL == 2 ? fold_row_octants(fb, u) : 0.0f;
             const int tok = tb + tt;
             if (u == 7 && tok < jb.ntok) {
                 float* yrow = jb.y + (size_t)tok * jb.y_stride;
                 if (pr < nvalid) yrow[r0 + pr] = y0;
-                if (pr + 8 < nvalid) yrow[r0 + pr + 8] = y1;
+                if (RPL == 2 && pr + 8 < nvalid) yrow[r0 + pr + 8] = y1;
             }
         }
     }
@@ -432,11 +443,12 @@ template <int TT>
 static cudaError_t launch_fp4_tile(const Fp4Job* jobs, int njobs, int max_rows, int C, cudaStream_t stream,
                                    const int* live, const int* n_live) {
     {
-        cudaError_t e = ensure_dynamic_smem((const void*)nvfp4_tile_kernel<TT>, (size_t)(200 * 1024));
+        cudaError_t e = ensure_dynamic_smem((const void*)nvfp4_tile_kernel<TT, (TT == 1 ? 1 : 2)>, (size_t)(200 * 1024));
         if (e != cudaSuccess) return e;
     }
     dim3 grid((max_rows + 15) / 16, njobs);
-    nvfp4_tile_kernel<TT><<<grid, 64, fp4_smem(C, TT), stream>>>(jobs, C, live, n_live);
+    constexpr int RPL = TT == 1 ? 1 : 2;
+    nvfp4_tile_kernel<TT, RPL><<<grid, 128 / RPL, fp4_smem(C, TT), stream>>>(jobs, C, live, n_live);
     return cudaGetLastError();
 }
 
