@@ -575,14 +575,14 @@ def run_b200(args):
                 kname = ("q4_gemm_tc_kernel<fused> (tcgen05 gate/up + GeGLU)" if tc_mode
                          else "q4_tile16_kernel<2,TT> / q4_fused_expert_kernel (gate/up + GeGLU)")
                 if fmt == "nvfp4":
-                    # the class brackets the whole NVFP4 expert phase of a layer (six launches)
+                    # the class brackets the whole NVFP4 expert phase of a layer (five launches)
                     alg = mean_distinct * 3 * TENSOR_BYTES + B * H * 4 + B * K * (2 * H + 4 * M) * 4
                     kname = ("NVFP4 expert phase of a layer: plan, activation quantise-dequantise, nvfp4_tile_kernel "
-                             "gate + up, GeGLU, quantise-dequantise, nvfp4_tile_kernel down (six launches)")
+                             "gate + up, GeGLU + quantise-dequantise, nvfp4_tile_kernel down (five launches)")
                     if tc_mode:
                         kname = ("NVFP4 expert phase of a layer: plan, activation quantise, nvfp4_gemm_tc_kernel "
-                                 "(tcgen05.mma.kind::mxf4nvf4 block-scaled) gate + up, GeGLU, quantise, "
-                                 "nvfp4_gemm_tc_kernel down (six launches)")
+                                 "(tcgen05.mma.kind::mxf4nvf4 block-scaled) gate + up, GeGLU + quantise, "
+                                 "nvfp4_gemm_tc_kernel down (five launches)")
             us_launch = gu["us_per_launch"]
             if one_launch and use_graph:
                 # the timed region itself: L launches of this kernel and one small reduce per step (the event

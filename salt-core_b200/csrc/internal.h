@@ -136,9 +136,10 @@ struct Fp4Job {
 };
 // ig_rows[row] = input global scale of the row's tensor; src_rows (optional): row r reads activation row
 // src_rows[r % src_mod] / src_div
+// geglu_up (optional, without src_rows): quantise gelu_tanh(x[i]) * geglu_up[i] instead of x[i]
 cudaError_t launch_nvfp4_qdq(const float* x, int rows, int C, const float* ig_rows, uint8_t* packed, uint8_t* scales,
                              float* dequant, int* status, cudaStream_t stream, const int* src_rows = nullptr,
-                             int src_mod = 1, int src_div = 1);
+                             int src_mod = 1, int src_div = 1, const float* geglu_up = nullptr);
 // An NVFP4 expert: gate, up, down codes / block scales, 1 / weight divisor and input global scale of each.
 struct Fp4ExpertDesc {
     const uint8_t* codes[3];
@@ -171,7 +172,6 @@ cudaError_t make_fp4_weight_map(CUtensorMap* out, const void* base, int C, int r
 cudaError_t make_fp4_act_maps(CUtensorMap* out3, const void* base, int C, int rows);
 cudaError_t launch_nvfp4_gemm_tc(const Fp4TcJob* jobs, int njobs, int R, int C, const Fp4TcMaps& maps, int* status,
                                  cudaStream_t stream);
-cudaError_t launch_geglu_rows(const float* gate, const float* up, float* chain, size_t n, cudaStream_t stream);
 // live / n_live (optional, device): indices of the jobs that have tokens and their number; njobs is then the
 // largest number of such jobs the call can have, and the grid spans only that many
 cudaError_t launch_nvfp4_jobs(const Fp4Job* jobs, int njobs, int max_rows, int max_tok, int C, bool aligned,

@@ -479,12 +479,11 @@ static int experts_run(Stack* s, const Layer& l, const float* d_x, int B, int K,
             !cuda_ok(launch_nvfp4_qdq(d_x, 2 * jobs, H, s->fp4_ig_gu, s->fp4_packed, s->fp4_scales, nullptr,
                                       s->status, st, s->g2c, jobs, K), "nvfp4 qdq x") ||
             !cuda_ok(launch_nvfp4_gemm_tc(s->fp4_tc_gu, 2 * E, M, H, mg, s->status, st), "nvfp4 tc gate/up") ||
-            !cuda_ok(launch_geglu_rows(s->fp4_gate, s->fp4_up, s->chain, (size_t)jobs * M, st), "geglu") ||
-            !cuda_ok(launch_nvfp4_qdq(s->chain, jobs, M, s->fp4_ig_dn, s->fp4_packed, s->fp4_scales, nullptr,
-                                      s->status, st), "nvfp4 qdq chain") ||
+            !cuda_ok(launch_nvfp4_qdq(s->fp4_gate, jobs, M, s->fp4_ig_dn, s->fp4_packed, s->fp4_scales, nullptr,
+                                      s->status, st, nullptr, 1, 1, s->fp4_up), "nvfp4 geglu + qdq") ||
             !cuda_ok(launch_nvfp4_gemm_tc(s->fp4_tc_dn, E, H, M, md, s->status, st), "nvfp4 tc down"))
             return -1;
-        count_launches(7);
+        count_launches(6);
         return 0;
     }
     if (l.nvfp4) {
@@ -500,13 +499,12 @@ static int experts_run(Stack* s, const Layer& l, const float* d_x, int B, int K,
                                       s->status, st, s->g2c, jobs, K), "nvfp4 qdq x") ||
             !cuda_ok(launch_nvfp4_jobs(s->fp4_gu_jobs, 2 * live_max, M, B, H, true, st, s->fp4_live + 2, s->fp4_live,
                                        typical), "nvfp4 gate/up") ||
-            !cuda_ok(launch_geglu_rows(s->fp4_gate, s->fp4_up, s->chain, (size_t)jobs * M, st), "geglu") ||
-            !cuda_ok(launch_nvfp4_qdq(s->chain, jobs, M, s->fp4_ig_dn, s->fp4_packed, s->fp4_scales, s->fp4_dq_dn,
-                                      s->status, st), "nvfp4 qdq chain") ||
+            !cuda_ok(launch_nvfp4_qdq(s->fp4_gate, jobs, M, s->fp4_ig_dn, s->fp4_packed, s->fp4_scales, s->fp4_dq_dn,
+                                      s->status, st, nullptr, 1, 1, s->fp4_up), "nvfp4 geglu + qdq") ||
             !cuda_ok(launch_nvfp4_jobs(s->fp4_dn_jobs, live_max, H, B, M, true, st, s->fp4_live + 2 + 2 * E,
                                        s->fp4_live + 1, typical), "nvfp4 down"))
             return -1;
-        count_launches(7);
+        count_launches(6);
         return 0;
     }
     if (fused) {

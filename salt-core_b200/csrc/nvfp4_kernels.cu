@@ -62,11 +62,13 @@ __device__ __forceinline__ float e2m1_decode(uint32_t code) {
 // function returns -1).
 // src_rows != null: row r of the call reads activation row src_rows[r % src_mod] / src_div (the grouped
 // order of a MoE layer: several quantisations of the same token row with different global scales).
-template <bool WANT_DQ>
+// GEGLU: the activations are formed on the fly as gelu_tanh(x[i]) * up[i] (reference gemma4.c:80-83 and the
+// product of gemma4_text.c:8927-8930) - the quantiser of a layer's second projection batch needs no GeGLU buffer.
+template <bool WANT_DQ, bool GEGLU>
 __global__ void __launch_bounds__(512)
-nvfp4_qdq_kernel(const float* __restrict__ x, int rows, int C, const float* __restrict__ ig_rows,
-                 uint8_t* __restrict__ packed, uint8_t* __restrict__ scales, float* __restrict__ dequant,
-                 int* status, const int* __restrict__ src_rows, int src_mod, int src_div) {
+nvfp4_qdq_kernel(const float* __restrict__ x, const float* __restrict__ up, int rows, int C,
+                 const float* __restrict__ ig_rows, uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
+                 float* __restrict__ dequant, int* status, const int* __restrict__ src_rows, int src_mod, int src_div) {
     // blocks (x, y): row x, 16-element blocks y * blockDim.x + thread; the row's source and scale are found once
     const int bpr = C >> 4;
     const int row = blockIdx.x;
@@ -80,6 +82,17 @@ nvfp4_qdq_kernel(const float* __restrict__ x, int rows, int C, const float* __re
         for (int i = 0; i < 4; i++) {
             const float4 t = in4[i];
             v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
+        }
+        if (GEGLU) {
+            const float4* up4 = (const float4*)(up + (size_t)in_row * C + blk * 16);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float4 t = up4[i];
+                v[4 * i] = __fmul_rn(gelu_tanh_exact(v[4 * i]), t.x);
+                v[4 * i + 1] = __fmul_rn(gelu_tanh_exact(v[4 * i + 1]), t.y);
+                v[4 * i + 2] = __fmul_rn(gelu_tanh_exact(v[4 * i + 2]), t.z);
+                v[4 * i + 3] = __fmul_rn(gelu_tanh_exact(v[4 * i + 3]), t.w);
+            }
         }
         float amax = 0.0f;
         bool bad = false;
@@ -123,18 +136,21 @@ nvfp4_qdq_kernel(const float* __restrict__ x, int rows, int C, const float* __re
 
 cudaError_t launch_nvfp4_qdq(const float* x, int rows, int C, const float* ig_rows, uint8_t* packed, uint8_t* scales,
                              float* dequant, int* status, cudaStream_t stream, const int* src_rows, int src_mod,
-                             int src_div) {
+                             int src_div, const float* geglu_up) {
     if (rows < 1) return cudaSuccess;
-    if (src_rows && (src_mod < 1 || src_div < 1)) return cudaErrorInvalidValue;
+    if (src_rows && (src_mod < 1 || src_div < 1 || geglu_up)) return cudaErrorInvalidValue;
     const int bpr = C >> 4;
     const int threads = bpr >= 512 ? 512 : ((bpr + 31) & ~31);
     const dim3 grid((unsigned)rows, (unsigned)std::min(65535, (bpr + threads - 1) / threads));
-    if (dequant)
-        nvfp4_qdq_kernel<true><<<grid, threads, 0, stream>>>(x, rows, C, ig_rows, packed, scales, dequant, status, src_rows,
-                                                            src_mod, src_div);
-    else            // the tensor-core consumer reads codes and scales only
-        nvfp4_qdq_kernel<false><<<grid, threads, 0, stream>>>(x, rows, C, ig_rows, packed, scales, dequant, status,
-                                                             src_rows, src_mod, src_div);
+#define SB_QDQ(DQ, GG) \
+    nvfp4_qdq_kernel<DQ, GG><<<grid, threads, 0, stream>>>(x, geglu_up, rows, C, ig_rows, packed, scales, dequant, status, \
+                                                          src_rows, src_mod, src_div)
+    if (dequant) {
+        if (geglu_up) SB_QDQ(true, true); else SB_QDQ(true, false);
+    } else {            // the tensor-core consumer reads codes and scales only
+        if (geglu_up) SB_QDQ(false, true); else SB_QDQ(false, false);
+    }
+#undef SB_QDQ
     return cudaGetLastError();
 }
 
@@ -411,13 +427,6 @@ nvfp4_plan_expert(int e, const int* __restrict__ group_offsets, int E, int exper
     }
 }
 
-// chain = gelu_tanh(gate) * up (reference gemma4.c:80-83 and the product of gemma4_text.c:8927-8930)
-__global__ void __launch_bounds__(256)
-geglu_rows_kernel(const float* __restrict__ gate, const float* __restrict__ up, float* __restrict__ chain, size_t n) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) chain[i] = __fmul_rn(gelu_tanh_exact(gate[i]), up[i]);
-}
-
 cudaError_t launch_nvfp4_moe_plan(const int* group_offsets, int E, int expert_begin, int expert_end, int J,
                                   const Fp4ExpertDesc* experts, int H, int M, const float* dq_gu, float* gate_out,
                                   float* up_out, const float* dq_dn, float* grouped_out, Fp4Job* gu_jobs, Fp4Job* dn_jobs,
@@ -426,12 +435,6 @@ cudaError_t launch_nvfp4_moe_plan(const int* group_offsets, int E, int expert_be
     nvfp4_moe_plan_kernel<<<1, 128, 0, stream>>>(group_offsets, E, expert_begin, expert_end, J, experts, H, M, dq_gu,
                                                  gate_out, up_out, dq_dn, grouped_out, gu_jobs, dn_jobs, ig_gu, ig_dn, tc_gu,
                                                  tc_dn, live);
-    return cudaGetLastError();
-}
-
-cudaError_t launch_geglu_rows(const float* gate, const float* up, float* chain, size_t n, cudaStream_t stream) {
-    if (n == 0) return cudaSuccess;
-    geglu_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(gate, up, chain, n);
     return cudaGetLastError();
 }
 
