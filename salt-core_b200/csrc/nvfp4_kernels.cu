@@ -13,6 +13,7 @@
 #include <algorithm>
 
 #include "internal.h"
+#include "pdl.cuh"
 #include "q4_core.cuh"
 
 namespace sb {
@@ -70,6 +71,8 @@ nvfp4_qdq_kernel(const float* __restrict__ x, const float* __restrict__ up, int 
                  const float* __restrict__ ig_rows, uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
                  float* __restrict__ dequant, int* status, const int* __restrict__ src_rows, int src_mod, int src_div) {
     // blocks (x, y): row x, 16-element blocks y * blockDim.x + thread; the row's source and scale are found once
+    pdl_wait();                    // scales, row table and activations come from the kernels before this one
+    pdl_launch_dependents();
     const int bpr = C >> 4;
     const int row = blockIdx.x;
     const float ig = ig_rows[row];
@@ -143,15 +146,11 @@ cudaError_t launch_nvfp4_qdq(const float* x, int rows, int C, const float* ig_ro
     const int threads = bpr >= 512 ? 512 : ((bpr + 31) & ~31);
     const dim3 grid((unsigned)rows, (unsigned)std::min(65535, (bpr + threads - 1) / threads));
 #define SB_QDQ(DQ, GG) \
-    nvfp4_qdq_kernel<DQ, GG><<<grid, threads, 0, stream>>>(x, geglu_up, rows, C, ig_rows, packed, scales, dequant, status, \
-                                                          src_rows, src_mod, src_div)
-    if (dequant) {
-        if (geglu_up) SB_QDQ(true, true); else SB_QDQ(true, false);
-    } else {            // the tensor-core consumer reads codes and scales only
-        if (geglu_up) SB_QDQ(false, true); else SB_QDQ(false, false);
-    }
+    launch_pdl(nvfp4_qdq_kernel<DQ, GG>, grid, dim3(threads), 0, stream, x, geglu_up, rows, C, ig_rows, packed, scales, \
+               dequant, status, src_rows, src_mod, src_div)
+    if (dequant) return geglu_up ? SB_QDQ(true, true) : SB_QDQ(true, false);
+    return geglu_up ? SB_QDQ(false, true) : SB_QDQ(false, false);     // the tensor-core consumer reads codes and scales only
 #undef SB_QDQ
-    return cudaGetLastError();
 }
 
 // Four E2M1 codes of one half-word as floats, by the hardware conversion (two codes -> f16x2, exact: every E2M1
@@ -194,6 +193,8 @@ __global__ void __launch_bounds__(128 / RPL)
 nvfp4_tile_kernel(const Fp4Job* __restrict__ jobs, int C, const int* __restrict__ live, const int* __restrict__ n_live) {
     constexpr int NTH = 128 / RPL;
     extern __shared__ __align__(16) uint8_t smem[];
+    pdl_wait();                    // jobs, live list and activations come from the kernels before this one
+    pdl_launch_dependents();
     // with a list of the jobs that have tokens the grid only spans those (a decode step touches 4 of 64 experts)
     if (live != nullptr && (int)blockIdx.y >= *n_live) return;
     const Fp4Job jb = jobs[live != nullptr ? live[blockIdx.y] : blockIdx.y];
@@ -364,6 +365,8 @@ nvfp4_moe_plan_kernel(const int* __restrict__ group_offsets, int E, int expert_b
     // into gu_jobs, [2 + 2E, 2 + 3E) into dn_jobs) so the projection launches span only those
     __shared__ int n_gu, n_dn;
     if (threadIdx.x == 0) n_gu = n_dn = 0;
+    pdl_wait();                    // the group offsets come from the plan kernel before this one
+    pdl_launch_dependents();
     __syncthreads();
     for (int e = threadIdx.x; e < E; e += blockDim.x)
         nvfp4_plan_expert(e, group_offsets, E, expert_begin, expert_end, J, experts, H, M, dq_gu, gate_out, up_out, dq_dn,
@@ -432,10 +435,9 @@ cudaError_t launch_nvfp4_moe_plan(const int* group_offsets, int E, int expert_be
                                   float* up_out, const float* dq_dn, float* grouped_out, Fp4Job* gu_jobs, Fp4Job* dn_jobs,
                                   float* ig_gu, float* ig_dn, cudaStream_t stream, Fp4TcJob* tc_gu, Fp4TcJob* tc_dn,
                                   int* live) {
-    nvfp4_moe_plan_kernel<<<1, 128, 0, stream>>>(group_offsets, E, expert_begin, expert_end, J, experts, H, M, dq_gu,
-                                                 gate_out, up_out, dq_dn, grouped_out, gu_jobs, dn_jobs, ig_gu, ig_dn, tc_gu,
-                                                 tc_dn, live);
-    return cudaGetLastError();
+    return launch_pdl(nvfp4_moe_plan_kernel, dim3(1), dim3(128), 0, stream, group_offsets, E, expert_begin, expert_end, J,
+                      experts, H, M, dq_gu, gate_out, up_out, dq_dn, grouped_out, gu_jobs, dn_jobs, ig_gu, ig_dn, tc_gu,
+                      tc_dn, live);
 }
 
 static size_t fp4_smem(int C, int tt) {
@@ -451,8 +453,7 @@ static cudaError_t launch_fp4_tile(const Fp4Job* jobs, int njobs, int max_rows, 
     }
     dim3 grid((max_rows + 15) / 16, njobs);
     constexpr int RPL = TT == 1 ? 1 : 2;
-    nvfp4_tile_kernel<TT, RPL><<<grid, 128 / RPL, fp4_smem(C, TT), stream>>>(jobs, C, live, n_live);
-    return cudaGetLastError();
+    return launch_pdl(nvfp4_tile_kernel<TT, RPL>, grid, dim3(128 / RPL), fp4_smem(C, TT), stream, jobs, C, live, n_live);
 }
 
 cudaError_t launch_nvfp4_jobs(const Fp4Job* jobs, int njobs, int max_rows, int max_tok, int C, bool aligned,
