@@ -446,6 +446,21 @@ def test_stack_two_layers_prefill_sized_batch_vs_oracle(orc, synth):
     st.close()
 
 
+def test_stack_two_layers_prefill_sized_batch_hidden_5120_vs_oracle(orc, synth):
+    """The same at hidden = 5120 (160 columns per lane in the warp-per-row glue, the hidden size of the NVFP4
+    configuration) with small experts so that the CPU side stays cheap: 260 rows, top-2 of 8."""
+    B, H, M, E, K = 260, 5120, 64, 8, 2
+    layers = [synth.make_q4_moe_layer(195 + i, hidden=H, inter=M, n_experts=E, topk=K) for i in range(2)]
+    x = synth.make_tokens(197, B, H)
+    st = stack_mod().MoeStack(B, H, M, E, K)
+    for layer in layers:
+        st.add_layer(layer)
+    y = st.forward_host(x)
+    want, _ = oracle_stack(orc, layers, x, threads=16)
+    assert_bits_equal(y, want, "2-layer stack, 260 rows, hidden 5120")
+    st.close()
+
+
 def test_stack_wide_hidden_takes_any_shape_kernels_vs_oracle(orc, synth):
     """hidden = 5696 is beyond what the tiled projection kernels hold in shared memory: the stack runs the
     any-shape kernels, one grid row per token of a group.  Groups of more than four tokens must all be
