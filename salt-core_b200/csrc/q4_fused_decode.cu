@@ -517,13 +517,15 @@ constexpr int LAYER_NV = 5;                 // columns per thread of the row-wis
 constexpr int LAYER_SLOTS = 40;
 
 struct LayerScratch {                        // offsets in floats from the start of shared memory
-    int sq, rin, wrow, logits, topk, scan, end;
+    int sq, rin, wrow, logits, pes, lit, topk, scan, end;
 };
 static __host__ __device__ __forceinline__ LayerScratch layer_scratch(int H, int E, int topk) {
     LayerScratch L;
     const int h4 = (H + 3) & ~3;
     L.sq = 0; L.rin = h4; L.wrow = 2 * h4; L.logits = 3 * h4;
-    L.topk = L.logits + ((E + 3) & ~3);
+    L.pes = L.logits + ((E + 3) & ~3);           // the layer's per-expert scales ...
+    L.lit = L.pes + ((E + 3) & ~3);              // ... and literal-dequantisation flags, fetched before the grid dependency
+    L.topk = L.lit + ((E + 3) & ~3);
     L.scan = L.topk + topk_scratch_floats(E, topk);
     L.end = L.scan + POSSUM_SCRATCH;
     return L;
@@ -551,6 +553,8 @@ __device__ __forceinline__ void layer_decode_body(const LayerDecodeArgs& a, uint
     float* const rin = fsm + L.rin;               // router input
     float* const wrow = fsm + L.wrow;             // router weights of this block's expert
     float* const s_logits = fsm + L.logits;
+    float* const s_pes = fsm + L.pes;
+    int* const s_lit = (int*)(fsm + L.lit);
     float* const tk = fsm + L.topk;
     uint32_t* const scan = (uint32_t*)(fsm + L.scan);
     __shared__ float s_inv, s_root, s_w[64], s_wts[64];
@@ -576,6 +580,11 @@ __device__ __forceinline__ void layer_decode_body(const LayerDecodeArgs& a, uint
         nw[j] = (a.norm_w != nullptr && d < H) ? __ldg(a.norm_w + d) : 1.0f;
         rs[j] = d < H ? __ldg(a.router_scale + d) : 1.0f;
         v[j] = 0.0f;
+    }
+    // layer constants the top-k and the job list need: in shared memory long before they are used
+    for (int e = tid; e < E; e += NT) {
+        s_pes[e] = a.per_expert_scale != nullptr ? __ldg(a.per_expert_scale + e) : 1.0f;
+        s_lit[e] = (e >= a.expert_begin && e < a.expert_end) ? __ldg(a.lit_flags + (e - a.expert_begin)) : 0;
     }
     if (!STACKED) {
         pdl_wait();                // the previous layer's outputs
@@ -750,14 +759,20 @@ __device__ __forceinline__ void layer_decode_body(const LayerDecodeArgs& a, uint
     __syncthreads();
     for (int e = tid; e < E; e += NT) s_logits[e] = __ldcg(a.logits + e);
     __syncthreads();
-    topk_group(tid < 128, s_logits, a.per_expert_scale, s_sel, s_wts, E, K, 1, cta == 0 ? a.f.status : nullptr, tk,
+    topk_group(tid < 128, s_logits, s_pes, s_sel, s_wts, E, K, 1, cta == 0 ? a.f.status : nullptr, tk,
                tk + topk_scratch_floats(E, K) - 4, tid & 127, 128);
     __syncthreads();
-    if (tid == 0) {
-        int n = 0;
-        for (int j = 0; j < K; j++) {
-            const int e = s_sel[j];
-            if (e < a.expert_begin || e >= a.expert_end || n >= FUSED_MAX_JOBS) continue;
+    // job list: thread j takes selection j (its slot = the local selections before it; the list keeps rank order)
+    if (tid < K) {
+        const int j = tid, e = s_sel[j];
+        int slot = 0, total = 0;
+        for (int i = 0; i < K; i++) {
+            const int ei = s_sel[i];
+            const int local = (ei >= a.expert_begin && ei < a.expert_end) ? 1 : 0;
+            total += local;
+            if (i < j) slot += local;
+        }
+        if (e >= a.expert_begin && e < a.expert_end && slot < FUSED_MAX_JOBS) {
             const uint8_t* base = a.pool + (size_t)(e - a.expert_begin) * a.expert_stride;
             FusedJob fj;
             const uint8_t* tb = a.tables + (size_t)(e - a.expert_begin) * 6 * a.group_bytes;
@@ -765,12 +780,12 @@ __device__ __forceinline__ void layer_decode_body(const LayerDecodeArgs& a, uint
                 fj.v[k] = base + (size_t)k * a.tensor_bytes;
                 fj.t[k] = (const uint32_t*)(tb + (size_t)k * 2 * a.group_bytes);
             }
-            fj.lit = a.lit_flags[e - a.expert_begin]; fj.pad = 0;
+            fj.lit = s_lit[e]; fj.pad = 0;
             for (int t = 0; t < FUSED_MAX_TOKENS; t++) fj.x_row[t] = 0;
             fj.g0 = j; fj.ntok = 1;              // one token: grouped order = rank order (experts ascending)
-            S.sJ[n++] = fj;
+            S.sJ[slot] = fj;
         }
-        s_njobs = n;
+        if (j == 0) s_njobs = min(total, FUSED_MAX_JOBS);
     }
     if (cta == 0) {                 // what the next layer's reduce and the caller read
         if (tid < K) {
