@@ -34,6 +34,8 @@ struct Layer {
     int* lit_flags = nullptr;       // [local] bit k: tensor k of the expert has a scale that needs the two-rounding form
     size_t expert_stride = 0;
     float eps = 0.0f;
+    bool q4_tc_ok = false;          // tiled maps of the tensor-core path over pool and sb_tables
+    TcWeightMaps q4_tc;
     // NVFP4 experts (W4A4: E2M1 codes + E4M3 block scales; reference src/nvfp4.c) instead of affine-Q4 ones
     bool nvfp4 = false;
     Fp4ExpertDesc* fp4_experts = nullptr;      // [local experts] device
@@ -207,7 +209,7 @@ int salt_b200_stack_create(int max_tokens, int hidden, int inter, int n_experts,
         free_stack(s);
         return -1;
     }
-    s->tc_ready = make_tc_maps(&s->x_maps, s->xh, s->xl, (int)J, hidden) == cudaSuccess &&
+    s->tc_ready = q4_tc_supported(hidden, inter) && make_tc_maps(&s->x_maps, s->xh, s->xl, (int)J, hidden) == cudaSuccess &&
                   make_tc_maps(&s->chain_maps, s->chain_h, s->chain_l, (int)J, inter) == cudaSuccess;
     *stack_out = s;
     return 0;
@@ -248,6 +250,8 @@ int salt_b200_stack_add_q4_layer(void* stack, const SaltB200Q4LayerSpec* spec) {
         cudaFree(l.norm_weight); cudaFree(l.sb_tables); cudaFree(l.lit_flags);
         return -1;
     }
+    l.q4_tc_ok = s->tc_ready && make_q4_tc_weight_maps(&l.q4_tc, l.pool, l.expert_stride, (const uint32_t*)l.sb_tables,
+                                                        s->hidden, s->inter, (int)local) == cudaSuccess;
     s->layers.push_back(l);
     return (int)s->layers.size() - 1;
 }
@@ -523,7 +527,7 @@ static int experts_run(Stack* s, const Layer& l, const float* d_x, int B, int K,
     const int tok_hint = B;
     if (flags & (SB_EXPERTS_TENSOR_CORE | SB_EXPERTS_TENSOR_CORE_SINGLE)) {
         const bool split = (flags & SB_EXPERTS_TENSOR_CORE) != 0;
-        if (!s->tc_ready) {
+        if (!s->tc_ready || !l.q4_tc_ok) {
             fprintf(stderr, "salt_b200: tensor-core path unavailable for this geometry\n");
             return -1;
         }
@@ -534,13 +538,13 @@ static int experts_run(Stack* s, const Layer& l, const float* d_x, int B, int K,
         }
         {
             Timed t(s, KC_GATE_UP, st);
-            if (!cuda_ok(launch_q4_gemm_tc(true, split, s->gateup_jobs, njobs_max, s->counters, s->x_maps, s->chain,
+            if (!cuda_ok(launch_q4_gemm_tc(true, split, s->gateup_jobs, njobs_max, s->counters, s->x_maps, l.q4_tc, s->chain,
                                            M, s->chain_h, s->chain_l, nullptr, M, jobs, s->status, st), "tc gate/up"))
                 return -1;
         }
         {
             Timed t(s, KC_DOWN, st);
-            if (!cuda_ok(launch_q4_gemm_tc(false, split, s->down_jobs, njobs_max, s->counters, s->chain_maps,
+            if (!cuda_ok(launch_q4_gemm_tc(false, split, s->down_jobs, njobs_max, s->counters, s->chain_maps, l.q4_tc,
                                            s->grouped_out, H, nullptr, nullptr, s->grouped_out, H, jobs, s->status, st), "tc down"))
                 return -1;
         }

@@ -44,14 +44,6 @@ constexpr int FT_MAX_TILES = 48;                  // tiles of one block's list
 constexpr uint32_t FT_TMEM_COLS = 512;            // accumulators at 0..63 and 64..127, scale stages from 128
 constexpr uint32_t FT_SF_BASE = 128, FT_SF_STAGE = 32, FT_SFB_OFF = 16;
 
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::
-            "r"(dst),
-        "l"((uint64_t)map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
-        : "memory");
-}
-
 // kind::mxf4nvf4 instruction descriptor: A = B = E2M1 (format 1), both K-major, scales unsigned E4M3
 // (format 0), scale ids 0 (a K = 64 MMA with 16-element blocks uses all four bytes of a scale column), K = 64.
 __device__ __forceinline__ uint32_t umma_idesc_fp4(int M, int N) {

@@ -43,30 +43,14 @@ namespace sb {
 
 constexpr int TC_STAGES = 3;
 constexpr int TC_CONVERTERS = 256;
-constexpr int TC_THREADS = TC_CONVERTERS + 32;
+constexpr int TC_THREADS = TC_CONVERTERS + 64;   // + issuer warp + producer warp
 constexpr int TC_KC = 64;                    // K columns per chunk
 constexpr int TC_A_BYTES = 128 * TC_KC * 2;  // one matrix' 128 x 64 fp16 tile
+constexpr int TC_PK_BYTES = 128 * TC_KC / 2; // its packed form
+constexpr int TC_TAB_BYTES = 128 * 16;       // scale | bias words of 128 rows x 4 chunks
 constexpr int TC_MAX_NT = 128;
-constexpr int TC_MAX_BSLOTS = 8;
+constexpr int TC_MAX_SLOTS = 8;
 constexpr int TC_SMEM_BYTES = 225 * 1024;    // dynamic shared memory of every launch (one block per SM)
-
-// Ring loads as volatile asm: an ordinary read-only load is an invariant load to the
-// compiler, which is then free to sink it down to its first use, chunks later, and the
-// prefetch distance is lost.  Volatile asm statements keep their program order.
-__device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
-}
-// 16-bit load straight into a 32-bit register (zero-extended by the load itself): a
-// separate widening instruction would wait for the data right behind the load.
-__device__ __forceinline__ uint32_t ld_stream_u16(const void* p) {
-    uint32_t v;
-    asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(v) : "l"(p));
-    return v;
-}
 
 // kind::f16 instruction descriptor: D = F32, A = B = F16, both K-major.
 __device__ __forceinline__ uint32_t umma_idesc_f16(int M, int N) {
@@ -190,16 +174,61 @@ struct TcArgs {
     __half* out_l;             // its fp16 residual (split precision) or null
     float* out_f;              // plain: projection output [grouped rows][R] fp32
     int* status;
+    const uint8_t* pool;       // the layer's expert slots (first local expert) and their stride
+    size_t expert_stride;
+    const uint32_t* tables;    // (scale << 16) | bias words, [local expert][3 tensors][R * C/64]
+    int tensor0;               // first tensor of the slot this launch reads (0: gate, then up; 2: down)
+    int tab_tma;               // table rows are a multiple of 16 bytes: blocks of 4 groups come by tiled TMA
 };
+
+// Bounded wait for two barriers at once: both polls are in flight together, so the pair costs one
+// barrier round trip instead of two.
+__device__ __forceinline__ bool mbar_wait2(uint64_t* bar_a, uint32_t par_a, uint64_t* bar_b, uint32_t par_b,
+                                           volatile int* fail) {
+    const uint32_t aa = smem_u32(bar_a), ab = smem_u32(bar_b);
+    uint32_t done_a = 0, done_b = 0;
+    for (uint32_t i = 0; i < TC_SPIN_LIMIT; i++) {
+        uint32_t ra = 1, rb = 1;
+        if (!done_a)
+            asm volatile(
+                "{\n\t.reg .pred p;\n\t"
+                "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                "selp.u32 %0, 1, 0, p;\n\t}\n"
+                : "=r"(ra)
+                : "r"(aa), "r"(par_a)
+                : "memory");
+        if (!done_b)
+            asm volatile(
+                "{\n\t.reg .pred p;\n\t"
+                "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                "selp.u32 %0, 1, 0, p;\n\t}\n"
+                : "=r"(rb)
+                : "r"(ab), "r"(par_b)
+                : "memory");
+        done_a |= ra;
+        done_b |= rb;
+        if (done_a && done_b) return true;
+        if ((i & 255u) == 255u && *fail) return false;
+    }
+    *fail = 1;
+    return false;
+}
+
+__device__ __forceinline__ uint4 lds_v4(const uint8_t* p) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(smem_u32(p)));
+    return v;
+}
 
 template <bool FUSED, bool SPLIT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps) {
+q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __grid_constant__ TcWeightMaps wm) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bar_free[TC_STAGES];   // stage's MMAs complete (tcgen05.commit)
-    __shared__ __align__(8) uint64_t bar_full[TC_STAGES];   // stage converted (8 warp arrivals)
-    __shared__ __align__(8) uint64_t bar_b[TC_MAX_BSLOTS];  // B tile landed (TMA transaction bytes)
-    __shared__ __align__(8) uint64_t bar_done;              // a token pass' accumulators are final
+    __shared__ __align__(8) uint64_t bar_in[TC_MAX_SLOTS];    // input slot landed (TMA transaction bytes)
+    __shared__ __align__(8) uint64_t bar_done[TC_MAX_SLOTS];  // the chunk's MMAs are complete (tcgen05.commit)
+    __shared__ __align__(8) uint64_t bar_full[TC_STAGES];     // stage converted (8 warp arrivals)
+    __shared__ __align__(8) uint64_t bar_acc;                 // a token pass' accumulators are final
+    __shared__ __align__(8) uint64_t bar_tab;                 // the tile's whole scale table landed (untiled form)
     __shared__ uint32_t s_tmem;
     __shared__ int s_fail;
 
@@ -221,30 +250,43 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int C = jb.C, nchunks = C / TC_KC;
     const int g0 = (int)((jb.y - a.y_base) / a.y_cols) + pass_shift;   // first grouped row of this block's tokens
+    const int expert = (int)((size_t)(jb.vals - a.pool) / a.expert_stride);   // local expert = slice of the weight maps
     constexpr int NMAT = FUSED ? 2 : 1;
     constexpr int NPART = SPLIT ? 2 : 1;                     // hi (+ lo) copies of every operand tile
     constexpr int STAGES = (FUSED && SPLIT) ? 2 : TC_STAGES;
     constexpr int STAGE_BYTES = NMAT * NPART * TC_A_BYTES;   // A tiles of a stage: [matrix][hi, lo]
-    // 1024-byte aligned carve-up: A stages, then the ring of B tiles (tokens' activations)
-    uint8_t* stage_base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    uint8_t* bring = stage_base + STAGES * STAGE_BYTES;
+    const bool tab_tma = a.tab_tma != 0;
     // B tile rows = smallest TMA box (16, 32, 64, 128 token rows) that holds a pass
     const int ntok_cap = min(jb.ntok, TC_MAX_NT);
     const int variant = ntok_cap <= 16 ? 0 : ntok_cap <= 32 ? 1 : ntok_cap <= 64 ? 2 : 3;
     const uint32_t part_bytes = (16u << variant) * 128u;
-    const uint32_t slot_bytes = NPART * part_bytes;
-    const uint32_t NB = (uint32_t)min(TC_MAX_BSLOTS, (int)((TC_SMEM_BYTES - 1024 - STAGES * STAGE_BYTES) / slot_bytes));
+    // 1024-byte aligned carve-up: A stages | whole-tile table (untiled form) | ring of input slots, each
+    // [packed weights, NMAT x 4 KB][table block, NMAT x 2 KB (tiled form)][activation tile(s)]
+    uint8_t* stage_base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    const uint32_t tabm_bytes = tab_tma ? 0u : (uint32_t)(128 * nchunks * 4);
+    const uint32_t tabw_bytes = (NMAT * tabm_bytes + 1023u) & ~1023u;
+    uint8_t* tabw = stage_base + STAGES * STAGE_BYTES;
+    uint8_t* in_base = tabw + tabw_bytes;
+    const uint32_t b_off = NMAT * (TC_PK_BYTES + (tab_tma ? TC_TAB_BYTES : 0));
+    const uint32_t slot_bytes = b_off + NPART * part_bytes;
+    const int avail = TC_SMEM_BYTES - 1024 - STAGES * STAGE_BYTES - (int)tabw_bytes;
+    const uint32_t NQ = (uint32_t)min(TC_MAX_SLOTS, avail / (int)slot_bytes);
+    if ((int)NQ < STAGES) {                                   // the host checks the geometry; never expected
+        if (tid == 0 && a.status) atomicOr(a.status, SB_ERR_INDEX);
+        return;
+    }
     const int npass = (jb.ntok + TC_MAX_NT - 1) / TC_MAX_NT;
     const uint32_t total = (uint32_t)npass * (uint32_t)nchunks;
     volatile int* fail = &s_fail;
 
     if (tid == 0) {
-        for (int s = 0; s < STAGES; s++) {
-            mbar_init(&bar_free[s], 1);
-            mbar_init(&bar_full[s], TC_CONVERTERS / 32);
+        for (int s = 0; s < TC_MAX_SLOTS; s++) {
+            mbar_init(&bar_in[s], 1);
+            mbar_init(&bar_done[s], 1);
         }
-        for (int s = 0; s < TC_MAX_BSLOTS; s++) mbar_init(&bar_b[s], 1);
-        mbar_init(&bar_done, 1);
+        for (int s = 0; s < TC_STAGES; s++) mbar_init(&bar_full[s], TC_CONVERTERS / 32);
+        mbar_init(&bar_acc, 1);
+        mbar_init(&bar_tab, 1);
         s_fail = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -259,93 +301,65 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = s_tmem;
 
-    // ---- converter set-up: one 32-element half of a 64-column chunk of one row, in every matrix.
-    // Eight consecutive lanes take eight consecutive rows; the swizzle sends their 16-byte
-    // stores to eight different bank groups.
-    constexpr int DEPTH = 4;                                  // chunks of packed weights in flight per thread
-    const int crow = ((tid & 7) | ((tid >> 4) << 3)) & 127, chalf = (tid >> 3) & 1;
-    const int grow = min(r0 + crow, jb.R - 1);
-    const uint8_t* cvals[NMAT];
-    const uint16_t* csc[NMAT];
-    const uint16_t* cbi[NMAT];
-#pragma unroll
-    for (int m = 0; m < NMAT; m++) {
-        cvals[m] = (m == 0 ? jb.vals : jb.vals2) + (size_t)grow * (C >> 1) + chalf * 16;
-        csc[m] = (const uint16_t*)(m == 0 ? jb.scales : jb.scales2) + (size_t)grow * nchunks;
-        const uint8_t* braw = (m == 0 ? jb.biases : jb.biases2);
-        cbi[m] = braw ? (const uint16_t*)braw + (size_t)grow * nchunks : nullptr;
-    }
-    const uint32_t a_off = (uint32_t)crow * 128;            // the row's 128-byte line in a 128 x 64 fp16 tile
-    const uint32_t a_c0 = (uint32_t)chalf * 4, a_sw = (uint32_t)crow & 7;
-    const NibbleMagic mg = load_nibble_magic();
+    uint32_t it = 0;          // running chunk counter across token passes (every role counts the same chunks)
+    uint32_t p_issued = 0;    // producer: chunks requested
+    uint32_t i_committed = 0; // issuer: chunks committed
 
-    // ---- issuer set-up
-    uint32_t b_issued = 0;                                    // B tiles requested so far
-    const uint32_t a_lo0 = DESC_B_LO | ((smem_u32(stage_base) & 0x3ffffu) >> 4);
-    const uint32_t b_lo0 = DESC_B_LO | ((smem_u32(bring) & 0x3ffffu) >> 4);
-    // request the B tile of chunk kq of token pass `pass` into ring slot `slot`
-    auto issue_b_at = [&](uint32_t slot, int kq, int pass) {
-        const uint32_t dst = smem_u32(bring + slot * slot_bytes);
-        mbar_expect_tx(&bar_b[slot], slot_bytes);
-        tma_load_2d(dst, &maps.hi[variant], kq * TC_KC, g0 + pass * TC_MAX_NT, &bar_b[slot]);
-        if (SPLIT) tma_load_2d(dst + part_bytes, &maps.lo[variant], kq * TC_KC, g0 + pass * TC_MAX_NT, &bar_b[slot]);
-    };
-    uint32_t b_slot = 0;                                      // next B request: ring slot, chunk, pass
-    int b_kq = 0, b_pass = 0;
-    uint32_t iss_s = 0, iss_ph = 0, iss_slot = 0, iss_bph = 0;   // issuer: stage / slot and their phase parities
-    if (warp == 8) {
-        if (lane == 0)
-            for (; b_issued < total && b_issued < NB; b_issued++) {
-                issue_b_at(b_slot, b_kq, b_pass);
-                if (++b_slot == NB) b_slot = 0;
-                if (++b_kq == nchunks) { b_kq = 0; b_pass++; }
-            }
-        __syncwarp();
-    }
-
-    uint32_t it = 0;          // running chunk counter across token passes (stage / parity bookkeeping)
-    for (int pass = 0; pass < npass; pass++) {
-        const int tb = pass * TC_MAX_NT;
-        const int nt_real = min(TC_MAX_NT, jb.ntok - tb);
-        const int NT = (nt_real + 15) & ~15;
-
-        if (warp < 8) {
-            // ================= converters =================
-            uint4 ring[DEPTH][NMAT];
-            uint32_t rsc[DEPTH][NMAT], rbi[DEPTH][NMAT];   // raw loads only: no arithmetic until consumed
+    if (warp < 8) {
+        // ================= converters (and the epilogue of every pass on warps 0-3) =================
+        // One 32-element half of a 64-column chunk of one row, in every matrix.  Eight consecutive lanes
+        // take eight consecutive rows; the swizzle sends their 16-byte stores to eight different bank groups.
+        const int crow = ((tid & 7) | ((tid >> 4) << 3)) & 127, chalf = (tid >> 3) & 1;
+        const uint32_t a_off = (uint32_t)crow * 128;            // the row's 128-byte line in a 128 x 64 fp16 tile
+        const uint32_t a_c0 = (uint32_t)chalf * 4, a_sw = (uint32_t)crow & 7;
+        const NibbleMagic mg = load_nibble_magic();
+        uint32_t cs = 0, cs_ph = 0;      // A stage and its parity
+        uint32_t cq = 0, cq_ph = 0;      // input slot and its parity
+        uint32_t dq = 0, dq_ph = 0;      // slot whose commit frees the A stage (chunk it - STAGES)
+        bool tab_ready = tab_tma;
+        for (int pass = 0; pass < npass && !*fail; pass++) {
+            const int tb = pass * TC_MAX_NT;
+            const int nt_real = min(TC_MAX_NT, jb.ntok - tb);
+            const int NT = (nt_real + 15) & ~15;
+            for (int kc0 = 0; kc0 < nchunks; kc0 += 4) {
+                uint32_t tw[NMAT][4];       // table words of this thread's row for four chunks
 #pragma unroll
-            for (int d = 0; d < DEPTH; d++)
-#pragma unroll
-                for (int m = 0; m < NMAT; m++) {
-                    const int kq = min(d, nchunks - 1);
-                    ring[d][m] = ld_stream_v4(cvals[m] + kq * 32);
-                    rsc[d][m] = ld_stream_u16(csc[m] + kq);
-                    rbi[d][m] = cbi[m] ? ld_stream_u16(cbi[m] + kq) : 0u;
-                }
-            for (int kc0 = 0; kc0 < nchunks; kc0 += DEPTH) {
-#pragma unroll
-                for (int d = 0; d < DEPTH; d++) {
+                for (int d = 0; d < 4; d++) {
                     const int kc = kc0 + d;
                     if (kc >= nchunks) break;
-                    const uint32_t s = it % STAGES;
-                    uint8_t* st = stage_base + s * STAGE_BYTES;
-                    // the MMAs that last read this stage must have completed
-                    const bool ok = it < (uint32_t)STAGES || mbar_wait(&bar_free[s], ((it / STAGES) - 1) & 1, fail);
-                    // take this chunk's packed data out of the ring and refill the slot DEPTH chunks ahead
-                    uint4 cur[NMAT];
-                    uint32_t cur_s[NMAT], cur_b[NMAT];
+                    uint8_t* st = stage_base + cs * STAGE_BYTES;
+                    const uint8_t* slot = in_base + cq * slot_bytes;
+                    // the chunk's packed weights have landed, and the MMAs that last read this stage are complete
+                    bool ok = it < (uint32_t)STAGES ? mbar_wait(&bar_in[cq], cq_ph, fail)
+                                                    : mbar_wait2(&bar_in[cq], cq_ph, &bar_done[dq], dq_ph, fail);
+                    if (ok && !tab_ready) { ok = mbar_wait(&bar_tab, 0, fail); tab_ready = true; }
+                    if (!ok) { kc0 = nchunks; break; }   // the failure flag is up: every role leaves its loop
+                    {
+                        if (d == 0) {
+                            if (tab_tma) {
 #pragma unroll
-                    for (int m = 0; m < NMAT; m++) {
-                        cur[m] = ring[d][m];
-                        cur_s[m] = rsc[d][m];
-                        cur_b[m] = rbi[d][m];
-                        if (kc + DEPTH < nchunks) {
-                            ring[d][m] = ld_stream_v4(cvals[m] + (kc + DEPTH) * 32);
-                            rsc[d][m] = ld_stream_u16(csc[m] + kc + DEPTH);
-                            if (cbi[m]) rbi[d][m] = ld_stream_u16(cbi[m] + kc + DEPTH);
+                                for (int m = 0; m < NMAT; m++) {
+                                    const uint4 t = lds_v4(slot + NMAT * TC_PK_BYTES + m * TC_TAB_BYTES + crow * 16);
+                                    tw[m][0] = t.x; tw[m][1] = t.y; tw[m][2] = t.z; tw[m][3] = t.w;
+                                }
+                            } else {
+#pragma unroll
+                                for (int m = 0; m < NMAT; m++)
+#pragma unroll
+                                    for (int dd = 0; dd < 4; dd++)
+                                        tw[m][dd] = kc0 + dd < nchunks
+                                                        ? *(const uint32_t*)(tabw + m * tabm_bytes + (size_t)(crow * nchunks + kc0 + dd) * 4)
+                                                        : 0u;
+                            }
                         }
-                    }
-                    if (ok) {
+                        uint4 cur[NMAT];
+                        uint32_t cur_s[NMAT], cur_b[NMAT];
+#pragma unroll
+                        for (int m = 0; m < NMAT; m++) {
+                            cur[m] = lds_v4(slot + m * TC_PK_BYTES + crow * 32 + chalf * 16);
+                            cur_s[m] = tw[m][d] >> 16;
+                            cur_b[m] = tw[m][d] & 0xffffu;
+                        }
                         // one decision for all matrices of the chunk: the conversions of gate and up then sit
                         // in one basic block and interleave
                         bool half_math = !SPLIT;
@@ -366,35 +380,74 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps) {
                         }
                     }
                     // generic-proxy writes -> visible to the tensor core (async proxy), then one
-                    // arrival per warp (always, so the issuer never waits for a converter that gave up)
+                    // arrival per warp
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&bar_full[s]);
+                    if (lane == 0) mbar_arrive(&bar_full[cs]);
+                    if (it >= (uint32_t)STAGES && ++dq == NQ) { dq = 0; dq_ph ^= 1u; }
+                    if (++cs == (uint32_t)STAGES) { cs = 0; cs_ph ^= 1u; }
+                    if (++cq == NQ) { cq = 0; cq_ph ^= 1u; }
                     it++;
                 }
             }
-        } else {
-            // ================= issuer warp =================
-            // All ring positions and phase parities are carried incrementally (iss_*): the loop
-            // is one thread's dependent instruction stream, so every division removed shortens
-            // the per-chunk critical path.
-            const uint32_t idesc = umma_idesc_f16(128, NT);
-            for (int kc = 0; kc < nchunks; kc++, it++) {
-                bool ok = true;
-                // stage free again => so is the B slot of chunk it - STAGES: refill it
-                if (it >= (uint32_t)STAGES) ok = mbar_wait(&bar_free[iss_s], iss_ph ^ 1u, fail);
-                if (ok && lane == 0 && it >= (uint32_t)STAGES && b_issued < total) {
-                    issue_b_at(b_slot, b_kq, b_pass);
-                    b_issued++;
-                    if (++b_slot == NB) b_slot = 0;
-                    if (++b_kq == nchunks) { b_kq = 0; b_pass++; }
+            // ---- epilogue of this token pass (warps 0-3): the next pass' first MMA needs these warps'
+            // arrival on its stage, which follows the accumulator reads in program order
+            if (warp < 4 && mbar_wait(&bar_acc, pass & 1, fail)) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const int m = r0 + warp * 32 + lane;
+                const int mpos = (m & ~7) | tc_kpos(m & 7);      // GeGLU output feeds the next GEMM's K
+                const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
+                for (int n0 = 0; n0 < NT; n0 += 32) {
+                    uint32_t g[32];
+                    tmem_ld32(trow + n0, g);
+                    if (FUSED) {
+                        uint32_t u[32];
+                        tmem_ld32(trow + 128 + n0, u);
+#pragma unroll
+                        for (int i = 0; i < 32; i++) {
+                            const int n = n0 + i;
+                            if (n < nt_real && m < jb.R) {
+                                const float gv = __uint_as_float(g[i]), uv = __uint_as_float(u[i]);
+                                const float inner = 0.7978845608028654f * (gv + 0.044715f * gv * gv * gv);
+                                const float act = 0.5f * gv * (1.0f + tanhf(inner));
+                                const float o = act * uv;
+                                const __half oh = __float2half_rn(o);
+                                a.out_h[(size_t)(g0 + tb + n) * jb.R + mpos] = oh;
+                                if (SPLIT)
+                                    a.out_l[(size_t)(g0 + tb + n) * jb.R + mpos] = __float2half_rn(o - __half2float(oh));
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i++) {
+                            const int n = n0 + i;
+                            if (n < nt_real && m < jb.R) a.out_f[(size_t)(g0 + tb + n) * jb.R + m] = __uint_as_float(g[i]);
+                        }
+                    }
                 }
-                if (ok) ok = mbar_wait(&bar_full[iss_s], iss_ph, fail);
-                if (ok) ok = mbar_wait(&bar_b[iss_slot], iss_bph, fail);
-                if (ok && lane == 0) {
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            }
+        }
+    } else if (warp == 8) {
+        // ================= issuer warp =================
+        // All ring positions and phase parities are carried incrementally: the loop is one thread's
+        // dependent instruction stream, and every barrier operation in it costs a round trip.
+        const uint32_t a_lo0 = DESC_B_LO | ((smem_u32(stage_base) & 0x3ffffu) >> 4);
+        const uint32_t b_lo0 = DESC_B_LO | ((smem_u32(in_base + b_off) & 0x3ffffu) >> 4);
+        uint32_t is = 0, is_ph = 0, iq = 0, iq_ph = 0;
+        for (int pass = 0; pass < npass && !*fail; pass++) {
+            const int nt_real = min(TC_MAX_NT, jb.ntok - pass * TC_MAX_NT);
+            const uint32_t idesc = umma_idesc_f16(128, (nt_real + 15) & ~15);
+            for (int kc = 0; kc < nchunks; kc++) {
+                // the converted weights of the stage and the activation tile of the slot (the converters
+                // waited for the same slot; the tensor core reads it through the async proxy, so the
+                // issuing thread observes the barrier itself)
+                const bool ok = mbar_wait2(&bar_full[is], is_ph, &bar_in[iq], iq_ph, fail);
+                if (!ok) break;
+                if (lane == 0) {
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t alo = a_lo0 + iss_s * (STAGE_BYTES >> 4);
-                    const uint32_t blo = b_lo0 + iss_slot * (slot_bytes >> 4);
+                    const uint32_t alo = a_lo0 + is * (STAGE_BYTES >> 4);
+                    const uint32_t blo = b_lo0 + iq * (slot_bytes >> 4);
                     const uint32_t blo_l = blo + (part_bytes >> 4);
 #pragma unroll
                     for (int j = 0; j < TC_KC / 16; j++) {
@@ -412,68 +465,70 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps) {
                             }
                         }
                     }
-                    umma_commit(&bar_free[iss_s]);
-                    if (kc == nchunks - 1) umma_commit(&bar_done);
+                    umma_commit(&bar_done[iq]);
+                    if (kc == nchunks - 1) umma_commit(&bar_acc);
                 }
-                if (++iss_s == (uint32_t)STAGES) { iss_s = 0; iss_ph ^= 1u; }
-                if (++iss_slot == NB) { iss_slot = 0; iss_bph ^= 1u; }
+                i_committed++;
+                if (++is == (uint32_t)STAGES) { is = 0; is_ph ^= 1u; }
+                if (++iq == NQ) { iq = 0; iq_ph ^= 1u; }
                 __syncwarp();
             }
         }
-
-        // ================= epilogue of this token pass (warps 0-3) =================
-        if (warp < 4 && mbar_wait(&bar_done, pass & 1, fail)) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int m = r0 + warp * 32 + lane;
-            const int mpos = (m & ~7) | tc_kpos(m & 7);      // GeGLU output feeds the next GEMM's K
-            const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
-            for (int n0 = 0; n0 < NT; n0 += 32) {
-                uint32_t g[32];
-                tmem_ld32(trow + n0, g);
-                if (FUSED) {
-                    uint32_t u[32];
-                    tmem_ld32(trow + 128 + n0, u);
+    } else if (lane == 0) {
+        // ================= producer (one thread) =================
+        // Packed weights (tiled TMA over the expert pool: bytes x rows x experts), the table block of four
+        // chunks (tiled form) and the tokens' fp16 activations (128-byte swizzle) of every chunk, NQ chunks ahead.
+        if (!tab_tma) {
+            const int rows_here = min(128, jb.R - r0);
+            const uint32_t bytes = (uint32_t)(rows_here * nchunks * 4);
+            mbar_expect_tx(&bar_tab, NMAT * bytes);
 #pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        const int n = n0 + i;
-                        if (n < nt_real && m < jb.R) {
-                            const float gv = __uint_as_float(g[i]), uv = __uint_as_float(u[i]);
-                            const float inner = 0.7978845608028654f * (gv + 0.044715f * gv * gv * gv);
-                            const float act = 0.5f * gv * (1.0f + tanhf(inner));
-                            const float o = act * uv;
-                            const __half oh = __float2half_rn(o);
-                            a.out_h[(size_t)(g0 + tb + n) * jb.R + mpos] = oh;
-                            if (SPLIT)
-                                a.out_l[(size_t)(g0 + tb + n) * jb.R + mpos] = __float2half_rn(o - __half2float(oh));
-                        }
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        const int n = n0 + i;
-                        if (n < nt_real && m < jb.R) a.out_f[(size_t)(g0 + tb + n) * jb.R + m] = __uint_as_float(g[i]);
-                    }
-                }
+            for (int m = 0; m < NMAT; m++) {
+                const uint32_t* src = a.tables + ((size_t)(expert * 3 + a.tensor0 + m) * jb.R + r0) * nchunks;
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 smem_u32(tabw + m * tabm_bytes)),
+                             "l"(src), "r"(bytes), "r"(smem_u32(&bar_tab))
+                             : "memory");
             }
         }
-        // all accumulator reads of this pass precede the next pass' first MMA
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (*fail) break;
+        uint32_t pq = 0, pq_ph = 0;
+        for (int pass = 0; pass < npass && !*fail; pass++) {
+            for (int kc = 0; kc < nchunks; kc++) {
+                // the slot's previous chunk has been consumed: its MMAs (which followed its conversion) are complete
+                if (p_issued >= NQ && !mbar_wait(&bar_done[pq], pq_ph ^ 1u, fail)) break;
+                const uint32_t dst = smem_u32(in_base + pq * slot_bytes);
+                const bool with_tab = tab_tma && (kc & 3) == 0;
+                mbar_expect_tx(&bar_in[pq], NMAT * (TC_PK_BYTES + (with_tab ? TC_TAB_BYTES : 0)) + NPART * part_bytes);
+#pragma unroll
+                for (int m = 0; m < NMAT; m++) {
+                    tma_load_3d(dst + m * TC_PK_BYTES, &wm.w[FUSED ? m : 2], kc * 32, r0, expert, &bar_in[pq]);
+                    if (with_tab)
+                        tma_load_3d(dst + NMAT * TC_PK_BYTES + m * TC_TAB_BYTES, &wm.t[FUSED ? m : 2], kc * 4, r0, expert,
+                                    &bar_in[pq]);
+                }
+                tma_load_2d(dst + b_off, &maps.hi[variant], kc * TC_KC, g0 + pass * TC_MAX_NT, &bar_in[pq]);
+                if (SPLIT)
+                    tma_load_2d(dst + b_off + part_bytes, &maps.lo[variant], kc * TC_KC, g0 + pass * TC_MAX_NT, &bar_in[pq]);
+                p_issued++;
+                if (++pq == NQ) { pq = 0; pq_ph ^= 1u; }
+            }
+        }
     }
     if (*fail) {
-        if (tid == 0 && a.status) atomicOr(a.status, SB_ERR_TIMEOUT);
-        // wait (bounded, no early exit) for MMAs and TMA copies still in flight before releasing
-        // TMEM and shared memory
-        if (tid == TC_CONVERTERS) {
-            int none = 0;
-            if (it > 0) (void)mbar_wait(&bar_free[(it - 1) % STAGES], ((it - 1) / STAGES) & 1, &none);
-            for (uint32_t t = (b_issued > NB ? b_issued - NB : 0); t < b_issued; t++)
-                (void)mbar_wait(&bar_b[t % NB], (t / NB) & 1, &none);
+        // wait (bounded, no early exit) for the copies and MMAs still in flight before shared memory and
+        // TMEM are released
+        int none = 0;
+        if (warp == 9 && lane == 0) {
+            if (!tab_tma) (void)mbar_wait(&bar_tab, 0, &none);
+            for (uint32_t t = (p_issued > NQ ? p_issued - NQ : 0); t < p_issued; t++)
+                (void)mbar_wait(&bar_in[t % NQ], (t / NQ) & 1, &none);
         }
-        __syncthreads();
+        if (warp == 8 && lane == 0 && i_committed > 0)
+            (void)mbar_wait(&bar_done[(i_committed - 1) % NQ], ((i_committed - 1) / NQ) & 1, &none);
     }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (tid == 0 && *fail && a.status) atomicOr(a.status, SB_ERR_TIMEOUT);
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
     }
@@ -550,39 +605,110 @@ cudaError_t make_tc_maps(TcMaps* out, const void* hi, const void* lo, int rows, 
     return cudaSuccess;
 }
 
+// Tiled maps over a layer's expert pool, one per tensor of a slot (gate, up, down): packed nibbles as
+// [C/2 bytes][R rows][experts] in boxes of one chunk (32 bytes) x 128 rows, and - where a table row is a multiple
+// of 16 bytes (C a multiple of 256) - the (scale << 16) | bias words as [C/16 bytes][R rows][experts] in boxes of
+// four chunks (16 bytes) x 128 rows.  Rows past R read as zero.
+cudaError_t make_q4_tc_weight_maps(TcWeightMaps* out, const uint8_t* pool, size_t expert_stride, const uint32_t* tables,
+                                   int hidden, int inter, int experts) {
+    TensorMapEncodeFn encode = nullptr;
+    {
+        cudaError_t e = tensor_map_encoder(&encode);
+        if (e != cudaSuccess) return e;
+    }
+    if ((hidden % TC_KC) != 0 || (inter % TC_KC) != 0 || experts < 1 || (expert_stride % 16) != 0 ||
+        ((uintptr_t)pool % 16) != 0 || ((uintptr_t)tables % 16) != 0)
+        return cudaErrorInvalidValue;
+    const size_t elems = (size_t)hidden * inter;
+    const size_t tensor_bytes = elems / 2 + 2 * (elems / 64 * 2);
+    if ((tensor_bytes % 16) != 0) return cudaErrorInvalidValue;
+    for (int k = 0; k < 3; k++) {
+        const int R = k < 2 ? inter : hidden, C = k < 2 ? hidden : inter;
+        {
+            cuuint64_t dims[3] = {(cuuint64_t)(C / 2), (cuuint64_t)R, (cuuint64_t)experts};
+            cuuint64_t strides[2] = {(cuuint64_t)(C / 2), (cuuint64_t)expert_stride};
+            cuuint32_t box[3] = {(cuuint32_t)(TC_KC / 2), 128u, 1u};
+            cuuint32_t estr[3] = {1, 1, 1};
+            if ((C / 2) % 16) return cudaErrorInvalidValue;
+            CUresult r = encode(&out->w[k], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
+                                const_cast<uint8_t*>(pool + (size_t)k * tensor_bytes), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+        }
+        out->tab_tma[k] = (C % 256) == 0 ? 1 : 0;
+        if (out->tab_tma[k]) {
+            cuuint64_t dims[3] = {(cuuint64_t)(C / 16), (cuuint64_t)R, (cuuint64_t)experts};
+            cuuint64_t strides[2] = {(cuuint64_t)(C / 16), (cuuint64_t)(3 * (elems / 64) * 4)};
+            cuuint32_t box[3] = {16u, 128u, 1u};
+            cuuint32_t estr[3] = {1, 1, 1};
+            CUresult r = encode(&out->t[k], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
+                                const_cast<uint32_t*>(tables + (size_t)k * (elems / 64)), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+        } else {
+            out->t[k] = out->w[k];   // never read
+        }
+    }
+    out->pool = pool;
+    out->expert_stride = expert_stride;
+    out->tables = tables;
+    return cudaSuccess;
+}
+
+// Does the kernel's shared-memory carve-up hold at least as many input slots as stages for a tensor with C
+// columns, in the widest token tile?  (The untiled table form keeps 128 rows x C/64 words per matrix resident.)
+static bool tc_geometry_ok(int C, bool fused, bool split) {
+    const int nmat = fused ? 2 : 1, npart = split ? 2 : 1;
+    const int stages = (fused && split) ? 2 : TC_STAGES;
+    const bool tab_tma = (C % 256) == 0;
+    const int tabw = tab_tma ? 0 : ((nmat * 128 * (C / TC_KC) * 4 + 1023) & ~1023);
+    const int slot = nmat * (TC_PK_BYTES + (tab_tma ? TC_TAB_BYTES : 0)) + npart * TC_MAX_NT * 128;
+    const int avail = TC_SMEM_BYTES - 1024 - stages * nmat * npart * TC_A_BYTES - tabw;
+    return avail / slot >= stages;
+}
+
+bool q4_tc_supported(int hidden, int inter) {
+    if (hidden < TC_KC || inter < TC_KC || (hidden % TC_KC) || (inter % TC_KC)) return false;
+    return tc_geometry_ok(hidden, true, false) && tc_geometry_ok(hidden, true, true) &&
+           tc_geometry_ok(inter, false, false) && tc_geometry_ok(inter, false, true);
+}
+
 template <bool FUSED, bool SPLIT>
-static cudaError_t launch_tc(const TcArgs& a, const TcMaps& maps, dim3 grid, cudaStream_t stream) {
+static cudaError_t launch_tc(const TcArgs& a, const TcMaps& maps, const TcWeightMaps& wm, dim3 grid,
+                             cudaStream_t stream) {
     // the full dynamic shared memory keeps one block per SM, so a block's 256 TMEM columns
     // can always be allocated without waiting for a neighbour
     {
         cudaError_t e = ensure_dynamic_smem((const void*)q4_gemm_tc_kernel<FUSED, SPLIT>, (size_t)TC_SMEM_BYTES);
         if (e != cudaSuccess) return e;
     }
-    q4_gemm_tc_kernel<FUSED, SPLIT><<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(a, maps);
+    q4_gemm_tc_kernel<FUSED, SPLIT><<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(a, maps, wm);
     return cudaGetLastError();
 }
 
 cudaError_t launch_q4_gemm_tc(bool fused, bool split, const Q4Job* jobs, int njobs_max, const int* njobs_dev,
-                              const TcMaps& bmaps, const float* y_base, int y_cols, void* out_h, void* out_l,
-                              float* out_f, int R, int rows_total, int* status, cudaStream_t stream) {
+                              const TcMaps& bmaps, const TcWeightMaps& wm, const float* y_base, int y_cols, void* out_h,
+                              void* out_l, float* out_f, int R, int rows_total, int* status, cudaStream_t stream) {
     if (njobs_max < 1) return cudaSuccess;
     TcArgs a;
     a.jobs = jobs; a.njobs_dev = njobs_dev;
     a.y_base = y_base; a.y_cols = y_cols;
     a.out_h = (__half*)out_h; a.out_l = (__half*)out_l; a.out_f = out_f; a.status = status;
+    a.pool = wm.pool; a.expert_stride = wm.expert_stride; a.tables = wm.tables;
+    a.tensor0 = fused ? 0 : 2;
+    a.tab_tma = wm.tab_tma[fused ? 0 : 2];
     dim3 grid((R + 127) / 128, njobs_max, 1);
     {
-        // Blocks per (row tile, expert) along the token passes.  Measured at B = 512 / 2048 (32 / 128 tokens
-        // per expert on average): the fused gate/up kernel gains 5 % / 20 % from 2 / 4 blocks (skewed routing
-        // leaves experts with several hundred tokens), the down kernel loses 3-10 % to the blocks that find
-        // nothing to do.
+        // Blocks per (row tile, expert) along the token passes: skewed routing leaves experts with several
+        // hundred tokens, whose 128-token passes would otherwise run one after the other on one SM.
         const int avg = rows_total / njobs_max;
         grid.z = fused ? (avg >= 96 ? 4u : (avg >= 24 ? 2u : 1u)) : 1u;
     }
     if (fused)
-        return split ? launch_tc<true, true>(a, bmaps, grid, stream) : launch_tc<true, false>(a, bmaps, grid, stream);
-    return split ? launch_tc<false, true>(a, bmaps, grid, stream) : launch_tc<false, false>(a, bmaps, grid, stream);
+        return split ? launch_tc<true, true>(a, bmaps, wm, grid, stream) : launch_tc<true, false>(a, bmaps, wm, grid, stream);
+    return split ? launch_tc<false, true>(a, bmaps, wm, grid, stream) : launch_tc<false, false>(a, bmaps, wm, grid, stream);
 }
 
 }  // namespace sb
-
