@@ -41,11 +41,14 @@
 
 namespace sb {
 
-constexpr int TC_STAGES = 3;
-constexpr int TC_CONVERTERS = 256;
+constexpr int TC_STAGES = 4;             // most A stages (in tensor memory)
+constexpr int TC_GROUP = 256;                // converter threads of one chunk (two groups take alternate chunks)
+constexpr int TC_CONVERTERS = 2 * TC_GROUP;
 constexpr int TC_THREADS = TC_CONVERTERS + 64;   // + issuer warp + producer warp
+constexpr int TC_ISSUER_WARP = TC_CONVERTERS / 32, TC_PRODUCER_WARP = TC_ISSUER_WARP + 1;
 constexpr int TC_KC = 64;                    // K columns per chunk
-constexpr int TC_A_BYTES = 128 * TC_KC * 2;  // one matrix' 128 x 64 fp16 tile
+constexpr int TC_A_COLS = TC_KC / 2;        // 32-bit TMEM columns of one matrix' 128 x 64 fp16 tile
+constexpr uint32_t TC_TMEM_COLS = 512;
 constexpr int TC_PK_BYTES = 128 * TC_KC / 2; // its packed form
 constexpr int TC_TAB_BYTES = 128 * 16;       // scale | bias words of 128 rows x 4 chunks
 constexpr int TC_MAX_NT = 128;
@@ -64,6 +67,18 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d),
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// The same with the A operand in tensor memory: row m of the 128 x 16 tile in lane m, two fp16 per
+// 32-bit column (8 columns per instruction, K order = column order).
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 
@@ -108,40 +123,35 @@ __device__ __forceinline__ bool fp16_path_ok(uint32_t s_bits, uint32_t b_bits) {
     return s_ok && b_ok;
 }
 
-// 32 consecutive Q4 elements of one row (16 packed bytes) -> four 16-byte chunks of the
-// row's 128-byte line at dst, chunk c0 + i stored at position (c0 + i) ^ sw (128-byte
-// swizzle, sw = row & 7), fp16 arithmetic: a nibble masked in place under the exponent of
-// 2^10 reads as 1024 + q (low nibble of a byte) or 1024 + 16 q (high nibble); subtracting
-// 1024 is exact and one half2 fma with s (or s/16) forms q*s + b with a single rounding.
-__device__ __forceinline__ void dequant_half_chunk_f16(const uint4& p, uint32_t s_bits, uint32_t b_bits, uint8_t* dst,
-                                                       uint32_t c0, uint32_t sw) {
+// 32 consecutive Q4 elements of one row (16 packed bytes) -> 16 half2 words in the operands' K order
+// (word 4 i + k holds columns (k, k + 4) of the i-th group of 8), fp16 arithmetic: a nibble masked in place
+// under the exponent of 2^10 reads as 1024 + q (low nibble of a byte) or 1024 + 16 q (high nibble);
+// subtracting 1024 is exact and one half2 fma with s (or s/16) forms q*s + b with a single rounding.
+__device__ __forceinline__ void dequant_half_chunk_f16(const uint4& p, uint32_t s_bits, uint32_t b_bits,
+                                                       uint32_t (&o)[16]) {
     const float s = bf16_bits_to_f32(s_bits), b = bf16_bits_to_f32(b_bits);
     const uint32_t s2 = f16x2_from(s, s), s2_16 = f16x2_from(s * 0.0625f, s * 0.0625f), b2 = f16x2_from(b, b);
     const uint32_t w[4] = {p.x, p.y, p.z, p.w};
     const uint32_t k1024 = 0x64006400u;
 #pragma unroll
-    for (int i = 0; i < 4; i++) {  // word i = 8 columns = one K core matrix
+    for (int i = 0; i < 4; i++) {  // word i = 8 columns
         const uint32_t w0 = w[i], w1 = w[i] >> 8;
         uint32_t a0, a1, a2, a3;
         asm("lop3.b32 %0, %1, 0x000f000f, %2, 0xEA;" : "=r"(a0) : "r"(w0), "r"(k1024));   // cols (0,4)
         asm("lop3.b32 %0, %1, 0x00f000f0, %2, 0xEA;" : "=r"(a1) : "r"(w0), "r"(k1024));   // cols (1,5) * 16
         asm("lop3.b32 %0, %1, 0x000f000f, %2, 0xEA;" : "=r"(a2) : "r"(w1), "r"(k1024));   // cols (2,6)
         asm("lop3.b32 %0, %1, 0x00f000f0, %2, 0xEA;" : "=r"(a3) : "r"(w1), "r"(k1024));   // cols (3,7) * 16
-        uint4 o;
-        o.x = hfma2(hsub2(a0, k1024), s2, b2);
-        o.y = hfma2(hsub2(a1, k1024), s2_16, b2);
-        o.z = hfma2(hsub2(a2, k1024), s2, b2);
-        o.w = hfma2(hsub2(a3, k1024), s2_16, b2);
-        *(uint4*)(dst + (((c0 + i) ^ sw) << 4)) = o;
+        o[4 * i + 0] = hfma2(hsub2(a0, k1024), s2, b2);
+        o[4 * i + 1] = hfma2(hsub2(a1, k1024), s2_16, b2);
+        o[4 * i + 2] = hfma2(hsub2(a2, k1024), s2, b2);
+        o[4 * i + 3] = hfma2(hsub2(a3, k1024), s2_16, b2);
     }
 }
 
-// The same 32 elements through fp32 (any scale), optionally with the fp16 residuals
-// lo = fp16(v - hi) at dst_lo.
+// The same 32 elements through fp32 (any scale), optionally with the fp16 residuals lo = fp16(v - hi).
 template <bool SPLIT>
 __device__ __forceinline__ void dequant_half_chunk_f32(const NibbleMagic& mg, const uint4& p, uint32_t s_bits,
-                                                       uint32_t b_bits, uint8_t* dst, uint8_t* dst_lo, uint32_t c0,
-                                                       uint32_t sw) {
+                                                       uint32_t b_bits, uint32_t (&hi)[16], uint32_t (&lo)[16]) {
     const float s = bf16_bits_to_f32(s_bits), b = bf16_bits_to_f32(b_bits);
     const uint32_t w[4] = {p.x, p.y, p.z, p.w};
     const f32x2 ss = pack2(s, s), bb = pack2(b, b);
@@ -153,15 +163,12 @@ __device__ __forceinline__ void dequant_half_chunk_f32(const NibbleMagic& mg, co
         float v[8];
 #pragma unroll
         for (int k = 0; k < 4; k++) unpack2(fma2(q[k], ss, bb), v[2 * k], v[2 * k + 1]);
-        uint32_t hi[4], lo[4];
 #pragma unroll
         for (int k = 0; k < 4; k++) {   // half2 k holds columns (k, k + 4)
-            hi[k] = f16x2_from(v[k], v[k + 4]);
-            if (SPLIT) lo[k] = f16x2_from(v[k] - f16_lo_to_f32(hi[k]), v[k + 4] - f16_hi_to_f32(hi[k]));
+            const uint32_t h = f16x2_from(v[k], v[k + 4]);
+            hi[4 * i + k] = h;
+            if (SPLIT) lo[4 * i + k] = f16x2_from(v[k] - f16_lo_to_f32(h), v[k + 4] - f16_hi_to_f32(h));
         }
-        const uint32_t off = ((c0 + i) ^ sw) << 4;
-        *(uint4*)(dst + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-        if (SPLIT) *(uint4*)(dst_lo + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
     }
 }
 
@@ -229,6 +236,7 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
     __shared__ __align__(8) uint64_t bar_full[TC_STAGES];     // stage converted (8 warp arrivals)
     __shared__ __align__(8) uint64_t bar_acc;                 // a token pass' accumulators are final
     __shared__ __align__(8) uint64_t bar_tab;                 // the tile's whole scale table landed (untiled form)
+    __shared__ __align__(8) uint64_t bar_epi;                 // a token pass' accumulators have been read (4 warp arrivals)
     __shared__ uint32_t s_tmem;
     __shared__ int s_fail;
 
@@ -253,30 +261,32 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
     const int expert = (int)((size_t)(jb.vals - a.pool) / a.expert_stride);   // local expert = slice of the weight maps
     constexpr int NMAT = FUSED ? 2 : 1;
     constexpr int NPART = SPLIT ? 2 : 1;                     // hi (+ lo) copies of every operand tile
+    // tensor memory: accumulators of the NMAT matrices (128 columns each), then the A stages, each
+    // [matrix][hi, lo] tiles of 32 columns
     constexpr int STAGES = (FUSED && SPLIT) ? 2 : TC_STAGES;
-    constexpr int STAGE_BYTES = NMAT * NPART * TC_A_BYTES;   // A tiles of a stage: [matrix][hi, lo]
+    constexpr uint32_t ACC_COLS = NMAT * 128;
+    constexpr uint32_t STAGE_COLS = NMAT * NPART * TC_A_COLS;
+    static_assert(ACC_COLS + STAGES * STAGE_COLS <= TC_TMEM_COLS, "tensor memory budget");
     const bool tab_tma = a.tab_tma != 0;
     // B tile rows = smallest TMA box (16, 32, 64, 128 token rows) that holds a pass
     const int ntok_cap = min(jb.ntok, TC_MAX_NT);
     const int variant = ntok_cap <= 16 ? 0 : ntok_cap <= 32 ? 1 : ntok_cap <= 64 ? 2 : 3;
     const uint32_t part_bytes = (16u << variant) * 128u;
-    // 1024-byte aligned carve-up: A stages | whole-tile table (untiled form) | ring of input slots, each
+    // 1024-byte aligned carve-up: whole-tile table (untiled form) | ring of input slots, each
     // [packed weights, NMAT x 4 KB][table block, NMAT x 2 KB (tiled form)][activation tile(s)]
-    uint8_t* stage_base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t* tabw = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const uint32_t tabm_bytes = tab_tma ? 0u : (uint32_t)(128 * nchunks * 4);
     const uint32_t tabw_bytes = (NMAT * tabm_bytes + 1023u) & ~1023u;
-    uint8_t* tabw = stage_base + STAGES * STAGE_BYTES;
     uint8_t* in_base = tabw + tabw_bytes;
     const uint32_t b_off = NMAT * (TC_PK_BYTES + (tab_tma ? TC_TAB_BYTES : 0));
     const uint32_t slot_bytes = b_off + NPART * part_bytes;
-    const int avail = TC_SMEM_BYTES - 1024 - STAGES * STAGE_BYTES - (int)tabw_bytes;
+    const int avail = TC_SMEM_BYTES - 1024 - (int)tabw_bytes;
     const uint32_t NQ = (uint32_t)min(TC_MAX_SLOTS, avail / (int)slot_bytes);
     if ((int)NQ < STAGES) {                                   // the host checks the geometry; never expected
         if (tid == 0 && a.status) atomicOr(a.status, SB_ERR_INDEX);
         return;
     }
     const int npass = (jb.ntok + TC_MAX_NT - 1) / TC_MAX_NT;
-    const uint32_t total = (uint32_t)npass * (uint32_t)nchunks;
     volatile int* fail = &s_fail;
 
     if (tid == 0) {
@@ -284,15 +294,16 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
             mbar_init(&bar_in[s], 1);
             mbar_init(&bar_done[s], 1);
         }
-        for (int s = 0; s < TC_STAGES; s++) mbar_init(&bar_full[s], TC_CONVERTERS / 32);
+        for (int s = 0; s < TC_STAGES; s++) mbar_init(&bar_full[s], TC_GROUP / 32);
         mbar_init(&bar_acc, 1);
         mbar_init(&bar_tab, 1);
+        mbar_init(&bar_epi, 4);
         s_fail = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)),
-                     "r"(256u)
+                     "r"(TC_TMEM_COLS)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -305,19 +316,22 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
     uint32_t p_issued = 0;    // producer: chunks requested
     uint32_t i_committed = 0; // issuer: chunks committed
 
-    if (warp < 8) {
+    if (warp < TC_ISSUER_WARP) {
         // ================= converters (and the epilogue of every pass on warps 0-3) =================
-        // One 32-element half of a 64-column chunk of one row, in every matrix.  Eight consecutive lanes
-        // take eight consecutive rows; the swizzle sends their 16-byte stores to eight different bank groups.
-        const int crow = ((tid & 7) | ((tid >> 4) << 3)) & 127, chalf = (tid >> 3) & 1;
-        const uint32_t a_off = (uint32_t)crow * 128;            // the row's 128-byte line in a 128 x 64 fp16 tile
-        const uint32_t a_c0 = (uint32_t)chalf * 4, a_sw = (uint32_t)crow & 7;
+        // Two groups of eight warps take alternate chunks, so one group's barrier round trips and
+        // tensor-memory stores overlap the other's arithmetic.
+        // One 32-element half of a 64-column chunk of one row, in every matrix, written straight into the
+        // A tile in tensor memory: row = TMEM lane (a warp reaches the lane quarter warp % 4), the half's 16
+        // half2 words = 16 columns.
+        const uint32_t grp = (uint32_t)warp >> 3;
+        const int crow = (warp & 3) * 32 + lane, chalf = (warp >> 2) & 1;
+        const uint32_t a_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + ACC_COLS + (uint32_t)chalf * 16;
         const NibbleMagic mg = load_nibble_magic();
         uint32_t cs = 0, cs_ph = 0;      // A stage and its parity
         uint32_t cq = 0, cq_ph = 0;      // input slot and its parity
         uint32_t dq = 0, dq_ph = 0;      // slot whose commit frees the A stage (chunk it - STAGES)
-        bool tab_ready = tab_tma;
-        for (int pass = 0; pass < npass && !*fail; pass++) {
+        bool alive = tab_tma || __all_sync(0xffffffffu, mbar_wait(&bar_tab, 0, fail));   // the tile's whole table (untiled form)
+        for (int pass = 0; pass < npass && alive && !*fail; pass++) {
             const int tb = pass * TC_MAX_NT;
             const int nt_real = min(TC_MAX_NT, jb.ntok - tb);
             const int NT = (nt_real + 15) & ~15;
@@ -327,29 +341,31 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
                 for (int d = 0; d < 4; d++) {
                     const int kc = kc0 + d;
                     if (kc >= nchunks) break;
-                    uint8_t* st = stage_base + cs * STAGE_BYTES;
+                    const uint32_t st = a_lane + cs * STAGE_COLS;
                     const uint8_t* slot = in_base + cq * slot_bytes;
-                    // the chunk's packed weights have landed, and the MMAs that last read this stage are complete
-                    bool ok = it < (uint32_t)STAGES ? mbar_wait(&bar_in[cq], cq_ph, fail)
-                                                    : mbar_wait2(&bar_in[cq], cq_ph, &bar_done[dq], dq_ph, fail);
-                    if (ok && !tab_ready) { ok = mbar_wait(&bar_tab, 0, fail); tab_ready = true; }
-                    if (!ok) { kc0 = nchunks; break; }   // the failure flag is up: every role leaves its loop
-                    {
-                        if (d == 0) {
-                            if (tab_tma) {
+                    const bool mine = (it & 1u) == grp;
+                    if (!tab_tma && d == 0) {
 #pragma unroll
-                                for (int m = 0; m < NMAT; m++) {
-                                    const uint4 t = lds_v4(slot + NMAT * TC_PK_BYTES + m * TC_TAB_BYTES + crow * 16);
-                                    tw[m][0] = t.x; tw[m][1] = t.y; tw[m][2] = t.z; tw[m][3] = t.w;
-                                }
-                            } else {
+                        for (int m = 0; m < NMAT; m++)
 #pragma unroll
-                                for (int m = 0; m < NMAT; m++)
+                            for (int dd = 0; dd < 4; dd++)
+                                tw[m][dd] = kc0 + dd < nchunks
+                                                ? *(const uint32_t*)(tabw + m * tabm_bytes + (size_t)(crow * nchunks + kc0 + dd) * 4)
+                                                : 0u;
+                    }
+                    if (mine) {
+                        // the chunk's packed weights have landed, and the MMAs that last read this stage are complete
+                        bool ok = it < (uint32_t)STAGES ? mbar_wait(&bar_in[cq], cq_ph, fail)
+                                                        : mbar_wait2(&bar_in[cq], cq_ph, &bar_done[dq], dq_ph, fail);
+                        ok = __all_sync(0xffffffffu, ok);      // the tensor-memory stores below are warp-wide
+                        if (!ok) { alive = false; kc0 = nchunks; break; }   // the failure flag is up: every role leaves its loop
+                        if (tab_tma && d < 2) {
+                            // tiled form: the table block of these four chunks rides in the slots of the block's first two
+                            // chunks, one copy for each group (chunk and column parities agree: C is a multiple of 256)
 #pragma unroll
-                                    for (int dd = 0; dd < 4; dd++)
-                                        tw[m][dd] = kc0 + dd < nchunks
-                                                        ? *(const uint32_t*)(tabw + m * tabm_bytes + (size_t)(crow * nchunks + kc0 + dd) * 4)
-                                                        : 0u;
+                            for (int m = 0; m < NMAT; m++) {
+                                const uint4 t = lds_v4(slot + NMAT * TC_PK_BYTES + m * TC_TAB_BYTES + crow * 16);
+                                tw[m][0] = t.x; tw[m][1] = t.y; tw[m][2] = t.z; tw[m][3] = t.w;
                             }
                         }
                         uint4 cur[NMAT];
@@ -365,34 +381,39 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
                         bool half_math = !SPLIT;
 #pragma unroll
                         for (int m = 0; m < NMAT; m++) half_math = half_math && fp16_path_ok(cur_s[m], cur_b[m]);
+                        half_math = __all_sync(0xffffffffu, half_math);   // the stores below are warp-wide
+                        // the MMAs that read this stage last are complete (observed above): order the stores after them
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         if (half_math) {
 #pragma unroll
-                            for (int m = 0; m < NMAT; m++)
-                                dequant_half_chunk_f16(cur[m], cur_s[m], cur_b[m], st + m * NPART * TC_A_BYTES + a_off,
-                                                       a_c0, a_sw);
+                            for (int m = 0; m < NMAT; m++) {
+                                uint32_t o[16];
+                                dequant_half_chunk_f16(cur[m], cur_s[m], cur_b[m], o);
+                                tmem_st16(st + m * NPART * TC_A_COLS, o);
+                            }
                         } else {
 #pragma unroll
                             for (int m = 0; m < NMAT; m++) {
-                                uint8_t* dst = st + m * NPART * TC_A_BYTES + a_off;
-                                dequant_half_chunk_f32<SPLIT>(mg, cur[m], cur_s[m], cur_b[m], dst, dst + TC_A_BYTES,
-                                                              a_c0, a_sw);
+                                uint32_t hi[16], lo[16];
+                                dequant_half_chunk_f32<SPLIT>(mg, cur[m], cur_s[m], cur_b[m], hi, lo);
+                                tmem_st16(st + m * NPART * TC_A_COLS, hi);
+                                if (SPLIT) tmem_st16(st + m * NPART * TC_A_COLS + TC_A_COLS, lo);
                             }
                         }
+                        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                        // tensor-memory stores -> ordered before the issuer's MMAs through the barrier, one arrival per warp
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&bar_full[cs]);
                     }
-                    // generic-proxy writes -> visible to the tensor core (async proxy), then one
-                    // arrival per warp
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&bar_full[cs]);
                     if (it >= (uint32_t)STAGES && ++dq == NQ) { dq = 0; dq_ph ^= 1u; }
                     if (++cs == (uint32_t)STAGES) { cs = 0; cs_ph ^= 1u; }
                     if (++cq == NQ) { cq = 0; cq_ph ^= 1u; }
                     it++;
                 }
             }
-            // ---- epilogue of this token pass (warps 0-3): the next pass' first MMA needs these warps'
-            // arrival on its stage, which follows the accumulator reads in program order
-            if (warp < 4 && mbar_wait(&bar_acc, pass & 1, fail)) {
+            // ---- epilogue of this token pass (warps 0-3); the issuer starts the next pass' MMAs after their arrival
+            if (warp < 4 && __all_sync(0xffffffffu, mbar_wait(&bar_acc, pass & 1, fail))) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const int m = r0 + warp * 32 + lane;
                 const int mpos = (m & ~7) | tc_kpos(m & 7);      // GeGLU output feeds the next GEMM's K
@@ -426,27 +447,51 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
                     }
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_epi);
             }
         }
-    } else if (warp == 8) {
-        // ================= issuer warp =================
-        // All ring positions and phase parities are carried incrementally: the loop is one thread's
-        // dependent instruction stream, and every barrier operation in it costs a round trip.
-        const uint32_t a_lo0 = DESC_B_LO | ((smem_u32(stage_base) & 0x3ffffu) >> 4);
-        const uint32_t b_lo0 = DESC_B_LO | ((smem_u32(in_base + b_off) & 0x3ffffu) >> 4);
-        uint32_t is = 0, is_ph = 0, iq = 0, iq_ph = 0;
-        for (int pass = 0; pass < npass && !*fail; pass++) {
-            const int nt_real = min(TC_MAX_NT, jb.ntok - pass * TC_MAX_NT);
-            const uint32_t idesc = umma_idesc_f16(128, (nt_real + 15) & ~15);
-            for (int kc = 0; kc < nchunks; kc++) {
-                // the converted weights of the stage and the activation tile of the slot (the converters
-                // waited for the same slot; the tensor core reads it through the async proxy, so the
-                // issuing thread observes the barrier itself)
-                const bool ok = mbar_wait2(&bar_full[is], is_ph, &bar_in[iq], iq_ph, fail);
-                if (!ok) break;
-                if (lane == 0) {
+    } else if (warp == TC_ISSUER_WARP) {
+        // ================= issuer (one thread) =================
+        // The loop is one thread's dependent instruction stream and every barrier operation in it costs a
+        // round trip: ring positions and parities are carried incrementally, and the next chunk's barriers
+        // are polled (without blocking) before this chunk's MMAs are issued, so the answer arrives behind them.
+        if (lane == 0) {
+            const uint32_t b_lo0 = DESC_B_LO | ((smem_u32(in_base + b_off) & 0x3ffffu) >> 4);
+            uint32_t is = 0, is_ph = 0, iq = 0, iq_ph = 0;
+            uint32_t ready = 0;
+            bool ok = true;
+            for (int pass = 0; pass < npass && ok && !*fail; pass++) {
+                const int nt_real = min(TC_MAX_NT, jb.ntok - pass * TC_MAX_NT);
+                const uint32_t idesc = umma_idesc_f16(128, (nt_real + 15) & ~15);
+                // the accumulators of the previous pass have been read
+                if (pass > 0 && !mbar_wait(&bar_epi, (pass - 1) & 1, fail)) break;
+                for (int kc = 0; kc < nchunks; kc++) {
+                    // the converted weights of the stage and the activation tile of the slot (the converters
+                    // waited for the same slot; the tensor core reads it through the async proxy, so the
+                    // issuing thread observes the barrier itself)
+                    if (!ready) ok = mbar_wait2(&bar_full[is], is_ph, &bar_in[iq], iq_ph, fail);
+                    if (!ok) break;
+                    uint32_t ns = is + 1, ns_ph = is_ph, nq = iq + 1, nq_ph = iq_ph;
+                    if (ns == (uint32_t)STAGES) { ns = 0; ns_ph ^= 1u; }
+                    if (nq == NQ) { nq = 0; nq_ph ^= 1u; }
+                    uint32_t r_full, r_in;
+                    asm volatile(
+                        "{\n\t.reg .pred p;\n\t"
+                        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                        "selp.u32 %0, 1, 0, p;\n\t}\n"
+                        : "=r"(r_full)
+                        : "r"(smem_u32(&bar_full[ns])), "r"(ns_ph)
+                        : "memory");
+                    asm volatile(
+                        "{\n\t.reg .pred p;\n\t"
+                        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                        "selp.u32 %0, 1, 0, p;\n\t}\n"
+                        : "=r"(r_in)
+                        : "r"(smem_u32(&bar_in[nq])), "r"(nq_ph)
+                        : "memory");
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t alo = a_lo0 + is * (STAGE_BYTES >> 4);
+                    const uint32_t a_st = tmem + ACC_COLS + is * STAGE_COLS;
                     const uint32_t blo = b_lo0 + iq * (slot_bytes >> 4);
                     const uint32_t blo_l = blo + (part_bytes >> 4);
 #pragma unroll
@@ -455,23 +500,23 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
                         const uint32_t acc = (kc > 0 || j > 0) ? 1u : 0u;
 #pragma unroll
                         for (int m = 0; m < NMAT; m++) {
-                            const uint32_t ah = alo + ((m * NPART * TC_A_BYTES + j * 32) >> 4);
+                            const uint32_t ah = a_st + m * NPART * TC_A_COLS + j * 8;
                             const uint32_t d = tmem + m * 128;
-                            umma_f16(d, make_desc(ah, DESC_B_HI), bh, idesc, acc);
+                            umma_f16_ts(d, ah, bh, idesc, acc);
                             if (SPLIT) {
                                 // A_lo * B_hi, then A_hi * B_lo
-                                umma_f16(d, make_desc(ah + (TC_A_BYTES >> 4), DESC_B_HI), bh, idesc, 1u);
-                                umma_f16(d, make_desc(ah, DESC_B_HI), make_desc(blo_l + j * 2, DESC_B_HI), idesc, 1u);
+                                umma_f16_ts(d, ah + TC_A_COLS, bh, idesc, 1u);
+                                umma_f16_ts(d, ah, make_desc(blo_l + j * 2, DESC_B_HI), idesc, 1u);
                             }
                         }
                     }
                     umma_commit(&bar_done[iq]);
                     if (kc == nchunks - 1) umma_commit(&bar_acc);
+                    i_committed++;
+                    // the poll is only good inside a pass: the next pass' first MMAs also wait for the epilogue
+                    ready = (kc + 1 < nchunks) ? (r_full & r_in) : 0u;
+                    is = ns; is_ph = ns_ph; iq = nq; iq_ph = nq_ph;
                 }
-                i_committed++;
-                if (++is == (uint32_t)STAGES) { is = 0; is_ph ^= 1u; }
-                if (++iq == NQ) { iq = 0; iq_ph ^= 1u; }
-                __syncwarp();
             }
         }
     } else if (lane == 0) {
@@ -497,13 +542,13 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
                 // the slot's previous chunk has been consumed: its MMAs (which followed its conversion) are complete
                 if (p_issued >= NQ && !mbar_wait(&bar_done[pq], pq_ph ^ 1u, fail)) break;
                 const uint32_t dst = smem_u32(in_base + pq * slot_bytes);
-                const bool with_tab = tab_tma && (kc & 3) == 0;
+                const bool with_tab = tab_tma && (kc & 3) < 2;     // one copy for each converter group
                 mbar_expect_tx(&bar_in[pq], NMAT * (TC_PK_BYTES + (with_tab ? TC_TAB_BYTES : 0)) + NPART * part_bytes);
 #pragma unroll
                 for (int m = 0; m < NMAT; m++) {
                     tma_load_3d(dst + m * TC_PK_BYTES, &wm.w[FUSED ? m : 2], kc * 32, r0, expert, &bar_in[pq]);
                     if (with_tab)
-                        tma_load_3d(dst + NMAT * TC_PK_BYTES + m * TC_TAB_BYTES, &wm.t[FUSED ? m : 2], kc * 4, r0, expert,
+                        tma_load_3d(dst + NMAT * TC_PK_BYTES + m * TC_TAB_BYTES, &wm.t[FUSED ? m : 2], (kc & ~3) * 4, r0, expert,
                                     &bar_in[pq]);
                 }
                 tma_load_2d(dst + b_off, &maps.hi[variant], kc * TC_KC, g0 + pass * TC_MAX_NT, &bar_in[pq]);
@@ -518,19 +563,19 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
         // wait (bounded, no early exit) for the copies and MMAs still in flight before shared memory and
         // TMEM are released
         int none = 0;
-        if (warp == 9 && lane == 0) {
+        if (warp == TC_PRODUCER_WARP && lane == 0) {
             if (!tab_tma) (void)mbar_wait(&bar_tab, 0, &none);
             for (uint32_t t = (p_issued > NQ ? p_issued - NQ : 0); t < p_issued; t++)
                 (void)mbar_wait(&bar_in[t % NQ], (t / NQ) & 1, &none);
         }
-        if (warp == 8 && lane == 0 && i_committed > 0)
+        if (warp == TC_ISSUER_WARP && lane == 0 && i_committed > 0)
             (void)mbar_wait(&bar_done[(i_committed - 1) % NQ], ((i_committed - 1) / NQ) & 1, &none);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (tid == 0 && *fail && a.status) atomicOr(a.status, SB_ERR_TIMEOUT);
     if (warp == 0) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_TMEM_COLS) : "memory");
     }
 }
 
@@ -665,7 +710,7 @@ static bool tc_geometry_ok(int C, bool fused, bool split) {
     const bool tab_tma = (C % 256) == 0;
     const int tabw = tab_tma ? 0 : ((nmat * 128 * (C / TC_KC) * 4 + 1023) & ~1023);
     const int slot = nmat * (TC_PK_BYTES + (tab_tma ? TC_TAB_BYTES : 0)) + npart * TC_MAX_NT * 128;
-    const int avail = TC_SMEM_BYTES - 1024 - stages * nmat * npart * TC_A_BYTES - tabw;
+    const int avail = TC_SMEM_BYTES - 1024 - tabw;
     return avail / slot >= stages;
 }
 
@@ -678,8 +723,7 @@ bool q4_tc_supported(int hidden, int inter) {
 template <bool FUSED, bool SPLIT>
 static cudaError_t launch_tc(const TcArgs& a, const TcMaps& maps, const TcWeightMaps& wm, dim3 grid,
                              cudaStream_t stream) {
-    // the full dynamic shared memory keeps one block per SM, so a block's 256 TMEM columns
-    // can always be allocated without waiting for a neighbour
+    // the full dynamic shared memory keeps one block per SM: a block allocates all 512 TMEM columns
     {
         cudaError_t e = ensure_dynamic_smem((const void*)q4_gemm_tc_kernel<FUSED, SPLIT>, (size_t)TC_SMEM_BYTES);
         if (e != cudaSuccess) return e;
