@@ -121,6 +121,8 @@ cudaError_t make_tc_maps(TcMaps* out, const void* hi, const void* lo, int rows, 
 struct TcWeightMaps {
     CUtensorMap w[3];
     CUtensorMap t[3];
+    CUtensorMap w256[3];      // the same with boxes of 256 rows (wide single-precision kernel)
+    CUtensorMap t256[3];
     const uint8_t* pool;
     size_t expert_stride;
     const uint32_t* tables;

@@ -579,6 +579,336 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Single-precision form with the operands swapped: the tokens of a pass (up to 128, stale rows above
+// them) are the MMA's M side, read from shared memory as they arrive by TMA; 256 weight rows are the N
+// side, dequantised into a K-major 128-byte-swizzled shared-memory tile.  One instruction (M128 x N256 x
+// K16) then covers twice the weights of the 128-row form; an instruction with N <= 128 costs the issuing
+// thread about 100 cycles whatever N (measured), so the instruction count is what this form halves.
+// The 256 rows are one tile of the down matrix, or - fused - 128 rows of gate followed by the same 128 rows
+// of up: gate and up of a chunk are ONE instruction, and the GeGLU pairs accumulator column c with 128 + c.
+// Accumulators: lane = token, column = weight row.
+// Roles as in the kernel above: two converter groups of 256 threads (thread = stage row) on alternate
+// chunks, one issuing thread, one producing thread; all 16 converter warps share the epilogue (warp w: lane
+// quarter w % 4, a quarter of the columns).
+constexpr int TW_ROWS = 256;                        // rows of a converted stage
+constexpr int TW_PK_BYTES = TW_ROWS * TC_KC / 2;    // packed chunk
+constexpr int TW_TAB_BYTES = TW_ROWS * 16;          // table block (4 chunks)
+constexpr int TW_B_BYTES = TW_ROWS * TC_KC * 2;     // converted chunk
+constexpr int TW_TOK_BYTES = TC_MAX_NT * TC_KC * 2; // token tile
+constexpr int TW_STAGES = 3;
+
+template <bool FUSED>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+q4_gemm_tc_wide_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __grid_constant__ TcWeightMaps wm) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_in[TC_MAX_SLOTS];    // input slot landed (TMA transaction bytes)
+    __shared__ __align__(8) uint64_t bar_done[TC_MAX_SLOTS];  // the chunk's MMAs are complete (tcgen05.commit)
+    __shared__ __align__(8) uint64_t bar_full[TW_STAGES];     // stage converted (8 warp arrivals)
+    __shared__ __align__(8) uint64_t bar_acc;                 // a token pass' accumulators are final
+    __shared__ __align__(8) uint64_t bar_tab;                 // the tile's whole scale table landed (untiled form)
+    __shared__ __align__(8) uint64_t bar_epi;                 // a token pass' accumulators have been read (16 warp arrivals)
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_fail;
+
+    constexpr int NMAT = FUSED ? 2 : 1;
+    constexpr int RT = TW_ROWS / NMAT;                        // weight rows of a tile, per matrix
+    const int job_id = blockIdx.y;
+    if (a.njobs_dev != nullptr && job_id >= *a.njobs_dev) return;
+    Q4Job jb = a.jobs[job_id];
+    const int r0 = blockIdx.x * RT;
+    if (r0 >= jb.R || jb.ntok < 1) return;
+    int pass_shift = 0;
+    if (gridDim.z > 1) {
+        const int npass_all = (jb.ntok + TC_MAX_NT - 1) / TC_MAX_NT;
+        const int per = (npass_all + (int)gridDim.z - 1) / (int)gridDim.z;
+        pass_shift = (int)blockIdx.z * per * TC_MAX_NT;
+        if (pass_shift >= jb.ntok) return;
+        jb.ntok = min(per * TC_MAX_NT, jb.ntok - pass_shift);
+    }
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int C = jb.C, nchunks = C / TC_KC;
+    const int g0 = (int)((jb.y - a.y_base) / a.y_cols) + pass_shift;   // first grouped row of this block's tokens
+    const int expert = (int)((size_t)(jb.vals - a.pool) / a.expert_stride);
+    const int rows_here = min(RT, jb.R - r0);                 // a multiple of 64
+    constexpr int STAGES = TW_STAGES;
+    const bool tab_tma = a.tab_tma != 0;
+    const int ntok_cap = min(jb.ntok, TC_MAX_NT);
+    const int variant = ntok_cap <= 16 ? 0 : ntok_cap <= 32 ? 1 : ntok_cap <= 64 ? 2 : 3;
+    const uint32_t tok_bytes = (16u << variant) * 128u;
+    // carve-up: converted stages | whole-tile table (untiled form) | input slots, each
+    // [packed weights, 8 KB][table block, 4 KB (tiled form)][token tile]
+    uint8_t* stage_base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    const uint32_t tabw_bytes = tab_tma ? 0u : (((uint32_t)(TW_ROWS * nchunks * 4) + 1023u) & ~1023u);
+    uint8_t* tabw = stage_base + STAGES * TW_B_BYTES;
+    uint8_t* in_base = tabw + tabw_bytes;
+    const uint32_t tok_off = TW_PK_BYTES + (tab_tma ? TW_TAB_BYTES : 0);
+    // The MMA always reads 128 token rows: rows above the copied box are stale bytes of the next slot (or of
+    // the pad behind the last one) and only reach accumulator lanes nobody reads.
+    const uint32_t tok_room = (tok_bytes + 1023u) & ~1023u;
+    const uint32_t slot_bytes = tok_off + tok_room;
+    const int avail = TC_SMEM_BYTES - 1024 - STAGES * TW_B_BYTES - (int)tabw_bytes - (TW_TOK_BYTES - (int)tok_room);
+    const uint32_t NQ = (uint32_t)min(TC_MAX_SLOTS, avail / (int)slot_bytes);
+    if ((int)NQ < STAGES) {                                   // the host checks the geometry; never expected
+        if (tid == 0 && a.status) atomicOr(a.status, SB_ERR_INDEX);
+        return;
+    }
+    const int npass = (jb.ntok + TC_MAX_NT - 1) / TC_MAX_NT;
+    volatile int* fail = &s_fail;
+
+    if (tid == 0) {
+        for (int s = 0; s < TC_MAX_SLOTS; s++) {
+            mbar_init(&bar_in[s], 1);
+            mbar_init(&bar_done[s], 1);
+        }
+        for (int s = 0; s < TW_STAGES; s++) mbar_init(&bar_full[s], TC_GROUP / 32);
+        mbar_init(&bar_acc, 1);
+        mbar_init(&bar_tab, 1);
+        mbar_init(&bar_epi, TC_CONVERTERS / 32);
+        s_fail = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)),
+                     "r"(TC_TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+
+    uint32_t it = 0;          // running chunk counter across token passes (every role counts the same chunks)
+    uint32_t p_issued = 0;    // producer: chunks requested
+    uint32_t i_committed = 0; // issuer: chunks committed
+
+    if (warp < TC_ISSUER_WARP) {
+        // ================= converters, then the epilogue of every pass =================
+        const uint32_t grp = (uint32_t)warp >> 3;
+        const int crow = (warp & 7) * 32 + lane;                 // stage row
+        const uint32_t b_off = (uint32_t)crow * 128;             // the row's 128-byte line in the 256 x 64 fp16 tile
+        const uint32_t b_sw = (uint32_t)crow & 7;
+        const NibbleMagic mg = load_nibble_magic();
+        uint32_t cs = 0, cq = 0, cq_ph = 0, dq = 0, dq_ph = 0;
+        bool alive = tab_tma || __all_sync(0xffffffffu, mbar_wait(&bar_tab, 0, fail));
+        for (int pass = 0; pass < npass && alive && !*fail; pass++) {
+            const int tb = pass * TC_MAX_NT;
+            const int nt_real = min(TC_MAX_NT, jb.ntok - tb);
+            for (int kc0 = 0; kc0 < nchunks; kc0 += 4) {
+                uint32_t tw[4];             // table words of this thread's row for four chunks
+#pragma unroll
+                for (int d = 0; d < 4; d++) {
+                    const int kc = kc0 + d;
+                    if (kc >= nchunks) break;
+                    uint8_t* st = stage_base + cs * TW_B_BYTES + b_off;
+                    const uint8_t* slot = in_base + cq * slot_bytes;
+                    const bool mine = (it & 1u) == grp;
+                    if (!tab_tma && d == 0) {
+#pragma unroll
+                        for (int dd = 0; dd < 4; dd++)
+                            tw[dd] = kc0 + dd < nchunks ? *(const uint32_t*)(tabw + (size_t)(crow * nchunks + kc0 + dd) * 4) : 0u;
+                    }
+                    if (mine) {
+                        // the chunk's packed weights have landed, and the MMAs that last read this stage are complete
+                        bool ok = it < (uint32_t)STAGES ? mbar_wait(&bar_in[cq], cq_ph, fail)
+                                                        : mbar_wait2(&bar_in[cq], cq_ph, &bar_done[dq], dq_ph, fail);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) { alive = false; kc0 = nchunks; break; }
+                        // tiled form: the table block of these four chunks rides in the slots of the block's first two
+                        // chunks, one copy for each group (chunk and column parities agree: C is a multiple of 256)
+                        if (tab_tma && d < 2) {
+                            const uint4 t = lds_v4(slot + TW_PK_BYTES + crow * 16);
+                            tw[0] = t.x; tw[1] = t.y; tw[2] = t.z; tw[3] = t.w;
+                        }
+                        const uint32_t s_bits = tw[d] >> 16, b_bits = tw[d] & 0xffffu;
+                        const bool half_math = fp16_path_ok(s_bits, b_bits);
+#pragma unroll
+                        for (int h = 0; h < 2; h++) {
+                            const uint4 pk = lds_v4(slot + crow * 32 + h * 16);
+                            uint32_t o[16], lo_unused[16];
+                            if (half_math) dequant_half_chunk_f16(pk, s_bits, b_bits, o);
+                            else dequant_half_chunk_f32<false>(mg, pk, s_bits, b_bits, o, lo_unused);
+#pragma unroll
+                            for (int i = 0; i < 4; i++)
+                                *(uint4*)(st + ((((uint32_t)(h * 4 + i)) ^ b_sw) << 4)) =
+                                    make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                        }
+                        // generic-proxy writes -> visible to the tensor core (async proxy), then one arrival per warp
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&bar_full[cs]);
+                    }
+                    if (it >= (uint32_t)STAGES && ++dq == NQ) { dq = 0; dq_ph ^= 1u; }
+                    if (++cs == (uint32_t)STAGES) cs = 0;
+                    if (++cq == NQ) { cq = 0; cq_ph ^= 1u; }
+                    it++;
+                }
+            }
+            // ---- epilogue of this pass: warp w reads lane quarter w % 4 (tokens) and a quarter of the columns
+            if (alive && __all_sync(0xffffffffu, mbar_wait(&bar_acc, pass & 1, fail))) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const int q = warp & 3;
+                const int n = q * 32 + lane;                        // token of the pass
+                const uint32_t trow = tmem + ((uint32_t)(q * 32) << 16);
+                if (q * 32 < nt_real) {                             // warp-uniform: the quarter holds tokens
+                    if (FUSED) {
+                        const int col = (warp >> 2) * 32;           // output columns col ... col + 31 of the tile
+                        if (col < rows_here) {
+                            uint32_t g[32], u[32];
+                            tmem_ld32(trow + col, g);
+                            tmem_ld32(trow + RT + col, u);
+                            if (n < nt_real) {
+                                __half* dst = a.out_h + (size_t)(g0 + tb + n) * jb.R + r0 + col;
+#pragma unroll
+                                for (int i8 = 0; i8 < 32; i8 += 8) {
+                                    float o[8];
+#pragma unroll
+                                    for (int i = 0; i < 8; i++) {
+                                        const float gv = __uint_as_float(g[i8 + i]), uv = __uint_as_float(u[i8 + i]);
+                                        const float inner = 0.7978845608028654f * (gv + 0.044715f * gv * gv * gv);
+                                        o[i] = 0.5f * gv * (1.0f + tanhf(inner)) * uv;
+                                    }
+                                    // the next GEMM's K order inside a group of 8: [0,4,1,5,2,6,3,7]
+                                    *(uint4*)(dst + i8) = make_uint4(f16x2_from(o[0], o[4]), f16x2_from(o[1], o[5]),
+                                                                     f16x2_from(o[2], o[6]), f16x2_from(o[3], o[7]));
+                                }
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int c0 = 0; c0 < 64; c0 += 32) {
+                            const int col = (warp >> 2) * 64 + c0;
+                            if (col >= rows_here) break;
+                            uint32_t g[32];
+                            tmem_ld32(trow + col, g);
+                            if (n < nt_real) {
+                                float* dst = a.out_f + (size_t)(g0 + tb + n) * jb.R + r0 + col;
+#pragma unroll
+                                for (int i = 0; i < 32; i += 4)
+                                    *(float4*)(dst + i) = make_float4(__uint_as_float(g[i]), __uint_as_float(g[i + 1]),
+                                                                      __uint_as_float(g[i + 2]), __uint_as_float(g[i + 3]));
+                            }
+                        }
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_epi);
+            }
+        }
+    } else if (warp == TC_ISSUER_WARP) {
+        // ================= issuer (one thread) =================
+        if (lane == 0) {
+            const uint32_t w_lo0 = DESC_B_LO | ((smem_u32(stage_base) & 0x3ffffu) >> 4);
+            const uint32_t t_lo0 = DESC_B_LO | ((smem_u32(in_base + tok_off) & 0x3ffffu) >> 4);
+            const uint32_t idesc = umma_idesc_f16(128, FUSED ? TW_ROWS : rows_here);
+            uint32_t is = 0, is_ph = 0, iq = 0, iq_ph = 0;
+            uint32_t ready = 0;
+            bool ok = true;
+            for (int pass = 0; pass < npass && ok && !*fail; pass++) {
+                // the accumulators of the previous pass have been read
+                if (pass > 0 && !mbar_wait(&bar_epi, (pass - 1) & 1, fail)) break;
+                for (int kc = 0; kc < nchunks; kc++) {
+                    // the converted weights of the stage, and the chunk's token tile: the tensor core reads it
+                    // through the async proxy, so the issuing thread observes that barrier itself
+                    if (!ready) ok = mbar_wait2(&bar_full[is], is_ph, &bar_in[iq], iq_ph, fail);
+                    if (!ok) break;
+                    // poll the next chunk's barriers now; the answer arrives behind this chunk's MMAs
+                    uint32_t ns = is + 1, ns_ph = is_ph, nq = iq + 1, nq_ph = iq_ph;
+                    if (ns == (uint32_t)STAGES) { ns = 0; ns_ph ^= 1u; }
+                    if (nq == NQ) { nq = 0; nq_ph ^= 1u; }
+                    uint32_t r_full, r_in;
+                    asm volatile(
+                        "{\n\t.reg .pred p;\n\t"
+                        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                        "selp.u32 %0, 1, 0, p;\n\t}\n"
+                        : "=r"(r_full)
+                        : "r"(smem_u32(&bar_full[ns])), "r"(ns_ph)
+                        : "memory");
+                    asm volatile(
+                        "{\n\t.reg .pred p;\n\t"
+                        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                        "selp.u32 %0, 1, 0, p;\n\t}\n"
+                        : "=r"(r_in)
+                        : "r"(smem_u32(&bar_in[nq])), "r"(nq_ph)
+                        : "memory");
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t wlo = w_lo0 + is * (TW_B_BYTES >> 4);
+                    const uint32_t tlo = t_lo0 + iq * (slot_bytes >> 4);
+#pragma unroll
+                    for (int j = 0; j < TC_KC / 16; j++)
+                        umma_f16(tmem, make_desc(tlo + j * 2, DESC_B_HI), make_desc(wlo + j * 2, DESC_B_HI), idesc,
+                                 (kc > 0 || j > 0) ? 1u : 0u);
+                    umma_commit(&bar_done[iq]);
+                    if (kc == nchunks - 1) umma_commit(&bar_acc);
+                    i_committed++;
+                    // a poll is only good inside a pass: the next pass' first MMAs also wait for the epilogue
+                    ready = (kc + 1 < nchunks) ? (r_full & r_in) : 0u;
+                    is = ns; is_ph = ns_ph; iq = nq; iq_ph = nq_ph;
+                }
+            }
+        }
+    } else if (lane == 0) {
+        // ================= producer (one thread) =================
+        if (!tab_tma) {
+            const uint32_t bytes = (uint32_t)(rows_here * nchunks * 4);
+            mbar_expect_tx(&bar_tab, NMAT * bytes);
+#pragma unroll
+            for (int m = 0; m < NMAT; m++) {
+                const uint32_t* src = a.tables + ((size_t)(expert * 3 + a.tensor0 + m) * jb.R + r0) * nchunks;
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 smem_u32(tabw + (size_t)m * RT * nchunks * 4)),
+                             "l"(src), "r"(bytes), "r"(smem_u32(&bar_tab))
+                             : "memory");
+            }
+        }
+        uint32_t pq = 0, pq_ph = 0;
+        for (int pass = 0; pass < npass && !*fail; pass++) {
+            for (int kc = 0; kc < nchunks; kc++) {
+                // the slot's previous chunk has been consumed: its MMAs (which followed its conversion) are complete
+                if (p_issued >= NQ && !mbar_wait(&bar_done[pq], pq_ph ^ 1u, fail)) break;
+                const uint32_t dst = smem_u32(in_base + pq * slot_bytes);
+                const bool with_tab = tab_tma && (kc & 3) < 2;     // one copy for each converter group
+                mbar_expect_tx(&bar_in[pq], TW_PK_BYTES + (with_tab ? TW_TAB_BYTES : 0) + tok_bytes);
+                if (FUSED) {
+                    // 128 rows of gate, then the same 128 rows of up
+#pragma unroll
+                    for (int m = 0; m < 2; m++) {
+                        tma_load_3d(dst + m * TC_PK_BYTES, &wm.w[m], kc * 32, r0, expert, &bar_in[pq]);
+                        if (with_tab)
+                            tma_load_3d(dst + TW_PK_BYTES + m * TC_TAB_BYTES, &wm.t[m], (kc & ~3) * 4, r0, expert, &bar_in[pq]);
+                    }
+                } else {
+                    tma_load_3d(dst, &wm.w256[2], kc * 32, r0, expert, &bar_in[pq]);
+                    if (with_tab) tma_load_3d(dst + TW_PK_BYTES, &wm.t256[2], (kc & ~3) * 4, r0, expert, &bar_in[pq]);
+                }
+                tma_load_2d(dst + tok_off, &maps.hi[variant], kc * TC_KC, g0 + pass * TC_MAX_NT, &bar_in[pq]);
+                p_issued++;
+                if (++pq == NQ) { pq = 0; pq_ph ^= 1u; }
+            }
+        }
+    }
+    if (*fail) {
+        // wait (bounded, no early exit) for the copies and MMAs still in flight before shared memory and
+        // TMEM are released
+        int none = 0;
+        if (warp == TC_PRODUCER_WARP && lane == 0) {
+            if (!tab_tma) (void)mbar_wait(&bar_tab, 0, &none);
+            for (uint32_t t = (p_issued > NQ ? p_issued - NQ : 0); t < p_issued; t++)
+                (void)mbar_wait(&bar_in[t % NQ], (t / NQ) & 1, &none);
+        }
+        if (warp == TC_ISSUER_WARP && lane == 0 && i_committed > 0)
+            (void)mbar_wait(&bar_done[(i_committed - 1) % NQ], ((i_committed - 1) / NQ) & 1, &none);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (tid == 0 && *fail && a.status) atomicOr(a.status, SB_ERR_TIMEOUT);
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_TMEM_COLS) : "memory");
+    }
+}
+
 // x (fp32, token rows) -> fp16 rows in grouped order: xh[g] = fp16(x[g2c[g] / topk]),
 // and (when xl != null) the residuals xl[g] = fp16(x - xh).  Columns inside every group
 // of 8 are written in the operands' K order.
@@ -681,6 +1011,17 @@ cudaError_t make_q4_tc_weight_maps(TcWeightMaps* out, const uint8_t* pool, size_
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
         }
+        {
+            cuuint64_t dims[3] = {(cuuint64_t)(C / 2), (cuuint64_t)R, (cuuint64_t)experts};
+            cuuint64_t strides[2] = {(cuuint64_t)(C / 2), (cuuint64_t)expert_stride};
+            cuuint32_t box[3] = {(cuuint32_t)(TC_KC / 2), (cuuint32_t)TW_ROWS, 1u};
+            cuuint32_t estr[3] = {1, 1, 1};
+            CUresult r = encode(&out->w256[k], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
+                                const_cast<uint8_t*>(pool + (size_t)k * tensor_bytes), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+        }
         out->tab_tma[k] = (C % 256) == 0 ? 1 : 0;
         if (out->tab_tma[k]) {
             cuuint64_t dims[3] = {(cuuint64_t)(C / 16), (cuuint64_t)R, (cuuint64_t)experts};
@@ -692,8 +1033,15 @@ cudaError_t make_q4_tc_weight_maps(TcWeightMaps* out, const uint8_t* pool, size_
                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+            box[1] = (cuuint32_t)TW_ROWS;
+            r = encode(&out->t256[k], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
+                       const_cast<uint32_t*>(tables + (size_t)k * (elems / 64)), dims, strides, box, estr,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
         } else {
             out->t[k] = out->w[k];   // never read
+            out->t256[k] = out->w256[k];
         }
     }
     out->pool = pool;
@@ -714,10 +1062,31 @@ static bool tc_geometry_ok(int C, bool fused, bool split) {
     return avail / slot >= stages;
 }
 
+// The same for the wide single-precision kernel (widest token tile).
+static bool tc_wide_geometry_ok(int C) {
+    const bool tab_tma = (C % 256) == 0;
+    const int tabw = tab_tma ? 0 : ((TW_ROWS * (C / TC_KC) * 4 + 1023) & ~1023);
+    const int slot = TW_PK_BYTES + (tab_tma ? TW_TAB_BYTES : 0) + TW_TOK_BYTES;
+    const int avail = TC_SMEM_BYTES - 1024 - TW_STAGES * TW_B_BYTES - tabw;
+    return avail / slot >= TW_STAGES;
+}
+
 bool q4_tc_supported(int hidden, int inter) {
     if (hidden < TC_KC || inter < TC_KC || (hidden % TC_KC) || (inter % TC_KC)) return false;
     return tc_geometry_ok(hidden, true, false) && tc_geometry_ok(hidden, true, true) &&
-           tc_geometry_ok(inter, false, false) && tc_geometry_ok(inter, false, true);
+           tc_geometry_ok(inter, false, false) && tc_geometry_ok(inter, false, true) &&
+           tc_wide_geometry_ok(hidden) && tc_wide_geometry_ok(inter);
+}
+
+template <bool FUSED>
+static cudaError_t launch_tc_wide(const TcArgs& a, const TcMaps& maps, const TcWeightMaps& wm, dim3 grid,
+                                  cudaStream_t stream) {
+    {
+        cudaError_t e = ensure_dynamic_smem((const void*)q4_gemm_tc_wide_kernel<FUSED>, (size_t)TC_SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+    }
+    q4_gemm_tc_wide_kernel<FUSED><<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(a, maps, wm);
+    return cudaGetLastError();
 }
 
 template <bool FUSED, bool SPLIT>
@@ -750,9 +1119,12 @@ cudaError_t launch_q4_gemm_tc(bool fused, bool split, const Q4Job* jobs, int njo
         const int avg = rows_total / njobs_max;
         grid.z = fused ? (avg >= 96 ? 4u : (avg >= 24 ? 2u : 1u)) : 1u;
     }
-    if (fused)
-        return split ? launch_tc<true, true>(a, bmaps, wm, grid, stream) : launch_tc<true, false>(a, bmaps, wm, grid, stream);
-    return split ? launch_tc<false, true>(a, bmaps, wm, grid, stream) : launch_tc<false, false>(a, bmaps, wm, grid, stream);
+    if (!split) {
+        // single precision: 256 weight rows (128 of gate + 128 of up when fused) on the MMA's N side
+        if (!fused) grid.x = (R + TW_ROWS - 1) / TW_ROWS;
+        return fused ? launch_tc_wide<true>(a, bmaps, wm, grid, stream) : launch_tc_wide<false>(a, bmaps, wm, grid, stream);
+    }
+    return fused ? launch_tc<true, true>(a, bmaps, wm, grid, stream) : launch_tc<false, true>(a, bmaps, wm, grid, stream);
 }
 
 }  // namespace sb
