@@ -4,27 +4,36 @@
 // fp16), accumulation is fp32 in TMEM.  The bit-exact kernels in q4_kernels.cu
 // remain the reference-conformant path.
 //
-// Two precisions (template SPLIT):
+// Two precisions:
 //   single  one MMA per k-step, operands rounded to fp16 once: measured
 //           max |err| / max(|ref|, row rms) about 2e-3 (5e-4 of the row maximum)
+//           -> q4_gemm_tc_wide_kernel (tokens on M, 256 weight rows on N)
 //   split   every operand is carried as hi + lo fp16 halves (lo = fp16(v - hi)) and
 //           each k-step issues Ah*Bh + Al*Bh + Ah*Bl: operand error ~2^-22, three
 //           times the tensor work
+//           -> q4_gemm_tc_kernel (128 weight rows on M, A operand in tensor memory)
 //
-// One block = one 128-row weight tile of one expert group.  Weight rows sit on
-// the MMA M dimension (always full), the group's tokens on N (16..128 per pass),
-// so small groups waste no tensor rows.  K advances in 64-column chunks = one
-// quantisation group per row.  Warp-specialised:
-//   warps 0-7 (converters)  dequantise 128 row-chunks per matrix Q4 -> fp16 into the
-//                           K-major 128-byte-swizzled tile layout;
-//                           packed weights come through a 4-chunk-deep register ring;
-//                           one elected mbarrier arrive per warp marks the stage full
-//   warp 8 (issuer)         feeds the tokens' fp16 activations by TMA (cp.async.bulk.tensor, 128-byte swizzle)
-//                           into a ring of B tiles several chunks ahead, issues the
-//                           tcgen05.mma.kind::f16 (M128 x N x K16) of every full stage
-//                           and tcgen05.commit on the stage's "free" mbarrier
-//   warps 0-3 (epilogue)    tcgen05.ld the accumulators, GeGLU (fused gate/up) or plain
-//                           store (down)
+// Common structure.  One block = one weight-row tile of one expert group and a run of its
+// 128-token passes.  K advances in 64-column chunks = one quantisation group per row.
+//   producer thread   packed nibbles (tiled TMA over the expert pool: bytes x rows x experts),
+//                     the (scale << 16) | bias words of the rows (tiled TMA in blocks of four
+//                     chunks where a table row is a multiple of 16 bytes, otherwise one bulk copy
+//                     of the tile's whole table) and the tokens' fp16 activations (128-byte swizzle)
+//                     into a ring of input slots, several chunks ahead
+//   converter warps   two groups of eight warps on alternate chunks: shared memory -> registers ->
+//                     Q4 -> fp16 -> the MMA operand (tensor memory via tcgen05.st, or a K-major
+//                     128-byte-swizzled shared-memory stage); one mbarrier arrival per warp
+//   issuer thread     tcgen05.mma.kind::f16 of every converted chunk, tcgen05.commit on the
+//                     chunk's "done" barrier (frees the input slot and, some chunks later, the stage);
+//                     polls the next chunk's barriers before issuing, so the answer arrives behind
+//                     the MMAs
+//   epilogue          converter warps tcgen05.ld the accumulators after a pass: GeGLU (fused
+//                     gate/up) or plain store (down)
+// What was measured on the way here (B200, 1965 MHz): a register ring of global loads does not prefetch -
+// waiting for the oldest load also waits for the younger ones that share its scoreboard, so every chunk paid
+// a full memory latency (hence TMA); one mbarrier operation costs the issuing thread 100-190 cycles, so the
+// one-thread issuer carries as few of them as possible; a tcgen05.mma with N <= 128 costs about 100 cycles
+// whatever N, so the single-precision kernel puts the weights on N (256 per instruction).
 // Column order inside every group of 8 K columns is permuted to [0,4,1,5,2,6,3,7] in
 // BOTH operands (a contraction does not care): it is the order in which two masks
 // and one shift peel half2 pairs out of a packed 32-bit word.
