@@ -4,36 +4,41 @@
 // fp16), accumulation is fp32 in TMEM.  The bit-exact kernels in q4_kernels.cu
 // remain the reference-conformant path.
 //
-// Two precisions:
+// Two precisions (template SPLIT):
 //   single  one MMA per k-step, operands rounded to fp16 once: measured
 //           max |err| / max(|ref|, row rms) about 2e-3 (5e-4 of the row maximum)
-//           -> q4_gemm_tc_wide_kernel (tokens on M, 256 weight rows on N)
 //   split   every operand is carried as hi + lo fp16 halves (lo = fp16(v - hi)) and
-//           each k-step issues Ah*Bh + Al*Bh + Ah*Bl: operand error ~2^-22, three
+//           each k-step issues Xh*Wh + Xh*Wl + Xl*Wh: operand error ~2^-22, three
 //           times the tensor work
-//           -> q4_gemm_tc_kernel (128 weight rows on M, A operand in tensor memory)
 //
-// Common structure.  One block = one weight-row tile of one expert group and a run of its
-// 128-token passes.  K advances in 64-column chunks = one quantisation group per row.
+// One block = one tile of weight rows of one expert group and a run of its 128-token passes.
+// The tokens of a pass (up to 128, stale rows above them) are the MMA's M side, read from shared
+// memory as they arrive by TMA; 256 weight rows are the N side, dequantised into a K-major
+// 128-byte-swizzled shared-memory stage.  The 256 rows are one tile of the down matrix, or - fused -
+// 128 rows of gate followed by the same 128 rows of up: gate and up of a chunk are ONE instruction
+// (M128 x N256 x K16), and the GeGLU pairs accumulator column c with 128 + c.  Accumulators: lane =
+// token, column = weight row.  K advances in 64-column chunks = one quantisation group per row.
 //   producer thread   packed nibbles (tiled TMA over the expert pool: bytes x rows x experts),
 //                     the (scale << 16) | bias words of the rows (tiled TMA in blocks of four
 //                     chunks where a table row is a multiple of 16 bytes, otherwise one bulk copy
 //                     of the tile's whole table) and the tokens' fp16 activations (128-byte swizzle)
 //                     into a ring of input slots, several chunks ahead
-//   converter warps   two groups of eight warps on alternate chunks: shared memory -> registers ->
-//                     Q4 -> fp16 -> the MMA operand (tensor memory via tcgen05.st, or a K-major
-//                     128-byte-swizzled shared-memory stage); one mbarrier arrival per warp
+//   converter warps   two groups of eight warps on alternate chunks (thread = stage row): shared
+//                     memory -> registers -> Q4 -> fp16 -> the stage; one mbarrier arrival per warp
 //   issuer thread     tcgen05.mma.kind::f16 of every converted chunk, tcgen05.commit on the
 //                     chunk's "done" barrier (frees the input slot and, some chunks later, the stage);
 //                     polls the next chunk's barriers before issuing, so the answer arrives behind
 //                     the MMAs
-//   epilogue          converter warps tcgen05.ld the accumulators after a pass: GeGLU (fused
-//                     gate/up) or plain store (down)
+//   epilogue          all converter warps tcgen05.ld the accumulators after a pass (warp w: lane
+//                     quarter w % 4, a quarter of the columns): GeGLU (fused gate/up) or plain store (down)
 // What was measured on the way here (B200, 1965 MHz): a register ring of global loads does not prefetch -
 // waiting for the oldest load also waits for the younger ones that share its scoreboard, so every chunk paid
 // a full memory latency (hence TMA); one mbarrier operation costs the issuing thread 100-190 cycles, so the
-// one-thread issuer carries as few of them as possible; a tcgen05.mma with N <= 128 costs about 100 cycles
-// whatever N, so the single-precision kernel puts the weights on N (256 per instruction).
+// one-thread issuer carries as few of them as possible; a tcgen05.mma costs the issuing thread about 100
+// cycles for any N <= 128 (weights on M, in shared memory or dequantised straight into tensor memory with
+// tcgen05.st, 128 rows per instruction: both forms ran 8 such instructions per fused chunk), so the weights sit
+// on N, 256 rows per instruction.  What bounds this form is shared-memory traffic: about 110 KB per fused chunk
+// (stage written once and read once, token tile read by every instruction) against 128 bytes per cycle.
 // Column order inside every group of 8 K columns is permuted to [0,4,1,5,2,6,3,7] in
 // BOTH operands (a contraction does not care): it is the order in which two masks
 // and one shift peel half2 pairs out of a packed 32-bit word.
@@ -50,15 +55,13 @@
 
 namespace sb {
 
-constexpr int TC_STAGES = 4;             // most A stages (in tensor memory)
 constexpr int TC_GROUP = 256;                // converter threads of one chunk (two groups take alternate chunks)
 constexpr int TC_CONVERTERS = 2 * TC_GROUP;
 constexpr int TC_THREADS = TC_CONVERTERS + 64;   // + issuer warp + producer warp
 constexpr int TC_ISSUER_WARP = TC_CONVERTERS / 32, TC_PRODUCER_WARP = TC_ISSUER_WARP + 1;
 constexpr int TC_KC = 64;                    // K columns per chunk
-constexpr int TC_A_COLS = TC_KC / 2;        // 32-bit TMEM columns of one matrix' 128 x 64 fp16 tile
 constexpr uint32_t TC_TMEM_COLS = 512;
-constexpr int TC_PK_BYTES = 128 * TC_KC / 2; // its packed form
+constexpr int TC_PK_BYTES = 128 * TC_KC / 2; // packed chunk of 128 rows (one matrix' share of a fused stage)
 constexpr int TC_TAB_BYTES = 128 * 16;       // scale | bias words of 128 rows x 4 chunks
 constexpr int TC_MAX_NT = 128;
 constexpr int TC_MAX_SLOTS = 8;
@@ -76,18 +79,6 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d),
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-// The same with the A operand in tensor memory: row m of the 128 x 16 tile in lane m, two fp16 per
-// 32-bit column (8 columns per instruction, K order = column order).
-__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
-                                            uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(tmem_d),
-        "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 
@@ -236,370 +227,6 @@ __device__ __forceinline__ uint4 lds_v4(const uint8_t* p) {
     return v;
 }
 
-template <bool FUSED, bool SPLIT>
-__global__ void __launch_bounds__(TC_THREADS, 1)
-q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __grid_constant__ TcWeightMaps wm) {
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bar_in[TC_MAX_SLOTS];    // input slot landed (TMA transaction bytes)
-    __shared__ __align__(8) uint64_t bar_done[TC_MAX_SLOTS];  // the chunk's MMAs are complete (tcgen05.commit)
-    __shared__ __align__(8) uint64_t bar_full[TC_STAGES];     // stage converted (8 warp arrivals)
-    __shared__ __align__(8) uint64_t bar_acc;                 // a token pass' accumulators are final
-    __shared__ __align__(8) uint64_t bar_tab;                 // the tile's whole scale table landed (untiled form)
-    __shared__ __align__(8) uint64_t bar_epi;                 // a token pass' accumulators have been read (4 warp arrivals)
-    __shared__ uint32_t s_tmem;
-    __shared__ int s_fail;
-
-    const int job_id = blockIdx.y;
-    if (a.njobs_dev != nullptr && job_id >= *a.njobs_dev) return;
-    Q4Job jb = a.jobs[job_id];
-    const int r0 = blockIdx.x * 128;
-    if (r0 >= jb.R || jb.ntok < 1) return;
-    // token passes of a large group are spread over blockIdx.z: block z takes a contiguous run of
-    // passes, so an expert with several hundred tokens does not keep one SM busy while others idle
-    int pass_shift = 0;
-    if (gridDim.z > 1) {
-        const int npass_all = (jb.ntok + TC_MAX_NT - 1) / TC_MAX_NT;
-        const int per = (npass_all + (int)gridDim.z - 1) / (int)gridDim.z;
-        pass_shift = (int)blockIdx.z * per * TC_MAX_NT;
-        if (pass_shift >= jb.ntok) return;
-        jb.ntok = min(per * TC_MAX_NT, jb.ntok - pass_shift);
-    }
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int C = jb.C, nchunks = C / TC_KC;
-    const int g0 = (int)((jb.y - a.y_base) / a.y_cols) + pass_shift;   // first grouped row of this block's tokens
-    const int expert = (int)((size_t)(jb.vals - a.pool) / a.expert_stride);   // local expert = slice of the weight maps
-    constexpr int NMAT = FUSED ? 2 : 1;
-    constexpr int NPART = SPLIT ? 2 : 1;                     // hi (+ lo) copies of every operand tile
-    // tensor memory: accumulators of the NMAT matrices (128 columns each), then the A stages, each
-    // [matrix][hi, lo] tiles of 32 columns
-    constexpr int STAGES = (FUSED && SPLIT) ? 2 : TC_STAGES;
-    constexpr uint32_t ACC_COLS = NMAT * 128;
-    constexpr uint32_t STAGE_COLS = NMAT * NPART * TC_A_COLS;
-    static_assert(ACC_COLS + STAGES * STAGE_COLS <= TC_TMEM_COLS, "tensor memory budget");
-    const bool tab_tma = a.tab_tma != 0;
-    // B tile rows = smallest TMA box (16, 32, 64, 128 token rows) that holds a pass
-    const int ntok_cap = min(jb.ntok, TC_MAX_NT);
-    const int variant = ntok_cap <= 16 ? 0 : ntok_cap <= 32 ? 1 : ntok_cap <= 64 ? 2 : 3;
-    const uint32_t part_bytes = (16u << variant) * 128u;
-    // 1024-byte aligned carve-up: whole-tile table (untiled form) | ring of input slots, each
-    // [packed weights, NMAT x 4 KB][table block, NMAT x 2 KB (tiled form)][activation tile(s)]
-    uint8_t* tabw = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    const uint32_t tabm_bytes = tab_tma ? 0u : (uint32_t)(128 * nchunks * 4);
-    const uint32_t tabw_bytes = (NMAT * tabm_bytes + 1023u) & ~1023u;
-    uint8_t* in_base = tabw + tabw_bytes;
-    const uint32_t b_off = NMAT * (TC_PK_BYTES + (tab_tma ? TC_TAB_BYTES : 0));
-    const uint32_t slot_bytes = b_off + NPART * part_bytes;
-    const int avail = TC_SMEM_BYTES - 1024 - (int)tabw_bytes;
-    const uint32_t NQ = (uint32_t)min(TC_MAX_SLOTS, avail / (int)slot_bytes);
-    if ((int)NQ < STAGES) {                                   // the host checks the geometry; never expected
-        if (tid == 0 && a.status) atomicOr(a.status, SB_ERR_INDEX);
-        return;
-    }
-    const int npass = (jb.ntok + TC_MAX_NT - 1) / TC_MAX_NT;
-    volatile int* fail = &s_fail;
-
-    if (tid == 0) {
-        for (int s = 0; s < TC_MAX_SLOTS; s++) {
-            mbar_init(&bar_in[s], 1);
-            mbar_init(&bar_done[s], 1);
-        }
-        for (int s = 0; s < TC_STAGES; s++) mbar_init(&bar_full[s], TC_GROUP / 32);
-        mbar_init(&bar_acc, 1);
-        mbar_init(&bar_tab, 1);
-        mbar_init(&bar_epi, 4);
-        s_fail = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)),
-                     "r"(TC_TMEM_COLS)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem = s_tmem;
-
-    uint32_t it = 0;          // running chunk counter across token passes (every role counts the same chunks)
-    uint32_t p_issued = 0;    // producer: chunks requested
-    uint32_t i_committed = 0; // issuer: chunks committed
-
-    if (warp < TC_ISSUER_WARP) {
-        // ================= converters (and the epilogue of every pass on warps 0-3) =================
-        // Two groups of eight warps take alternate chunks, so one group's barrier round trips and
-        // tensor-memory stores overlap the other's arithmetic.
-        // One 32-element half of a 64-column chunk of one row, in every matrix, written straight into the
-        // A tile in tensor memory: row = TMEM lane (a warp reaches the lane quarter warp % 4), the half's 16
-        // half2 words = 16 columns.
-        const uint32_t grp = (uint32_t)warp >> 3;
-        const int crow = (warp & 3) * 32 + lane, chalf = (warp >> 2) & 1;
-        const uint32_t a_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + ACC_COLS + (uint32_t)chalf * 16;
-        const NibbleMagic mg = load_nibble_magic();
-        uint32_t cs = 0, cs_ph = 0;      // A stage and its parity
-        uint32_t cq = 0, cq_ph = 0;      // input slot and its parity
-        uint32_t dq = 0, dq_ph = 0;      // slot whose commit frees the A stage (chunk it - STAGES)
-        bool alive = tab_tma || __all_sync(0xffffffffu, mbar_wait(&bar_tab, 0, fail));   // the tile's whole table (untiled form)
-        for (int pass = 0; pass < npass && alive && !*fail; pass++) {
-            const int tb = pass * TC_MAX_NT;
-            const int nt_real = min(TC_MAX_NT, jb.ntok - tb);
-            const int NT = (nt_real + 15) & ~15;
-            for (int kc0 = 0; kc0 < nchunks; kc0 += 4) {
-                uint32_t tw[NMAT][4];       // table words of this thread's row for four chunks
-#pragma unroll
-                for (int d = 0; d < 4; d++) {
-                    const int kc = kc0 + d;
-                    if (kc >= nchunks) break;
-                    const uint32_t st = a_lane + cs * STAGE_COLS;
-                    const uint8_t* slot = in_base + cq * slot_bytes;
-                    const bool mine = (it & 1u) == grp;
-                    if (!tab_tma && d == 0) {
-#pragma unroll
-                        for (int m = 0; m < NMAT; m++)
-#pragma unroll
-                            for (int dd = 0; dd < 4; dd++)
-                                tw[m][dd] = kc0 + dd < nchunks
-                                                ? *(const uint32_t*)(tabw + m * tabm_bytes + (size_t)(crow * nchunks + kc0 + dd) * 4)
-                                                : 0u;
-                    }
-                    if (mine) {
-                        // the chunk's packed weights have landed, and the MMAs that last read this stage are complete
-                        bool ok = it < (uint32_t)STAGES ? mbar_wait(&bar_in[cq], cq_ph, fail)
-                                                        : mbar_wait2(&bar_in[cq], cq_ph, &bar_done[dq], dq_ph, fail);
-                        ok = __all_sync(0xffffffffu, ok);      // the tensor-memory stores below are warp-wide
-                        if (!ok) { alive = false; kc0 = nchunks; break; }   // the failure flag is up: every role leaves its loop
-                        if (tab_tma && d < 2) {
-                            // tiled form: the table block of these four chunks rides in the slots of the block's first two
-                            // chunks, one copy for each group (chunk and column parities agree: C is a multiple of 256)
-#pragma unroll
-                            for (int m = 0; m < NMAT; m++) {
-                                const uint4 t = lds_v4(slot + NMAT * TC_PK_BYTES + m * TC_TAB_BYTES + crow * 16);
-                                tw[m][0] = t.x; tw[m][1] = t.y; tw[m][2] = t.z; tw[m][3] = t.w;
-                            }
-                        }
-                        uint4 cur[NMAT];
-                        uint32_t cur_s[NMAT], cur_b[NMAT];
-#pragma unroll
-                        for (int m = 0; m < NMAT; m++) {
-                            cur[m] = lds_v4(slot + m * TC_PK_BYTES + crow * 32 + chalf * 16);
-                            cur_s[m] = tw[m][d] >> 16;
-                            cur_b[m] = tw[m][d] & 0xffffu;
-                        }
-                        // one decision for all matrices of the chunk: the conversions of gate and up then sit
-                        // in one basic block and interleave
-                        bool half_math = !SPLIT;
-#pragma unroll
-                        for (int m = 0; m < NMAT; m++) half_math = half_math && fp16_path_ok(cur_s[m], cur_b[m]);
-                        half_math = __all_sync(0xffffffffu, half_math);   // the stores below are warp-wide
-                        // the MMAs that read this stage last are complete (observed above): order the stores after them
-                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        if (half_math) {
-#pragma unroll
-                            for (int m = 0; m < NMAT; m++) {
-                                uint32_t o[16];
-                                dequant_half_chunk_f16(cur[m], cur_s[m], cur_b[m], o);
-                                tmem_st16(st + m * NPART * TC_A_COLS, o);
-                            }
-                        } else {
-#pragma unroll
-                            for (int m = 0; m < NMAT; m++) {
-                                uint32_t hi[16], lo[16];
-                                dequant_half_chunk_f32<SPLIT>(mg, cur[m], cur_s[m], cur_b[m], hi, lo);
-                                tmem_st16(st + m * NPART * TC_A_COLS, hi);
-                                if (SPLIT) tmem_st16(st + m * NPART * TC_A_COLS + TC_A_COLS, lo);
-                            }
-                        }
-                        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                        // tensor-memory stores -> ordered before the issuer's MMAs through the barrier, one arrival per warp
-                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&bar_full[cs]);
-                    }
-                    if (it >= (uint32_t)STAGES && ++dq == NQ) { dq = 0; dq_ph ^= 1u; }
-                    if (++cs == (uint32_t)STAGES) { cs = 0; cs_ph ^= 1u; }
-                    if (++cq == NQ) { cq = 0; cq_ph ^= 1u; }
-                    it++;
-                }
-            }
-            // ---- epilogue of this token pass (warps 0-3); the issuer starts the next pass' MMAs after their arrival
-            if (warp < 4 && __all_sync(0xffffffffu, mbar_wait(&bar_acc, pass & 1, fail))) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const int m = r0 + warp * 32 + lane;
-                const int mpos = (m & ~7) | tc_kpos(m & 7);      // GeGLU output feeds the next GEMM's K
-                const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
-                for (int n0 = 0; n0 < NT; n0 += 32) {
-                    uint32_t g[32];
-                    tmem_ld32(trow + n0, g);
-                    if (FUSED) {
-                        uint32_t u[32];
-                        tmem_ld32(trow + 128 + n0, u);
-#pragma unroll
-                        for (int i = 0; i < 32; i++) {
-                            const int n = n0 + i;
-                            if (n < nt_real && m < jb.R) {
-                                const float gv = __uint_as_float(g[i]), uv = __uint_as_float(u[i]);
-                                const float inner = 0.7978845608028654f * (gv + 0.044715f * gv * gv * gv);
-                                const float act = 0.5f * gv * (1.0f + tanhf(inner));
-                                const float o = act * uv;
-                                const __half oh = __float2half_rn(o);
-                                a.out_h[(size_t)(g0 + tb + n) * jb.R + mpos] = oh;
-                                if (SPLIT)
-                                    a.out_l[(size_t)(g0 + tb + n) * jb.R + mpos] = __float2half_rn(o - __half2float(oh));
-                            }
-                        }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; i++) {
-                            const int n = n0 + i;
-                            if (n < nt_real && m < jb.R) a.out_f[(size_t)(g0 + tb + n) * jb.R + m] = __uint_as_float(g[i]);
-                        }
-                    }
-                }
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bar_epi);
-            }
-        }
-    } else if (warp == TC_ISSUER_WARP) {
-        // ================= issuer (one thread) =================
-        // The loop is one thread's dependent instruction stream and every barrier operation in it costs a
-        // round trip: ring positions and parities are carried incrementally, and the next chunk's barriers
-        // are polled (without blocking) before this chunk's MMAs are issued, so the answer arrives behind them.
-        if (lane == 0) {
-            const uint32_t b_lo0 = DESC_B_LO | ((smem_u32(in_base + b_off) & 0x3ffffu) >> 4);
-            uint32_t is = 0, is_ph = 0, iq = 0, iq_ph = 0;
-            uint32_t ready = 0;
-            bool ok = true;
-            for (int pass = 0; pass < npass && ok && !*fail; pass++) {
-                const int nt_real = min(TC_MAX_NT, jb.ntok - pass * TC_MAX_NT);
-                const uint32_t idesc = umma_idesc_f16(128, (nt_real + 15) & ~15);
-                // the accumulators of the previous pass have been read
-                if (pass > 0 && !mbar_wait(&bar_epi, (pass - 1) & 1, fail)) break;
-                for (int kc = 0; kc < nchunks; kc++) {
-                    // the converted weights of the stage and the activation tile of the slot (the converters
-                    // waited for the same slot; the tensor core reads it through the async proxy, so the
-                    // issuing thread observes the barrier itself)
-                    if (!ready) ok = mbar_wait2(&bar_full[is], is_ph, &bar_in[iq], iq_ph, fail);
-                    if (!ok) break;
-                    uint32_t ns = is + 1, ns_ph = is_ph, nq = iq + 1, nq_ph = iq_ph;
-                    if (ns == (uint32_t)STAGES) { ns = 0; ns_ph ^= 1u; }
-                    if (nq == NQ) { nq = 0; nq_ph ^= 1u; }
-                    uint32_t r_full, r_in;
-                    asm volatile(
-                        "{\n\t.reg .pred p;\n\t"
-                        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                        "selp.u32 %0, 1, 0, p;\n\t}\n"
-                        : "=r"(r_full)
-                        : "r"(smem_u32(&bar_full[ns])), "r"(ns_ph)
-                        : "memory");
-                    asm volatile(
-                        "{\n\t.reg .pred p;\n\t"
-                        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                        "selp.u32 %0, 1, 0, p;\n\t}\n"
-                        : "=r"(r_in)
-                        : "r"(smem_u32(&bar_in[nq])), "r"(nq_ph)
-                        : "memory");
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a_st = tmem + ACC_COLS + is * STAGE_COLS;
-                    const uint32_t blo = b_lo0 + iq * (slot_bytes >> 4);
-                    const uint32_t blo_l = blo + (part_bytes >> 4);
-#pragma unroll
-                    for (int j = 0; j < TC_KC / 16; j++) {
-                        const uint64_t bh = make_desc(blo + j * 2, DESC_B_HI);
-                        const uint32_t acc = (kc > 0 || j > 0) ? 1u : 0u;
-#pragma unroll
-                        for (int m = 0; m < NMAT; m++) {
-                            const uint32_t ah = a_st + m * NPART * TC_A_COLS + j * 8;
-                            const uint32_t d = tmem + m * 128;
-                            umma_f16_ts(d, ah, bh, idesc, acc);
-                            if (SPLIT) {
-                                // A_lo * B_hi, then A_hi * B_lo
-                                umma_f16_ts(d, ah + TC_A_COLS, bh, idesc, 1u);
-                                umma_f16_ts(d, ah, make_desc(blo_l + j * 2, DESC_B_HI), idesc, 1u);
-                            }
-                        }
-                    }
-                    umma_commit(&bar_done[iq]);
-                    if (kc == nchunks - 1) umma_commit(&bar_acc);
-                    i_committed++;
-                    // the poll is only good inside a pass: the next pass' first MMAs also wait for the epilogue
-                    ready = (kc + 1 < nchunks) ? (r_full & r_in) : 0u;
-                    is = ns; is_ph = ns_ph; iq = nq; iq_ph = nq_ph;
-                }
-            }
-        }
-    } else if (lane == 0) {
-        // ================= producer (one thread) =================
-        // Packed weights (tiled TMA over the expert pool: bytes x rows x experts), the table block of four
-        // chunks (tiled form) and the tokens' fp16 activations (128-byte swizzle) of every chunk, NQ chunks ahead.
-        if (!tab_tma) {
-            const int rows_here = min(128, jb.R - r0);
-            const uint32_t bytes = (uint32_t)(rows_here * nchunks * 4);
-            mbar_expect_tx(&bar_tab, NMAT * bytes);
-#pragma unroll
-            for (int m = 0; m < NMAT; m++) {
-                const uint32_t* src = a.tables + ((size_t)(expert * 3 + a.tensor0 + m) * jb.R + r0) * nchunks;
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                                 smem_u32(tabw + m * tabm_bytes)),
-                             "l"(src), "r"(bytes), "r"(smem_u32(&bar_tab))
-                             : "memory");
-            }
-        }
-        uint32_t pq = 0, pq_ph = 0;
-        for (int pass = 0; pass < npass && !*fail; pass++) {
-            for (int kc = 0; kc < nchunks; kc++) {
-                // the slot's previous chunk has been consumed: its MMAs (which followed its conversion) are complete
-                if (p_issued >= NQ && !mbar_wait(&bar_done[pq], pq_ph ^ 1u, fail)) break;
-                const uint32_t dst = smem_u32(in_base + pq * slot_bytes);
-                const bool with_tab = tab_tma && (kc & 3) < 2;     // one copy for each converter group
-                mbar_expect_tx(&bar_in[pq], NMAT * (TC_PK_BYTES + (with_tab ? TC_TAB_BYTES : 0)) + NPART * part_bytes);
-#pragma unroll
-                for (int m = 0; m < NMAT; m++) {
-                    tma_load_3d(dst + m * TC_PK_BYTES, &wm.w[FUSED ? m : 2], kc * 32, r0, expert, &bar_in[pq]);
-                    if (with_tab)
-                        tma_load_3d(dst + NMAT * TC_PK_BYTES + m * TC_TAB_BYTES, &wm.t[FUSED ? m : 2], (kc & ~3) * 4, r0, expert,
-                                    &bar_in[pq]);
-                }
-                tma_load_2d(dst + b_off, &maps.hi[variant], kc * TC_KC, g0 + pass * TC_MAX_NT, &bar_in[pq]);
-                if (SPLIT)
-                    tma_load_2d(dst + b_off + part_bytes, &maps.lo[variant], kc * TC_KC, g0 + pass * TC_MAX_NT, &bar_in[pq]);
-                p_issued++;
-                if (++pq == NQ) { pq = 0; pq_ph ^= 1u; }
-            }
-        }
-    }
-    if (*fail) {
-        // wait (bounded, no early exit) for the copies and MMAs still in flight before shared memory and
-        // TMEM are released
-        int none = 0;
-        if (warp == TC_PRODUCER_WARP && lane == 0) {
-            if (!tab_tma) (void)mbar_wait(&bar_tab, 0, &none);
-            for (uint32_t t = (p_issued > NQ ? p_issued - NQ : 0); t < p_issued; t++)
-                (void)mbar_wait(&bar_in[t % NQ], (t / NQ) & 1, &none);
-        }
-        if (warp == TC_ISSUER_WARP && lane == 0 && i_committed > 0)
-            (void)mbar_wait(&bar_done[(i_committed - 1) % NQ], ((i_committed - 1) / NQ) & 1, &none);
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (tid == 0 && *fail && a.status) atomicOr(a.status, SB_ERR_TIMEOUT);
-    if (warp == 0) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_TMEM_COLS) : "memory");
-    }
-}
-
-// ---------------------------------------------------------------------------------------------
-// Single-precision form with the operands swapped: the tokens of a pass (up to 128, stale rows above
-// them) are the MMA's M side, read from shared memory as they arrive by TMA; 256 weight rows are the N
-// side, dequantised into a K-major 128-byte-swizzled shared-memory tile.  One instruction (M128 x N256 x
-// K16) then covers twice the weights of the 128-row form; an instruction with N <= 128 costs the issuing
-// thread about 100 cycles whatever N (measured), so the instruction count is what this form halves.
-// The 256 rows are one tile of the down matrix, or - fused - 128 rows of gate followed by the same 128 rows
-// of up: gate and up of a chunk are ONE instruction, and the GeGLU pairs accumulator column c with 128 + c.
-// Accumulators: lane = token, column = weight row.
-// Roles as in the kernel above: two converter groups of 256 threads (thread = stage row) on alternate
-// chunks, one issuing thread, one producing thread; all 16 converter warps share the epilogue (warp w: lane
-// quarter w % 4, a quarter of the columns).
 constexpr int TW_ROWS = 256;                        // rows of a converted stage
 constexpr int TW_PK_BYTES = TW_ROWS * TC_KC / 2;    // packed chunk
 constexpr int TW_TAB_BYTES = TW_ROWS * 16;          // table block (4 chunks)
@@ -607,9 +234,9 @@ constexpr int TW_B_BYTES = TW_ROWS * TC_KC * 2;     // converted chunk
 constexpr int TW_TOK_BYTES = TC_MAX_NT * TC_KC * 2; // token tile
 constexpr int TW_STAGES = 3;
 
-template <bool FUSED>
+template <bool FUSED, bool SPLIT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-q4_gemm_tc_wide_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __grid_constant__ TcWeightMaps wm) {
+q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __grid_constant__ TcWeightMaps wm) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_in[TC_MAX_SLOTS];    // input slot landed (TMA transaction bytes)
     __shared__ __align__(8) uint64_t bar_done[TC_MAX_SLOTS];  // the chunk's MMAs are complete (tcgen05.commit)
@@ -640,23 +267,25 @@ q4_gemm_tc_wide_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, cons
     const int g0 = (int)((jb.y - a.y_base) / a.y_cols) + pass_shift;   // first grouped row of this block's tokens
     const int expert = (int)((size_t)(jb.vals - a.pool) / a.expert_stride);
     const int rows_here = min(RT, jb.R - r0);                 // a multiple of 64
-    constexpr int STAGES = TW_STAGES;
+    constexpr int NPART = SPLIT ? 2 : 1;                     // hi (+ lo) copies of every operand tile
+    constexpr int STAGES = SPLIT ? 2 : TW_STAGES;
+    constexpr int STAGE_BYTES = NPART * TW_B_BYTES;          // [hi][lo] converted chunks
     const bool tab_tma = a.tab_tma != 0;
     const int ntok_cap = min(jb.ntok, TC_MAX_NT);
     const int variant = ntok_cap <= 16 ? 0 : ntok_cap <= 32 ? 1 : ntok_cap <= 64 ? 2 : 3;
     const uint32_t tok_bytes = (16u << variant) * 128u;
     // carve-up: converted stages | whole-tile table (untiled form) | input slots, each
-    // [packed weights, 8 KB][table block, 4 KB (tiled form)][token tile]
+    // [packed weights, 8 KB][table block, 4 KB (tiled form)][token tile(s): hi, lo]
     uint8_t* stage_base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const uint32_t tabw_bytes = tab_tma ? 0u : (((uint32_t)(TW_ROWS * nchunks * 4) + 1023u) & ~1023u);
-    uint8_t* tabw = stage_base + STAGES * TW_B_BYTES;
+    uint8_t* tabw = stage_base + STAGES * STAGE_BYTES;
     uint8_t* in_base = tabw + tabw_bytes;
     const uint32_t tok_off = TW_PK_BYTES + (tab_tma ? TW_TAB_BYTES : 0);
     // The MMA always reads 128 token rows: rows above the copied box are stale bytes of the next slot (or of
     // the pad behind the last one) and only reach accumulator lanes nobody reads.
     const uint32_t tok_room = (tok_bytes + 1023u) & ~1023u;
-    const uint32_t slot_bytes = tok_off + tok_room;
-    const int avail = TC_SMEM_BYTES - 1024 - STAGES * TW_B_BYTES - (int)tabw_bytes - (TW_TOK_BYTES - (int)tok_room);
+    const uint32_t slot_bytes = tok_off + NPART * tok_room;
+    const int avail = TC_SMEM_BYTES - 1024 - STAGES * STAGE_BYTES - (int)tabw_bytes - (TW_TOK_BYTES - (int)tok_room);
     const uint32_t NQ = (uint32_t)min(TC_MAX_SLOTS, avail / (int)slot_bytes);
     if ((int)NQ < STAGES) {                                   // the host checks the geometry; never expected
         if (tid == 0 && a.status) atomicOr(a.status, SB_ERR_INDEX);
@@ -710,7 +339,7 @@ q4_gemm_tc_wide_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, cons
                 for (int d = 0; d < 4; d++) {
                     const int kc = kc0 + d;
                     if (kc >= nchunks) break;
-                    uint8_t* st = stage_base + cs * TW_B_BYTES + b_off;
+                    uint8_t* st = stage_base + cs * STAGE_BYTES + b_off;
                     const uint8_t* slot = in_base + cq * slot_bytes;
                     const bool mine = (it & 1u) == grp;
                     if (!tab_tma && d == 0) {
@@ -731,17 +360,20 @@ q4_gemm_tc_wide_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, cons
                             tw[0] = t.x; tw[1] = t.y; tw[2] = t.z; tw[3] = t.w;
                         }
                         const uint32_t s_bits = tw[d] >> 16, b_bits = tw[d] & 0xffffu;
-                        const bool half_math = fp16_path_ok(s_bits, b_bits);
+                        const bool half_math = !SPLIT && fp16_path_ok(s_bits, b_bits);
 #pragma unroll
                         for (int h = 0; h < 2; h++) {
                             const uint4 pk = lds_v4(slot + crow * 32 + h * 16);
-                            uint32_t o[16], lo_unused[16];
+                            uint32_t o[16], lo[16];
                             if (half_math) dequant_half_chunk_f16(pk, s_bits, b_bits, o);
-                            else dequant_half_chunk_f32<false>(mg, pk, s_bits, b_bits, o, lo_unused);
+                            else dequant_half_chunk_f32<SPLIT>(mg, pk, s_bits, b_bits, o, lo);
 #pragma unroll
-                            for (int i = 0; i < 4; i++)
-                                *(uint4*)(st + ((((uint32_t)(h * 4 + i)) ^ b_sw) << 4)) =
-                                    make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                            for (int i = 0; i < 4; i++) {
+                                const uint32_t off = (((uint32_t)(h * 4 + i)) ^ b_sw) << 4;
+                                *(uint4*)(st + off) = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                                if (SPLIT)
+                                    *(uint4*)(st + TW_B_BYTES + off) = make_uint4(lo[4 * i], lo[4 * i + 1], lo[4 * i + 2], lo[4 * i + 3]);
+                            }
                         }
                         // generic-proxy writes -> visible to the tensor core (async proxy), then one arrival per warp
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -768,7 +400,8 @@ q4_gemm_tc_wide_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, cons
                             tmem_ld32(trow + col, g);
                             tmem_ld32(trow + RT + col, u);
                             if (n < nt_real) {
-                                __half* dst = a.out_h + (size_t)(g0 + tb + n) * jb.R + r0 + col;
+                                const size_t o_off = (size_t)(g0 + tb + n) * jb.R + r0 + col;
+                                __half* dst = a.out_h + o_off;
 #pragma unroll
                                 for (int i8 = 0; i8 < 32; i8 += 8) {
                                     float o[8];
@@ -779,8 +412,17 @@ q4_gemm_tc_wide_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, cons
                                         o[i] = 0.5f * gv * (1.0f + tanhf(inner)) * uv;
                                     }
                                     // the next GEMM's K order inside a group of 8: [0,4,1,5,2,6,3,7]
-                                    *(uint4*)(dst + i8) = make_uint4(f16x2_from(o[0], o[4]), f16x2_from(o[1], o[5]),
-                                                                     f16x2_from(o[2], o[6]), f16x2_from(o[3], o[7]));
+                                    const uint4 hv = make_uint4(f16x2_from(o[0], o[4]), f16x2_from(o[1], o[5]),
+                                                                f16x2_from(o[2], o[6]), f16x2_from(o[3], o[7]));
+                                    *(uint4*)(dst + i8) = hv;
+                                    if (SPLIT) {
+                                        const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
+                                        uint32_t lw[4];
+#pragma unroll
+                                        for (int kk = 0; kk < 4; kk++)
+                                            lw[kk] = f16x2_from(o[kk] - f16_lo_to_f32(hw[kk]), o[kk + 4] - f16_hi_to_f32(hw[kk]));
+                                        *(uint4*)(a.out_l + o_off + i8) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+                                    }
                                 }
                             }
                         }
@@ -843,12 +485,18 @@ q4_gemm_tc_wide_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, cons
                         : "r"(smem_u32(&bar_in[nq])), "r"(nq_ph)
                         : "memory");
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t wlo = w_lo0 + is * (TW_B_BYTES >> 4);
+                    const uint32_t wlo = w_lo0 + is * (STAGE_BYTES >> 4);
                     const uint32_t tlo = t_lo0 + iq * (slot_bytes >> 4);
 #pragma unroll
-                    for (int j = 0; j < TC_KC / 16; j++)
-                        umma_f16(tmem, make_desc(tlo + j * 2, DESC_B_HI), make_desc(wlo + j * 2, DESC_B_HI), idesc,
-                                 (kc > 0 || j > 0) ? 1u : 0u);
+                    for (int j = 0; j < TC_KC / 16; j++) {
+                        const uint64_t th = make_desc(tlo + j * 2, DESC_B_HI), wh = make_desc(wlo + j * 2, DESC_B_HI);
+                        umma_f16(tmem, th, wh, idesc, (kc > 0 || j > 0) ? 1u : 0u);
+                        if (SPLIT) {
+                            // x_hi * w_lo, then x_lo * w_hi
+                            umma_f16(tmem, th, make_desc(wlo + (TW_B_BYTES >> 4) + j * 2, DESC_B_HI), idesc, 1u);
+                            umma_f16(tmem, make_desc(tlo + (tok_room >> 4) + j * 2, DESC_B_HI), wh, idesc, 1u);
+                        }
+                    }
                     umma_commit(&bar_done[iq]);
                     if (kc == nchunks - 1) umma_commit(&bar_acc);
                     i_committed++;
@@ -879,7 +527,7 @@ q4_gemm_tc_wide_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, cons
                 if (p_issued >= NQ && !mbar_wait(&bar_done[pq], pq_ph ^ 1u, fail)) break;
                 const uint32_t dst = smem_u32(in_base + pq * slot_bytes);
                 const bool with_tab = tab_tma && (kc & 3) < 2;     // one copy for each converter group
-                mbar_expect_tx(&bar_in[pq], TW_PK_BYTES + (with_tab ? TW_TAB_BYTES : 0) + tok_bytes);
+                mbar_expect_tx(&bar_in[pq], TW_PK_BYTES + (with_tab ? TW_TAB_BYTES : 0) + NPART * tok_bytes);
                 if (FUSED) {
                     // 128 rows of gate, then the same 128 rows of up
 #pragma unroll
@@ -893,6 +541,8 @@ q4_gemm_tc_wide_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, cons
                     if (with_tab) tma_load_3d(dst + TW_PK_BYTES, &wm.t256[2], (kc & ~3) * 4, r0, expert, &bar_in[pq]);
                 }
                 tma_load_2d(dst + tok_off, &maps.hi[variant], kc * TC_KC, g0 + pass * TC_MAX_NT, &bar_in[pq]);
+                if (SPLIT)
+                    tma_load_2d(dst + tok_off + tok_room, &maps.lo[variant], kc * TC_KC, g0 + pass * TC_MAX_NT, &bar_in[pq]);
                 p_issued++;
                 if (++pq == NQ) { pq = 0; pq_ph ^= 1u; }
             }
@@ -1060,48 +710,25 @@ cudaError_t make_q4_tc_weight_maps(TcWeightMaps* out, const uint8_t* pool, size_
 }
 
 // Does the kernel's shared-memory carve-up hold at least as many input slots as stages for a tensor with C
-// columns, in the widest token tile?  (The untiled table form keeps 128 rows x C/64 words per matrix resident.)
-static bool tc_geometry_ok(int C, bool fused, bool split) {
-    const int nmat = fused ? 2 : 1, npart = split ? 2 : 1;
-    const int stages = (fused && split) ? 2 : TC_STAGES;
-    const bool tab_tma = (C % 256) == 0;
-    const int tabw = tab_tma ? 0 : ((nmat * 128 * (C / TC_KC) * 4 + 1023) & ~1023);
-    const int slot = nmat * (TC_PK_BYTES + (tab_tma ? TC_TAB_BYTES : 0)) + npart * TC_MAX_NT * 128;
-    const int avail = TC_SMEM_BYTES - 1024 - tabw;
-    return avail / slot >= stages;
-}
-
-// The same for the wide single-precision kernel (widest token tile).
-static bool tc_wide_geometry_ok(int C) {
+// columns, in the widest token tile?  (The untiled table form keeps 256 rows x C/64 words resident.)
+static bool tc_geometry_ok(int C, bool split) {
+    const int npart = split ? 2 : 1, stages = split ? 2 : TW_STAGES;
     const bool tab_tma = (C % 256) == 0;
     const int tabw = tab_tma ? 0 : ((TW_ROWS * (C / TC_KC) * 4 + 1023) & ~1023);
-    const int slot = TW_PK_BYTES + (tab_tma ? TW_TAB_BYTES : 0) + TW_TOK_BYTES;
-    const int avail = TC_SMEM_BYTES - 1024 - TW_STAGES * TW_B_BYTES - tabw;
-    return avail / slot >= TW_STAGES;
+    const int slot = TW_PK_BYTES + (tab_tma ? TW_TAB_BYTES : 0) + npart * TW_TOK_BYTES;
+    const int avail = TC_SMEM_BYTES - 1024 - stages * npart * TW_B_BYTES - tabw;
+    return avail / slot >= stages;
 }
 
 bool q4_tc_supported(int hidden, int inter) {
     if (hidden < TC_KC || inter < TC_KC || (hidden % TC_KC) || (inter % TC_KC)) return false;
-    return tc_geometry_ok(hidden, true, false) && tc_geometry_ok(hidden, true, true) &&
-           tc_geometry_ok(inter, false, false) && tc_geometry_ok(inter, false, true) &&
-           tc_wide_geometry_ok(hidden) && tc_wide_geometry_ok(inter);
-}
-
-template <bool FUSED>
-static cudaError_t launch_tc_wide(const TcArgs& a, const TcMaps& maps, const TcWeightMaps& wm, dim3 grid,
-                                  cudaStream_t stream) {
-    {
-        cudaError_t e = ensure_dynamic_smem((const void*)q4_gemm_tc_wide_kernel<FUSED>, (size_t)TC_SMEM_BYTES);
-        if (e != cudaSuccess) return e;
-    }
-    q4_gemm_tc_wide_kernel<FUSED><<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(a, maps, wm);
-    return cudaGetLastError();
+    return tc_geometry_ok(hidden, false) && tc_geometry_ok(inter, false) &&
+           tc_geometry_ok(hidden, true) && tc_geometry_ok(inter, true);
 }
 
 template <bool FUSED, bool SPLIT>
 static cudaError_t launch_tc(const TcArgs& a, const TcMaps& maps, const TcWeightMaps& wm, dim3 grid,
-                             cudaStream_t stream) {
-    // the full dynamic shared memory keeps one block per SM: a block allocates all 512 TMEM columns
+                                  cudaStream_t stream) {
     {
         cudaError_t e = ensure_dynamic_smem((const void*)q4_gemm_tc_kernel<FUSED, SPLIT>, (size_t)TC_SMEM_BYTES);
         if (e != cudaSuccess) return e;
@@ -1128,12 +755,11 @@ cudaError_t launch_q4_gemm_tc(bool fused, bool split, const Q4Job* jobs, int njo
         const int avg = rows_total / njobs_max;
         grid.z = fused ? (avg >= 96 ? 4u : (avg >= 24 ? 2u : 1u)) : 1u;
     }
-    if (!split) {
-        // single precision: 256 weight rows (128 of gate + 128 of up when fused) on the MMA's N side
-        if (!fused) grid.x = (R + TW_ROWS - 1) / TW_ROWS;
-        return fused ? launch_tc_wide<true>(a, bmaps, wm, grid, stream) : launch_tc_wide<false>(a, bmaps, wm, grid, stream);
-    }
-    return fused ? launch_tc<true, true>(a, bmaps, wm, grid, stream) : launch_tc<false, true>(a, bmaps, wm, grid, stream);
+    // 256 weight rows (128 of gate + 128 of up when fused) on the MMA's N side
+    if (!fused) grid.x = (R + TW_ROWS - 1) / TW_ROWS;
+    if (fused)
+        return split ? launch_tc<true, true>(a, bmaps, wm, grid, stream) : launch_tc<true, false>(a, bmaps, wm, grid, stream);
+    return split ? launch_tc<false, true>(a, bmaps, wm, grid, stream) : launch_tc<false, false>(a, bmaps, wm, grid, stream);
 }
 
 }  // namespace sb
