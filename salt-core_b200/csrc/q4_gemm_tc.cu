@@ -48,6 +48,7 @@
 #include <cuda_fp16.h>
 
 #include <stdlib.h>
+#include <algorithm>
 #include "internal.h"
 #include "mbar.cuh"
 #include "umma.cuh"
@@ -186,6 +187,7 @@ struct TcArgs {
     const uint32_t* tables;    // (scale << 16) | bias words, [local expert][3 tensors][R * C/64]
     int tensor0;               // first tensor of the slot this launch reads (0: gate, then up; 2: down)
     int tab_tma;               // table rows are a multiple of 16 bytes: blocks of 4 groups come by tiled TMA
+    int tiles_per_block;       // consecutive row tiles one block walks (its pipeline runs on across them)
 };
 
 // Bounded wait for two barriers at once: both polls are in flight together, so the pair costs one
@@ -233,6 +235,10 @@ constexpr int TW_TAB_BYTES = TW_ROWS * 16;          // table block (4 chunks)
 constexpr int TW_B_BYTES = TW_ROWS * TC_KC * 2;     // converted chunk
 constexpr int TW_TOK_BYTES = TC_MAX_NT * TC_KC * 2; // token tile
 constexpr int TW_STAGES = 3;
+// Row tiles one block walks: its pipeline runs on across tiles (no prologue, no empty ring at a tile's start).
+// Measured at B = 512 / 2048: two tiles gain 3-4 % (gate|up) and 10 % / 0 % (down); six tiles lose 30 % at B = 2048
+// (too few blocks to balance experts of unequal size).
+constexpr int TW_TILES_PER_BLOCK = 2;
 
 template <bool FUSED, bool SPLIT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -241,9 +247,11 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
     __shared__ __align__(8) uint64_t bar_in[TC_MAX_SLOTS];    // input slot landed (TMA transaction bytes)
     __shared__ __align__(8) uint64_t bar_done[TC_MAX_SLOTS];  // the chunk's MMAs are complete (tcgen05.commit)
     __shared__ __align__(8) uint64_t bar_full[TW_STAGES];     // stage converted (8 warp arrivals)
-    __shared__ __align__(8) uint64_t bar_acc;                 // a token pass' accumulators are final
-    __shared__ __align__(8) uint64_t bar_tab;                 // the tile's whole scale table landed (untiled form)
-    __shared__ __align__(8) uint64_t bar_epi;                 // a token pass' accumulators have been read (16 warp arrivals)
+    // A unit = one token pass of one row tile.  Accumulators are double-buffered by unit parity (256 columns each).
+    __shared__ __align__(8) uint64_t bar_acc[2];              // a unit's accumulators are final
+    __shared__ __align__(8) uint64_t bar_epi[2];              // ... and have been read (16 warp arrivals)
+    __shared__ __align__(8) uint64_t bar_tab[2];              // a tile's whole scale table landed (untiled form)
+    __shared__ __align__(8) uint64_t bar_tabfree[2];          // ... and its last conversion is over (16 warp arrivals)
     __shared__ uint32_t s_tmem;
     __shared__ int s_fail;
 
@@ -252,8 +260,9 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
     const int job_id = blockIdx.y;
     if (a.njobs_dev != nullptr && job_id >= *a.njobs_dev) return;
     Q4Job jb = a.jobs[job_id];
-    const int r0 = blockIdx.x * RT;
-    if (r0 >= jb.R || jb.ntok < 1) return;
+    const int x0 = (int)blockIdx.x * a.tiles_per_block;          // first row tile of this block
+    if (x0 * RT >= jb.R || jb.ntok < 1) return;
+    const int ntiles = min(a.tiles_per_block, (jb.R - x0 * RT + RT - 1) / RT);
     int pass_shift = 0;
     if (gridDim.z > 1) {
         const int npass_all = (jb.ntok + TC_MAX_NT - 1) / TC_MAX_NT;
@@ -266,7 +275,6 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
     const int C = jb.C, nchunks = C / TC_KC;
     const int g0 = (int)((jb.y - a.y_base) / a.y_cols) + pass_shift;   // first grouped row of this block's tokens
     const int expert = (int)((size_t)(jb.vals - a.pool) / a.expert_stride);
-    const int rows_here = min(RT, jb.R - r0);                 // a multiple of 64
     constexpr int NPART = SPLIT ? 2 : 1;                     // hi (+ lo) copies of every operand tile
     constexpr int STAGES = SPLIT ? 2 : TW_STAGES;
     constexpr int STAGE_BYTES = NPART * TW_B_BYTES;          // [hi][lo] converted chunks
@@ -277,15 +285,18 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
     // carve-up: converted stages | whole-tile table (untiled form) | input slots, each
     // [packed weights, 8 KB][table block, 4 KB (tiled form)][token tile(s): hi, lo]
     uint8_t* stage_base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    // untiled tables: two buffers, so the next tile's table lands while this one is in use (split precision has
+    // room for one: the producer then waits for the tile's last conversion)
+    constexpr uint32_t TABBUF = SPLIT ? 1 : 2;
     const uint32_t tabw_bytes = tab_tma ? 0u : (((uint32_t)(TW_ROWS * nchunks * 4) + 1023u) & ~1023u);
     uint8_t* tabw = stage_base + STAGES * STAGE_BYTES;
-    uint8_t* in_base = tabw + tabw_bytes;
+    uint8_t* in_base = tabw + TABBUF * tabw_bytes;
     const uint32_t tok_off = TW_PK_BYTES + (tab_tma ? TW_TAB_BYTES : 0);
     // The MMA always reads 128 token rows: rows above the copied box are stale bytes of the next slot (or of
     // the pad behind the last one) and only reach accumulator lanes nobody reads.
     const uint32_t tok_room = (tok_bytes + 1023u) & ~1023u;
     const uint32_t slot_bytes = tok_off + NPART * tok_room;
-    const int avail = TC_SMEM_BYTES - 1024 - STAGES * STAGE_BYTES - (int)tabw_bytes - (TW_TOK_BYTES - (int)tok_room);
+    const int avail = TC_SMEM_BYTES - 1024 - STAGES * STAGE_BYTES - (int)(TABBUF * tabw_bytes) - (TW_TOK_BYTES - (int)tok_room);
     const uint32_t NQ = (uint32_t)min(TC_MAX_SLOTS, avail / (int)slot_bytes);
     if ((int)NQ < STAGES) {                                   // the host checks the geometry; never expected
         if (tid == 0 && a.status) atomicOr(a.status, SB_ERR_INDEX);
@@ -300,9 +311,12 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
             mbar_init(&bar_done[s], 1);
         }
         for (int s = 0; s < TW_STAGES; s++) mbar_init(&bar_full[s], TC_GROUP / 32);
-        mbar_init(&bar_acc, 1);
-        mbar_init(&bar_tab, 1);
-        mbar_init(&bar_epi, TC_CONVERTERS / 32);
+        for (int s = 0; s < 2; s++) {
+            mbar_init(&bar_acc[s], 1);
+            mbar_init(&bar_epi[s], TC_CONVERTERS / 32);
+            mbar_init(&bar_tab[s], 1);
+            mbar_init(&bar_tabfree[s], TC_CONVERTERS / 32);
+        }
         s_fail = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -320,6 +334,7 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
     uint32_t it = 0;          // running chunk counter across token passes (every role counts the same chunks)
     uint32_t p_issued = 0;    // producer: chunks requested
     uint32_t i_committed = 0; // issuer: chunks committed
+    uint32_t p_tabs = 0;      // producer: whole-tile table copies requested
 
     if (warp < TC_ISSUER_WARP) {
         // ================= converters, then the epilogue of every pass =================
@@ -329,8 +344,14 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
         const uint32_t b_sw = (uint32_t)crow & 7;
         const NibbleMagic mg = load_nibble_magic();
         uint32_t cs = 0, cq = 0, cq_ph = 0, dq = 0, dq_ph = 0;
-        bool alive = tab_tma || __all_sync(0xffffffffu, mbar_wait(&bar_tab, 0, fail));
-        for (int pass = 0; pass < npass && alive && !*fail; pass++) {
+        bool alive = true;
+        uint32_t unit = 0;
+        for (int tix = 0; tix < ntiles && alive && !*fail; tix++) {
+        const int r0 = (x0 + tix) * RT, rows_here = min(RT, jb.R - r0);   // rows_here: a multiple of 64
+        const uint32_t tbuf = (uint32_t)tix % TABBUF;
+        const uint8_t* tabt = tabw + tbuf * tabw_bytes;
+        if (!tab_tma) alive = __all_sync(0xffffffffu, mbar_wait(&bar_tab[tbuf], ((uint32_t)tix / TABBUF) & 1u, fail));
+        for (int pass = 0; pass < npass && alive && !*fail; pass++, unit++) {
             const int tb = pass * TC_MAX_NT;
             const int nt_real = min(TC_MAX_NT, jb.ntok - tb);
             for (int kc0 = 0; kc0 < nchunks; kc0 += 4) {
@@ -345,7 +366,7 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
                     if (!tab_tma && d == 0) {
 #pragma unroll
                         for (int dd = 0; dd < 4; dd++)
-                            tw[dd] = kc0 + dd < nchunks ? *(const uint32_t*)(tabw + (size_t)(crow * nchunks + kc0 + dd) * 4) : 0u;
+                            tw[dd] = kc0 + dd < nchunks ? *(const uint32_t*)(tabt + (size_t)(crow * nchunks + kc0 + dd) * 4) : 0u;
                     }
                     if (mine) {
                         // the chunk's packed weights have landed, and the MMAs that last read this stage are complete
@@ -387,11 +408,15 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
                 }
             }
             // ---- epilogue of this pass: warp w reads lane quarter w % 4 (tokens) and a quarter of the columns
-            if (alive && __all_sync(0xffffffffu, mbar_wait(&bar_acc, pass & 1, fail))) {
+            if (!tab_tma && pass == npass - 1 && alive) {             // this tile's table is no longer read
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_tabfree[tbuf]);
+            }
+            if (alive && __all_sync(0xffffffffu, mbar_wait(&bar_acc[unit & 1u], (unit >> 1) & 1u, fail))) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const int q = warp & 3;
                 const int n = q * 32 + lane;                        // token of the pass
-                const uint32_t trow = tmem + ((uint32_t)(q * 32) << 16);
+                const uint32_t trow = tmem + ((uint32_t)(q * 32) << 16) + (unit & 1u) * TW_ROWS;
                 if (q * 32 < nt_real) {                             // warp-uniform: the quarter holds tokens
                     if (FUSED) {
                         const int col = (warp >> 2) * 32;           // output columns col ... col + 31 of the tile
@@ -445,21 +470,24 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&bar_epi);
+                if (lane == 0) mbar_arrive(&bar_epi[unit & 1u]);
             }
+        }
         }
     } else if (warp == TC_ISSUER_WARP) {
         // ================= issuer (one thread) =================
         if (lane == 0) {
             const uint32_t w_lo0 = DESC_B_LO | ((smem_u32(stage_base) & 0x3ffffu) >> 4);
             const uint32_t t_lo0 = DESC_B_LO | ((smem_u32(in_base + tok_off) & 0x3ffffu) >> 4);
-            const uint32_t idesc = umma_idesc_f16(128, FUSED ? TW_ROWS : rows_here);
             uint32_t is = 0, is_ph = 0, iq = 0, iq_ph = 0;
-            uint32_t ready = 0;
+            uint32_t ready = 0, unit = 0;
             bool ok = true;
-            for (int pass = 0; pass < npass && ok && !*fail; pass++) {
-                // the accumulators of the previous pass have been read
-                if (pass > 0 && !mbar_wait(&bar_epi, (pass - 1) & 1, fail)) break;
+            for (int tix = 0; tix < ntiles && ok && !*fail; tix++) {
+            const uint32_t idesc = umma_idesc_f16(128, FUSED ? TW_ROWS : min(RT, jb.R - (x0 + tix) * RT));
+            for (int pass = 0; pass < npass && ok && !*fail; pass++, unit++) {
+                // this unit's accumulator buffer was last used two units ago: those accumulators have been read
+                if (unit >= 2 && !mbar_wait(&bar_epi[unit & 1u], ((unit >> 1) - 1) & 1u, fail)) { ok = false; break; }
+                const uint32_t acc_base = tmem + (unit & 1u) * TW_ROWS;
                 for (int kc = 0; kc < nchunks; kc++) {
                     // the converted weights of the stage, and the chunk's token tile: the tensor core reads it
                     // through the async proxy, so the issuing thread observes that barrier itself
@@ -490,41 +518,48 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
 #pragma unroll
                     for (int j = 0; j < TC_KC / 16; j++) {
                         const uint64_t th = make_desc(tlo + j * 2, DESC_B_HI), wh = make_desc(wlo + j * 2, DESC_B_HI);
-                        umma_f16(tmem, th, wh, idesc, (kc > 0 || j > 0) ? 1u : 0u);
+                        umma_f16(acc_base, th, wh, idesc, (kc > 0 || j > 0) ? 1u : 0u);
                         if (SPLIT) {
                             // x_hi * w_lo, then x_lo * w_hi
-                            umma_f16(tmem, th, make_desc(wlo + (TW_B_BYTES >> 4) + j * 2, DESC_B_HI), idesc, 1u);
-                            umma_f16(tmem, make_desc(tlo + (tok_room >> 4) + j * 2, DESC_B_HI), wh, idesc, 1u);
+                            umma_f16(acc_base, th, make_desc(wlo + (TW_B_BYTES >> 4) + j * 2, DESC_B_HI), idesc, 1u);
+                            umma_f16(acc_base, make_desc(tlo + (tok_room >> 4) + j * 2, DESC_B_HI), wh, idesc, 1u);
                         }
                     }
                     umma_commit(&bar_done[iq]);
-                    if (kc == nchunks - 1) umma_commit(&bar_acc);
+                    if (kc == nchunks - 1) umma_commit(&bar_acc[unit & 1u]);
                     i_committed++;
-                    // a poll is only good inside a pass: the next pass' first MMAs also wait for the epilogue
-                    ready = (kc + 1 < nchunks) ? (r_full & r_in) : 0u;
+                    ready = r_full & r_in;
                     is = ns; is_ph = ns_ph; iq = nq; iq_ph = nq_ph;
                 }
+            }
             }
         }
     } else if (lane == 0) {
         // ================= producer (one thread) =================
+        uint32_t pq = 0, pq_ph = 0;
+        bool pok = true;
+        for (int tix = 0; tix < ntiles && pok && !*fail; tix++) {
+        const int r0 = (x0 + tix) * RT;
         if (!tab_tma) {
-            const uint32_t bytes = (uint32_t)(rows_here * nchunks * 4);
-            mbar_expect_tx(&bar_tab, NMAT * bytes);
+            // the tile's whole table, into the buffer whose previous tile has been converted to the end
+            const uint32_t tbuf = (uint32_t)tix % TABBUF, round = (uint32_t)tix / TABBUF;
+            if (round > 0 && !mbar_wait(&bar_tabfree[tbuf], (round - 1) & 1u, fail)) break;
+            const uint32_t bytes = (uint32_t)(min(RT, jb.R - r0) * nchunks * 4);
+            mbar_expect_tx(&bar_tab[tbuf], NMAT * bytes);
+            p_tabs++;
 #pragma unroll
             for (int m = 0; m < NMAT; m++) {
                 const uint32_t* src = a.tables + ((size_t)(expert * 3 + a.tensor0 + m) * jb.R + r0) * nchunks;
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                                 smem_u32(tabw + (size_t)m * RT * nchunks * 4)),
-                             "l"(src), "r"(bytes), "r"(smem_u32(&bar_tab))
+                                 smem_u32(tabw + tbuf * tabw_bytes + (size_t)m * RT * nchunks * 4)),
+                             "l"(src), "r"(bytes), "r"(smem_u32(&bar_tab[tbuf]))
                              : "memory");
             }
         }
-        uint32_t pq = 0, pq_ph = 0;
-        for (int pass = 0; pass < npass && !*fail; pass++) {
+        for (int pass = 0; pass < npass && pok && !*fail; pass++) {
             for (int kc = 0; kc < nchunks; kc++) {
                 // the slot's previous chunk has been consumed: its MMAs (which followed its conversion) are complete
-                if (p_issued >= NQ && !mbar_wait(&bar_done[pq], pq_ph ^ 1u, fail)) break;
+                if (p_issued >= NQ && !mbar_wait(&bar_done[pq], pq_ph ^ 1u, fail)) { pok = false; break; }
                 const uint32_t dst = smem_u32(in_base + pq * slot_bytes);
                 const bool with_tab = tab_tma && (kc & 3) < 2;     // one copy for each converter group
                 mbar_expect_tx(&bar_in[pq], TW_PK_BYTES + (with_tab ? TW_TAB_BYTES : 0) + NPART * tok_bytes);
@@ -547,13 +582,17 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
                 if (++pq == NQ) { pq = 0; pq_ph ^= 1u; }
             }
         }
+        }
     }
     if (*fail) {
         // wait (bounded, no early exit) for the copies and MMAs still in flight before shared memory and
         // TMEM are released
         int none = 0;
         if (warp == TC_PRODUCER_WARP && lane == 0) {
-            if (!tab_tma) (void)mbar_wait(&bar_tab, 0, &none);
+            if (p_tabs > 0) {       // the last table copy requested
+                const uint32_t t = p_tabs - 1;
+                (void)mbar_wait(&bar_tab[t % TABBUF], (t / TABBUF) & 1u, &none);
+            }
             for (uint32_t t = (p_issued > NQ ? p_issued - NQ : 0); t < p_issued; t++)
                 (void)mbar_wait(&bar_in[t % NQ], (t / NQ) & 1, &none);
         }
@@ -714,7 +753,7 @@ cudaError_t make_q4_tc_weight_maps(TcWeightMaps* out, const uint8_t* pool, size_
 static bool tc_geometry_ok(int C, bool split) {
     const int npart = split ? 2 : 1, stages = split ? 2 : TW_STAGES;
     const bool tab_tma = (C % 256) == 0;
-    const int tabw = tab_tma ? 0 : ((TW_ROWS * (C / TC_KC) * 4 + 1023) & ~1023);
+    const int tabw = tab_tma ? 0 : (split ? 1 : 2) * ((TW_ROWS * (C / TC_KC) * 4 + 1023) & ~1023);
     const int slot = TW_PK_BYTES + (tab_tma ? TW_TAB_BYTES : 0) + npart * TW_TOK_BYTES;
     const int avail = TC_SMEM_BYTES - 1024 - stages * npart * TW_B_BYTES - tabw;
     return avail / slot >= stages;
@@ -755,8 +794,11 @@ cudaError_t launch_q4_gemm_tc(bool fused, bool split, const Q4Job* jobs, int njo
         const int avg = rows_total / njobs_max;
         grid.z = fused ? (avg >= 96 ? 4u : (avg >= 24 ? 2u : 1u)) : 1u;
     }
-    // 256 weight rows (128 of gate + 128 of up when fused) on the MMA's N side
-    if (!fused) grid.x = (R + TW_ROWS - 1) / TW_ROWS;
+    // 256 weight rows (128 of gate + 128 of up when fused) on the MMA's N side; a block walks tiles_per_block
+    // consecutive row tiles
+    const int nx = fused ? (R + 127) / 128 : (R + TW_ROWS - 1) / TW_ROWS;
+    a.tiles_per_block = std::min(nx, TW_TILES_PER_BLOCK);
+    grid.x = (nx + a.tiles_per_block - 1) / a.tiles_per_block;
     if (fused)
         return split ? launch_tc<true, true>(a, bmaps, wm, grid, stream) : launch_tc<true, false>(a, bmaps, wm, grid, stream);
     return split ? launch_tc<false, true>(a, bmaps, wm, grid, stream) : launch_tc<false, false>(a, bmaps, wm, grid, stream);
