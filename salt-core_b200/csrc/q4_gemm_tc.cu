@@ -235,10 +235,11 @@ constexpr int TW_TAB_BYTES = TW_ROWS * 16;          // table block (4 chunks)
 constexpr int TW_B_BYTES = TW_ROWS * TC_KC * 2;     // converted chunk
 constexpr int TW_TOK_BYTES = TC_MAX_NT * TC_KC * 2; // token tile
 constexpr int TW_STAGES = 3;
-// Row tiles one block walks: its pipeline runs on across tiles (no prologue, no empty ring at a tile's start).
-// Measured at B = 512 / 2048: two tiles gain 3-4 % (gate|up) and 10 % / 0 % (down); six tiles lose 30 % at B = 2048
-// (too few blocks to balance experts of unequal size).
-constexpr int TW_TILES_PER_BLOCK = 2;
+// Row tiles one block walks with its pipeline running on across them (no prologue, no empty ring at a tile's
+// start).  Measured: with every expert holding tokens (B = 512, 32 per expert) two tiles gain 3-4 % (gate|up) and
+// 10 % (down); with the skewed routing of a deep random-weight stack (42 of 128 experts active at B = 512) the
+// fewer, longer blocks balance worse and lose 2-15 %.  One tile per block it stays.
+constexpr int TW_TILES_PER_BLOCK = 1;
 
 template <bool FUSED, bool SPLIT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
