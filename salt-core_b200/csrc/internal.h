@@ -113,8 +113,6 @@ struct TcMaps {
 cudaError_t make_tc_maps(TcMaps* out, const void* hi, const void* lo, int rows, int cols);
 // fused: gate/up + GeGLU -> out_h (+ out_l) [grouped rows][R] fp16; plain: -> out_f [grouped rows][R] fp32.
 // split: operands carried as hi + lo fp16 halves.  bmaps describes the activations (grouped order).
-// y_base / y_cols locate each job's first grouped row from its y pointer.  rows_total = grouped rows of the
-// call (tokens x top-k): with njobs_max it gives the mean group size that picks the token split of the grid.
 // Tiled maps over a layer's expert pool (packed nibbles) and its (scale << 16) | bias tables, one per tensor
 // of an expert slot (gate, up, down); tab_tma[k]: tensor k's table rows are a multiple of 16 bytes and come
 // by tiled copies (otherwise a row tile's table is copied whole).
@@ -131,9 +129,17 @@ struct TcWeightMaps {
 cudaError_t make_q4_tc_weight_maps(TcWeightMaps* out, const uint8_t* pool, size_t expert_stride, const uint32_t* tables,
                                    int hidden, int inter, int experts);
 bool q4_tc_supported(int hidden, int inter);
-cudaError_t launch_q4_gemm_tc(bool fused, bool split, const Q4Job* jobs, int njobs_max, const int* njobs_dev,
-                              const TcMaps& bmaps, const TcWeightMaps& wm, const float* y_base, int y_cols, void* out_h,
-                              void* out_l, float* out_f, int R, int rows_total, int* status, cudaStream_t stream);
+// Work lists of a layer's two tensor-core launches (written on the device from the grouped jobs): items_* hold
+// q4_tc_work_items_max() entries of 16 bytes each, work eight ints: {items, next, largest pass, -} of the fused
+// launch, then of the plain one.
+size_t q4_tc_work_items_max(int n_experts, int rows_total, int hidden, int inter);
+cudaError_t launch_q4_tc_work_list(const Q4Job* gateup_jobs, const int* njobs_dev, int njobs_max, const float* y_base,
+                                   int y_cols, const TcWeightMaps& wm, int hidden, int inter, void* items_fused,
+                                   void* items_plain, int* work, cudaStream_t stream);
+// items / work: this launch's list and its {items, next, largest pass} triple.  R, C: rows and columns of the weight matrices.
+cudaError_t launch_q4_gemm_tc(bool fused, bool split, const void* items, int* work, const TcMaps& bmaps,
+                              const TcWeightMaps& wm, void* out_h, void* out_l, float* out_f, int R, int C, int* status,
+                              cudaStream_t stream);
 
 // ---- bf16_kernels.cu ---------------------------------------------------------
 // y[r] = W[r][:] . x in the reference's eight-accumulator order; ys[t][r] in the serial column order

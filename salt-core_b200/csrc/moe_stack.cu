@@ -88,6 +88,8 @@ struct Stack {
     void *xh = nullptr, *xl = nullptr, *chain_h = nullptr, *chain_l = nullptr;   // fp16 operands (hi, lo) of the tensor-core path
     bool tc_ready = false;                     // tensor maps built (needs hidden, inter multiples of 64)
     TcMaps x_maps, chain_maps;                 // TMA descriptors of (xh, xl) and (chain_h, chain_l)
+    void *tc_items_fused = nullptr, *tc_items_plain = nullptr;   // work lists of the tensor-core launches (device-written)
+    int* tc_work = nullptr;                    // {items, next, largest pass, -} of the fused launch, then of the plain one
     // workspace of the whole feed-forward block (allocated by the first attach)
     float *norm_a = nullptr, *norm_b = nullptr, *dense_chain = nullptr, *dense_out = nullptr;
     float *routed_out = nullptr, *combine_scratch = nullptr;
@@ -146,6 +148,7 @@ static void free_stack(Stack* s) {
     cudaFree(s->fp4_ig_dn); cudaFree(s->fp4_packed); cudaFree(s->fp4_scales); cudaFree(s->fp4_gu_jobs); cudaFree(s->fp4_dn_jobs);
     cudaFree(s->fp4_tc_gu); cudaFree(s->fp4_tc_dn); cudaFree(s->fp4_live);
     cudaFree(s->xh); cudaFree(s->xl); cudaFree(s->chain_h); cudaFree(s->chain_l);
+    cudaFree(s->tc_items_fused); cudaFree(s->tc_items_plain); cudaFree(s->tc_work);
     if (s->h_in) cudaFreeHost(s->h_in);
     if (s->h_out) cudaFreeHost(s->h_out);
     for (auto e : s->ev) cudaEventDestroy(e);
@@ -208,6 +211,14 @@ int salt_b200_stack_create(int max_tokens, int hidden, int inter, int n_experts,
     if (!ok) {
         free_stack(s);
         return -1;
+    }
+    {
+        const size_t items = q4_tc_work_items_max(n_experts, (int)J, hidden, inter);
+        if (!dev_alloc((uint8_t**)&s->tc_items_fused, items * 16) || !dev_alloc((uint8_t**)&s->tc_items_plain, items * 16) ||
+            !dev_alloc(&s->tc_work, 8)) {
+            free_stack(s);
+            return -1;
+        }
     }
     s->tc_ready = q4_tc_supported(hidden, inter) && make_tc_maps(&s->x_maps, s->xh, s->xl, (int)J, hidden) == cudaSuccess &&
                   make_tc_maps(&s->chain_maps, s->chain_h, s->chain_l, (int)J, inter) == cudaSuccess;
@@ -535,20 +546,23 @@ static int experts_run(Stack* s, const Layer& l, const float* d_x, int B, int K,
         {
             Timed t(s, KC_ROUTER_INPUT, st);
             if (!cuda_ok(launch_gather_convert(d_x, s->g2c, s->xh, split ? s->xl : nullptr, jobs, K, H, st), "gather/convert")) return -1;
+            if (!cuda_ok(launch_q4_tc_work_list(s->gateup_jobs, s->counters, njobs_max, s->chain, M, l.q4_tc, H, M,
+                                                s->tc_items_fused, s->tc_items_plain, s->tc_work, st), "tc work list"))
+                return -1;
         }
         {
             Timed t(s, KC_GATE_UP, st);
-            if (!cuda_ok(launch_q4_gemm_tc(true, split, s->gateup_jobs, njobs_max, s->counters, s->x_maps, l.q4_tc, s->chain,
-                                           M, s->chain_h, s->chain_l, nullptr, M, jobs, s->status, st), "tc gate/up"))
+            if (!cuda_ok(launch_q4_gemm_tc(true, split, s->tc_items_fused, s->tc_work, s->x_maps, l.q4_tc, s->chain_h,
+                                           s->chain_l, nullptr, M, H, s->status, st), "tc gate/up"))
                 return -1;
         }
         {
             Timed t(s, KC_DOWN, st);
-            if (!cuda_ok(launch_q4_gemm_tc(false, split, s->down_jobs, njobs_max, s->counters, s->chain_maps, l.q4_tc,
-                                           s->grouped_out, H, nullptr, nullptr, s->grouped_out, H, jobs, s->status, st), "tc down"))
+            if (!cuda_ok(launch_q4_gemm_tc(false, split, s->tc_items_plain, s->tc_work + 4, s->chain_maps, l.q4_tc, nullptr,
+                                           nullptr, s->grouped_out, H, M, s->status, st), "tc down"))
                 return -1;
         }
-        count_launches(5);
+        count_launches(6);
         return 0;
     }
     {

@@ -66,6 +66,10 @@ constexpr int TC_PK_BYTES = 128 * TC_KC / 2; // packed chunk of 128 rows (one ma
 constexpr int TC_TAB_BYTES = 128 * 16;       // scale | bias words of 128 rows x 4 chunks
 constexpr int TC_MAX_NT = 128;
 constexpr int TC_MAX_SLOTS = 8;
+// Entries of the ring through which the producing thread passes work items to the other roles.  The producer is
+// at most TC_MAX_SLOTS chunks, i.e. at most TC_MAX_SLOTS units, ahead of the last completed MMA, and no role is more
+// than two units behind that, so 16 entries are never overrun and need no "free" barrier.
+constexpr int TC_ITEM_RING = 16;
 constexpr int TC_SMEM_BYTES = 225 * 1024;    // dynamic shared memory of every launch (one block per SM)
 
 // kind::f16 instruction descriptor: D = F32, A = B = F16, both K-major.
@@ -173,21 +177,25 @@ __device__ __forceinline__ void dequant_half_chunk_f32(const NibbleMagic& mg, co
     }
 }
 
+// One unit of work: one token pass (up to 128 tokens) of one row tile of one expert group.
+struct TcItem {
+    int expert;   // local expert = slice of the weight maps
+    int r0;       // first weight row of the tile (in each matrix)
+    int grow;     // first grouped row of the pass
+    int nt;       // tokens of the pass (1..128); 0 in a block's ring marks the end of the work
+};
+
 struct TcArgs {
-    const Q4Job* jobs;         // per expert group: weights (A = gate or the only matrix, B = up), R, C, ntok
-    const int* njobs_dev;
-    const float* y_base;       // base the jobs' y pointers are relative to (to recover the group's first row)
-    int y_cols;                // columns of that buffer (inter for gate/up, hidden for down)
+    const TcItem* items;       // the launch's work list (written on the device)
+    int* work;                 // [0] number of items, [1] next item to hand out, [2] most tokens of any item
+    int R, C;                  // rows and columns of the weight matrices of this launch
     __half* out_h;             // fused: GeGLU output [grouped rows][R] fp16, columns in operand K order
     __half* out_l;             // its fp16 residual (split precision) or null
     float* out_f;              // plain: projection output [grouped rows][R] fp32
     int* status;
-    const uint8_t* pool;       // the layer's expert slots (first local expert) and their stride
-    size_t expert_stride;
     const uint32_t* tables;    // (scale << 16) | bias words, [local expert][3 tensors][R * C/64]
     int tensor0;               // first tensor of the slot this launch reads (0: gate, then up; 2: down)
     int tab_tma;               // table rows are a multiple of 16 bytes: blocks of 4 groups come by tiled TMA
-    int tiles_per_block;       // consecutive row tiles one block walks (its pipeline runs on across them)
 };
 
 // Bounded wait for two barriers at once: both polls are in flight together, so the pair costs one
@@ -235,11 +243,6 @@ constexpr int TW_TAB_BYTES = TW_ROWS * 16;          // table block (4 chunks)
 constexpr int TW_B_BYTES = TW_ROWS * TC_KC * 2;     // converted chunk
 constexpr int TW_TOK_BYTES = TC_MAX_NT * TC_KC * 2; // token tile
 constexpr int TW_STAGES = 3;
-// Row tiles one block walks with its pipeline running on across them (no prologue, no empty ring at a tile's
-// start).  Measured: with every expert holding tokens (B = 512, 32 per expert) two tiles gain 3-4 % (gate|up) and
-// 10 % (down); with the skewed routing of a deep random-weight stack (42 of 128 experts active at B = 512) the
-// fewer, longer blocks balance worse and lose 2-15 %.  One tile per block it stays.
-constexpr int TW_TILES_PER_BLOCK = 1;
 
 template <bool FUSED, bool SPLIT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -253,36 +256,21 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
     __shared__ __align__(8) uint64_t bar_epi[2];              // ... and have been read (16 warp arrivals)
     __shared__ __align__(8) uint64_t bar_tab[2];              // a tile's whole scale table landed (untiled form)
     __shared__ __align__(8) uint64_t bar_tabfree[2];          // ... and its last conversion is over (16 warp arrivals)
+    // The block draws units from the launch's work list (one atomic per unit, by the producing thread, which
+    // passes the item to the other roles through a small ring).
+    __shared__ __align__(16) TcItem s_items[TC_ITEM_RING];
+    __shared__ __align__(8) uint64_t bar_item[TC_ITEM_RING];  // ring entry published
     __shared__ uint32_t s_tmem;
     __shared__ int s_fail;
 
     constexpr int NMAT = FUSED ? 2 : 1;
     constexpr int RT = TW_ROWS / NMAT;                        // weight rows of a tile, per matrix
-    const int job_id = blockIdx.y;
-    if (a.njobs_dev != nullptr && job_id >= *a.njobs_dev) return;
-    Q4Job jb = a.jobs[job_id];
-    const int x0 = (int)blockIdx.x * a.tiles_per_block;          // first row tile of this block
-    if (x0 * RT >= jb.R || jb.ntok < 1) return;
-    const int ntiles = min(a.tiles_per_block, (jb.R - x0 * RT + RT - 1) / RT);
-    int pass_shift = 0;
-    if (gridDim.z > 1) {
-        const int npass_all = (jb.ntok + TC_MAX_NT - 1) / TC_MAX_NT;
-        const int per = (npass_all + (int)gridDim.z - 1) / (int)gridDim.z;
-        pass_shift = (int)blockIdx.z * per * TC_MAX_NT;
-        if (pass_shift >= jb.ntok) return;
-        jb.ntok = min(per * TC_MAX_NT, jb.ntok - pass_shift);
-    }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int C = jb.C, nchunks = C / TC_KC;
-    const int g0 = (int)((jb.y - a.y_base) / a.y_cols) + pass_shift;   // first grouped row of this block's tokens
-    const int expert = (int)((size_t)(jb.vals - a.pool) / a.expert_stride);
+    const int C = a.C, nchunks = C / TC_KC;
     constexpr int NPART = SPLIT ? 2 : 1;                     // hi (+ lo) copies of every operand tile
     constexpr int STAGES = SPLIT ? 2 : TW_STAGES;
     constexpr int STAGE_BYTES = NPART * TW_B_BYTES;          // [hi][lo] converted chunks
     const bool tab_tma = a.tab_tma != 0;
-    const int ntok_cap = min(jb.ntok, TC_MAX_NT);
-    const int variant = ntok_cap <= 16 ? 0 : ntok_cap <= 32 ? 1 : ntok_cap <= 64 ? 2 : 3;
-    const uint32_t tok_bytes = (16u << variant) * 128u;
     // carve-up: converted stages | whole-tile table (untiled form) | input slots, each
     // [packed weights, 8 KB][table block, 4 KB (tiled form)][token tile(s): hi, lo]
     uint8_t* stage_base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -293,9 +281,12 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
     uint8_t* tabw = stage_base + STAGES * STAGE_BYTES;
     uint8_t* in_base = tabw + TABBUF * tabw_bytes;
     const uint32_t tok_off = TW_PK_BYTES + (tab_tma ? TW_TAB_BYTES : 0);
-    // The MMA always reads 128 token rows: rows above the copied box are stale bytes of the next slot (or of
-    // the pad behind the last one) and only reach accumulator lanes nobody reads.
-    const uint32_t tok_room = (tok_bytes + 1023u) & ~1023u;
+    // The MMA always reads 128 token rows: rows above the copied box (16, 32, 64 or 128 rows, by the pass' size)
+    // are stale bytes of the slot's other part, of the next slot or of the pad behind the last one, and only reach
+    // accumulator lanes nobody reads.
+    // room of a token tile: the TMA box (16, 32, 64 or 128 rows) that holds the launch's largest pass
+    const int nt_max = *(volatile const int*)&a.work[2];
+    const uint32_t tok_room = nt_max <= 16 ? 2048u : nt_max <= 32 ? 4096u : nt_max <= 64 ? 8192u : (uint32_t)TW_TOK_BYTES;
     const uint32_t slot_bytes = tok_off + NPART * tok_room;
     const int avail = TC_SMEM_BYTES - 1024 - STAGES * STAGE_BYTES - (int)(TABBUF * tabw_bytes) - (TW_TOK_BYTES - (int)tok_room);
     const uint32_t NQ = (uint32_t)min(TC_MAX_SLOTS, avail / (int)slot_bytes);
@@ -303,7 +294,6 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
         if (tid == 0 && a.status) atomicOr(a.status, SB_ERR_INDEX);
         return;
     }
-    const int npass = (jb.ntok + TC_MAX_NT - 1) / TC_MAX_NT;
     volatile int* fail = &s_fail;
 
     if (tid == 0) {
@@ -312,6 +302,7 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
             mbar_init(&bar_done[s], 1);
         }
         for (int s = 0; s < TW_STAGES; s++) mbar_init(&bar_full[s], TC_GROUP / 32);
+        for (int s = 0; s < TC_ITEM_RING; s++) mbar_init(&bar_item[s], 1);
         for (int s = 0; s < 2; s++) {
             mbar_init(&bar_acc[s], 1);
             mbar_init(&bar_epi[s], TC_CONVERTERS / 32);
@@ -346,15 +337,17 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
         const NibbleMagic mg = load_nibble_magic();
         uint32_t cs = 0, cq = 0, cq_ph = 0, dq = 0, dq_ph = 0;
         bool alive = true;
-        uint32_t unit = 0;
-        for (int tix = 0; tix < ntiles && alive && !*fail; tix++) {
-        const int r0 = (x0 + tix) * RT, rows_here = min(RT, jb.R - r0);   // rows_here: a multiple of 64
-        const uint32_t tbuf = (uint32_t)tix % TABBUF;
-        const uint8_t* tabt = tabw + tbuf * tabw_bytes;
-        if (!tab_tma) alive = __all_sync(0xffffffffu, mbar_wait(&bar_tab[tbuf], ((uint32_t)tix / TABBUF) & 1u, fail));
-        for (int pass = 0; pass < npass && alive && !*fail; pass++, unit++) {
-            const int tb = pass * TC_MAX_NT;
-            const int nt_real = min(TC_MAX_NT, jb.ntok - tb);
+        for (uint32_t unit = 0; alive && !*fail; unit++) {
+            alive = __all_sync(0xffffffffu, mbar_wait(&bar_item[unit % TC_ITEM_RING], (unit / TC_ITEM_RING) & 1u, fail));
+            if (!alive) break;
+            const TcItem item = s_items[unit % TC_ITEM_RING];
+            if (item.nt < 1) break;                                      // end of the work
+            const int r0 = item.r0, rows_here = min(RT, a.R - r0);      // rows_here: a multiple of 64
+            const int nt_real = item.nt;
+            const uint32_t tbuf = unit % TABBUF;
+            const uint8_t* tabt = tabw + tbuf * tabw_bytes;
+            if (!tab_tma) alive = __all_sync(0xffffffffu, mbar_wait(&bar_tab[tbuf], (unit / TABBUF) & 1u, fail));
+            if (!alive) break;
             for (int kc0 = 0; kc0 < nchunks; kc0 += 4) {
                 uint32_t tw[4];             // table words of this thread's row for four chunks
 #pragma unroll
@@ -409,7 +402,7 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
                 }
             }
             // ---- epilogue of this pass: warp w reads lane quarter w % 4 (tokens) and a quarter of the columns
-            if (!tab_tma && pass == npass - 1 && alive) {             // this tile's table is no longer read
+            if (!tab_tma && alive) {                                  // this unit's table is no longer read
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bar_tabfree[tbuf]);
             }
@@ -426,7 +419,7 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
                             tmem_ld32(trow + col, g);
                             tmem_ld32(trow + RT + col, u);
                             if (n < nt_real) {
-                                const size_t o_off = (size_t)(g0 + tb + n) * jb.R + r0 + col;
+                                const size_t o_off = (size_t)(item.grow + n) * a.R + r0 + col;
                                 __half* dst = a.out_h + o_off;
 #pragma unroll
                                 for (int i8 = 0; i8 < 32; i8 += 8) {
@@ -460,7 +453,7 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
                             uint32_t g[32];
                             tmem_ld32(trow + col, g);
                             if (n < nt_real) {
-                                float* dst = a.out_f + (size_t)(g0 + tb + n) * jb.R + r0 + col;
+                                float* dst = a.out_f + (size_t)(item.grow + n) * a.R + r0 + col;
 #pragma unroll
                                 for (int i = 0; i < 32; i += 4)
                                     *(float4*)(dst + i) = make_float4(__uint_as_float(g[i]), __uint_as_float(g[i + 1]),
@@ -474,18 +467,19 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
                 if (lane == 0) mbar_arrive(&bar_epi[unit & 1u]);
             }
         }
-        }
     } else if (warp == TC_ISSUER_WARP) {
         // ================= issuer (one thread) =================
         if (lane == 0) {
             const uint32_t w_lo0 = DESC_B_LO | ((smem_u32(stage_base) & 0x3ffffu) >> 4);
             const uint32_t t_lo0 = DESC_B_LO | ((smem_u32(in_base + tok_off) & 0x3ffffu) >> 4);
             uint32_t is = 0, is_ph = 0, iq = 0, iq_ph = 0;
-            uint32_t ready = 0, unit = 0;
+            uint32_t ready = 0;
             bool ok = true;
-            for (int tix = 0; tix < ntiles && ok && !*fail; tix++) {
-            const uint32_t idesc = umma_idesc_f16(128, FUSED ? TW_ROWS : min(RT, jb.R - (x0 + tix) * RT));
-            for (int pass = 0; pass < npass && ok && !*fail; pass++, unit++) {
+            for (uint32_t unit = 0; ok && !*fail; unit++) {
+                if (!mbar_wait(&bar_item[unit % TC_ITEM_RING], (unit / TC_ITEM_RING) & 1u, fail)) break;
+                const TcItem item = s_items[unit % TC_ITEM_RING];
+                if (item.nt < 1) break;                                  // end of the work
+                const uint32_t idesc = umma_idesc_f16(128, FUSED ? TW_ROWS : min(RT, a.R - item.r0));
                 // this unit's accumulator buffer was last used two units ago: those accumulators have been read
                 if (unit >= 2 && !mbar_wait(&bar_epi[unit & 1u], ((unit >> 1) - 1) & 1u, fail)) { ok = false; break; }
                 const uint32_t acc_base = tmem + (unit & 1u) * TW_ROWS;
@@ -533,31 +527,43 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
                     is = ns; is_ph = ns_ph; iq = nq; iq_ph = nq_ph;
                 }
             }
-            }
         }
     } else if (lane == 0) {
         // ================= producer (one thread) =================
         uint32_t pq = 0, pq_ph = 0;
         bool pok = true;
-        for (int tix = 0; tix < ntiles && pok && !*fail; tix++) {
-        const int r0 = (x0 + tix) * RT;
-        if (!tab_tma) {
-            // the tile's whole table, into the buffer whose previous tile has been converted to the end
-            const uint32_t tbuf = (uint32_t)tix % TABBUF, round = (uint32_t)tix / TABBUF;
-            if (round > 0 && !mbar_wait(&bar_tabfree[tbuf], (round - 1) & 1u, fail)) break;
-            const uint32_t bytes = (uint32_t)(min(RT, jb.R - r0) * nchunks * 4);
-            mbar_expect_tx(&bar_tab[tbuf], NMAT * bytes);
-            p_tabs++;
-#pragma unroll
-            for (int m = 0; m < NMAT; m++) {
-                const uint32_t* src = a.tables + ((size_t)(expert * 3 + a.tensor0 + m) * jb.R + r0) * nchunks;
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                                 smem_u32(tabw + tbuf * tabw_bytes + (size_t)m * RT * nchunks * 4)),
-                             "l"(src), "r"(bytes), "r"(smem_u32(&bar_tab[tbuf]))
-                             : "memory");
+        const int n_items = *(volatile const int*)&a.work[0];
+        for (uint32_t unit = 0; pok && !*fail; unit++) {
+            const int idx = atomicAdd(&a.work[1], 1);
+            TcItem item;
+            if (idx < n_items) {
+                const int4 v = *(const int4*)&a.items[idx];
+                item.expert = v.x; item.r0 = v.y; item.grow = v.z; item.nt = v.w;
+            } else {
+                item.expert = 0; item.r0 = 0; item.grow = 0; item.nt = 0;
             }
-        }
-        for (int pass = 0; pass < npass && pok && !*fail; pass++) {
+            s_items[unit % TC_ITEM_RING] = item;
+            mbar_arrive(&bar_item[unit % TC_ITEM_RING]);       // release: the entry is visible to who sees the phase
+            if (item.nt < 1) break;
+            const int r0 = item.r0, expert = item.expert;
+            const int variant = item.nt <= 16 ? 0 : item.nt <= 32 ? 1 : item.nt <= 64 ? 2 : 3;
+            const uint32_t tok_bytes = (16u << variant) * 128u;
+            if (!tab_tma) {
+                // the tile's whole table, into the buffer whose previous unit has been converted to the end
+                const uint32_t tbuf = unit % TABBUF, round = unit / TABBUF;
+                if (round > 0 && !mbar_wait(&bar_tabfree[tbuf], (round - 1) & 1u, fail)) break;
+                const uint32_t bytes = (uint32_t)(min(RT, a.R - r0) * nchunks * 4);
+                mbar_expect_tx(&bar_tab[tbuf], NMAT * bytes);
+                p_tabs++;
+#pragma unroll
+                for (int m = 0; m < NMAT; m++) {
+                    const uint32_t* src = a.tables + ((size_t)(expert * 3 + a.tensor0 + m) * a.R + r0) * nchunks;
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                     smem_u32(tabw + tbuf * tabw_bytes + (size_t)m * RT * nchunks * 4)),
+                                 "l"(src), "r"(bytes), "r"(smem_u32(&bar_tab[tbuf]))
+                                 : "memory");
+                }
+            }
             for (int kc = 0; kc < nchunks; kc++) {
                 // the slot's previous chunk has been consumed: its MMAs (which followed its conversion) are complete
                 if (p_issued >= NQ && !mbar_wait(&bar_done[pq], pq_ph ^ 1u, fail)) { pok = false; break; }
@@ -576,13 +582,11 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
                     tma_load_3d(dst, &wm.w256[2], kc * 32, r0, expert, &bar_in[pq]);
                     if (with_tab) tma_load_3d(dst + TW_PK_BYTES, &wm.t256[2], (kc & ~3) * 4, r0, expert, &bar_in[pq]);
                 }
-                tma_load_2d(dst + tok_off, &maps.hi[variant], kc * TC_KC, g0 + pass * TC_MAX_NT, &bar_in[pq]);
-                if (SPLIT)
-                    tma_load_2d(dst + tok_off + tok_room, &maps.lo[variant], kc * TC_KC, g0 + pass * TC_MAX_NT, &bar_in[pq]);
+                tma_load_2d(dst + tok_off, &maps.hi[variant], kc * TC_KC, item.grow, &bar_in[pq]);
+                if (SPLIT) tma_load_2d(dst + tok_off + tok_room, &maps.lo[variant], kc * TC_KC, item.grow, &bar_in[pq]);
                 p_issued++;
                 if (++pq == NQ) { pq = 0; pq_ph ^= 1u; }
             }
-        }
         }
     }
     if (*fail) {
@@ -777,29 +781,79 @@ static cudaError_t launch_tc(const TcArgs& a, const TcMaps& maps, const TcWeight
     return cudaGetLastError();
 }
 
-cudaError_t launch_q4_gemm_tc(bool fused, bool split, const Q4Job* jobs, int njobs_max, const int* njobs_dev,
-                              const TcMaps& bmaps, const TcWeightMaps& wm, const float* y_base, int y_cols, void* out_h,
-                              void* out_l, float* out_f, int R, int rows_total, int* status, cudaStream_t stream) {
+// Work lists of a layer's two launches: for every expert group with tokens, every 128-token pass, every row
+// tile one item (tiles of a pass adjacent, so neighbouring blocks share the pass' token rows in L2).  One block.
+__global__ void __launch_bounds__(256)
+q4_tc_work_list_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ njobs_dev, int njobs_max,
+                       const float* y_base, int y_cols, const uint8_t* pool, size_t expert_stride, int nx_fused,
+                       int nx_plain, TcItem* __restrict__ items_fused, TcItem* __restrict__ items_plain,
+                       int* __restrict__ work) {
+    extern __shared__ int s_base[];           // [njobs_max + 1] first pass of every job
+    const int njobs = njobs_dev ? min(*njobs_dev, njobs_max) : njobs_max;
+    for (int j = threadIdx.x; j < njobs_max; j += blockDim.x)
+        s_base[j + 1] = j < njobs && jobs[j].ntok > 0 ? (jobs[j].ntok + TC_MAX_NT - 1) / TC_MAX_NT : 0;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        s_base[0] = 0;
+        for (int j = 0; j < njobs_max; j++) s_base[j + 1] += s_base[j];
+        const int passes = s_base[njobs_max];
+        int nt_max = 0;
+        for (int j = 0; j < njobs; j++) nt_max = max(nt_max, min(jobs[j].ntok, TC_MAX_NT));
+        work[0] = passes * nx_fused; work[1] = 0; work[2] = nt_max;
+        work[4] = passes * nx_plain; work[5] = 0; work[6] = nt_max;
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < njobs; j += blockDim.x) {
+        const int np = s_base[j + 1] - s_base[j];
+        if (np < 1) continue;
+        const Q4Job jb = jobs[j];
+        const int expert = (int)((size_t)(jb.vals - pool) / expert_stride);
+        const int g0 = (int)((jb.y - y_base) / y_cols);
+        for (int p = 0; p < np; p++) {
+            const int nt = min(TC_MAX_NT, jb.ntok - p * TC_MAX_NT);
+            for (int x = 0; x < nx_fused; x++) {
+                TcItem it; it.expert = expert; it.r0 = x * (TW_ROWS / 2); it.grow = g0 + p * TC_MAX_NT; it.nt = nt;
+                items_fused[(size_t)(s_base[j] + p) * nx_fused + x] = it;
+            }
+            for (int x = 0; x < nx_plain; x++) {
+                TcItem it; it.expert = expert; it.r0 = x * TW_ROWS; it.grow = g0 + p * TC_MAX_NT; it.nt = nt;
+                items_plain[(size_t)(s_base[j] + p) * nx_plain + x] = it;
+            }
+        }
+    }
+}
+
+size_t q4_tc_work_items_max(int n_experts, int rows_total, int hidden, int inter) {
+    const size_t passes = (size_t)n_experts + (size_t)rows_total / TC_MAX_NT + 1;
+    return passes * (size_t)std::max((inter + 127) / 128, (hidden + TW_ROWS - 1) / TW_ROWS);
+}
+
+cudaError_t launch_q4_tc_work_list(const Q4Job* gateup_jobs, const int* njobs_dev, int njobs_max, const float* y_base,
+                                   int y_cols, const TcWeightMaps& wm, int hidden, int inter, void* items_fused,
+                                   void* items_plain, int* work, cudaStream_t stream) {
     if (njobs_max < 1) return cudaSuccess;
+    q4_tc_work_list_kernel<<<1, 256, (size_t)(njobs_max + 1) * sizeof(int), stream>>>(
+        gateup_jobs, njobs_dev, njobs_max, y_base, y_cols, wm.pool, wm.expert_stride, (inter + 127) / 128,
+        (hidden + TW_ROWS - 1) / TW_ROWS, (TcItem*)items_fused, (TcItem*)items_plain, work);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_q4_gemm_tc(bool fused, bool split, const void* items, int* work, const TcMaps& bmaps,
+                              const TcWeightMaps& wm, void* out_h, void* out_l, float* out_f, int R, int C, int* status,
+                              cudaStream_t stream) {
     TcArgs a;
-    a.jobs = jobs; a.njobs_dev = njobs_dev;
-    a.y_base = y_base; a.y_cols = y_cols;
+    a.items = (const TcItem*)items; a.work = work;
+    a.R = R; a.C = C;
     a.out_h = (__half*)out_h; a.out_l = (__half*)out_l; a.out_f = out_f; a.status = status;
-    a.pool = wm.pool; a.expert_stride = wm.expert_stride; a.tables = wm.tables;
+    a.tables = wm.tables;
     a.tensor0 = fused ? 0 : 2;
     a.tab_tma = wm.tab_tma[fused ? 0 : 2];
-    dim3 grid((R + 127) / 128, njobs_max, 1);
-    {
-        // Blocks per (row tile, expert) along the token passes: skewed routing leaves experts with several
-        // hundred tokens, whose 128-token passes would otherwise run one after the other on one SM.
-        const int avg = rows_total / njobs_max;
-        grid.z = fused ? (avg >= 96 ? 4u : (avg >= 24 ? 2u : 1u)) : 1u;
-    }
-    // 256 weight rows (128 of gate + 128 of up when fused) on the MMA's N side; a block walks tiles_per_block
-    // consecutive row tiles
-    const int nx = fused ? (R + 127) / 128 : (R + TW_ROWS - 1) / TW_ROWS;
-    a.tiles_per_block = std::min(nx, TW_TILES_PER_BLOCK);
-    grid.x = (nx + a.tiles_per_block - 1) / a.tiles_per_block;
+    int dev = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+    // one resident block per SM; each draws units (one token pass of one row tile) from the work list until it is empty
+    dim3 grid((unsigned)sms, 1, 1);
     if (fused)
         return split ? launch_tc<true, true>(a, bmaps, wm, grid, stream) : launch_tc<true, false>(a, bmaps, wm, grid, stream);
     return split ? launch_tc<false, true>(a, bmaps, wm, grid, stream) : launch_tc<false, false>(a, bmaps, wm, grid, stream);
