@@ -11,14 +11,20 @@
 //           each k-step issues Xh*Wh + Xh*Wl + Xl*Wh: operand error ~2^-22, three
 //           times the tensor work
 //
-// One block = one tile of weight rows of one expert group and a run of its 128-token passes.
+// A unit of work = one 128-token pass of one tile of weight rows of one expert group.  A small kernel writes
+// the layer's units into a work list from the grouped jobs (pass and tile counts are only known on the device);
+// one resident block per SM draws units from it with an atomic counter until it is empty, its pipeline (input
+// ring, converted stages, double-buffered accumulators) running on from one unit into the next.  Grids of one
+// block per tile paid for every block's launch with 225 KB of shared memory, for the empty blocks of experts
+// with fewer passes than the grid allowed, and for experts with several hundred tokens finishing last.
 // The tokens of a pass (up to 128, stale rows above them) are the MMA's M side, read from shared
 // memory as they arrive by TMA; 256 weight rows are the N side, dequantised into a K-major
 // 128-byte-swizzled shared-memory stage.  The 256 rows are one tile of the down matrix, or - fused -
 // 128 rows of gate followed by the same 128 rows of up: gate and up of a chunk are ONE instruction
 // (M128 x N256 x K16), and the GeGLU pairs accumulator column c with 128 + c.  Accumulators: lane =
 // token, column = weight row.  K advances in 64-column chunks = one quantisation group per row.
-//   producer thread   packed nibbles (tiled TMA over the expert pool: bytes x rows x experts),
+//   producer thread   draws the unit and passes it to the other roles through a shared-memory ring; packed
+//                     nibbles (tiled TMA over the expert pool: bytes x rows x experts),
 //                     the (scale << 16) | bias words of the rows (tiled TMA in blocks of four
 //                     chunks where a table row is a multiple of 16 bytes, otherwise one bulk copy
 //                     of the tile's whole table) and the tokens' fp16 activations (128-byte swizzle)
@@ -29,8 +35,9 @@
 //                     chunk's "done" barrier (frees the input slot and, some chunks later, the stage);
 //                     polls the next chunk's barriers before issuing, so the answer arrives behind
 //                     the MMAs
-//   epilogue          all converter warps tcgen05.ld the accumulators after a pass (warp w: lane
-//                     quarter w % 4, a quarter of the columns): GeGLU (fused gate/up) or plain store (down)
+//   epilogue          all converter warps tcgen05.ld the accumulators after a unit (warp w: lane
+//                     quarter w % 4, a quarter of the columns): GeGLU (fused gate/up) or plain store (down);
+//                     the issuer is already filling the other accumulator buffer
 // What was measured on the way here (B200, 1965 MHz): a register ring of global loads does not prefetch -
 // waiting for the oldest load also waits for the younger ones that share its scoreboard, so every chunk paid
 // a full memory latency (hence TMA); one mbarrier operation costs the issuing thread 100-190 cycles, so the
