@@ -438,7 +438,10 @@ int salt_b200_ffn_block_forward(void *stack, int layer, const float *d_residual,
  *                                          hi + lo fp16 halves: a TOLERANCE path for prefill-sized batches,
  *                                          max |err| / max(|ref|, row rms) <= 1e-3; router and reduce stay exact
  *   SALT_B200_EXPERTS_TENSOR_CORE_SINGLE  same with operands rounded to fp16 once (a third of the tensor work):
- *                                          max |err| <= 1e-3 of the row maximum, about 2e-3 of the row rms */
+ *                                          max |err| <= 1e-3 of the row maximum, about 2e-3 of the row rms
+ *                                          Both need hidden and inter to be multiples of 64; a size that is no
+ *                                          multiple of 256 must not exceed 960 (hi + lo) or 3520 (single).
+ *                                          Otherwise the call returns -1. */
 #define SALT_B200_EXPERTS_TENSOR_CORE 4
 #define SALT_B200_EXPERTS_TENSOR_CORE_SINGLE 8
 /*   SALT_B200_EXPERTS_TWO_LAUNCHES        run gate/up + GeGLU and down as two launches even where the

@@ -128,7 +128,9 @@ struct TcWeightMaps {
 };
 cudaError_t make_q4_tc_weight_maps(TcWeightMaps* out, const uint8_t* pool, size_t expert_stride, const uint32_t* tables,
                                    int hidden, int inter, int experts);
-bool q4_tc_supported(int hidden, int inter);
+// Can the tensor-core kernels take this geometry?  Sizes must be multiples of 64; a size that is no multiple of
+// 256 keeps a tile's scale table in shared memory and must not exceed 3520 (single) / 960 (hi + lo halves).
+bool q4_tc_supported(int hidden, int inter, bool split);
 // Work lists of a layer's two tensor-core launches (written on the device from the grouped jobs): items_* hold
 // q4_tc_work_items_max() entries of 16 bytes each, work eight ints: {items, next, largest pass, -} of the fused
 // launch, then of the plain one.

@@ -86,7 +86,8 @@ struct Stack {
     bool fp4_maps_ok = false;
     int fused_decode = 1;                      // 0: phase kernels; 1: one-launch expert kernel (B <= 4) and one launch per decode layer (B = 1); 2: all layers of a B = 1 pass in one launch (measured slower than 1)
     void *xh = nullptr, *xl = nullptr, *chain_h = nullptr, *chain_l = nullptr;   // fp16 operands (hi, lo) of the tensor-core path
-    bool tc_ready = false;                     // tensor maps built (needs hidden, inter multiples of 64)
+    bool tc_ready = false;                     // tensor maps built and the geometry fits the single-precision tensor-core kernel
+    bool tc_split_ready = false;               // ... and the hi + lo form
     TcMaps x_maps, chain_maps;                 // TMA descriptors of (xh, xl) and (chain_h, chain_l)
     void *tc_items_fused = nullptr, *tc_items_plain = nullptr;   // work lists of the tensor-core launches (device-written)
     int* tc_work = nullptr;                    // {items, next, largest pass, -} of the fused launch, then of the plain one
@@ -220,8 +221,9 @@ int salt_b200_stack_create(int max_tokens, int hidden, int inter, int n_experts,
             return -1;
         }
     }
-    s->tc_ready = q4_tc_supported(hidden, inter) && make_tc_maps(&s->x_maps, s->xh, s->xl, (int)J, hidden) == cudaSuccess &&
+    s->tc_ready = q4_tc_supported(hidden, inter, false) && make_tc_maps(&s->x_maps, s->xh, s->xl, (int)J, hidden) == cudaSuccess &&
                   make_tc_maps(&s->chain_maps, s->chain_h, s->chain_l, (int)J, inter) == cudaSuccess;
+    s->tc_split_ready = s->tc_ready && q4_tc_supported(hidden, inter, true);
     *stack_out = s;
     return 0;
 }
@@ -538,7 +540,7 @@ static int experts_run(Stack* s, const Layer& l, const float* d_x, int B, int K,
     const int tok_hint = B;
     if (flags & (SB_EXPERTS_TENSOR_CORE | SB_EXPERTS_TENSOR_CORE_SINGLE)) {
         const bool split = (flags & SB_EXPERTS_TENSOR_CORE) != 0;
-        if (!s->tc_ready || !l.q4_tc_ok) {
+        if (!s->tc_ready || !l.q4_tc_ok || (split && !s->tc_split_ready)) {
             fprintf(stderr, "salt_b200: tensor-core path unavailable for this geometry\n");
             return -1;
         }

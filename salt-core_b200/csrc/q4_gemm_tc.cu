@@ -203,6 +203,7 @@ struct TcArgs {
     const uint32_t* tables;    // (scale << 16) | bias words, [local expert][3 tensors][R * C/64]
     int tensor0;               // first tensor of the slot this launch reads (0: gate, then up; 2: down)
     int tab_tma;               // table rows are a multiple of 16 bytes: blocks of 4 groups come by tiled TMA
+    int tab_bufs;              // untiled form: buffers for a tile's whole table (2, or 1 where shared memory is short)
 };
 
 // Bounded wait for two barriers at once: both polls are in flight together, so the pair costs one
@@ -281,9 +282,9 @@ q4_gemm_tc_kernel(const TcArgs a, const __grid_constant__ TcMaps maps, const __g
     // carve-up: converted stages | whole-tile table (untiled form) | input slots, each
     // [packed weights, 8 KB][table block, 4 KB (tiled form)][token tile(s): hi, lo]
     uint8_t* stage_base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    // untiled tables: two buffers, so the next tile's table lands while this one is in use (split precision has
-    // room for one: the producer then waits for the tile's last conversion)
-    constexpr uint32_t TABBUF = SPLIT ? 1 : 2;
+    // untiled tables: two buffers, so the next unit's table lands while this one is in use - or one where two do
+    // not fit (the host decides): the producer then waits for the unit's last conversion
+    const uint32_t TABBUF = (uint32_t)a.tab_bufs;
     const uint32_t tabw_bytes = tab_tma ? 0u : (((uint32_t)(TW_ROWS * nchunks * 4) + 1023u) & ~1023u);
     uint8_t* tabw = stage_base + STAGES * STAGE_BYTES;
     uint8_t* in_base = tabw + TABBUF * tabw_bytes;
@@ -762,19 +763,22 @@ cudaError_t make_q4_tc_weight_maps(TcWeightMaps* out, const uint8_t* pool, size_
 
 // Does the kernel's shared-memory carve-up hold at least as many input slots as stages for a tensor with C
 // columns, in the widest token tile?  (The untiled table form keeps 256 rows x C/64 words resident.)
-static bool tc_geometry_ok(int C, bool split) {
+static bool tc_geometry_ok(int C, bool split, int tab_bufs) {
     const int npart = split ? 2 : 1, stages = split ? 2 : TW_STAGES;
     const bool tab_tma = (C % 256) == 0;
-    const int tabw = tab_tma ? 0 : (split ? 1 : 2) * ((TW_ROWS * (C / TC_KC) * 4 + 1023) & ~1023);
+    const int tabw = tab_tma ? 0 : tab_bufs * ((TW_ROWS * (C / TC_KC) * 4 + 1023) & ~1023);
     const int slot = TW_PK_BYTES + (tab_tma ? TW_TAB_BYTES : 0) + npart * TW_TOK_BYTES;
     const int avail = TC_SMEM_BYTES - 1024 - stages * npart * TW_B_BYTES - tabw;
     return avail / slot >= stages;
 }
+// Buffers for the untiled tables of a tensor with C columns: 2 where they fit, else 1, 0 if the plan does not hold at all.
+static int tc_table_buffers(int C, bool split) {
+    return tc_geometry_ok(C, split, 2) ? 2 : (tc_geometry_ok(C, split, 1) ? 1 : 0);
+}
 
-bool q4_tc_supported(int hidden, int inter) {
+bool q4_tc_supported(int hidden, int inter, bool split) {
     if (hidden < TC_KC || inter < TC_KC || (hidden % TC_KC) || (inter % TC_KC)) return false;
-    return tc_geometry_ok(hidden, false) && tc_geometry_ok(inter, false) &&
-           tc_geometry_ok(hidden, true) && tc_geometry_ok(inter, true);
+    return tc_table_buffers(hidden, split) > 0 && tc_table_buffers(inter, split) > 0;
 }
 
 template <bool FUSED, bool SPLIT>
@@ -855,6 +859,8 @@ cudaError_t launch_q4_gemm_tc(bool fused, bool split, const void* items, int* wo
     a.tables = wm.tables;
     a.tensor0 = fused ? 0 : 2;
     a.tab_tma = wm.tab_tma[fused ? 0 : 2];
+    a.tab_bufs = tc_table_buffers(C, split);
+    if (a.tab_bufs < 1) return cudaErrorInvalidValue;
     int dev = 0, sms = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

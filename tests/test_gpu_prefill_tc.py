@@ -61,3 +61,26 @@ def test_tensor_core_prefill_within_tolerance(orc, synth, geom):
     assert err1 <= TOL, err1
     assert st.status() == 0
     st.close()
+
+
+def test_tensor_core_prefill_one_table_buffer_and_refusal(orc, synth):
+    """hidden = 2112 is no multiple of 256: the gate/up tables of a tile stay in shared memory, where only one
+    buffer fits (33 chunks, an odd count); inter = 64 gives the down projection a single chunk per unit and
+    nine row tiles (8 x 256 + 64).  The hi + lo form does not fit this hidden size and must refuse the call."""
+    import torch
+    H, M, E, K, B = 2112, 64, 2, 1, 40
+    layer = synth.make_q4_moe_layer(91, hidden=H, inter=M, n_experts=E, topk=K)
+    x = synth.make_tokens(92, B, H)
+    st = stack_mod().MoeStack(B, H, M, E, K)
+    st.add_layer(layer)
+    d_x = torch.from_numpy(x).cuda()
+    assert st.layer_experts(0, d_x.data_ptr(), B, tensor_core="split") == -1
+    y1 = _run_tc_layer(st, x, B, H, "single")
+    want, sel, w = orc.moe_layer_q4(layer, x, threads=16)
+    ws = st.workspace()
+    assert_bits_equal(d2h(ws.selected, B * K, np.int32).reshape(B, K), sel, "selected (exact)")
+    err1 = _rel_err_rowmax(y1, want)
+    print(f"tensor-core prefill H={H} M={M}: single-pass fp16 {err1:.3e} of the row maximum")
+    assert err1 <= TOL, err1
+    assert st.status() == 0
+    st.close()
