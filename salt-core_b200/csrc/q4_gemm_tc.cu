@@ -799,36 +799,49 @@ q4_tc_work_list_kernel(const Q4Job* __restrict__ jobs, const int* __restrict__ n
                        const float* y_base, int y_cols, const uint8_t* pool, size_t expert_stride, int nx_fused,
                        int nx_plain, TcItem* __restrict__ items_fused, TcItem* __restrict__ items_plain,
                        int* __restrict__ work) {
-    extern __shared__ int s_base[];           // [njobs_max + 1] first pass of every job
+    extern __shared__ int s_list[];           // [njobs_max + 1] first pass of every job, then expert, first row, tokens
+    int* s_base = s_list;
+    int* s_expert = s_list + njobs_max + 1;
+    int* s_g0 = s_expert + njobs_max;
+    int* s_ntok = s_g0 + njobs_max;
+    __shared__ int s_nt_max;
     const int njobs = njobs_dev ? min(*njobs_dev, njobs_max) : njobs_max;
-    for (int j = threadIdx.x; j < njobs_max; j += blockDim.x)
-        s_base[j + 1] = j < njobs && jobs[j].ntok > 0 ? (jobs[j].ntok + TC_MAX_NT - 1) / TC_MAX_NT : 0;
+    if (threadIdx.x == 0) s_nt_max = 0;
+    __syncthreads();
+    for (int j = threadIdx.x; j < njobs_max; j += blockDim.x) {
+        int ntok = 0;
+        if (j < njobs) {
+            const Q4Job jb = jobs[j];
+            ntok = max(jb.ntok, 0);
+            s_expert[j] = (int)((size_t)(jb.vals - pool) / expert_stride);
+            s_g0[j] = (int)((jb.y - y_base) / y_cols);
+        }
+        s_ntok[j] = ntok;
+        s_base[j + 1] = (ntok + TC_MAX_NT - 1) / TC_MAX_NT;
+        if (ntok > 0) atomicMax(&s_nt_max, min(ntok, TC_MAX_NT));
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
         s_base[0] = 0;
         for (int j = 0; j < njobs_max; j++) s_base[j + 1] += s_base[j];
         const int passes = s_base[njobs_max];
-        int nt_max = 0;
-        for (int j = 0; j < njobs; j++) nt_max = max(nt_max, min(jobs[j].ntok, TC_MAX_NT));
-        work[0] = passes * nx_fused; work[1] = 0; work[2] = nt_max;
-        work[4] = passes * nx_plain; work[5] = 0; work[6] = nt_max;
+        work[0] = passes * nx_fused; work[1] = 0; work[2] = s_nt_max;
+        work[4] = passes * nx_plain; work[5] = 0; work[6] = s_nt_max;
     }
     __syncthreads();
-    for (int j = threadIdx.x; j < njobs; j += blockDim.x) {
-        const int np = s_base[j + 1] - s_base[j];
-        if (np < 1) continue;
-        const Q4Job jb = jobs[j];
-        const int expert = (int)((size_t)(jb.vals - pool) / expert_stride);
-        const int g0 = (int)((jb.y - y_base) / y_cols);
-        for (int p = 0; p < np; p++) {
-            const int nt = min(TC_MAX_NT, jb.ntok - p * TC_MAX_NT);
-            for (int x = 0; x < nx_fused; x++) {
-                TcItem it; it.expert = expert; it.r0 = x * (TW_ROWS / 2); it.grow = g0 + p * TC_MAX_NT; it.nt = nt;
-                items_fused[(size_t)(s_base[j] + p) * nx_fused + x] = it;
-            }
-            for (int x = 0; x < nx_plain; x++) {
-                TcItem it; it.expert = expert; it.r0 = x * TW_ROWS; it.grow = g0 + p * TC_MAX_NT; it.nt = nt;
-                items_plain[(size_t)(s_base[j] + p) * nx_plain + x] = it;
+    const int nxt = nx_fused + nx_plain;
+    for (int j = 0; j < njobs; j++) {
+        const int base = s_base[j], np = s_base[j + 1] - base;
+        for (int i = threadIdx.x; i < np * nxt; i += blockDim.x) {
+            const int p = i / nxt, x = i - p * nxt;
+            TcItem it;
+            it.expert = s_expert[j]; it.grow = s_g0[j] + p * TC_MAX_NT; it.nt = min(TC_MAX_NT, s_ntok[j] - p * TC_MAX_NT);
+            if (x < nx_fused) {
+                it.r0 = x * (TW_ROWS / 2);
+                items_fused[(size_t)(base + p) * nx_fused + x] = it;
+            } else {
+                it.r0 = (x - nx_fused) * TW_ROWS;
+                items_plain[(size_t)(base + p) * nx_plain + (x - nx_fused)] = it;
             }
         }
     }
@@ -843,7 +856,7 @@ cudaError_t launch_q4_tc_work_list(const Q4Job* gateup_jobs, const int* njobs_de
                                    int y_cols, const TcWeightMaps& wm, int hidden, int inter, void* items_fused,
                                    void* items_plain, int* work, cudaStream_t stream) {
     if (njobs_max < 1) return cudaSuccess;
-    q4_tc_work_list_kernel<<<1, 256, (size_t)(njobs_max + 1) * sizeof(int), stream>>>(
+    q4_tc_work_list_kernel<<<1, 256, (size_t)(4 * njobs_max + 1) * sizeof(int), stream>>>(
         gateup_jobs, njobs_dev, njobs_max, y_base, y_cols, wm.pool, wm.expert_stride, (inter + 127) / 128,
         (hidden + TW_ROWS - 1) / TW_ROWS, (TcItem*)items_fused, (TcItem*)items_plain, work);
     return cudaGetLastError();
